@@ -1,0 +1,62 @@
+// C ABI of the sm_100a kernel library. Every entry point takes raw device pointers and a stream,
+// returns 0 on success (negative: argument / launch error) and never allocates device memory
+// unless its comment says so. Kernels that can wait (mbarrier pipelines, peer signals) take a
+// `status` word in device memory: 0 = ok, otherwise one of the sx::ST_* codes.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// ------------------------------------------------------------------ G1 / G2 GEMM
+typedef struct SxGemmArgs {
+  const void* A;      // a_mn == 0: [M, K] row-major (lda);  a_mn == 1: [K, M] row-major (lda)
+  const void* B;      // b_mn == 0: [N, K] row-major (ldb);  b_mn == 1: [K, N] row-major (ldb)
+  void* D;            // [M, N] row-major (ldd), bf16 or fp32
+  const void* C;      // optional addend, same indexing as D (ldc), bf16 or fp32
+  const float* bias;  // optional [N]
+  int M, N, K, batch;
+  long long lda, ldb, ldd, ldc;
+  long long strideA, strideB, strideD, strideC;  // batch strides in elements (0: operand shared)
+  int a_mn, b_mn;
+  int out_fp32, c_fp32;
+  int act;  // 0 none, 1 gelu(tanh), 2 silu, 3 relu
+  float alpha, beta;
+  const int* tile_group;  // grouped GEMM: per 128-row block of A, index of the B matrix (-1 skips the block)
+  int num_groups;         // number of B matrices when tile_group is set
+  const int* k_ranges;    // per batch [k_begin, k_end) rows of the MN-major operands to reduce over
+  int k_total;            // total rows of the MN-major operands when k_ranges is set
+  int* status;
+  int sm_limit;  // cap on CTAs (0: one per SM)
+  int force_bn;  // 0 auto, 128 or 256
+} SxGemmArgs;
+int sx_gemm_bf16(const SxGemmArgs* args, cudaStream_t stream);
+
+// ------------------------------------------------------------------ A1 / A2 flash attention
+// Q [B, Sq, Hq, D], K [B, Skv, Hk, D], V [B, Skv, Hk / v_head_div, D], O [B, Sq, Hq, D]; bf16; each given as a
+// base pointer plus token (row) and batch strides in elements, so slices of a fused QKV buffer work in place.
+typedef struct SxAttnArgs {
+  const void* Q; const void* K; const void* V; void* O;
+  float* lse;              // [B, Hq, Sq] natural-log LSE (forward: out; backward: in)
+  const void* dO;          // backward only
+  void* dQ; void* dK; void* dV;  // backward outputs (bf16), same strides as Q / K / V
+  float* dq_accum;         // backward scratch: [B, Sq, Hq, D] fp32, zero-filled by the call
+  float* delta;            // backward scratch: [B, Hq, Sq] fp32
+  long long q_row_stride, k_row_stride, v_row_stride, o_row_stride;
+  long long q_batch_stride, k_batch_stride, v_batch_stride;
+  long long do_row_stride, dq_row_stride, dk_row_stride, dv_row_stride;
+  long long dq_batch_stride, dk_batch_stride, dv_batch_stride;
+  int B, Sq, Skv, Hq, Hk, D;
+  int v_head_div;          // 1; 2 for differential attention (two score heads share a V head)
+  int causal, window;
+  float scale;
+  int* status;
+} SxAttnArgs;
+int sx_attn_fwd(const SxAttnArgs* args, cudaStream_t stream);
+int sx_attn_bwd(const SxAttnArgs* args, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,201 @@
+"""G1/G2 GEMM front-end: shape checks, allocation and the autograd ``Linear`` function.
+
+CUDA bf16 tensors go to the tcgen05 kernel (``csrc/gemm_tc.cu``); anything else (CPU tensors, the
+fp32 oracle in tests) takes the plain PyTorch path with identical semantics. The counterpart in the
+reference is ``sneppx_gemm_fused`` / ``sneppx_cuda_gemm_bwd`` (kernel/cuda/tensor_cuda.cu:497-558,
+kernel/cuda/autodiff_cuda.cu:28-171).
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+
+ACT = {None: 0, "none": 0, "gelu": 1, "silu": 2, "relu": 3}
+
+
+def _act_ref(x, act):
+    if act in (None, "none", 0):
+        return x
+    if act in ("gelu", 1):
+        return torch.nn.functional.gelu(x, approximate="tanh")
+    if act in ("silu", 2):
+        return torch.nn.functional.silu(x)
+    return torch.relu(x)
+
+
+def gemm_reference(a, b, *, a_mn=False, b_mn=False, c=None, beta=0.0, alpha=1.0, bias=None, act=None,
+                   out_dtype=None, tile_group=None, k_ranges=None):
+    """fp32 PyTorch statement of what the kernel computes (also the CPU path)."""
+    out_dtype = out_dtype or a.dtype
+    A = a.float().transpose(-1, -2) if a_mn else a.float()
+    Bm = b.float() if b_mn else b.float().transpose(-1, -2)  # [K, N]
+    if tile_group is not None:
+        M = A.shape[0]
+        d = torch.zeros(M, Bm.shape[-1], dtype=torch.float32, device=a.device)
+        tg = tile_group.tolist()
+        for blk, g in enumerate(tg):
+            if g < 0:
+                continue
+            r0, r1 = blk * 128, min((blk + 1) * 128, M)
+            d[r0:r1] = A[r0:r1] @ Bm[g]
+    elif k_ranges is not None:
+        kr = k_ranges.view(-1, 2).tolist()
+        d = torch.stack([A[:, k0:k1] @ Bm[k0:k1] for (k0, k1) in kr])
+    else:
+        d = A @ Bm
+    d = d * alpha
+    if bias is not None:
+        d = d + bias.float()
+    if c is not None and beta != 0.0:
+        d = d + beta * c.float()
+    return _act_ref(d, act).to(out_dtype)
+
+
+def _use_kernel(*ts) -> bool:
+    t = ts[0]
+    return t.is_cuda and all(x is None or (x.is_cuda) for x in ts) and t.dtype == torch.bfloat16 and _lib.available()
+
+
+def gemm(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=None, c=None, beta=0.0, alpha=1.0, bias=None,
+         act=None, tile_group=None, k_ranges=None, sm_limit=0, force_bn=0):
+    """D = act(alpha * A @ B^T + bias + beta * C).
+
+    a: [.., M, K] (or [.., K, M] when ``a_mn``); b: [.., N, K] (or [.., K, N] when ``b_mn``).
+    ``tile_group`` (int32 [ceil(M/128)]): grouped GEMM, b is [G, N, K]; block i of a multiplies b[tile_group[i]].
+    ``k_ranges`` (int32 [G, 2]): a and b are MN-major with shared rows; batch g reduces rows [k0, k1) -> out [G, M, N].
+    """
+    if not _use_kernel(a, b, c, bias):
+        r = gemm_reference(a, b, a_mn=a_mn, b_mn=b_mn, c=c, beta=beta, alpha=alpha, bias=bias, act=act,
+                           out_dtype=out_dtype or (out.dtype if out is not None else None),
+                           tile_group=tile_group, k_ranges=k_ranges)
+        if out is not None:
+            out.copy_(r)
+            return out
+        return r
+
+    assert b.dtype == torch.bfloat16
+    # Resolve operand storage into (matrix dims, leading dim, batch stride).
+    def prep(t, mn_major):
+        if t.stride(-1) != 1 or (t.dim() == 3 and t.stride(1) < t.shape[2]):
+            t = t.contiguous()
+        rows, cols = t.shape[-2], t.shape[-1]
+        ext_mn, ext_k = (cols, rows) if mn_major else (rows, cols)
+        ld = t.stride(-2)
+        bs = t.stride(0) if t.dim() == 3 else 0
+        return t, ext_mn, ext_k, ld, bs
+
+    if a_mn and a.shape[-1] % 64 != 0:
+        a, a_mn = a.transpose(-1, -2).contiguous(), False
+    if b_mn and b.shape[-1] % 64 != 0:
+        b, b_mn = b.transpose(-1, -2).contiguous(), False
+    a, M, K, lda, sA = prep(a, a_mn)
+    b, N, Kb, ldb, sB = prep(b, b_mn)
+    assert K == Kb, f"reduction mismatch {K} vs {Kb}"
+    if K % 8 != 0 or lda % 8 != 0 or ldb % 8 != 0:
+        r = gemm_reference(a, b, a_mn=a_mn, b_mn=b_mn, c=c, beta=beta, alpha=alpha, bias=bias, act=act,
+                           out_dtype=out_dtype, tile_group=tile_group, k_ranges=k_ranges)
+        if out is not None:
+            out.copy_(r)
+            return out
+        return r
+    batch = 1
+    k_total = 0
+    if k_ranges is not None:
+        batch = k_ranges.numel() // 2
+        k_total = K
+        sA = sB = 0
+    elif tile_group is not None:
+        assert b.dim() == 3
+        batch = 1
+    else:
+        if a.dim() == 3:
+            batch = a.shape[0]
+        if b.dim() == 3:
+            batch = max(batch, b.shape[0])
+    odt = out_dtype or (out.dtype if out is not None else torch.bfloat16)
+    if out is None:
+        shape = (batch, M, N) if (batch > 1 or a.dim() == 3 or (b.dim() == 3 and tile_group is None) or
+                                  k_ranges is not None) else (M, N)
+        out = torch.empty(shape, dtype=odt, device=a.device)
+    assert out.stride(-1) == 1
+    ldd = out.stride(-2)
+    sD = out.stride(0) if out.dim() == 3 else 0
+    args = _lib.SxGemmArgs()
+    args.A, args.B, args.D = a.data_ptr(), b.data_ptr(), out.data_ptr()
+    args.C = c.data_ptr() if (c is not None and beta != 0.0) else None
+    args.bias = bias.float().data_ptr() if bias is not None else None
+    if bias is not None:
+        _keep = bias.float()
+        args.bias = _keep.data_ptr()
+    args.M, args.N, args.K, args.batch = M, N, K, batch
+    args.lda, args.ldb, args.ldd = lda, ldb, ldd
+    args.ldc = c.stride(-2) if c is not None else 0
+    args.strideA, args.strideB, args.strideD = sA, sB, sD
+    args.strideC = (c.stride(0) if (c is not None and c.dim() == 3) else 0)
+    args.a_mn, args.b_mn = int(a_mn), int(b_mn)
+    args.out_fp32 = int(out.dtype == torch.float32)
+    args.c_fp32 = int(c is not None and c.dtype == torch.float32)
+    args.act = ACT[act] if not isinstance(act, int) else act
+    args.alpha, args.beta = float(alpha), float(beta)
+    if tile_group is not None:
+        args.tile_group = tile_group.data_ptr()
+        args.num_groups = b.shape[0]
+        args.strideB = b.stride(0)
+    if k_ranges is not None:
+        args.k_ranges = k_ranges.data_ptr()
+        args.k_total = k_total
+    args.status = _lib.status_word(a.device).data_ptr()
+    args.sm_limit = sm_limit
+    args.force_bn = force_bn
+    _lib.call("sx_gemm_bf16", C.byref(args), _lib.stream())
+    return out
+
+
+class _LinearFn(torch.autograd.Function):
+    """y = x W^T (+ b). Backward runs dgrad and wgrad on the same kernel with MN-major operands;
+    when the weight carries ``main_grad`` (a view into a flat gradient buffer) wgrad accumulates
+    into it in place and ``.grad`` stays empty."""
+
+    @staticmethod
+    def forward(ctx, x, w, bias, act):
+        x2 = x.reshape(-1, x.shape[-1])
+        y = gemm(x2, w, bias=bias, act=act)
+        ctx.save_for_backward(x2, w)
+        ctx.has_bias = bias is not None
+        ctx.act = act
+        ctx.xshape = x.shape
+        assert act in (None, "none"), "fused activation is inference-only; training applies it separately"
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, w, b_mn=True).view(ctx.xshape)
+        if ctx.needs_input_grad[1]:
+            mg = getattr(w, "main_grad", None)
+            if mg is not None:
+                first = not getattr(w, "_main_grad_written", False)
+                gemm(dy2, x2, a_mn=True, b_mn=True, out=mg, c=None if first else mg, beta=0.0 if first else 1.0)
+                w._main_grad_written = True
+                dw = None
+            else:
+                dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=w.dtype)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dy2.float().sum(0).to(dy.dtype)
+        return dx, dw, db, None
+
+
+def linear(x, w, bias=None, act=None):
+    if torch.is_grad_enabled() and (x.requires_grad or w.requires_grad):
+        return _LinearFn.apply(x, w, bias, None) if act in (None, "none") else _act_ref(
+            _LinearFn.apply(x, w, bias, None), act)
+    x2 = x.reshape(-1, x.shape[-1])
+    return gemm(x2, w, bias=bias, act=act).view(*x.shape[:-1], w.shape[0])

@@ -1,0 +1,83 @@
+"""tcgen05 GEMM (G1/G2) against an fp32 PyTorch reference of the same op."""
+import pytest
+import torch
+
+from sneppx_alg_b200 import ops
+from sneppx_alg_b200.ops.gemm import gemm, gemm_reference
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+    return (a.float() - b.float()).abs().max().item() / (b.float().abs().max().item() + 1e-6)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (300, 200, 136), (4096, 1024, 512), (64, 128, 4096)])
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+def test_gemm_layouts(M, N, K, a_mn, b_mn):
+    torch.manual_seed(0)
+    if (a_mn and M % 64) or (b_mn and N % 64):
+        pytest.skip("MN-major operands need a multiple of 64")
+    a = torch.randn((K, M) if a_mn else (M, K), device="cuda", dtype=torch.bfloat16)
+    b = torch.randn((K, N) if b_mn else (N, K), device="cuda", dtype=torch.bfloat16)
+    d = gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+    ref = gemm_reference(a, b, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32)
+    ops.check_status()
+    assert _rel(d, ref) < 1e-2
+
+
+def test_gemm_epilogue_bias_beta_act_fp32out():
+    torch.manual_seed(1)
+    M, N, K = 384, 320, 192
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    c = torch.randn(M, N, device="cuda", dtype=torch.float32)
+    bias = torch.randn(N, device="cuda", dtype=torch.float32)
+    d = gemm(a, b, c=c, beta=0.5, alpha=0.25, bias=bias, act="gelu", out_dtype=torch.float32)
+    ref = gemm_reference(a, b, c=c, beta=0.5, alpha=0.25, bias=bias, act="gelu", out_dtype=torch.float32)
+    ops.check_status()
+    assert _rel(d, ref) < 1e-2
+
+
+def test_gemm_batched():
+    torch.manual_seed(2)
+    a = torch.randn(3, 256, 128, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(3, 192, 128, device="cuda", dtype=torch.bfloat16)
+    d = gemm(a, b)
+    ref = torch.matmul(a.float(), b.float().transpose(1, 2))
+    ops.check_status()
+    assert d.shape == (3, 256, 192) and _rel(d, ref) < 1e-2
+
+
+def test_gemm_grouped_forward_and_wgrad():
+    torch.manual_seed(3)
+    E, K, N = 4, 256, 384
+    counts = [128, 0, 256, 128]
+    tile_group = torch.tensor([0, 2, 2, 3], dtype=torch.int32, device="cuda")
+    a = torch.randn(sum(counts), K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(E, N, K, device="cuda", dtype=torch.bfloat16)
+    d = gemm(a, w, tile_group=tile_group)
+    ref = gemm_reference(a, w, tile_group=tile_group, out_dtype=torch.float32)
+    assert _rel(d, ref) < 1e-2
+    # per-expert wgrad: dW[e] = dY_e^T X_e over the expert's row range
+    dy = torch.randn(sum(counts), N, device="cuda", dtype=torch.bfloat16)
+    kr = torch.tensor([[0, 128], [128, 128], [128, 384], [384, 512]], dtype=torch.int32, device="cuda")
+    dw = gemm(dy, a, a_mn=True, b_mn=True, k_ranges=kr, out_dtype=torch.float32)
+    refw = gemm_reference(dy, a, a_mn=True, b_mn=True, k_ranges=kr, out_dtype=torch.float32)
+    ops.check_status()
+    assert dw.shape == (E, N, K) and _rel(dw, refw) < 1e-2
+
+
+def test_linear_autograd_matches_torch():
+    torch.manual_seed(4)
+    x = torch.randn(2, 192, 256, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = torch.randn(320, 256, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    y = ops.linear(x, w)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_(True)
+    wr = w.detach().float().requires_grad_(True)
+    yr = torch.nn.functional.linear(xr, wr)
+    yr.backward(g.float())
+    ops.check_status()
+    assert _rel(y, yr) < 1e-2 and _rel(x.grad, xr.grad) < 1e-2 and _rel(w.grad, wr.grad) < 1e-2
