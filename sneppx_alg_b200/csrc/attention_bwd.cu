@@ -23,7 +23,7 @@ namespace sx {
 constexpr int BWD_KV = 128;
 constexpr int BWD_Q = 64;
 constexpr int BWD_D = 128;
-constexpr int BWD_THREADS = 192;
+constexpr int BWD_THREADS = 320;  // TMA warp, MMA warp, 2 x 4 softmax-gradient warps (each group owns 32 query columns)
 
 struct AttnBwdParams {
   CUtensorMap tmQ, tmK, tmV, tmdO;
@@ -69,7 +69,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_kernel(const __grid_c
   uint64_t* qdo_empty = bars + 3;    // [2]
   uint64_t* s_full = bars + 5;       // 1
   uint64_t* dp_full = bars + 6;      // 1
-  uint64_t* pds_ready = bars + 7;    // 1 (4 arrivals)
+  uint64_t* pds_ready = bars + 7;    // 1 (8 arrivals)
   uint64_t* dq_full = bars + 8;      // 1
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
   volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -101,7 +101,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_kernel(const __grid_c
     }
     mbar_init(s_full, 1);
     mbar_init(dp_full, 1);
-    mbar_init(pds_ready, 4);
+    mbar_init(pds_ready, 8);
     mbar_init(dq_full, 1);
     *s_abort = 0;
     mbar_fence_init();
@@ -198,57 +198,50 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_kernel(const __grid_c
     }
   } else {
     // ------------------------------------------------------------ softmax-gradient warps
+    const int wg = (warp - 2) >> 2;     // column group: query columns [32*wg, 32*wg + 32) of the tile
     const int qd = warp & 3;
-    const int r = qd * 32 + lane;      // key row inside the tile == TMEM lane
+    const int r = qd * 32 + lane;       // key row inside the tile == TMEM lane
     const int kv_idx = kv0 + r;
+    const int c0 = wg * 32;
     const uint32_t lane_addr = static_cast<uint32_t>(qd * 32) << 16;
     bool ok = n_it > 0;
     auto drain_dq = [&](int it) {
       // dQ^T tile: lane = head-dim index, column = query row; one coalesced fp32 reduction per column
       const int head = kv_head * G + it / n_qt;
-      const int qrow0 = (qt_lo + it % n_qt) * BWD_Q;
+      const int qrow0 = (qt_lo + it % n_qt) * BWD_Q + c0;
       float* base = p.dq_accum + (((long long)b * p.Sq + qrow0) * p.Hq + head) * BWD_D + r;
-#pragma unroll 1
-      for (int c = 0; c < BWD_Q / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld32(tmem_base + Cfg::TM_DQ + lane_addr + c * 32, v);
-        tmem_ld_wait();
+      uint32_t v[32];
+      tmem_ld32(tmem_base + Cfg::TM_DQ + lane_addr + c0, v);
+      tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int qi = qrow0 + c * 32 + i;
-          if (qi < p.Sq) atomicAdd(base + (long long)(c * 32 + i) * p.Hq * BWD_D, __uint_as_float(v[i]));
-        }
+      for (int i = 0; i < 32; ++i) {
+        if (qrow0 + i < p.Sq) atomicAdd(base + (long long)i * p.Hq * BWD_D, __uint_as_float(v[i]));
       }
     };
     for (int it = 0; it < n_it && ok; ++it) {
       const int head = kv_head * G + it / n_qt;
       const int qrow0 = (qt_lo + it % n_qt) * BWD_Q;
-      // lane i keeps LSE / delta of query columns i and i + 32; columns are broadcast by shuffle
-      float lse_r[2], dl_r[2];
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        const int qi = qrow0 + c * 32 + lane;
-        const long long o = ((long long)b * p.Hq + head) * p.Sq + qi;
-        lse_r[c] = qi < p.Sq ? p.lse[o] * 1.4426950408889634f : INFINITY;
-        dl_r[c] = qi < p.Sq ? p.delta[o] : 0.f;
-      }
+      // lane i keeps LSE / delta of query column c0 + i; columns are broadcast by shuffle
+      const int qi_l = qrow0 + c0 + lane;
+      const long long so = ((long long)b * p.Hq + head) * p.Sq + qi_l;
+      const float lse_r = qi_l < p.Sq ? p.lse[so] * 1.4426950408889634f : INFINITY;
+      const float dl_r = qi_l < p.Sq ? p.delta[so] : 0.f;
       const bool need_mask = (p.causal && kv0 + BWD_KV - 1 > qrow0 + offset) || (kv0 + BWD_KV > p.Skv) ||
                              (p.window > 0 && kv0 < qrow0 + BWD_Q - 1 + offset - p.window + 1);
-      uint32_t pt[BWD_Q / 2];
-      uint32_t ds[BWD_Q / 2];
+      uint32_t pt[16];
+      uint32_t ds[16];
       if (!mbar_wait_warp(s_full, it & 1, s_abort, p.status, ST_TIMEOUT_EPILOGUE)) { ok = false; break; }
       tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < BWD_Q / 32; ++c) {
+      {
         uint32_t v[32];
-        tmem_ld32(tmem_base + Cfg::TM_S + lane_addr + c * 32, v);
+        tmem_ld32(tmem_base + Cfg::TM_S + lane_addr + c0, v);
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float p0 = exp2f(__uint_as_float(v[i]) * p.scale_log2 - __shfl_sync(0xffffffffu, lse_r[c], i));
-          float p1 = exp2f(__uint_as_float(v[i + 1]) * p.scale_log2 - __shfl_sync(0xffffffffu, lse_r[c], i + 1));
+          float p0 = exp2f(__uint_as_float(v[i]) * p.scale_log2 - __shfl_sync(0xffffffffu, lse_r, i));
+          float p1 = exp2f(__uint_as_float(v[i + 1]) * p.scale_log2 - __shfl_sync(0xffffffffu, lse_r, i + 1));
           if (need_mask) {
-            const int q0i = qrow0 + c * 32 + i + offset;
+            const int q0i = qrow0 + c0 + i + offset;
             if (kv_idx > q0i && p.causal) p0 = 0.f;
             if (kv_idx > q0i + 1 && p.causal) p1 = 0.f;
             if (p.window > 0) {
@@ -257,23 +250,21 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_kernel(const __grid_c
             }
             if (kv_idx >= p.Skv) { p0 = 0.f; p1 = 0.f; }
           }
-          pt[c * 16 + i / 2] = pack_bf16x2(p0, p1);
+          pt[i / 2] = pack_bf16x2(p0, p1);
         }
       }
       if (!mbar_wait_warp(dp_full, it & 1, s_abort, p.status, ST_TIMEOUT_EPILOGUE)) { ok = false; break; }
       tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < BWD_Q / 32; ++c) {
+      {
         uint32_t v[32];
-        tmem_ld32(tmem_base + Cfg::TM_DP + lane_addr + c * 32, v);
+        tmem_ld32(tmem_base + Cfg::TM_DP + lane_addr + c0, v);
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const __nv_bfloat162 pb = *reinterpret_cast<const __nv_bfloat162*>(&pt[c * 16 + i / 2]);
-          const float d0 = __low2float(pb) * (__uint_as_float(v[i]) - __shfl_sync(0xffffffffu, dl_r[c], i)) * p.scale;
-          const float d1 =
-              __high2float(pb) * (__uint_as_float(v[i + 1]) - __shfl_sync(0xffffffffu, dl_r[c], i + 1)) * p.scale;
-          ds[c * 16 + i / 2] = pack_bf16x2(d0, d1);
+          const float pl = __uint_as_float(pt[i / 2] << 16), ph = __uint_as_float(pt[i / 2] & 0xffff0000u);
+          const float d0 = pl * (__uint_as_float(v[i]) - __shfl_sync(0xffffffffu, dl_r, i)) * p.scale;
+          const float d1 = ph * (__uint_as_float(v[i + 1]) - __shfl_sync(0xffffffffu, dl_r, i + 1)) * p.scale;
+          ds[i / 2] = pack_bf16x2(d0, d1);
         }
       }
       // the P^T / dS^T tiles and the dQ^T accumulator are free once iteration it-1 has fully executed
@@ -283,10 +274,11 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_kernel(const __grid_c
         drain_dq(it - 1);
       }
 #pragma unroll
-      for (int cc = 0; cc < 8; ++cc) {
+      for (int k = 0; k < 4; ++k) {
+        const int cc = wg * 4 + k;
         const int off = r * 128 + ((cc ^ (r & 7)) << 4);
-        *reinterpret_cast<uint4*>(sPT + off) = make_uint4(pt[cc * 4], pt[cc * 4 + 1], pt[cc * 4 + 2], pt[cc * 4 + 3]);
-        *reinterpret_cast<uint4*>(sDST + off) = make_uint4(ds[cc * 4], ds[cc * 4 + 1], ds[cc * 4 + 2], ds[cc * 4 + 3]);
+        *reinterpret_cast<uint4*>(sPT + off) = make_uint4(pt[k * 4], pt[k * 4 + 1], pt[k * 4 + 2], pt[k * 4 + 3]);
+        *reinterpret_cast<uint4*>(sDST + off) = make_uint4(ds[k * 4], ds[k * 4 + 1], ds[k * 4 + 2], ds[k * 4 + 3]);
       }
       fence_proxy_async_smem();
       tc_fence_before();
@@ -304,7 +296,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_kernel(const __grid_c
         __nv_bfloat16* dvr = p.dV + (long long)b * p.dv_batch_stride + (long long)kv_idx * p.dv_row_stride +
                              (long long)kv_head * BWD_D;
 #pragma unroll 1
-        for (int which = 0; which < 2; ++which) {
+        for (int which = wg; which <= wg; ++which) {  // group 0 stores dV, group 1 stores dK
           const uint32_t src = tmem_base + (which ? Cfg::TM_DK : Cfg::TM_DV) + lane_addr;
           __nv_bfloat16* dst = which ? dkr : dvr;
 #pragma unroll 1

@@ -1,14 +1,17 @@
 // A1: flash attention forward on tcgen05 (sm_100a).
 //
-// One CTA owns 128 query rows of one (batch, head). Per 128-row KV tile:
-//   S = Q K^T        tcgen05.mma SS, fp32 in TMEM (two S buffers so QK^T of tile j+1 overlaps softmax j)
-//   P = exp2(S - m)  four softmax warps, one query row per thread (TMEM lane == row, no shuffles);
-//                    P is written as bf16 into a 128B-swizzled smem tile
-//   O += P V         tcgen05.mma SS with V consumed MN-major straight from its [kv, d] layout
-// The running max is only refreshed when it grew by more than 2^8 (the stale max keeps every
-// exponent bounded), which makes the O rescale in TMEM rare. Causal / sliding-window masks, GQA
-// head mapping and the differential-attention V mapping (two score heads share one V head) are
-// index arithmetic in the kernel; nothing is materialised.
+// One CTA owns 256 query rows of one (batch, head) as two 128-row tiles X in {A, B}, each served
+// by its own softmax warpgroup, and walks the visible 128-row KV tiles:
+//   S_X = Q_X K^T       tcgen05.mma SS, fp32 in TMEM
+//   P_X = exp2(S_X - m) one query row per thread (TMEM lane == row, no shuffles); P is written back
+//                       as packed bf16 over the S columns it came from
+//   O_X += P_X V        tcgen05.mma TS: P straight from TMEM, V consumed MN-major from its [kv, d] tile
+// The MMA warp ping-pongs the two tiles (PV(A,j), QK(A,j+1), PV(B,j), QK(B,j+1), ...), so the tensor
+// pipe works on one tile while the other tile's warpgroup does its softmax. tcgen05.mma executes in
+// issue order, which is what makes the S/P aliasing safe. The running max is only refreshed when
+// it grew by more than 2^8, so rescaling O in TMEM is rare. Causal / sliding-window masks, GQA head
+// mapping and the differential-attention V mapping (two score heads share one V head) are index
+// arithmetic; nothing is materialised.
 // Takes the place of the reference's SIMT flash-attention forward, GQA and block-sparse kernels
 // (kernel/cuda/attention_cuda.cu:37-328, 498-573, 1154-1230) and its empty "v3" kernel (:1262-1286).
 #include <limits.h>
@@ -18,10 +21,9 @@
 
 namespace sx {
 
-constexpr int ATT_BM = 128;
+constexpr int ATT_BM = 128;   // rows per q tile (two per CTA)
 constexpr int ATT_BN = 128;
-constexpr int ATT_THREADS = 192;
-constexpr int KV_STAGES = 2;
+constexpr int ATT_THREADS = 320;  // TMA warp, MMA warp, 2 x 4 softmax warps
 
 struct AttnFwdParams {
   CUtensorMap tmQ, tmK, tmV;
@@ -37,16 +39,31 @@ struct AttnFwdParams {
 
 template <int D>
 struct AttnCfg {
-  static constexpr int Q_BYTES = ATT_BM * D * 2;
+  static constexpr int Q_BYTES = ATT_BM * D * 2;   // one q tile
   static constexpr int KV_BYTES = ATT_BN * D * 2;
-  static constexpr int P_BYTES = ATT_BM * ATT_BN * 2;
-  static constexpr int OFF_K = Q_BYTES;
-  static constexpr int OFF_V = OFF_K + KV_STAGES * KV_BYTES;
-  static constexpr int OFF_P = OFF_V + KV_STAGES * KV_BYTES;
-  static constexpr int OFF_BAR = OFF_P + P_BYTES;
+  static constexpr int OFF_K = 2 * Q_BYTES;
+  static constexpr int OFF_V = OFF_K + 2 * KV_BYTES;
+  static constexpr int OFF_BAR = OFF_V + 2 * KV_BYTES;
   static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
-  static constexpr int TMEM_COLS = 512;  // S0 | S1 | O (128 + 128 + D columns used)
+  static constexpr int TMEM_COLS = 512;  // per tile: S/P at +0 (128 cols), O at +128; tile B at +256
 };
+
+// Visible KV tile range [lo, hi) of a 128-row q tile starting at q0.
+__device__ __forceinline__ void kv_range(const AttnFwdParams& p, int q0, int& lo, int& hi) {
+  const int offset = p.Skv - p.Sq;
+  lo = 0;
+  hi = (p.Skv + ATT_BN - 1) / ATT_BN;
+  if (q0 >= p.Sq) { hi = 0; return; }
+  if (p.causal) {
+    const int last = q0 + ATT_BM - 1 + offset;
+    hi = last < 0 ? 0 : min(hi, last / ATT_BN + 1);
+  }
+  if (p.window > 0) {
+    const int first = q0 + offset - p.window + 1;
+    if (first > 0) lo = first / ATT_BN;
+  }
+  if (hi < lo) hi = lo;
+}
 
 template <int D>
 __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
@@ -56,41 +73,35 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
   uint8_t* sQ = smem;
   uint8_t* sK = smem + Cfg::OFF_K;
   uint8_t* sV = smem + Cfg::OFF_V;
-  uint8_t* sP = smem + Cfg::OFF_P;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
   uint64_t* q_full = bars;            // 1
   uint64_t* k_full = bars + 1;        // [2]
   uint64_t* k_empty = bars + 3;       // [2]
   uint64_t* v_full = bars + 5;        // [2]
   uint64_t* v_empty = bars + 7;       // [2]
-  uint64_t* s_full = bars + 9;        // [2]
-  uint64_t* s_empty = bars + 11;      // [2]
-  uint64_t* p_full = bars + 13;       // 1
-  uint64_t* o_done = bars + 14;       // 1
+  uint64_t* s_full = bars + 9;        // [2 tiles]
+  uint64_t* p_full = bars + 11;       // [2 tiles]
+  uint64_t* o_done = bars + 13;       // [2 tiles]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // heavy (late) query tiles first: better tail behaviour under the causal mask
-  const int q_tile = gridDim.x - 1 - blockIdx.x;
+  const int pair = gridDim.x - 1 - blockIdx.x;
   const int head = blockIdx.y, b = blockIdx.z;
   const int kv_head = head / (p.Hq / p.Hk);
   const int v_head = kv_head / p.v_head_div;
-  const int q0 = q_tile * ATT_BM;
-  const int offset = p.Skv - p.Sq;  // query i sees keys <= i + offset under the causal mask
+  const int q0 = pair * 2 * ATT_BM;
 
-  int tile_lo = 0;
-  int tile_hi = (p.Skv + ATT_BN - 1) / ATT_BN;  // exclusive
-  if (p.causal) {
-    const int last = q0 + ATT_BM - 1 + offset;
-    tile_hi = min(tile_hi, last / ATT_BN + 1);
-    if (last < 0) tile_hi = 0;
-  }
-  if (p.window > 0) {
-    const int first = q0 + offset - p.window + 1;
-    if (first > 0) tile_lo = first / ATT_BN;
-  }
-  const int n_tiles = max(tile_hi - tile_lo, 0);
+  int lo[2], hi[2];
+  kv_range(p, q0, lo[0], hi[0]);
+  kv_range(p, q0 + ATT_BM, lo[1], hi[1]);
+  // union range walked by the loaders; tile X takes part in step j when lo[X] <= j < hi[X]
+  int jlo = INT_MAX, jhi = 0;
+#pragma unroll
+  for (int x = 0; x < 2; ++x)
+    if (hi[x] > lo[x]) { jlo = min(jlo, lo[x]); jhi = max(jhi, hi[x]); }
+  const int n_steps = jhi > jlo ? jhi - jlo : 0;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -100,10 +111,9 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
       mbar_init(&v_full[i], 1);
       mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_empty[i], 4);
+      mbar_init(&p_full[i], 4);
+      mbar_init(&o_done[i], 1);
     }
-    mbar_init(p_full, 4);
-    mbar_init(o_done, 1);
     *s_abort = 0;
     mbar_fence_init();
     tma_prefetch_desc(&p.tmQ);
@@ -115,8 +125,6 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_S0 = tmem_base;           // S buffers at columns 0 and 128
-  const uint32_t tmem_O = tmem_base + 256;
 
   auto tma5 = [](void* dst, const CUtensorMap* m, uint64_t* bar, int c1, int c3, int c4) {
     asm volatile(
@@ -127,13 +135,15 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
   };
 
   if (warp == 0) {
-    if (lane == 0 && n_tiles > 0) {
-      mbar_expect_tx(q_full, Cfg::Q_BYTES);
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0 && n_steps > 0) {
+      mbar_expect_tx(q_full, 2 * Cfg::Q_BYTES);
       tma5(sQ, &p.tmQ, q_full, q0, head, b);
-      for (int j = 0; j < n_tiles; ++j) {
+      tma5(sQ + Cfg::Q_BYTES, &p.tmQ, q_full, q0 + ATT_BM, head, b);
+      for (int j = 0; j < n_steps; ++j) {
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
-        const int kv0 = (tile_lo + j) * ATT_BN;
+        const int kv0 = (jlo + j) * ATT_BN;
         if (!mbar_wait(&k_empty[s], ph ^ 1, s_abort, p.status, ST_TIMEOUT_PRODUCER)) break;
         mbar_expect_tx(&k_full[s], Cfg::KV_BYTES);
         tma5(sK + s * Cfg::KV_BYTES, &p.tmK, &k_full[s], kv0, kv_head, b);
@@ -143,173 +153,158 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
       }
     }
   } else if (warp == 1) {
-    if (lane == 0 && n_tiles > 0) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0 && n_steps > 0) {
       constexpr uint32_t idesc_qk = umma_idesc_f16(ATT_BM, ATT_BN, 1, 0, 0);
       constexpr uint32_t idesc_pv = umma_idesc_f16(ATT_BM, D, 1, 0, 1);
-      auto issue_qk = [&](int j) {
-        const uint32_t a0 = smem_u32(sQ), b0 = smem_u32(sK + (j & 1) * Cfg::KV_BYTES);
-        const uint32_t d = tmem_S0 + (j & 1) * ATT_BN;
+      auto active = [&](int x, int j) { return jlo + j >= lo[x] && jlo + j < hi[x]; };
+      auto issue_qk = [&](int x, int j) {
+        const uint32_t a0 = smem_u32(sQ + x * Cfg::Q_BYTES), b0 = smem_u32(sK + (j & 1) * Cfg::KV_BYTES);
+        const uint32_t d = tmem_base + x * 256;
 #pragma unroll
         for (int c = 0; c < D / 64; ++c)
 #pragma unroll
           for (int k = 0; k < 4; ++k)
             umma_f16_ss(d, umma_desc_sw128(a0 + c * (ATT_BM * 128) + k * 32, 16, 1024),
                         umma_desc_sw128(b0 + c * (ATT_BN * 128) + k * 32, 16, 1024), idesc_qk, (c | k) ? 1u : 0u);
-        umma_commit(&k_empty[j & 1]);
-        umma_commit(&s_full[j & 1]);
+        umma_commit(&s_full[x]);
       };
+      // number of steps each tile has taken part in so far (gives barrier parities and accumulate flags)
+      int cnt[2] = {0, 0};
       bool ok = mbar_wait(q_full, 0, s_abort, p.status, ST_TIMEOUT_MMA);
       if (ok) ok = mbar_wait(&k_full[0], 0, s_abort, p.status, ST_TIMEOUT_MMA);
       if (ok) {
         tc_fence_after();
-        issue_qk(0);
+        for (int x = 0; x < 2; ++x)
+          if (active(x, 0)) issue_qk(x, 0);
+        umma_commit(&k_empty[0]);
       }
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        if (j + 1 < n_tiles) {
-          const int jn = j + 1;
-          if (!mbar_wait(&k_full[jn & 1], (jn >> 1) & 1, s_abort, p.status, ST_TIMEOUT_MMA)) { ok = false; break; }
-          if (!mbar_wait(&s_empty[jn & 1], ((jn >> 1) & 1) ^ 1, s_abort, p.status, ST_TIMEOUT_MMA)) { ok = false; break; }
-          tc_fence_after();
-          issue_qk(jn);
-        }
-        if (!mbar_wait(p_full, j & 1, s_abort, p.status, ST_TIMEOUT_MMA)) { ok = false; break; }
+      for (int j = 0; j < n_steps && ok; ++j) {
+        const bool more = j + 1 < n_steps;
         if (!mbar_wait(&v_full[j & 1], (j >> 1) & 1, s_abort, p.status, ST_TIMEOUT_MMA)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t a0 = smem_u32(sP), b0 = smem_u32(sV + (j & 1) * Cfg::KV_BYTES);
+        if (more && !mbar_wait(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, s_abort, p.status, ST_TIMEOUT_MMA)) {
+          ok = false;
+          break;
+        }
+        for (int x = 0; x < 2 && ok; ++x) {
+          if (active(x, j)) {
+            if (!mbar_wait(&p_full[x], cnt[x] & 1, s_abort, p.status, ST_TIMEOUT_MMA)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t b0 = smem_u32(sV + (j & 1) * Cfg::KV_BYTES);
+            const uint32_t dO = tmem_base + x * 256 + 128, aP = tmem_base + x * 256;
 #pragma unroll
-        for (int c = 0; c < 2; ++c)
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma_f16_ss(tmem_O, umma_desc_sw128(a0 + c * (ATT_BM * 128) + k * 32, 16, 1024),
-                        umma_desc_sw128(b0 + (c * 4 + k) * 2048, ATT_BN * 128, 1024), idesc_pv,
-                        (j | c | k) ? 1u : 0u);
+            for (int k = 0; k < 8; ++k)
+              umma_f16_ts(dO, aP + k * 8, umma_desc_sw128(b0 + k * 2048, ATT_BN * 128, 1024), idesc_pv,
+                          (cnt[x] | k) ? 1u : 0u);
+            ++cnt[x];
+            if (!(more && active(x, j + 1))) umma_commit(&o_done[x]);  // last step of this tile
+          }
+          if (more && active(x, j + 1)) issue_qk(x, j + 1);
+        }
         umma_commit(&v_empty[j & 1]);
-        umma_commit(o_done);
+        if (more) umma_commit(&k_empty[(j + 1) & 1]);
       }
     }
   } else {
-    // ------------------------------------------------------------ softmax / correction / epilogue
-    const int qd = warp & 3;
-    const int row = qd * 32 + lane;           // row inside the tile == TMEM lane
-    const int q_idx = q0 + row;
+    // ------------------------------------------------------------ softmax warpgroups
+    const int x = (warp - 2) >> 2;          // which q tile
+    const int qd = warp & 3;                // TMEM lane quadrant of this warp
+    const int row = qd * 32 + lane;         // row inside the tile == TMEM lane
+    const int q_idx = q0 + x * ATT_BM + row;
+    const int offset = p.Skv - p.Sq;
     const uint32_t lane_addr = static_cast<uint32_t>(qd * 32) << 16;
+    const uint32_t tS = tmem_base + x * 256 + lane_addr;
+    const uint32_t tO = tS + 128;
+    const int n_mine = hi[x] - lo[x];
     float m_used = -INFINITY;  // running (possibly stale) max, log2 domain
     float l = 0.f;
-    bool ok = n_tiles > 0;
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      const int kv0 = (tile_lo + j) * ATT_BN;
-      if (!mbar_wait_warp(&s_full[j & 1], (j >> 1) & 1, s_abort, p.status, ST_TIMEOUT_EPILOGUE)) { ok = false; break; }
+    bool ok = true;
+    int hi_k = p.Skv - 1;  // last visible key index for this row
+    if (p.causal) hi_k = min(hi_k, q_idx + offset);
+    const int lo_k = p.window > 0 ? q_idx + offset - p.window + 1 : INT_MIN;
+    for (int j = 0; j < n_mine && ok; ++j) {
+      const int kv0 = (lo[x] + j) * ATT_BN;
+      if (!mbar_wait_warp(&s_full[x], j & 1, s_abort, p.status, ST_TIMEOUT_EPILOGUE)) { ok = false; break; }
       tc_fence_after();
-      const uint32_t s_addr = tmem_S0 + (j & 1) * ATT_BN + lane_addr;
-      const bool need_mask = (p.causal && kv0 + ATT_BN - 1 > q0 + offset) || (kv0 + ATT_BN > p.Skv) ||
-                             (p.window > 0 && kv0 < q0 + ATT_BM - 1 + offset - p.window + 1);
-      int hi = p.Skv - 1;  // last visible key index for this row
-      if (p.causal) hi = min(hi, q_idx + offset);
-      const int lo = p.window > 0 ? q_idx + offset - p.window + 1 : INT_MIN;
-      // pass 1: row max
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < ATT_BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(s_addr + c * 32, r);
-        tmem_ld_wait();
+      const int qt0 = q0 + x * ATT_BM;
+      const bool need_mask = (p.causal && kv0 + ATT_BN - 1 > qt0 + offset) || (kv0 + ATT_BN > p.Skv) ||
+                             (p.window > 0 && kv0 < qt0 + ATT_BM - 1 + offset - p.window + 1);
+      uint32_t r[ATT_BN];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float v = __uint_as_float(r[i]);
-          if (need_mask) {
-            const int kv = kv0 + c * 32 + i;
-            if (kv > hi || kv < lo) v = -INFINITY;
-          }
-          mx = fmaxf(mx, v);
+      for (int c = 0; c < ATT_BN / 32; ++c) tmem_ld32(tS + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[c * 32]));
+      tmem_ld_wait();
+      float mx = -INFINITY;
+      if (need_mask) {
+#pragma unroll
+        for (int i = 0; i < ATT_BN; ++i) {
+          const int kv = kv0 + i;
+          if (kv > hi_k || kv < lo_k) r[i] = 0xff800000u;  // -inf
+          mx = fmaxf(mx, __uint_as_float(r[i]));
         }
+      } else {
+#pragma unroll
+        for (int i = 0; i < ATT_BN; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
       }
       mx *= p.scale_log2;
       float alpha = 1.f;
       bool rescale = false;
-      if (mx > m_used + 8.f || m_used == -INFINITY) {
-        if (mx != -INFINITY) {
-          alpha = (m_used == -INFINITY) ? 0.f : exp2f(m_used - mx);
-          rescale = (m_used != -INFINITY);
-          m_used = mx;
-        }
+      if ((mx > m_used + 8.f || m_used == -INFINITY) && mx != -INFINITY) {
+        alpha = (m_used == -INFINITY) ? 0.f : exp2f(m_used - mx);
+        rescale = (m_used != -INFINITY);
+        m_used = mx;
       }
       l *= alpha;
       const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
-      // pass 2: probabilities, packed to bf16 in registers
-      uint32_t pk[ATT_BN / 2];
+      float lsum = 0.f;
 #pragma unroll
-      for (int c = 0; c < ATT_BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld32(s_addr + c * 32, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float v0 = exp2f(__uint_as_float(r[i]) * p.scale_log2 - m_sub);
-          float v1 = exp2f(__uint_as_float(r[i + 1]) * p.scale_log2 - m_sub);
-          if (need_mask) {
-            const int kv = kv0 + c * 32 + i;
-            if (kv > hi || kv < lo) v0 = 0.f;
-            if (kv + 1 > hi || kv + 1 < lo) v1 = 0.f;
-          }
-          const uint32_t pb = pack_bf16x2(v0, v1);
-          pk[c * 16 + i / 2] = pb;
-          // accumulate the row sum from the rounded values so that l matches what P V sees
-          const __nv_bfloat162 pv = *reinterpret_cast<const __nv_bfloat162*>(&pb);
-          l += __low2float(pv) + __high2float(pv);
-        }
+      for (int i = 0; i < ATT_BN; i += 2) {
+        const float v0 = exp2f(fmaf(__uint_as_float(r[i]), p.scale_log2, -m_sub));
+        const float v1 = exp2f(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, -m_sub));
+        const uint32_t pb = pack_bf16x2(v0, v1);
+        r[i / 2] = pb;
+        // row sum from the rounded values so that l matches what P V sees
+        lsum += __uint_as_float(pb << 16) + __uint_as_float(pb & 0xffff0000u);
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_empty[j & 1]);
-      // P buffer and O are free once P V of the previous tile has completed
-      if (j > 0) {
-        if (!mbar_wait_warp(o_done, (j - 1) & 1, s_abort, p.status, ST_TIMEOUT_EPILOGUE)) { ok = false; break; }
-        tc_fence_after();
-        if (__any_sync(0xffffffffu, rescale)) {
+      l += lsum;
+      // s_full(j) was committed after P V of step j-1 (in-order pipe), so O and the S/P columns are ours
+      if (j > 0 && __any_sync(0xffffffffu, rescale)) {
 #pragma unroll 1
-          for (int c = 0; c < D / 32; ++c) {
-            uint32_t r[32];
-            tmem_ld32(tmem_O + lane_addr + c * 32, r);
-            tmem_ld_wait();
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld32(tO + c * 32, o);
+          tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st32(tmem_O + lane_addr + c * 32, r);
-          }
-          tmem_st_wait();
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st32(tO + c * 32, o);
         }
       }
-      // write P (row-major [128 x 128] bf16) as two 128B-swizzled K-major tiles
-#pragma unroll
-      for (int ch = 0; ch < 16; ++ch) {
-        const int tile = ch >> 3, cc = ch & 7;
-        uint4 val = make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
-        *reinterpret_cast<uint4*>(sP + tile * (ATT_BM * 128) + row * 128 + ((cc ^ (row & 7)) << 4)) = val;
-      }
-      fence_proxy_async_smem();
+      tmem_st32(tS, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+      tmem_st32(tS + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+      tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_full);
+      if (lane == 0) mbar_arrive(&p_full[x]);
     }
-    if (ok && n_tiles > 0) {
-      if (mbar_wait_warp(o_done, (n_tiles - 1) & 1, s_abort, p.status, ST_TIMEOUT_EPILOGUE)) {
+    if (ok && n_mine > 0) {
+      if (mbar_wait_warp(&o_done[x], 0, s_abort, p.status, ST_TIMEOUT_EPILOGUE)) {
         tc_fence_after();
         const float inv_l = l > 0.f ? 1.f / l : 0.f;
         const bool row_ok = q_idx < p.Sq;
         __nv_bfloat16* orow = p.O + ((long long)b * p.Sq + q_idx) * p.o_row_stride + (long long)head * D;
 #pragma unroll 1
         for (int c = 0; c < D / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld32(tmem_O + lane_addr + c * 32, r);
+          uint32_t o[32];
+          tmem_ld32(tO + c * 32, o);
           tmem_ld_wait();
           if (row_ok) {
 #pragma unroll
             for (int i = 0; i < 32; i += 8) {
-              uint4 o;
-              o.x = pack_bf16x2(__uint_as_float(r[i]) * inv_l, __uint_as_float(r[i + 1]) * inv_l);
-              o.y = pack_bf16x2(__uint_as_float(r[i + 2]) * inv_l, __uint_as_float(r[i + 3]) * inv_l);
-              o.z = pack_bf16x2(__uint_as_float(r[i + 4]) * inv_l, __uint_as_float(r[i + 5]) * inv_l);
-              o.w = pack_bf16x2(__uint_as_float(r[i + 6]) * inv_l, __uint_as_float(r[i + 7]) * inv_l);
-              *reinterpret_cast<uint4*>(orow + c * 32 + i) = o;
+              uint4 w;
+              w.x = pack_bf16x2(__uint_as_float(o[i]) * inv_l, __uint_as_float(o[i + 1]) * inv_l);
+              w.y = pack_bf16x2(__uint_as_float(o[i + 2]) * inv_l, __uint_as_float(o[i + 3]) * inv_l);
+              w.z = pack_bf16x2(__uint_as_float(o[i + 4]) * inv_l, __uint_as_float(o[i + 5]) * inv_l);
+              w.w = pack_bf16x2(__uint_as_float(o[i + 6]) * inv_l, __uint_as_float(o[i + 7]) * inv_l);
+              *reinterpret_cast<uint4*>(orow + c * 32 + i) = w;
             }
           }
         }
@@ -317,8 +312,8 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
           p.lse[((long long)b * p.Hq + head) * p.Sq + q_idx] =
               (l > 0.f) ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
       }
-    } else if (n_tiles == 0) {
-      // no visible keys: zero output
+    } else if (n_mine <= 0) {
+      // no visible keys for this tile: zero output
       if (q_idx < p.Sq) {
         __nv_bfloat16* orow = p.O + ((long long)b * p.Sq + q_idx) * p.o_row_stride + (long long)head * D;
         for (int i = 0; i < D; i += 8) *reinterpret_cast<uint4*>(orow + i) = make_uint4(0, 0, 0, 0);
@@ -369,7 +364,7 @@ extern "C" int sx_attn_fwd(const SxAttnArgs* a, cudaStream_t st) {
   p.v_head_div = a->v_head_div > 0 ? a->v_head_div : 1;
   p.causal = a->causal; p.window = a->window;
   p.scale_log2 = a->scale * 1.4426950408889634f;
-  dim3 grid((a->Sq + ATT_BM - 1) / ATT_BM, a->Hq, a->B);
+  dim3 grid((a->Sq + 2 * ATT_BM - 1) / (2 * ATT_BM), a->Hq, a->B);
   if (a->D == 128) {
     static bool set = false;
     if (!set) {
