@@ -57,6 +57,60 @@ typedef struct SxAttnArgs {
 int sx_attn_fwd(const SxAttnArgs* args, cudaStream_t stream);
 int sx_attn_bwd(const SxAttnArgs* args, cudaStream_t stream);
 
+// ------------------------------------------------------------------ fused collectives over symmetric memory
+// Peer tables hold, for every rank of the group, the peer-mapped address of the same symmetric allocation.
+// `pad` is the group's signal pad (uint32 words, zero-initialised once). Every wait inside these kernels is
+// bounded by timeout_ns and reports through `status`.
+typedef struct SxPeers {
+  void* buf[8];
+  void* pad[8];
+  int rank, world;
+  unsigned long long timeout_ns;
+} SxPeers;
+
+// Barrier across the group on `channel` (epoch must increase by one per call on that channel).
+int sx_peer_barrier(const SxPeers* peers, int channel, unsigned epoch, int* status, cudaStream_t stream);
+
+// F1, ZeRO gradient reduce-scatter fused with the partitioned optimizer.
+//   peers->buf[r]  : rank r's flat bf16 gradient buffer (all ranks hold the full bucket)
+//   elem_offset/n  : this rank's shard of the bucket, in elements (n % 8 == 0, offset % 8 == 0)
+//   mode 1 (reduce): reduced = (sum_r grad_r) / world -> `reduced` (fp32, local, indexed from 0), per-CTA
+//                    sum-of-squares partials -> sumsq_partials[0..grid) ; waits for every rank's `ready_epoch`
+//                    on channel `ready_channel` first (peers signal it when their bucket is complete).
+//   mode 2 (update): exchanges this rank's total sum of squares with all peers (channel norm_channel), derives the
+//                    clip coefficient from the global norm, runs AdamW on (p32, m, v) with `reduced` and writes
+//                    the bf16 shard to p16_out; ends with a barrier on channel done_channel.
+//   mode 3 (fused) : no clipping: reduce + AdamW in one pass, nothing stored in between; same start / end barriers.
+typedef struct SxZeroArgs {
+  SxPeers peers;
+  long long elem_offset, n;
+  float* reduced;            // fp32 [n] (modes 1, 2)
+  float* sumsq_partials;     // fp32 [num_partials] (mode 1 writes `grid` entries at partial_offset; mode 2 reads all)
+  int partial_offset, num_partials;
+  float* p32; float* m; float* v; void* p16_out;
+  float lr, beta1, beta2, eps, wd; int step;
+  float max_norm;            // <= 0: no clipping
+  float* norm_out;           // [3] {sum of squares, norm, coefficient}
+  int ready_channel; unsigned ready_epoch;
+  int norm_channel; unsigned norm_epoch;
+  int done_channel; unsigned done_epoch;
+  int mode;
+  int grid;                  // CTAs to use (0: default)
+  int* status;
+} SxZeroArgs;
+int sx_zero_grid_default(void);
+int sx_zero_step(const SxZeroArgs* args, cudaStream_t stream);
+// Tell all peers that this rank's bucket is complete (one tiny launch on the stream that produced the gradients).
+int sx_signal_peers(const SxPeers* peers, int channel, unsigned epoch, cudaStream_t stream);
+
+// F2 (copy form): pull every rank's shard [n elements of `elem_bytes`] into dst[r * n ...] over NVLink.
+// Waits for `epoch` on `channel` from every rank first when channel >= 0.
+int sx_allgather_pull(const SxPeers* peers, void* dst, long long shard_bytes, long long src_offset_bytes, int channel,
+                      unsigned epoch, int grid, int* status, cudaStream_t stream);
+
+// AR1: small all-reduce (sum) of fp32 values through the peers' buffers; n <= 4096. In place on peers->buf[rank].
+int sx_allreduce_small(const SxPeers* peers, int n, int channel, unsigned epoch, int* status, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

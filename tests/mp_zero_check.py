@@ -1,0 +1,53 @@
+"""Worker for the multi-GPU ZeRO test: run under torch.distributed.run, one rank per GPU.
+Compares the fused (peer-memory) ZeRO path with the torch.distributed library path on the same model/data."""
+import copy
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from sneppx_alg_b200.models import ModelConfig, build_model  # noqa: E402
+from sneppx_alg_b200.ops import check_status  # noqa: E402
+from sneppx_alg_b200.parallel.zero_engine import ZeroEngine  # noqa: E402
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dev = torch.device("cuda", torch.cuda.current_device())
+    dist.init_process_group("nccl", device_id=dev)
+    stage = int(sys.argv[1]) if len(sys.argv) > 1 else 3
+    cfg = ModelConfig(hidden_size=512, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2,
+                      intermediate_size=1024, vocab_size=2048, max_position_embeddings=256, rms_norm_eps=1e-5)
+    torch.manual_seed(0)
+    base = build_model(cfg, dtype=torch.bfloat16, device=dev)
+    lib_model = copy.deepcopy(base)
+    fused = ZeroEngine(base, zero_stage=stage, lr=1e-3, fused=True)
+    lib = ZeroEngine(lib_model, zero_stage=stage, lr=1e-3, fused=False)
+    worst = 0.0
+    for step in range(4):
+        ids = torch.randint(0, cfg.vocab_size, (2, 256), generator=torch.Generator().manual_seed(10 * step + rank)).to(dev)
+        lf = fused.step(ids, ids).item()
+        ll = lib.step(ids, ids).item()
+        worst = max(worst, abs(lf - ll))
+    torch.cuda.synchronize()
+    check_status()
+    # after the last step the gathered parameters are refreshed asynchronously; wait for them
+    fused.comm_stream.synchronize()
+    pf, pl = fused.fp.flat.float(), lib.fp.flat.float()
+    rel = (pf - pl).abs().max().item() / (pl.abs().max().item() + 1e-6)
+    nf, nl = float(fused.last_norm[1]), float(lib.last_norm[1])
+    ok = worst < 0.05 and rel < 2e-2 and abs(nf - nl) < 2e-2 * max(nl, 1.0)
+    t = torch.tensor([int(ok)], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        print(f"zero stage {stage} world {world}: loss diff {worst:.4f} param rel {rel:.2e} norm {nf:.4f}/{nl:.4f} ->",
+              "OK" if t.item() else "MISMATCH")
+    dist.destroy_process_group()
+    sys.exit(0 if t.item() else 1)
+
+
+if __name__ == "__main__":
+    main()
