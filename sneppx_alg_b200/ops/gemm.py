@@ -199,3 +199,38 @@ def linear(x, w, bias=None, act=None):
             _LinearFn.apply(x, w, bias, None), act)
     x2 = x.reshape(-1, x.shape[-1])
     return gemm(x2, w, bias=bias, act=act).view(*x.shape[:-1], w.shape[0])
+
+
+class _BmmFn(torch.autograd.Function):
+    """Batched C = A @ B on the tcgen05 GEMM (A [n, M, K], B [n, K, N]); both gradients reuse the kernel with
+    MN-major operand flags instead of transposed copies."""
+
+    @staticmethod
+    def forward(ctx, a, b):
+        ctx.save_for_backward(a, b)
+        return gemm(a, b, b_mn=True)
+
+    @staticmethod
+    def backward(ctx, g):
+        a, b = ctx.saved_tensors
+        g = g.contiguous()
+        da = db = None
+        if ctx.needs_input_grad[0]:
+            da = gemm(g, b)                      # [n,M,N] x [n,K,N]^T -> [n,M,K]
+        if ctx.needs_input_grad[1]:
+            db = gemm(a, g, a_mn=True, b_mn=True)  # A^T [K,M] x G [M,N] -> [n,K,N]
+        return da, db
+
+
+def bmm(a, b):
+    """Batched matmul with autograd; leading dims are flattened. bf16 CUDA tensors run on the tcgen05 GEMM."""
+    if _use_kernel(a, b) and a.shape[-1] % 8 == 0 and b.shape[-1] % 8 == 0:
+        lead = a.shape[:-2]
+        a3 = a.reshape(-1, a.shape[-2], a.shape[-1])
+        b3 = b.reshape(-1, b.shape[-2], b.shape[-1])
+        if not a3.is_contiguous():
+            a3 = a3.contiguous()
+        if not b3.is_contiguous():
+            b3 = b3.contiguous()
+        return _BmmFn.apply(a3, b3).reshape(*lead, a.shape[-2], b.shape[-1])
+    return torch.matmul(a, b)

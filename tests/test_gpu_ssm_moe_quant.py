@@ -1,0 +1,124 @@
+"""conv1d, chunked SSD scan, router / MoE and quantisation kernels against fp32 PyTorch references."""
+import pytest
+import torch
+
+from sneppx_alg_b200 import ops
+from sneppx_alg_b200.ops import moe, quant, ssm
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+    return (a.float() - b.float()).abs().max().item() / (b.float().abs().max().item() + 1e-6)
+
+
+@pytest.mark.parametrize("with_prev,act", [(False, True), (True, True), (False, False)])
+def test_conv1d(with_prev, act):
+    torch.manual_seed(0)
+    B, L, C, K = 2, 200, 320, 4
+    x = torch.randn(B, L, C, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (0.5 * torch.randn(C, K, device="cuda")).to(torch.bfloat16).requires_grad_(True)
+    b = torch.randn(C, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    prev = torch.randn(B, K - 1, C, device="cuda", dtype=torch.bfloat16) if with_prev else None
+    y = ssm.causal_conv1d(x, w, b, act, prev)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr, wr, br = [t.detach().float().requires_grad_(True) for t in (x, w, b)]
+    yr = ssm.conv1d_reference(xr, wr, br, act, prev.float() if with_prev else None)
+    yr.backward(g.float())
+    assert _rel(y, yr) < 2e-2
+    assert _rel(x.grad, xr.grad) < 3e-2 and _rel(w.grad, wr.grad) < 3e-2 and _rel(b.grad, br.grad) < 3e-2
+
+
+@pytest.mark.parametrize("L,chunk,G", [(256, 64, 1), (512, 256, 2), (200, 64, 1)])
+def test_ssd_chunked_vs_recurrence(L, chunk, G):
+    torch.manual_seed(0)
+    B, H, P, N = 2, 4, 64, 64
+    x = torch.randn(B, L, H, P, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    dt = (torch.rand(B, L, H, device="cuda") * 0.1 + 1e-3).requires_grad_(True)
+    A = (-torch.rand(H, device="cuda") * 4 - 0.5).requires_grad_(True)
+    Bm = torch.randn(B, L, G, N, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    Cm = torch.randn(B, L, G, N, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    D = torch.randn(H, device="cuda", requires_grad=True)
+    y = ssm.ssd_scan(x, dt, A, Bm, Cm, D, chunk=chunk)
+    g = torch.randn_like(y)
+    y.backward(g)
+    ops.check_status()
+    ref_in = [t.detach().float().requires_grad_(True) for t in (x, dt, A, Bm, Cm, D)]
+    yr = ssm.ssd_reference(*ref_in)
+    yr.backward(g.float())
+    assert _rel(y, yr) < 3e-2
+    for got, ref, name in zip((x, dt, A, Bm, Cm, D), ref_in, "x dt A B C D".split()):
+        assert _rel(got.grad, ref.grad) < 6e-2, name
+
+
+def test_router_and_moe_layer():
+    torch.manual_seed(0)
+    T, d, E, k, Fd = 1000, 256, 16, 4, 192
+    x = torch.randn(T, d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    logits = torch.randn(T, E, device="cuda")
+    idx, w, probs, counts = moe.route(logits, k)
+    ref_idx = moe.topk_reference(torch.softmax(logits, -1), k)
+    assert torch.equal(idx.sort(-1).values, ref_idx.sort(-1).values)
+    assert torch.allclose(w.sum(-1), torch.ones(T, device="cuda"), atol=1e-5)
+    assert counts.sum().item() == T * k
+    W1 = (0.05 * torch.randn(E, 2 * Fd, d, device="cuda")).to(torch.bfloat16).requires_grad_(True)
+    W2 = (0.05 * torch.randn(E, d, Fd, device="cuda")).to(torch.bfloat16).requires_grad_(True)
+    w = w.detach().requires_grad_(True)
+    y = moe.experts_forward(x, idx, w, W1, W2)
+    g = torch.randn_like(y)
+    y.backward(g)
+    ops.check_status()
+    xr, wr, W1r, W2r = [t.detach().float().requires_grad_(True) for t in (x, w, W1, W2)]
+    yr = moe.moe_reference(xr, idx, wr, W1r, W2r)
+    yr.backward(g.float())
+    assert _rel(y, yr) < 3e-2
+    assert _rel(x.grad, xr.grad) < 4e-2 and _rel(w.grad, wr.grad) < 4e-2
+    assert _rel(W1.grad, W1r.grad) < 4e-2 and _rel(W2.grad, W2r.grad) < 4e-2
+
+
+def test_quant_roundtrip_and_reference():
+    torch.manual_seed(0)
+    x = torch.randn(300, 512, device="cuda", dtype=torch.bfloat16) * 3
+    q, s = quant.quant_fp8_1x128(x)
+    qr, sr = quant.quant_fp8_1x128_reference(x)
+    assert torch.allclose(s, sr, rtol=1e-6)
+    assert (q.float() - qr.float()).abs().max().item() <= 32.0  # at most one e4m3 step at the top binade
+    assert (q.view(torch.uint8) != qr.view(torch.uint8)).float().mean().item() < 0.01
+    assert _rel(quant.dequant_fp8(q, s, "1x128"), x) < 0.07
+    w = torch.randn(200, 384, device="cuda", dtype=torch.bfloat16)
+    qw, sw = quant.quant_fp8_128x128(w)
+    qwr, swr = quant.quant_fp8_128x128_reference(w)
+    assert torch.allclose(sw, swr, rtol=1e-6)
+    assert _rel(quant.dequant_fp8(qw, sw, "128x128"), w) < 0.07
+    w4 = torch.randn(128, 256, device="cuda", dtype=torch.bfloat16)
+    p, s4 = quant.quant_int4(w4)
+    pr, s4r = quant.quant_int4_reference(w4)
+    assert torch.allclose(s4, s4r, rtol=1e-6) and (p != pr).float().mean().item() < 0.01
+    assert _rel(quant.dequant_int4(p, s4), w4) < 0.2
+
+
+def test_models_train_on_gpu():
+    from sneppx_alg_b200.models import ModelConfig, build_model
+    from sneppx_alg_b200.training.engine import TrainEngine
+    torch.manual_seed(0)
+    cfgs = [
+        ModelConfig(architecture="mamba2", hidden_size=256, num_hidden_layers=2, vocab_size=1000, ssm_state_size=64,
+                    ssm_head_dim=64, ssm_ngroups=1, ssm_chunk_size=64, tie_word_embeddings=True),
+        ModelConfig(architecture="hss_ser", hidden_size=256, num_hidden_layers=2, vocab_size=1024, ssm_state_size=64,
+                    ssm_head_dim=64, ssm_chunk_size=64, num_experts=8, num_experts_per_token=2,
+                    moe_intermediate_size=256, router_aux_loss_coef=0.01, tie_word_embeddings=True),
+        ModelConfig(architecture="deepseek_moe", hidden_size=256, num_hidden_layers=2, num_attention_heads=2,
+                    head_dim=128, intermediate_size=512, vocab_size=1024, num_experts=8, num_experts_per_token=2,
+                    num_shared_experts=1, moe_intermediate_size=128, first_dense_layers=1,
+                    router_aux_loss_coef=0.001, max_position_embeddings=256),
+    ]
+    for cfg in cfgs:
+        model = build_model(cfg, dtype=torch.bfloat16, device="cuda")
+        eng = TrainEngine(model, lr=2e-3, max_grad_norm=1.0)
+        ids = torch.randint(0, 1000, (2, 256), device="cuda")
+        first = eng.step(ids, ids).item()
+        for _ in range(6):
+            last = eng.step(ids, ids).item()
+        ops.check_status()
+        assert last == last and last < first, (cfg.architecture, first, last)
