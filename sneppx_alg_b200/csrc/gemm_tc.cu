@@ -15,6 +15,8 @@
 // Takes the place of the reference's mma.sync / SIMT GEMMs (kernel/cuda/tensor_cuda.cu:28-285) and
 // its cuBLAS backward calls (kernel/cuda/autodiff_cuda.cu:28-171).
 #include "tc_common.cuh"
+#include "comm_common.cuh"
+#include "common.cuh"
 #include "tmap.h"
 #include "sx_api.h"
 
@@ -23,6 +25,36 @@ namespace sx {
 constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int GEMM_THREADS = 192;
+
+// Collective fused into the GEMM (template parameter COMM):
+//   COMM == 1  all-gather -> GEMM (F3 for activations, F2 for ZeRO-3 weights). The gathered operand (A rows or B rows)
+//              is split in `world` chunks of chunk_rows rows; rank r's chunk lives at the same offset of rank r's copy of
+//              the symmetric full-size buffer. The first n_copy CTAs pull remote chunks over NVLink in sub-chunks and
+//              publish a device-scope flag per sub-chunk; the other CTAs run the GEMM with tiles ordered so that the
+//              local chunk comes first, and their TMA producer waits for the flag of the sub-chunk a tile reads.
+//   COMM == 2  GEMM -> reduce-scatter (F4). Output rows are split in `world` chunks; a tile that belongs to rank c is
+//              written (bf16) into slot `rank` of c's symmetric staging buffer and counted on c's per-row-block counter
+//              (system-scope release add). After its own tiles each CTA reduces row blocks of the local chunk in rank
+//              order as soon as their counters are complete. Tiles are ordered remote chunks first, local chunk last.
+// Every wait is bounded (pt.timeout_ns) and reports ST_TIMEOUT_SIGNAL through the status word.
+struct CommParams {
+  PeerTable pt;
+  uint8_t* full;        // COMM 1: local full operand buffer (== pt.buf[rank])
+  uint32_t* flags;      // COMM 1: local flags [world * subs_per_chunk]
+  uint32_t epoch;
+  int n_copy;           // COMM 1: CTAs that copy
+  int gather_b;         // COMM 1: 0 = A rows are gathered, 1 = B rows
+  int chunk_rows;       // rows per rank chunk (multiple of sub_rows)
+  int sub_rows;         // COMM 1: rows per flag (multiple of 128 for A, of BN for B)
+  long long row_bytes;  // COMM 1: bytes per row of the gathered operand
+  int sig_channel, done_channel;
+  int counter_word;     // COMM 2: first word of the row-block counters inside the signal pad
+  uint32_t rs_expected; // COMM 2: counter value at which a row block of this call is complete
+  void* rs_out;         // COMM 2: [chunk_rows, N] local result
+  const void* rs_residual;  // COMM 2: optional [chunk_rows, N] added to the result
+  long long rs_ldd;
+  uint32_t* cta_counter;    // local word used to find the last CTA of the grid
+};
 
 struct GemmKernelParams {
   CUtensorMap tmA;
@@ -39,6 +71,7 @@ struct GemmKernelParams {
   int out_fp32, c_fp32, act;
   float alpha, beta;
   int m_blks, n_blks;
+  CommParams cm;
 };
 
 template <int BN>
@@ -65,7 +98,7 @@ __device__ __forceinline__ void tile_coords(int t, int m_blks, int n_blks, int& 
   n_blk = rr / gsz;
 }
 
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN, int COMM>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_constant__ GemmKernelParams p) {
   using Cfg = GemmCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
@@ -95,13 +128,57 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
     tma_prefetch_desc(&p.tmA);
     tma_prefetch_desc(&p.tmB);
   }
-  if (warp == 1) tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+  const bool is_copy_cta = (COMM == 1) && ((int)blockIdx.x < p.cm.n_copy);
+  if (warp == 1 && !is_copy_cta) tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_base = is_copy_cta ? 0u : *tmem_slot;
 
   const int total_tiles = p.batch * p.m_blks * p.n_blks;
+  // CTAs that run GEMM tiles: all of them, minus the copy CTAs of the all-gather form
+  const int cta0 = (COMM == 1) ? p.cm.n_copy : 0;
+  const int tile_first = (int)blockIdx.x - cta0;
+  const int tile_step = (int)gridDim.x - cta0;
+  // tile rotation so that every rank starts on rows it already has (COMM 1) / ends on rows it owns (COMM 2)
+  int rot_m = 0, rot_n = 0;
+  if (COMM == 1) {
+    if (p.cm.gather_b) rot_n = p.cm.pt.rank * (p.cm.chunk_rows / BN);
+    else rot_m = p.cm.pt.rank * (p.cm.chunk_rows / BM);
+  } else if (COMM == 2) {
+    rot_m = ((p.cm.pt.rank + 1) % p.cm.pt.world) * (p.cm.chunk_rows / BM);
+  }
+
+  if (is_copy_cta) {
+    // ------------------------------------------------------------ all-gather copy CTAs
+    const PeerTable& pt = p.cm.pt;
+    __shared__ int s_ok;
+    if (blockIdx.x == 0) signal_all(pt, p.cm.sig_channel, p.cm.epoch);  // my chunk is complete (stream order)
+    const int subs = p.cm.chunk_rows / p.cm.sub_rows;
+    const long long sub_bytes = (long long)p.cm.sub_rows * p.cm.row_bytes;
+    bool ok = true;
+    for (int rr = 1; rr < pt.world && ok; ++rr) {
+      const int r = (pt.rank + rr) % pt.world;
+      if (threadIdx.x == 0)
+        s_ok = wait_flag_sys(pt.pad[pt.rank] + p.cm.sig_channel * SX_PAD_STRIDE + r, p.cm.epoch, pt.timeout_ns, p.status);
+      __syncthreads();
+      ok = s_ok != 0;
+      __syncthreads();
+      if (!ok) break;
+      for (int sub = blockIdx.x; sub < subs; sub += p.cm.n_copy) {
+        const long long off = ((long long)r * p.cm.chunk_rows + (long long)sub * p.cm.sub_rows) * p.cm.row_bytes;
+        const uint8_t* src = reinterpret_cast<const uint8_t*>(pt.buf[r]) + off;
+        uint8_t* dst = p.cm.full + off;
+        for (long long i = threadIdx.x; i < (sub_bytes >> 4); i += GEMM_THREADS) {
+          // 4 loads in flight per thread
+          *reinterpret_cast<uint4*>(dst + (i << 4)) = ld_peer_v4(src + (i << 4));
+        }
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) st_release_gpu(&p.cm.flags[r * subs + sub], p.cm.epoch);
+      }
+    }
+  } else
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -109,9 +186,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      for (int t = tile_first; t < total_tiles && ok; t += tile_step) {
         int b, m_blk, n_blk;
         tile_coords(t, p.m_blks, p.n_blks, b, m_blk, n_blk);
+        if (COMM != 0) { m_blk = (m_blk + rot_m) % p.m_blks; n_blk = (n_blk + rot_n) % p.n_blks; }
         int bsel = b;
         if (p.tile_group) {
           bsel = p.tile_group[m_blk];
@@ -125,6 +203,21 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
         const int ab = p.a_batched ? b : 0;
         const int bb = p.b_batched ? bsel : 0;
         const int num_kb = (k1 - k0 + BK - 1) / BK;
+        if (COMM == 1) {
+          const int row0 = p.cm.gather_b ? n_blk * BN : m_blk * BM;
+          const int src = row0 / p.cm.chunk_rows;
+          if (src != p.cm.pt.rank) {
+            const int subs = p.cm.chunk_rows / p.cm.sub_rows;
+            const int sub = (row0 - src * p.cm.chunk_rows) / p.cm.sub_rows;
+            if (!wait_flag_gpu(&p.cm.flags[src * subs + sub], p.cm.epoch, p.cm.pt.timeout_ns, p.status)) {
+              *s_abort = 1;
+              ok = false;
+              break;
+            }
+            // rows were written by ordinary stores of the copy CTAs; order them before this thread's TMA reads
+            asm volatile("fence.proxy.async;" ::: "memory");
+          }
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, s_abort, p.status, ST_TIMEOUT_PRODUCER)) {
             ok = false;
@@ -150,9 +243,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      for (int t = tile_first; t < total_tiles && ok; t += tile_step) {
         int b, m_blk, n_blk;
         tile_coords(t, p.m_blks, p.n_blks, b, m_blk, n_blk);
+        if (COMM != 0) { m_blk = (m_blk + rot_m) % p.m_blks; n_blk = (n_blk + rot_n) % p.n_blks; }
         if (p.tile_group && p.tile_group[m_blk] < 0) continue;
         int k0 = 0, k1 = p.K;
         if (p.k_ranges) {
@@ -197,9 +291,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
     const int q = warp & 3;  // TMEM lane quadrant this warp may access
     int it = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+    for (int t = tile_first; t < total_tiles && ok; t += tile_step) {
       int b, m_blk, n_blk;
       tile_coords(t, p.m_blks, p.n_blks, b, m_blk, n_blk);
+        if (COMM != 0) { m_blk = (m_blk + rot_m) % p.m_blks; n_blk = (n_blk + rot_n) % p.n_blks; }
       if (p.tile_group && p.tile_group[m_blk] < 0) continue;
       bool empty_k = false;
       if (p.k_ranges) empty_k = (p.k_ranges[2 * b + 1] <= p.k_ranges[2 * b]);
@@ -209,7 +304,15 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
       tc_fence_after();
       const int row = m_blk * BM + q * 32 + lane;
       const bool row_ok = row < p.M;
-      const long long drow = (long long)b * p.strideD + (long long)row * p.ldd;
+      long long drow = (long long)b * p.strideD + (long long)row * p.ldd;
+      void* Dptr = p.D;
+      int rs_owner = 0, rs_rb = 0;
+      if (COMM == 2) {
+        rs_owner = (m_blk * BM) / p.cm.chunk_rows;
+        rs_rb = (m_blk * BM - rs_owner * p.cm.chunk_rows) / BM;
+        Dptr = p.cm.pt.buf[rs_owner];   // owner's staging buffer, slot `rank`
+        drow = ((long long)p.cm.pt.rank * p.cm.chunk_rows + (row - rs_owner * p.cm.chunk_rows)) * (long long)p.N;
+      }
       const long long crow = (long long)b * p.strideC + (long long)row * p.ldc;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
@@ -252,7 +355,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
           for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
         }
         if (p.out_fp32) {
-          float* dp = reinterpret_cast<float*>(p.D) + drow + col0;
+          float* dp = reinterpret_cast<float*>(Dptr) + drow + col0;
           if (full && ((reinterpret_cast<uintptr_t>(dp) & 15) == 0)) {
 #pragma unroll
             for (int j = 0; j < 32; j += 4)
@@ -262,7 +365,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
               if (col0 + j < p.N) dp[j] = v[j];
           }
         } else {
-          __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(p.D) + drow + col0;
+          __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(Dptr) + drow + col0;
           if (full && ((reinterpret_cast<uintptr_t>(dp) & 15) == 0)) {
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
@@ -280,8 +383,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
         }
       }
       tc_fence_before();
+      if (COMM == 2) __threadfence_system();   // partial tile visible to its owner before the count moves
       __syncwarp();
-      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+      if (lane == 0) {
+        mbar_arrive(&tempty_bar[acc]);
+        if (COMM == 2) red_release_sys_add(p.cm.pt.pad[rs_owner] + p.cm.counter_word + rs_rb, 1u);
+      }
       ++it;
     }
   }
@@ -290,17 +397,71 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
   tc_fence_before();
   __syncthreads();
   if (*s_abort) bounded_delay_ns(2000000);  // let copies in flight land before freeing
-  if (warp == 1) {
+  if (warp == 1 && !is_copy_cta) {
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
+
+  if (COMM == 2) {
+    // ---------------------------------------------------------- reduce the row blocks this rank owns
+    const PeerTable& pt = p.cm.pt;
+    __shared__ int s_ok2;
+    const int blks = p.cm.chunk_rows / BM;
+    const int units = blks * p.n_blks;
+    const uint32_t expected = p.cm.rs_expected;  // cumulative arrivals per row block, tracked by the host per call site
+    const __nv_bfloat16* stage = reinterpret_cast<const __nv_bfloat16*>(pt.buf[pt.rank]);
+    for (int u = tile_first; u < units; u += tile_step) {
+      const int rb = u / p.n_blks, nb = u % p.n_blks;
+      if (threadIdx.x == 0)
+        s_ok2 = wait_flag_sys(pt.pad[pt.rank] + p.cm.counter_word + rb, expected, pt.timeout_ns, p.status);
+      __syncthreads();
+      const bool okk = s_ok2 != 0;
+      __syncthreads();
+      if (!okk) break;
+      constexpr int VPR = BN / 8;  // 16-byte vectors per row of the strip
+      for (int idx = threadIdx.x; idx < BM * VPR; idx += GEMM_THREADS) {
+        const int rr = idx / VPR, col = nb * BN + (idx % VPR) * 8;
+        if (col >= p.N) continue;
+        const int lrow = rb * BM + rr;
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        for (int r = 0; r < pt.world; ++r)
+          acc_bf16x8(acc, ld_peer_v4(stage + ((long long)r * p.cm.chunk_rows + lrow) * p.N + col));
+        if (p.cm.rs_residual) {
+          float e[8];
+          unpack8(ld8(reinterpret_cast<const __nv_bfloat16*>(p.cm.rs_residual) + (long long)lrow * p.cm.rs_ldd + col), e);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] += e[j];
+        }
+        st8(reinterpret_cast<__nv_bfloat16*>(p.cm.rs_out) + (long long)lrow * p.cm.rs_ldd + col, pack8(acc));
+      }
+    }
+  }
+  if (COMM != 0) {
+    // Last CTA of the grid tells the peers that this rank no longer reads their memory / has consumed its staging
+    // buffer, and waits for the same from everyone, so the buffers may be reused once the kernel has returned.
+    __shared__ int s_last;
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const uint32_t prev = atomicAdd(p.cm.cta_counter, 1u);
+      s_last = (prev + 1 == gridDim.x);
+      if (s_last) *p.cm.cta_counter = 0;
+    }
+    __syncthreads();
+    if (s_last) {
+      signal_all(p.cm.pt, p.cm.done_channel, p.cm.epoch);
+      wait_all(p.cm.pt, p.cm.done_channel, p.cm.epoch, p.status);
+    }
+  }
 }
 
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN, int COMM = 0>
 static int launch_cfg(const GemmKernelParams& kp, int grid, cudaStream_t st) {
   using Cfg = GemmCfg<BN>;
   static bool attr_set = false;
-  auto kern = gemm_tc_kernel<BN, A_MN, B_MN>;
+  auto kern = gemm_tc_kernel<BN, A_MN, B_MN, COMM>;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) != cudaSuccess)
       return -10;
@@ -328,7 +489,7 @@ static int make_operand_map(CUtensorMap* tm, const void* ptr, int mn, int K, lon
 
 }  // namespace sx
 
-extern "C" int sx_gemm_bf16(const SxGemmArgs* a, cudaStream_t st) {
+static int gemm_launch(const SxGemmArgs* a, const SxGemmCommArgs* cm, cudaStream_t st) {
   using namespace sx;
   if (a->M <= 0 || a->N <= 0 || a->batch <= 0) return 0;
   if ((a->lda % 8) || (a->ldb % 8) || (reinterpret_cast<uintptr_t>(a->A) & 15) ||
@@ -336,7 +497,8 @@ extern "C" int sx_gemm_bf16(const SxGemmArgs* a, cudaStream_t st) {
     return -1;
   if (a->K % 8) return -2;
   GemmKernelParams kp;
-  const int BN = (a->N > 128 || a->force_bn == 256) && a->force_bn != 128 ? 256 : 128;
+  int BN = (a->N > 128 || a->force_bn == 256) && a->force_bn != 128 ? 256 : 128;
+  if (cm && cm->mode == 2 && (cm->sub_rows % 256) != 0) BN = 128;
   const int a_batched = a->strideA != 0 && a->batch > 1;
   const int b_batched = (a->strideB != 0 && a->batch > 1) || a->tile_group != nullptr;
   const int b_nbatch = a->tile_group ? a->num_groups : a->batch;
@@ -379,8 +541,54 @@ extern "C" int sx_gemm_bf16(const SxGemmArgs* a, cudaStream_t st) {
   if (dev < 16) sms = cached_sms[dev];
   if (a->sm_limit > 0 && a->sm_limit < sms) sms = a->sm_limit;
   const long long tiles = (long long)kp.batch * kp.m_blks * kp.n_blks;
-  const int grid = (int)(tiles < sms ? tiles : sms);
+  int grid = (int)(tiles < sms ? tiles : sms);
   const int am = a->a_mn != 0, bm = a->b_mn != 0;
+  if (cm) {
+    if (am || a->batch != 1 || a->tile_group || a->k_ranges) return -30;
+    CommParams& c = kp.cm;
+    for (int i = 0; i < SX_MAX_RANKS; ++i) {
+      c.pt.buf[i] = cm->peers.buf[i];
+      c.pt.pad[i] = reinterpret_cast<uint32_t*>(cm->peers.pad[i]);
+    }
+    c.pt.rank = cm->peers.rank;
+    c.pt.world = cm->peers.world;
+    c.pt.timeout_ns = cm->peers.timeout_ns ? cm->peers.timeout_ns : 2000000000ull;
+    c.flags = reinterpret_cast<uint32_t*>(cm->flags);
+    c.epoch = cm->epoch;
+    c.chunk_rows = cm->chunk_rows;
+    c.sub_rows = cm->sub_rows;
+    c.sig_channel = cm->sig_channel;
+    c.done_channel = cm->done_channel;
+    c.counter_word = cm->counter_word;
+    c.rs_expected = cm->rs_expected;
+    c.rs_out = cm->rs_out;
+    c.rs_residual = cm->rs_residual;
+    c.rs_ldd = cm->rs_ldd;
+    c.cta_counter = reinterpret_cast<uint32_t*>(cm->cta_counter);
+    c.n_copy = 0;
+    c.gather_b = 0;
+    if (cm->mode == 1 || cm->mode == 2) {
+      c.gather_b = cm->mode == 2;
+      const int rows_total = c.gather_b ? a->N : a->M;
+      const int tile_rows = c.gather_b ? BN : BM;
+      if (cm->chunk_rows * cm->peers.world != rows_total || (cm->chunk_rows % cm->sub_rows) ||
+          (cm->sub_rows % tile_rows) || (a->K % 8))
+        return -31;
+      c.full = reinterpret_cast<uint8_t*>(cm->peers.buf[cm->peers.rank]);
+      c.row_bytes = (long long)(c.gather_b ? a->ldb : a->lda) * 2;
+      c.n_copy = cm->n_copy > 0 ? cm->n_copy : 8;
+      if (cm->peers.world == 1) c.n_copy = 0;
+      if (grid + c.n_copy > sms) grid = sms - c.n_copy;
+      grid += c.n_copy;  // every CTA must be resident at once: copy CTAs feed the GEMM CTAs of the same launch
+      if (!bm) return BN == 256 ? launch_cfg<256, false, false, 1>(kp, grid, st) : launch_cfg<128, false, false, 1>(kp, grid, st);
+      return BN == 256 ? launch_cfg<256, false, true, 1>(kp, grid, st) : launch_cfg<128, false, true, 1>(kp, grid, st);
+    } else if (cm->mode == 3) {
+      if (cm->chunk_rows * cm->peers.world != a->M || (cm->chunk_rows % BM) || a->out_fp32 || (a->N % 8)) return -32;
+      if (!bm) return BN == 256 ? launch_cfg<256, false, false, 2>(kp, grid, st) : launch_cfg<128, false, false, 2>(kp, grid, st);
+      return BN == 256 ? launch_cfg<256, false, true, 2>(kp, grid, st) : launch_cfg<128, false, true, 2>(kp, grid, st);
+    }
+    return -33;
+  }
   if (BN == 256) {
     if (!am && !bm) return launch_cfg<256, false, false>(kp, grid, st);
     if (!am && bm) return launch_cfg<256, false, true>(kp, grid, st);
@@ -392,4 +600,12 @@ extern "C" int sx_gemm_bf16(const SxGemmArgs* a, cudaStream_t st) {
     if (am && !bm) return launch_cfg<128, true, false>(kp, grid, st);
     return launch_cfg<128, true, true>(kp, grid, st);
   }
+}
+
+extern "C" int sx_gemm_bf16(const SxGemmArgs* a, cudaStream_t st) { return gemm_launch(a, nullptr, st); }
+
+// F2 / F3 / F4: the same GEMM with a collective fused in (see CommParams above and SxGemmCommArgs in sx_api.h).
+extern "C" int sx_gemm_bf16_comm(const SxGemmArgs* a, const SxGemmCommArgs* cm, cudaStream_t st) {
+  if (!cm) return -30;
+  return gemm_launch(a, cm, st);
 }

@@ -108,6 +108,30 @@ int sx_signal_peers(const SxPeers* peers, int channel, unsigned epoch, cudaStrea
 int sx_allgather_pull(const SxPeers* peers, void* dst, long long shard_bytes, long long src_offset_bytes, int channel,
                       unsigned epoch, int grid, int* status, cudaStream_t stream);
 
+// F2 / F3 / F4: GEMM with a collective fused into the same kernel.
+//   mode 1  all-gather A rows -> GEMM   (TP column-parallel / sequence-parallel input; F3)
+//   mode 2  all-gather B rows -> GEMM   (ZeRO-3 weight shards pulled by the consuming GEMM; F2)
+//   mode 3  GEMM -> reduce-scatter of output rows (TP row-parallel output; F4)
+// Modes 1/2: peers.buf[r] is rank r's copy of the full-size symmetric operand buffer, whose chunk r (chunk_rows rows)
+// rank r has filled before the launch; the local copy is the GEMM operand (args->A or args->B must be
+// peers.buf[rank]). flags: local uint32 [world * chunk_rows / sub_rows], zeroed once; epoch increases per call.
+// Mode 3: peers.buf[r] is rank r's staging buffer, bf16 [world][chunk_rows][N]; rs_out [chunk_rows, N] (ld rs_ldd) gets
+// the sum over ranks (+ rs_residual); counter_word: first of chunk_rows/128 words of the signal pad used as counters.
+// The grid never exceeds the SM count: all CTAs of a launch are resident together, which the in-kernel waits rely on.
+typedef struct SxGemmCommArgs {
+  SxPeers peers;
+  int mode;
+  void* flags;
+  unsigned epoch;
+  int n_copy;
+  int chunk_rows, sub_rows;
+  int sig_channel, done_channel, counter_word;
+  unsigned rs_expected;  // mode 3: counter value that marks a row block complete (previous value + 4 * ceil(N/BN) * world)
+  void* rs_out; const void* rs_residual; long long rs_ldd;
+  void* cta_counter;   // local uint32 word, zeroed once
+} SxGemmCommArgs;
+int sx_gemm_bf16_comm(const SxGemmArgs* args, const SxGemmCommArgs* comm, cudaStream_t stream);
+
 // AR1: small all-reduce (sum) of fp32 values through the peers' buffers; n <= 4096. In place on peers->buf[rank].
 int sx_allreduce_small(const SxPeers* peers, int n, int channel, unsigned epoch, int* status, cudaStream_t stream);
 

@@ -35,12 +35,16 @@ class FlatParams:
         self.params = list(params) if params is not None else _unique_params(module)
         assert self.params, "no trainable parameters"
         p0 = self.params[0]
-        self.dtype, self.device = p0.dtype, p0.device
-        self.grad_dtype = grad_dtype or p0.dtype
+        # one storage dtype for the whole buffer: the widest-used 16-bit type if any parameter has one (fp32
+        # scalars such as SSM decay rates are then computed from their fp32 master copy, rounded for the forward pass)
+        dts = {p.dtype for p in self.params}
+        self.dtype = torch.bfloat16 if torch.bfloat16 in dts else (torch.float16 if torch.float16 in dts else p0.dtype)
+        self.device = p0.device
+        self.grad_dtype = grad_dtype or self.dtype
         self.offsets = []
         off = 0
         for p in self.params:
-            assert p.dtype == self.dtype and p.device == self.device
+            assert p.device == self.device
             self.offsets.append(off)
             off += (p.numel() + align - 1) // align * align
         unit = align * shard_multiple

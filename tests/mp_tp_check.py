@@ -1,0 +1,80 @@
+"""Worker for the multi-GPU tensor-parallel test (run under torch.distributed.run): fused all-gather->GEMM and
+GEMM->reduce-scatter kernels against torch.distributed collectives around a plain matmul, forward and backward."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from sneppx_alg_b200.ops import check_status  # noqa: E402
+from sneppx_alg_b200.parallel.tp import ColumnParallelLinear, RowParallelLinear, TPContext  # noqa: E402
+
+
+def rel(a, b):
+    return (a.float() - b.float()).abs().max().item() / (b.float().abs().max().item() + 1e-6)
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dev = torch.device("cuda", torch.cuda.current_device())
+    dist.init_process_group("nccl", device_id=dev)
+    tp = TPContext(fused=True)
+    T, d, F = 512 * world, 512, 1024
+    torch.manual_seed(0)
+    col = ColumnParallelLinear(d, F, tp, dtype=torch.bfloat16, device=dev)
+    row = RowParallelLinear(F, d, tp, dtype=torch.bfloat16, device=dev)
+    torch.manual_seed(100 + rank)
+    with torch.no_grad():
+        col.weight.normal_(std=0.05)
+        row.weight.normal_(std=0.05)
+    worst = 0.0
+    for it in range(3):
+        x_s = torch.randn(T // world, d, device=dev, dtype=torch.bfloat16, requires_grad=True)
+        res = torch.randn(T // world, d, device=dev, dtype=torch.bfloat16)
+        h = col(x_s)
+        y_s = row(torch.nn.functional.silu(h), residual=res)
+        g = torch.randn_like(y_s)
+        col.weight.grad = row.weight.grad = None
+        y_s.backward(g)
+        # reference with library collectives in fp32
+        xr = x_s.detach().float().requires_grad_(True)
+        wc, wr = col.weight.detach().float().requires_grad_(True), row.weight.detach().float().requires_grad_(True)
+        xs = [torch.empty_like(xr) for _ in range(world)]
+        dist.all_gather(xs, xr.detach())
+        xs[rank] = xr
+        xf = torch.cat(xs, 0)
+        part = torch.nn.functional.silu(xf @ wc.t()) @ wr.t()
+        tot = part.detach().clone()
+        dist.all_reduce(tot)
+        rs = T // world
+        ref_y = tot[rank * rs: (rank + 1) * rs] + res.float()
+        # backward reference: d part = gathered g (each rank's rows)
+        gs = [torch.empty_like(g) for _ in range(world)]
+        dist.all_gather(gs, g)
+        part.backward(torch.cat(gs, 0).float())
+        gx = xf.grad if False else None
+        worst = max(worst, rel(y_s, ref_y), rel(col.weight.grad, wc.grad), rel(row.weight.grad, wr.grad))
+        # dx for my shard sums contributions of all ranks' column shards
+        dxs = xr.grad.clone() if xr.grad is not None else torch.zeros_like(xr)
+        full_dx = torch.zeros(T, d, device=dev)
+        # every rank holds d(loss)/d(x rows) for its own weight shard only: recompute as (dh @ wc) over the full batch
+        h_ref = xf.detach() @ wc.detach().t()
+        dh = (torch.cat(gs, 0).float() @ wr.detach()) * (torch.sigmoid(h_ref) * (1 + h_ref * (1 - torch.sigmoid(h_ref))))
+        full_dx = dh @ wc.detach()
+        dist.all_reduce(full_dx)
+        worst = max(worst, rel(x_s.grad, full_dx[rank * rs: (rank + 1) * rs]))
+    torch.cuda.synchronize()
+    check_status()
+    ok = worst < 4e-2
+    t = torch.tensor([int(ok)], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        print(f"tp world {world}: worst rel err {worst:.3e} ->", "OK" if t.item() else "MISMATCH")
+    dist.destroy_process_group()
+    sys.exit(0 if t.item() else 1)
+
+
+if __name__ == "__main__":
+    main()
