@@ -54,6 +54,17 @@ struct CommParams {
   const void* rs_residual;  // COMM 2: optional [chunk_rows, N] added to the result
   long long rs_ldd;
   uint32_t* cta_counter;    // local word used to find the last CTA of the grid
+  // COMM 3 (F5: expert all-to-all dispatch -> grouped GEMM). pt.buf[r] is rank r's expert-sorted row buffer
+  // [rows, d]; the first n_copy CTAs push this rank's routed rows (optionally scaled) straight into the owners'
+  // buffers and bump the owner's per-tile arrival counter; GEMM CTAs wait until a tile's counter reaches
+  // tile_expected[tile] before reading it.
+  const __nv_bfloat16* ep_x;     // [T, d] local tokens
+  const int* ep_dest_rank;       // [T*k]  (-1: dropped)
+  const int* ep_dest_row;        // [T*k]
+  const float* ep_row_scale;     // optional [T*k]
+  int ep_entries, ep_k, ep_d;
+  uint32_t* ep_arrive[SX_MAX_RANKS];   // peer-mapped arrival counters, one word per 128-row tile
+  const uint32_t* ep_tile_expected;    // local [m_blks] cumulative expected arrivals
 };
 
 struct GemmKernelParams {
@@ -128,7 +139,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
     tma_prefetch_desc(&p.tmA);
     tma_prefetch_desc(&p.tmB);
   }
-  const bool is_copy_cta = (COMM == 1) && ((int)blockIdx.x < p.cm.n_copy);
+  const bool is_copy_cta = (COMM == 1 || COMM == 3) && ((int)blockIdx.x < p.cm.n_copy);
   if (warp == 1 && !is_copy_cta) tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
   tc_fence_before();
   __syncthreads();
@@ -137,7 +148,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
 
   const int total_tiles = p.batch * p.m_blks * p.n_blks;
   // CTAs that run GEMM tiles: all of them, minus the copy CTAs of the all-gather form
-  const int cta0 = (COMM == 1) ? p.cm.n_copy : 0;
+  const int cta0 = (COMM == 1 || COMM == 3) ? p.cm.n_copy : 0;
   const int tile_first = (int)blockIdx.x - cta0;
   const int tile_step = (int)gridDim.x - cta0;
   // tile rotation so that every rank starts on rows it already has (COMM 1) / ends on rows it owns (COMM 2)
@@ -149,7 +160,41 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
     rot_m = ((p.cm.pt.rank + 1) % p.cm.pt.world) * (p.cm.chunk_rows / BM);
   }
 
-  if (is_copy_cta) {
+  if (is_copy_cta && COMM == 3) {
+    // ------------------------------------------------------------ expert dispatch CTAs (push rows to their owners)
+    const PeerTable& pt = p.cm.pt;
+    __shared__ int s_ok3;
+    // the owners clear their row buffers before this launch; tell everyone mine is ready, wait for theirs
+    if (blockIdx.x == 0) signal_all(pt, p.cm.sig_channel, p.cm.epoch);
+    const bool ready = wait_all(pt, p.cm.sig_channel, p.cm.epoch, p.status);
+    (void)s_ok3;
+    if (ready) {
+      const int d = p.cm.ep_d;
+      const int nw = p.cm.n_copy * (GEMM_THREADS / 32);
+      for (int e = blockIdx.x * (GEMM_THREADS / 32) + warp; e < p.cm.ep_entries; e += nw) {
+        const int dr = p.cm.ep_dest_rank[e];
+        if (dr < 0) continue;
+        const int row = p.cm.ep_dest_row[e];
+        const float sc = p.cm.ep_row_scale ? p.cm.ep_row_scale[e] : 1.f;
+        const __nv_bfloat16* src = p.cm.ep_x + (long long)(e / p.cm.ep_k) * d;
+        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(pt.buf[dr]) + (long long)row * d;
+        for (int c = lane * 8; c < d; c += 256) {
+          bf16x8 v = ld8(src + c);
+          if (p.cm.ep_row_scale) {
+            float f[8];
+            unpack8(v, f);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f[j] *= sc;
+            v = pack8(f);
+          }
+          st_peer_v4(dst + c, *reinterpret_cast<uint4*>(&v));
+        }
+        __threadfence_system();
+        __syncwarp();
+        if (lane == 0) red_release_sys_add(p.cm.ep_arrive[dr] + (row >> 7), 1u);
+      }
+    }
+  } else if (is_copy_cta) {
     // ------------------------------------------------------------ all-gather copy CTAs
     const PeerTable& pt = p.cm.pt;
     __shared__ int s_ok;
@@ -189,7 +234,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
       for (int t = tile_first; t < total_tiles && ok; t += tile_step) {
         int b, m_blk, n_blk;
         tile_coords(t, p.m_blks, p.n_blks, b, m_blk, n_blk);
-        if (COMM != 0) { m_blk = (m_blk + rot_m) % p.m_blks; n_blk = (n_blk + rot_n) % p.n_blks; }
+        if (COMM == 1 || COMM == 2) { m_blk = (m_blk + rot_m) % p.m_blks; n_blk = (n_blk + rot_n) % p.n_blks; }
         int bsel = b;
         if (p.tile_group) {
           bsel = p.tile_group[m_blk];
@@ -217,6 +262,15 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
             // rows were written by ordinary stores of the copy CTAs; order them before this thread's TMA reads
             asm volatile("fence.proxy.async;" ::: "memory");
           }
+        }
+        if (COMM == 3) {
+          if (!wait_flag_sys(p.cm.ep_arrive[p.cm.pt.rank] + m_blk, p.cm.ep_tile_expected[m_blk], p.cm.pt.timeout_ns,
+                             p.status)) {
+            *s_abort = 1;
+            ok = false;
+            break;
+          }
+          asm volatile("fence.proxy.async;" ::: "memory");
         }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, s_abort, p.status, ST_TIMEOUT_PRODUCER)) {
@@ -246,7 +300,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
       for (int t = tile_first; t < total_tiles && ok; t += tile_step) {
         int b, m_blk, n_blk;
         tile_coords(t, p.m_blks, p.n_blks, b, m_blk, n_blk);
-        if (COMM != 0) { m_blk = (m_blk + rot_m) % p.m_blks; n_blk = (n_blk + rot_n) % p.n_blks; }
+        if (COMM == 1 || COMM == 2) { m_blk = (m_blk + rot_m) % p.m_blks; n_blk = (n_blk + rot_n) % p.n_blks; }
         if (p.tile_group && p.tile_group[m_blk] < 0) continue;
         int k0 = 0, k1 = p.K;
         if (p.k_ranges) {
@@ -294,7 +348,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
     for (int t = tile_first; t < total_tiles && ok; t += tile_step) {
       int b, m_blk, n_blk;
       tile_coords(t, p.m_blks, p.n_blks, b, m_blk, n_blk);
-        if (COMM != 0) { m_blk = (m_blk + rot_m) % p.m_blks; n_blk = (n_blk + rot_n) % p.n_blks; }
+        if (COMM == 1 || COMM == 2) { m_blk = (m_blk + rot_m) % p.m_blks; n_blk = (n_blk + rot_n) % p.n_blks; }
       if (p.tile_group && p.tile_group[m_blk] < 0) continue;
       bool empty_k = false;
       if (p.k_ranges) empty_k = (p.k_ranges[2 * b + 1] <= p.k_ranges[2 * b]);
@@ -544,7 +598,8 @@ static int gemm_launch(const SxGemmArgs* a, const SxGemmCommArgs* cm, cudaStream
   int grid = (int)(tiles < sms ? tiles : sms);
   const int am = a->a_mn != 0, bm = a->b_mn != 0;
   if (cm) {
-    if (am || a->batch != 1 || a->tile_group || a->k_ranges) return -30;
+    if (am || a->batch != 1 || a->k_ranges) return -30;
+    if ((cm->mode == 4) != (a->tile_group != nullptr)) return -30;
     CommParams& c = kp.cm;
     for (int i = 0; i < SX_MAX_RANKS; ++i) {
       c.pt.buf[i] = cm->peers.buf[i];
@@ -586,6 +641,23 @@ static int gemm_launch(const SxGemmArgs* a, const SxGemmCommArgs* cm, cudaStream
       if (cm->chunk_rows * cm->peers.world != a->M || (cm->chunk_rows % BM) || a->out_fp32 || (a->N % 8)) return -32;
       if (!bm) return BN == 256 ? launch_cfg<256, false, false, 2>(kp, grid, st) : launch_cfg<128, false, false, 2>(kp, grid, st);
       return BN == 256 ? launch_cfg<256, false, true, 2>(kp, grid, st) : launch_cfg<128, false, true, 2>(kp, grid, st);
+    }
+    else if (cm->mode == 4) {
+      if (cm->ep_d % 8) return -34;
+      c.ep_x = reinterpret_cast<const __nv_bfloat16*>(cm->ep_x);
+      c.ep_dest_rank = cm->ep_dest_rank;
+      c.ep_dest_row = cm->ep_dest_row;
+      c.ep_row_scale = cm->ep_row_scale;
+      c.ep_entries = cm->ep_entries;
+      c.ep_k = cm->ep_k;
+      c.ep_d = cm->ep_d;
+      for (int i = 0; i < SX_MAX_RANKS; ++i) c.ep_arrive[i] = reinterpret_cast<uint32_t*>(cm->ep_arrive[i]);
+      c.ep_tile_expected = reinterpret_cast<const uint32_t*>(cm->ep_tile_expected);
+      c.n_copy = cm->n_copy > 0 ? cm->n_copy : 16;
+      if (grid + c.n_copy > sms) grid = sms - c.n_copy;
+      grid += c.n_copy;
+      if (!bm) return BN == 256 ? launch_cfg<256, false, false, 3>(kp, grid, st) : launch_cfg<128, false, false, 3>(kp, grid, st);
+      return BN == 256 ? launch_cfg<256, false, true, 3>(kp, grid, st) : launch_cfg<128, false, true, 3>(kp, grid, st);
     }
     return -33;
   }

@@ -129,6 +129,15 @@ typedef struct SxGemmCommArgs {
   unsigned rs_expected;  // mode 3: counter value that marks a row block complete (previous value + 4 * ceil(N/BN) * world)
   void* rs_out; const void* rs_residual; long long rs_ldd;
   void* cta_counter;   // local uint32 word, zeroed once
+  // mode 4 (F5): expert all-to-all dispatch fused with the grouped GEMM (args->tile_group must be set; args->A is
+  // peers.buf[rank], the local expert-sorted row buffer that every rank pushes into). Entry e = (token e / ep_k,
+  // choice e % ep_k) goes to row ep_dest_row[e] of rank ep_dest_rank[e] (-1: dropped), scaled by ep_row_scale[e]
+  // when given. ep_arrive[r]: rank r's arrival counters (one uint32 per 128-row tile, symmetric memory);
+  // ep_tile_expected: local cumulative arrival targets per tile.
+  const void* ep_x; const int* ep_dest_rank; const int* ep_dest_row; const float* ep_row_scale;
+  int ep_entries, ep_k, ep_d;
+  void* ep_arrive[8];
+  const void* ep_tile_expected;
 } SxGemmCommArgs;
 int sx_gemm_bf16_comm(const SxGemmArgs* args, const SxGemmCommArgs* comm, cudaStream_t stream);
 
