@@ -29,7 +29,10 @@ class SxGemmCommArgs(C.Structure):
     _fields_ = [("peers", SxPeers), ("mode", C.c_int), ("flags", C.c_void_p), ("epoch", C.c_uint), ("n_copy", C.c_int),
                 ("chunk_rows", C.c_int), ("sub_rows", C.c_int), ("sig_channel", C.c_int), ("done_channel", C.c_int),
                 ("counter_word", C.c_int), ("rs_expected", C.c_uint), ("rs_out", C.c_void_p),
-                ("rs_residual", C.c_void_p), ("rs_ldd", C.c_longlong), ("cta_counter", C.c_void_p)]
+                ("rs_residual", C.c_void_p), ("rs_ldd", C.c_longlong), ("cta_counter", C.c_void_p),
+                ("ep_x", C.c_void_p), ("ep_dest_rank", C.c_void_p), ("ep_dest_row", C.c_void_p),
+                ("ep_row_scale", C.c_void_p), ("ep_entries", C.c_int), ("ep_k", C.c_int), ("ep_d", C.c_int),
+                ("ep_arrive", C.c_void_p * 8), ("ep_tile_expected", C.c_void_p)]
 
 
 def _gemm_args(a, b, out, b_mn):
