@@ -200,13 +200,25 @@ __global__ void __launch_bounds__(512) allgather_pull_kernel(PeerTable pt, uint8
     if (!wait_all(pt, channel, epoch, status)) return;
   }
   const long long nvec = shard_bytes >> 4;
+  constexpr int U = 8;  // 16-byte loads in flight per thread: NVLink latency needs megabytes in flight per GPU
+  const long long stride = (long long)gridDim.x * blockDim.x;
   for (int rr = 0; rr < pt.world; ++rr) {
     const int r = (pt.rank + rr) % pt.world;  // start with the local shard, then rotate so peers are hit evenly
     const uint8_t* src = reinterpret_cast<const uint8_t*>(pt.buf[r]) + src_off;
     uint8_t* d = dst + (long long)r * shard_bytes;
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
-         i += (long long)gridDim.x * blockDim.x)
-      *reinterpret_cast<uint4*>(d + (i << 4)) = ld_peer_v4(src + (i << 4));
+    for (long long i0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; i0 < nvec; i0 += stride * U) {
+      uint4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < nvec) v[u] = ld_peer_v4(src + (i << 4));
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < nvec) *reinterpret_cast<uint4*>(d + (i << 4)) = v[u];
+      }
+    }
   }
 }
 

@@ -202,6 +202,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
     const int subs = p.cm.chunk_rows / p.cm.sub_rows;
     const long long sub_bytes = (long long)p.cm.sub_rows * p.cm.row_bytes;
     bool ok = true;
+    int copy_uses = 0;  // pieces issued so far by this CTA (gives ring slot and mbarrier parity)
     for (int rr = 1; rr < pt.world && ok; ++rr) {
       const int r = (pt.rank + rr) % pt.world;
       if (threadIdx.x == 0)
@@ -210,17 +211,52 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
       ok = s_ok != 0;
       __syncthreads();
       if (!ok) break;
-      for (int sub = blockIdx.x; sub < subs; sub += p.cm.n_copy) {
+      // One thread drives bulk copies peer -> shared -> local through a ring of 32 KB pieces in the (otherwise
+      // unused) tile staging area, NBUF pieces in flight per CTA, so that a handful of CTAs keep NVLink full.
+      constexpr int PIECE = 32768, NBUF = 4;
+      for (int sub = blockIdx.x; sub < subs && ok; sub += p.cm.n_copy) {
         const long long off = ((long long)r * p.cm.chunk_rows + (long long)sub * p.cm.sub_rows) * p.cm.row_bytes;
         const uint8_t* src = reinterpret_cast<const uint8_t*>(pt.buf[r]) + off;
         uint8_t* dst = p.cm.full + off;
-        for (long long i = threadIdx.x; i < (sub_bytes >> 4); i += GEMM_THREADS) {
-          // 4 loads in flight per thread
-          *reinterpret_cast<uint4*>(dst + (i << 4)) = ld_peer_v4(src + (i << 4));
+        if (threadIdx.x == 0) {
+          const int npieces = (int)((sub_bytes + PIECE - 1) / PIECE);
+          int issued = 0, done = 0;
+          bool good = true;
+          while (done < npieces && good) {
+            while (issued < npieces && issued - done < NBUF) {
+              const int bidx = copy_uses % NBUF;
+              const long long o = (long long)issued * PIECE;
+              const uint32_t bytes = (uint32_t)min((long long)PIECE, sub_bytes - o);
+              mbar_expect_tx(&full_bar[bidx], bytes);
+              asm volatile(
+                  "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                      smem_u32(smem + bidx * PIECE)),
+                  "l"(src + o), "r"(bytes), "r"(smem_u32(&full_bar[bidx]))
+                  : "memory");
+              ++issued;
+              ++copy_uses;
+            }
+            const int use = copy_uses - (issued - done);     // global index of the piece being retired
+            const int bidx = use % NBUF;
+            if (!mbar_wait(&full_bar[bidx], (use / NBUF) & 1, s_abort, p.status, ST_TIMEOUT_SIGNAL)) { good = false; break; }
+            const long long o = (long long)done * PIECE;
+            const uint32_t bytes = (uint32_t)min((long long)PIECE, sub_bytes - o);
+            asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst + o),
+                         "r"(smem_u32(smem + bidx * PIECE)), "r"(bytes)
+                         : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            ++done;
+          }
+          asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+          asm volatile("fence.proxy.async;" ::: "memory");
+          __threadfence();
+          if (good) st_release_gpu(&p.cm.flags[r * subs + sub], p.cm.epoch);
+          s_ok = good ? 1 : 0;
         }
-        __threadfence();
         __syncthreads();
-        if (threadIdx.x == 0) st_release_gpu(&p.cm.flags[r * subs + sub], p.cm.epoch);
+        ok = s_ok != 0;
+        __syncthreads();
       }
     }
   } else

@@ -224,7 +224,7 @@ class ZeroEngine:
         for bi in order:
             b0, b1 = self.bounds[bi]
             sz = (b1 - b0) // self.world
-            self.sg.allgather_pull(self.pshard, self.fp.flat[b0:b1], sz * es, self.shard_off[bi] * es, grid=24,
+            self.sg.allgather_pull(self.pshard, self.fp.flat[b0:b1], sz * es, self.shard_off[bi] * es, grid=48,
                                    stream=sptr)
             ev = torch.cuda.Event()
             ev.record(cs)
