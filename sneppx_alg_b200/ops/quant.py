@@ -110,3 +110,63 @@ def dequant_int4(packed, scales, dtype=torch.bfloat16):
     hi = (packed >> 4).to(torch.int32) - 8
     q = torch.stack([lo, hi], dim=-1).view(N, K).float()
     return (q * scales.repeat_interleave(128, dim=1)).to(dtype)
+
+
+# ----------------------------------------------------------------------------- Q2 dequant-GEMM
+def gemm_dequant(x, qweight, scales, mode="fp8", bias=None):
+    """y = x @ dequant(W)^T. x bf16 [.., K]; mode 'fp8': qweight float8_e4m3fn/uint8 [N, K], scales [N/128, K/128];
+    mode 'int4': qweight uint8 [N, K/2], scales [N, K/128]. CUDA: weights are expanded to bf16 inside the GEMM."""
+    K = x.shape[-1]
+    x2 = x.reshape(-1, K)
+    N = qweight.shape[0]
+    if x.is_cuda and x.dtype == torch.bfloat16 and _lib.available() and K % 128 == 0:
+        x2 = x2.contiguous()
+        out = torch.empty(x2.shape[0], N, dtype=torch.bfloat16, device=x.device)
+        b = bias.float().contiguous() if bias is not None else None
+        _lib.call("sx_gemm_dequant", ptr(x2), c_ll(x2.stride(0)), ptr(qweight), ptr(scales.contiguous()), ptr(b),
+                  ptr(out), c_ll(out.stride(0)), c_int(x2.shape[0]), c_int(N), c_int(K),
+                  c_int(0 if mode == "fp8" else 1), ptr(_lib.status_word(x.device)), stream())
+        return out.view(*x.shape[:-1], N)
+    w = dequant_fp8(qweight.view(torch.float8_e4m3fn) if qweight.dtype == torch.uint8 else qweight, scales, "128x128",
+                    torch.float32) if mode == "fp8" else dequant_int4(qweight, scales, torch.float32)
+    y = x2.float() @ w.t()
+    if bias is not None:
+        y = y + bias.float()
+    return y.to(x.dtype).view(*x.shape[:-1], N)
+
+
+class QuantizedLinear(torch.nn.Module):
+    """Weight-only quantised linear layer (fp8 e4m3 128x128-block scales, or INT4 group 128); the reference's
+    ``QuantizedLinear`` (interface_bindings/quantization.py) dequantises in NumPy before a dense matmul."""
+
+    def __init__(self, weight, mode="fp8", bias=None):
+        super().__init__()
+        self.mode = mode
+        self.out_features, self.in_features = weight.shape
+        w = weight.detach().to(torch.bfloat16)
+        if mode == "fp8":
+            q, s = quant_fp8_128x128(w)
+            q = q.view(torch.uint8)
+        else:
+            q, s = quant_int4(w)
+        self.register_buffer("qweight", q)
+        self.register_buffer("scales", s)
+        self.bias = None if bias is None else torch.nn.Parameter(bias.detach().clone(), requires_grad=False)
+
+    @classmethod
+    def from_linear(cls, lin, mode="fp8"):
+        return cls(lin.weight, mode, getattr(lin, "bias", None))
+
+    def forward(self, x):
+        return gemm_dequant(x, self.qweight, self.scales, self.mode, self.bias)
+
+
+def quantize_model_(model, mode="fp8", min_features=128, skip=("lm_head", "router")):
+    """Replace every large ``Linear`` by a ``QuantizedLinear`` in place (serving)."""
+    from ..nn.modules import Linear
+    for name, mod in list(model.named_modules()):
+        for cname, child in list(mod.named_children()):
+            if isinstance(child, (Linear, torch.nn.Linear)) and child.weight.shape[1] % 128 == 0 \
+                    and min(child.weight.shape) >= min_features and not any(s in cname for s in skip):
+                setattr(mod, cname, QuantizedLinear.from_linear(child, mode))
+    return model

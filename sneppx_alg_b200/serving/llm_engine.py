@@ -1,0 +1,214 @@
+"""Continuous-batching inference engine with a paged KV cache (real KV reuse, chunked prefill, prefix caching).
+
+Each ``step()`` admits waiting requests while KV blocks and batch slots allow (FCFS or priority), prefills at
+most ``max_prefill_tokens`` prompt tokens (one sequence at a time through the flash-attention kernel, writing K/V
+into the block pool), then decodes one token for every running sequence in a single batch through the paged decode
+kernel. The reference's scheduler has the same admission rules (max_batch_size 32, FCFS / priority;
+interface_bindings/continuous_batching.py:64-179) but re-runs the whole prefix every token; its C serving engine
+(net/http/serving_engine.c) holds the queue / metrics logic mirrored in ``csrc/host/serving_core.cpp``.
+"""
+from __future__ import annotations
+
+import heapq
+import itertools
+import time
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional
+
+import torch
+
+from ..ops import functional as ops
+from ..ops import paged
+from .generation import apply_repetition_penalty, sample_from_logits
+from .kv_cache import PagedKVCache
+
+
+@dataclass
+class SamplingParams:
+    max_new_tokens: int = 64
+    do_sample: bool = False
+    temperature: float = 1.0
+    top_k: int = 0
+    top_p: float = 1.0
+    repetition_penalty: float = 1.0
+    eos_token_id: Optional[int] = None
+    stop_token_ids: tuple = ()
+
+
+@dataclass(order=True)
+class Request:
+    priority: int
+    arrival: float
+    req_id: int = field(compare=False)
+    prompt: List[int] = field(compare=False)
+    params: SamplingParams = field(compare=False, default_factory=SamplingParams)
+    output: List[int] = field(compare=False, default_factory=list)
+    prefilled: int = field(compare=False, default=0)
+    first_token_time: Optional[float] = field(compare=False, default=None)
+    finish_time: Optional[float] = field(compare=False, default=None)
+    on_token: Optional[Callable] = field(compare=False, default=None)
+
+    @property
+    def tokens(self):
+        return self.prompt + self.output
+
+
+class LlamaPagedRunner:
+    """Runs a Llama-family model (``models/llama.py``) against the paged cache: fused QKV GEMM -> RoPE + cache append
+    kernel -> flash attention (prefill) or paged decode attention -> rest of the block."""
+
+    def __init__(self, model, cache: PagedKVCache):
+        self.model, self.cache = model, cache
+        cfg = model.config
+        self.H, self.Hk, self.D = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
+
+    def _layers(self, x, attn_fn):
+        m = self.model
+        delta, resid = x, None
+        for li, layer in enumerate(m.layers):
+            if resid is None:
+                h, resid = layer.attn_norm(delta), delta
+            else:
+                h, resid = layer.attn_norm(delta, residual=resid)
+            qkv = layer.attn.qkv_proj(h)
+            o = attn_fn(li, qkv)
+            a = layer.attn.o_proj(o)
+            h, resid = layer.mlp_norm(a, residual=resid)
+            delta = layer.mlp(h)
+        h, _ = m.norm(delta, residual=resid)
+        return h
+
+    @torch.no_grad()
+    def prefill(self, seq_id: int, tokens: List[int], start: int):
+        """Process prompt tokens [start, len) of one sequence; returns logits of the last position."""
+        m, H, Hk, D = self.model, self.H, self.Hk, self.D
+        dev = m.embedding.weight.device
+        ids = torch.tensor(tokens[start:], dtype=torch.long, device=dev)
+        T = ids.numel()
+        slots = torch.tensor(self.cache.reserve(seq_id, T), dtype=torch.int32, device=dev)
+        pos = torch.arange(start, start + T, dtype=torch.int32, device=dev)
+        cos, sin = m.rope(dev, start + T)
+
+        def attn(li, qkv):
+            q2 = qkv.view(T, (H + 2 * Hk) * D)
+            paged.kv_append_(q2, cos, sin, pos, slots, self.cache.k[li], self.cache.v[li], H, Hk, D)
+            q = q2[:, : H * D].view(1, T, H, D)
+            if start == 0:
+                k = q2[:, H * D: (H + Hk) * D].view(1, T, Hk, D)
+                v = q2[:, (H + Hk) * D:].view(1, T, Hk, D)
+            else:   # later chunk / cached prefix: keys and values of the whole sequence come from the pool
+                kk, vv = self.cache.gather(li, seq_id, start + T)
+                k, v = kk.unsqueeze(0), vv.unsqueeze(0)
+            return ops.attention(q, k, v, causal=True).reshape(1, T, H * D)
+
+        h = self._layers(m.embedding(ids).unsqueeze(0), attn)
+        return ops.linear(h[:, -1], m.head_weight()).float()
+
+    @torch.no_grad()
+    def decode(self, seq_ids: List[int], last_tokens: List[int]):
+        """One token for each running sequence; returns logits [B, V]."""
+        m, H, Hk, D = self.model, self.H, self.Hk, self.D
+        dev = m.embedding.weight.device
+        B = len(seq_ids)
+        pos_list = [self.cache.lens[s] for s in seq_ids]
+        slots = torch.tensor([self.cache.reserve(s, 1)[0] for s in seq_ids], dtype=torch.int32, device=dev)
+        pos = torch.tensor(pos_list, dtype=torch.int32, device=dev)
+        bt, lens = self.cache.block_table_tensor(seq_ids, dev)
+        cos, sin = m.rope(dev, max(pos_list) + 1)
+        ids = torch.tensor(last_tokens, dtype=torch.long, device=dev)
+
+        def attn(li, qkv):
+            q2 = qkv.view(B, (H + 2 * Hk) * D)
+            paged.kv_append_(q2, cos, sin, pos, slots, self.cache.k[li], self.cache.v[li], H, Hk, D)
+            q = q2[:, : H * D].view(B, H, D)
+            return paged.paged_decode(q, self.cache.k[li], self.cache.v[li], bt, lens).reshape(B, 1, H * D)
+
+        h = self._layers(m.embedding(ids).unsqueeze(1), attn)
+        return ops.linear(h[:, -1], m.head_weight()).float()
+
+
+class LLMEngine:
+    def __init__(self, model, num_blocks=2048, block_size=16, max_batch_size=32, max_prefill_tokens=8192,
+                 policy="fcfs", enable_prefix_cache=True, runner=None):
+        cfg = model.config
+        p = next(model.parameters())
+        self.cache = PagedKVCache(cfg.num_hidden_layers, num_blocks, block_size, cfg.num_key_value_heads, cfg.head_dim,
+                                  dtype=p.dtype, device=p.device, enable_prefix_cache=enable_prefix_cache)
+        self.runner = runner or LlamaPagedRunner(model, self.cache)
+        self.max_batch_size, self.max_prefill_tokens, self.policy = max_batch_size, max_prefill_tokens, policy
+        self.waiting: List[Request] = []
+        self.running: Dict[int, Request] = {}
+        self.finished: Dict[int, Request] = {}
+        self._ids = itertools.count()
+        self.generator = None
+        self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "cached_prefix_tokens": 0, "steps": 0}
+
+    # ------------------------------------------------------------------ API
+    def submit(self, prompt: List[int], params: Optional[SamplingParams] = None, priority: int = 0, on_token=None) -> int:
+        rid = next(self._ids)
+        req = Request(priority if self.policy == "priority" else 0, time.perf_counter(), rid, list(prompt),
+                      params or SamplingParams(), on_token=on_token)
+        heapq.heappush(self.waiting, req)
+        return rid
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    def _blocks_needed(self, req: Request) -> int:
+        bs = self.cache.block_size
+        return (len(req.prompt) + req.params.max_new_tokens + bs - 1) // bs
+
+    def _emit(self, req: Request, logits_row):
+        p = req.params
+        hist = torch.tensor(req.tokens, device=logits_row.device).unsqueeze(0)
+        lg = apply_repetition_penalty(logits_row.unsqueeze(0), hist, p.repetition_penalty)
+        tok = int(sample_from_logits(lg, p.do_sample, p.temperature, p.top_k, p.top_p, self.generator)[0])
+        now = time.perf_counter()
+        if req.first_token_time is None:
+            req.first_token_time = now
+        req.output.append(tok)
+        if req.on_token:
+            req.on_token(req.req_id, tok)
+        stop = (p.eos_token_id is not None and tok == p.eos_token_id) or tok in p.stop_token_ids
+        if stop or len(req.output) >= p.max_new_tokens:
+            req.finish_time = now
+            self.cache.free_sequence(req.req_id, req.tokens)
+            self.running.pop(req.req_id, None)
+            self.finished[req.req_id] = req
+
+    def step(self):
+        """One scheduler iteration: admit + prefill, then one decode step for all running sequences."""
+        self.stats["steps"] += 1
+        budget = self.max_prefill_tokens
+        while self.waiting and len(self.running) < self.max_batch_size and budget > 0:
+            req = self.waiting[0]
+            if self._blocks_needed(req) > self.cache.pool.num_free:
+                break
+            heapq.heappop(self.waiting)
+            cached = self.cache.add_sequence(req.req_id, req.prompt)
+            self.stats["cached_prefix_tokens"] += cached
+            logits = self.runner.prefill(req.req_id, req.prompt, cached)
+            n = len(req.prompt) - cached
+            budget -= n
+            self.stats["prefill_tokens"] += n
+            self.running[req.req_id] = req
+            self._emit(req, logits[0])
+        active = [r for r in self.running.values() if r.output]
+        if active:
+            ids = [r.req_id for r in active]
+            logits = self.runner.decode(ids, [r.output[-1] for r in active])
+            self.stats["decode_tokens"] += len(active)
+            for r, row in zip(active, logits):
+                self._emit(r, row)
+
+    def run_until_done(self, max_steps: int = 1_000_000):
+        n = 0
+        while self.has_work() and n < max_steps:
+            self.step()
+            n += 1
+        return self.finished
+
+    def generate(self, prompts: List[List[int]], params: Optional[SamplingParams] = None) -> List[List[int]]:
+        ids = [self.submit(p, params) for p in prompts]
+        self.run_until_done()
+        return [self.finished[i].output for i in ids]
