@@ -40,11 +40,11 @@ def test_kv_append_and_paged_decode():
         slot = (tables[b, :nb].cuda().repeat_interleave(bs)[:n] * bs + pos % bs).to(torch.int32)
         ref_in = qkv.clone()
         paged.kv_append_(qkv, cos, sin, pos, slot, kc, vc, Hq, Hkv, D)
-        paged.kv_append_reference(ref_in.float(), cos, sin, pos, slot, kc_ref_f := kc_ref.float(), vc_ref_f := vc_ref.float(),
-                                  Hq, Hkv, D)
+        ref_f, kc_ref_f, vc_ref_f = ref_in.float(), kc_ref.float(), vc_ref.float()
+        paged.kv_append_reference(ref_f, cos, sin, pos, slot, kc_ref_f, vc_ref_f, Hq, Hkv, D)
         kc_ref.copy_(kc_ref_f)
         vc_ref.copy_(vc_ref_f)
-        assert _rel(qkv, ref_in.float()) < 1e-2
+        assert _rel(qkv, ref_f) < 1e-2
     assert _rel(kc, kc_ref) < 1e-2 and _rel(vc, vc_ref) < 1e-2
     q = torch.randn(B, Hq, D, device="cuda", dtype=torch.bfloat16)
     sl = torch.tensor(lens, dtype=torch.int32, device="cuda")
