@@ -143,7 +143,7 @@ def validate_checkpoint(path: str) -> bool:
 # ----------------------------------------------------------------------------- tensor-level helpers
 def _to_bytes(t: torch.Tensor) -> bytes:
     t = t.detach().cpu().contiguous()
-    return t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
+    return t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""
 
 
 def save_tensors(path: str, tensors: Dict[str, torch.Tensor], metadata: Optional[dict] = None, saver=None):
