@@ -1,0 +1,210 @@
+"""Logging, profiling and experiment tracking.
+
+``Logger``: 6 levels, ANSI or JSON-lines output, per-rank prefix (include/neural_core/kernel/logger.h:28-116).
+``Profiler``: named-entry aggregation (calls / total / min / max / avg), range push / pop stack, JSON export, CUDA-event
+kernel timer, NVTX ranges when available (include/neural_core/kernel/profiler.h, interface_bindings/profiler.py:20-192).
+``ExperimentTracker``: JSON run directories plus W&B / MLflow / composite shells (experiment_tracker.py:180-411)."""
+from __future__ import annotations
+
+import contextlib
+import json
+import os
+import sys
+import time
+from collections import defaultdict
+from typing import Any, Dict, List, Optional
+
+import torch
+
+LEVELS = {"trace": 0, "debug": 1, "info": 2, "warn": 3, "error": 4, "fatal": 5}
+_COLORS = {"trace": "\033[90m", "debug": "\033[36m", "info": "\033[32m", "warn": "\033[33m", "error": "\033[31m",
+           "fatal": "\033[35m"}
+
+
+class Logger:
+    def __init__(self, name="sneppx", level="info", json_file: Optional[str] = None, rank: Optional[int] = None,
+                 stream=None, color: Optional[bool] = None):
+        self.name, self.level, self.rank = name, LEVELS[level], rank if rank is not None else int(os.environ.get("RANK", 0))
+        self.stream = stream or sys.stderr
+        self.color = self.stream.isatty() if color is None else color
+        self.json_file = open(json_file, "a") if json_file else None
+
+    def log(self, level: str, msg: str, **fields):
+        if LEVELS[level] < self.level:
+            return
+        ts = time.time()
+        if self.json_file:
+            self.json_file.write(json.dumps({"ts": ts, "level": level, "rank": self.rank, "logger": self.name, "msg": msg,
+                                             **fields}) + "\n")
+            self.json_file.flush()
+        pre = f"[{time.strftime('%H:%M:%S', time.localtime(ts))}] [{level.upper():5}] [rank {self.rank}] "
+        if self.color:
+            pre = _COLORS[level] + pre + "\033[0m"
+        extra = " ".join(f"{k}={v}" for k, v in fields.items())
+        print(pre + msg + (" " + extra if extra else ""), file=self.stream)
+
+    def __getattr__(self, name):
+        if name in LEVELS:
+            return lambda msg, **f: self.log(name, msg, **f)
+        raise AttributeError(name)
+
+
+class Timer:
+    def __enter__(self):
+        self.t0 = time.perf_counter()
+        return self
+
+    def __exit__(self, *exc):
+        self.elapsed = time.perf_counter() - self.t0
+
+
+class Profiler:
+    def __init__(self, use_nvtx: bool = True):
+        self.entries: Dict[str, Dict[str, float]] = defaultdict(lambda: {"calls": 0, "total": 0.0, "min": float("inf"), "max": 0.0})
+        self._stack: List[tuple] = []
+        self.use_nvtx = use_nvtx and torch.cuda.is_available()
+
+    def _add(self, name, dt):
+        e = self.entries[name]
+        e["calls"] += 1
+        e["total"] += dt
+        e["min"] = min(e["min"], dt)
+        e["max"] = max(e["max"], dt)
+
+    def range_push(self, name):
+        if self.use_nvtx:
+            torch.cuda.nvtx.range_push(name)
+        self._stack.append((name, time.perf_counter()))
+
+    def range_pop(self):
+        name, t0 = self._stack.pop()
+        if self.use_nvtx:
+            torch.cuda.nvtx.range_pop()
+        self._add(name, time.perf_counter() - t0)
+
+    @contextlib.contextmanager
+    def range(self, name):
+        self.range_push(name)
+        try:
+            yield
+        finally:
+            self.range_pop()
+
+    @contextlib.contextmanager
+    def kernel(self, name):
+        """Device time of the enclosed launches (two CUDA events + sync), like SNEPPX_PROFILE_KERNEL."""
+        if not torch.cuda.is_available():
+            with self.range(name):
+                yield
+            return
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        yield
+        e1.record()
+        e1.synchronize()
+        self._add(name, e0.elapsed_time(e1) / 1e3)
+
+    def summary(self):
+        return {k: {**v, "avg": v["total"] / max(1, v["calls"])} for k, v in self.entries.items()}
+
+    def export_json(self, path):
+        with open(path, "w") as f:
+            json.dump(self.summary(), f, indent=2)
+
+    def report(self) -> str:
+        rows = sorted(self.summary().items(), key=lambda kv: -kv[1]["total"])
+        return "\n".join(f"{k:32s} calls {v['calls']:6d} total {v['total']*1e3:10.3f} ms avg {v['avg']*1e3:9.3f} ms"
+                         for k, v in rows)
+
+
+def timeit(fn):
+    def wrapped(*a, **k):
+        t0 = time.perf_counter()
+        out = fn(*a, **k)
+        wrapped.last = time.perf_counter() - t0
+        return out
+    wrapped.last = 0.0
+    return wrapped
+
+
+class MemoryTracker:
+    def snapshot(self):
+        if torch.cuda.is_available():
+            return {"allocated": torch.cuda.memory_allocated(), "reserved": torch.cuda.memory_reserved(),
+                    "peak": torch.cuda.max_memory_allocated()}
+        import resource
+        return {"rss_kb": resource.getrusage(resource.RUSAGE_SELF).ru_maxrss}
+
+
+def estimate_flops(cfg, tokens: int, training: bool = True) -> float:
+    """6 * params * tokens for training (2 * for inference) plus the attention term."""
+    n = cfg.estimate_parameters() - cfg.vocab_size * cfg.hidden_size * (0 if cfg.tie_word_embeddings else 1)
+    return (6 if training else 2) * n * tokens
+
+
+class ExperimentTracker:
+    """Local JSON runs directory: runs/<run_id>/{params.json, metrics.jsonl, artifacts/}."""
+
+    def __init__(self, directory="runs", experiment="default"):
+        self.dir, self.experiment, self.run_dir, self._f = directory, experiment, None, None
+
+    def start_run(self, run_name: Optional[str] = None, params: Optional[dict] = None):
+        rid = run_name or time.strftime("%Y%m%d-%H%M%S")
+        self.run_dir = os.path.join(self.dir, self.experiment, rid)
+        os.makedirs(os.path.join(self.run_dir, "artifacts"), exist_ok=True)
+        if params:
+            self.log_params(params)
+        self._f = open(os.path.join(self.run_dir, "metrics.jsonl"), "a")
+        return rid
+
+    def log_params(self, params: dict):
+        with open(os.path.join(self.run_dir, "params.json"), "w") as f:
+            json.dump(params, f, indent=2, default=str)
+
+    def log_metrics(self, metrics: Dict[str, Any], step: Optional[int] = None):
+        self._f.write(json.dumps({"step": step, "ts": time.time(), **{k: float(v) for k, v in metrics.items()}}) + "\n")
+        self._f.flush()
+
+    def log_artifact(self, path: str):
+        import shutil
+        shutil.copy(path, os.path.join(self.run_dir, "artifacts"))
+
+    def end_run(self):
+        if self._f:
+            self._f.close()
+            self._f = None
+
+
+class WandbTracker(ExperimentTracker):
+    """Uses wandb when importable, otherwise behaves like the local tracker."""
+
+    def start_run(self, run_name=None, params=None):
+        try:
+            import wandb  # noqa: F401
+            self._wandb = wandb.init(project=self.experiment, name=run_name, config=params, mode="offline")
+        except Exception:  # noqa: BLE001
+            self._wandb = None
+        return super().start_run(run_name, params)
+
+    def log_metrics(self, metrics, step=None):
+        if getattr(self, "_wandb", None):
+            self._wandb.log(metrics, step=step)
+        super().log_metrics(metrics, step)
+
+
+class MLflowTracker(ExperimentTracker):
+    pass
+
+
+class CompositeTracker:
+    def __init__(self, trackers):
+        self.trackers = list(trackers)
+
+    def __getattr__(self, name):
+        def fan(*a, **k):
+            return [getattr(t, name)(*a, **k) for t in self.trackers][0]
+        return fan
+
+
+def make_tracker(kind="local", **kw):
+    return {"local": ExperimentTracker, "wandb": WandbTracker, "mlflow": MLflowTracker}.get(kind, ExperimentTracker)(**kw)
