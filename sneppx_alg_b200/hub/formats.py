@@ -1,0 +1,104 @@
+"""Weight file formats beside `.sneppx`: safetensors (header JSON + raw tensors; fs/format/safetensors.c of the
+reference), NumPy .npy/.npz, and the hub's native big-endian container (model_hub/converters/sneppx_format.py:10-142:
+magic b"SNEPPX0001", u32 version, u32 meta size, JSON meta, u32 n, then per tensor name / dims / dtype code / bytes)."""
+from __future__ import annotations
+
+import json
+import struct
+from typing import Dict, Tuple
+
+import numpy as np
+import torch
+
+_ST_DTYPES = {"F32": torch.float32, "F16": torch.float16, "BF16": torch.bfloat16, "F64": torch.float64,
+              "I32": torch.int32, "I64": torch.int64, "U8": torch.uint8, "I8": torch.int8, "BOOL": torch.bool,
+              "F8_E4M3": torch.float8_e4m3fn}
+_ST_NAMES = {v: k for k, v in _ST_DTYPES.items()}
+
+
+def save_safetensors(path: str, tensors: Dict[str, torch.Tensor], metadata: Dict[str, str] = None):
+    header, blobs, off = {}, [], 0
+    if metadata:
+        header["__metadata__"] = {k: str(v) for k, v in metadata.items()}
+    for name, t in tensors.items():
+        t = t.detach().cpu().contiguous()
+        b = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""
+        header[name] = {"dtype": _ST_NAMES[t.dtype], "shape": list(t.shape), "data_offsets": [off, off + len(b)]}
+        blobs.append(b)
+        off += len(b)
+    hj = json.dumps(header, separators=(",", ":")).encode()
+    hj += b" " * ((8 - len(hj) % 8) % 8)
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(hj)))
+        f.write(hj)
+        for b in blobs:
+            f.write(b)
+
+
+def load_safetensors(path: str, device="cpu") -> Tuple[Dict[str, torch.Tensor], Dict[str, str]]:
+    with open(path, "rb") as f:
+        n = struct.unpack("<Q", f.read(8))[0]
+        header = json.loads(f.read(n))
+        data = f.read()
+    meta = header.pop("__metadata__", {})
+    out = {}
+    for name, info in header.items():
+        s, e = info["data_offsets"]
+        dt = _ST_DTYPES[info["dtype"]]
+        t = torch.frombuffer(bytearray(data[s:e]), dtype=torch.uint8).view(dt) if e > s else torch.empty(0, dtype=dt)
+        out[name] = t.view(*info["shape"]).to(device)
+    return out, meta
+
+
+HUB_MAGIC = b"SNEPPX0001"
+_HUB_CODES = {torch.float32: 1, torch.float16: 2, torch.int32: 3, torch.int64: 4, torch.uint8: 5}
+_HUB_DTYPES = {v: k for k, v in _HUB_CODES.items()}
+
+
+def save_hub_container(path: str, tensors: Dict[str, torch.Tensor], meta: dict = None):
+    meta = dict(meta or {})
+    meta["_tensors"] = list(tensors)
+    mj = json.dumps(meta).encode()
+    with open(path, "wb") as f:
+        f.write(HUB_MAGIC)
+        f.write(struct.pack(">II", 1, len(mj)))
+        f.write(mj)
+        f.write(struct.pack(">I", len(tensors)))
+        for name, t in tensors.items():
+            t = t.detach().cpu().contiguous()
+            if t.dtype not in _HUB_CODES:
+                t = t.float()
+            nb = name.encode()
+            raw = t.numpy().tobytes()
+            f.write(struct.pack(">I", len(nb)) + nb + struct.pack(">I", t.dim()))
+            f.write(struct.pack(f">{t.dim()}I", *t.shape) if t.dim() else b"")
+            f.write(struct.pack(">IQ", _HUB_CODES[t.dtype], len(raw)))
+            f.write(raw)
+
+
+def load_hub_container(path: str):
+    with open(path, "rb") as f:
+        if f.read(10) != HUB_MAGIC:
+            raise ValueError("not a hub container")
+        _, msz = struct.unpack(">II", f.read(8))
+        meta = json.loads(f.read(msz))
+        n = struct.unpack(">I", f.read(4))[0]
+        out = {}
+        for _ in range(n):
+            ln = struct.unpack(">I", f.read(4))[0]
+            name = f.read(ln).decode()
+            nd = struct.unpack(">I", f.read(4))[0]
+            dims = struct.unpack(f">{nd}I", f.read(4 * nd)) if nd else ()
+            code, nbytes = struct.unpack(">IQ", f.read(12))
+            dt = _HUB_DTYPES[code]
+            out[name] = torch.frombuffer(bytearray(f.read(nbytes)), dtype=dt).view(*dims) if nbytes else torch.empty(dims, dtype=dt)
+    return out, meta
+
+
+def save_npz(path, tensors):
+    np.savez(path, **{k: v.detach().float().cpu().numpy() for k, v in tensors.items()})
+
+
+def load_npz(path):
+    with np.load(path) as z:
+        return {k: torch.from_numpy(z[k]) for k in z.files}
