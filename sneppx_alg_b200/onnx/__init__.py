@@ -1,1 +1,2 @@
-"""onnx sub-package."""
+"""Stand-alone ONNX toolkit."""
+from .toolkit import *  # noqa: F401,F403
