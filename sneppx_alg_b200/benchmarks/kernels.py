@@ -1,0 +1,251 @@
+"""Per-kernel micro-benchmarks with roofline fractions (the reference's ``benchmark.py`` / ``benchmark_suite.py``
+time whole NumPy ops; here every case is one native sm_100a kernel).
+
+``python -m sneppx_alg_b200.benchmarks.kernels <case> [--small] [--iters N] [--out file.json]``
+
+Cases: gemm, gemm_wgrad, attn_fwd, attn_bwd, rmsnorm, glu, rope, ce, adamw, sumsq, paged_decode, gemm_dq_fp8,
+gemm_dq_int4, conv1d, router, quant_fp8, all.  ``--small`` picks a problem that still exceeds L2 but holds well
+under 2 GB so that one launch can be captured by a profiler in seconds.  Timing: CUDA events on the launching
+stream after 3 warm-up launches; inputs are larger than L2 or rotated between iterations.  Fractions are against the
+measured copy bandwidth / cuBLAS bf16 throughput in ``MEASURED_PEAKS.json`` when that file is present at the
+repository root, else the stated fallback.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+
+def _peaks():
+    here = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    p = os.path.join(here, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d["hbm_gbs"], d["bf16_tflops"], "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def _time(fn, iters):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def _bf(*shape, grad=False):
+    return torch.randn(*shape, device="cuda", dtype=torch.bfloat16, requires_grad=grad)
+
+
+def case_gemm(small, iters, a_mn=False, b_mn=False):
+    from ..ops.gemm import gemm
+    M, N, K = (4096, 4096, 4096) if small else (8192, 8192, 8192)
+    a = _bf(K, M) if a_mn else _bf(M, K)
+    b = _bf(K, N) if b_mn else _bf(N, K)
+    out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    ms = _time(lambda: gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=out), iters)
+    A, B = (a.t() if a_mn else a), (b if b_mn else b.t())
+    ms_lib = _time(lambda: torch.matmul(A, B, out=out), iters)
+    return dict(shape=[M, N, K], ms=ms, flops=2 * M * N * K, bytes=2 * (M * K + N * K + M * N), lib_ms=ms_lib, lib="cuBLAS")
+
+
+def case_gemm_wgrad(small, iters):
+    return case_gemm(small, iters, a_mn=True, b_mn=True)
+
+
+def _attn_inputs(small, grad):
+    B, S, H, Hk, D = (1, 2048, 16, 4, 128) if small else (1, 4096, 32, 8, 128)
+    qkv = _bf(B, S, (H + 2 * Hk) * D, grad=grad)
+    q = qkv[..., : H * D].view(B, S, H, D)
+    k = qkv[..., H * D:(H + Hk) * D].view(B, S, Hk, D)
+    v = qkv[..., (H + Hk) * D:].view(B, S, Hk, D)
+    return qkv, q, k, v, 4 * B * H * S * S * D / 2, (B, S, H, Hk, D)
+
+
+def case_attn_fwd(small, iters):
+    from ..ops import functional as F
+    qkv, q, k, v, fl, shp = _attn_inputs(small, False)
+    with torch.no_grad():
+        ms = _time(lambda: F.attention(q, k, v, causal=True), iters)
+        qq, kk, vv = [x.transpose(1, 2) for x in (q, k, v)]
+        ms_lib = _time(lambda: torch.nn.functional.scaled_dot_product_attention(qq, kk, vv, is_causal=True, enable_gqa=True), iters)
+    B, S, H, Hk, D = shp
+    return dict(shape=list(shp), ms=ms, flops=fl, bytes=2 * B * S * D * (2 * H + 2 * Hk), lib_ms=ms_lib, lib="torch SDPA")
+
+
+def case_attn_bwd(small, iters):
+    from ..ops import functional as F
+    qkv, q, k, v, fl, shp = _attn_inputs(small, True)
+    with torch.no_grad():
+        ms_f = _time(lambda: F.attention(q, k, v, causal=True), iters)
+    g = torch.randn_like(F.attention(q, k, v, causal=True))
+    ms_fb = _time(lambda: torch.autograd.grad(F.attention(q, k, v, causal=True), qkv, g), iters)
+    B, S, H, Hk, D = shp
+    return dict(shape=list(shp), ms=ms_fb - ms_f, flops=2.5 * fl, bytes=2 * B * S * D * (4 * H + 4 * Hk), note="forward+backward minus forward")
+
+
+def case_rmsnorm(small, iters):
+    from ..ops import functional as F
+    T, Dm = (32768, 4096) if small else (131072, 4096)
+    x, r, w = _bf(T, Dm), _bf(T, Dm), torch.ones(Dm, device="cuda", dtype=torch.bfloat16)
+    with torch.no_grad():
+        ms = _time(lambda: F.rmsnorm(x, w, 1e-5, residual=r), iters)
+    return dict(shape=[T, Dm], ms=ms, bytes=2 * T * Dm * 4, note="fused residual add: reads x,r writes y,sum")
+
+
+def case_glu(small, iters):
+    from ..ops import functional as F
+    T, Dm = (16384, 14336) if small else (65536, 14336)
+    gu = _bf(T, 2 * Dm)
+    with torch.no_grad():
+        ms = _time(lambda: F.glu(gu), iters)
+    return dict(shape=[T, 2 * Dm], ms=ms, bytes=2 * T * Dm * 3)
+
+
+def case_rope(small, iters):
+    from ..ops import functional as F
+    B, S, H, Hk, D = (4, 4096, 32, 8, 128) if small else (16, 4096, 32, 8, 128)
+    qkv = _bf(B, S, (H + 2 * Hk) * D)
+    cos, sin = F.rope_tables(S, D, 5e5, "cuda")
+    with torch.no_grad():
+        ms = _time(lambda: F.rope_qk_(qkv, cos, sin, H + Hk, D), iters)
+    return dict(shape=[B, S, H, Hk, D], ms=ms, bytes=2 * B * S * (H + Hk) * D * 2 + 2 * B * S * (H + 2 * Hk) * D * 2,
+                note="out-of-place: clone of qkv plus rotate of q,k heads")
+
+
+def case_ce(small, iters):
+    from ..ops import functional as F
+    T, V = (2048, 128256) if small else (8192, 128256)
+    logits = _bf(T, V)
+    tgt = torch.randint(0, V, (T,), device="cuda")
+    ms = _time(lambda: F.cross_entropy(logits.detach().requires_grad_(True), tgt), iters)
+    return dict(shape=[T, V], ms=ms, bytes=2 * T * V * 3, note="forward; gradient written in place in the same pass (2 reads + 1 write)")
+
+
+def case_adamw(small, iters):
+    from ..optim.fused import adamw_flat_
+    n = (64 if small else 512) * 1024 * 1024
+    p32 = torch.randn(n, device="cuda")
+    m, v = torch.zeros_like(p32), torch.zeros_like(p32)
+    g = torch.randn(n, device="cuda", dtype=torch.bfloat16)
+    p16 = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    ms = _time(lambda: adamw_flat_(p32, m, v, g, p16, 3e-4, 0.9, 0.95, 1e-8, 0.1, 10), iters)
+    return dict(shape=[n], ms=ms, bytes=n * (12 + 2 + 12 + 2))
+
+
+def case_sumsq(small, iters):
+    from ..optim.fused import grad_norm_
+    n = (256 if small else 1024) * 1024 * 1024
+    g = torch.randn(n, device="cuda", dtype=torch.bfloat16)
+    ms = _time(lambda: grad_norm_([g]), iters)
+    return dict(shape=[n], ms=ms, bytes=2 * n)
+
+
+def case_paged_decode(small, iters):
+    from ..ops import paged
+    B, Hq, Hkv, D, bs, L = (32, 32, 8, 128, 16, 4096) if small else (64, 32, 8, 128, 16, 8192)
+    nb = L // bs
+    kc = _bf(B * nb, bs, Hkv, D)
+    vc = _bf(B * nb, bs, Hkv, D)
+    tables = torch.arange(B * nb, device="cuda", dtype=torch.int32).view(B, nb)
+    lens = torch.full((B,), L, device="cuda", dtype=torch.int32)
+    q = _bf(B, Hq, D)
+    with torch.no_grad():
+        ms = _time(lambda: paged.paged_decode(q, kc, vc, tables, lens), iters)
+    return dict(shape=[B, Hq, Hkv, D, L], ms=ms, bytes=2 * 2 * B * L * Hkv * D)
+
+
+def _case_dq(mode, small, iters):
+    from ..ops import quant
+    M, N, K = (16, 14336, 4096) if small else (64, 28672, 8192)
+    w = _bf(N, K)
+    x = _bf(M, K)
+    qw, sc = (quant.quant_fp8_128x128(w) if mode == "fp8" else quant.quant_int4(w))
+    with torch.no_grad():
+        ms = _time(lambda: quant.gemm_dequant(x, qw, sc, mode=mode), iters)
+        ms_lib = _time(lambda: torch.matmul(x, w.t()), iters)
+    wb = N * K * (1 if mode == "fp8" else 0.5)
+    return dict(shape=[M, N, K], ms=ms, flops=2 * M * N * K, bytes=wb + 2 * M * K + 2 * M * N, lib_ms=ms_lib, lib="cuBLAS bf16 weights")
+
+
+def case_gemm_dq_fp8(small, iters):
+    return _case_dq("fp8", small, iters)
+
+
+def case_gemm_dq_int4(small, iters):
+    return _case_dq("int4", small, iters)
+
+
+def case_conv1d(small, iters):
+    from ..ops import ssm
+    B, S, C = (4, 4096, 4352) if small else (16, 4096, 4352)
+    x, w, b = _bf(B, S, C), _bf(C, 4), _bf(C)
+    with torch.no_grad():
+        ms = _time(lambda: ssm.causal_conv1d(x, w, b), iters)
+    return dict(shape=[B, S, C], ms=ms, bytes=2 * B * S * C * 2)
+
+
+def case_router(small, iters):
+    from ..ops import moe
+    T, E = (262144, 8) if small else (1048576, 8)
+    logits = torch.randn(T, E, device="cuda")
+    with torch.no_grad():
+        ms = _time(lambda: moe.route(logits, 2), iters)
+    return dict(shape=[T, E], ms=ms, bytes=T * E * 4 * 2 + T * 2 * 8)
+
+
+def case_quant_fp8(small, iters):
+    from ..ops import quant
+    T, Dm = (32768, 4096) if small else (131072, 4096)
+    x = _bf(T, Dm)
+    with torch.no_grad():
+        ms = _time(lambda: quant.quant_fp8_1x128(x), iters)
+    return dict(shape=[T, Dm], ms=ms, bytes=T * Dm * 3 + T * Dm // 128 * 4)
+
+
+CASES = {k[5:]: v for k, v in list(globals().items()) if k.startswith("case_")}
+
+
+def run(name, small=False, iters=10):
+    from .. import ops
+    hbm, tf, src = _peaks()
+    r = CASES[name](small, iters)
+    r["case"], r["small"] = name, small
+    if "flops" in r:
+        r["tflops"] = r["flops"] / r["ms"] / 1e9
+        r[f"frac_tensor_of_{src}"] = r["tflops"] / tf
+    r["gbs"] = r["bytes"] / r["ms"] / 1e6
+    r[f"frac_hbm_of_{src}"] = r["gbs"] / hbm
+    ops.check_status()
+    return r
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
+    ap.add_argument("case", choices=sorted(CASES) + ["all"])
+    ap.add_argument("--small", action="store_true")
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--out")
+    a = ap.parse_args(argv)
+    names = sorted(CASES) if a.case == "all" else [a.case]
+    res = []
+    for n in names:
+        r = run(n, a.small, a.iters)
+        print(json.dumps(r), flush=True)
+        res.append(r)
+    if a.out:
+        json.dump(res, open(a.out, "w"), indent=1)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
