@@ -1,0 +1,69 @@
+"""Flat re-export with the reference's public names (interface_bindings/__init__.py of the reference lists them per
+module).  A name resolves lazily on first access so that importing the shim stays cheap."""
+import importlib
+
+_WHERE = {
+    # nn
+    **{n: "nn" for n in ("Module", "Linear", "Embedding", "Dropout", "LayerNorm", "RMSNorm", "GELU", "SiLU", "ReLU",
+                         "Sigmoid", "Tanh", "Sequential", "MultiheadAttention", "TransformerBlock", "Transformer")},
+    **{n: "nn.attention" for n in ("Attention", "DifferentialAttention", "FlexAttention", "SlidingWindowAttention",
+                                   "SparseAttention", "ALiBiAttention", "CrossAttention", "MultiHeadLatentAttention",
+                                   "MixtureOfDepths")},
+    "Mamba2": "nn.ssm",
+    # optim / schedulers
+    **{n: "optim.zoo" for n in ("SGD", "AdamW", "Lion", "LAMB", "LARS", "AdaFactor", "SM3", "SOAP", "DistributedAdam", "Demeter", "CaProp", "OrthoAdam",
+                                "get_optimizer")},
+    **{n: "training.schedulers" for n in ("CosineAnnealingLR", "get_scheduler")},
+    # training
+    **{n: "training.config" for n in ("TrainConfig",)},
+    **{n: "training.trainer" for n in ("Trainer",)},
+    **{n: "training.amp" for n in ("autocast", "GradScaler")},
+    **{n: "training.lora" for n in ("LoRALinear", "apply_lora", "DPOTrainer", "GRPOTrainer")},
+    **{n: "training.data" for n in ("DataLoader", "MemoryMappedTextDataset", "StreamingTokenDataset", "DistributedSampler")},
+    # distributed
+    **{n: "parallel.distributed" for n in ("init_process_group", "destroy_process_group", "get_world_size", "get_rank",
+                                           "barrier", "all_reduce", "broadcast", "DistributedContext",
+                                           "DistributedDataParallel", "launch", "ProcessGroup")},
+    **{n: "parallel.fsdp" for n in ("FullyShardedDataParallel", "FSDPConfig", "ShardingStrategy", "MixedPrecision",
+                                    "shard_model", "fsdp_save_checkpoint", "fsdp_load_checkpoint")},
+    # checkpoint / fault tolerance
+    **{n: "checkpoint.sneppx_format" for n in ("CheckpointWriter", "CheckpointReader", "validate_checkpoint")},
+    **{n: "checkpoint.manager" for n in ("CheckpointManager", "CheckpointCoordinator")},
+    **{n: "parallel.host_runtime" for n in ("HeartbeatMonitor", "ElasticTrainer", "FaultToleranceManager")},
+    # algorithms
+    **{n: "algorithms" for n in ("Model", "ModelConfig", "HSSConfig", "HSSModel", "HSSDiscretize", "HSSScan", "HSSStep",
+                                 "SERConfig", "SERModel", "SERLayer", "SERRoute", "SERLoss", "ARCConfig", "ARCModel",
+                                 "NPEConfig", "NPEModel", "FMConfig", "FMModel", "FMSyncNCCL")},
+    # models / zoo / hub
+    **{n: "models" for n in ("LlamaForCausalLM", "MistralForCausalLM", "Qwen2ForCausalLM", "create_model", "LlamaConfig",
+                             "MistralConfig", "Qwen2Config", "DeepSeekV2Config", "get_model_config", "extend_context")},
+    "DeepSeekV2ForCausalLM": "models.deepseek",
+    **{n: "models.families" for n in ("BertModel", "BertForMaskedLM", "GPTModel", "GPT2LMHeadModel",
+                                      "T5ForConditionalGeneration", "VisionTransformer")},
+    **{n: "hub.model_hub" for n in ("from_pretrained", "ModelHub", "convert_hf_to_sneppx", "Hub")},
+    # quantisation
+    **{n: "quant" for n in ("QuantMode", "quantize_int8", "awq_quantize", "gptq_quantize", "QuantizedLinear",
+                            "mx_quantize", "nvfp4_quantize")},
+    # serving
+    **{n: "serving.kv_cache" for n in ("KVBlockPool", "PagedKVCache", "PrefixCache")},
+    **{n: "serving.generation" for n in ("generate", "greedy_search", "beam_search", "batch_generate")},
+    **{n: "serving.serving_engine" for n in ("ServingEngine",)},
+    **{n: "serving.server" for n in ("create_app",)},
+    # observability
+    **{n: "utils.observability" for n in ("Profiler", "ExperimentTracker", "Logger")},
+}
+
+__all__ = sorted(_WHERE)
+
+
+def __getattr__(name):
+    where = _WHERE.get(name)
+    if where is None:
+        raise AttributeError(f"module 'SneppX_ALG' has no attribute '{name}'")
+    obj = getattr(importlib.import_module(f"sneppx_alg_b200.{where}"), name)
+    globals()[name] = obj
+    return obj
+
+
+def __dir__():
+    return __all__

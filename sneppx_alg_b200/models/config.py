@@ -204,6 +204,9 @@ _MODEL_REGISTRY: Dict[str, Dict[str, dict]] = {
                    num_key_value_heads=8, vocab_size=32000, max_position_embeddings=4096, rope_theta=1e4, rms_norm_eps=1e-5),
     },
     "llama3": {
+        "tiny": _tf(hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=2,
+                    num_key_value_heads=1, head_dim=64, vocab_size=512, max_position_embeddings=512, rope_theta=1e4,
+                    rms_norm_eps=1e-5),
         "8B": _tf(hidden_size=4096, intermediate_size=14336, num_hidden_layers=32, num_attention_heads=32,
                   num_key_value_heads=8, vocab_size=128256, max_position_embeddings=8192, rope_theta=5e5, rms_norm_eps=1e-5),
         "70B": _tf(hidden_size=8192, intermediate_size=28672, num_hidden_layers=80, num_attention_heads=64,

@@ -230,9 +230,186 @@ class AdaFactor(_Simple):
         return p * (1 - grp["lr"] * grp["weight_decay"]) - grp["lr"] * u
 
 
+
+class SM3(_Simple):
+    """Memory-efficient adaptive method: one accumulator per row and per column of a matrix (full accumulator for
+    vectors); nu = min(row, col) + g^2 (the reference's ``optim_advanced.SM3``)."""
+
+    def __init__(self, params, lr=0.1, momentum=0.0, eps=1e-30, weight_decay=0.0):
+        super().__init__(params, lr=lr, momentum=momentum, eps=eps, weight_decay=weight_decay)
+
+    def update(self, p, g, st, grp):
+        if p.dim() == 2:
+            r = st.setdefault("row", torch.zeros(p.shape[0], 1, device=p.device))
+            c = st.setdefault("col", torch.zeros(1, p.shape[1], device=p.device))
+            nu = torch.minimum(r, c) + g * g
+            st["row"], st["col"] = nu.amax(1, keepdim=True), nu.amax(0, keepdim=True)
+        else:
+            nu = st.setdefault("acc", torch.zeros_like(p)).add_(g * g)
+        u = g / (nu.sqrt() + grp["eps"])
+        if grp["momentum"]:
+            u = st.setdefault("m", torch.zeros_like(p)).mul_(grp["momentum"]).add_(u, alpha=1 - grp["momentum"])
+        return p * (1 - grp["lr"] * grp["weight_decay"]) - grp["lr"] * u
+
+
+class Demeter(_Simple):
+    """Adam whose second moment of a matrix gradient is a rank-r estimate from two power iterations
+    (``optim_advanced.Demeter``): v tracks the low-rank reconstruction U diag(S) V^T squared."""
+
+    def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01, rank=8):
+        super().__init__(params, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, rank=rank)
+
+    def update(self, p, g, st, grp):
+        b1, b2 = grp["betas"]
+        t = st["step"]
+        m = st.setdefault("m", torch.zeros_like(p)).mul_(b1).add_(g, alpha=1 - b1)
+        if p.dim() == 2:
+            r = min(grp["rank"], *p.shape)
+            V = st.get("V")
+            if V is None:
+                V = torch.randn(p.shape[1], r, device=p.device, generator=None) * 0.01
+            for _ in range(2):
+                U = torch.linalg.qr(g @ V).Q
+                V = torch.linalg.qr(g.T @ U).Q
+            st["V"] = V
+            low = U @ (U.T @ g)
+            sq = low * low
+        else:
+            sq = g * g
+        v = st.setdefault("v", torch.zeros_like(p)).mul_(b2).add_(sq, alpha=1 - b2)
+        u = (m / (1 - b1 ** t)) / ((v / (1 - b2 ** t)).sqrt() + grp["eps"])
+        return p * (1 - grp["lr"] * grp["weight_decay"]) - grp["lr"] * u.clamp(-10, 10)
+
+
+class CaProp(_Simple):
+    """Cautious RMS-style update: the step grows by ``cautious_factor`` x max(0, cos(g, m)) when the gradient agrees
+    with its running mean (``optim_advanced.CaProp``; one beta for both moments)."""
+
+    def __init__(self, params, lr=1e-3, beta=0.9, eps=1e-8, weight_decay=0.0, cautious_factor=0.5):
+        super().__init__(params, lr=lr, beta=beta, eps=eps, weight_decay=weight_decay, cautious_factor=cautious_factor)
+
+    def update(self, p, g, st, grp):
+        b, t = grp["beta"], st["step"]
+        m = st.setdefault("m", torch.zeros_like(p)).mul_(b).add_(g, alpha=1 - b)
+        v = st.setdefault("v", torch.zeros_like(p)).mul_(b).addcmul_(g, g, value=1 - b)
+        bc = 1 - b ** t
+        mh, vh = m / bc, v / bc
+        align = (g * mh).sum() / (g.norm() * mh.norm() + grp["eps"])
+        scale = 1.0 + grp["cautious_factor"] * align.clamp_min(0)
+        return p - grp["lr"] * (scale * mh / (vh.sqrt() + grp["eps"]) + grp["weight_decay"] * p)
+
+
+class SOAP(_Simple):
+    """Adam run in the eigenbasis of the Shampoo preconditioners L = E[G G^T], R = E[G^T G]; the bases are refreshed
+    every ``precondition_frequency`` steps (``optim_advanced.SOAP``)."""
+
+    def __init__(self, params, lr=3e-3, betas=(0.95, 0.95), eps=1e-8, weight_decay=0.01, shampoo_beta=0.95,
+                 precondition_frequency=10, max_dim=4096):
+        super().__init__(params, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, shampoo_beta=shampoo_beta,
+                         precondition_frequency=precondition_frequency, max_dim=max_dim)
+
+    def update(self, p, g, st, grp):
+        b1, b2 = grp["betas"]
+        t = st["step"]
+        rot = p.dim() == 2 and max(p.shape) <= grp["max_dim"]
+        if rot:
+            sb = grp["shampoo_beta"]
+            L = st.setdefault("L", torch.zeros(p.shape[0], p.shape[0], device=p.device)).mul_(sb).add_(g @ g.T, alpha=1 - sb)
+            R = st.setdefault("R", torch.zeros(p.shape[1], p.shape[1], device=p.device)).mul_(sb).add_(g.T @ g, alpha=1 - sb)
+            if "QL" not in st or t % grp["precondition_frequency"] == 0:
+                st["QL"], st["QR"] = torch.linalg.eigh(L).eigenvectors, torch.linalg.eigh(R).eigenvectors
+            g = st["QL"].T @ g @ st["QR"]
+        m = st.setdefault("m", torch.zeros_like(p)).mul_(b1).add_(g, alpha=1 - b1)
+        v = st.setdefault("v", torch.zeros_like(p)).mul_(b2).addcmul_(g, g, value=1 - b2)
+        u = (m / (1 - b1 ** t)) / ((v / (1 - b2 ** t)).sqrt() + grp["eps"])
+        if rot:
+            u = st["QL"] @ u @ st["QR"].T
+        return p * (1 - grp["lr"] * grp["weight_decay"]) - grp["lr"] * u
+
+
+class OrthoAdam(_Simple):
+    """Adam-normalised step along the gradient component orthogonal to the last ``history_size`` gradients
+    (``optim_advanced.OrthoAdam``)."""
+
+    def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, history_size=3):
+        super().__init__(params, lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, history_size=history_size)
+
+    def update(self, p, g, st, grp):
+        b1, b2 = grp["betas"]
+        t = st["step"]
+        st.setdefault("m", torch.zeros_like(p)).mul_(b1).add_(g, alpha=1 - b1)
+        v = st.setdefault("v", torch.zeros_like(p)).mul_(b2).addcmul_(g, g, value=1 - b2)
+        hist = st.setdefault("hist", [])
+        og, basis = g.clone(), []
+        for h in hist:                                   # Gram-Schmidt over the history, then project it out
+            u = h.clone()
+            for q in basis:
+                u -= (u * q).sum() / ((q * q).sum() + 1e-12) * q
+            basis.append(u)
+        for q in basis:
+            og -= (og * q).sum() / ((q * q).sum() + 1e-12) * q
+        hist.append(g.clone())
+        if len(hist) > grp["history_size"]:
+            hist.pop(0)
+        return p - grp["lr"] * (og / ((v / (1 - b2 ** t)).sqrt() + grp["eps"]) + grp["weight_decay"] * p)
+
+
+class DistributedAdam(Optimizer):
+    """ZeRO-1 AdamW: gradients are averaged, each rank keeps Adam state for and updates only its contiguous 1/world
+    slice of every parameter, then the slices are all-gathered (``optim_advanced.DistributedAdam``).  On a single
+    process it is plain AdamW.  The fused flat-buffer path for LLM training is ``parallel.zero_engine.ZeroEngine``;
+    this class is the drop-in optimizer object of the reference's API."""
+
+    def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01, group=None):
+        super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay))
+        self.group = group
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        import torch.distributed as dist
+        loss = closure() if closure else None
+        on = dist.is_available() and dist.is_initialized()
+        world = dist.get_world_size(self.group) if on else 1
+        rank = dist.get_rank(self.group) if on else 0
+        for g in self.param_groups:
+            b1, b2 = g["betas"]
+            for p in g["params"]:
+                if p.grad is None:
+                    continue
+                grad = p.grad.float().reshape(-1)
+                if world > 1:
+                    dist.all_reduce(grad, group=self.group)
+                    grad /= world
+                n = grad.numel()
+                per = -(-n // world)
+                lo, hi = min(n, rank * per), min(n, (rank + 1) * per)
+                st = self.state[p]
+                if not st:
+                    st["step"], st["m"], st["v"] = 0, torch.zeros(hi - lo, device=p.device), torch.zeros(hi - lo, device=p.device)
+                st["step"] += 1
+                t = st["step"]
+                flat = p.data.float().reshape(-1)
+                gs = grad[lo:hi]
+                st["m"].mul_(b1).add_(gs, alpha=1 - b1)
+                st["v"].mul_(b2).addcmul_(gs, gs, value=1 - b2)
+                upd = (st["m"] / (1 - b1 ** t)) / ((st["v"] / (1 - b2 ** t)).sqrt() + g["eps"])
+                mine = flat[lo:hi] * (1 - g["lr"] * g["weight_decay"]) - g["lr"] * upd
+                if world > 1:
+                    pad = torch.zeros(per, device=p.device)
+                    pad[: hi - lo] = mine
+                    out = torch.empty(world * per, device=p.device)
+                    dist.all_gather_into_tensor(out, pad, group=self.group)
+                    flat = out[:n]
+                else:
+                    flat = mine
+                p.data.copy_(flat.view_as(p).to(p.dtype))
+        return loss
+
+
 _REGISTRY = {"sgd": SGD, "adam": Adam, "adamw": AdamW, "adamax": Adamax, "rmsprop": RMSprop, "adagrad": Adagrad,
              "adadelta": Adadelta, "radam": RAdam, "sf_adamw": ScheduleFreeAdamW, "schedule_free_adamw": ScheduleFreeAdamW,
-             "lion": Lion, "lamb": LAMB, "lars": LARS, "adafactor": AdaFactor}
+             "lion": Lion, "lamb": LAMB, "lars": LARS, "adafactor": AdaFactor, "sm3": SM3, "demeter": Demeter,
+             "caprop": CaProp, "soap": SOAP, "orthoadam": OrthoAdam, "distributed_adam": DistributedAdam}
 
 
 def get_optimizer(name: str, params, **kw):
