@@ -6,7 +6,8 @@
 //   S^T  = K Q^T            dP^T = V dO^T                         (128 x 64, fp32 in TMEM)
 //   P^T  = exp2(S^T*c - LSE)    dS^T = P^T o (dP^T - delta) * scale  (registers -> bf16 smem tiles)
 //   dV  += P^T dO           dK  += dS^T Q                          (128 x 128 accumulators in TMEM)
-//   dQ^T = K^T dS^T         (128 x 64; drained with coalesced fp32 reductions into dq_accum)
+//   dQ^T = K^T dS^T         (128 x 64; staged through shared memory and added into dq_accum with bulk
+//                            fp32 reductions, cp.reduce.async.bulk, one 4 KB slice per warp, off the critical path)
 // The MN-major operand forms (dO, Q, K^T, dS^T as B/A operands) are read from the very tiles TMA
 // brought or the softmax warps wrote; no transposed copy exists. dK/dV need no atomics because
 // the whole GQA group is reduced inside the CTA.
@@ -48,7 +49,9 @@ struct BwdCfg {
   static constexpr int OFF_Q = 2 * KV_BYTES;             // 2 stages of (Q | dO)
   static constexpr int OFF_PT = OFF_Q + 2 * 2 * Q_BYTES;
   static constexpr int OFF_DST = OFF_PT + PT_BYTES;
-  static constexpr int OFF_STAT = OFF_DST + PT_BYTES;    // lse2 / delta, 2 x 2 x 64 floats
+  static constexpr int OFF_DQS = OFF_DST + PT_BYTES;     // dQ staging: 8 warps x [32 query rows][32 head-dim] fp32
+  static constexpr int DQS_BYTES = BWD_Q * BWD_D * 4;    // 32 KB
+  static constexpr int OFF_STAT = OFF_DQS + DQS_BYTES;   // spare
   static constexpr int OFF_BAR = OFF_STAT + 1024;
   static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
   static constexpr uint32_t TM_S = 0, TM_DP = 64, TM_DQ = 128, TM_DV = 256, TM_DK = 384;
@@ -71,11 +74,13 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_kernel(const __grid_c
   uint64_t* dp_full = bars + 6;      // 1
   uint64_t* pds_ready = bars + 7;    // 1 (8 arrivals)
   uint64_t* dq_full = bars + 8;      // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  uint64_t* dq_drained = bars + 9;   // 1 (8 arrivals): the dQ^T accumulator has been read out of TMEM
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
   volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kv_tile = blockIdx.x, kv_head = blockIdx.y, b = blockIdx.z;
+  // Heaviest key tiles first (under a causal mask tile 0 sees every query tile): kv head is the fastest block index.
+  const int kv_tile = blockIdx.x / p.Hk, kv_head = blockIdx.x % p.Hk, b = blockIdx.z;
   const int G = p.Hq / p.Hk;
   const int kv0 = kv_tile * BWD_KV;
   const int offset = p.Skv - p.Sq;
@@ -103,6 +108,7 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_kernel(const __grid_c
     mbar_init(dp_full, 1);
     mbar_init(pds_ready, 8);
     mbar_init(dq_full, 1);
+    mbar_init(dq_drained, 8);
     *s_abort = 0;
     mbar_fence_init();
     tma_prefetch_desc(&p.tmQ);
@@ -187,7 +193,11 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_kernel(const __grid_c
         for (int k = 0; k < 4; ++k)
           umma_f16_ss(tmem_base + Cfg::TM_DK, umma_desc_sw128(aDST + k * 32, 16, 1024),
                       umma_desc_sw128(q + k * 2048, 8192, 1024), idesc_acc, (it | k) ? 1u : 0u);
-        // dQ^T = K^T dS^T  (K = 128 key rows: 8 k-steps)
+        // dQ^T = K^T dS^T  (K = 128 key rows: 8 k-steps); the accumulator of the previous iteration must be read out
+        if (it > 0) {
+          if (!mbar_wait(dq_drained, (it - 1) & 1, s_abort, p.status, ST_TIMEOUT_MMA)) { ok = false; break; }
+          tc_fence_after();
+        }
 #pragma unroll
         for (int k = 0; k < 8; ++k)
           umma_f16_ss(tmem_base + Cfg::TM_DQ, umma_desc_sw128(aK + k * 2048, 16384, 1024),
@@ -205,17 +215,32 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_kernel(const __grid_c
     const int c0 = wg * 32;
     const uint32_t lane_addr = static_cast<uint32_t>(qd * 32) << 16;
     bool ok = n_it > 0;
+    float* stage = reinterpret_cast<float*>(smem + Cfg::OFF_DQS) + (warp - 2) * 1024;  // this warp's [32 q][32 d] slice
     auto drain_dq = [&](int it) {
-      // dQ^T tile: lane = head-dim index, column = query row; one coalesced fp32 reduction per column
+      // dQ^T tile: lane = head-dim index, column = query row. dq_accum is tiled so that every warp's slice is one
+      // contiguous 4 KB run: [b][head][q tile][column group][lane quarter][32 query rows][32 head-dim].
       const int head = kv_head * G + it / n_qt;
-      const int qrow0 = (qt_lo + it % n_qt) * BWD_Q + c0;
-      float* base = p.dq_accum + (((long long)b * p.Sq + qrow0) * p.Hq + head) * BWD_D + r;
+      const int qt = qt_lo + it % n_qt;
+      float* dst = p.dq_accum + (((((long long)b * p.Hq + head) * n_qt_total + qt) * 2 + wg) * 4 + qd) * 1024;
       uint32_t v[32];
       tmem_ld32(tmem_base + Cfg::TM_DQ + lane_addr + c0, v);
       tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(dq_drained);
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // the previous reduction has read the slice
+      }
+      __syncwarp();
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        if (qrow0 + i < p.Sq) atomicAdd(base + (long long)i * p.Hq * BWD_D, __uint_as_float(v[i]));
+      for (int i = 0; i < 32; ++i) stage[i * 32 + lane] = __uint_as_float(v[i]);
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(dst),
+                     "r"(smem_u32(stage)), "r"(4096)
+                     : "memory");
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
       }
     };
     for (int it = 0; it < n_it && ok; ++it) {
@@ -267,11 +292,10 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_kernel(const __grid_c
           ds[i / 2] = pack_bf16x2(d0, d1);
         }
       }
-      // the P^T / dS^T tiles and the dQ^T accumulator are free once iteration it-1 has fully executed
+      // the P^T / dS^T tiles are free, and dQ^T of iteration it-1 is complete, once iteration it-1 has fully executed
       if (it > 0) {
         if (!mbar_wait_warp(dq_full, (it - 1) & 1, s_abort, p.status, ST_TIMEOUT_EPILOGUE)) { ok = false; break; }
         tc_fence_after();
-        drain_dq(it - 1);
       }
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
@@ -284,11 +308,14 @@ __global__ void __launch_bounds__(BWD_THREADS, 1) attn_bwd_kernel(const __grid_c
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(pds_ready);
+      if (it > 0) drain_dq(it - 1);  // overlaps the S / dP / dV / dK MMAs the arrive above released
     }
+    if (lane == 0 && !ok) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     if (ok && n_it > 0) {
       if (mbar_wait_warp(dq_full, (n_it - 1) & 1, s_abort, p.status, ST_TIMEOUT_EPILOGUE)) {
         tc_fence_after();
         drain_dq(n_it - 1);
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
         // dK / dV accumulators -> bf16 rows
         const bool row_ok = kv_idx < p.Skv;
         __nv_bfloat16* dkr = p.dK + (long long)b * p.dk_batch_stride + (long long)kv_idx * p.dk_row_stride +
@@ -365,19 +392,31 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ dO, const __
   }
 }
 
-__global__ void attn_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dQ, long long tokens,
-                                       int HD, long long dq_row_stride) {
-  const long long n = tokens * (HD / 4);
+// dq_accum (tiled as the backward kernel writes it) -> bf16 dQ rows. One thread converts 4 head-dim values.
+__global__ void attn_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dQ, int B, int Sq,
+                                       int Hq, long long dq_row_stride) {
+  const int n_qt = (Sq + BWD_Q - 1) / BWD_Q;
+  const long long n = (long long)B * Hq * n_qt * (BWD_Q * BWD_D / 4);
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n;
        i += (long long)gridDim.x * blockDim.x) {
-    const long long t = i / (HD / 4);
-    const int c = (i % (HD / 4)) * 4;
-    const float4 v = *reinterpret_cast<const float4*>(acc + t * HD + c);
+    // i enumerates float4 groups of the tiled buffer in storage order
+    const int di4 = i & 7;                 // 8 float4 per 32-wide head-dim run
+    const int qi = (i >> 3) & 31;
+    const int qd = (i >> 8) & 3;
+    const int wg = (i >> 10) & 1;
+    const long long t = i >> 11;           // (b * Hq + head) * n_qt + tile
+    const int tile = t % n_qt;
+    const long long bh = t / n_qt;
+    const int head = bh % Hq;
+    const long long bb = bh / Hq;
+    const int srow = tile * BWD_Q + wg * 32 + qi;
+    if (srow >= Sq) continue;
+    const float4 v = *reinterpret_cast<const float4*>(acc + i * 4);
     __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
     uint2 o;
     o.x = *reinterpret_cast<uint32_t*>(&lo);
     o.y = *reinterpret_cast<uint32_t*>(&hi);
-    *reinterpret_cast<uint2*>(dQ + t * dq_row_stride + c) = o;
+    *reinterpret_cast<uint2*>(dQ + (bb * Sq + srow) * dq_row_stride + (long long)head * BWD_D + qd * 32 + di4 * 4) = o;
   }
 }
 
@@ -392,7 +431,8 @@ static int make_attn_map_bwd(CUtensorMap* tm, const void* base, int B, int S, in
 }  // namespace sx
 using namespace sx;
 
-// Requirements: D == 128, v_head_div == 1, dQ batch stride == Sq * dq_row_stride.
+// Requirements: D == 128, v_head_div == 1, dQ batch stride == Sq * dq_row_stride; dq_accum holds
+// B * Hq * ceil(Sq / 64) * 64 * 128 floats.
 extern "C" int sx_attn_bwd(const SxAttnArgs* a, cudaStream_t st) {
   if (a->D != BWD_D) return -1;
   if (a->Hq % a->Hk) return -2;
@@ -411,8 +451,10 @@ extern "C" int sx_attn_bwd(const SxAttnArgs* a, cudaStream_t st) {
   rc = make_attn_map_bwd(&p.tmV, a->V, a->B, a->Skv, a->Hk, a->D, a->v_row_stride, a->v_batch_stride, BWD_KV);
   if (rc) return rc;
   const long long tokens = (long long)a->B * a->Sq;
-  const int HD = a->Hq * a->D;
-  cudaMemsetAsync(a->dq_accum, 0, sizeof(float) * tokens * HD, st);
+  const int n_qt = (a->Sq + BWD_Q - 1) / BWD_Q;
+  // dq_accum holds whole 64-row query tiles: B * Hq * n_qt * 64 * 128 floats
+  const long long acc_floats = (long long)a->B * a->Hq * n_qt * BWD_Q * BWD_D;
+  cudaMemsetAsync(a->dq_accum, 0, sizeof(float) * acc_floats, st);
   {
     const long long warps = tokens * a->Hq;
     const int blocks = (int)((warps * 32 + 255) / 256);
@@ -434,12 +476,13 @@ extern "C" int sx_attn_bwd(const SxAttnArgs* a, cudaStream_t st) {
       return -10;
     set = true;
   }
-  dim3 grid((a->Skv + BWD_KV - 1) / BWD_KV, a->Hk, a->B);
+  dim3 grid(((a->Skv + BWD_KV - 1) / BWD_KV) * a->Hk, 1, a->B);
   attn_bwd_kernel<<<grid, BWD_THREADS, BwdCfg::SMEM_BYTES, st>>>(p);
   {
-    const long long n = tokens * (HD / 4);
+    const long long n = acc_floats / 4;
     const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
-    attn_dq_convert_kernel<<<blocks, 256, 0, st>>>(a->dq_accum, (__nv_bfloat16*)a->dQ, tokens, HD, a->dq_row_stride);
+    attn_dq_convert_kernel<<<blocks, 256, 0, st>>>(a->dq_accum, (__nv_bfloat16*)a->dQ, a->B, a->Sq, a->Hq,
+                                                   a->dq_row_stride);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }

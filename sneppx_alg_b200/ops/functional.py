@@ -292,7 +292,7 @@ class _AttnFn(torch.autograd.Function):
             dk = torch.empty(B, Skv, Hk, D, dtype=q.dtype, device=q.device)
             dv = torch.empty(B, Skv, Hk, D, dtype=q.dtype, device=q.device)
         a = _attn_args(q, k, v_use, o, lse, causal, window, scale, 1)
-        dq_acc = torch.empty(B, Sq, Hq, D, dtype=torch.float32, device=q.device)
+        dq_acc = torch.empty(B, Hq, (Sq + 63) // 64 * 64, D, dtype=torch.float32, device=q.device)  # tiled by the kernel
         delta = torch.empty(B, Hq, Sq, dtype=torch.float32, device=q.device)
         a.dO, a.dQ, a.dK, a.dV = do.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
         a.dq_accum, a.delta = dq_acc.data_ptr(), delta.data_ptr()
