@@ -14,6 +14,7 @@
 // STAGES tiles, two TMEM accumulators so the epilogue of tile i overlaps the main loop of tile i+1.
 // Takes the place of the reference's mma.sync / SIMT GEMMs (kernel/cuda/tensor_cuda.cu:28-285) and
 // its cuBLAS backward calls (kernel/cuda/autodiff_cuda.cu:28-171).
+#include <stdlib.h>
 #include "tc_common.cuh"
 #include "comm_common.cuh"
 #include "common.cuh"
@@ -577,6 +578,308 @@ static int make_operand_map(CUtensorMap* tm, const void* ptr, int mn, int K, lon
   }
 }
 
+
+// ================================================================================================
+// G1 on a CTA pair: the same GEMM with `cta_group::2`. A cluster of two CTAs (two SMs) owns one 256 x 256 output
+// tile: each CTA stages its own 128 rows of A and its own 128 rows of B per k-block (32 KB instead of the 48 KB a
+// single CTA needs for 128 x 256), the even CTA's MMA thread issues 256 x 256 x 16 instructions that read both
+// CTAs' shared memory, and each CTA's TMEM receives the accumulator rows of its A half. Per SM this halves the
+// B-operand shared-memory traffic and leaves room for six pipeline stages.
+// Protocol (barrier arrays live at the same shared-memory offsets in both CTAs):
+//   full[s]   even CTA only: its producer arms 64 KB, the TMA loads of BOTH CTAs complete on it
+//   empty[s]  both CTAs: released by the even CTA's tcgen05.commit, multicast to the pair
+//   tfull[a]  both CTAs: accumulator a complete, multicast commit
+//   tempty[a] even CTA only, 8 arrivals: the four epilogue warps of each CTA arrive on it (the odd CTA remotely)
+// Dense, non-grouped, non-fused calls only; everything else stays on gemm_tc_kernel.
+constexpr int G2_STAGES = 6;
+constexpr int G2_A_BYTES = 128 * BK * 2;   // 16 KB
+constexpr int G2_B_BYTES = 128 * BK * 2;   // 16 KB: this CTA's half of the 256-row B tile
+constexpr int G2_STAGE_BYTES = G2_A_BYTES + G2_B_BYTES;
+constexpr int G2_SMEM_BYTES = G2_STAGES * G2_STAGE_BYTES + 1024 + 256;
+constexpr uint32_t PEER_MASK = 0xFEFFFFFFu;  // clears the CTA-rank bit of a shared::cluster address: the even CTA's copy
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tma2_load_3d(void* dst, const CUtensorMap* m, uint32_t bar_cluster_addr, int c0, int c1,
+                                             int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void tma2_load_4d(void* dst, const CUtensorMap* m, uint32_t bar_cluster_addr, int c0, int c1,
+                                             int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+__device__ __forceinline__ void umma2_f16_ss(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n}\n" ::"r"(tmem_d),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+// Arrives (once the MMAs issued so far have executed) on the barrier at this offset in BOTH CTAs of the pair.
+__device__ __forceinline__ void umma2_commit_pair(uint64_t* bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+          smem_u32(bar)),
+      "h"((uint16_t)3)
+      : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_even_cta(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(smem_u32(bar) & PEER_MASK) : "memory");
+}
+
+template <bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+    gemm2_kernel(const __grid_constant__ GemmKernelParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + G2_STAGES * G2_STAGE_BYTES);
+  uint64_t* full_bar = bars;                     // [STAGES]
+  uint64_t* empty_bar = bars + G2_STAGES;        // [STAGES]
+  uint64_t* tfull_bar = bars + 2 * G2_STAGES;    // [2]
+  uint64_t* tempty_bar = tfull_bar + 2;          // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();       // 0: issues the MMAs, owns full[] / tempty[]
+  const int cluster_id = blockIdx.x >> 1;
+  const int n_clusters = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < G2_STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tfull_bar[i], 1);
+      mbar_init(&tempty_bar[i], 8);
+    }
+    *s_abort = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&p.tmA);
+    tma_prefetch_desc(&p.tmB);
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // barriers of both CTAs are initialised before any remote arrive or TMA completion
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // p.m_blks counts 256-row pair tiles, p.n_blks 256-column tiles
+  const int total_tiles = p.batch * p.m_blks * p.n_blks;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int t = cluster_id; t < total_tiles; t += n_clusters) {
+        int b, m_blk, n_blk;
+        tile_coords(t, p.m_blks, p.n_blks, b, m_blk, n_blk);
+        const int ab = p.a_batched ? b : 0, bb = p.b_batched ? b : 0;
+        const int num_kb = (p.K + BK - 1) / BK;
+        const int arow = m_blk * 256 + (int)rank * 128, brow = n_blk * 256 + (int)rank * 128;
+        bool ok = true;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, s_abort, p.status, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
+          uint8_t* sa = smem + stage * G2_STAGE_BYTES;
+          uint8_t* sb = sa + G2_A_BYTES;
+          if (rank == 0) mbar_expect_tx(&full_bar[stage], 2 * G2_STAGE_BYTES);
+          const uint32_t fb = smem_u32(&full_bar[stage]) & PEER_MASK;
+          const int kc = kb * BK;
+          if (A_MN) tma2_load_4d(sa, &p.tmA, fb, 0, kc, arow / 64, ab);
+          else      tma2_load_3d(sa, &p.tmA, fb, kc, arow, ab);
+          if (B_MN) tma2_load_4d(sb, &p.tmB, fb, 0, kc, brow / 64, bb);
+          else      tma2_load_3d(sb, &p.tmB, fb, kc, brow, bb);
+          if (++stage == G2_STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (even CTA only)
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = umma_idesc_f16(256, 256, 1, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int t = cluster_id; t < total_tiles && ok; t += n_clusters) {
+        const int num_kb = (p.K + BK - 1) / BK;
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, s_abort, p.status, ST_TIMEOUT_MMA)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * 256;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, s_abort, p.status, ST_TIMEOUT_MMA)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * G2_STAGE_BYTES);
+          const uint32_t sb = sa + G2_A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t adesc = A_MN ? umma_desc_sw128(sa + k * 2048, BK * 128, 1024)
+                                        : umma_desc_sw128(sa + k * 32, 16, 1024);
+            const uint64_t bdesc = B_MN ? umma_desc_sw128(sb + k * 2048, BK * 128, 1024)
+                                        : umma_desc_sw128(sb + k * 32, 16, 1024);
+            umma2_f16_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma2_commit_pair(&empty_bar[stage]);
+          if (++stage == G2_STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma2_commit_pair(&tfull_bar[acc]);
+        ++it;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (4 warps per CTA, this CTA's 128 rows)
+    const int q = warp & 3;
+    int it = 0;
+    for (int t = cluster_id; t < total_tiles; t += n_clusters) {
+      int b, m_blk, n_blk;
+      tile_coords(t, p.m_blks, p.n_blks, b, m_blk, n_blk);
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      if (!mbar_wait_warp(&tfull_bar[acc], acc_phase, s_abort, p.status, ST_TIMEOUT_EPILOGUE)) break;
+      tc_fence_after();
+      const int row = m_blk * 256 + (int)rank * 128 + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      const long long drow = (long long)b * p.strideD + (long long)row * p.ldd;
+      const long long crow = (long long)b * p.strideC + (long long)row * p.ldc;
+#pragma unroll 1
+      for (int c = 0; c < 256 / 32; ++c) {
+        const int col0 = n_blk * 256 + c * 32;
+        if (col0 >= p.N) break;  // uniform across the warp
+        uint32_t r[32];
+        tmem_ld32(tmem_base + acc * 256 + c * 32 + (static_cast<uint32_t>(q * 32) << 16), r);
+        tmem_ld_wait();
+        if (!row_ok) continue;
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
+        const bool full = (col0 + 32 <= p.N);
+        if (p.bias) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (full || col0 + j < p.N) v[j] += p.bias[col0 + j];
+        }
+        if (p.beta != 0.f && p.C) {
+          if (p.c_fp32) {
+            const float* cp = reinterpret_cast<const float*>(p.C) + crow + col0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (full || col0 + j < p.N) v[j] += p.beta * cp[j];
+          } else {
+            const __nv_bfloat16* cp = reinterpret_cast<const __nv_bfloat16*>(p.C) + crow + col0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (full || col0 + j < p.N) v[j] += p.beta * __bfloat162float(cp[j]);
+          }
+        }
+        if (p.act == 1) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
+        } else if (p.act == 2) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = silu(v[j]);
+        } else if (p.act == 3) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
+        }
+        if (p.out_fp32) {
+          float* dp = reinterpret_cast<float*>(p.D) + drow + col0;
+          if (full && ((reinterpret_cast<uintptr_t>(dp) & 15) == 0)) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+              *reinterpret_cast<float4*>(dp + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+          } else {
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.N) dp[j] = v[j];
+          }
+        } else {
+          __nv_bfloat16* dp = reinterpret_cast<__nv_bfloat16*>(p.D) + drow + col0;
+          if (full && ((reinterpret_cast<uintptr_t>(dp) & 15) == 0)) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              uint4 o;
+              o.x = pack_bf16x2(v[j], v[j + 1]);
+              o.y = pack_bf16x2(v[j + 2], v[j + 3]);
+              o.z = pack_bf16x2(v[j + 4], v[j + 5]);
+              o.w = pack_bf16x2(v[j + 6], v[j + 7]);
+              *reinterpret_cast<uint4*>(dp + j) = o;
+            }
+          } else {
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.N) dp[j] = __float2bfloat16(v[j]);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_even_cta(&tempty_bar[acc]);
+      ++it;
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (*s_abort) bounded_delay_ns(2000000);  // let copies in flight land before freeing
+  cluster_sync_all();  // neither CTA leaves (or frees TMEM) while its peer may still read its memory or signal it
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+  }
+}
+
+template <bool A_MN, bool B_MN>
+static int launch_cfg2(const GemmKernelParams& kp, int sms, cudaStream_t st) {
+  static bool attr_set = false;
+  static int max_clusters = 0;
+  auto kern = gemm2_kernel<A_MN, B_MN>;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM_BYTES) != cudaSuccess) return -10;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(sms & ~1, 1, 1);
+    cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = G2_SMEM_BYTES;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    if (cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg) != cudaSuccess || max_clusters <= 0) {
+      cudaGetLastError();
+      max_clusters = sms / 2;
+    }
+    attr_set = true;
+  }
+  const long long tiles = (long long)kp.batch * kp.m_blks * kp.n_blks;
+  int clusters = (int)(tiles < max_clusters ? tiles : max_clusters);
+  if (clusters > sms / 2) clusters = sms / 2;
+  kern<<<2 * clusters, GEMM_THREADS, G2_SMEM_BYTES, st>>>(kp);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
 }  // namespace sx
 
 static int gemm_launch(const SxGemmArgs* a, const SxGemmCommArgs* cm, cudaStream_t st) {
@@ -594,6 +897,34 @@ static int gemm_launch(const SxGemmArgs* a, const SxGemmCommArgs* cm, cudaStream
   const int b_nbatch = a->tile_group ? a->num_groups : a->batch;
   // Reduction length seen by the tensor maps: total K rows/cols of the operand storage.
   const int Kfull = a->k_ranges ? a->k_total : a->K;
+  // CTA-pair kernel for plain dense products that fill at least one 256 x 256 pair tile.
+  static int use_pair = -1;
+  if (use_pair < 0) {
+    const char* e = getenv("SX_GEMM_2CTA");  // set to 0 to force the single-CTA kernel
+    use_pair = e ? atoi(e) : 1;
+  }
+  if (use_pair && !cm && !a->tile_group && !a->k_ranges && a->M >= 256 && a->N >= 256 && a->force_bn == 0 &&
+      a->sm_limit == 0 && (!a->a_mn || a->M % 64 == 0) && (!a->b_mn || a->N % 64 == 0)) {
+    const int bb2 = a->strideB != 0 && a->batch > 1;
+    int rc2 = make_operand_map(&kp.tmA, a->A, a->M, a->K, a->lda, a_batched, a->batch, a->strideA, a->a_mn != 0, 128);
+    if (rc2) return rc2;
+    rc2 = make_operand_map(&kp.tmB, a->B, a->N, a->K, a->ldb, bb2, a->batch, a->strideB, a->b_mn != 0, 128);
+    if (rc2) return rc2;
+    kp.D = a->D; kp.C = a->C; kp.bias = a->bias; kp.tile_group = nullptr; kp.k_ranges = nullptr; kp.status = a->status;
+    kp.ldd = a->ldd; kp.ldc = a->ldc; kp.strideD = a->strideD; kp.strideC = a->strideC;
+    kp.M = a->M; kp.N = a->N; kp.K = a->K; kp.batch = a->batch;
+    kp.a_batched = a_batched; kp.b_batched = bb2;
+    kp.out_fp32 = a->out_fp32; kp.c_fp32 = a->c_fp32; kp.act = a->act; kp.alpha = a->alpha; kp.beta = a->beta;
+    kp.m_blks = (a->M + 255) / 256; kp.n_blks = (a->N + 255) / 256;
+    int dev2 = 0, sms2 = 148;
+    cudaGetDevice(&dev2);
+    cudaDeviceGetAttribute(&sms2, cudaDevAttrMultiProcessorCount, dev2);
+    const int am2 = a->a_mn != 0, bm2 = a->b_mn != 0;
+    if (!am2 && !bm2) return launch_cfg2<false, false>(kp, sms2, st);
+    if (!am2 && bm2) return launch_cfg2<false, true>(kp, sms2, st);
+    if (am2 && !bm2) return launch_cfg2<true, false>(kp, sms2, st);
+    return launch_cfg2<true, true>(kp, sms2, st);
+  }
   int rc = make_operand_map(&kp.tmA, a->A, a->M, Kfull, a->lda, a_batched, a->batch, a->strideA, a->a_mn != 0, BM);
   if (rc) return rc;
   rc = make_operand_map(&kp.tmB, a->B, a->N, Kfull, a->ldb, b_batched, b_nbatch, a->strideB, a->b_mn != 0, BN);

@@ -74,12 +74,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* s_abort,
                                           int* g_status, int code) {
   if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = globaltimer_ns();
+  // The clock is read only after a batch of failed polls: a wait that completes within a few polls (the common case on
+  // the critical path of a pipelined kernel) never touches the timer.
+  uint64_t t0 = 0;
   uint32_t it = 0;
   while (!mbar_try_wait(bar, parity)) {
-    if (((++it) & 31u) == 0u) {
+    if (((++it) & 63u) == 0u) {
       if (*s_abort) return false;
-      if (globaltimer_ns() - t0 > SX_WAIT_TIMEOUT_NS) {
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > SX_WAIT_TIMEOUT_NS) {
         *s_abort = 1;
         if (g_status) atomicCAS(g_status, 0, code);
         return false;
@@ -91,6 +95,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 
 // Same wait executed by every lane of a converged warp; the outcome is made warp-uniform so that
 // the .sync.aligned tcgen05 instructions that follow are never reached by a partial warp.
+// (One poller per warp plus a broadcast was measured slower: the shuffle adds latency to every wake-up.)
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* s_abort,
                                                int* g_status, int code) {
   const bool ok = mbar_wait(bar, parity, s_abort, g_status, code);
