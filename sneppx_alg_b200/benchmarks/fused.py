@@ -1,0 +1,134 @@
+"""Fused compute+collective kernels against their rooflines and their library (cuBLAS + NCCL) equivalents.
+
+Run one process per GPU, e.g.
+``python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 -m sneppx_alg_b200.benchmarks.fused``
+
+For each path the roofline time is the slower of FLOPs / measured GEMM peak and bytes that must cross NVLink / link
+bandwidth (770 GB/s per direction per GPU measured on this pool, 900 nominal).  Times are CUDA-event times on each
+rank, maximum over ranks; rank 0 prints one JSON line per case.
+
+Cases
+  ag_gemm    all-gather of activation rows -> GEMM (TP column-parallel in_proj / QKV)
+  gemm_rs    GEMM -> reduce-scatter of output rows (TP row-parallel o_proj / down_proj)
+  zero_ag    ZeRO-3 parameter all-gather (pull kernel) of a 1 GiB bf16 bucket
+  allreduce  small all-reduce (norms / loss / router statistics)
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+import torch.distributed as dist
+
+NVLINK_GBS = 770.0
+
+
+def _peaks():
+    here = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    p = os.path.join(here, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d["bf16_tflops"], "measured"
+    return 1590.0, "fallback"
+
+
+def _time(fn, iters, group):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    dist.barrier(group)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / iters], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+    return float(t)
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--tokens", type=int, default=8192, help="total token rows of the TP group")
+    ap.add_argument("--d", type=int, default=4096)
+    ap.add_argument("--ff", type=int, default=14336)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--out", default=None)
+    a = ap.parse_args(argv)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    from ..ops import check_status
+    from ..parallel.symm import SymmGroup
+    from ..parallel.tp import FusedTP, _all_gather_rows, _reduce_scatter_rows
+    sg = SymmGroup()
+    tp = FusedTP(sg)
+    group = dist.group.WORLD
+    tf, src = _peaks()
+    res = []
+    T, d, ff = a.tokens, a.d, a.ff
+    rows = T // world
+    bf = dict(device="cuda", dtype=torch.bfloat16)
+
+    def report(name, shape, ms, ms_lib, flops, link_bytes, note=""):
+        t_compute = flops / (tf * 1e12) * 1e3
+        t_link = link_bytes / (NVLINK_GBS * 1e9) * 1e3
+        roof = max(t_compute, t_link)
+        r = {"case": name, "world": world, "shape": shape, "ms": ms, "library_ms": ms_lib, "speedup_vs_library": ms_lib / ms,
+             "roofline_ms": roof, f"frac_of_roofline_{src}": roof / ms, "bound": "compute" if t_compute >= t_link else "nvlink",
+             "note": note}
+        res.append(r)
+        if rank == 0:
+            print(json.dumps(r), flush=True)
+
+    # ---- all-gather -> GEMM: x [T/world, d] per rank, W_col [ff_local, d]
+    n_loc = (2 * ff // world) // 256 * 256
+    x_shard = torch.randn(rows, d, **bf)
+    w_col = torch.randn(n_loc, d, **bf) * 0.02
+    ms = _time(lambda: tp.ag_gemm(x_shard, w_col, key="bench_ag"), a.iters, group)
+    ms_lib = _time(lambda: torch.matmul(_all_gather_rows(x_shard, group), w_col.t()), a.iters, group)
+    report("ag_gemm", [T, n_loc, d], ms, ms_lib, 2.0 * T * n_loc * d, (world - 1) * rows * d * 2,
+           "gate_up column shard; link bytes = rows pulled from the other ranks")
+
+    # ---- GEMM -> reduce-scatter: h [T, ff_local] x W_row [d, ff_local] -> [T/world, d]
+    k_loc = (ff // world) // 64 * 64
+    h = torch.randn(T, k_loc, **bf)
+    w_row = torch.randn(d, k_loc, **bf) * 0.02
+    ms = _time(lambda: tp.gemm_rs(h, w_row), a.iters, group)
+    ms_lib = _time(lambda: _reduce_scatter_rows(torch.matmul(h, w_row.t()), group), a.iters, group)
+    report("gemm_rs", [T, d, k_loc], ms, ms_lib, 2.0 * T * d * k_loc, (world - 1) * rows * d * 2,
+           "down_proj row shard; link bytes = partial rows sent to their owners (bf16)")
+
+    # ---- ZeRO-3 parameter all-gather, 1 GiB bucket
+    n = (512 * 1024 * 1024) // world // 256 * 256
+    shard = sg.alloc(n, torch.bfloat16)
+    shard.tensor.normal_()
+    full = torch.empty(world * n, **bf)
+    lib_out = torch.empty(world * n, **bf)
+    ms = _time(lambda: sg.allgather_pull(shard, full, n * 2, grid=48), a.iters, group)
+    ms_lib = _time(lambda: dist.all_gather_into_tensor(lib_out, shard.tensor, group=group), a.iters, group)
+    report("zero_ag", [world * n], ms, ms_lib, 0.0, (world - 1) * n * 2, "pull kernel over peer loads")
+
+    # ---- small all-reduce
+    small = sg.alloc(1024, torch.float32)
+    small.tensor.fill_(1.0)
+    lib_small = torch.ones(1024, device="cuda")
+    ms = _time(lambda: sg.allreduce_small(small, 1024), 50, group)
+    ms_lib = _time(lambda: dist.all_reduce(lib_small, group=group), 50, group)
+    report("allreduce_4KB", [1024], ms, ms_lib, 0.0, 0.0, "latency bound: roofline not meaningful")
+    check_status()
+    if a.out and rank == 0:
+        json.dump(res, open(a.out, "w"), indent=1)
+    dist.barrier()
+    dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -4,7 +4,7 @@ time whole NumPy ops; here every case is one native sm_100a kernel).
 ``python -m sneppx_alg_b200.benchmarks.kernels <case> [--small] [--iters N] [--out file.json]``
 
 Cases: gemm, gemm_wgrad, attn_fwd, attn_bwd, rmsnorm, glu, rope, ce, adamw, sumsq, paged_decode, gemm_dq_fp8,
-gemm_dq_int4, conv1d, router, quant_fp8, all.  ``--small`` picks a problem that still exceeds L2 but holds well
+gemm_dq_int4, gemm_fp8, gemm_fp8_prefill, conv1d, router, quant_fp8, all.  ``--small`` picks a problem that still exceeds L2 but holds well
 under 2 GB so that one launch can be captured by a profiler in seconds.  Timing: CUDA events on the launching
 stream after 3 warm-up launches; inputs are larger than L2 or rotated between iterations.  Fractions are against the
 measured copy bandwidth / cuBLAS bf16 throughput in ``MEASURED_PEAKS.json`` when that file is present at the
@@ -183,6 +183,33 @@ def case_gemm_dq_fp8(small, iters):
 
 def case_gemm_dq_int4(small, iters):
     return _case_dq("int4", small, iters)
+
+
+def case_gemm_fp8(small, iters):
+    """Block-scaled fp8 x fp8 GEMM at decode size: weights streamed once."""
+    from ..ops import quant
+    M, N, K = (16, 14336, 4096) if small else (64, 28672, 8192)
+    w, x = _bf(N, K), _bf(M, K)
+    wq, sw = quant.quant_fp8_128x128(w)
+    xq, sx = quant.quant_fp8_1x128(x)
+    with torch.no_grad():
+        ms = _time(lambda: quant.gemm_fp8(None, wq, sw, xq=xq, sx=sx), iters)
+        ms_q = _time(lambda: quant.gemm_fp8(x, wq, sw), iters)
+        ms_lib = _time(lambda: torch.matmul(x, w.t()), iters)
+    return dict(shape=[M, N, K], ms=ms, ms_with_activation_quant=ms_q, flops=2 * M * N * K, bytes=N * K + M * K + 2 * M * N,
+                lib_ms=ms_lib, lib="cuBLAS bf16 weights")
+
+
+def case_gemm_fp8_prefill(small, iters):
+    from ..ops import quant
+    M, N, K = (1024, 4096, 4096) if small else (4096, 14336, 4096)
+    w, x = _bf(N, K), _bf(M, K)
+    wq, sw = quant.quant_fp8_128x128(w)
+    xq, sx = quant.quant_fp8_1x128(x)
+    with torch.no_grad():
+        ms = _time(lambda: quant.gemm_fp8(None, wq, sw, xq=xq, sx=sx), iters)
+        ms_lib = _time(lambda: torch.matmul(x, w.t()), iters)
+    return dict(shape=[M, N, K], ms=ms, flops=2 * M * N * K, bytes=N * K + M * K + 2 * M * N, lib_ms=ms_lib, lib="cuBLAS bf16")
 
 
 def case_conv1d(small, iters):

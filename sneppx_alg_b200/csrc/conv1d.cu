@@ -17,41 +17,74 @@ __device__ __forceinline__ float silu_grad(float x) {
   return s * (1.f + x * (1.f - s));
 }
 
-// one thread: 8 channels of one (b, l)
-__global__ void conv1d_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ prev,
-                                  const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ bias,
-                                  __nv_bfloat16* __restrict__ y, __nv_bfloat16* __restrict__ state_out, int B, int L,
-                                  int C, int K, int act) {
+// One thread: 8 channels x CONV_TL consecutive positions. The 8 x K weights and the bias live in registers and the
+// K-1 previous inputs slide through registers, so each input vector is loaded once and each output costs one 16-byte
+// load and one 16-byte store; consecutive threads own consecutive channel vectors (coalesced rows).
+constexpr int CONV_TL = 16;
+template <int K>
+__global__ void __launch_bounds__(256) conv1d_fwd_kernel(const __nv_bfloat16* __restrict__ x,
+                                                         const __nv_bfloat16* __restrict__ prev,
+                                                         const __nv_bfloat16* __restrict__ w,
+                                                         const __nv_bfloat16* __restrict__ bias,
+                                                         __nv_bfloat16* __restrict__ y,
+                                                         __nv_bfloat16* __restrict__ state_out, int B, int L, int C,
+                                                         int act) {
   const int cv = C >> 3;
-  const long long total = (long long)B * L * cv;
+  const int lchunks = (L + CONV_TL - 1) / CONV_TL;
+  const long long total = (long long)B * lchunks * cv;
   for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
        idx += (long long)gridDim.x * blockDim.x) {
-    const int c = (idx % cv) * 8;
+    const int c = (int)(idx % cv) * 8;
     const long long bl = idx / cv;
-    const int l = bl % L;
-    const int b = bl / L;
-    float acc[8];
-    if (bias) unpack8(ld8(bias + c), acc);
+    const int l0 = (int)(bl % lchunks) * CONV_TL;
+    const int b = (int)(bl / lchunks);
+    float wv[CONV_MAXK][8], bv[8];
+#pragma unroll
+    for (int k = 0; k < CONV_MAXK; ++k)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) wv[k][j] = (k < K) ? __bfloat162float(w[(c + j) * K + k]) : 0.f;
+    if (bias) unpack8(ld8(bias + c), bv);
     else {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      for (int j = 0; j < 8; ++j) bv[j] = 0.f;
     }
-    for (int k = 0; k < K; ++k) {
-      const int ls = l - (K - 1) + k;
-      float xv[8];
-      if (ls >= 0) unpack8(ld8(x + ((long long)b * L + ls) * C + c), xv);
-      else if (prev) unpack8(ld8(prev + ((long long)b * (K - 1) + (K - 1 + ls)) * C + c), xv);
-      else continue;
+    // hist[i] = input at position l - (K-1) + i for the current l; hist[K-1] is the current input
+    float hist[CONV_MAXK][8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) acc[j] += xv[j] * __bfloat162float(w[(c + j) * K + k]);
-    }
-    if (act) {
+    for (int i = 0; i < CONV_MAXK; ++i)
 #pragma unroll
-      for (int j = 0; j < 8; ++j) acc[j] = silu_f(acc[j]);
+      for (int j = 0; j < 8; ++j) hist[i][j] = 0.f;
+    for (int i = 0; i < K - 1; ++i) {
+      const int ls = l0 - (K - 1) + i;
+      if (ls >= 0) unpack8(ld8(x + ((long long)b * L + ls) * C + c), hist[i]);
+      else if (prev) unpack8(ld8(prev + ((long long)b * (K - 1) + (K - 1 + ls)) * C + c), hist[i]);
     }
-    st8(y + bl * C + c, pack8(acc));
-    if (state_out && l >= L - (K - 1)) st8(state_out + ((long long)b * (K - 1) + (l - (L - (K - 1)))) * C + c,
-                                           ld8(x + bl * C + c));
+    const int l1 = min(L, l0 + CONV_TL);
+    for (int l = l0; l < l1; ++l) {
+      const bf16x8 raw = ld8(x + ((long long)b * L + l) * C + c);
+      unpack8(raw, hist[K - 1]);
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = bv[j];
+#pragma unroll
+      for (int k = 0; k < CONV_MAXK; ++k)
+        if (k < K) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] = fmaf(hist[k][j], wv[k][j], acc[j]);
+        }
+      if (act) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = silu_f(acc[j]);
+      }
+      st8(y + ((long long)b * L + l) * C + c, pack8(acc));
+      if (state_out && l >= L - (K - 1)) st8(state_out + ((long long)b * (K - 1) + (l - (L - (K - 1)))) * C + c, raw);
+#pragma unroll
+      for (int i = 0; i < CONV_MAXK - 1; ++i)
+        if (i < K - 1) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) hist[i][j] = hist[i + 1][j];
+        }
+    }
   }
 }
 
@@ -161,12 +194,20 @@ using namespace sx;
 extern "C" int sx_conv1d_fwd(const void* x, const void* prev, const void* w, const void* bias, void* y, void* state_out,
                              int B, int L, int C, int K, int act, cudaStream_t st) {
   if (C % 8 || K > CONV_MAXK || K < 1) return -1;
-  const long long total = (long long)B * L * (C / 8);
+  const long long total = (long long)B * ((L + CONV_TL - 1) / CONV_TL) * (C / 8);
   if (total == 0) return 0;
   const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
-  conv1d_fwd_kernel<<<blocks, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)prev,
-                                            (const __nv_bfloat16*)w, (const __nv_bfloat16*)bias, (__nv_bfloat16*)y,
-                                            (__nv_bfloat16*)state_out, B, L, C, K, act);
+#define SX_CONV_FWD(KK)                                                                                          \
+  conv1d_fwd_kernel<KK><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)prev,              \
+                                                (const __nv_bfloat16*)w, (const __nv_bfloat16*)bias, (__nv_bfloat16*)y, \
+                                                (__nv_bfloat16*)state_out, B, L, C, act)
+  switch (K) {
+    case 1: SX_CONV_FWD(1); break;
+    case 2: SX_CONV_FWD(2); break;
+    case 3: SX_CONV_FWD(3); break;
+    default: SX_CONV_FWD(4); break;
+  }
+#undef SX_CONV_FWD
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

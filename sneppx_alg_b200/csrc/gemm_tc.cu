@@ -591,11 +591,15 @@ static int make_operand_map(CUtensorMap* tm, const void* ptr, int mn, int K, lon
 //   tfull[a]  both CTAs: accumulator a complete, multicast commit
 //   tempty[a] even CTA only, 8 arrivals: the four epilogue warps of each CTA arrive on it (the odd CTA remotely)
 // Dense, non-grouped, non-fused calls only; everything else stays on gemm_tc_kernel.
-constexpr int G2_STAGES = 6;
-constexpr int G2_A_BYTES = 128 * BK * 2;   // 16 KB
-constexpr int G2_B_BYTES = 128 * BK * 2;   // 16 KB: this CTA's half of the 256-row B tile
-constexpr int G2_STAGE_BYTES = G2_A_BYTES + G2_B_BYTES;
-constexpr int G2_SMEM_BYTES = G2_STAGES * G2_STAGE_BYTES + 1024 + 256;
+// Pair tile 256 x BN2 (BN2 = 256, or 128 when the wider tile would leave the last wave of pairs mostly idle).
+template <int BN2>
+struct G2Cfg {
+  static constexpr int STAGES = BN2 == 256 ? 6 : 8;
+  static constexpr int A_BYTES = 128 * BK * 2;          // 16 KB
+  static constexpr int B_BYTES = (BN2 / 2) * BK * 2;    // this CTA's half of the B tile
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+};
 constexpr uint32_t PEER_MASK = 0xFEFFFFFFu;  // clears the CTA-rank bit of a shared::cluster address: the even CTA's copy
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -640,9 +644,12 @@ __device__ __forceinline__ void mbar_arrive_even_cta(uint64_t* bar) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(smem_u32(bar) & PEER_MASK) : "memory");
 }
 
-template <bool A_MN, bool B_MN>
+template <int BN2, bool A_MN, bool B_MN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
     gemm2_kernel(const __grid_constant__ GemmKernelParams p) {
+  constexpr int G2_STAGES = G2Cfg<BN2>::STAGES;
+  constexpr int G2_A_BYTES = G2Cfg<BN2>::A_BYTES;
+  constexpr int G2_STAGE_BYTES = G2Cfg<BN2>::STAGE_BYTES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + G2_STAGES * G2_STAGE_BYTES);
@@ -684,7 +691,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  // p.m_blks counts 256-row pair tiles, p.n_blks 256-column tiles
+  // p.m_blks counts 256-row pair tiles, p.n_blks BN2-column tiles
   const int total_tiles = p.batch * p.m_blks * p.n_blks;
 
   if (warp == 0) {
@@ -697,7 +704,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
         tile_coords(t, p.m_blks, p.n_blks, b, m_blk, n_blk);
         const int ab = p.a_batched ? b : 0, bb = p.b_batched ? b : 0;
         const int num_kb = (p.K + BK - 1) / BK;
-        const int arow = m_blk * 256 + (int)rank * 128, brow = n_blk * 256 + (int)rank * 128;
+        const int arow = m_blk * 256 + (int)rank * 128, brow = n_blk * BN2 + (int)rank * (BN2 / 2);
         bool ok = true;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, s_abort, p.status, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
@@ -718,7 +725,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (even CTA only)
     if (lane == 0 && rank == 0) {
-      constexpr uint32_t idesc = umma_idesc_f16(256, 256, 1, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      constexpr uint32_t idesc = umma_idesc_f16(256, BN2, 1, A_MN ? 1 : 0, B_MN ? 1 : 0);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
@@ -729,7 +736,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
         const uint32_t acc_phase = (it >> 1) & 1;
         if (!mbar_wait(&tempty_bar[acc], acc_phase ^ 1, s_abort, p.status, ST_TIMEOUT_MMA)) break;
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * 256;
+        const uint32_t d_tmem = tmem_base + acc * BN2;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, s_abort, p.status, ST_TIMEOUT_MMA)) { ok = false; break; }
           tc_fence_after();
@@ -767,11 +774,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
       const long long drow = (long long)b * p.strideD + (long long)row * p.ldd;
       const long long crow = (long long)b * p.strideC + (long long)row * p.ldc;
 #pragma unroll 1
-      for (int c = 0; c < 256 / 32; ++c) {
-        const int col0 = n_blk * 256 + c * 32;
+      for (int c = 0; c < BN2 / 32; ++c) {
+        const int col0 = n_blk * BN2 + c * 32;
         if (col0 >= p.N) break;  // uniform across the warp
         uint32_t r[32];
-        tmem_ld32(tmem_base + acc * 256 + c * 32 + (static_cast<uint32_t>(q * 32) << 16), r);
+        tmem_ld32(tmem_base + acc * BN2 + c * 32 + (static_cast<uint32_t>(q * 32) << 16), r);
         tmem_ld_wait();
         if (!row_ok) continue;
         float v[32];
@@ -852,32 +859,46 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
   }
 }
 
-template <bool A_MN, bool B_MN>
+static int g2_max_clusters(int sms) {
+  // the largest number of 2-CTA clusters of this kernel family that can be co-resident (74 on a 148-SM part)
+  return sms / 2;
+}
+
+template <int BN2, bool A_MN, bool B_MN>
 static int launch_cfg2(const GemmKernelParams& kp, int sms, cudaStream_t st) {
   static bool attr_set = false;
   static int max_clusters = 0;
-  auto kern = gemm2_kernel<A_MN, B_MN>;
+  auto kern = gemm2_kernel<BN2, A_MN, B_MN>;
+  constexpr int SMEM = G2Cfg<BN2>::SMEM_BYTES;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, G2_SMEM_BYTES) != cudaSuccess) return -10;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return -10;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(sms & ~1, 1, 1);
     cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
-    cfg.dynamicSmemBytes = G2_SMEM_BYTES;
+    cfg.dynamicSmemBytes = SMEM;
     cudaLaunchAttribute at[1];
     at[0].id = cudaLaunchAttributeClusterDimension;
     at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
     cfg.attrs = at; cfg.numAttrs = 1;
     if (cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg) != cudaSuccess || max_clusters <= 0) {
       cudaGetLastError();
-      max_clusters = sms / 2;
+      max_clusters = g2_max_clusters(sms);
     }
     attr_set = true;
   }
   const long long tiles = (long long)kp.batch * kp.m_blks * kp.n_blks;
   int clusters = (int)(tiles < max_clusters ? tiles : max_clusters);
   if (clusters > sms / 2) clusters = sms / 2;
-  kern<<<2 * clusters, GEMM_THREADS, G2_SMEM_BYTES, st>>>(kp);
+  kern<<<2 * clusters, GEMM_THREADS, SMEM, st>>>(kp);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+template <int BN2>
+static int launch_cfg2_any(const GemmKernelParams& kp, int am, int bm, int sms, cudaStream_t st) {
+  if (!am && !bm) return launch_cfg2<BN2, false, false>(kp, sms, st);
+  if (!am && bm) return launch_cfg2<BN2, false, true>(kp, sms, st);
+  if (am && !bm) return launch_cfg2<BN2, true, false>(kp, sms, st);
+  return launch_cfg2<BN2, true, true>(kp, sms, st);
 }
 
 }  // namespace sx
@@ -906,24 +927,26 @@ static int gemm_launch(const SxGemmArgs* a, const SxGemmCommArgs* cm, cudaStream
   if (use_pair && !cm && !a->tile_group && !a->k_ranges && a->M >= 256 && a->N >= 256 && a->force_bn == 0 &&
       a->sm_limit == 0 && (!a->a_mn || a->M % 64 == 0) && (!a->b_mn || a->N % 64 == 0)) {
     const int bb2 = a->strideB != 0 && a->batch > 1;
+    int dev2 = 0, sms2 = 148;
+    cudaGetDevice(&dev2);
+    cudaDeviceGetAttribute(&sms2, cudaDevAttrMultiProcessorCount, dev2);
+    // Tile width: 256 unless the narrower tile wastes less of the last wave (a 256 x 128 tile costs ~0.53 of a 256 x 256 one).
+    const long long mp = (a->M + 255) / 256, pairs = sms2 / 2;
+    const long long t256 = (long long)a->batch * mp * ((a->N + 255) / 256), t128 = (long long)a->batch * mp * ((a->N + 127) / 128);
+    const double c256 = (double)((t256 + pairs - 1) / pairs), c128 = 0.53 * (double)((t128 + pairs - 1) / pairs);
+    const int bn2 = (a->force_bn == 0 && c128 < c256) ? 128 : 256;
     int rc2 = make_operand_map(&kp.tmA, a->A, a->M, a->K, a->lda, a_batched, a->batch, a->strideA, a->a_mn != 0, 128);
     if (rc2) return rc2;
-    rc2 = make_operand_map(&kp.tmB, a->B, a->N, a->K, a->ldb, bb2, a->batch, a->strideB, a->b_mn != 0, 128);
+    rc2 = make_operand_map(&kp.tmB, a->B, a->N, a->K, a->ldb, bb2, a->batch, a->strideB, a->b_mn != 0, bn2 / 2);
     if (rc2) return rc2;
     kp.D = a->D; kp.C = a->C; kp.bias = a->bias; kp.tile_group = nullptr; kp.k_ranges = nullptr; kp.status = a->status;
     kp.ldd = a->ldd; kp.ldc = a->ldc; kp.strideD = a->strideD; kp.strideC = a->strideC;
     kp.M = a->M; kp.N = a->N; kp.K = a->K; kp.batch = a->batch;
     kp.a_batched = a_batched; kp.b_batched = bb2;
     kp.out_fp32 = a->out_fp32; kp.c_fp32 = a->c_fp32; kp.act = a->act; kp.alpha = a->alpha; kp.beta = a->beta;
-    kp.m_blks = (a->M + 255) / 256; kp.n_blks = (a->N + 255) / 256;
-    int dev2 = 0, sms2 = 148;
-    cudaGetDevice(&dev2);
-    cudaDeviceGetAttribute(&sms2, cudaDevAttrMultiProcessorCount, dev2);
+    kp.m_blks = (a->M + 255) / 256; kp.n_blks = (a->N + bn2 - 1) / bn2;
     const int am2 = a->a_mn != 0, bm2 = a->b_mn != 0;
-    if (!am2 && !bm2) return launch_cfg2<false, false>(kp, sms2, st);
-    if (!am2 && bm2) return launch_cfg2<false, true>(kp, sms2, st);
-    if (am2 && !bm2) return launch_cfg2<true, false>(kp, sms2, st);
-    return launch_cfg2<true, true>(kp, sms2, st);
+    return bn2 == 256 ? launch_cfg2_any<256>(kp, am2, bm2, sms2, st) : launch_cfg2_any<128>(kp, am2, bm2, sms2, st);
   }
   int rc = make_operand_map(&kp.tmA, a->A, a->M, Kfull, a->lda, a_batched, a->batch, a->strideA, a->a_mn != 0, BM);
   if (rc) return rc;

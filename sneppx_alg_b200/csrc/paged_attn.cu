@@ -9,119 +9,120 @@
 
 namespace sx {
 
-constexpr int PA_TILE = 128;   // positions per tile == threads per CTA
+constexpr int PA_TILE = 128;   // threads per CTA
 constexpr int PA_MAX_G = 8;    // query heads per KV head
 
-template <int D>
+// One CTA: (sequence b, KV head hk, split). A K/V row (D bf16) is read by D/8 adjacent lanes with one 16-byte load
+// each, so a warp reads 2 (D=128) or 4 (D=64) whole rows per load instruction, fully coalesced; the lanes of a row
+// keep their 8-wide slice of every query head in registers, reduce the partial dot products with shuffles and
+// accumulate P*V for their slice. Every lane group runs its own online softmax over the positions it owns; groups
+// are merged through shared memory at the end, splits by paged_merge_kernel.
+template <int D, int GT>
 __global__ void __launch_bounds__(PA_TILE) paged_decode_kernel(
     const __nv_bfloat16* __restrict__ q, long long q_row_stride, const __nv_bfloat16* __restrict__ k_cache,
     const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_table, const int* __restrict__ seq_lens,
     float* __restrict__ o_part, float* __restrict__ ml_part, int Hq, int Hkv, int block_size, int max_blocks,
     int nsplit, float scale) {
+  constexpr int LPR = D / 8;            // lanes per row
+  constexpr int RPW = 32 / LPR;         // rows per warp-wide load
+  constexpr int NGRP = (PA_TILE / 32) * RPW;
+  constexpr int U = 4;                  // rows in flight per lane group
   const int b = blockIdx.x, hk = blockIdx.y, split = blockIdx.z;
   const int G = Hq / Hkv;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  __shared__ float s_q[PA_MAX_G][D];
-  __shared__ float s_p[PA_MAX_G][PA_TILE];
-  __shared__ long long s_row[PA_TILE];
-  __shared__ float s_red[PA_MAX_G][4];
-  __shared__ float s_alpha[PA_MAX_G];
+  const int sub = lane % LPR, grp = warp * RPW + lane / LPR;
+  __shared__ float s_m[NGRP][GT], s_l[NGRP][GT];
+  __shared__ float s_acc[NGRP][GT][D];
   const int len = seq_lens[b];
   const int per = (len + nsplit - 1) / nsplit;
   const int p0 = split * per, p1 = min(len, p0 + per);
+  float qr[GT][8], m[GT], l[GT], acc[GT][8];
+#pragma unroll
+  for (int g = 0; g < GT; ++g) {
+    if (g < G) {
+      unpack8(ld8(q + (long long)b * q_row_stride + (long long)(hk * G + g) * D + sub * 8), qr[g]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) qr[g][j] *= scale;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) qr[g][j] = 0.f;
+    }
+    m[g] = -INFINITY;
+    l[g] = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[g][j] = 0.f;
+  }
+  const int* tbl = block_table + (long long)b * max_blocks;
+  for (int base = p0; base < p1; base += NGRP * U) {   // uniform trip count for the whole CTA
+    bf16x8 kraw[U], vraw[U];
+    bool valid[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int pos = base + u * NGRP + grp;
+      valid[u] = pos < p1;
+      if (valid[u]) {
+        const int blk = tbl[pos / block_size];
+        const long long row = (((long long)blk * block_size + pos % block_size) * Hkv + hk) * D + sub * 8;
+        kraw[u] = ld8(k_cache + row);
+        vraw[u] = ld8(v_cache + row);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      float kv[8], vv[8];
+      if (valid[u]) { unpack8(kraw[u], kv); unpack8(vraw[u], vv); }
+      else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { kv[j] = 0.f; vv[j] = 0.f; }
+      }
+#pragma unroll
+      for (int g = 0; g < GT; ++g) {
+        float sc = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sc = fmaf(kv[j], qr[g][j], sc);
+#pragma unroll
+        for (int o = LPR / 2; o > 0; o >>= 1) sc += __shfl_xor_sync(0xffffffffu, sc, o);
+        if (valid[u]) {
+          if (sc > m[g]) {
+            const float alpha = __expf(m[g] - sc);   // exp(-inf) = 0 on the first row
+            l[g] *= alpha;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[g][j] *= alpha;
+            m[g] = sc;
+          }
+          const float pr = __expf(sc - m[g]);
+          l[g] += pr;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[g][j] = fmaf(pr, vv[j], acc[g][j]);
+        }
+      }
+    }
+  }
+  // merge the lane groups
+#pragma unroll
+  for (int g = 0; g < GT; ++g) {
+    if (sub == 0) { s_m[grp][g] = m[g]; s_l[grp][g] = l[g]; }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s_acc[grp][g][sub * 8 + j] = acc[g][j];
+  }
+  __syncthreads();
   for (int i = tid; i < G * D; i += PA_TILE) {
     const int g = i / D, d = i % D;
-    s_q[g][d] = __bfloat162float(q[(long long)b * q_row_stride + (long long)(hk * G + g) * D + d]) * scale;
-  }
-  float m_run[PA_MAX_G], l_run[PA_MAX_G], acc[PA_MAX_G];
+    float mm = -INFINITY;
 #pragma unroll
-  for (int g = 0; g < PA_MAX_G; ++g) { m_run[g] = -INFINITY; l_run[g] = 0.f; acc[g] = 0.f; }
-  __syncthreads();
-  for (int t0 = p0; t0 < p1; t0 += PA_TILE) {
-    const int pos = t0 + tid;
-    const bool valid = pos < p1;
-    long long rowoff = 0;
-    if (valid) {
-      const int blk = block_table[(long long)b * max_blocks + pos / block_size];
-      rowoff = (((long long)blk * block_size + pos % block_size) * Hkv + hk) * D;
+    for (int r = 0; r < NGRP; ++r) mm = fmaxf(mm, s_m[r][g]);
+    float ll = 0.f, oo = 0.f;
+#pragma unroll
+    for (int r = 0; r < NGRP; ++r) {
+      const float w = (s_m[r][g] == -INFINITY) ? 0.f : __expf(s_m[r][g] - mm);
+      ll += s_l[r][g] * w;
+      oo += s_acc[r][g][d] * w;
     }
-    s_row[tid] = valid ? rowoff : -1;
-    // scores of this thread's position against all G query heads
-    float sc[PA_MAX_G];
-#pragma unroll
-    for (int g = 0; g < PA_MAX_G; ++g) sc[g] = 0.f;
-    if (valid) {
-      const __nv_bfloat16* kr = k_cache + rowoff;
-      for (int d = 0; d < D; d += 8) {
-        float kv[8];
-        unpack8(ld8(kr + d), kv);
-#pragma unroll
-        for (int g = 0; g < PA_MAX_G; ++g)
-          if (g < G) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) sc[g] += kv[j] * s_q[g][d + j];
-          }
-      }
-    }
-    // tile max per head
-#pragma unroll
-    for (int g = 0; g < PA_MAX_G; ++g) {
-      if (g < G) {
-        const float v = warp_max(valid ? sc[g] : -INFINITY);
-        if (lane == 0) s_red[g][warp] = v;
-      }
-    }
-    __syncthreads();
-#pragma unroll
-    for (int g = 0; g < PA_MAX_G; ++g) {
-      if (g < G) {
-        const float tm = fmaxf(fmaxf(s_red[g][0], s_red[g][1]), fmaxf(s_red[g][2], s_red[g][3]));
-        const float mn = fmaxf(m_run[g], tm);
-        const float pr = valid ? __expf(sc[g] - mn) : 0.f;
-        s_p[g][tid] = pr;
-        const float alpha = (m_run[g] == -INFINITY) ? 0.f : __expf(m_run[g] - mn);
-        if (tid == 0) s_alpha[g] = alpha;
-        m_run[g] = mn;
-        sc[g] = pr;
-      }
-    }
-    __syncthreads();
-    // row sums
-#pragma unroll
-    for (int g = 0; g < PA_MAX_G; ++g) {
-      if (g < G) {
-        const float v = warp_sum(sc[g]);
-        if (lane == 0) s_red[g][warp] = v;
-      }
-    }
-    __syncthreads();
-#pragma unroll
-    for (int g = 0; g < PA_MAX_G; ++g)
-      if (g < G) l_run[g] = l_run[g] * s_alpha[g] + (s_red[g][0] + s_red[g][1] + s_red[g][2] + s_red[g][3]);
-    // P V: thread = head-dim index
-    if (tid < D) {
-#pragma unroll
-      for (int g = 0; g < PA_MAX_G; ++g)
-        if (g < G) acc[g] *= s_alpha[g];
-      const int n = min(PA_TILE, p1 - t0);
-      for (int t = 0; t < n; ++t) {
-        const float v = __bfloat162float(v_cache[s_row[t] + tid]);
-#pragma unroll
-        for (int g = 0; g < PA_MAX_G; ++g)
-          if (g < G) acc[g] += s_p[g][t] * v;
-      }
-    }
-    __syncthreads();
-  }
-#pragma unroll
-  for (int g = 0; g < PA_MAX_G; ++g) {
-    if (g < G) {
-      const long long idx = ((long long)b * Hq + hk * G + g) * nsplit + split;
-      if (tid < D) o_part[idx * D + tid] = acc[g];
-      if (tid == 0) {
-        ml_part[idx * 2] = m_run[g];
-        ml_part[idx * 2 + 1] = l_run[g];
-      }
+    const long long idx = ((long long)b * Hq + hk * G + g) * nsplit + split;
+    o_part[idx * D + d] = oo;
+    if (d == 0) {
+      ml_part[idx * 2] = mm;
+      ml_part[idx * 2 + 1] = ll;
     }
   }
 }
@@ -184,6 +185,13 @@ __global__ void kv_append_kernel(__nv_bfloat16* __restrict__ qkv, long long row_
 }  // namespace sx
 using namespace sx;
 
+// Splits along the sequence: enough CTAs to fill the machine a few times over, at least 256 positions per split.
+extern "C" int sx_paged_decode_splits2(int max_len, int ctas_per_split) {
+  int by_len = (max_len + 255) / 256;
+  int want = (148 * 4 + ctas_per_split - 1) / (ctas_per_split > 0 ? ctas_per_split : 1);
+  int s = by_len < want ? by_len : want;
+  return s < 1 ? 1 : (s > 64 ? 64 : s);
+}
 extern "C" int sx_paged_decode_splits(int max_len) {
   int s = (max_len + 1023) / 1024;
   return s < 1 ? 1 : (s > 32 ? 32 : s);
@@ -196,16 +204,18 @@ extern "C" int sx_paged_decode(const void* q, long long q_row_stride, const void
                                int max_blocks, int nsplit, float scale, cudaStream_t st) {
   if (Hq % Hkv || Hq / Hkv > PA_MAX_G || (D != 64 && D != 128)) return -1;
   dim3 grid(B, Hkv, nsplit);
-  if (D == 128)
-    paged_decode_kernel<128><<<grid, PA_TILE, 0, st>>>((const __nv_bfloat16*)q, q_row_stride,
-                                                       (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
-                                                       block_table, seq_lens, o_part, ml_part, Hq, Hkv, block_size,
-                                                       max_blocks, nsplit, scale);
-  else
-    paged_decode_kernel<64><<<grid, PA_TILE, 0, st>>>((const __nv_bfloat16*)q, q_row_stride,
-                                                      (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
-                                                      block_table, seq_lens, o_part, ml_part, Hq, Hkv, block_size,
-                                                      max_blocks, nsplit, scale);
+  const int G = Hq / Hkv;
+#define SX_PD(DD, GG)                                                                                              \
+  paged_decode_kernel<DD, GG><<<grid, PA_TILE, 0, st>>>((const __nv_bfloat16*)q, q_row_stride,                       \
+                                                        (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, \
+                                                        block_table, seq_lens, o_part, ml_part, Hq, Hkv, block_size, \
+                                                        max_blocks, nsplit, scale)
+  if (D == 128) {
+    if (G == 1) SX_PD(128, 1); else if (G == 2) SX_PD(128, 2); else if (G <= 4) SX_PD(128, 4); else SX_PD(128, 8);
+  } else {
+    if (G == 1) SX_PD(64, 1); else if (G == 2) SX_PD(64, 2); else if (G <= 4) SX_PD(64, 4); else SX_PD(64, 8);
+  }
+#undef SX_PD
   paged_merge_kernel<<<dim3(B, Hq), D, 0, st>>>(o_part, ml_part, (__nv_bfloat16*)out, out_row_stride, Hq, D, nsplit);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }

@@ -59,7 +59,7 @@ def paged_decode(q, k_cache, v_cache, block_table, seq_lens, scale=None):
     if q.is_cuda and q.dtype == torch.bfloat16 and _lib.available() and D in (64, 128) and Hq // Hkv <= 8:
         q = q if q.stride(2) == 1 and q.stride(1) == D else q.contiguous()
         max_len = block_table.shape[1] * bs
-        ns = _lib.lib().sx_paged_decode_splits(c_int(max_len))
+        ns = _lib.lib().sx_paged_decode_splits2(c_int(max_len), c_int(B * Hkv))
         out = torch.empty(B, Hq, D, dtype=q.dtype, device=q.device)
         o_part = torch.empty(B * Hq * ns * D, dtype=torch.float32, device=q.device)
         ml = torch.empty(B * Hq * ns * 2, dtype=torch.float32, device=q.device)

@@ -4,6 +4,8 @@ restatements serve CPU tensors and act as the oracle. Formats: activations 1x128
 Reference API names: ``quantize_fp8_e4m3`` / ``quantize_int4`` (interface_bindings/quantization.py)."""
 from __future__ import annotations
 
+import ctypes
+
 import torch
 
 from . import _lib
@@ -113,6 +115,44 @@ def dequant_int4(packed, scales, dtype=torch.bfloat16):
 
 
 # ----------------------------------------------------------------------------- Q2 dequant-GEMM
+def gemm_fp8_reference(xq, sx, wq, sw, bias=None, out_dtype=torch.bfloat16):
+    """fp32 oracle of the block-scaled product: dequantise both operands, multiply."""
+    M, K = xq.shape
+    N = wq.shape[0]
+    x = xq.float().view(M, K // 128, 128) * sx.float()[..., None]
+    w = dequant_fp8(wq, sw, "128x128", torch.float32)
+    y = x.view(M, K) @ w.t()
+    if bias is not None:
+        y = y + bias.float()
+    return y.to(out_dtype)
+
+
+def gemm_fp8(x, wq, sw, bias=None, xq=None, sx=None):
+    """y = x @ W^T with both operands in block-scaled e4m3 on the fp8 tensor-core path.
+
+    x bf16 [.., K] is quantised per 1 x 128 block on the fly (or pass ``xq`` / ``sx``); ``wq`` float8_e4m3fn [N, K] with
+    ``sw`` fp32 [ceil(N/128), K/128] (``quant_fp8_128x128``). Weights are streamed once; suited to decode-size M as
+    well as expert GEMMs."""
+    K = x.shape[-1] if x is not None else xq.shape[-1]
+    lead = x.shape[:-1] if x is not None else xq.shape[:-1]
+    if xq is None:
+        xq, sx = quant_fp8_1x128(x.reshape(-1, K))
+    M, N = xq.shape[0], wq.shape[0]
+    if xq.is_cuda and _lib.available() and K % 128 == 0:
+        xq_, wq_ = xq.view(torch.uint8).contiguous(), wq.view(torch.uint8).contiguous()
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=xq.device)
+        fn = _lib.lib().sx_gemm_fp8_workspace
+        fn.restype = ctypes.c_longlong
+        nbytes = fn(c_int(M), c_int(N), c_int(K))
+        work = torch.empty(max(nbytes // 4, 1), dtype=torch.float32, device=xq.device) if nbytes else None
+        b = bias.float().contiguous() if bias is not None else None
+        _lib.call("sx_gemm_fp8", ptr(xq_), c_ll(xq_.stride(0)), ptr(sx.contiguous()), ptr(wq_), c_ll(wq_.stride(0)),
+                  ptr(sw.contiguous()), ptr(b), ptr(out), c_ll(out.stride(0)), ptr(work), c_int(M), c_int(N), c_int(K),
+                  ptr(_lib.status_word(xq.device)), stream())
+        return out.view(*lead, N)
+    return gemm_fp8_reference(xq, sx, wq, sw, bias).view(*lead, N)
+
+
 def gemm_dequant(x, qweight, scales, mode="fp8", bias=None):
     """y = x @ dequant(W)^T. x bf16 [.., K]; mode 'fp8': qweight float8_e4m3fn/uint8 [N, K], scales [N/128, K/128];
     mode 'int4': qweight uint8 [N, K/2], scales [N, K/128]. CUDA: weights are expanded to bf16 inside the GEMM."""

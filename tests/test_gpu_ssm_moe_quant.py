@@ -122,3 +122,26 @@ def test_models_train_on_gpu():
             last = eng.step(ids, ids).item()
         ops.check_status()
         assert last == last and last < first, (cfg.architecture, first, last)
+
+
+def test_gemm_fp8_block_scaled():
+    """fp8 x fp8 tensor-core GEMM against the fp32 product of the dequantised operands (same quantised inputs, so
+    the only differences are accumulation order and the bf16 output rounding)."""
+    from sneppx_alg_b200.ops import quant
+    torch.manual_seed(0)
+    for M, N, K in ((5, 256, 512), (64, 384, 1024), (33, 1000, 256), (200, 128, 2048), (16, 4096, 4096)):
+        x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.05
+        bias = torch.randn(N, device="cuda")
+        wq, sw = quant.quant_fp8_128x128(w)
+        xq, sx = quant.quant_fp8_1x128(x)
+        y = quant.gemm_fp8(None, wq, sw, bias=bias, xq=xq, sx=sx)
+        ref = quant.gemm_fp8_reference(xq, sx, wq, sw, bias, torch.float32)
+        err = (y.float() - ref).abs().max() / ref.abs().max()
+        assert err < 1e-2, (M, N, K, float(err))
+        # end to end against the unquantised product: fp8 quantisation noise only
+        y2 = quant.gemm_fp8(x, wq, sw, bias=bias)
+        full = x.float() @ w.float().t() + bias
+        assert (y2.float() - full).abs().max() / full.abs().max() < 8e-2
+    from sneppx_alg_b200 import ops
+    ops.check_status()
