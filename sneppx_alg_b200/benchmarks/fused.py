@@ -115,6 +115,85 @@ def main(argv=None):
     ms_lib = _time(lambda: dist.all_gather_into_tensor(lib_out, shard.tensor, group=group), a.iters, group)
     report("zero_ag", [world * n], ms, ms_lib, 0.0, (world - 1) * n * 2, "pull kernel over peer loads")
 
+
+    # ---- ZeRO reduce-scatter + AdamW in one kernel: every rank holds a full bf16 gradient bucket
+    if world > 1:
+        import ctypes as C
+        from ..ops import _lib
+        from ..parallel.symm import SxZeroArgs
+        nb = (256 * 1024 * 1024) // world // 256 * 256 * world          # bucket elements (512 MiB of bf16)
+        sz = nb // world
+        gbuf = sg.alloc(nb, torch.bfloat16)
+        gbuf.tensor.normal_()
+        p32 = torch.randn(sz, device="cuda")
+        m_, v_ = torch.zeros_like(p32), torch.zeros_like(p32)
+        p16 = torch.empty(sz, **bf)
+        partials = torch.zeros(4096, device="cuda")
+        state = {"e": 0}
+
+        def fused_rs_adamw():
+            state["e"] += 1
+            sg.signal(2, state["e"])
+            za = SxZeroArgs()
+            za.peers = sg.peers(gbuf)
+            za.elem_offset, za.n = rank * sz, sz
+            za.sumsq_partials, za.num_partials = partials.data_ptr(), partials.numel()
+            za.p32, za.m, za.v, za.p16_out = p32.data_ptr(), m_.data_ptr(), v_.data_ptr(), p16.data_ptr()
+            za.lr, za.beta1, za.beta2, za.eps, za.wd, za.step, za.max_norm = 1e-4, 0.9, 0.95, 1e-8, 0.1, 5, 0.0
+            za.ready_channel, za.ready_epoch = 2, state["e"]
+            za.done_channel, za.done_epoch = 3, state["e"]
+            za.mode, za.grid = 3, _lib.lib().sx_zero_grid_default()
+            za.status = _lib.status_word(sg.device).data_ptr()
+            _lib.call("sx_zero_step", C.byref(za), _lib.stream())
+
+        red = torch.empty(sz, **bf)
+        opt_p = torch.nn.Parameter(p32.clone())
+        opt = torch.optim.AdamW([opt_p], lr=1e-4, betas=(0.9, 0.95), weight_decay=0.1, fused=True)
+
+        def lib_rs_adamw():
+            dist.reduce_scatter_tensor(red, gbuf.tensor, group=group)
+            opt_p.grad = red.float() / world
+            opt.step()
+            p16.copy_(opt_p.data)
+
+        ms = _time(fused_rs_adamw, a.iters, group)
+        ms_lib = _time(lib_rs_adamw, a.iters, group)
+        # bytes: every rank reads (world-1) remote shards of bf16 grads; HBM side 28 B per owned parameter
+        report("zero_rs_adamw", [nb], ms, ms_lib, 0.0, (world - 1) * sz * 2,
+               "peer loads of the other ranks' slices, reduce, AdamW, bf16 shadow write in one pass")
+
+    # ---- expert-parallel SER layer (DeepSeek-V2-Lite shape: d 2048, 64 experts of d_ff 1408, top-6, 2 shared)
+    if world > 1 and 64 % world == 0:
+        from ..nn.moe import SERMoE
+        from ..parallel import expert as ep
+        dm, dff, E, k, Tm = 2048, 1408, 64, 6, 8192
+        layer = SERMoE(dm, dff, num_experts=E, top_k=k, num_shared_experts=2, dtype=torch.bfloat16, device="cuda",
+                       ep_group=group, init_std=0.02)
+        with torch.no_grad():
+            dist.broadcast(layer.router.weight, 0)
+            for prm in layer.shared.parameters():
+                dist.broadcast(prm, 0)
+        xm = torch.randn(Tm, dm, **bf)
+        gm = torch.randn(Tm, dm, **bf)
+        orig = ep.ep_experts_forward
+
+        def run(fused):
+            ep.ep_experts_forward = lambda *aa, _f=fused: orig(*aa, fused=_f)
+            import sneppx_alg_b200.nn.moe  # noqa: F401  (the layer resolves the function at call time)
+            xx = xm.detach().requires_grad_(True)
+            y = layer(xx)
+            y.backward(gm)
+            for prm in layer.parameters():
+                prm.grad = None
+
+        ms = _time(lambda: run(True), a.iters, group)
+        ms_lib = _time(lambda: run(False), a.iters, group)
+        ep.ep_experts_forward = orig
+        flops = 3 * 2.0 * Tm * k * 3 * dm * dff + 3 * 2.0 * Tm * 2 * 3 * dm * dff      # routed + shared experts, fwd + bwd
+        link = 2 * 2 * Tm * k * dm * 2 * (world - 1) / world                              # dispatch + combine, fwd + bwd
+        report("ep_moe_fwd_bwd", [Tm, dm, dff, E, k], ms, ms_lib, flops, link,
+               "whole SER layer incl. router and shared experts; library = all_to_all + grouped GEMM")
+
     # ---- small all-reduce
     small = sg.alloc(1024, torch.float32)
     small.tensor.fill_(1.0)
