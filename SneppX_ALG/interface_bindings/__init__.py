@@ -49,6 +49,19 @@ _WHERE = {
     **{n: "serving.generation" for n in ("generate", "greedy_search", "beam_search", "batch_generate")},
     **{n: "serving.serving_engine" for n in ("ServingEngine",)},
     **{n: "serving.server" for n in ("create_app",)},
+    **{n: "training.keras_api" for n in ("UltraTrainer",)},
+    **{n: "serving.middleware" for n in ("SecurityMiddleware",)},
+    **{n: "serving.watermark" for n in ("Watermark",)},
+    **{n: "serving.client" for n in ("ServingClient",)},
+    **{n: "utils.vizmon" for n in ("VizMon",)},
+    **{n: "utils.registry" for n in ("ModelRegistry", "PromptRegistry")},
+    **{n: "security.services" for n in ("KeyVault", "AuditLogger", "DDoSMitigator", "Firewall", "IntegrityMonitor",
+                                        "ApiKeyStore", "UsageTracker")},
+    **{n: "security.ai_filter" for n in ("PromptFilter", "OutputVerifier")},
+    **{n: "hub.hf" for n in ("from_huggingface", "to_huggingface", "pipeline", "load_hf_dataset", "load_hf_model",
+                             "save_hf_model")},
+    **{n: "jit" for n in ("trace", "grad", "vmap", "jacobian", "hessian")},
+    **{n: "tensor" for n in ("Tensor", "Function", "Context", "no_grad")},
     # observability
     **{n: "utils.observability" for n in ("Profiler", "ExperimentTracker", "Logger")},
 }

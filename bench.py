@@ -33,6 +33,9 @@ def parse():
     ap.add_argument("--seq", type=int, default=4096)
     ap.add_argument("--micro-batch", type=int, default=1)
     ap.add_argument("--layers", type=int, default=0, help="debug only: override depth (result is marked invalid)")
+    ap.add_argument("--ep", action="store_true", help="expert parallelism over all ranks (SER MoE models): experts are "
+                    "sharded, the other parameters use ZeRO-1")
+    ap.add_argument("--zero-stage", type=int, default=3)
     return ap.parse_args()
 
 
@@ -128,8 +131,14 @@ def main():
         cfg.num_hidden_layers = cfg.num_layers = args.layers
     cfg.max_position_embeddings = max(args.seq, 8)
     torch.manual_seed(1234)
-    model = build_model(cfg, dtype=torch.bfloat16, device=dev)
-    engine = make_engine(model, zero_stage=3, lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1,
+    if args.ep and world > 1:
+        from sneppx_alg_b200.models.deepseek import DeepSeekV2ForCausalLM
+        model = DeepSeekV2ForCausalLM(cfg, dtype=torch.bfloat16, device=dev, ep_group=dist.group.WORLD)
+        stage = 1
+    else:
+        model = build_model(cfg, dtype=torch.bfloat16, device=dev)
+        stage = args.zero_stage
+    engine = make_engine(model, zero_stage=stage, lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1,
                          max_grad_norm=1.0)
     B, S, V = args.micro_batch, args.seq, cfg.vocab_size
     gen = torch.Generator().manual_seed(100 + rank)
@@ -190,8 +199,10 @@ def main():
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic token ids, random-init weights",
             "impl": "ours",
-            "config": {"model": "llama3-8b-shape" if not args.layers else f"llama3-8b-shape-{args.layers}L(debug, invalid)",
-                       "global_batch": B * world, "seq_len": S, "parallelism": f"zero3-dp{world}",
+            "config": {"model": (f"{cfg.name}-shape" if not args.layers else f"{cfg.name}-shape-{args.layers}L(debug, invalid)")
+                       .replace("llama3-8B", "llama3-8b"),
+                       "global_batch": B * world, "seq_len": S,
+                       "parallelism": (f"ep{world}+zero1" if (args.ep and world > 1) else f"zero{stage}-dp{world}"),
                        "optimizer": "AdamW b=(0.9,0.95) wd=0.1 fp32 master+moments",
                        "l2": "per-step working set (>= 16 GB of weights) far exceeds the 126 MB L2"},
             "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,

@@ -39,8 +39,11 @@ struct F8Cfg {
   static constexpr int W_BYTES = 128 * F8_BK;
   static constexpr int X_BYTES = BT * F8_BK;
   static constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
-  static constexpr int STAGES = (200 * 1024) / STAGE_BYTES > 8 ? 8 : (200 * 1024) / STAGE_BYTES;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+  static constexpr int SCALE_FLOATS = 16384;             // activation scales of the CTA's (k range, token tile), 64 KB
+  static constexpr int STAGES = (150 * 1024) / STAGE_BYTES > 8 ? 8 : (150 * 1024) / STAGE_BYTES;
+  static constexpr int OFF_SCALE = STAGES * STAGE_BYTES;
+  static constexpr int OFF_BAR = OFF_SCALE + SCALE_FLOATS * 4;
+  static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;
 };
 
 template <int BT>
@@ -48,7 +51,8 @@ __global__ void __launch_bounds__(F8_THREADS, 1) gemm_f8_kernel(const __grid_con
   using Cfg = F8Cfg<BT>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::STAGES * Cfg::STAGE_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
+  float* s_sx = reinterpret_cast<float*>(smem + Cfg::OFF_SCALE);   // [k-block of this CTA][token of the tile]
   uint64_t* full_bar = bars;                    // [STAGES]
   uint64_t* empty_bar = bars + Cfg::STAGES;     // [STAGES]
   uint64_t* tfull = bars + 2 * Cfg::STAGES;     // [2]
@@ -126,21 +130,45 @@ __global__ void __launch_bounds__(F8_THREADS, 1) gemm_f8_kernel(const __grid_con
     for (int j = 0; j < BT; ++j) acc[j] = 0.f;
     bool ok = true;
     const int tok0 = tb * BT;
+    // Stage the activation scales of this CTA's k range, transposed to [k-block][token], so that a k-block's BT
+    // scales are one contiguous run read with 16-byte shared loads (identical for every lane: broadcast).
+    const bool staged = nkb * BT <= Cfg::SCALE_FLOATS;
+    if (staged) {
+      const int t4 = threadIdx.x - 64;   // 0..127 over the four promotion warps
+      for (int e = t4; e < nkb * BT; e += 128) {
+        const int j = e % BT, i = e / BT;     // consecutive threads write consecutive shared-memory words
+        const int tok = tok0 + j;
+        s_sx[i * BT + j] = tok < p.M ? p.sx[(long long)tok * p.kblks + kb0 + i] : 0.f;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");   // the four promotion warps only; no wait can abort before this point
+    }
     for (int i = 0; i < nkb && ok; ++i) {
       const int buf = i & 1, kb = kb0 + i;
       const float swv = p.sw[(long long)nb * p.kblks + kb];
       if (!mbar_wait_warp(&tfull[buf], (i >> 1) & 1, s_abort, p.status, ST_TIMEOUT_EPILOGUE)) { ok = false; break; }
       tc_fence_after();
 #pragma unroll
-      for (int c = 0; c < BT / 16; ++c) {
-        uint32_t v[16];
-        tmem_ld16(tmem_base + buf * BT + c * 16 + lane_addr, v);
+      for (int c = 0; c < BT / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld32(tmem_base + buf * BT + c * 32 + lane_addr, v);
         tmem_ld_wait();
+        if (staged) {
+          const float4* sp4 = reinterpret_cast<const float4*>(s_sx + i * BT + c * 32);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const int tok = tok0 + c * 16 + j;
-          const float sxv = tok < p.M ? __ldg(p.sx + (long long)tok * p.kblks + kb) : 0.f;   // warp-uniform address
-          acc[c * 16 + j] = fmaf(__uint_as_float(v[j]), swv * sxv, acc[c * 16 + j]);
+          for (int j = 0; j < 32; j += 4) {
+            const float4 s4 = sp4[j >> 2];
+            acc[c * 32 + j] = fmaf(__uint_as_float(v[j]), swv * s4.x, acc[c * 32 + j]);
+            acc[c * 32 + j + 1] = fmaf(__uint_as_float(v[j + 1]), swv * s4.y, acc[c * 32 + j + 1]);
+            acc[c * 32 + j + 2] = fmaf(__uint_as_float(v[j + 2]), swv * s4.z, acc[c * 32 + j + 2]);
+            acc[c * 32 + j + 3] = fmaf(__uint_as_float(v[j + 3]), swv * s4.w, acc[c * 32 + j + 3]);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int tok = tok0 + c * 32 + j;
+            const float sxv = tok < p.M ? __ldg(p.sx + (long long)tok * p.kblks + kb) : 0.f;   // warp-uniform address
+            acc[c * 32 + j] = fmaf(__uint_as_float(v[j]), swv * sxv, acc[c * 32 + j]);
+          }
         }
       }
       tc_fence_before();

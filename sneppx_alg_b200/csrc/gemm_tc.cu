@@ -930,11 +930,14 @@ static int gemm_launch(const SxGemmArgs* a, const SxGemmCommArgs* cm, cudaStream
     int dev2 = 0, sms2 = 148;
     cudaGetDevice(&dev2);
     cudaDeviceGetAttribute(&sms2, cudaDevAttrMultiProcessorCount, dev2);
-    // Tile width: 256 unless the narrower tile wastes less of the last wave (a 256 x 128 tile costs ~0.53 of a 256 x 256 one).
-    const long long mp = (a->M + 255) / 256, pairs = sms2 / 2;
-    const long long t256 = (long long)a->batch * mp * ((a->N + 255) / 256), t128 = (long long)a->batch * mp * ((a->N + 127) / 128);
-    const double c256 = (double)((t256 + pairs - 1) / pairs), c128 = 0.53 * (double)((t128 + pairs - 1) / pairs);
-    const int bn2 = (a->force_bn == 0 && c128 < c256) ? 128 : 256;
+    // Tile width: 256. The 256 x 128 pair tile measured 0.75 of a 256 x 256 tile's time (not the ~0.53 that would make
+    // it pay off against wave quantisation), so it is only taken on request (force_bn == 128 through SX_GEMM_PAIR_BN).
+    static int pair_bn = 0;
+    if (pair_bn == 0) {
+      const char* e = getenv("SX_GEMM_PAIR_BN");
+      pair_bn = (e && atoi(e) == 128) ? 128 : 256;
+    }
+    const int bn2 = pair_bn;
     int rc2 = make_operand_map(&kp.tmA, a->A, a->M, a->K, a->lda, a_batched, a->batch, a->strideA, a->a_mn != 0, 128);
     if (rc2) return rc2;
     rc2 = make_operand_map(&kp.tmB, a->B, a->N, a->K, a->ldb, bb2, a->batch, a->strideB, a->b_mn != 0, bn2 / 2);

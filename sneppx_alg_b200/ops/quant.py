@@ -138,7 +138,7 @@ def gemm_fp8(x, wq, sw, bias=None, xq=None, sx=None):
     if xq is None:
         xq, sx = quant_fp8_1x128(x.reshape(-1, K))
     M, N = xq.shape[0], wq.shape[0]
-    if xq.is_cuda and _lib.available() and K % 128 == 0:
+    if xq.is_cuda and _lib.available() and K % 128 == 0 and M <= 256:
         xq_, wq_ = xq.view(torch.uint8).contiguous(), wq.view(torch.uint8).contiguous()
         out = torch.empty(M, N, dtype=torch.bfloat16, device=xq.device)
         fn = _lib.lib().sx_gemm_fp8_workspace
@@ -150,6 +150,10 @@ def gemm_fp8(x, wq, sw, bias=None, xq=None, sx=None):
                   ptr(sw.contiguous()), ptr(b), ptr(out), c_ll(out.stride(0)), ptr(work), c_int(M), c_int(N), c_int(K),
                   ptr(_lib.status_word(xq.device)), stream())
         return out.view(*lead, N)
+    if xq.is_cuda and _lib.available() and K % 128 == 0:
+        # large M: the swap-AB kernel would re-read the weights per 128-token tile; expand the weights inside the bf16 GEMM
+        xb = dequant_fp8(xq, sx, "1x128", torch.bfloat16)
+        return gemm_dequant(xb, wq, sw, "fp8", bias).view(*lead, N)
     return gemm_fp8_reference(xq, sx, wq, sw, bias).view(*lead, N)
 
 

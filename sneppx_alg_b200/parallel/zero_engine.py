@@ -56,7 +56,10 @@ class ZeroEngine:
         self.stage = zero_stage
         self.lr, self.betas, self.eps, self.wd, self.max_grad_norm = lr, betas, eps, weight_decay, max_grad_norm
         self.step_count = 0
-        params = _unique_params(model)
+        # Expert weights of an expert-parallel model (``is_expert``) differ between ranks: they are not reduced or
+        # partitioned over the data-parallel group; this rank keeps their full optimizer state and updates them locally.
+        self.expert_params = [p for p in _unique_params(model) if getattr(p, "is_expert", False)]
+        params = [p for p in _unique_params(model) if not getattr(p, "is_expert", False)]
         dev = params[0].device
         self.device = dev
         self.fused = (dev.type == "cuda" and params[0].dtype == torch.bfloat16) if fused is None else fused
@@ -67,7 +70,7 @@ class ZeroEngine:
         self.bucket_modules = []
         if layers is not None:
             for layer in layers:
-                ps = [p for p in _unique_params(layer) if id(p) not in taken]
+                ps = [p for p in _unique_params(layer) if id(p) not in taken and not getattr(p, "is_expert", False)]
                 if ps:
                     taken.update(id(p) for p in ps)
                     bucket_params.append(ps)
@@ -96,6 +99,11 @@ class ZeroEngine:
                     return b.tensor
                 return torch.zeros(n, dtype=dt, device=dev)
         self.fp = FlatParams(model, params=ordered, align=64, shard_multiple=self.world, alloc=alloc)
+        self.efp = None
+        if self.expert_params:
+            self.efp = FlatParams(model, params=self.expert_params, align=64)
+            self.e_master = self.efp.flat.float()
+            self.e_m, self.e_v = torch.zeros_like(self.e_master), torch.zeros_like(self.e_master)
         if self.world > 1:
             dist.broadcast(self.fp.flat, src=dist.get_global_rank(self.group, 0), group=self.group)
         # bucket extents in the flat buffer (each a multiple of 64 * world elements)
@@ -131,7 +139,8 @@ class ZeroEngine:
             self.pshard.tensor.copy_(self.master)
             self.reduced = torch.empty(self.shard_total, dtype=torch.float32, device=dev)
             self.grid = comm_grid or 2 * torch.cuda.get_device_properties(dev).multi_processor_count
-            self.partials = torch.zeros(len(self.bounds) * self.grid, dtype=torch.float32, device=dev)
+            # one extra slot after the per-bucket partials carries the sum of squares of the local expert gradients
+            self.partials = torch.zeros(len(self.bounds) * self.grid + 1, dtype=torch.float32, device=dev)
             self.norm_out = torch.zeros(4, dtype=torch.float32, device=dev)
             self.comm_stream = torch.cuda.Stream(device=dev)
             self.gather_events = [None] * len(self.bounds)
@@ -240,6 +249,8 @@ class ZeroEngine:
     def _step_fused(self, input_ids, labels, **kw):
         self.step_count += 1
         self.fp.begin_step()
+        if self.efp is not None:
+            self.efp.begin_step()
         self._pending = set(range(len(self.bounds)))
         out = self.model(input_ids, labels=labels, **kw)
         loss = out["loss"] if isinstance(out, dict) else out
@@ -249,6 +260,13 @@ class ZeroEngine:
             self._launch_reduce(bi)
         self._pending = set()
         cs = self.comm_stream
+        if self.efp is not None:
+            self.efp.finalize_grads()
+            esq, _ = grad_norm_([self.efp.grad])
+            self.partials[-1:].copy_(esq[0:1])
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream())
+            cs.wait_event(ev)
         sptr = C.c_void_p(cs.cuda_stream)
         a = self._zero_args()
         a.peers = self.sg.peers(self._symm["grad"])
@@ -262,16 +280,32 @@ class ZeroEngine:
         a.mode = 2
         _lib.call("sx_zero_step", C.byref(a), sptr)
         self.last_norm = self.norm_out
+        if self.efp is not None:
+            with torch.cuda.stream(cs):   # after the kernel above has produced the clip coefficient
+                self._expert_update(self.norm_out[2:3])
+            done = torch.cuda.Event()
+            done.record(cs)
+            torch.cuda.current_stream().wait_event(done)
         self._prefetch_params()
         return loss.detach()
+
+    def _expert_update(self, coef):
+        p16 = self.efp.flat if self.efp.flat.dtype != torch.float32 else None
+        target = self.e_master if p16 is not None else self.efp.flat
+        adamw_flat_(target, self.e_m, self.e_v, self.efp.grad, p16, self.lr, self.betas[0], self.betas[1], self.eps,
+                    self.wd, self.step_count, 1.0, coef)
 
     def _step_library(self, input_ids, labels, **kw):
         self.step_count += 1
         self.fp.begin_step()
+        if self.efp is not None:
+            self.efp.begin_step()
         out = self.model(input_ids, labels=labels, **kw)
         loss = out["loss"] if isinstance(out, dict) else out
         loss.backward()
         self.fp.finalize_grads()
+        if self.efp is not None:
+            self.efp.finalize_grads()
         w, r = self.world, self.rank
         for bi, (b0, b1) in enumerate(self.bounds):
             sz = (b1 - b0) // w
@@ -287,6 +321,8 @@ class ZeroEngine:
                 dst.copy_(gf[r * sz: (r + 1) * sz])
             dst.div_(w)
         ss = self.reduced.pow(2).sum().reshape(1)
+        if self.efp is not None:
+            ss = ss + self.efp.grad.float().pow(2).sum().reshape(1)
         dist.all_reduce(ss, group=self.group)
         nrm = ss.sqrt()
         coef = torch.where((nrm > self.max_grad_norm) & (self.max_grad_norm > 0), self.max_grad_norm / (nrm + 1e-6),
@@ -295,6 +331,8 @@ class ZeroEngine:
         p16 = self.pshard_local if self.fp.dtype != torch.float32 else None
         adamw_flat_(self.master, self.m, self.v, self.reduced, p16, self.lr, self.betas[0], self.betas[1], self.eps,
                     self.wd, self.step_count, 1.0, coef)
+        if self.efp is not None:
+            self._expert_update(coef)
         src = self.pshard_local if p16 is not None else self.master
         if p16 is None:
             self.pshard_local.copy_(self.master)
@@ -307,8 +345,11 @@ class ZeroEngine:
 
     # ------------------------------------------------------------------ sharded state for checkpoints
     def state_dict(self):
-        return {"step": self.step_count, "master": self.master, "m": self.m, "v": self.v, "rank": self.rank,
-                "world": self.world, "bounds": self.bounds}
+        sd = {"step": self.step_count, "master": self.master, "m": self.m, "v": self.v, "rank": self.rank,
+              "world": self.world, "bounds": self.bounds}
+        if self.efp is not None:
+            sd.update(e_master=self.e_master, e_m=self.e_m, e_v=self.e_v)
+        return sd
 
     def load_state_dict(self, sd):
         assert sd["world"] == self.world, "use checkpoint.reshard to change the world size"
@@ -316,3 +357,8 @@ class ZeroEngine:
         self.master.copy_(sd["master"])
         self.m.copy_(sd["m"])
         self.v.copy_(sd["v"])
+        if self.efp is not None and "e_master" in sd:
+            self.e_master.copy_(sd["e_master"])
+            self.e_m.copy_(sd["e_m"])
+            self.e_v.copy_(sd["e_v"])
+            self.efp.flat.copy_(self.e_master)
