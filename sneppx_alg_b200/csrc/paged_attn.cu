@@ -11,6 +11,8 @@ namespace sx {
 
 constexpr int PA_TILE = 128;   // threads per CTA
 constexpr int PA_MAX_G = 8;    // query heads per KV head
+constexpr int PA_NST = 8;      // cp.async ring depth per lane
+constexpr int PA_TBL = 1024;   // block-table entries staged per CTA
 
 // One CTA: (sequence b, KV head hk, split). A K/V row (D bf16) is read by D/8 adjacent lanes with one 16-byte load
 // each, so a warp reads 2 (D=128) or 4 (D=64) whole rows per load instruction, fully coalesced; the lanes of a row
@@ -26,13 +28,18 @@ __global__ void __launch_bounds__(PA_TILE) paged_decode_kernel(
   constexpr int LPR = D / 8;            // lanes per row
   constexpr int RPW = 32 / LPR;         // rows per warp-wide load
   constexpr int NGRP = (PA_TILE / 32) * RPW;
-  constexpr int U = 4;                  // rows in flight per lane group
   const int b = blockIdx.x, hk = blockIdx.y, split = blockIdx.z;
   const int G = Hq / Hkv;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int sub = lane % LPR, grp = warp * RPW + lane / LPR;
-  __shared__ float s_m[NGRP][GT], s_l[NGRP][GT];
-  __shared__ float s_acc[NGRP][GT][D];
+  // one shared buffer: the cp.async ring while streaming, the per-group partial results for the final merge
+  constexpr int RING_BYTES = PA_NST * 2 * PA_TILE * 16;
+  constexpr int MERGE_BYTES = NGRP * GT * (D + 2) * 4;
+  __shared__ __align__(16) uint8_t s_raw[RING_BYTES > MERGE_BYTES ? RING_BYTES : MERGE_BYTES];
+  uint4 (*s_ring)[2][PA_TILE] = reinterpret_cast<uint4 (*)[2][PA_TILE]>(s_raw);
+  float (*s_acc)[GT][D] = reinterpret_cast<float (*)[GT][D]>(s_raw);
+  float (*s_m)[GT] = reinterpret_cast<float (*)[GT]>(s_raw + NGRP * GT * D * 4);
+  float (*s_l)[GT] = reinterpret_cast<float (*)[GT]>(s_raw + NGRP * GT * D * 4 + NGRP * GT * 4);
   const int len = seq_lens[b];
   const int per = (len + nsplit - 1) / nsplit;
   const int p0 = split * per, p1 = min(len, p0 + per);
@@ -52,52 +59,72 @@ __global__ void __launch_bounds__(PA_TILE) paged_decode_kernel(
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[g][j] = 0.f;
   }
+  // Block-table entries of this CTA's position range, staged once (a lookup on the load path costs a shared-memory
+  // read instead of a dependent global load).
+  __shared__ int s_tbl[PA_TBL];
   const int* tbl = block_table + (long long)b * max_blocks;
-  for (int base = p0; base < p1; base += NGRP * U) {   // uniform trip count for the whole CTA
-    bf16x8 kraw[U], vraw[U];
-    bool valid[U];
+  const int blk0 = p0 / block_size;
+  const int nblk = p1 > p0 ? (p1 - 1) / block_size - blk0 + 1 : 0;
+  const bool tbl_staged = nblk <= PA_TBL;
+  if (tbl_staged)
+    for (int i = tid; i < nblk; i += PA_TILE) s_tbl[i] = tbl[blk0 + i];
+  __syncthreads();
+  // Per-lane ring of 16-byte K and V pieces filled by cp.async: PA_NST - 1 rows per lane group are in flight while one
+  // is consumed, without holding registers for them. A lane reads back exactly the bytes it copied, so the only
+  // synchronisation is its own cp.async.wait_group.
+  const int n_it = p1 > p0 ? (p1 - p0 + NGRP - 1) / NGRP : 0;   // uniform for the whole CTA
+  auto issue = [&](int i) {
+    const int pos = p0 + i * NGRP + grp;
+    if (i < n_it && pos < p1) {
+      const int blk = tbl_staged ? s_tbl[pos / block_size - blk0] : tbl[pos / block_size];
+      const long long row = (((long long)blk * block_size + pos % block_size) * Hkv + hk) * D + sub * 8;
+      const uint32_t dk = (uint32_t)__cvta_generic_to_shared(&s_ring[i % PA_NST][0][tid]);
+      const uint32_t dv = (uint32_t)__cvta_generic_to_shared(&s_ring[i % PA_NST][1][tid]);
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dk), "l"(k_cache + row) : "memory");
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dv), "l"(v_cache + row) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int pos = base + u * NGRP + grp;
-      valid[u] = pos < p1;
-      if (valid[u]) {
-        const int blk = tbl[pos / block_size];
-        const long long row = (((long long)blk * block_size + pos % block_size) * Hkv + hk) * D + sub * 8;
-        kraw[u] = ld8(k_cache + row);
-        vraw[u] = ld8(v_cache + row);
-      }
+  for (int i = 0; i < PA_NST - 1; ++i) issue(i);
+  for (int i = 0; i < n_it; ++i) {
+    issue(i + PA_NST - 1);
+    asm volatile("cp.async.wait_group %0;" ::"n"(PA_NST - 1) : "memory");
+    const int pos = p0 + i * NGRP + grp;
+    const bool valid = pos < p1;
+    float kv[8], vv[8];
+    if (valid) {
+      const uint4 kq = s_ring[i % PA_NST][0][tid], vq = s_ring[i % PA_NST][1][tid];
+      unpack8(*reinterpret_cast<const bf16x8*>(&kq), kv);
+      unpack8(*reinterpret_cast<const bf16x8*>(&vq), vv);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { kv[j] = 0.f; vv[j] = 0.f; }
     }
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      float kv[8], vv[8];
-      if (valid[u]) { unpack8(kraw[u], kv); unpack8(vraw[u], vv); }
-      else {
+    for (int g = 0; g < GT; ++g) {
+      float sc = 0.f;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) { kv[j] = 0.f; vv[j] = 0.f; }
-      }
+      for (int j = 0; j < 8; ++j) sc = fmaf(kv[j], qr[g][j], sc);
 #pragma unroll
-      for (int g = 0; g < GT; ++g) {
-        float sc = 0.f;
+      for (int o = LPR / 2; o > 0; o >>= 1) sc += __shfl_xor_sync(0xffffffffu, sc, o);
+      if (valid) {
+        if (sc > m[g]) {
+          const float alpha = __expf(m[g] - sc);   // exp(-inf) = 0 on the first row
+          l[g] *= alpha;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) sc = fmaf(kv[j], qr[g][j], sc);
-#pragma unroll
-        for (int o = LPR / 2; o > 0; o >>= 1) sc += __shfl_xor_sync(0xffffffffu, sc, o);
-        if (valid[u]) {
-          if (sc > m[g]) {
-            const float alpha = __expf(m[g] - sc);   // exp(-inf) = 0 on the first row
-            l[g] *= alpha;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) acc[g][j] *= alpha;
-            m[g] = sc;
-          }
-          const float pr = __expf(sc - m[g]);
-          l[g] += pr;
-#pragma unroll
-          for (int j = 0; j < 8; ++j) acc[g][j] = fmaf(pr, vv[j], acc[g][j]);
+          for (int j = 0; j < 8; ++j) acc[g][j] *= alpha;
+          m[g] = sc;
         }
+        const float pr = __expf(sc - m[g]);
+        l[g] += pr;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[g][j] = fmaf(pr, vv[j], acc[g][j]);
       }
     }
   }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncthreads();   // the ring is dead from here on: its storage holds the merge buffers
   // merge the lane groups
 #pragma unroll
   for (int g = 0; g < GT; ++g) {
