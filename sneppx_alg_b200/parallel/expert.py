@@ -95,7 +95,7 @@ def _dispatch_gemm(ws, plan, x, w, rows_buf, arrive, expected, scale, b_mn):
     cm.peers = ws.sg.peers(rows_buf)
     cm.mode = 4
     cm.epoch = ws.sg.next_epoch(CH_DISP_SIG)
-    cm.n_copy = 16
+    cm.n_copy = 32
     cm.sig_channel, cm.done_channel = CH_DISP_SIG, CH_DISP_DONE
     cm.cta_counter = ws.cta_counter.data_ptr()
     cm.ep_x = x.data_ptr()
