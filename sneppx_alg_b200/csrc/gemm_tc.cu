@@ -86,14 +86,19 @@ struct GemmKernelParams {
   CommParams cm;
 };
 
-template <int BN>
+template <int BN, int COMM = 0>
 struct GemmCfg {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (BN == 256) ? 4 : (BN == 128 ? 6 : 8);
+  // GEMM -> reduce-scatter stages its bf16 output tile in shared memory (BM x BN x 2 bytes) so that rows leave for
+  // the owner's staging buffer as whole 2*BN-byte runs; it pays for that with one pipeline stage.
+  static constexpr int OUT_BYTES = COMM == 2 ? BM * BN * 2 : 0;
+  static constexpr int STAGES = (BN == 256) ? (COMM == 2 ? 3 : 4) : (BN == 128 ? (COMM == 2 ? 5 : 6) : 8);
   static constexpr int TMEM_COLS = 2 * BN;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align slack*/ + 256 /*barriers*/;
+  static constexpr int OFF_OUT = STAGES * STAGE_BYTES;
+  static constexpr int OFF_BAR = OFF_OUT + OUT_BYTES;
+  static constexpr int SMEM_BYTES = OFF_BAR + 1024 /*align slack*/ + 256 /*barriers*/;
 };
 
 __device__ __forceinline__ void tile_coords(int t, int m_blks, int n_blks, int& b, int& m_blk, int& n_blk) {
@@ -112,10 +117,10 @@ __device__ __forceinline__ void tile_coords(int t, int m_blks, int n_blks, int& 
 
 template <int BN, bool A_MN, bool B_MN, int COMM>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_constant__ GemmKernelParams p) {
-  using Cfg = GemmCfg<BN>;
+  using Cfg = GemmCfg<BN, COMM>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::STAGES * Cfg::STAGE_BYTES);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
   uint64_t* full_bar = bars;                      // [STAGES]
   uint64_t* empty_bar = bars + Cfg::STAGES;       // [STAGES]
   uint64_t* tfull_bar = bars + 2 * Cfg::STAGES;   // [2]
@@ -505,7 +510,21 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
         }
-        if (p.out_fp32) {
+        if (COMM == 2) {
+          // this lane's 64 bytes of the row go to the warp's slab: 16-byte chunk index XOR row keeps both the writes
+          // here (same chunk index, 32 rows) and the row-wise reads below free of bank conflicts
+          uint8_t* slab = smem + Cfg::OFF_OUT + q * (32 * BN * 2) + lane * (BN * 2);
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint4 o;
+            o.x = pack_bf16x2(v[j], v[j + 1]);
+            o.y = pack_bf16x2(v[j + 2], v[j + 3]);
+            o.z = pack_bf16x2(v[j + 4], v[j + 5]);
+            o.w = pack_bf16x2(v[j + 6], v[j + 7]);
+            const int ci = c * 4 + (j >> 3);
+            *reinterpret_cast<uint4*>(slab + (((ci ^ lane) & (BN / 8 - 1)) << 4)) = o;
+          }
+        } else if (p.out_fp32) {
           float* dp = reinterpret_cast<float*>(Dptr) + drow + col0;
           if (full && ((reinterpret_cast<uintptr_t>(dp) & 15) == 0)) {
 #pragma unroll
@@ -534,7 +553,29 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
         }
       }
       tc_fence_before();
-      if (COMM == 2) __threadfence_system();   // partial tile visible to its owner before the count moves
+      if (COMM == 2) {
+        // write the slab out row by row: lane l carries 16-byte chunk l (and l + 32 for BN = 256) of the row, so each
+        // store instruction is one contiguous 512-byte run of the owner's staging buffer
+        __syncwarp();
+        const uint8_t* slab0 = smem + Cfg::OFF_OUT + q * (32 * BN * 2);
+        const int row_base = m_blk * BM + q * 32;
+        for (int rr = 0; rr < 32; ++rr) {
+          const int grow = row_base + rr;
+          if (grow >= p.M) break;
+          __nv_bfloat16* drp = reinterpret_cast<__nv_bfloat16*>(Dptr) +
+                               ((long long)p.cm.pt.rank * p.cm.chunk_rows + (grow - rs_owner * p.cm.chunk_rows)) * (long long)p.N +
+                               n_blk * BN;
+#pragma unroll
+          for (int h = 0; h < BN / 256 + (BN % 256 ? 1 : 0); ++h) {
+            const int ci = lane + h * 32;
+            if (ci < BN / 8 && n_blk * BN + ci * 8 < p.N) {
+              const uint4 o = *reinterpret_cast<const uint4*>(slab0 + rr * (BN * 2) + (((ci ^ rr) & (BN / 8 - 1)) << 4));
+              st_peer_v4(drp + ci * 8, o);
+            }
+          }
+        }
+        __threadfence_system();   // partial tile visible to its owner before the count moves
+      }
       __syncwarp();
       if (lane == 0) {
         mbar_arrive(&tempty_bar[acc]);
@@ -610,7 +651,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
 
 template <int BN, bool A_MN, bool B_MN, int COMM = 0>
 static int launch_cfg(const GemmKernelParams& kp, int grid, cudaStream_t st) {
-  using Cfg = GemmCfg<BN>;
+  using Cfg = GemmCfg<BN, COMM>;
   static bool attr_set = false;
   auto kern = gemm_tc_kernel<BN, A_MN, B_MN, COMM>;
   if (!attr_set) {

@@ -52,10 +52,12 @@ class FusedTP:
     """Per-group workspace for the fused TP kernels: symmetric gather / staging buffers keyed by shape, flag arrays,
     epochs and reduce-scatter counter sites."""
 
-    def __init__(self, sg, n_copy=8):
+    def __init__(self, sg, n_copy=None):
         self.sg = sg
         self.rank, self.world = sg.rank, sg.world
-        self.n_copy = n_copy
+        # copy CTAs of the all-gather form: one remote chunk at a time is pulled by all of them; with more than two
+        # ranks most of the operand is remote and the pull, not the GEMM, sets the pace
+        self.n_copy = n_copy if n_copy is not None else (8 if sg.world <= 2 else 16)
         self._gather = {}
         self._stage = {}
         self._rs_sites = {}
