@@ -258,7 +258,7 @@ __global__ void moe_gather_bwd_kernel(const __nv_bfloat16* __restrict__ dxs, con
 }  // namespace sx
 using namespace sx;
 
-extern "C" int sx_router_parts(void) { return 148; }
+extern "C" int sx_router_parts(void) { return 148 * 6; }  // CTAs (and partial-sum rows): enough warps in flight to hide the per-token latency chain
 
 // counts must be zeroed by the caller. psum_partial: [sx_router_parts() * E], zsum_partial: [sx_router_parts()].
 extern "C" int sx_router_topk(const float* logits, float* probs, int* topk_idx, float* topk_w, int* counts,

@@ -191,6 +191,40 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, const float* __restri
   }
 }
 
+// Rotate-half layout, 8 rotation pairs per thread: two 16-byte loads of x (the halves), 2 x 32 bytes of cos / sin.
+__global__ void rope_vec8_kernel(__nv_bfloat16* __restrict__ x, const float* __restrict__ cos_t,
+                                 const float* __restrict__ sin_t, const int* __restrict__ pos, long long tokens,
+                                 int seq, int heads, int D, long long row_stride, float sign) {
+  const int half = D >> 1, hv = half >> 3;
+  const long long total = tokens * heads * hv;
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const int i = (int)(idx % hv) * 8;
+    const long long th = idx / hv;
+    const int hd = (int)(th % heads);
+    const long long t = th / heads;
+    const int p = pos ? pos[t] : (int)(t % seq);
+    const float4* cp = reinterpret_cast<const float4*>(cos_t + (long long)p * half + i);
+    const float4* sp = reinterpret_cast<const float4*>(sin_t + (long long)p * half + i);
+    const float4 c0 = cp[0], c1 = cp[1], s0 = sp[0], s1 = sp[1];
+    const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+    __nv_bfloat16* base = x + t * row_stride + (long long)hd * D + i;
+    float a[8], b[8];
+    unpack8(ld8(base), a);
+    unpack8(ld8(base + half), b);
+    float ra[8], rb[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float s = sn[j] * sign;
+      ra[j] = a[j] * c[j] - b[j] * s;
+      rb[j] = b[j] * c[j] + a[j] * s;
+    }
+    st8(base, pack8(ra));
+    st8(base + half, pack8(rb));
+  }
+}
+
 // h = act(gate) * up ; gu = [T, 2F] (gate | up). act: 0 silu (SwiGLU), 1 gelu (GeGLU), 2 relu (ReGLU)
 __device__ __forceinline__ float gate_act(float g, int act) {
   if (act == 0) return g / (1.f + __expf(-g));
@@ -303,6 +337,14 @@ extern "C" int sx_layernorm_fwd(const void* x, const void* w, const void* b, voi
 extern "C" int sx_rope(void* x, const float* cos_t, const float* sin_t, const int* pos, long long tokens, int seq,
                        int heads, int D, long long row_stride, int interleaved, int backward, cudaStream_t st) {
   if (tokens == 0) return 0;
+  if (!interleaved && (D / 2) % 8 == 0 && row_stride % 8 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(cos_t) & 15) == 0 && (reinterpret_cast<uintptr_t>(sin_t) & 15) == 0) {
+    const long long tv = tokens * heads * (D / 16);
+    const int bv = (int)((tv + 255) / 256 < 148 * 16 ? (tv + 255) / 256 : 148 * 16);
+    rope_vec8_kernel<<<bv, 256, 0, st>>>((__nv_bfloat16*)x, cos_t, sin_t, pos, tokens, seq, heads, D, row_stride,
+                                         backward ? -1.f : 1.f);
+    return cudaGetLastError() == cudaSuccess ? 0 : -11;
+  }
   const long long total = tokens * heads * (D / 2);
   const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
   rope_kernel<<<blocks, 256, 0, st>>>((__nv_bfloat16*)x, cos_t, sin_t, pos, tokens, seq, heads, D, row_stride,
