@@ -183,9 +183,13 @@ class QuantizedLinear(torch.nn.Module):
     """Weight-only quantised linear layer (fp8 e4m3 128x128-block scales, or INT4 group 128); the reference's
     ``QuantizedLinear`` (interface_bindings/quantization.py) dequantises in NumPy before a dense matmul."""
 
-    def __init__(self, weight, mode="fp8", bias=None):
+    def __init__(self, weight, mode="fp8", bias=None, fp8_activations=True):
         super().__init__()
         self.mode = mode
+        # fp8 mode, up to 256 rows (decode and small prefill chunks): quantise the activations per 1 x 128 block and run
+        # the fp8 x fp8 tensor-core GEMM, which streams the weights once; larger inputs expand the weights to bf16 inside
+        # the GEMM (weight-only).
+        self.fp8_activations = fp8_activations
         self.out_features, self.in_features = weight.shape
         w = weight.detach().to(torch.bfloat16)
         if mode == "fp8":
@@ -202,6 +206,9 @@ class QuantizedLinear(torch.nn.Module):
         return cls(lin.weight, mode, getattr(lin, "bias", None))
 
     def forward(self, x):
+        if self.mode == "fp8" and self.fp8_activations and x.is_cuda and x.dtype == torch.bfloat16 \
+                and x.numel() // x.shape[-1] <= 256 and _lib.available():
+            return gemm_fp8(x, self.qweight, self.scales, self.bias)
         return gemm_dequant(x, self.qweight, self.scales, self.mode, self.bias)
 
 
