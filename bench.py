@@ -91,7 +91,7 @@ def run_reference(args):
     ref_dir = os.path.join(REPO, "baseline", "_ref")
     why = None
     if not os.path.isdir(os.path.join(ref_dir, "SneppX_ALG")):
-        why = "reference not installed under baseline/_ref (pip install of /root/reference not done on this box)"
+        why = "reference not installed under baseline/_ref (offline pip install of the reference source tree not done on this box)"
     else:
         sys.path.insert(0, ref_dir)
         try:

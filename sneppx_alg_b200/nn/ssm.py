@@ -66,7 +66,8 @@ class Mamba2Block(Module):
         A = -torch.exp(self.A_log)
         init = state["ssm"] if state is not None and state.get("ssm") is not None else None
         out = ssm.ssd_scan(x.reshape(B, L, H, P), dt, A, Bm.reshape(B, L, G, N), Cm.reshape(B, L, G, N), self.D,
-                           chunk=min(self.chunk, max(L, 1)) if L < self.chunk else self.chunk, init_state=init,
+                           chunk=min(self.chunk, 128), init_state=init,   # result is independent of the tiling; 128 = one MMA tile
+                          
                            return_state=state is not None)
         if state is not None:
             y, state["ssm"] = out

@@ -16,7 +16,7 @@ import torch.nn.functional as F
 
 from . import _lib
 from ._lib import c_int, c_ll, ptr, stream
-from .gemm import bmm
+from .gemm import bmm, gemm
 
 
 # ----------------------------------------------------------------------------- conv1d (C1)
@@ -144,8 +144,243 @@ def ssd_chunked(x, dt, A, Bm, Cm, D=None, chunk=64, init_state=None, return_stat
     return (y, h) if return_state else y
 
 
+# ---- building blocks of the chunked scan; each has a CUDA kernel and the plain PyTorch statement below it
+def _mask(Q, dev):
+    return torch.ones(Q, Q, dtype=torch.bool, device=dev).tril()
+
+
+def _build_m(CB, csh, dth, rep, cdt):
+    """M[l,s] = CB[l,s] exp(cs_l - cs_s) dt_s for s <= l (else 0). CB [B,nc,G,Q,Q] fp32; csh, dth [B,nc,H,Q] fp32."""
+    Bsz, nc, G, Q, _ = CB.shape
+    H = csh.shape[2]
+    if CB.is_cuda and cdt == torch.bfloat16 and _lib.available():
+        M = torch.empty(Bsz, nc, H, Q, Q, dtype=cdt, device=CB.device)
+        _lib.call("sx_ssd_build_m", ptr(CB), ptr(csh), ptr(dth), ptr(M), c_ll(Bsz * nc), c_int(H), c_int(G), c_int(Q),
+                  stream())
+        return M
+    seg = csh[..., :, None] - csh[..., None, :]
+    Lm = torch.exp(seg.masked_fill(~_mask(Q, CB.device), float("-inf"))) * dth[..., None, :]
+    return (CB.repeat_interleave(rep, dim=2) * Lm).to(cdt)
+
+
+def _bwd_qq(dM, CB, csh, dth, rep, cdt):
+    """From dM = dY X^T per head: M (as in ``_build_m``), dGh = dM o L o dt, rowW[l] = sum_s dM M,
+    colU[s] = sum_l dM CB L (so that sum_l dM M = colU dt_s without a division by dt)."""
+    Bsz, nc, G, Q, _ = CB.shape
+    H = csh.shape[2]
+    if CB.is_cuda and cdt == torch.bfloat16 and _lib.available():
+        M = torch.empty(Bsz, nc, H, Q, Q, dtype=cdt, device=CB.device)
+        dGh = torch.empty_like(M)
+        rowW = torch.empty(Bsz, nc, H, Q, dtype=torch.float32, device=CB.device)
+        colU = torch.empty_like(rowW)
+        _lib.call("sx_ssd_bwd_qq", ptr(dM), ptr(CB), ptr(csh), ptr(dth), ptr(M), ptr(dGh), ptr(rowW), ptr(colU),
+                  c_ll(Bsz * nc), c_int(H), c_int(G), c_int(Q), stream())
+        return M, dGh, rowW, colU
+    seg = csh[..., :, None] - csh[..., None, :]
+    Lexp = torch.exp(seg.masked_fill(~_mask(Q, CB.device), float("-inf")))
+    CBh = CB.repeat_interleave(rep, dim=2)
+    dMf = dM.float().view(Bsz, nc, H, Q, Q)
+    Lm = Lexp * dth[..., None, :]
+    U = dMf * CBh * Lexp
+    return (CBh * Lm).to(cdt), (dMf * Lm).to(cdt), (U * dth[..., None, :]).sum(-1), U.sum(-2)
+
+
+def _state_fwd(S, tot, init, cdt):
+    """H_0 = init; H_{c+1} = tot_c H_c + S_c. Returns the state entering every chunk (cdt) and the final state (fp32)."""
+    Bsz, nc, H, P, N = S.shape
+    if S.is_cuda and cdt == torch.bfloat16 and _lib.available() and (P * N) % 8 == 0:
+        Hprev = torch.empty(Bsz, nc, H, P, N, dtype=cdt, device=S.device)
+        final = torch.empty(Bsz, H, P, N, dtype=torch.float32, device=S.device)
+        init32 = init.float().contiguous() if init is not None else None
+        _lib.call("sx_ssd_state_fwd", ptr(S), ptr(tot), ptr(init32), ptr(Hprev), ptr(final), c_int(Bsz), c_int(nc),
+                  c_int(H), c_int(P * N), stream())
+        return Hprev, final
+    h = torch.zeros(Bsz, H, P, N, dtype=torch.float32, device=S.device) if init is None else init.float()
+    prev = []
+    for c in range(nc):
+        prev.append(h.to(cdt))
+        h = h * tot[:, c, :, None, None] + S[:, c]
+    return torch.stack(prev, dim=1), h
+
+
+def _state_bwd(dHprev, tot, Hprev, dfinal):
+    """Reverse of ``_state_fwd``: dS_c = dH_{c+1}; dtot_c = <dH_{c+1}, H_c>; dH_c = tot_c dH_{c+1} + dHprev_c."""
+    Bsz, nc, H, P, N = dHprev.shape
+    if dHprev.is_cuda and Hprev.dtype == torch.bfloat16 and _lib.available() and (P * N) % 8 == 0:
+        dS = torch.empty(Bsz, nc, H, P, N, dtype=torch.bfloat16, device=dHprev.device)
+        dtot = torch.zeros(Bsz, nc, H, dtype=torch.float32, device=dHprev.device)
+        dinit = torch.empty(Bsz, H, P, N, dtype=torch.float32, device=dHprev.device)
+        df = dfinal.float().contiguous() if dfinal is not None else None
+        _lib.call("sx_ssd_state_bwd", ptr(dHprev), ptr(tot), ptr(Hprev), ptr(df), ptr(dS), ptr(dtot), ptr(dinit),
+                  c_int(Bsz), c_int(nc), c_int(H), c_int(P * N), stream())
+        return dS, dtot, dinit
+    run = torch.zeros(Bsz, H, P, N, dtype=torch.float32, device=dHprev.device) if dfinal is None else dfinal.float()
+    dS, dtot = [None] * nc, [None] * nc
+    for c in range(nc - 1, -1, -1):
+        dS[c] = run
+        dtot[c] = (run * Hprev[:, c].float()).sum((-1, -2))
+        run = run * tot[:, c, :, None, None] + dHprev[:, c]
+    return torch.stack(dS, dim=1).to(Hprev.dtype), torch.stack(dtot, dim=1), run
+
+
+def _scale_rows(t5, scale, cdt):
+    """t5 [B,nc,Q,H,P] times scale [B,nc,Q,H] (fp32), rounded to the compute dtype."""
+    if t5.is_cuda and t5.dtype == torch.bfloat16 and cdt == torch.bfloat16 and _lib.available() and t5.shape[-1] % 8 == 0:
+        out = torch.empty_like(t5)
+        _lib.call("sx_ssd_scale_rows", ptr(t5), ptr(scale.contiguous()), ptr(out), c_ll(scale.numel()),
+                  c_int(t5.shape[-1]), stream())
+        return out
+    return (t5.float() * scale[..., None]).to(cdt)
+
+
+class _Chunks:
+    """Shapes, padded chunk views and the per-chunk cumulative decay shared by forward and backward."""
+
+    def __init__(self, x, dt, A, Bm, Cm, Q):
+        self.Bsz, self.L, self.H, self.P = x.shape
+        self.G, self.N = Bm.shape[2], Bm.shape[3]
+        self.rep = self.H // self.G
+        self.Q = Q
+        self.pad = (-self.L) % Q
+        if self.pad:
+            x = F.pad(x, (0, 0, 0, 0, 0, self.pad))
+            dt = F.pad(dt, (0, 0, 0, self.pad))
+            Bm = F.pad(Bm, (0, 0, 0, 0, 0, self.pad))
+            Cm = F.pad(Cm, (0, 0, 0, 0, 0, self.pad))
+        self.Lp = self.L + self.pad
+        self.nc = nc = self.Lp // Q
+        B_, H, P, G, N = self.Bsz, self.H, self.P, self.G, self.N
+        self.cdt = x.dtype
+        self.x5 = x.contiguous().view(B_, nc, Q, H, P)                          # token-major ("natural") layout
+        self.dtf = dt.float().reshape(B_, nc, Q, H)
+        self.cs = torch.cumsum(self.dtf * A.float(), dim=2)                      # [B,nc,Q,H] inclusive
+        self.csh = self.cs.permute(0, 1, 3, 2).contiguous()                      # [B,nc,H,Q]
+        self.dth = self.dtf.permute(0, 1, 3, 2).contiguous()
+        self.Bc = Bm.to(self.cdt).reshape(B_, nc, Q, G, N).permute(0, 1, 3, 2, 4).contiguous().view(B_ * nc, G, Q, N)
+        self.Cc = Cm.to(self.cdt).reshape(B_, nc, Q, G, N).permute(0, 1, 3, 2, 4).contiguous().view(B_ * nc, G, Q, N)
+        self.CB = gemm(self.Cc.view(-1, Q, N), self.Bc.view(-1, Q, N), out_dtype=torch.float32).view(B_, nc, G, Q, Q)
+        self.eL = torch.exp(self.cs[:, :, -1:, :] - self.cs)                     # exp(cs_last - cs_s)
+        self.decay = self.eL * self.dtf
+        self.tot = torch.exp(self.cs[:, :, -1, :]).contiguous()                  # [B,nc,H]
+        self.xw = _scale_rows(self.x5, self.decay, self.cdt).view(B_ * nc, Q, H * P)
+
+    def gs(self, g):
+        w = self.rep * self.P
+        return slice(g * w, (g + 1) * w)
+
+    def heads_first(self, t5):
+        """[B,nc,Q,H,P] -> contiguous [B*nc*H, Q, P]."""
+        return t5.permute(0, 1, 3, 2, 4).contiguous().view(-1, self.Q, self.P)
+
+    def y_off(self, Hprev):
+        B_, nc, Q, H, P, N = self.Bsz, self.nc, self.Q, self.H, self.P, self.N
+        out = torch.empty(B_ * nc, Q, H * P, dtype=torch.float32, device=Hprev.device)
+        Hp = Hprev.view(B_ * nc, H * P, N)
+        for g in range(self.G):
+            gemm(self.Cc[:, g], Hp[:, self.gs(g)], out=out[:, :, self.gs(g)])
+        return out.view(B_, nc, Q, H, P)
+
+
+class _SSDFn(torch.autograd.Function):
+    """Chunked SSD scan with a hand-written backward. Only the inputs and the chunk-entry states are kept for
+    backward; every Q x Q quantity is rebuilt there, so the memory held per layer is O(L) rather than O(L Q)."""
+
+    @staticmethod
+    def forward(ctx, x, dt, A, Bm, Cm, D, init_state, chunk):
+        ctx.set_materialize_grads(False)
+        k = _Chunks(x, dt, A, Bm, Cm, chunk)
+        B_, nc, Q, H, P, N = k.Bsz, k.nc, k.Q, k.H, k.P, k.N
+        M = _build_m(k.CB, k.csh, k.dth, k.rep, k.cdt)
+        Yi = gemm(M.view(-1, Q, Q), k.heads_first(k.x5), b_mn=True, out_dtype=torch.float32).view(B_, nc, H, Q, P)
+        S = torch.empty(B_ * nc, H * P, N, dtype=torch.float32, device=x.device)
+        for g in range(k.G):
+            gemm(k.xw[:, :, k.gs(g)], k.Bc[:, g], a_mn=True, b_mn=True, out=S[:, k.gs(g)])
+        Hprev, final = _state_fwd(S.view(B_, nc, H, P, N), k.tot, init_state, k.cdt)
+        y = Yi.permute(0, 1, 3, 2, 4) + k.y_off(Hprev) * torch.exp(k.cs)[..., None]
+        if D is not None:
+            y = y + k.x5.float() * D.float().view(H, 1)
+        ctx.save_for_backward(x, dt, A, Bm, Cm, D, Hprev)
+        ctx.chunk = chunk
+        ctx.has_init = init_state is not None
+        return y.reshape(B_, k.Lp, H, P)[:, :k.L].to(x.dtype), final
+
+    @staticmethod
+    def backward(ctx, dy, dfinal):
+        x, dt, A, Bm, Cm, D, Hprev = ctx.saved_tensors
+        k = _Chunks(x, dt, A, Bm, Cm, ctx.chunk)
+        B_, nc, Q, H, P, N, G = k.Bsz, k.nc, k.Q, k.H, k.P, k.N, k.G
+        dev, cdt = x.device, k.cdt
+        if dy is None:
+            dy = torch.zeros_like(x)
+        if k.pad:
+            dy = F.pad(dy, (0, 0, 0, 0, 0, k.pad))
+        dy5 = dy.contiguous().view(B_, nc, Q, H, P)
+        dyf, xf = dy5.float(), k.x5.float()
+        dD = (dyf * xf).sum((0, 1, 2, 4)) if D is not None else None
+        dx = dyf * D.float().view(H, 1) if D is not None else torch.zeros_like(dyf)
+        # ---- contribution of earlier chunks: y_off = exp(cs) C H_prev^T
+        E = torch.exp(k.cs)
+        dyeE = dyf * E[..., None]
+        dcs = (dyeE * k.y_off(Hprev)).sum(-1)                                    # [B,nc,Q,H]
+        dye = dyeE.to(cdt).view(B_ * nc, Q, H * P)
+        Hp = Hprev.view(B_ * nc, H * P, N)
+        dC = torch.empty(B_ * nc, G, Q, N, dtype=torch.float32, device=dev)
+        dHprev = torch.empty(B_ * nc, H * P, N, dtype=torch.float32, device=dev)
+        for g in range(G):
+            gemm(dye[:, :, k.gs(g)], Hp[:, k.gs(g)], b_mn=True, out=dC[:, g])
+            gemm(dye[:, :, k.gs(g)], k.Cc[:, g], a_mn=True, b_mn=True, out=dHprev[:, k.gs(g)])
+        # ---- chunk-to-chunk recurrence, reversed
+        dS, dtot, dinit = _state_bwd(dHprev.view(B_, nc, H, P, N), k.tot, Hprev, dfinal)
+        dcs_last = dtot * k.tot                                                  # [B,nc,H]
+        # ---- chunk states S = (x o decay)^T B
+        dSb = dS.view(B_ * nc, H * P, N)
+        dxw = torch.empty(B_ * nc, Q, H * P, dtype=torch.float32, device=dev)
+        dB = torch.empty(B_ * nc, G, Q, N, dtype=torch.float32, device=dev)
+        for g in range(G):
+            gemm(k.Bc[:, g], dSb[:, k.gs(g)], out=dxw[:, :, k.gs(g)])
+            gemm(k.xw[:, :, k.gs(g)], dSb[:, k.gs(g)], b_mn=True, out=dB[:, g])
+        dxw = dxw.view(B_, nc, Q, H, P)
+        dx += dxw * k.decay[..., None]
+        ddecay = (dxw * xf).sum(-1)
+        gdec = ddecay * k.decay
+        dcs_last = dcs_last + gdec.sum(2)
+        dcs -= gdec
+        ddt = ddecay * k.eL
+        # ---- quadratic term within the chunk
+        dyh = k.heads_first(dy5)
+        xh = k.heads_first(k.x5)
+        dM = gemm(dyh, xh)                                                       # [n,Q,Q]
+        M, dGh, rowW, colU = _bwd_qq(dM.view(B_, nc, H, Q, Q), k.CB, k.csh, k.dth, k.rep, cdt)
+        dxi = gemm(M.view(-1, Q, Q), dyh, a_mn=True, b_mn=True, out_dtype=torch.float32)
+        dx += dxi.view(B_, nc, H, Q, P).permute(0, 1, 3, 2, 4)
+        dcs += (rowW - colU * k.dth).permute(0, 1, 3, 2)
+        ddt += colU.permute(0, 1, 3, 2)
+        dG = dGh.view(B_ * nc, G, k.rep, Q, Q)
+        dG = (dG.sum(2, dtype=torch.float32).to(cdt) if k.rep > 1 else dG[:, :, 0]).reshape(-1, Q, Q)
+        dC += gemm(dG, k.Bc.view(-1, Q, N), b_mn=True, out_dtype=torch.float32).view(B_ * nc, G, Q, N)
+        dB += gemm(dG, k.Cc.view(-1, Q, N), a_mn=True, b_mn=True, out_dtype=torch.float32).view(B_ * nc, G, Q, N)
+        # ---- cs = cumsum(dt A) within the chunk
+        dcs[:, :, -1, :] += dcs_last
+        da = torch.flip(torch.cumsum(torch.flip(dcs, (2,)), 2), (2,))
+        ddt += da * A.float()
+        dA = (da * k.dtf).sum((0, 1, 2))
+        L = k.L
+        tok = lambda t: t.view(B_, nc, G, Q, N).permute(0, 1, 3, 2, 4).reshape(B_, k.Lp, G, N)[:, :L]
+        return (dx.reshape(B_, k.Lp, H, P)[:, :L].to(x.dtype), ddt.reshape(B_, k.Lp, H)[:, :L].to(dt.dtype),
+                dA.to(A.dtype), tok(dB).to(Bm.dtype), tok(dC).to(Cm.dtype),
+                dD.to(D.dtype) if D is not None else None, dinit if ctx.has_init else None, None)
+
+
 def ssd_scan(x, dt, A, Bm, Cm, D=None, chunk=64, init_state=None, return_state=False):
-    return ssd_chunked(x, dt, A, Bm, Cm, D, chunk, init_state, return_state)
+    """Chunked SSD scan (forward and backward hand-written; see ``_SSDFn``). Same arguments as ``ssd_reference``."""
+    L = x.shape[1]
+    chunk = max(8, min(int(chunk), 256))
+    if chunk & (chunk - 1):
+        chunk = 1 << (chunk.bit_length() - 1)          # the Q x Q kernels take power-of-two chunks
+    while chunk > 8 and chunk // 2 >= L:
+        chunk //= 2
+    y, final = _SSDFn.apply(x, dt, A, Bm, Cm, D, init_state, chunk)
+    return (y, final) if return_state else y
 
 
 def ssd_step(h, x, dt, A, Bm, Cm, D=None):

@@ -52,6 +52,30 @@ def test_ssd_chunked_vs_recurrence(L, chunk, G):
         assert _rel(got.grad, ref.grad) < 6e-2, name
 
 
+def test_ssd_scan_states_and_long_chunks():
+    """Initial and final state, their gradients, chunk 128 with 128 state columns (the Mamba-2 2.7B tiling)."""
+    torch.manual_seed(1)
+    B, L, H, P, N, G = 1, 384, 8, 64, 128, 1
+    mk = lambda *s, dt=torch.bfloat16: torch.randn(*s, device="cuda", dtype=dt)
+    x = mk(B, L, H, P).requires_grad_(True)
+    dt = (torch.rand(B, L, H, device="cuda") * 0.1 + 1e-3).requires_grad_(True)
+    A = (-torch.rand(H, device="cuda") * 4 - 0.5).requires_grad_(True)
+    Bm, Cm = mk(B, L, G, N).requires_grad_(True), mk(B, L, G, N).requires_grad_(True)
+    D = mk(H, dt=torch.float32).requires_grad_(True)
+    h0 = mk(B, H, P, N, dt=torch.float32).requires_grad_(True)
+    ins = [x, dt, A, Bm, Cm, D, h0]
+    y, hf = ssm.ssd_scan(x, dt, A, Bm, Cm, D, chunk=128, init_state=h0, return_state=True)
+    g, gf = torch.randn_like(y), torch.randn_like(hf)
+    grads = torch.autograd.grad((y.float() * g.float()).sum() + (hf * gf).sum(), ins)
+    ops.check_status()
+    ref = [t.detach().float().requires_grad_(True) for t in ins]
+    yr, hr = ssm.ssd_reference(*ref[:6], init_state=ref[6], return_state=True)
+    gr = torch.autograd.grad((yr * g.float()).sum() + (hr * gf).sum(), ref)
+    assert _rel(y, yr) < 3e-2 and _rel(hf, hr) < 3e-2
+    for got, want, name in zip(grads, gr, "x dt A B C D h0".split()):
+        assert _rel(got, want) < 6e-2, name
+
+
 def test_router_and_moe_layer():
     torch.manual_seed(0)
     T, d, E, k, Fd = 1000, 256, 16, 4, 192
