@@ -28,7 +28,7 @@ __global__ void __launch_bounds__(256) conv1d_fwd_kernel(const __nv_bfloat16* __
                                                          const __nv_bfloat16* __restrict__ bias,
                                                          __nv_bfloat16* __restrict__ y,
                                                          __nv_bfloat16* __restrict__ state_out, int B, int L, int C,
-                                                         int act) {
+                                                         int act, long long xld) {
   const int cv = C >> 3;
   const int lchunks = (L + CONV_TL - 1) / CONV_TL;
   const long long total = (long long)B * lchunks * cv;
@@ -56,12 +56,12 @@ __global__ void __launch_bounds__(256) conv1d_fwd_kernel(const __nv_bfloat16* __
       for (int j = 0; j < 8; ++j) hist[i][j] = 0.f;
     for (int i = 0; i < K - 1; ++i) {
       const int ls = l0 - (K - 1) + i;
-      if (ls >= 0) unpack8(ld8(x + ((long long)b * L + ls) * C + c), hist[i]);
+      if (ls >= 0) unpack8(ld8(x + ((long long)b * L + ls) * xld + c), hist[i]);
       else if (prev) unpack8(ld8(prev + ((long long)b * (K - 1) + (K - 1 + ls)) * C + c), hist[i]);
     }
     const int l1 = min(L, l0 + CONV_TL);
     for (int l = l0; l < l1; ++l) {
-      const bf16x8 raw = ld8(x + ((long long)b * L + l) * C + c);
+      const bf16x8 raw = ld8(x + ((long long)b * L + l) * xld + c);
       unpack8(raw, hist[K - 1]);
       float acc[8];
 #pragma unroll
@@ -88,95 +88,122 @@ __global__ void __launch_bounds__(256) conv1d_fwd_kernel(const __nv_bfloat16* __
   }
 }
 
-// dx and per-CTA partials of dw / dbias. Each CTA owns a contiguous range of (b, l) rows and all channels;
-// thread t owns channel vectors t, t + blockDim, ... (C/8 <= blockDim * CONV_VEC).
-constexpr int CONV_VEC = 4;
+// dx and per-CTA partials of dw / dbias. A CTA is 32 channel vectors (one per lane: 512 contiguous bytes per row) by
+// 8 runs of CONV_BTL consecutive positions (one per warp). A thread walks its run once: the last K inputs and the
+// last K pre-activation gradients slide through registers, so every x and dy vector is loaded once (plus the K-1
+// row overlap between runs) and dx is stored once. The 8 warps add their dw / db into shared memory and the CTA
+// writes one partial row; conv1d_reduce_partials sums the rows.
+constexpr int CONV_BTL = 16;
+template <int K>
 __global__ void __launch_bounds__(256) conv1d_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
                                                          const __nv_bfloat16* __restrict__ x,
                                                          const __nv_bfloat16* __restrict__ prev,
                                                          const __nv_bfloat16* __restrict__ w,
                                                          const __nv_bfloat16* __restrict__ bias,
                                                          __nv_bfloat16* __restrict__ dx, float* __restrict__ partial,
-                                                         int B, int L, int C, int K, int act, int rows_per_cta) {
+                                                         int B, int L, int C, int act, long long xld) {
+  __shared__ float s_acc[32][(CONV_MAXK + 1) * 8 + 1];
+  const int lane = threadIdx.x & 31, sub = threadIdx.x >> 5;
   const int cv = C >> 3;
-  const long long rows = (long long)B * L;
-  const long long r0 = (long long)blockIdx.x * rows_per_cta;
-  const long long r1 = min(rows, r0 + rows_per_cta);
-  for (int vi = 0; vi < CONV_VEC; ++vi) {
-    const int v = threadIdx.x + vi * blockDim.x;
-    if (v >= cv) break;
-    const int c = v * 8;
-    float wv[CONV_MAXK][8], bv[8];
+  const int v = blockIdx.x * 32 + lane;
+  const bool live = v < cv;
+  const int c = v * 8;
+  for (int i = threadIdx.x; i < 32 * ((CONV_MAXK + 1) * 8 + 1); i += 256) (&s_acc[0][0])[i] = 0.f;
+  __syncthreads();
+  if (live) {
+    float wv[K][8], bv[8], dwacc[K][8], dbacc[8];
+#pragma unroll
     for (int k = 0; k < K; ++k)
 #pragma unroll
-      for (int j = 0; j < 8; ++j) wv[k][j] = __bfloat162float(w[(c + j) * K + k]);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) bv[j] = bias ? __bfloat162float(bias[c + j]) : 0.f;
-    float dwacc[CONV_MAXK][8], dbacc[8];
-    for (int k = 0; k < CONV_MAXK; ++k)
-#pragma unroll
-      for (int j = 0; j < 8; ++j) dwacc[k][j] = 0.f;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) dbacc[j] = 0.f;
-    auto load_x = [&](int b, int ls, float (&o)[8]) {
-      if (ls >= 0) unpack8(ld8(x + ((long long)b * L + ls) * C + c), o);
-      else if (prev) unpack8(ld8(prev + ((long long)b * (K - 1) + (K - 1 + ls)) * C + c), o);
-      else {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = 0.f;
+      for (int j = 0; j < 8; ++j) {
+        wv[k][j] = __bfloat162float(w[(c + j) * K + k]);
+        dwacc[k][j] = 0.f;
       }
-    };
-    // dpre at row (b, l) = dy * act'(pre); recompute pre from x
-    auto dpre_at = [&](int b, int l, float (&o)[8]) {
-      unpack8(ld8(dy + ((long long)b * L + l) * C + c), o);
-      if (act) {
-        float pre[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) pre[j] = bv[j];
-        for (int k = 0; k < K; ++k) {
-          float xv[8];
-          load_x(b, l - (K - 1) + k, xv);
+    for (int j = 0; j < 8; ++j) {
+      bv[j] = bias ? __bfloat162float(bias[c + j]) : 0.f;
+      dbacc[j] = 0.f;
+    }
+    const int lchunks = (L + CONV_BTL - 1) / CONV_BTL;
+    const int nchunks = B * lchunks;
+    for (int ch = blockIdx.y * 8 + sub; ch < nchunks; ch += gridDim.y * 8) {
+      const int b = ch / lchunks, l0 = (ch % lchunks) * CONV_BTL;
+      const int lend = min(l0 + CONV_BTL, L);
+      float xh[K][8], dph[K][8];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) pre[j] += xv[j] * wv[k][j];
+      for (int i = 0; i < K; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) xh[i][j] = dph[i][j] = 0.f;
+#pragma unroll
+      for (int i = 1; i < K; ++i) {
+        const int ls = l0 - K + i;
+        if (ls >= 0) unpack8(ld8(x + ((long long)b * L + ls) * xld + c), xh[i]);
+        else if (prev) unpack8(ld8(prev + ((long long)b * (K - 1) + (K - 1 + ls)) * C + c), xh[i]);
+      }
+#pragma unroll 4
+      for (int l = l0; l < lend + K - 1; ++l) {
+#pragma unroll
+        for (int i = 0; i + 1 < K; ++i)
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            xh[i][j] = xh[i + 1][j];
+            dph[i][j] = dph[i + 1][j];
+          }
+        if (l < L) {
+          unpack8(ld8(x + ((long long)b * L + l) * xld + c), xh[K - 1]);
+          unpack8(ld8(dy + ((long long)b * L + l) * C + c), dph[K - 1]);
+          if (act) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float pre = bv[j];
+#pragma unroll
+              for (int k = 0; k < K; ++k) pre += xh[k][j] * wv[k][j];
+              dph[K - 1][j] *= silu_grad(pre);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) xh[K - 1][j] = dph[K - 1][j] = 0.f;
         }
+        if (l < lend) {   // this run's own rows: dw[k] += dpre[l] x[l-(K-1)+k], db += dpre[l]
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] *= silu_grad(pre[j]);
-      }
-    };
-    for (long long r = r0; r < r1; ++r) {
-      const int l = r % L, b = r / L;
-      // dx[l] = sum_k w[k] * dpre[l + (K-1) - k]
-      float dxa[8];
+          for (int j = 0; j < 8; ++j) {
+            dbacc[j] += dph[K - 1][j];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) dxa[j] = 0.f;
-      for (int k = 0; k < K; ++k) {
-        const int lo = l + (K - 1) - k;
-        if (lo >= L) continue;
-        float dp[8];
-        dpre_at(b, lo, dp);
+            for (int k = 0; k < K; ++k) dwacc[k][j] += dph[K - 1][j] * xh[k][j];
+          }
+        }
+        const int lo = l - (K - 1);   // dx[lo] = sum_k w[k] dpre[lo + (K-1) - k]
+        if (lo >= l0) {
+          float dxa[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) dxa[j] += wv[k][j] * dp[j];
-      }
-      st8(dx + r * C + c, pack8(dxa));
-      // dw[k] += dpre[l] * x[l - (K-1) + k] ; db += dpre[l]
-      float dp[8];
-      dpre_at(b, l, dp);
+          for (int j = 0; j < 8; ++j) {
+            float a = 0.f;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) dbacc[j] += dp[j];
-      for (int k = 0; k < K; ++k) {
-        float xv[8];
-        load_x(b, l - (K - 1) + k, xv);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) dwacc[k][j] += dp[j] * xv[j];
+            for (int k = 0; k < K; ++k) a += wv[k][j] * dph[K - 1 - k][j];
+            dxa[j] = a;
+          }
+          st8(dx + ((long long)b * L + lo) * C + c, pack8(dxa));
+        }
       }
     }
-    // partial layout: [cta][ (K+1) * C ] : dw as [c][k] flattened (C*K) then db (C)
-    float* pp = partial + (long long)blockIdx.x * (K + 1) * C;
-    for (int k = 0; k < K; ++k)
 #pragma unroll
-      for (int j = 0; j < 8; ++j) pp[(c + j) * K + k] = dwacc[k][j];
+    for (int j = 0; j < 8; ++j) {
 #pragma unroll
-    for (int j = 0; j < 8; ++j) pp[(long long)C * K + c + j] = dbacc[j];
+      for (int k = 0; k < K; ++k) atomicAdd(&s_acc[lane][k * 8 + j], dwacc[k][j]);
+      atomicAdd(&s_acc[lane][K * 8 + j], dbacc[j]);
+    }
+  }
+  __syncthreads();
+  // partial layout: [part][(K+1) * C]: dw as [c][k] flattened (C*K) then db (C)
+  float* pp = partial + (long long)blockIdx.y * (K + 1) * C;
+  for (int i = threadIdx.x; i < 32 * (K + 1) * 8; i += 256) {
+    const int ln = i / ((K + 1) * 8), r = i % ((K + 1) * 8);
+    const int k = r / 8, j = r % 8;
+    const int cc = (blockIdx.x * 32 + ln) * 8 + j;
+    if (cc >= C) continue;
+    if (k < K) pp[(long long)cc * K + k] = s_acc[ln][r];
+    else pp[(long long)C * K + cc] = s_acc[ln][r];
   }
 }
 
@@ -192,15 +219,15 @@ __global__ void conv1d_reduce_partials(const float* __restrict__ part, int npart
 using namespace sx;
 
 extern "C" int sx_conv1d_fwd(const void* x, const void* prev, const void* w, const void* bias, void* y, void* state_out,
-                             int B, int L, int C, int K, int act, cudaStream_t st) {
-  if (C % 8 || K > CONV_MAXK || K < 1) return -1;
+                             int B, int L, int C, int K, int act, long long xld, cudaStream_t st) {
+  if (C % 8 || K > CONV_MAXK || K < 1 || xld % 8 || xld < C) return -1;
   const long long total = (long long)B * ((L + CONV_TL - 1) / CONV_TL) * (C / 8);
   if (total == 0) return 0;
   const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
 #define SX_CONV_FWD(KK)                                                                                          \
   conv1d_fwd_kernel<KK><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)prev,              \
                                                 (const __nv_bfloat16*)w, (const __nv_bfloat16*)bias, (__nv_bfloat16*)y, \
-                                                (__nv_bfloat16*)state_out, B, L, C, act)
+                                                (__nv_bfloat16*)state_out, B, L, C, act, xld)
   switch (K) {
     case 1: SX_CONV_FWD(1); break;
     case 2: SX_CONV_FWD(2); break;
@@ -211,23 +238,32 @@ extern "C" int sx_conv1d_fwd(const void* x, const void* prev, const void* w, con
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
-extern "C" int sx_conv1d_bwd_parts(long long rows) {
-  long long p = (rows + 63) / 64;
-  return (int)(p < 1 ? 1 : (p > 592 ? 592 : p));
+// Number of partial rows the backward kernel writes for B sequences of L tokens.
+extern "C" int sx_conv1d_bwd_parts(int B, int L) {
+  const long long chunks = (long long)B * ((L + CONV_BTL - 1) / CONV_BTL);
+  const long long p = (chunks + 7) / 8;
+  return (int)(p < 1 ? 1 : (p > 1024 ? 1024 : p));
 }
 
-// partial: scratch of sx_conv1d_bwd_parts(B*L) * (K+1) * C floats; dwdb: fp32 [(K+1)*C] = dw [C][K] then db [C].
+// partial: scratch of sx_conv1d_bwd_parts(B, L) * (K+1) * C floats; dwdb: fp32 [(K+1)*C] = dw [C][K] then db [C].
 extern "C" int sx_conv1d_bwd(const void* dy, const void* x, const void* prev, const void* w, const void* bias, void* dx,
-                             float* partial, float* dwdb, int B, int L, int C, int K, int act, cudaStream_t st) {
-  if (C % 8 || K > CONV_MAXK || K < 1 || C / 8 > 256 * CONV_VEC) return -1;
-  const long long rows = (long long)B * L;
-  if (rows == 0) return 0;
-  const int parts = sx_conv1d_bwd_parts(rows);
-  const int rpc = (int)((rows + parts - 1) / parts);
-  conv1d_bwd_kernel<<<parts, 256, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
-                                           (const __nv_bfloat16*)prev, (const __nv_bfloat16*)w,
-                                           (const __nv_bfloat16*)bias, (__nv_bfloat16*)dx, partial, B, L, C, K, act,
-                                           rpc);
+                             float* partial, float* dwdb, int B, int L, int C, int K, int act, long long xld,
+                             cudaStream_t st) {
+  if (C % 8 || K > CONV_MAXK || K < 1 || xld % 8 || xld < C) return -1;
+  if ((long long)B * L == 0) return 0;
+  const int parts = sx_conv1d_bwd_parts(B, L);
+  const dim3 grid((C / 8 + 31) / 32, parts);
+#define SX_CONV_BWD(KK)                                                                                          \
+  conv1d_bwd_kernel<KK><<<grid, 256, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,                  \
+                                              (const __nv_bfloat16*)prev, (const __nv_bfloat16*)w,                \
+                                              (const __nv_bfloat16*)bias, (__nv_bfloat16*)dx, partial, B, L, C, act, xld)
+  switch (K) {
+    case 1: SX_CONV_BWD(1); break;
+    case 2: SX_CONV_BWD(2); break;
+    case 3: SX_CONV_BWD(3); break;
+    default: SX_CONV_BWD(4); break;
+  }
+#undef SX_CONV_BWD
   const int n = (K + 1) * C;
   conv1d_reduce_partials<<<(n + 255) / 256, 256, 0, st>>>(partial, parts, n, dwdb);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;

@@ -179,6 +179,153 @@ __global__ void __launch_bounds__(256) ssd_scale_rows_kernel(const __nv_bfloat16
   }
 }
 
+
+// Row kernels on the token-major layout: row r = ((bc * Q) + q) * H + h holds P = 8 * vp elements (vp a power of
+// two <= 32); the vp lanes of a row are adjacent, so row sums are shuffles inside a warp. `hf` is the index of the
+// same row in the heads-first layout [bc][H][Q] that the per-head GEMMs write.
+__device__ __forceinline__ float seg_sum(float v, int vp) {
+  for (int o = vp >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ void ld8f(const float* p, float (&f)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+
+// y = Yi (heads-first fp32) + E[r] * Yoff (fp32) + D[h] * x
+__global__ void __launch_bounds__(256) ssd_combine_kernel(const float* __restrict__ Yi, const float* __restrict__ Yoff,
+                                                          const __nv_bfloat16* __restrict__ x,
+                                                          const float* __restrict__ E, const float* __restrict__ D,
+                                                          __nv_bfloat16* __restrict__ y, long long rows, int H, int Q,
+                                                          int vp) {
+  const long long total = rows * vp;
+  for (long long i = blockIdx.x * 256ll + threadIdx.x; i < total; i += gridDim.x * 256ll) {
+    const long long r = i / vp;
+    const int pv = (int)(i % vp);
+    const int h = (int)(r % H);
+    const long long t = r / H;
+    const long long hf = ((t / Q) * H + h) * Q + (t % Q);
+    float a[8], b[8], xv[8], o[8];
+    ld8f(Yi + (hf * vp + pv) * 8, a);
+    ld8f(Yoff + i * 8, b);
+    unpack8(ld8(x + i * 8), xv);
+    const float e = E[r], d = D ? D[h] : 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = a[j] + e * b[j] + d * xv[j];
+    st8(y + i * 8, pack8(o));
+  }
+}
+
+// dye = dy * E[r]; dcs_off[r] = sum_p dy E Yoff; ddrow[r] = sum_p dy x
+__global__ void __launch_bounds__(256) ssd_bwd_rows1_kernel(const __nv_bfloat16* __restrict__ dy,
+                                                            const __nv_bfloat16* __restrict__ x,
+                                                            const float* __restrict__ Yoff, const float* __restrict__ E,
+                                                            __nv_bfloat16* __restrict__ dye, float* __restrict__ dcs,
+                                                            float* __restrict__ ddrow, long long rows, int vp) {
+  const long long total = rows * vp;
+  const long long span = ((total + 255) / 256) * 256;   // whole warps stay in the loop together for the shuffles
+  for (long long i = blockIdx.x * 256ll + threadIdx.x; i < span; i += gridDim.x * 256ll) {
+    const bool live = i < total;
+    const long long r = live ? i / vp : 0;
+    float g[8], xv[8], yo[8], o[8], s1 = 0.f, s2 = 0.f;
+    if (live) {
+      unpack8(ld8(dy + i * 8), g);
+      unpack8(ld8(x + i * 8), xv);
+      ld8f(Yoff + i * 8, yo);
+      const float e = E[r];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        o[j] = g[j] * e;
+        s1 += o[j] * yo[j];
+        s2 += g[j] * xv[j];
+      }
+      st8(dye + i * 8, pack8(o));
+    }
+    s1 = seg_sum(s1, vp);
+    s2 = seg_sum(s2, vp);
+    if (live && (i % vp) == 0) {
+      dcs[r] = s1;
+      ddrow[r] = s2;
+    }
+  }
+}
+
+// dx = D[h] dy + decay[r] dxw + dxi (heads-first); ddecay[r] = sum_p dxw x
+__global__ void __launch_bounds__(256) ssd_bwd_rows2_kernel(const __nv_bfloat16* __restrict__ dy,
+                                                            const __nv_bfloat16* __restrict__ x,
+                                                            const float* __restrict__ dxw, const float* __restrict__ dxi,
+                                                            const float* __restrict__ decay, const float* __restrict__ D,
+                                                            __nv_bfloat16* __restrict__ dx, float* __restrict__ ddecay,
+                                                            long long rows, int H, int Q, int vp) {
+  const long long total = rows * vp;
+  const long long span = ((total + 255) / 256) * 256;
+  for (long long i = blockIdx.x * 256ll + threadIdx.x; i < span; i += gridDim.x * 256ll) {
+    const bool live = i < total;
+    const long long r = live ? i / vp : 0;
+    float s = 0.f;
+    if (live) {
+      const int pv = (int)(i % vp);
+      const int h = (int)(r % H);
+      const long long t = r / H;
+      const long long hf = ((t / Q) * H + h) * Q + (t % Q);
+      float g[8], xv[8], a[8], b[8], o[8];
+      unpack8(ld8(dy + i * 8), g);
+      unpack8(ld8(x + i * 8), xv);
+      ld8f(dxw + i * 8, a);
+      ld8f(dxi + (hf * vp + pv) * 8, b);
+      const float dc = decay[r], d = D ? D[h] : 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        o[j] = d * g[j] + dc * a[j] + b[j];
+        s += a[j] * xv[j];
+      }
+      st8(dx + i * 8, pack8(o));
+    }
+    s = seg_sum(s, vp);
+    if (live && (i % vp) == 0) ddecay[r] = s;
+  }
+}
+
+// Gate of the Mamba-2 block: out = y * silu(z), z read in place from a wider row-major tensor (row stride zld).
+__global__ void __launch_bounds__(256) gate_mul_fwd_kernel(const __nv_bfloat16* __restrict__ y,
+                                                           const __nv_bfloat16* __restrict__ z, long long zld,
+                                                           __nv_bfloat16* __restrict__ out, long long rows, int cv) {
+  const long long total = rows * cv;
+  for (long long i = blockIdx.x * 256ll + threadIdx.x; i < total; i += gridDim.x * 256ll) {
+    const long long r = i / cv;
+    const int c = (int)(i % cv) * 8;
+    float a[8], b[8];
+    unpack8(ld8(y + i * 8), a);
+    unpack8(ld8(z + r * zld + c), b);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) a[j] *= b[j] / (1.f + __expf(-b[j]));
+    st8(out + i * 8, pack8(a));
+  }
+}
+__global__ void __launch_bounds__(256) gate_mul_bwd_kernel(const __nv_bfloat16* __restrict__ g,
+                                                           const __nv_bfloat16* __restrict__ y,
+                                                           const __nv_bfloat16* __restrict__ z, long long zld,
+                                                           __nv_bfloat16* __restrict__ dy, __nv_bfloat16* __restrict__ dz,
+                                                           long long rows, int cv) {
+  const long long total = rows * cv;
+  for (long long i = blockIdx.x * 256ll + threadIdx.x; i < total; i += gridDim.x * 256ll) {
+    const long long r = i / cv;
+    const int c = (int)(i % cv) * 8;
+    float gv[8], a[8], b[8], oy[8], oz[8];
+    unpack8(ld8(g + i * 8), gv);
+    unpack8(ld8(y + i * 8), a);
+    unpack8(ld8(z + r * zld + c), b);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float sg = 1.f / (1.f + __expf(-b[j]));
+      oy[j] = gv[j] * b[j] * sg;
+      oz[j] = gv[j] * a[j] * sg * (1.f + b[j] * (1.f - sg));
+    }
+    st8(dy + i * 8, pack8(oy));
+    st8(dz + i * 8, pack8(oz));
+  }
+}
+
 }  // namespace sx
 
 using namespace sx;
@@ -229,5 +376,62 @@ extern "C" int sx_ssd_scale_rows(const void* a, const void* scale, void* out, lo
   const long long nb = (total + 255) / 256;
   ssd_scale_rows_kernel<<<(unsigned)(nb < 148 * 16 ? nb : 148 * 16), 256, 0, st>>>(
       (const __nv_bfloat16*)a, (const float*)scale, (__nv_bfloat16*)out, rows, P);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+static bool vp_ok(int P) { const int vp = P / 8; return P % 8 == 0 && vp >= 1 && vp <= 32 && (vp & (vp - 1)) == 0; }
+static unsigned row_grid(long long total) {
+  const long long nb = (total + 255) / 256;
+  return (unsigned)(nb < 148 * 16 ? nb : 148 * 16);
+}
+
+extern "C" int sx_ssd_combine(const void* Yi, const void* Yoff, const void* x, const void* E, const void* D, void* y,
+                              long long rows, int H, int Q, int P, cudaStream_t st) {
+  if (!vp_ok(P)) return -1;
+  if (rows == 0) return 0;
+  ssd_combine_kernel<<<row_grid(rows * (P / 8)), 256, 0, st>>>((const float*)Yi, (const float*)Yoff,
+                                                                (const __nv_bfloat16*)x, (const float*)E,
+                                                                (const float*)D, (__nv_bfloat16*)y, rows, H, Q, P / 8);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+extern "C" int sx_ssd_bwd_rows1(const void* dy, const void* x, const void* Yoff, const void* E, void* dye, void* dcs,
+                                void* ddrow, long long rows, int P, cudaStream_t st) {
+  if (!vp_ok(P)) return -1;
+  if (rows == 0) return 0;
+  ssd_bwd_rows1_kernel<<<row_grid(rows * (P / 8)), 256, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
+                                                                  (const float*)Yoff, (const float*)E,
+                                                                  (__nv_bfloat16*)dye, (float*)dcs, (float*)ddrow, rows,
+                                                                  P / 8);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+extern "C" int sx_ssd_bwd_rows2(const void* dy, const void* x, const void* dxw, const void* dxi, const void* decay,
+                                const void* D, void* dx, void* ddecay, long long rows, int H, int Q, int P,
+                                cudaStream_t st) {
+  if (!vp_ok(P)) return -1;
+  if (rows == 0) return 0;
+  ssd_bwd_rows2_kernel<<<row_grid(rows * (P / 8)), 256, 0, st>>>(
+      (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const float*)dxw, (const float*)dxi, (const float*)decay,
+      (const float*)D, (__nv_bfloat16*)dx, (float*)ddecay, rows, H, Q, P / 8);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+extern "C" int sx_gate_mul_fwd(const void* y, const void* z, long long zld, void* out, long long rows, int C,
+                               cudaStream_t st) {
+  if (C % 8 || zld % 8) return -1;
+  if (rows == 0) return 0;
+  gate_mul_fwd_kernel<<<row_grid(rows * (C / 8)), 256, 0, st>>>((const __nv_bfloat16*)y, (const __nv_bfloat16*)z, zld,
+                                                                 (__nv_bfloat16*)out, rows, C / 8);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+extern "C" int sx_gate_mul_bwd(const void* g, const void* y, const void* z, long long zld, void* dy, void* dz,
+                               long long rows, int C, cudaStream_t st) {
+  if (C % 8 || zld % 8) return -1;
+  if (rows == 0) return 0;
+  gate_mul_bwd_kernel<<<row_grid(rows * (C / 8)), 256, 0, st>>>((const __nv_bfloat16*)g, (const __nv_bfloat16*)y,
+                                                                 (const __nv_bfloat16*)z, zld, (__nv_bfloat16*)dy,
+                                                                 (__nv_bfloat16*)dz, rows, C / 8);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }

@@ -56,7 +56,7 @@ class Mamba2Block(Module):
         H, P, G, N = self.nheads, self.headdim, self.ngroups, self.d_state
         z, xBC, dt = self.split(self.in_proj(u))
         prev = state["conv"] if state is not None else None
-        xBC_c = ssm.causal_conv1d(xBC.contiguous(), self.conv_weight, self.conv_bias, act=True, prev=prev)
+        xBC_c = ssm.causal_conv1d(xBC, self.conv_weight, self.conv_bias, act=True, prev=prev)
         if state is not None:
             K = self.d_conv
             hist = torch.cat([prev, xBC], dim=1) if prev is not None else xBC
@@ -74,7 +74,7 @@ class Mamba2Block(Module):
         else:
             y = out
         y = y.reshape(B, L, self.d_inner)
-        y = self.norm((y.float() * F.silu(z.float())).to(u.dtype))   # gated RMSNorm
+        y = self.norm(ssm.gate_mul(y, z))   # gated RMSNorm
         return self.out_proj(y)
 
     def allocate_state(self, batch, device=None, dtype=None):

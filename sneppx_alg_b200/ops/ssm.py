@@ -35,10 +35,13 @@ class _Conv1dFn(torch.autograd.Function):
     def forward(ctx, x, w, bias, act, prev):
         B, L, C = x.shape
         K = w.shape[1]
-        x = x.contiguous()
-        y = torch.empty_like(x)
+        # a column slice of a wider row-major tensor (the xBC part of in_proj's output) is read in place
+        if not (x.stride(2) == 1 and x.stride(1) % 8 == 0 and x.stride(1) >= C and x.stride(0) == L * x.stride(1)
+                and x.data_ptr() % 16 == 0):
+            x = x.contiguous()
+        y = torch.empty(B, L, C, dtype=x.dtype, device=x.device)
         _lib.call("sx_conv1d_fwd", ptr(x), ptr(prev), ptr(w), ptr(bias), ptr(y), ptr(None), c_int(B), c_int(L),
-                  c_int(C), c_int(K), c_int(int(act)), stream())
+                  c_int(C), c_int(K), c_int(int(act)), c_ll(x.stride(1)), stream())
         ctx.save_for_backward(x, w, bias if bias is not None else torch.empty(0), prev if prev is not None else torch.empty(0))
         ctx.meta = (act, bias is not None, prev is not None)
         return y
@@ -50,22 +53,55 @@ class _Conv1dFn(torch.autograd.Function):
         B, L, C = x.shape
         K = w.shape[1]
         dy = dy.contiguous()
-        dx = torch.empty_like(x)
-        parts = _lib.lib().sx_conv1d_bwd_parts(c_ll(B * L))
+        dx = torch.empty(B, L, C, dtype=x.dtype, device=x.device)
+        parts = _lib.lib().sx_conv1d_bwd_parts(c_int(B), c_int(L))
         partial = torch.empty(parts * (K + 1) * C, dtype=torch.float32, device=x.device)
         dwdb = torch.empty((K + 1) * C, dtype=torch.float32, device=x.device)
         _lib.call("sx_conv1d_bwd", ptr(dy), ptr(x), ptr(prev if has_p else None), ptr(w), ptr(bias if has_b else None),
-                  ptr(dx), ptr(partial), ptr(dwdb), c_int(B), c_int(L), c_int(C), c_int(K), c_int(int(act)), stream())
+                  ptr(dx), ptr(partial), ptr(dwdb), c_int(B), c_int(L), c_int(C), c_int(K), c_int(int(act)),
+                  c_ll(x.stride(1)), stream())
         dw = dwdb[: C * K].view(C, K).to(w.dtype)
         db = dwdb[C * K:].to(w.dtype) if has_b else None
         return dx, dw, db, None, None
 
 
 def causal_conv1d(x, w, bias=None, act=True, prev=None):
-    if x.is_cuda and x.dtype == torch.bfloat16 and _lib.available() and x.shape[-1] % 8 == 0 and w.shape[1] <= 4 \
-            and x.shape[-1] // 8 <= 1024:
+    if x.is_cuda and x.dtype == torch.bfloat16 and _lib.available() and x.shape[-1] % 8 == 0 and w.shape[1] <= 4:
         return _Conv1dFn.apply(x, w, bias, act, prev)
     return conv1d_reference(x, w, bias, act, prev)
+
+
+class _GateMulFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, y, z):
+        C_ = y.shape[-1]
+        rows = y.numel() // C_
+        y = y.contiguous()
+        zld = z.stride(-2)
+        out = torch.empty_like(y)
+        _lib.call("sx_gate_mul_fwd", ptr(y), ptr(z), c_ll(zld), ptr(out), c_ll(rows), c_int(C_), stream())
+        ctx.save_for_backward(y, z)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        y, z = ctx.saved_tensors
+        C_ = y.shape[-1]
+        g = g.contiguous()
+        dy, dz = torch.empty_like(y), torch.empty(z.shape, dtype=z.dtype, device=z.device)
+        _lib.call("sx_gate_mul_bwd", ptr(g), ptr(y), ptr(z), c_ll(z.stride(-2)), ptr(dy), ptr(dz),
+                  c_ll(y.numel() // C_), c_int(C_), stream())
+        return dy, dz
+
+
+def gate_mul(y, z):
+    """y * silu(z) (the Mamba-2 output gate); z may be a column slice of a wider row-major tensor."""
+    C_ = y.shape[-1]
+    if (y.is_cuda and y.dtype == torch.bfloat16 and z.dtype == torch.bfloat16 and _lib.available() and C_ % 8 == 0
+            and z.shape == y.shape and z.stride(-1) == 1 and z.stride(-2) % 8 == 0 and z.data_ptr() % 16 == 0
+            and (z.dim() == 2 or all(z.stride(i) == z.stride(i + 1) * z.shape[i + 1] for i in range(z.dim() - 2)))):
+        return _GateMulFn.apply(y, z)
+    return (y.float() * F.silu(z.float())).to(y.dtype)
 
 
 # ----------------------------------------------------------------------------- SSD scan (S1/S2)
@@ -233,6 +269,56 @@ def _scale_rows(t5, scale, cdt):
     return (t5.float() * scale[..., None]).to(cdt)
 
 
+def _rows_kernel_ok(t5, cdt):
+    P = t5.shape[-1]
+    return (t5.is_cuda and cdt == torch.bfloat16 and t5.dtype == torch.bfloat16 and _lib.available() and P % 8 == 0
+            and (P // 8) & (P // 8 - 1) == 0 and P <= 256)
+
+
+def _combine(Yi, Yoff, x5, E, D, cdt):
+    """y = Yi (heads-first [B,nc,H,Q,P]) + E Yoff + D x on the token-major layout [B,nc,Q,H,P]."""
+    B_, nc, Q, H, P = x5.shape
+    if _rows_kernel_ok(x5, cdt):
+        y = torch.empty_like(x5)
+        _lib.call("sx_ssd_combine", ptr(Yi), ptr(Yoff), ptr(x5), ptr(E), ptr(D.float().contiguous() if D is not None else None),
+                  ptr(y), c_ll(B_ * nc * Q * H), c_int(H), c_int(Q), c_int(P), stream())
+        return y
+    y = Yi.permute(0, 1, 3, 2, 4) + Yoff * E[..., None]
+    if D is not None:
+        y = y + x5.float() * D.float().view(H, 1)
+    return y.to(cdt)
+
+
+def _bwd_rows1(dy5, x5, Yoff, E, cdt):
+    """dye = dy E (compute dtype); dcs = sum_p dy E Yoff; ddrow = sum_p dy x."""
+    if _rows_kernel_ok(x5, cdt) and dy5.dtype == cdt:
+        dye = torch.empty_like(dy5)
+        dcs = torch.empty(E.shape, dtype=torch.float32, device=E.device)
+        ddrow = torch.empty_like(dcs)
+        _lib.call("sx_ssd_bwd_rows1", ptr(dy5), ptr(x5), ptr(Yoff), ptr(E), ptr(dye), ptr(dcs), ptr(ddrow),
+                  c_ll(E.numel()), c_int(x5.shape[-1]), stream())
+        return dye, dcs, ddrow
+    dyf = dy5.float()
+    dyeE = dyf * E[..., None]
+    return dyeE.to(cdt), (dyeE * Yoff).sum(-1), (dyf * x5.float()).sum(-1)
+
+
+def _bwd_rows2(dy5, x5, dxw5, dxi, decay, D, cdt):
+    """dx = D dy + decay dxw + dxi (heads-first [B,nc,H,Q,P]); ddecay = sum_p dxw x."""
+    B_, nc, Q, H, P = x5.shape
+    if _rows_kernel_ok(x5, cdt) and dy5.dtype == cdt:
+        dx = torch.empty_like(x5)
+        ddecay = torch.empty(decay.shape, dtype=torch.float32, device=decay.device)
+        _lib.call("sx_ssd_bwd_rows2", ptr(dy5), ptr(x5), ptr(dxw5), ptr(dxi), ptr(decay),
+                  ptr(D.float().contiguous() if D is not None else None), ptr(dx), ptr(ddecay), c_ll(decay.numel()),
+                  c_int(H), c_int(Q), c_int(P), stream())
+        return dx, ddecay
+    dx = dxw5 * decay[..., None] + dxi.permute(0, 1, 3, 2, 4)
+    if D is not None:
+        dx = dx + dy5.float() * D.float().view(H, 1)
+    return dx.to(cdt), (dxw5 * x5.float()).sum(-1)
+
+
 class _Chunks:
     """Shapes, padded chunk views and the per-chunk cumulative decay shared by forward and backward."""
 
@@ -296,13 +382,11 @@ class _SSDFn(torch.autograd.Function):
         for g in range(k.G):
             gemm(k.xw[:, :, k.gs(g)], k.Bc[:, g], a_mn=True, b_mn=True, out=S[:, k.gs(g)])
         Hprev, final = _state_fwd(S.view(B_, nc, H, P, N), k.tot, init_state, k.cdt)
-        y = Yi.permute(0, 1, 3, 2, 4) + k.y_off(Hprev) * torch.exp(k.cs)[..., None]
-        if D is not None:
-            y = y + k.x5.float() * D.float().view(H, 1)
+        y = _combine(Yi, k.y_off(Hprev), k.x5, torch.exp(k.cs), D, k.cdt)
         ctx.save_for_backward(x, dt, A, Bm, Cm, D, Hprev)
         ctx.chunk = chunk
         ctx.has_init = init_state is not None
-        return y.reshape(B_, k.Lp, H, P)[:, :k.L].to(x.dtype), final
+        return y.reshape(B_, k.Lp, H, P)[:, :k.L], final
 
     @staticmethod
     def backward(ctx, dy, dfinal):
@@ -314,15 +398,11 @@ class _SSDFn(torch.autograd.Function):
             dy = torch.zeros_like(x)
         if k.pad:
             dy = F.pad(dy, (0, 0, 0, 0, 0, k.pad))
-        dy5 = dy.contiguous().view(B_, nc, Q, H, P)
-        dyf, xf = dy5.float(), k.x5.float()
-        dD = (dyf * xf).sum((0, 1, 2, 4)) if D is not None else None
-        dx = dyf * D.float().view(H, 1) if D is not None else torch.zeros_like(dyf)
+        dy5 = dy.to(cdt).contiguous().view(B_, nc, Q, H, P)
         # ---- contribution of earlier chunks: y_off = exp(cs) C H_prev^T
-        E = torch.exp(k.cs)
-        dyeE = dyf * E[..., None]
-        dcs = (dyeE * k.y_off(Hprev)).sum(-1)                                    # [B,nc,Q,H]
-        dye = dyeE.to(cdt).view(B_ * nc, Q, H * P)
+        dye, dcs, ddrow = _bwd_rows1(dy5, k.x5, k.y_off(Hprev), torch.exp(k.cs), cdt)
+        dD = ddrow.sum((0, 1, 2)) if D is not None else None
+        dye = dye.view(B_ * nc, Q, H * P)
         Hp = Hprev.view(B_ * nc, H * P, N)
         dC = torch.empty(B_ * nc, G, Q, N, dtype=torch.float32, device=dev)
         dHprev = torch.empty(B_ * nc, H * P, N, dtype=torch.float32, device=dev)
@@ -340,21 +420,17 @@ class _SSDFn(torch.autograd.Function):
             gemm(k.Bc[:, g], dSb[:, k.gs(g)], out=dxw[:, :, k.gs(g)])
             gemm(k.xw[:, :, k.gs(g)], dSb[:, k.gs(g)], b_mn=True, out=dB[:, g])
         dxw = dxw.view(B_, nc, Q, H, P)
-        dx += dxw * k.decay[..., None]
-        ddecay = (dxw * xf).sum(-1)
-        gdec = ddecay * k.decay
-        dcs_last = dcs_last + gdec.sum(2)
-        dcs -= gdec
-        ddt = ddecay * k.eL
         # ---- quadratic term within the chunk
         dyh = k.heads_first(dy5)
         xh = k.heads_first(k.x5)
         dM = gemm(dyh, xh)                                                       # [n,Q,Q]
         M, dGh, rowW, colU = _bwd_qq(dM.view(B_, nc, H, Q, Q), k.CB, k.csh, k.dth, k.rep, cdt)
-        dxi = gemm(M.view(-1, Q, Q), dyh, a_mn=True, b_mn=True, out_dtype=torch.float32)
-        dx += dxi.view(B_, nc, H, Q, P).permute(0, 1, 3, 2, 4)
-        dcs += (rowW - colU * k.dth).permute(0, 1, 3, 2)
-        ddt += colU.permute(0, 1, 3, 2)
+        dxi = gemm(M.view(-1, Q, Q), dyh, a_mn=True, b_mn=True, out_dtype=torch.float32).view(B_, nc, H, Q, P)
+        dx, ddecay = _bwd_rows2(dy5, k.x5, dxw, dxi, k.decay, D, cdt)
+        gdec = ddecay * k.decay
+        dcs_last = dcs_last + gdec.sum(2)
+        dcs = dcs - gdec + (rowW - colU * k.dth).permute(0, 1, 3, 2)
+        ddt = ddecay * k.eL + colU.permute(0, 1, 3, 2)
         dG = dGh.view(B_ * nc, G, k.rep, Q, Q)
         dG = (dG.sum(2, dtype=torch.float32).to(cdt) if k.rep > 1 else dG[:, :, 0]).reshape(-1, Q, Q)
         dC += gemm(dG, k.Bc.view(-1, Q, N), b_mn=True, out_dtype=torch.float32).view(B_ * nc, G, Q, N)

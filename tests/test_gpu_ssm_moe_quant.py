@@ -52,6 +52,25 @@ def test_ssd_chunked_vs_recurrence(L, chunk, G):
         assert _rel(got.grad, ref.grad) < 6e-2, name
 
 
+def test_conv1d_strided_input_and_gate_mul():
+    """conv1d reads a column slice of a wider tensor in place; the output gate y * silu(z) does the same for z."""
+    torch.manual_seed(2)
+    B, L, C, W = 2, 300, 192, 512
+    wide = torch.randn(B, L, W, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (torch.randn(C, 4, device="cuda") * 0.3).to(torch.bfloat16).requires_grad_(True)
+    b = torch.randn(C, device="cuda", dtype=torch.bfloat16).requires_grad_(True)
+    y = ssm.causal_conv1d(wide[..., 64:64 + C], w, b, act=True)
+    out = ssm.gate_mul(y, wide[..., 320:320 + C])
+    g = torch.randn_like(out)
+    out.backward(g)
+    wr, ww, bb = [t.detach().float().requires_grad_(True) for t in (wide, w, b)]
+    yr = ssm.conv1d_reference(wr[..., 64:64 + C], ww, bb, True, None)
+    outr = yr * torch.nn.functional.silu(wr[..., 320:320 + C])
+    outr.backward(g.float())
+    assert _rel(out, outr) < 2e-2
+    assert _rel(wide.grad, wr.grad) < 3e-2 and _rel(w.grad, ww.grad) < 3e-2 and _rel(b.grad, bb.grad) < 3e-2
+
+
 def test_ssd_scan_states_and_long_chunks():
     """Initial and final state, their gradients, chunk 128 with 128 state columns (the Mamba-2 2.7B tiling)."""
     torch.manual_seed(1)
