@@ -165,13 +165,14 @@ __global__ void __launch_bounds__(256) ssd_state_bwd_kernel(const float* __restr
 // out = a * scale[row] (bf16 out); optional second output dot[row] = sum_p a * b * scale[row] (b fp32).
 __global__ void __launch_bounds__(256) ssd_scale_rows_kernel(const __nv_bfloat16* __restrict__ a,
                                                              const float* __restrict__ scale,
-                                                             __nv_bfloat16* __restrict__ out, long long rows, int P) {
+                                                             __nv_bfloat16* __restrict__ out, long long rows, int P,
+                                                             int H, long long ald) {
   const int vp = P >> 3;
   const long long total = rows * vp;
   for (long long i = blockIdx.x * 256ll + threadIdx.x; i < total; i += gridDim.x * 256ll) {
     const long long r = i / vp;
     float f[8];
-    unpack8(ld8(a + i * 8), f);
+    unpack8(ld8(a + (r / H) * ald + (i % ((long long)H * vp)) * 8), f);
     const float s = scale[r];
 #pragma unroll
     for (int j = 0; j < 8; ++j) f[j] *= s;
@@ -197,7 +198,7 @@ __global__ void __launch_bounds__(256) ssd_combine_kernel(const float* __restric
                                                           const __nv_bfloat16* __restrict__ x,
                                                           const float* __restrict__ E, const float* __restrict__ D,
                                                           __nv_bfloat16* __restrict__ y, long long rows, int H, int Q,
-                                                          int vp) {
+                                                          int vp, long long xld) {
   const long long total = rows * vp;
   for (long long i = blockIdx.x * 256ll + threadIdx.x; i < total; i += gridDim.x * 256ll) {
     const long long r = i / vp;
@@ -208,7 +209,7 @@ __global__ void __launch_bounds__(256) ssd_combine_kernel(const float* __restric
     float a[8], b[8], xv[8], o[8];
     ld8f(Yi + (hf * vp + pv) * 8, a);
     ld8f(Yoff + i * 8, b);
-    unpack8(ld8(x + i * 8), xv);
+    unpack8(ld8(x + t * xld + (h * vp + pv) * 8), xv);
     const float e = E[r], d = D ? D[h] : 0.f;
 #pragma unroll
     for (int j = 0; j < 8; ++j) o[j] = a[j] + e * b[j] + d * xv[j];
@@ -221,7 +222,8 @@ __global__ void __launch_bounds__(256) ssd_bwd_rows1_kernel(const __nv_bfloat16*
                                                             const __nv_bfloat16* __restrict__ x,
                                                             const float* __restrict__ Yoff, const float* __restrict__ E,
                                                             __nv_bfloat16* __restrict__ dye, float* __restrict__ dcs,
-                                                            float* __restrict__ ddrow, long long rows, int vp) {
+                                                            float* __restrict__ ddrow, long long rows, int vp,
+                                                            int H, long long xld) {
   const long long total = rows * vp;
   const long long span = ((total + 255) / 256) * 256;   // whole warps stay in the loop together for the shuffles
   for (long long i = blockIdx.x * 256ll + threadIdx.x; i < span; i += gridDim.x * 256ll) {
@@ -230,7 +232,7 @@ __global__ void __launch_bounds__(256) ssd_bwd_rows1_kernel(const __nv_bfloat16*
     float g[8], xv[8], yo[8], o[8], s1 = 0.f, s2 = 0.f;
     if (live) {
       unpack8(ld8(dy + i * 8), g);
-      unpack8(ld8(x + i * 8), xv);
+      unpack8(ld8(x + (r / H) * xld + (i % ((long long)H * vp)) * 8), xv);
       ld8f(Yoff + i * 8, yo);
       const float e = E[r];
 #pragma unroll
@@ -256,7 +258,7 @@ __global__ void __launch_bounds__(256) ssd_bwd_rows2_kernel(const __nv_bfloat16*
                                                             const float* __restrict__ dxw, const float* __restrict__ dxi,
                                                             const float* __restrict__ decay, const float* __restrict__ D,
                                                             __nv_bfloat16* __restrict__ dx, float* __restrict__ ddecay,
-                                                            long long rows, int H, int Q, int vp) {
+                                                            long long rows, int H, int Q, int vp, long long xld) {
   const long long total = rows * vp;
   const long long span = ((total + 255) / 256) * 256;
   for (long long i = blockIdx.x * 256ll + threadIdx.x; i < span; i += gridDim.x * 256ll) {
@@ -270,7 +272,7 @@ __global__ void __launch_bounds__(256) ssd_bwd_rows2_kernel(const __nv_bfloat16*
       const long long hf = ((t / Q) * H + h) * Q + (t % Q);
       float g[8], xv[8], a[8], b[8], o[8];
       unpack8(ld8(dy + i * 8), g);
-      unpack8(ld8(x + i * 8), xv);
+      unpack8(ld8(x + t * xld + (h * vp + pv) * 8), xv);
       ld8f(dxw + i * 8, a);
       ld8f(dxi + (hf * vp + pv) * 8, b);
       const float dc = decay[r], d = D ? D[h] : 0.f;
@@ -283,6 +285,23 @@ __global__ void __launch_bounds__(256) ssd_bwd_rows2_kernel(const __nv_bfloat16*
     }
     s = seg_sum(s, vp);
     if (live && (i % vp) == 0) ddecay[r] = s;
+  }
+}
+
+// Token-major [bc][Q][H][P] (token stride ild) -> heads-first [bc][H][Q][P]; 16 bytes per thread, both sides move
+// whole P-element rows (128 bytes for headdim 64).
+__global__ void __launch_bounds__(256) ssd_heads_first_kernel(const __nv_bfloat16* __restrict__ in, long long ild,
+                                                              __nv_bfloat16* __restrict__ out, long long rows, int H,
+                                                              int Q, int vp) {
+  const long long total = rows * vp;
+  for (long long o = blockIdx.x * 256ll + threadIdx.x; o < total; o += gridDim.x * 256ll) {
+    const int pv = (int)(o % vp);
+    const long long hf = o / vp;          // (bc * H + h) * Q + q
+    const int q = (int)(hf % Q);
+    const long long bh = hf / Q;
+    const int h = (int)(bh % H);
+    const long long t = (bh / H) * Q + q;
+    st8(out + o * 8, ld8(in + t * ild + (h * vp + pv) * 8));
   }
 }
 
@@ -369,13 +388,15 @@ extern "C" int sx_ssd_state_bwd(const void* dHprev, const void* tot, const void*
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
-extern "C" int sx_ssd_scale_rows(const void* a, const void* scale, void* out, long long rows, int P, cudaStream_t st) {
-  if (P % 8) return -1;
+// `ald` (and `xld` below): elements between consecutive tokens of the bf16 input, >= H * P, a multiple of 8.
+extern "C" int sx_ssd_scale_rows(const void* a, const void* scale, void* out, long long rows, int P, int H,
+                                 long long ald, cudaStream_t st) {
+  if (P % 8 || ald % 8) return -1;
   const long long total = rows * (P / 8);
   if (total == 0) return 0;
   const long long nb = (total + 255) / 256;
   ssd_scale_rows_kernel<<<(unsigned)(nb < 148 * 16 ? nb : 148 * 16), 256, 0, st>>>(
-      (const __nv_bfloat16*)a, (const float*)scale, (__nv_bfloat16*)out, rows, P);
+      (const __nv_bfloat16*)a, (const float*)scale, (__nv_bfloat16*)out, rows, P, H, ald);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
@@ -386,34 +407,34 @@ static unsigned row_grid(long long total) {
 }
 
 extern "C" int sx_ssd_combine(const void* Yi, const void* Yoff, const void* x, const void* E, const void* D, void* y,
-                              long long rows, int H, int Q, int P, cudaStream_t st) {
-  if (!vp_ok(P)) return -1;
+                              long long rows, int H, int Q, int P, long long xld, cudaStream_t st) {
+  if (!vp_ok(P) || xld % 8) return -1;
   if (rows == 0) return 0;
   ssd_combine_kernel<<<row_grid(rows * (P / 8)), 256, 0, st>>>((const float*)Yi, (const float*)Yoff,
                                                                 (const __nv_bfloat16*)x, (const float*)E,
-                                                                (const float*)D, (__nv_bfloat16*)y, rows, H, Q, P / 8);
+                                                                (const float*)D, (__nv_bfloat16*)y, rows, H, Q, P / 8, xld);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
 extern "C" int sx_ssd_bwd_rows1(const void* dy, const void* x, const void* Yoff, const void* E, void* dye, void* dcs,
-                                void* ddrow, long long rows, int P, cudaStream_t st) {
-  if (!vp_ok(P)) return -1;
+                                void* ddrow, long long rows, int P, int H, long long xld, cudaStream_t st) {
+  if (!vp_ok(P) || xld % 8) return -1;
   if (rows == 0) return 0;
   ssd_bwd_rows1_kernel<<<row_grid(rows * (P / 8)), 256, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
                                                                   (const float*)Yoff, (const float*)E,
                                                                   (__nv_bfloat16*)dye, (float*)dcs, (float*)ddrow, rows,
-                                                                  P / 8);
+                                                                  P / 8, H, xld);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
 extern "C" int sx_ssd_bwd_rows2(const void* dy, const void* x, const void* dxw, const void* dxi, const void* decay,
                                 const void* D, void* dx, void* ddecay, long long rows, int H, int Q, int P,
-                                cudaStream_t st) {
-  if (!vp_ok(P)) return -1;
+                                long long xld, cudaStream_t st) {
+  if (!vp_ok(P) || xld % 8) return -1;
   if (rows == 0) return 0;
   ssd_bwd_rows2_kernel<<<row_grid(rows * (P / 8)), 256, 0, st>>>(
       (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const float*)dxw, (const float*)dxi, (const float*)decay,
-      (const float*)D, (__nv_bfloat16*)dx, (float*)ddecay, rows, H, Q, P / 8);
+      (const float*)D, (__nv_bfloat16*)dx, (float*)ddecay, rows, H, Q, P / 8, xld);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
@@ -433,5 +454,14 @@ extern "C" int sx_gate_mul_bwd(const void* g, const void* y, const void* z, long
   gate_mul_bwd_kernel<<<row_grid(rows * (C / 8)), 256, 0, st>>>((const __nv_bfloat16*)g, (const __nv_bfloat16*)y,
                                                                  (const __nv_bfloat16*)z, zld, (__nv_bfloat16*)dy,
                                                                  (__nv_bfloat16*)dz, rows, C / 8);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+extern "C" int sx_ssd_heads_first(const void* in, long long ild, void* out, long long rows, int H, int Q, int P,
+                                  cudaStream_t st) {
+  if (P % 8 || ild % 8) return -1;
+  if (rows == 0) return 0;
+  ssd_heads_first_kernel<<<row_grid(rows * (P / 8)), 256, 0, st>>>((const __nv_bfloat16*)in, ild, (__nv_bfloat16*)out,
+                                                                    rows, H, Q, P / 8);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }

@@ -262,9 +262,9 @@ def _state_bwd(dHprev, tot, Hprev, dfinal):
 def _scale_rows(t5, scale, cdt):
     """t5 [B,nc,Q,H,P] times scale [B,nc,Q,H] (fp32), rounded to the compute dtype."""
     if t5.is_cuda and t5.dtype == torch.bfloat16 and cdt == torch.bfloat16 and _lib.available() and t5.shape[-1] % 8 == 0:
-        out = torch.empty_like(t5)
+        out = torch.empty(t5.shape, dtype=cdt, device=t5.device)
         _lib.call("sx_ssd_scale_rows", ptr(t5), ptr(scale.contiguous()), ptr(out), c_ll(scale.numel()),
-                  c_int(t5.shape[-1]), stream())
+                  c_int(t5.shape[-1]), c_int(t5.shape[-2]), c_ll(t5.stride(2)), stream())
         return out
     return (t5.float() * scale[..., None]).to(cdt)
 
@@ -279,9 +279,9 @@ def _combine(Yi, Yoff, x5, E, D, cdt):
     """y = Yi (heads-first [B,nc,H,Q,P]) + E Yoff + D x on the token-major layout [B,nc,Q,H,P]."""
     B_, nc, Q, H, P = x5.shape
     if _rows_kernel_ok(x5, cdt):
-        y = torch.empty_like(x5)
+        y = torch.empty(x5.shape, dtype=cdt, device=x5.device)
         _lib.call("sx_ssd_combine", ptr(Yi), ptr(Yoff), ptr(x5), ptr(E), ptr(D.float().contiguous() if D is not None else None),
-                  ptr(y), c_ll(B_ * nc * Q * H), c_int(H), c_int(Q), c_int(P), stream())
+                  ptr(y), c_ll(B_ * nc * Q * H), c_int(H), c_int(Q), c_int(P), c_ll(x5.stride(2)), stream())
         return y
     y = Yi.permute(0, 1, 3, 2, 4) + Yoff * E[..., None]
     if D is not None:
@@ -296,7 +296,7 @@ def _bwd_rows1(dy5, x5, Yoff, E, cdt):
         dcs = torch.empty(E.shape, dtype=torch.float32, device=E.device)
         ddrow = torch.empty_like(dcs)
         _lib.call("sx_ssd_bwd_rows1", ptr(dy5), ptr(x5), ptr(Yoff), ptr(E), ptr(dye), ptr(dcs), ptr(ddrow),
-                  c_ll(E.numel()), c_int(x5.shape[-1]), stream())
+                  c_ll(E.numel()), c_int(x5.shape[-1]), c_int(x5.shape[-2]), c_ll(x5.stride(2)), stream())
         return dye, dcs, ddrow
     dyf = dy5.float()
     dyeE = dyf * E[..., None]
@@ -307,11 +307,11 @@ def _bwd_rows2(dy5, x5, dxw5, dxi, decay, D, cdt):
     """dx = D dy + decay dxw + dxi (heads-first [B,nc,H,Q,P]); ddecay = sum_p dxw x."""
     B_, nc, Q, H, P = x5.shape
     if _rows_kernel_ok(x5, cdt) and dy5.dtype == cdt:
-        dx = torch.empty_like(x5)
+        dx = torch.empty(x5.shape, dtype=cdt, device=x5.device)
         ddecay = torch.empty(decay.shape, dtype=torch.float32, device=decay.device)
         _lib.call("sx_ssd_bwd_rows2", ptr(dy5), ptr(x5), ptr(dxw5), ptr(dxi), ptr(decay),
                   ptr(D.float().contiguous() if D is not None else None), ptr(dx), ptr(ddecay), c_ll(decay.numel()),
-                  c_int(H), c_int(Q), c_int(P), stream())
+                  c_int(H), c_int(Q), c_int(P), c_ll(x5.stride(2)), stream())
         return dx, ddecay
     dx = dxw5 * decay[..., None] + dxi.permute(0, 1, 3, 2, 4)
     if D is not None:
@@ -337,7 +337,12 @@ class _Chunks:
         self.nc = nc = self.Lp // Q
         B_, H, P, G, N = self.Bsz, self.H, self.P, self.G, self.N
         self.cdt = x.dtype
-        self.x5 = x.contiguous().view(B_, nc, Q, H, P)                          # token-major ("natural") layout
+        # token-major ("natural") layout; a column slice of a wider row-major tensor (x inside the conv output)
+        # is used in place: the kernels take the token stride
+        if not (x.is_cuda and x.stride(3) == 1 and x.stride(2) == P and x.stride(0) == self.Lp * x.stride(1)
+                and x.stride(1) % 8 == 0 and x.data_ptr() % 16 == 0):
+            x = x.contiguous()
+        self.x5 = x.view(B_, nc, Q, H, P)
         self.dtf = dt.float().reshape(B_, nc, Q, H)
         self.cs = torch.cumsum(self.dtf * A.float(), dim=2)                      # [B,nc,Q,H] inclusive
         self.csh = self.cs.permute(0, 1, 3, 2).contiguous()                      # [B,nc,H,Q]
@@ -356,6 +361,11 @@ class _Chunks:
 
     def heads_first(self, t5):
         """[B,nc,Q,H,P] -> contiguous [B*nc*H, Q, P]."""
+        if t5.is_cuda and t5.dtype == torch.bfloat16 and _lib.available() and self.P % 8 == 0:
+            out = torch.empty(self.Bsz * self.nc * self.H, self.Q, self.P, dtype=t5.dtype, device=t5.device)
+            _lib.call("sx_ssd_heads_first", ptr(t5), c_ll(t5.stride(2)), ptr(out), c_ll(out.shape[0] * self.Q),
+                      c_int(self.H), c_int(self.Q), c_int(self.P), stream())
+            return out
         return t5.permute(0, 1, 3, 2, 4).contiguous().view(-1, self.Q, self.P)
 
     def y_off(self, Hprev):
