@@ -188,13 +188,10 @@ __device__ __forceinline__ float seg_sum(float v, int vp) {
   for (int o = vp >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   return v;
 }
-__device__ __forceinline__ void ld8f(const float* p, float (&f)[8]) {
-  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
-  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
-}
 
-// y = Yi (heads-first fp32) + E[r] * Yoff (fp32) + D[h] * x
-__global__ void __launch_bounds__(256) ssd_combine_kernel(const float* __restrict__ Yi, const float* __restrict__ Yoff,
+// y = Yi (heads-first) + E[r] * Yoff + D[h] * x
+__global__ void __launch_bounds__(256) ssd_combine_kernel(const __nv_bfloat16* __restrict__ Yi,
+                                                          const __nv_bfloat16* __restrict__ Yoff,
                                                           const __nv_bfloat16* __restrict__ x,
                                                           const float* __restrict__ E, const float* __restrict__ D,
                                                           __nv_bfloat16* __restrict__ y, long long rows, int H, int Q,
@@ -207,8 +204,8 @@ __global__ void __launch_bounds__(256) ssd_combine_kernel(const float* __restric
     const long long t = r / H;
     const long long hf = ((t / Q) * H + h) * Q + (t % Q);
     float a[8], b[8], xv[8], o[8];
-    ld8f(Yi + (hf * vp + pv) * 8, a);
-    ld8f(Yoff + i * 8, b);
+    unpack8(ld8(Yi + (hf * vp + pv) * 8), a);
+    unpack8(ld8(Yoff + i * 8), b);
     unpack8(ld8(x + t * xld + (h * vp + pv) * 8), xv);
     const float e = E[r], d = D ? D[h] : 0.f;
 #pragma unroll
@@ -220,7 +217,8 @@ __global__ void __launch_bounds__(256) ssd_combine_kernel(const float* __restric
 // dye = dy * E[r]; dcs_off[r] = sum_p dy E Yoff; ddrow[r] = sum_p dy x
 __global__ void __launch_bounds__(256) ssd_bwd_rows1_kernel(const __nv_bfloat16* __restrict__ dy,
                                                             const __nv_bfloat16* __restrict__ x,
-                                                            const float* __restrict__ Yoff, const float* __restrict__ E,
+                                                            const __nv_bfloat16* __restrict__ Yoff,
+                                                            const float* __restrict__ E,
                                                             __nv_bfloat16* __restrict__ dye, float* __restrict__ dcs,
                                                             float* __restrict__ ddrow, long long rows, int vp,
                                                             int H, long long xld) {
@@ -233,7 +231,7 @@ __global__ void __launch_bounds__(256) ssd_bwd_rows1_kernel(const __nv_bfloat16*
     if (live) {
       unpack8(ld8(dy + i * 8), g);
       unpack8(ld8(x + (r / H) * xld + (i % ((long long)H * vp)) * 8), xv);
-      ld8f(Yoff + i * 8, yo);
+      unpack8(ld8(Yoff + i * 8), yo);
       const float e = E[r];
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
@@ -255,7 +253,8 @@ __global__ void __launch_bounds__(256) ssd_bwd_rows1_kernel(const __nv_bfloat16*
 // dx = D[h] dy + decay[r] dxw + dxi (heads-first); ddecay[r] = sum_p dxw x
 __global__ void __launch_bounds__(256) ssd_bwd_rows2_kernel(const __nv_bfloat16* __restrict__ dy,
                                                             const __nv_bfloat16* __restrict__ x,
-                                                            const float* __restrict__ dxw, const float* __restrict__ dxi,
+                                                            const __nv_bfloat16* __restrict__ dxw,
+                                                            const __nv_bfloat16* __restrict__ dxi,
                                                             const float* __restrict__ decay, const float* __restrict__ D,
                                                             __nv_bfloat16* __restrict__ dx, float* __restrict__ ddecay,
                                                             long long rows, int H, int Q, int vp, long long xld) {
@@ -273,8 +272,8 @@ __global__ void __launch_bounds__(256) ssd_bwd_rows2_kernel(const __nv_bfloat16*
       float g[8], xv[8], a[8], b[8], o[8];
       unpack8(ld8(dy + i * 8), g);
       unpack8(ld8(x + t * xld + (h * vp + pv) * 8), xv);
-      ld8f(dxw + i * 8, a);
-      ld8f(dxi + (hf * vp + pv) * 8, b);
+      unpack8(ld8(dxw + i * 8), a);
+      unpack8(ld8(dxi + (hf * vp + pv) * 8), b);
       const float dc = decay[r], d = D ? D[h] : 0.f;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
@@ -410,7 +409,7 @@ extern "C" int sx_ssd_combine(const void* Yi, const void* Yoff, const void* x, c
                               long long rows, int H, int Q, int P, long long xld, cudaStream_t st) {
   if (!vp_ok(P) || xld % 8) return -1;
   if (rows == 0) return 0;
-  ssd_combine_kernel<<<row_grid(rows * (P / 8)), 256, 0, st>>>((const float*)Yi, (const float*)Yoff,
+  ssd_combine_kernel<<<row_grid(rows * (P / 8)), 256, 0, st>>>((const __nv_bfloat16*)Yi, (const __nv_bfloat16*)Yoff,
                                                                 (const __nv_bfloat16*)x, (const float*)E,
                                                                 (const float*)D, (__nv_bfloat16*)y, rows, H, Q, P / 8, xld);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
@@ -421,7 +420,7 @@ extern "C" int sx_ssd_bwd_rows1(const void* dy, const void* x, const void* Yoff,
   if (!vp_ok(P) || xld % 8) return -1;
   if (rows == 0) return 0;
   ssd_bwd_rows1_kernel<<<row_grid(rows * (P / 8)), 256, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
-                                                                  (const float*)Yoff, (const float*)E,
+                                                                  (const __nv_bfloat16*)Yoff, (const float*)E,
                                                                   (__nv_bfloat16*)dye, (float*)dcs, (float*)ddrow, rows,
                                                                   P / 8, H, xld);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
@@ -433,7 +432,8 @@ extern "C" int sx_ssd_bwd_rows2(const void* dy, const void* x, const void* dxw, 
   if (!vp_ok(P) || xld % 8) return -1;
   if (rows == 0) return 0;
   ssd_bwd_rows2_kernel<<<row_grid(rows * (P / 8)), 256, 0, st>>>(
-      (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const float*)dxw, (const float*)dxi, (const float*)decay,
+      (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)dxw, (const __nv_bfloat16*)dxi,
+      (const float*)decay,
       (const float*)D, (__nv_bfloat16*)dx, (float*)ddecay, rows, H, Q, P / 8, xld);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }

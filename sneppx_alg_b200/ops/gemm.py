@@ -87,6 +87,19 @@ def gemm(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=None, c=None, beta
         bs = t.stride(0) if t.dim() == 3 else 0
         return t, ext_mn, ext_k, ld, bs
 
+    if (a_mn and a.dim() == 2 and a.shape[-1] % 64 != 0 and a.shape[-1] > 256 and tile_group is None
+            and k_ranges is None and a.stride(-1) == 1 and (out is None or out.dim() == 2)
+            and (c is None or c.dim() == 2)):
+        # MN-major operands are tiled in 64-element atoms: run the aligned part in place and only the ragged
+        # tail (< 64 rows of the result) through a transposed copy
+        m0 = a.shape[-1] // 64 * 64
+        if out is None:
+            n_out = b.shape[-1] if b_mn else b.shape[-2]
+            out = torch.empty(a.shape[-1], n_out, dtype=out_dtype or torch.bfloat16, device=a.device)
+        kw = dict(b_mn=b_mn, alpha=alpha, beta=beta, bias=bias, act=act, sm_limit=sm_limit, force_bn=force_bn)
+        gemm(a[:, :m0], b, a_mn=True, out=out[:m0], c=None if c is None else c[:m0], **kw)
+        gemm(a[:, m0:].t().contiguous(), b, a_mn=False, out=out[m0:], c=None if c is None else c[m0:], **kw)
+        return out
     if a_mn and a.shape[-1] % 64 != 0:
         a, a_mn = a.transpose(-1, -2).contiguous(), False
     if b_mn and b.shape[-1] % 64 != 0:

@@ -283,7 +283,7 @@ def _combine(Yi, Yoff, x5, E, D, cdt):
         _lib.call("sx_ssd_combine", ptr(Yi), ptr(Yoff), ptr(x5), ptr(E), ptr(D.float().contiguous() if D is not None else None),
                   ptr(y), c_ll(B_ * nc * Q * H), c_int(H), c_int(Q), c_int(P), c_ll(x5.stride(2)), stream())
         return y
-    y = Yi.permute(0, 1, 3, 2, 4) + Yoff * E[..., None]
+    y = Yi.float().permute(0, 1, 3, 2, 4) + Yoff.float() * E[..., None]
     if D is not None:
         y = y + x5.float() * D.float().view(H, 1)
     return y.to(cdt)
@@ -300,7 +300,7 @@ def _bwd_rows1(dy5, x5, Yoff, E, cdt):
         return dye, dcs, ddrow
     dyf = dy5.float()
     dyeE = dyf * E[..., None]
-    return dyeE.to(cdt), (dyeE * Yoff).sum(-1), (dyf * x5.float()).sum(-1)
+    return dyeE.to(cdt), (dyeE * Yoff.float()).sum(-1), (dyf * x5.float()).sum(-1)
 
 
 def _bwd_rows2(dy5, x5, dxw5, dxi, decay, D, cdt):
@@ -313,7 +313,8 @@ def _bwd_rows2(dy5, x5, dxw5, dxi, decay, D, cdt):
                   ptr(D.float().contiguous() if D is not None else None), ptr(dx), ptr(ddecay), c_ll(decay.numel()),
                   c_int(H), c_int(Q), c_int(P), c_ll(x5.stride(2)), stream())
         return dx, ddecay
-    dx = dxw5 * decay[..., None] + dxi.permute(0, 1, 3, 2, 4)
+    dxw5 = dxw5.float()
+    dx = dxw5 * decay[..., None] + dxi.float().permute(0, 1, 3, 2, 4)
     if D is not None:
         dx = dx + dy5.float() * D.float().view(H, 1)
     return dx.to(cdt), (dxw5 * x5.float()).sum(-1)
@@ -344,9 +345,9 @@ class _Chunks:
             x = x.contiguous()
         self.x5 = x.view(B_, nc, Q, H, P)
         self.dtf = dt.float().reshape(B_, nc, Q, H)
-        self.cs = torch.cumsum(self.dtf * A.float(), dim=2)                      # [B,nc,Q,H] inclusive
-        self.csh = self.cs.permute(0, 1, 3, 2).contiguous()                      # [B,nc,H,Q]
-        self.dth = self.dtf.permute(0, 1, 3, 2).contiguous()
+        self.dth = self.dtf.permute(0, 1, 3, 2).contiguous()                     # [B,nc,H,Q]
+        self.csh = torch.cumsum(self.dth * A.float().view(H, 1), dim=-1)         # inclusive, along the chunk
+        self.cs = self.csh.permute(0, 1, 3, 2).contiguous()                      # [B,nc,Q,H]
         self.Bc = Bm.to(self.cdt).reshape(B_, nc, Q, G, N).permute(0, 1, 3, 2, 4).contiguous().view(B_ * nc, G, Q, N)
         self.Cc = Cm.to(self.cdt).reshape(B_, nc, Q, G, N).permute(0, 1, 3, 2, 4).contiguous().view(B_ * nc, G, Q, N)
         self.CB = gemm(self.Cc.view(-1, Q, N), self.Bc.view(-1, Q, N), out_dtype=torch.float32).view(B_, nc, G, Q, Q)
@@ -370,7 +371,7 @@ class _Chunks:
 
     def y_off(self, Hprev):
         B_, nc, Q, H, P, N = self.Bsz, self.nc, self.Q, self.H, self.P, self.N
-        out = torch.empty(B_ * nc, Q, H * P, dtype=torch.float32, device=Hprev.device)
+        out = torch.empty(B_ * nc, Q, H * P, dtype=self.cdt, device=Hprev.device)
         Hp = Hprev.view(B_ * nc, H * P, N)
         for g in range(self.G):
             gemm(self.Cc[:, g], Hp[:, self.gs(g)], out=out[:, :, self.gs(g)])
@@ -387,7 +388,7 @@ class _SSDFn(torch.autograd.Function):
         k = _Chunks(x, dt, A, Bm, Cm, chunk)
         B_, nc, Q, H, P, N = k.Bsz, k.nc, k.Q, k.H, k.P, k.N
         M = _build_m(k.CB, k.csh, k.dth, k.rep, k.cdt)
-        Yi = gemm(M.view(-1, Q, Q), k.heads_first(k.x5), b_mn=True, out_dtype=torch.float32).view(B_, nc, H, Q, P)
+        Yi = gemm(M.view(-1, Q, Q), k.heads_first(k.x5), b_mn=True).view(B_, nc, H, Q, P)
         S = torch.empty(B_ * nc, H * P, N, dtype=torch.float32, device=x.device)
         for g in range(k.G):
             gemm(k.xw[:, :, k.gs(g)], k.Bc[:, g], a_mn=True, b_mn=True, out=S[:, k.gs(g)])
@@ -424,7 +425,7 @@ class _SSDFn(torch.autograd.Function):
         dcs_last = dtot * k.tot                                                  # [B,nc,H]
         # ---- chunk states S = (x o decay)^T B
         dSb = dS.view(B_ * nc, H * P, N)
-        dxw = torch.empty(B_ * nc, Q, H * P, dtype=torch.float32, device=dev)
+        dxw = torch.empty(B_ * nc, Q, H * P, dtype=cdt, device=dev)
         dB = torch.empty(B_ * nc, G, Q, N, dtype=torch.float32, device=dev)
         for g in range(G):
             gemm(k.Bc[:, g], dSb[:, k.gs(g)], out=dxw[:, :, k.gs(g)])
@@ -435,7 +436,7 @@ class _SSDFn(torch.autograd.Function):
         xh = k.heads_first(k.x5)
         dM = gemm(dyh, xh)                                                       # [n,Q,Q]
         M, dGh, rowW, colU = _bwd_qq(dM.view(B_, nc, H, Q, Q), k.CB, k.csh, k.dth, k.rep, cdt)
-        dxi = gemm(M.view(-1, Q, Q), dyh, a_mn=True, b_mn=True, out_dtype=torch.float32).view(B_, nc, H, Q, P)
+        dxi = gemm(M.view(-1, Q, Q), dyh, a_mn=True, b_mn=True).view(B_, nc, H, Q, P)
         dx, ddecay = _bwd_rows2(dy5, k.x5, dxw, dxi, k.decay, D, cdt)
         gdec = ddecay * k.decay
         dcs_last = dcs_last + gdec.sum(2)
@@ -447,7 +448,8 @@ class _SSDFn(torch.autograd.Function):
         dB += gemm(dG, k.Cc.view(-1, Q, N), a_mn=True, b_mn=True, out_dtype=torch.float32).view(B_ * nc, G, Q, N)
         # ---- cs = cumsum(dt A) within the chunk
         dcs[:, :, -1, :] += dcs_last
-        da = torch.flip(torch.cumsum(torch.flip(dcs, (2,)), 2), (2,))
+        dch = dcs.permute(0, 1, 3, 2).contiguous()                               # reverse cumulative sum along the chunk
+        da = (dch.sum(-1, keepdim=True) - torch.cumsum(dch, -1) + dch).permute(0, 1, 3, 2)
         ddt += da * A.float()
         dA = (da * k.dtf).sum((0, 1, 2))
         L = k.L

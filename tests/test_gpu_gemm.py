@@ -81,3 +81,21 @@ def test_linear_autograd_matches_torch():
     yr.backward(g.float())
     ops.check_status()
     assert _rel(y, yr) < 1e-2 and _rel(x.grad, xr.grad) < 1e-2 and _rel(w.grad, wr.grad) < 1e-2
+
+
+def test_gemm_mn_major_a_with_ragged_rows():
+    """Weight-gradient shape whose output rows are not a multiple of the 64-element MN-major atom (Mamba-2's
+    in_proj has 10576): the aligned part runs in place, the tail through a small transposed copy; with and
+    without accumulation into an fp32 buffer."""
+    torch.manual_seed(3)
+    T, M, N = 1024, 400, 320
+    g = torch.randn(T, M, device="cuda", dtype=torch.bfloat16)
+    x = torch.randn(T, N, device="cuda", dtype=torch.bfloat16)
+    ref = g.float().t() @ x.float()
+    d = gemm(g, x, a_mn=True, b_mn=True)
+    assert d.shape == (M, N) and _rel(d, ref) < 1e-2
+    acc = torch.randn(M, N, device="cuda")
+    want = ref + acc
+    gemm(g, x, a_mn=True, b_mn=True, out=acc, c=acc, beta=1.0)
+    ops.check_status()
+    assert _rel(acc, want) < 1e-2
