@@ -365,6 +365,16 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, ms_e2e = t.tolist()
     tokens = B * S * world * args.steps
+    ep_note = None
+    if args.ep and world > 1:
+        # capacity-factor expert parallelism: report how many routed (token, expert) entries were over capacity
+        from sneppx_alg_b200.parallel import expert as _ep
+        d = torch.tensor([float(_ep.dropped_entries())], device=dev, dtype=torch.float64)
+        dist.all_reduce(d)
+        n_moe = sum(1 for m in model.modules() if hasattr(m, "ep_group") and hasattr(m, "router"))
+        routed = float(B * S * world) * cfg.num_experts_per_token * max(n_moe, 1) * (args.warmup + 2 * args.steps)
+        ep_note = {"capacity_factor": float(os.environ.get("SX_EP_CAPACITY", "2.0")),
+                   "dropped_fraction_of_routed_entries": float(d.item()) / routed}
     value = tokens / (ms / 1e3)
     e2e = tokens / (ms_e2e / 1e3)
     if rank == 0:
@@ -384,6 +394,8 @@ def main():
             "gpu_launches": launches,
             "clocks": clocks,
         }
+        if ep_note:
+            line["config"]["expert_parallel"] = ep_note
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

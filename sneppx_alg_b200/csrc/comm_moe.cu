@@ -86,8 +86,9 @@ __global__ void __launch_bounds__(256) ep_exchange_kernel(PeerTable pt, const in
   for (int el = threadIdx.x; el < E_local; el += blockDim.x) {
     const int e = pt.rank * E_local + el;
     const int pad = (s_total[e] + 127) / 128 * 128;
-    k_ranges[2 * el] = s_off[e];
-    k_ranges[2 * el + 1] = s_off[e] + pad;
+    // rows past the end of the buffer are dropped by their senders (capacity), so the ranges stop there too
+    k_ranges[2 * el] = min(s_off[e], max_tiles * 128);
+    k_ranges[2 * el + 1] = min(s_off[e] + pad, max_tiles * 128);
   }
   for (int t = threadIdx.x; t < max_tiles; t += blockDim.x) {
     const int row = t * 128;
@@ -112,7 +113,7 @@ __global__ void __launch_bounds__(256) ep_exchange_kernel(PeerTable pt, const in
 
 __global__ void ep_assign_kernel(const int* __restrict__ idx, long long n, const int* __restrict__ e_base,
                                  int* __restrict__ cursors, int E_local, int max_rows, int* __restrict__ dest_rank,
-                                 int* __restrict__ dest_row, int* __restrict__ status) {
+                                 int* __restrict__ dest_row, int* __restrict__ dropped) {
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
     const int e = idx[i];
     if (e < 0) {
@@ -120,10 +121,10 @@ __global__ void ep_assign_kernel(const int* __restrict__ idx, long long n, const
       dest_row[i] = 0;
     } else {
       const int row = e_base[e] + atomicAdd(&cursors[e], 1);
-      if (row >= max_rows) {  // owner buffer too small for this routing: drop the entry and report
+      if (row >= max_rows) {  // past the owner's capacity: the entry is dropped (its gate weight gets no gradient)
         dest_rank[i] = -1;
         dest_row[i] = 0;
-        atomicCAS(status, 0, 5);
+        atomicAdd(dropped, 1);
       } else {
         dest_rank[i] = e / E_local;
         dest_row[i] = row;
@@ -207,7 +208,8 @@ using namespace sx;
 // tile_cum (persistent uint32 [max_tiles], zeroed once) and tile_expected (uint32 [max_tiles]).
 extern "C" int sx_ep_plan(const SxPeers* peers, const int* idx, long long n, int E, int* counts, int channel,
                           unsigned epoch, int* e_base, int* cursors, int* tile_group, int* k_ranges, void* tile_cum,
-                          void* tile_expected, int* total_rows, int max_tiles, int* dest_rank, int* dest_row, int* status,
+                          void* tile_expected, int* total_rows, int max_tiles, int* dest_rank, int* dest_row, int* dropped,
+                          int* status,
                           cudaStream_t st) {
   if (E > EP_MAX_E || E % peers->world) return -1;
   cudaMemsetAsync(counts, 0, sizeof(int) * E, st);
@@ -216,7 +218,7 @@ extern "C" int sx_ep_plan(const SxPeers* peers, const int* idx, long long n, int
   ep_exchange_kernel<<<1, 256, 0, st>>>(ep_table(peers), counts, E, channel, epoch, e_base, cursors, tile_group, k_ranges,
                                         (uint32_t*)tile_cum, (uint32_t*)tile_expected, total_rows, max_tiles, status);
   ep_assign_kernel<<<blocks < 1 ? 1 : blocks, 256, 0, st>>>(idx, n, e_base, cursors, E / peers->world, max_tiles * 128, dest_rank,
-                                                            dest_row, status);
+                                                            dest_row, dropped);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

@@ -10,6 +10,7 @@ sum. Library path (CPU / ``fused=False``): ``all_to_all_single`` around the loca
 from __future__ import annotations
 
 import ctypes as C
+import os
 
 import torch
 import torch.distributed as dist
@@ -26,9 +27,16 @@ CH_PLAN, CH_DISP_SIG, CH_DISP_DONE, CH_COMB_SIG, CH_COMB_DONE = 48, 49, 50, 51, 
 class EPWorkspace:
     """Symmetric buffers of one EP group, shared by all MoE layers (sizes fixed at first use)."""
 
-    def __init__(self, sg, T, k, d, E, cap_mult=2.0):
+    def __init__(self, sg, T, k, d, E, cap_mult=None):
         self.sg, self.world, self.rank = sg, sg.world, sg.rank
         self.E, self.E_local = E, E // sg.world
+        # Capacity factor: an owner accepts up to cap_mult times its fair share of routed rows (never more than every
+        # row of every rank); rows routed past it are dropped, as in capacity-factor MoE training, and counted in
+        # ``dropped``. The reference has no capacity limit because its experts run on the token's own rank
+        # (kernel/distributed/expert_parallel.c:70-110).
+        if cap_mult is None:
+            cap_mult = float(os.environ.get("SX_EP_CAPACITY", "2.0"))
+        self.cap_mult = cap_mult
         rows = min(sg.world * T * k, int(cap_mult * T * k)) + self.E_local * 128
         self.max_rows = (rows + 127) // 128 * 128
         self.max_tiles = self.max_rows // 128
@@ -45,6 +53,7 @@ class EPWorkspace:
         self.cum_b = torch.zeros(self.max_tiles, dtype=torch.int32, device=dev)
         self.counts = torch.zeros(E, dtype=torch.int32, device=dev)
         self.cta_counter = torch.zeros(8, dtype=torch.int32, device=dev)
+        self.dropped = torch.zeros(1, dtype=torch.int32, device=dev)     # routed entries dropped so far (all layers)
         self.d = d
         torch.cuda.synchronize()
         dist.barrier(sg.group)
@@ -70,7 +79,7 @@ class EPPlan:
                   _lib.ptr(ws.counts), C.c_int(CH_PLAN), C.c_uint(ws.sg.next_epoch(CH_PLAN)), _lib.ptr(e_base),
                   _lib.ptr(cursors), _lib.ptr(self.tile_group), _lib.ptr(self.k_ranges), _lib.ptr(ws.cum_a),
                   _lib.ptr(self.expected_a), _lib.ptr(self.total_rows), C.c_int(ws.max_tiles), _lib.ptr(self.dest_rank),
-                  _lib.ptr(self.dest_row), ws.status(), _lib.stream())
+                  _lib.ptr(self.dest_row), _lib.ptr(ws.dropped), ws.status(), _lib.stream())
         self.valid = self.expected_a - prev       # rows that will arrive per tile for this routing
 
 
@@ -205,6 +214,16 @@ def _library_forward(layer, x, idx, w, base):
 
 
 _WORKSPACES = {}
+
+
+def dropped_entries(reset=False) -> int:
+    """Routed (token, expert) entries dropped for capacity by this rank's dispatches since start (or last reset)."""
+    n = 0
+    for ws in _WORKSPACES.values():
+        n += int(ws.dropped.item())
+        if reset:
+            ws.dropped.zero_()
+    return n
 
 
 def ep_experts_forward(layer, x, idx, w, base, fused=None):

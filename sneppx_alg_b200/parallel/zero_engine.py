@@ -98,7 +98,12 @@ class ZeroEngine:
                     b.tensor.zero_()
                     return b.tensor
                 return torch.zeros(n, dtype=dt, device=dev)
-        self.fp = FlatParams(model, params=ordered, align=64, shard_multiple=self.world, alloc=alloc)
+        starts, k = [], 0
+        for ps in bucket_params:
+            starts.append(k)
+            k += len(ps)
+        self.fp = FlatParams(model, params=ordered, align=64, shard_multiple=self.world, alloc=alloc,
+                             group_starts=starts)
         self.efp = None
         if self.expert_params:
             self.efp = FlatParams(model, params=self.expert_params, align=64)

@@ -28,10 +28,12 @@ def _unique_params(module) -> List[torch.nn.Parameter]:
 class FlatParams:
     """Re-homes the parameters of ``module`` into one flat buffer and gives each a ``main_grad`` view
     into one flat gradient buffer. ``align`` pads every tensor so that views stay 16-byte aligned and
-    the total is divisible by ``shard_multiple`` (so it splits evenly across ranks)."""
+    the total is divisible by ``shard_multiple`` (so it splits evenly across ranks). ``group_starts`` lists the
+    indices of parameters that open a bucket: their offsets are rounded up to ``align * shard_multiple`` so every
+    bucket splits evenly too, whatever the sizes of the tensors inside it."""
 
     def __init__(self, module, grad_dtype: Optional[torch.dtype] = None, align: int = 64, shard_multiple: int = 1,
-                 params: Optional[Iterable[torch.nn.Parameter]] = None, alloc=None):
+                 params: Optional[Iterable[torch.nn.Parameter]] = None, alloc=None, group_starts=()):
         self.params = list(params) if params is not None else _unique_params(module)
         assert self.params, "no trainable parameters"
         p0 = self.params[0]
@@ -43,11 +45,14 @@ class FlatParams:
         self.grad_dtype = grad_dtype or self.dtype
         self.offsets = []
         off = 0
-        for p in self.params:
+        unit = align * shard_multiple
+        starts = set(group_starts)
+        for i, p in enumerate(self.params):
             assert p.device == self.device
+            if i in starts:
+                off = (off + unit - 1) // unit * unit
             self.offsets.append(off)
             off += (p.numel() + align - 1) // align * align
-        unit = align * shard_multiple
         self.total = (off + unit - 1) // unit * unit
         alloc = alloc or (lambda n, dt: torch.zeros(n, dtype=dt, device=self.device))
         self.flat = alloc(self.total, self.dtype)

@@ -13,17 +13,21 @@ from sneppx_alg_b200.parallel.zero_engine import ZeroEngine, partition_range
 from sneppx_alg_b200.training.engine import TrainEngine
 
 
-def _cfg():
+def _cfg(arch="transformer"):
+    if arch == "mamba2":   # many small tensors (per-head scalars, conv taps): bucket sizes need their own padding
+        return ModelConfig(architecture="mamba2", hidden_size=64, num_hidden_layers=3, vocab_size=256,
+                           ssm_state_size=16, ssm_expand=2, ssm_head_dim=16, ssm_ngroups=1, ssm_conv_kernel=4,
+                           ssm_chunk_size=8, max_position_embeddings=32, rms_norm_eps=1e-5, tie_word_embeddings=True)
     return ModelConfig(hidden_size=64, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2,
                        intermediate_size=128, vocab_size=256, max_position_embeddings=32, rms_norm_eps=1e-5)
 
 
-def _worker(rank, world, port, stage, q):
+def _worker(rank, world, port, stage, q, arch="transformer"):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     torch.manual_seed(0)
-    model = build_model(_cfg())
+    model = build_model(_cfg(arch))
     eng = ZeroEngine(model, zero_stage=stage, lr=1e-2, weight_decay=0.1, max_grad_norm=1.0)
     losses = []
     for step in range(3):
@@ -57,6 +61,28 @@ def test_zero_matches_single_process(stage):
     assert max(abs(a - b) for a, b in zip(losses, ref_losses)) < 1e-4
     # compare parameter values tensor by tensor (flat layouts differ in padding)
     assert abs(nrm - float(eng.last_norm[1])) < 1e-3 * max(1.0, nrm)
+
+
+def test_zero_buckets_of_small_tensors_split_evenly():
+    """Mamba-2 layers hold tensors of 8 and 512 elements; every bucket must still be a multiple of 64 * world."""
+    torch.manual_seed(0)
+    ref = build_model(_cfg("mamba2"))
+    eng = TrainEngine(ref, lr=1e-2, weight_decay=0.1, max_grad_norm=1.0)
+    ref_losses = []
+    for step in range(3):
+        ids = torch.randint(0, 256, (2, 16), generator=torch.Generator().manual_seed(step))
+        ref_losses.append(eng.step(ids, ids).item())
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + os.getpid() % 2000 + 7
+    procs = [ctx.Process(target=_worker, args=(r, 3, port, 3, q, "mamba2")) for r in range(3)]
+    for p in procs:
+        p.start()
+    losses, flat, nrm = q.get(timeout=180)
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    assert max(abs(a - b) for a, b in zip(losses, ref_losses)) < 1e-4
 
 
 def test_partition_range_reference_rule():
