@@ -4,7 +4,7 @@ time whole NumPy ops; here every case is one native sm_100a kernel).
 ``python -m sneppx_alg_b200.benchmarks.kernels <case> [--small] [--iters N] [--out file.json]``
 
 Cases: gemm, gemm_wgrad, attn_fwd, attn_bwd, rmsnorm, glu, rope, ce, adamw, sumsq, paged_decode, gemm_dq_fp8,
-gemm_dq_int4, gemm_fp8, gemm_fp8_prefill, conv1d, router, quant_fp8, all.  ``--small`` picks a problem that still exceeds L2 but holds well
+gemm_dq_int4, gemm_fp8, gemm_fp8_prefill, conv1d, conv1d_bwd, ssd_fwd, ssd_bwd, router, quant_fp8, all.  ``--small`` picks a problem that still exceeds L2 but holds well
 under 2 GB so that one launch can be captured by a profiler in seconds.  Timing: CUDA events on the launching
 stream after 3 warm-up launches; inputs are larger than L2 or rotated between iterations.  Fractions are against the
 measured copy bandwidth / cuBLAS bf16 throughput in ``MEASURED_PEAKS.json`` when that file is present at the
@@ -219,6 +219,46 @@ def case_conv1d(small, iters):
     with torch.no_grad():
         ms = _time(lambda: ssm.causal_conv1d(x, w, b), iters)
     return dict(shape=[B, S, C], ms=ms, bytes=2 * B * S * C * 2)
+
+
+def case_conv1d_bwd(small, iters):
+    from ..ops import ssm
+    B, S, C = (4, 4096, 4352) if small else (16, 4096, 4352)
+    x, w, b = _bf(B, S, C).requires_grad_(True), _bf(C, 4).requires_grad_(True), _bf(C).requires_grad_(True)
+    y = ssm.causal_conv1d(x, w, b)
+    g = torch.randn_like(y)
+    ms = _time(lambda: torch.autograd.grad(y, (x, w, b), g, retain_graph=True), iters)
+    return dict(shape=[B, S, C], ms=ms, bytes=3 * B * S * C * 2)      # dy and x in, dx out
+
+
+def _ssd_inputs(small):
+    B, L, H, P, G, N = (1, 4096, 80, 64, 1, 128) if small else (1, 8192, 80, 64, 8, 128)
+    x = _bf(B, L, H, P).requires_grad_(True)
+    dt = (torch.rand(B, L, H, device="cuda") * 0.1 + 1e-3).requires_grad_(True)
+    A = (-torch.rand(H, device="cuda") * 4 - 0.5).requires_grad_(True)
+    Bm, Cm = _bf(B, L, G, N).requires_grad_(True), _bf(B, L, G, N).requires_grad_(True)
+    D = torch.randn(H, device="cuda").requires_grad_(True)
+    return (x, dt, A, Bm, Cm, D), (B, L, H, P, G, N)
+
+
+def case_ssd_fwd(small, iters):
+    """Mamba-2 2.7B scan shape (80 heads of 64, state 128, chunk 128). bytes = x in + y out + chunk states written and
+    read once (bf16): what one kernel per chunk would have to move."""
+    from ..ops import ssm
+    ins, (B, L, H, P, G, N) = _ssd_inputs(small)
+    with torch.no_grad():
+        ms = _time(lambda: ssm.ssd_scan(*ins, chunk=128), iters)
+    return dict(shape=[B, L, H, P, G, N], ms=ms, bytes=2 * B * L * H * P * 2 + 2 * B * (L // 128) * H * P * N * 2,
+                flops=2.0 * B * L * H * (128 * P + 2 * P * N) + 2.0 * B * L * G * 128 * N)
+
+
+def case_ssd_bwd(small, iters):
+    from ..ops import ssm
+    ins, (B, L, H, P, G, N) = _ssd_inputs(small)
+    y = ssm.ssd_scan(*ins, chunk=128)
+    g = torch.randn_like(y)
+    ms = _time(lambda: torch.autograd.grad(y, ins, g, retain_graph=True), iters)
+    return dict(shape=[B, L, H, P, G, N], ms=ms, bytes=4 * B * L * H * P * 2 + 3 * B * (L // 128) * H * P * N * 2)
 
 
 def case_router(small, iters):

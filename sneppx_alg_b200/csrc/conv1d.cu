@@ -60,67 +60,92 @@ __global__ void __launch_bounds__(256) conv1d_fwd_kernel(const __nv_bfloat16* __
       else if (prev) unpack8(ld8(prev + ((long long)b * (K - 1) + (K - 1 + ls)) * C + c), hist[i]);
     }
     const int l1 = min(L, l0 + CONV_TL);
-    for (int l = l0; l < l1; ++l) {
-      const bf16x8 raw = ld8(x + ((long long)b * L + l) * xld + c);
-      unpack8(raw, hist[K - 1]);
-      float acc[8];
+    for (int lb = l0; lb < l1; lb += 4) {
+      bf16x8 raw4[4];   // four independent 16-byte loads in flight per thread
 #pragma unroll
-      for (int j = 0; j < 8; ++j) acc[j] = bv[j];
+      for (int u = 0; u < 4; ++u)
+        if (lb + u < l1) raw4[u] = ld8(x + ((long long)b * L + lb + u) * xld + c);
 #pragma unroll
-      for (int k = 0; k < CONV_MAXK; ++k)
-        if (k < K) {
+      for (int u = 0; u < 4; ++u) {
+        const int l = lb + u;
+        if (l >= l1) break;
+        const bf16x8 raw = raw4[u];
+        unpack8(raw, hist[K - 1]);
+        float acc[8];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) acc[j] = fmaf(hist[k][j], wv[k][j], acc[j]);
+        for (int j = 0; j < 8; ++j) acc[j] = bv[j];
+#pragma unroll
+        for (int k = 0; k < CONV_MAXK; ++k)
+          if (k < K) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = fmaf(hist[k][j], wv[k][j], acc[j]);
+          }
+        if (act) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] = silu_f(acc[j]);
         }
-      if (act) {
+        st8(y + ((long long)b * L + l) * C + c, pack8(acc));
+        if (state_out && l >= L - (K - 1)) st8(state_out + ((long long)b * (K - 1) + (l - (L - (K - 1)))) * C + c, raw);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] = silu_f(acc[j]);
+        for (int i = 0; i < CONV_MAXK - 1; ++i)
+          if (i < K - 1) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) hist[i][j] = hist[i + 1][j];
+          }
       }
-      st8(y + ((long long)b * L + l) * C + c, pack8(acc));
-      if (state_out && l >= L - (K - 1)) st8(state_out + ((long long)b * (K - 1) + (l - (L - (K - 1)))) * C + c, raw);
-#pragma unroll
-      for (int i = 0; i < CONV_MAXK - 1; ++i)
-        if (i < K - 1) {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) hist[i][j] = hist[i + 1][j];
-        }
     }
   }
 }
 
-// dx and per-CTA partials of dw / dbias. A CTA is 32 channel vectors (one per lane: 512 contiguous bytes per row) by
-// 8 runs of CONV_BTL consecutive positions (one per warp). A thread walks its run once: the last K inputs and the
-// last K pre-activation gradients slide through registers, so every x and dy vector is loaded once (plus the K-1
-// row overlap between runs) and dx is stored once. The 8 warps add their dw / db into shared memory and the CTA
+// dx and per-CTA partials of dw / dbias. A CTA is 32 channel groups of 4 (one per lane: 256 contiguous bytes per
+// row) by 8 runs of CONV_BTL consecutive positions (one per warp). A thread walks its run once: the last K inputs and
+// the last K pre-activation gradients slide through registers, so every x and dy value is loaded once (plus the K-1
+// row overlap between runs) and dx is stored once. Four channels per thread keep the kernel near 100 registers (two
+// CTAs per SM); with eight it needed 205 and ran at one. The 8 warps add their dw / db into shared memory and the CTA
 // writes one partial row; conv1d_reduce_partials sums the rows.
 constexpr int CONV_BTL = 16;
+constexpr int CONV_BV = 4;
+__device__ __forceinline__ void ld4(const __nv_bfloat16* p, float (&f)[CONV_BV]) {
+  const uint2 r = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.y));
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+}
+__device__ __forceinline__ void st4(__nv_bfloat16* p, const float (&f)[CONV_BV]) {
+  const __nv_bfloat162 a = __floats2bfloat162_rn(f[0], f[1]), b = __floats2bfloat162_rn(f[2], f[3]);
+  uint2 r;
+  r.x = *reinterpret_cast<const uint32_t*>(&a);
+  r.y = *reinterpret_cast<const uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = r;
+}
 template <int K>
-__global__ void __launch_bounds__(256) conv1d_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
-                                                         const __nv_bfloat16* __restrict__ x,
-                                                         const __nv_bfloat16* __restrict__ prev,
-                                                         const __nv_bfloat16* __restrict__ w,
-                                                         const __nv_bfloat16* __restrict__ bias,
-                                                         __nv_bfloat16* __restrict__ dx, float* __restrict__ partial,
-                                                         int B, int L, int C, int act, long long xld) {
-  __shared__ float s_acc[32][(CONV_MAXK + 1) * 8 + 1];
+__global__ void __launch_bounds__(256, 2) conv1d_bwd_kernel(const __nv_bfloat16* __restrict__ dy,
+                                                            const __nv_bfloat16* __restrict__ x,
+                                                            const __nv_bfloat16* __restrict__ prev,
+                                                            const __nv_bfloat16* __restrict__ w,
+                                                            const __nv_bfloat16* __restrict__ bias,
+                                                            __nv_bfloat16* __restrict__ dx, float* __restrict__ partial,
+                                                            int B, int L, int C, int act, long long xld) {
+  constexpr int V = CONV_BV;
+  __shared__ float s_acc[32][(CONV_MAXK + 1) * V + 1];
   const int lane = threadIdx.x & 31, sub = threadIdx.x >> 5;
-  const int cv = C >> 3;
+  const int cv = C / V;
   const int v = blockIdx.x * 32 + lane;
   const bool live = v < cv;
-  const int c = v * 8;
-  for (int i = threadIdx.x; i < 32 * ((CONV_MAXK + 1) * 8 + 1); i += 256) (&s_acc[0][0])[i] = 0.f;
+  const int c = v * V;
+  for (int i = threadIdx.x; i < 32 * ((CONV_MAXK + 1) * V + 1); i += 256) (&s_acc[0][0])[i] = 0.f;
   __syncthreads();
   if (live) {
-    float wv[K][8], bv[8], dwacc[K][8], dbacc[8];
+    float wv[K][V], bv[V], dwacc[K][V], dbacc[V];
 #pragma unroll
     for (int k = 0; k < K; ++k)
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
+      for (int j = 0; j < V; ++j) {
         wv[k][j] = __bfloat162float(w[(c + j) * K + k]);
         dwacc[k][j] = 0.f;
       }
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
+    for (int j = 0; j < V; ++j) {
       bv[j] = bias ? __bfloat162float(bias[c + j]) : 0.f;
       dbacc[j] = 0.f;
     }
@@ -129,32 +154,32 @@ __global__ void __launch_bounds__(256) conv1d_bwd_kernel(const __nv_bfloat16* __
     for (int ch = blockIdx.y * 8 + sub; ch < nchunks; ch += gridDim.y * 8) {
       const int b = ch / lchunks, l0 = (ch % lchunks) * CONV_BTL;
       const int lend = min(l0 + CONV_BTL, L);
-      float xh[K][8], dph[K][8];
+      float xh[K][V], dph[K][V];
 #pragma unroll
       for (int i = 0; i < K; ++i)
 #pragma unroll
-        for (int j = 0; j < 8; ++j) xh[i][j] = dph[i][j] = 0.f;
+        for (int j = 0; j < V; ++j) xh[i][j] = dph[i][j] = 0.f;
 #pragma unroll
       for (int i = 1; i < K; ++i) {
         const int ls = l0 - K + i;
-        if (ls >= 0) unpack8(ld8(x + ((long long)b * L + ls) * xld + c), xh[i]);
-        else if (prev) unpack8(ld8(prev + ((long long)b * (K - 1) + (K - 1 + ls)) * C + c), xh[i]);
+        if (ls >= 0) ld4(x + ((long long)b * L + ls) * xld + c, xh[i]);
+        else if (prev) ld4(prev + ((long long)b * (K - 1) + (K - 1 + ls)) * C + c, xh[i]);
       }
 #pragma unroll 4
       for (int l = l0; l < lend + K - 1; ++l) {
 #pragma unroll
         for (int i = 0; i + 1 < K; ++i)
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
+          for (int j = 0; j < V; ++j) {
             xh[i][j] = xh[i + 1][j];
             dph[i][j] = dph[i + 1][j];
           }
         if (l < L) {
-          unpack8(ld8(x + ((long long)b * L + l) * xld + c), xh[K - 1]);
-          unpack8(ld8(dy + ((long long)b * L + l) * C + c), dph[K - 1]);
+          ld4(x + ((long long)b * L + l) * xld + c, xh[K - 1]);
+          ld4(dy + ((long long)b * L + l) * C + c, dph[K - 1]);
           if (act) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
+            for (int j = 0; j < V; ++j) {
               float pre = bv[j];
 #pragma unroll
               for (int k = 0; k < K; ++k) pre += xh[k][j] * wv[k][j];
@@ -163,11 +188,11 @@ __global__ void __launch_bounds__(256) conv1d_bwd_kernel(const __nv_bfloat16* __
           }
         } else {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) xh[K - 1][j] = dph[K - 1][j] = 0.f;
+          for (int j = 0; j < V; ++j) xh[K - 1][j] = dph[K - 1][j] = 0.f;
         }
         if (l < lend) {   // this run's own rows: dw[k] += dpre[l] x[l-(K-1)+k], db += dpre[l]
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
+          for (int j = 0; j < V; ++j) {
             dbacc[j] += dph[K - 1][j];
 #pragma unroll
             for (int k = 0; k < K; ++k) dwacc[k][j] += dph[K - 1][j] * xh[k][j];
@@ -175,32 +200,32 @@ __global__ void __launch_bounds__(256) conv1d_bwd_kernel(const __nv_bfloat16* __
         }
         const int lo = l - (K - 1);   // dx[lo] = sum_k w[k] dpre[lo + (K-1) - k]
         if (lo >= l0) {
-          float dxa[8];
+          float dxa[V];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
+          for (int j = 0; j < V; ++j) {
             float a = 0.f;
 #pragma unroll
             for (int k = 0; k < K; ++k) a += wv[k][j] * dph[K - 1 - k][j];
             dxa[j] = a;
           }
-          st8(dx + ((long long)b * L + lo) * C + c, pack8(dxa));
+          st4(dx + ((long long)b * L + lo) * C + c, dxa);
         }
       }
     }
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
+    for (int j = 0; j < V; ++j) {
 #pragma unroll
-      for (int k = 0; k < K; ++k) atomicAdd(&s_acc[lane][k * 8 + j], dwacc[k][j]);
-      atomicAdd(&s_acc[lane][K * 8 + j], dbacc[j]);
+      for (int k = 0; k < K; ++k) atomicAdd(&s_acc[lane][k * V + j], dwacc[k][j]);
+      atomicAdd(&s_acc[lane][K * V + j], dbacc[j]);
     }
   }
   __syncthreads();
   // partial layout: [part][(K+1) * C]: dw as [c][k] flattened (C*K) then db (C)
   float* pp = partial + (long long)blockIdx.y * (K + 1) * C;
-  for (int i = threadIdx.x; i < 32 * (K + 1) * 8; i += 256) {
-    const int ln = i / ((K + 1) * 8), r = i % ((K + 1) * 8);
-    const int k = r / 8, j = r % 8;
-    const int cc = (blockIdx.x * 32 + ln) * 8 + j;
+  for (int i = threadIdx.x; i < 32 * (K + 1) * V; i += 256) {
+    const int ln = i / ((K + 1) * V), r = i % ((K + 1) * V);
+    const int k = r / V, j = r % V;
+    const int cc = (blockIdx.x * 32 + ln) * V + j;
     if (cc >= C) continue;
     if (k < K) pp[(long long)cc * K + k] = s_acc[ln][r];
     else pp[(long long)C * K + cc] = s_acc[ln][r];
@@ -252,7 +277,7 @@ extern "C" int sx_conv1d_bwd(const void* dy, const void* x, const void* prev, co
   if (C % 8 || K > CONV_MAXK || K < 1 || xld % 8 || xld < C) return -1;
   if ((long long)B * L == 0) return 0;
   const int parts = sx_conv1d_bwd_parts(B, L);
-  const dim3 grid((C / 8 + 31) / 32, parts);
+  const dim3 grid((C / CONV_BV + 31) / 32, parts);
 #define SX_CONV_BWD(KK)                                                                                          \
   conv1d_bwd_kernel<KK><<<grid, 256, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,                  \
                                               (const __nv_bfloat16*)prev, (const __nv_bfloat16*)w,                \

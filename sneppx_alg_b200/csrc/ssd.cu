@@ -161,12 +161,21 @@ __global__ void __launch_bounds__(256) ssd_state_bwd_kernel(const float* __restr
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// Token-major helpers on [rows = tokens*heads][P]: one warp per row group, 8 elements per lane.
-// out = a * scale[row] (bf16 out); optional second output dot[row] = sum_p a * b * scale[row] (b fp32).
+// Layouts of the [tokens, heads, P] tensors. Token-major row r = (bc * Q + q) * H + h. The operands of the GEMMs that
+// fold the heads of a B / C group into one matrix dimension are kept group-first, [bc][G][Q][H/G][P], so that
+// (bc, group) is one linear batch index; gf_row maps a token-major row to its group-first row (the identity for G = 1).
+__device__ __forceinline__ long long gf_row(long long r, int H, int Q, int G) {
+  const int rep = H / G;
+  const int h = (int)(r % H);
+  const long long t = r / H;
+  return (((t / Q) * G + h / rep) * Q + (t % Q)) * rep + h % rep;
+}
+
+// out (group-first) = a (token-major, token stride ald) * scale[row]
 __global__ void __launch_bounds__(256) ssd_scale_rows_kernel(const __nv_bfloat16* __restrict__ a,
                                                              const float* __restrict__ scale,
                                                              __nv_bfloat16* __restrict__ out, long long rows, int P,
-                                                             int H, long long ald) {
+                                                             int H, long long ald, int Q, int G) {
   const int vp = P >> 3;
   const long long total = rows * vp;
   for (long long i = blockIdx.x * 256ll + threadIdx.x; i < total; i += gridDim.x * 256ll) {
@@ -176,7 +185,7 @@ __global__ void __launch_bounds__(256) ssd_scale_rows_kernel(const __nv_bfloat16
     const float s = scale[r];
 #pragma unroll
     for (int j = 0; j < 8; ++j) f[j] *= s;
-    st8(out + i * 8, pack8(f));
+    st8(out + (gf_row(r, H, Q, G) * vp + i % vp) * 8, pack8(f));
   }
 }
 
@@ -195,7 +204,7 @@ __global__ void __launch_bounds__(256) ssd_combine_kernel(const __nv_bfloat16* _
                                                           const __nv_bfloat16* __restrict__ x,
                                                           const float* __restrict__ E, const float* __restrict__ D,
                                                           __nv_bfloat16* __restrict__ y, long long rows, int H, int Q,
-                                                          int vp, long long xld) {
+                                                          int vp, long long xld, int G) {
   const long long total = rows * vp;
   for (long long i = blockIdx.x * 256ll + threadIdx.x; i < total; i += gridDim.x * 256ll) {
     const long long r = i / vp;
@@ -205,7 +214,7 @@ __global__ void __launch_bounds__(256) ssd_combine_kernel(const __nv_bfloat16* _
     const long long hf = ((t / Q) * H + h) * Q + (t % Q);
     float a[8], b[8], xv[8], o[8];
     unpack8(ld8(Yi + (hf * vp + pv) * 8), a);
-    unpack8(ld8(Yoff + i * 8), b);
+    unpack8(ld8(Yoff + (gf_row(r, H, Q, G) * vp + pv) * 8), b);
     unpack8(ld8(x + t * xld + (h * vp + pv) * 8), xv);
     const float e = E[r], d = D ? D[h] : 0.f;
 #pragma unroll
@@ -221,7 +230,7 @@ __global__ void __launch_bounds__(256) ssd_bwd_rows1_kernel(const __nv_bfloat16*
                                                             const float* __restrict__ E,
                                                             __nv_bfloat16* __restrict__ dye, float* __restrict__ dcs,
                                                             float* __restrict__ ddrow, long long rows, int vp,
-                                                            int H, long long xld) {
+                                                            int H, long long xld, int Q, int G) {
   const long long total = rows * vp;
   const long long span = ((total + 255) / 256) * 256;   // whole warps stay in the loop together for the shuffles
   for (long long i = blockIdx.x * 256ll + threadIdx.x; i < span; i += gridDim.x * 256ll) {
@@ -231,7 +240,8 @@ __global__ void __launch_bounds__(256) ssd_bwd_rows1_kernel(const __nv_bfloat16*
     if (live) {
       unpack8(ld8(dy + i * 8), g);
       unpack8(ld8(x + (r / H) * xld + (i % ((long long)H * vp)) * 8), xv);
-      unpack8(ld8(Yoff + i * 8), yo);
+      const long long gi = (gf_row(r, H, Q, G) * vp + i % vp) * 8;
+      unpack8(ld8(Yoff + gi), yo);
       const float e = E[r];
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
@@ -239,7 +249,7 @@ __global__ void __launch_bounds__(256) ssd_bwd_rows1_kernel(const __nv_bfloat16*
         s1 += o[j] * yo[j];
         s2 += g[j] * xv[j];
       }
-      st8(dye + i * 8, pack8(o));
+      st8(dye + gi, pack8(o));
     }
     s1 = seg_sum(s1, vp);
     s2 = seg_sum(s2, vp);
@@ -257,7 +267,8 @@ __global__ void __launch_bounds__(256) ssd_bwd_rows2_kernel(const __nv_bfloat16*
                                                             const __nv_bfloat16* __restrict__ dxi,
                                                             const float* __restrict__ decay, const float* __restrict__ D,
                                                             __nv_bfloat16* __restrict__ dx, float* __restrict__ ddecay,
-                                                            long long rows, int H, int Q, int vp, long long xld) {
+                                                            long long rows, int H, int Q, int vp, long long xld,
+                                                            int G) {
   const long long total = rows * vp;
   const long long span = ((total + 255) / 256) * 256;
   for (long long i = blockIdx.x * 256ll + threadIdx.x; i < span; i += gridDim.x * 256ll) {
@@ -272,7 +283,7 @@ __global__ void __launch_bounds__(256) ssd_bwd_rows2_kernel(const __nv_bfloat16*
       float g[8], xv[8], a[8], b[8], o[8];
       unpack8(ld8(dy + i * 8), g);
       unpack8(ld8(x + t * xld + (h * vp + pv) * 8), xv);
-      unpack8(ld8(dxw + i * 8), a);
+      unpack8(ld8(dxw + (gf_row(r, H, Q, G) * vp + pv) * 8), a);
       unpack8(ld8(dxi + (hf * vp + pv) * 8), b);
       const float dc = decay[r], d = D ? D[h] : 0.f;
 #pragma unroll
@@ -389,13 +400,13 @@ extern "C" int sx_ssd_state_bwd(const void* dHprev, const void* tot, const void*
 
 // `ald` (and `xld` below): elements between consecutive tokens of the bf16 input, >= H * P, a multiple of 8.
 extern "C" int sx_ssd_scale_rows(const void* a, const void* scale, void* out, long long rows, int P, int H,
-                                 long long ald, cudaStream_t st) {
-  if (P % 8 || ald % 8) return -1;
+                                 long long ald, int Q, int G, cudaStream_t st) {
+  if (P % 8 || ald % 8 || H % G) return -1;
   const long long total = rows * (P / 8);
   if (total == 0) return 0;
   const long long nb = (total + 255) / 256;
   ssd_scale_rows_kernel<<<(unsigned)(nb < 148 * 16 ? nb : 148 * 16), 256, 0, st>>>(
-      (const __nv_bfloat16*)a, (const float*)scale, (__nv_bfloat16*)out, rows, P, H, ald);
+      (const __nv_bfloat16*)a, (const float*)scale, (__nv_bfloat16*)out, rows, P, H, ald, Q, G);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
@@ -406,35 +417,36 @@ static unsigned row_grid(long long total) {
 }
 
 extern "C" int sx_ssd_combine(const void* Yi, const void* Yoff, const void* x, const void* E, const void* D, void* y,
-                              long long rows, int H, int Q, int P, long long xld, cudaStream_t st) {
-  if (!vp_ok(P) || xld % 8) return -1;
+                              long long rows, int H, int Q, int P, long long xld, int G, cudaStream_t st) {
+  if (!vp_ok(P) || xld % 8 || H % G) return -1;
   if (rows == 0) return 0;
   ssd_combine_kernel<<<row_grid(rows * (P / 8)), 256, 0, st>>>((const __nv_bfloat16*)Yi, (const __nv_bfloat16*)Yoff,
                                                                 (const __nv_bfloat16*)x, (const float*)E,
-                                                                (const float*)D, (__nv_bfloat16*)y, rows, H, Q, P / 8, xld);
+                                                                (const float*)D, (__nv_bfloat16*)y, rows, H, Q, P / 8, xld, G);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
 extern "C" int sx_ssd_bwd_rows1(const void* dy, const void* x, const void* Yoff, const void* E, void* dye, void* dcs,
-                                void* ddrow, long long rows, int P, int H, long long xld, cudaStream_t st) {
-  if (!vp_ok(P) || xld % 8) return -1;
+                                void* ddrow, long long rows, int P, int H, long long xld, int Q, int G,
+                                cudaStream_t st) {
+  if (!vp_ok(P) || xld % 8 || H % G) return -1;
   if (rows == 0) return 0;
   ssd_bwd_rows1_kernel<<<row_grid(rows * (P / 8)), 256, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
                                                                   (const __nv_bfloat16*)Yoff, (const float*)E,
                                                                   (__nv_bfloat16*)dye, (float*)dcs, (float*)ddrow, rows,
-                                                                  P / 8, H, xld);
+                                                                  P / 8, H, xld, Q, G);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 
 extern "C" int sx_ssd_bwd_rows2(const void* dy, const void* x, const void* dxw, const void* dxi, const void* decay,
                                 const void* D, void* dx, void* ddecay, long long rows, int H, int Q, int P,
-                                long long xld, cudaStream_t st) {
-  if (!vp_ok(P) || xld % 8) return -1;
+                                long long xld, int G, cudaStream_t st) {
+  if (!vp_ok(P) || xld % 8 || H % G) return -1;
   if (rows == 0) return 0;
   ssd_bwd_rows2_kernel<<<row_grid(rows * (P / 8)), 256, 0, st>>>(
       (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)dxw, (const __nv_bfloat16*)dxi,
       (const float*)decay,
-      (const float*)D, (__nv_bfloat16*)dx, (float*)ddecay, rows, H, Q, P / 8, xld);
+      (const float*)D, (__nv_bfloat16*)dx, (float*)ddecay, rows, H, Q, P / 8, xld, G);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

@@ -259,14 +259,31 @@ def _state_bwd(dHprev, tot, Hprev, dfinal):
     return torch.stack(dS, dim=1).to(Hprev.dtype), torch.stack(dtot, dim=1), run
 
 
-def _scale_rows(t5, scale, cdt):
-    """t5 [B,nc,Q,H,P] times scale [B,nc,Q,H] (fp32), rounded to the compute dtype."""
-    if t5.is_cuda and t5.dtype == torch.bfloat16 and cdt == torch.bfloat16 and _lib.available() and t5.shape[-1] % 8 == 0:
-        out = torch.empty(t5.shape, dtype=cdt, device=t5.device)
+def _to_gf(t5, G):
+    """Token-major [B,nc,Q,H,P] -> group-first [B*nc*G, Q, (H/G)*P] (a view of the same memory for G == 1)."""
+    B_, nc, Q, H, P = t5.shape
+    if G == 1:
+        return t5.reshape(B_ * nc, Q, H * P)
+    return t5.reshape(B_, nc, Q, G, (H // G) * P).permute(0, 1, 3, 2, 4).reshape(B_ * nc * G, Q, (H // G) * P)
+
+
+def _from_gf(t3, shape5, G):
+    """Inverse of ``_to_gf``."""
+    B_, nc, Q, H, P = shape5
+    if G == 1:
+        return t3.reshape(shape5)
+    return t3.reshape(B_, nc, G, Q, (H // G) * P).permute(0, 1, 3, 2, 4).reshape(shape5)
+
+
+def _scale_rows(t5, scale, cdt, G):
+    """t5 [B,nc,Q,H,P] times scale [B,nc,Q,H] (fp32), rounded to the compute dtype, in group-first layout."""
+    B_, nc, Q, H, P = t5.shape
+    if t5.is_cuda and t5.dtype == torch.bfloat16 and cdt == torch.bfloat16 and _lib.available() and P % 8 == 0:
+        out = torch.empty(B_ * nc * G, Q, (H // G) * P, dtype=cdt, device=t5.device)
         _lib.call("sx_ssd_scale_rows", ptr(t5), ptr(scale.contiguous()), ptr(out), c_ll(scale.numel()),
-                  c_int(t5.shape[-1]), c_int(t5.shape[-2]), c_ll(t5.stride(2)), stream())
+                  c_int(P), c_int(H), c_ll(t5.stride(2)), c_int(Q), c_int(G), stream())
         return out
-    return (t5.float() * scale[..., None]).to(cdt)
+    return _to_gf((t5.float() * scale[..., None]).to(cdt), G)
 
 
 def _rows_kernel_ok(t5, cdt):
@@ -275,45 +292,47 @@ def _rows_kernel_ok(t5, cdt):
             and (P // 8) & (P // 8 - 1) == 0 and P <= 256)
 
 
-def _combine(Yi, Yoff, x5, E, D, cdt):
-    """y = Yi (heads-first [B,nc,H,Q,P]) + E Yoff + D x on the token-major layout [B,nc,Q,H,P]."""
+def _combine(Yi, Yoff, x5, E, D, cdt, G):
+    """y = Yi (heads-first [B,nc,H,Q,P]) + E Yoff (group-first) + D x on the token-major layout [B,nc,Q,H,P]."""
     B_, nc, Q, H, P = x5.shape
     if _rows_kernel_ok(x5, cdt):
         y = torch.empty(x5.shape, dtype=cdt, device=x5.device)
         _lib.call("sx_ssd_combine", ptr(Yi), ptr(Yoff), ptr(x5), ptr(E), ptr(D.float().contiguous() if D is not None else None),
-                  ptr(y), c_ll(B_ * nc * Q * H), c_int(H), c_int(Q), c_int(P), c_ll(x5.stride(2)), stream())
+                  ptr(y), c_ll(B_ * nc * Q * H), c_int(H), c_int(Q), c_int(P), c_ll(x5.stride(2)), c_int(G), stream())
         return y
-    y = Yi.float().permute(0, 1, 3, 2, 4) + Yoff.float() * E[..., None]
+    y = Yi.float().permute(0, 1, 3, 2, 4) + _from_gf(Yoff, x5.shape, G).float() * E[..., None]
     if D is not None:
         y = y + x5.float() * D.float().view(H, 1)
     return y.to(cdt)
 
 
-def _bwd_rows1(dy5, x5, Yoff, E, cdt):
-    """dye = dy E (compute dtype); dcs = sum_p dy E Yoff; ddrow = sum_p dy x."""
+def _bwd_rows1(dy5, x5, Yoff, E, cdt, G):
+    """dye = dy E (compute dtype, group-first); dcs = sum_p dy E Yoff; ddrow = sum_p dy x. Yoff is group-first."""
     if _rows_kernel_ok(x5, cdt) and dy5.dtype == cdt:
-        dye = torch.empty_like(dy5)
+        dye = torch.empty_like(Yoff)
         dcs = torch.empty(E.shape, dtype=torch.float32, device=E.device)
         ddrow = torch.empty_like(dcs)
         _lib.call("sx_ssd_bwd_rows1", ptr(dy5), ptr(x5), ptr(Yoff), ptr(E), ptr(dye), ptr(dcs), ptr(ddrow),
-                  c_ll(E.numel()), c_int(x5.shape[-1]), c_int(x5.shape[-2]), c_ll(x5.stride(2)), stream())
+                  c_ll(E.numel()), c_int(x5.shape[-1]), c_int(x5.shape[-2]), c_ll(x5.stride(2)), c_int(x5.shape[2]),
+                  c_int(G), stream())
         return dye, dcs, ddrow
     dyf = dy5.float()
     dyeE = dyf * E[..., None]
-    return dyeE.to(cdt), (dyeE * Yoff.float()).sum(-1), (dyf * x5.float()).sum(-1)
+    return (_to_gf(dyeE.to(cdt), G), (dyeE * _from_gf(Yoff, x5.shape, G).float()).sum(-1),
+            (dyf * x5.float()).sum(-1))
 
 
-def _bwd_rows2(dy5, x5, dxw5, dxi, decay, D, cdt):
-    """dx = D dy + decay dxw + dxi (heads-first [B,nc,H,Q,P]); ddecay = sum_p dxw x."""
+def _bwd_rows2(dy5, x5, dxw, dxi, decay, D, cdt, G):
+    """dx = D dy + decay dxw (group-first) + dxi (heads-first [B,nc,H,Q,P]); ddecay = sum_p dxw x."""
     B_, nc, Q, H, P = x5.shape
     if _rows_kernel_ok(x5, cdt) and dy5.dtype == cdt:
         dx = torch.empty(x5.shape, dtype=cdt, device=x5.device)
         ddecay = torch.empty(decay.shape, dtype=torch.float32, device=decay.device)
-        _lib.call("sx_ssd_bwd_rows2", ptr(dy5), ptr(x5), ptr(dxw5), ptr(dxi), ptr(decay),
+        _lib.call("sx_ssd_bwd_rows2", ptr(dy5), ptr(x5), ptr(dxw), ptr(dxi), ptr(decay),
                   ptr(D.float().contiguous() if D is not None else None), ptr(dx), ptr(ddecay), c_ll(decay.numel()),
-                  c_int(H), c_int(Q), c_int(P), c_ll(x5.stride(2)), stream())
+                  c_int(H), c_int(Q), c_int(P), c_ll(x5.stride(2)), c_int(G), stream())
         return dx, ddecay
-    dxw5 = dxw5.float()
+    dxw5 = _from_gf(dxw, x5.shape, G).float()
     dx = dxw5 * decay[..., None] + dxi.float().permute(0, 1, 3, 2, 4)
     if D is not None:
         dx = dx + dy5.float() * D.float().view(H, 1)
@@ -354,11 +373,11 @@ class _Chunks:
         self.eL = torch.exp(self.cs[:, :, -1:, :] - self.cs)                     # exp(cs_last - cs_s)
         self.decay = self.eL * self.dtf
         self.tot = torch.exp(self.cs[:, :, -1, :]).contiguous()                  # [B,nc,H]
-        self.xw = _scale_rows(self.x5, self.decay, self.cdt).view(B_ * nc, Q, H * P)
+        self.xw = _scale_rows(self.x5, self.decay, self.cdt, G)               # group-first [B*nc*G, Q, rep*P]
 
-    def gs(self, g):
-        w = self.rep * self.P
-        return slice(g * w, (g + 1) * w)
+    def by_group(self, t):
+        """[.., H*P, N] states or [B*nc, G, Q, N] projections as one batch of (chunk, group) matrices."""
+        return t.reshape(self.Bsz * self.nc * self.G, -1, self.N)
 
     def heads_first(self, t5):
         """[B,nc,Q,H,P] -> contiguous [B*nc*H, Q, P]."""
@@ -371,11 +390,7 @@ class _Chunks:
 
     def y_off(self, Hprev):
         B_, nc, Q, H, P, N = self.Bsz, self.nc, self.Q, self.H, self.P, self.N
-        out = torch.empty(B_ * nc, Q, H * P, dtype=self.cdt, device=Hprev.device)
-        Hp = Hprev.view(B_ * nc, H * P, N)
-        for g in range(self.G):
-            gemm(self.Cc[:, g], Hp[:, self.gs(g)], out=out[:, :, self.gs(g)])
-        return out.view(B_, nc, Q, H, P)
+        return gemm(self.by_group(self.Cc), self.by_group(Hprev))              # group-first [B*nc*G, Q, rep*P]
 
 
 class _SSDFn(torch.autograd.Function):
@@ -389,11 +404,9 @@ class _SSDFn(torch.autograd.Function):
         B_, nc, Q, H, P, N = k.Bsz, k.nc, k.Q, k.H, k.P, k.N
         M = _build_m(k.CB, k.csh, k.dth, k.rep, k.cdt)
         Yi = gemm(M.view(-1, Q, Q), k.heads_first(k.x5), b_mn=True).view(B_, nc, H, Q, P)
-        S = torch.empty(B_ * nc, H * P, N, dtype=torch.float32, device=x.device)
-        for g in range(k.G):
-            gemm(k.xw[:, :, k.gs(g)], k.Bc[:, g], a_mn=True, b_mn=True, out=S[:, k.gs(g)])
+        S = gemm(k.xw, k.by_group(k.Bc), a_mn=True, b_mn=True, out_dtype=torch.float32)   # [B*nc*G, rep*P, N]
         Hprev, final = _state_fwd(S.view(B_, nc, H, P, N), k.tot, init_state, k.cdt)
-        y = _combine(Yi, k.y_off(Hprev), k.x5, torch.exp(k.cs), D, k.cdt)
+        y = _combine(Yi, k.y_off(Hprev), k.x5, torch.exp(k.cs), D, k.cdt, k.G)
         ctx.save_for_backward(x, dt, A, Bm, Cm, D, Hprev)
         ctx.chunk = chunk
         ctx.has_init = init_state is not None
@@ -411,33 +424,25 @@ class _SSDFn(torch.autograd.Function):
             dy = F.pad(dy, (0, 0, 0, 0, 0, k.pad))
         dy5 = dy.to(cdt).contiguous().view(B_, nc, Q, H, P)
         # ---- contribution of earlier chunks: y_off = exp(cs) C H_prev^T
-        dye, dcs, ddrow = _bwd_rows1(dy5, k.x5, k.y_off(Hprev), torch.exp(k.cs), cdt)
+        dye, dcs, ddrow = _bwd_rows1(dy5, k.x5, k.y_off(Hprev), torch.exp(k.cs), cdt, G)
         dD = ddrow.sum((0, 1, 2)) if D is not None else None
-        dye = dye.view(B_ * nc, Q, H * P)
-        Hp = Hprev.view(B_ * nc, H * P, N)
-        dC = torch.empty(B_ * nc, G, Q, N, dtype=torch.float32, device=dev)
-        dHprev = torch.empty(B_ * nc, H * P, N, dtype=torch.float32, device=dev)
-        for g in range(G):
-            gemm(dye[:, :, k.gs(g)], Hp[:, k.gs(g)], b_mn=True, out=dC[:, g])
-            gemm(dye[:, :, k.gs(g)], k.Cc[:, g], a_mn=True, b_mn=True, out=dHprev[:, k.gs(g)])
+        Hp, Cg, Bg = k.by_group(Hprev), k.by_group(k.Cc), k.by_group(k.Bc)
+        dC = gemm(dye, Hp, b_mn=True, out_dtype=torch.float32).view(B_ * nc, G, Q, N)
+        dHprev = gemm(dye, Cg, a_mn=True, b_mn=True, out_dtype=torch.float32)     # [B*nc*G, rep*P, N]
         # ---- chunk-to-chunk recurrence, reversed
         dS, dtot, dinit = _state_bwd(dHprev.view(B_, nc, H, P, N), k.tot, Hprev, dfinal)
         dcs_last = dtot * k.tot                                                  # [B,nc,H]
         # ---- chunk states S = (x o decay)^T B
-        dSb = dS.view(B_ * nc, H * P, N)
-        dxw = torch.empty(B_ * nc, Q, H * P, dtype=cdt, device=dev)
-        dB = torch.empty(B_ * nc, G, Q, N, dtype=torch.float32, device=dev)
-        for g in range(G):
-            gemm(k.Bc[:, g], dSb[:, k.gs(g)], out=dxw[:, :, k.gs(g)])
-            gemm(k.xw[:, :, k.gs(g)], dSb[:, k.gs(g)], b_mn=True, out=dB[:, g])
-        dxw = dxw.view(B_, nc, Q, H, P)
+        dSb = k.by_group(dS)
+        dxw = gemm(Bg, dSb)                                                      # group-first [B*nc*G, Q, rep*P]
+        dB = gemm(k.xw, dSb, b_mn=True, out_dtype=torch.float32).view(B_ * nc, G, Q, N)
         # ---- quadratic term within the chunk
         dyh = k.heads_first(dy5)
         xh = k.heads_first(k.x5)
         dM = gemm(dyh, xh)                                                       # [n,Q,Q]
         M, dGh, rowW, colU = _bwd_qq(dM.view(B_, nc, H, Q, Q), k.CB, k.csh, k.dth, k.rep, cdt)
         dxi = gemm(M.view(-1, Q, Q), dyh, a_mn=True, b_mn=True).view(B_, nc, H, Q, P)
-        dx, ddecay = _bwd_rows2(dy5, k.x5, dxw, dxi, k.decay, D, cdt)
+        dx, ddecay = _bwd_rows2(dy5, k.x5, dxw, dxi, k.decay, D, cdt, G)
         gdec = ddecay * k.decay
         dcs_last = dcs_last + gdec.sum(2)
         dcs = dcs - gdec + (rowW - colU * k.dth).permute(0, 1, 3, 2)
