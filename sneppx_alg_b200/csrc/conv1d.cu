@@ -137,18 +137,27 @@ __global__ void __launch_bounds__(256, 2) conv1d_bwd_kernel(const __nv_bfloat16*
   __syncthreads();
   if (live) {
     float wv[K][V], bv[V], dwacc[K][V], dbacc[V];
+    if (K == 4) {   // a channel's four taps are 8 contiguous bytes
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        float t[4];
+        ld4(w + (c + j) * 4, t);
+#pragma unroll
+        for (int k = 0; k < K; ++k) wv[k][j] = t[k];
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < K; ++k)
+#pragma unroll
+        for (int j = 0; j < V; ++j) wv[k][j] = __bfloat162float(w[(c + j) * K + k]);
+    }
 #pragma unroll
     for (int k = 0; k < K; ++k)
 #pragma unroll
-      for (int j = 0; j < V; ++j) {
-        wv[k][j] = __bfloat162float(w[(c + j) * K + k]);
-        dwacc[k][j] = 0.f;
-      }
+      for (int j = 0; j < V; ++j) dwacc[k][j] = 0.f;
 #pragma unroll
-    for (int j = 0; j < V; ++j) {
-      bv[j] = bias ? __bfloat162float(bias[c + j]) : 0.f;
-      dbacc[j] = 0.f;
-    }
+    for (int j = 0; j < V; ++j) dbacc[j] = bv[j] = 0.f;
+    if (bias) ld4(bias + c, bv);
     const int lchunks = (L + CONV_BTL - 1) / CONV_BTL;
     const int nchunks = B * lchunks;
     for (int ch = blockIdx.y * 8 + sub; ch < nchunks; ch += gridDim.y * 8) {
@@ -232,12 +241,14 @@ __global__ void __launch_bounds__(256, 2) conv1d_bwd_kernel(const __nv_bfloat16*
   }
 }
 
+// out must be zero: blockIdx.y owns every gridDim.y-th partial row and adds its sum with one atomic per element.
 __global__ void conv1d_reduce_partials(const float* __restrict__ part, int nparts, int n, float* __restrict__ out) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   float s = 0.f;
-  for (int p = 0; p < nparts; ++p) s += part[(long long)p * n + i];
-  out[i] = s;
+#pragma unroll 4
+  for (int p = blockIdx.y; p < nparts; p += gridDim.y) s += part[(long long)p * n + i];
+  atomicAdd(out + i, s);
 }
 
 }  // namespace sx
@@ -265,9 +276,11 @@ extern "C" int sx_conv1d_fwd(const void* x, const void* prev, const void* w, con
 
 // Number of partial rows the backward kernel writes for B sequences of L tokens.
 extern "C" int sx_conv1d_bwd_parts(int B, int L) {
+  // four runs per warp (32 per CTA): the per-CTA prologue (taps, bias) and epilogue (partial row) cost about as much
+  // as one run
   const long long chunks = (long long)B * ((L + CONV_BTL - 1) / CONV_BTL);
-  const long long p = (chunks + 7) / 8;
-  return (int)(p < 1 ? 1 : (p > 1024 ? 1024 : p));
+  const long long p = (chunks + 31) / 32;
+  return (int)(p < 1 ? 1 : (p > 512 ? 512 : p));
 }
 
 // partial: scratch of sx_conv1d_bwd_parts(B, L) * (K+1) * C floats; dwdb: fp32 [(K+1)*C] = dw [C][K] then db [C].
@@ -290,6 +303,7 @@ extern "C" int sx_conv1d_bwd(const void* dy, const void* x, const void* prev, co
   }
 #undef SX_CONV_BWD
   const int n = (K + 1) * C;
-  conv1d_reduce_partials<<<(n + 255) / 256, 256, 0, st>>>(partial, parts, n, dwdb);
+  cudaMemsetAsync(dwdb, 0, sizeof(float) * n, st);
+  conv1d_reduce_partials<<<dim3((n + 255) / 256, parts < 8 ? parts : 8), 256, 0, st>>>(partial, parts, n, dwdb);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
