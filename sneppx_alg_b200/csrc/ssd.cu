@@ -33,9 +33,13 @@ __global__ void __launch_bounds__(256) ssd_qq_kernel(const __nv_bfloat16* __rest
   const int vpr = Q >> 3;
   const int cg = threadIdx.x % vpr;
   const int s0 = cg * 8;
-  float col[8];
+  float col[8], cs_s[8], dt_s[8];   // the thread's eight columns stay the same for every row it visits
 #pragma unroll
-  for (int j = 0; j < 8; ++j) col[j] = 0.f;
+  for (int j = 0; j < 8; ++j) {
+    col[j] = 0.f;
+    cs_s[j] = s_cs[s0 + j];
+    dt_s[j] = s_dt[s0 + j];
+  }
   const long long base = head * (long long)Q * Q;
   for (int l = threadIdx.x / vpr; l < Q; l += 256 / vpr) {
     const long long off = base + (long long)l * Q + s0;
@@ -53,14 +57,14 @@ __global__ void __launch_bounds__(256) ssd_qq_kernel(const __nv_bfloat16* __rest
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const int s = s0 + j;
-        const float le = s <= l ? __expf(csl - s_cs[s]) : 0.f;
-        const float lm = le * s_dt[s];
+        const float le = s <= l ? __expf(csl - cs_s[j]) : 0.f;
+        const float lm = le * dt_s[j];
         m[j] = c[j] * lm;
         if (BWD) {
           dg[j] = d[j] * lm;
           const float u = d[j] * c[j] * le;
           col[j] += u;
-          rw += u * s_dt[s];
+          rw += u * dt_s[j];
         }
       }
     }
@@ -116,14 +120,14 @@ __global__ void __launch_bounds__(256) ssd_state_fwd_kernel(const float* __restr
 }
 
 // Reverse: run = dfinal; for c = nc-1..0: dS_c = run; dtot_c = <run, H_c>; run = tot_c run + dHprev_c.
-// PN is covered by gridDim.x blocks of 2048 elements; each adds its part of dtot with one atomic per chunk.
+// PN is covered by gridDim.x blocks of 2048 elements; each warp adds its part of dtot with one atomic per chunk (no
+// block barrier inside the sequential loop).
 __global__ void __launch_bounds__(256) ssd_state_bwd_kernel(const float* __restrict__ dHprev,
                                                             const float* __restrict__ tot,
                                                             const __nv_bfloat16* __restrict__ Hprev,
                                                             const float* __restrict__ dfin,
                                                             __nv_bfloat16* __restrict__ dS, float* __restrict__ dtot,
                                                             float* __restrict__ dinit, int nc, int H, int PN) {
-  __shared__ float red[40];
   const int bh = blockIdx.y, b = bh / H, h = bh % H;
   const int e = (blockIdx.x * 256 + threadIdx.x) * 8;
   const bool live = e < PN;
@@ -135,6 +139,7 @@ __global__ void __launch_bounds__(256) ssd_state_bwd_kernel(const float* __restr
     const float4 c = *reinterpret_cast<const float4*>(dfin + (long long)bh * PN + e + 4);
     run[0] = a.x; run[1] = a.y; run[2] = a.z; run[3] = a.w; run[4] = c.x; run[5] = c.y; run[6] = c.z; run[7] = c.w;
   }
+#pragma unroll 2
   for (int c = nc - 1; c >= 0; --c) {
     const long long o = (((long long)b * nc + c) * H + h) * PN + e;
     float dot = 0.f;
@@ -150,8 +155,8 @@ __global__ void __launch_bounds__(256) ssd_state_bwd_kernel(const float* __restr
       run[0] = run[0] * t + g0.x; run[1] = run[1] * t + g0.y; run[2] = run[2] * t + g0.z; run[3] = run[3] * t + g0.w;
       run[4] = run[4] * t + g1.x; run[5] = run[5] * t + g1.y; run[6] = run[6] * t + g1.z; run[7] = run[7] * t + g1.w;
     }
-    dot = block_sum(dot, red);
-    if (threadIdx.x == 0) atomicAdd(dtot + ((long long)b * nc + c) * H + h, dot);
+    dot = warp_sum(dot);
+    if ((threadIdx.x & 31) == 0) atomicAdd(dtot + ((long long)b * nc + c) * H + h, dot);
   }
   if (live) {
     float4* f = reinterpret_cast<float4*>(dinit + (long long)bh * PN + e);
