@@ -369,11 +369,20 @@ class _Chunks:
         self.cs = self.csh.permute(0, 1, 3, 2).contiguous()                      # [B,nc,Q,H]
         self.Bc = Bm.to(self.cdt).reshape(B_, nc, Q, G, N).permute(0, 1, 3, 2, 4).contiguous().view(B_ * nc, G, Q, N)
         self.Cc = Cm.to(self.cdt).reshape(B_, nc, Q, G, N).permute(0, 1, 3, 2, 4).contiguous().view(B_ * nc, G, Q, N)
-        self.CB = gemm(self.Cc.view(-1, Q, N), self.Bc.view(-1, Q, N), out_dtype=torch.float32).view(B_, nc, G, Q, Q)
+        self._CB = None
         self.eL = torch.exp(self.cs[:, :, -1:, :] - self.cs)                     # exp(cs_last - cs_s)
         self.decay = self.eL * self.dtf
         self.tot = torch.exp(self.cs[:, :, -1, :]).contiguous()                  # [B,nc,H]
         self.xw = _scale_rows(self.x5, self.decay, self.cdt, G)               # group-first [B*nc*G, Q, rep*P]
+
+    @property
+    def CB(self):
+        """C B^T per (chunk, group), fp32 [B,nc,G,Q,Q] (built on first use: the fused forward kernel keeps it in TMEM)."""
+        if self._CB is None:
+            Q, N = self.Q, self.N
+            self._CB = gemm(self.Cc.view(-1, Q, N), self.Bc.view(-1, Q, N), out_dtype=torch.float32).view(
+                self.Bsz, self.nc, self.G, Q, Q)
+        return self._CB
 
     def by_group(self, t):
         """[.., H*P, N] states or [B*nc, G, Q, N] projections as one batch of (chunk, group) matrices."""
@@ -393,6 +402,34 @@ class _Chunks:
         return gemm(self.by_group(self.Cc), self.by_group(Hprev))              # group-first [B*nc*G, Q, rep*P]
 
 
+def _token_major_ok(t, inner):
+    """[B, L, G, inner] readable in place by TMA: unit inner stride, dense (G, inner), batch stride = L * token stride."""
+    return (t.stride(3) == 1 and t.stride(2) == inner and t.stride(0) == t.shape[1] * t.stride(1)
+            and t.stride(1) % 8 == 0 and t.data_ptr() % 16 == 0)
+
+
+def _chunk_fwd_fused(k, Bm, Cm, D, Hprev):
+    """Output stage of the scan in one tcgen05 kernel (csrc/ssd_fwd.cu): C B^T stays in TMEM across the heads of a
+    group, M = C B^T o L o dt goes to the M X product straight from TMEM and the C Hprev^T term, the exp(cs) scaling
+    and D x are applied in its epilogue. Covers chunk 128, state 128, headdim 64 without padding; returns None
+    otherwise (``SX_SSD_FUSED=0`` forces the staged path)."""
+    import os
+    if not (k.x5.is_cuda and k.cdt == torch.bfloat16 and k.Q == 128 and k.N == 128 and k.P == 64 and k.pad == 0
+            and _lib.available() and k.Bsz * k.nc <= 65535 and os.environ.get("SX_SSD_FUSED", "1") != "0"
+            and Bm.dtype == torch.bfloat16 and Cm.dtype == torch.bfloat16):
+        return None
+    if not _token_major_ok(Bm, k.N):
+        Bm = Bm.contiguous()
+    if not _token_major_ok(Cm, k.N):
+        Cm = Cm.contiguous()
+    y = torch.empty(k.Bsz, k.nc, k.Q, k.H, k.P, dtype=k.cdt, device=k.x5.device)
+    Dp = D.float().contiguous() if D is not None else None
+    _lib.call("sx_ssd_chunk_fwd", ptr(Cm), c_ll(Cm.stride(1)), ptr(Bm), c_ll(Bm.stride(1)), ptr(k.x5),
+              c_ll(k.x5.stride(2)), ptr(Hprev), ptr(k.csh), ptr(k.dth), ptr(Dp), ptr(y), c_ll(k.Bsz * k.nc),
+              c_int(k.H), c_int(k.G), _lib.c_void_p(_lib.status_word(k.x5.device).data_ptr()), stream())
+    return y
+
+
 class _SSDFn(torch.autograd.Function):
     """Chunked SSD scan with a hand-written backward. Only the inputs and the chunk-entry states are kept for
     backward; every Q x Q quantity is rebuilt there, so the memory held per layer is O(L) rather than O(L Q)."""
@@ -402,11 +439,13 @@ class _SSDFn(torch.autograd.Function):
         ctx.set_materialize_grads(False)
         k = _Chunks(x, dt, A, Bm, Cm, chunk)
         B_, nc, Q, H, P, N = k.Bsz, k.nc, k.Q, k.H, k.P, k.N
-        M = _build_m(k.CB, k.csh, k.dth, k.rep, k.cdt)
-        Yi = gemm(M.view(-1, Q, Q), k.heads_first(k.x5), b_mn=True).view(B_, nc, H, Q, P)
         S = gemm(k.xw, k.by_group(k.Bc), a_mn=True, b_mn=True, out_dtype=torch.float32)   # [B*nc*G, rep*P, N]
         Hprev, final = _state_fwd(S.view(B_, nc, H, P, N), k.tot, init_state, k.cdt)
-        y = _combine(Yi, k.y_off(Hprev), k.x5, torch.exp(k.cs), D, k.cdt, k.G)
+        y = _chunk_fwd_fused(k, Bm, Cm, D, Hprev)
+        if y is None:
+            M = _build_m(k.CB, k.csh, k.dth, k.rep, k.cdt)
+            Yi = gemm(M.view(-1, Q, Q), k.heads_first(k.x5), b_mn=True).view(B_, nc, H, Q, P)
+            y = _combine(Yi, k.y_off(Hprev), k.x5, torch.exp(k.cs), D, k.cdt, k.G)
         ctx.save_for_backward(x, dt, A, Bm, Cm, D, Hprev)
         ctx.chunk = chunk
         ctx.has_init = init_state is not None

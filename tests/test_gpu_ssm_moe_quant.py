@@ -95,6 +95,29 @@ def test_ssd_scan_states_and_long_chunks():
         assert _rel(got, want) < 6e-2, name
 
 
+def test_ssd_fused_chunk_kernel_matches_staged_path(monkeypatch):
+    """tcgen05 output-stage kernel (chunk 128, state 128, headdim 64) against the staged path and the fp32 recurrence;
+    x, B and C are column slices of one wider token-major tensor, as in the Mamba-2 block; two B/C groups."""
+    torch.manual_seed(4)
+    B, L, H, P, N, G = 2, 512, 8, 64, 128, 2
+    wide = torch.randn(B, L, H * P + 2 * G * N + 64, device="cuda", dtype=torch.bfloat16)
+    x = wide[..., :H * P].reshape(B, L, H, P)
+    Bm = wide[..., H * P:H * P + G * N].reshape(B, L, G, N)
+    Cm = wide[..., H * P + G * N:H * P + 2 * G * N].reshape(B, L, G, N)
+    dt = torch.rand(B, L, H, device="cuda") * 0.1 + 1e-3
+    A = -torch.rand(H, device="cuda") * 4 - 0.5
+    D = torch.randn(H, device="cuda")
+    h0 = torch.randn(B, H, P, N, device="cuda")
+    with torch.no_grad():
+        y1, f1 = ssm.ssd_scan(x, dt, A, Bm, Cm, D, chunk=128, init_state=h0, return_state=True)
+        ops.check_status()
+        monkeypatch.setenv("SX_SSD_FUSED", "0")
+        y0, f0 = ssm.ssd_scan(x, dt, A, Bm, Cm, D, chunk=128, init_state=h0, return_state=True)
+        yr = ssm.ssd_reference(x.float(), dt, A, Bm.float(), Cm.float(), D, init_state=h0)
+    assert _rel(y1, yr) < 2e-2 and _rel(y0, yr) < 2e-2
+    assert _rel(y1, y0) < 1e-2 and torch.equal(f1, f0)
+
+
 def test_router_and_moe_layer():
     torch.manual_seed(0)
     T, d, E, k, Fd = 1000, 256, 16, 4, 192
