@@ -82,6 +82,9 @@ class GradientObfuscator:
         return grad
 
     def sinusoid(self, grad):
+        if grad.is_cuda and grad.dtype == torch.float32 and grad.numel() % 4 == 0:
+            from ..ops import aux
+            return aux.arc_step("obfuscate", grad, eps=self.noise_scale).view_as(grad)
         return grad + self.noise_scale * torch.sin(100.0 * grad)
 
     def attach(self, module, method=OBF_MIXED):
@@ -134,7 +137,12 @@ def simulate_attack(x, attack_type=ATTACK_FGSM, epsilon=0.1, loss_fn=None, steps
         (grad,) = torch.autograd.grad(loss_fn(xa), xa)
         return grad.sign()
 
+    native = x.is_cuda and x.dtype == torch.float32 and x.numel() % 4 == 0
+    if native:
+        from ..ops import aux  # one fused kernel per step: sign, step, projection and clamp
     if attack_type == ATTACK_FGSM:
+        if native:
+            return aux.arc_step("fgsm", x, sign_of(x), eps=epsilon, lo=lo, hi=hi).view_as(x)
         return (x + epsilon * sign_of(x)).clamp(lo, hi).detach()
     if attack_type == ATTACK_CW:
         return (x + 0.5 * epsilon * sign_of(x)).clamp(lo, hi).detach()
@@ -142,14 +150,22 @@ def simulate_attack(x, attack_type=ATTACK_FGSM, epsilon=0.1, loss_fn=None, steps
         adv = (x + (torch.rand(x.shape, generator=g, device=x.device).to(x.dtype) - 0.5) * 2 * epsilon).clamp(lo, hi)
         step = epsilon / steps
         for _ in range(steps):
+            if native:
+                adv = aux.arc_step("pgd", adv, sign_of(adv), x, eps=epsilon, alpha=step, lo=lo, hi=hi).view_as(x)
+                continue
             adv = adv + step * sign_of(adv)
             adv = torch.min(torch.max(adv, x - epsilon), x + epsilon).clamp(lo, hi)
         return adv.detach()
     raise ValueError(f"unknown attack {attack_type}")
 
 
-def randomized_smoothing(fn, x, sigma=0.1, samples=8):
-    """Mean prediction under Gaussian input noise (arc_cuda.cu:118)."""
+def randomized_smoothing(fn, x, sigma=0.1, samples=8, seed=None):
+    """Mean prediction under Gaussian input noise (arc_cuda.cu:118). With ``seed`` the noise comes from the
+    counter-based generator (sample i uses stream offset i), so the result is reproducible on any device."""
+    if seed is not None:
+        from ..ops import aux
+        return torch.stack([fn(aux.arc_step("smooth", x, eps=sigma, seed=seed, offset=i).view_as(x).to(x.dtype))
+                            for i in range(samples)]).mean(0)
     return torch.stack([fn(x + sigma * torch.randn_like(x)) for _ in range(samples)]).mean(0)
 
 

@@ -131,6 +131,54 @@ def compress_topk(grad, ratio):
     return out.view_as(grad)
 
 
+def compress_block_top2(grad):
+    """Keeps the two largest-magnitude entries of every 32 (fm_cuda.cu:176-209); returns (kept, residual). The block
+    form needs no global sort, so it is one bandwidth-bound pass; the tail that does not fill a block is kept."""
+    from ..ops import aux
+    flat = grad.reshape(-1).float()
+    n = flat.numel() // 32 * 32
+    kept, res = aux.block_top2(flat[:n]) if n else (flat[:0], flat[:0])
+    return torch.cat([kept, flat[n:]]).view_as(grad), torch.cat([res, torch.zeros_like(flat[n:])]).view_as(grad)
+
+
+class BlockErrorFeedback:
+    """Error feedback around ``compress_block_top2``: what a step drops is added to the next gradient."""
+
+    def __init__(self):
+        self.residual = None
+
+    def compress(self, grad):
+        acc = grad.float() if self.residual is None else grad.float() + self.residual
+        kept, self.residual = compress_block_top2(acc)
+        return kept
+
+
+def quantize_grad_int8(grad):
+    """int8 codes with one scale per 256 values (fm_cuda.cu:100-173); returns (codes, scales, numel). The buffer is
+    zero-padded to a multiple of 256."""
+    from ..ops import aux
+    flat = grad.reshape(-1).float()
+    pad = (-flat.numel()) % 256
+    if pad:
+        flat = torch.cat([flat, flat.new_zeros(pad)])
+    q, s = aux.quant_int8(flat)
+    return q, s, grad.numel()
+
+
+def dequantize_grad_int8(q, scales, numel, shape=None):
+    from ..ops import aux
+    y = aux.dequant_int8(q, scales)[:numel]
+    return y.view(shape) if shape is not None else y
+
+
+def federated_average(tensors, weights=None):
+    """Weighted mean of the nodes' buffers (fm_cuda.cu:225-240); weights default to uniform and are normalised."""
+    from ..ops import aux
+    w = [1.0] * len(tensors) if weights is None else [float(v) for v in weights]
+    tot = sum(w)
+    return aux.weighted_average(list(tensors), [v / tot for v in w]).view_as(tensors[0])
+
+
 def add_privacy_noise(t, epsilon, generator=None):
     """In-place Laplace(0, 1/epsilon) noise (sync.c:41-47)."""
     if epsilon <= 0:

@@ -4,7 +4,7 @@ time whole NumPy ops; here every case is one native sm_100a kernel).
 ``python -m sneppx_alg_b200.benchmarks.kernels <case> [--small] [--iters N] [--out file.json]``
 
 Cases: gemm, gemm_wgrad, attn_fwd, attn_bwd, rmsnorm, glu, rope, ce, adamw, sumsq, paged_decode, gemm_dq_fp8,
-gemm_dq_int4, gemm_fp8, gemm_fp8_prefill, conv1d, conv1d_bwd, ssd_fwd, ssd_bwd, router, quant_fp8, all.  ``--small`` picks a problem that still exceeds L2 but holds well
+gemm_dq_int4, gemm_fp8, gemm_fp8_prefill, conv1d, conv1d_bwd, ssd_fwd, ssd_bwd, router, quant_fp8, dropout, rng_normal, layernorm_bwd, block_top2, all.  ``--small`` picks a problem that still exceeds L2 but holds well
 under 2 GB so that one launch can be captured by a profiler in seconds.  Timing: CUDA events on the launching
 stream after 3 warm-up launches; inputs are larger than L2 or rotated between iterations.  Fractions are against the
 measured copy bandwidth / cuBLAS bf16 throughput in ``MEASURED_PEAKS.json`` when that file is present at the
@@ -277,6 +277,40 @@ def case_quant_fp8(small, iters):
     with torch.no_grad():
         ms = _time(lambda: quant.quant_fp8_1x128(x), iters)
     return dict(shape=[T, Dm], ms=ms, bytes=T * Dm * 3 + T * Dm // 128 * 4)
+
+
+def case_dropout(small, iters):
+    from ..ops import aux
+    T, Dm = (32768, 4096) if small else (131072, 4096)
+    x = _bf(T, Dm)
+    with torch.no_grad():
+        ms = _time(lambda: aux.dropout(x, 0.1, seed=1), iters)
+    return dict(shape=[T, Dm], ms=ms, bytes=T * Dm * 4, note="mask regenerated from the counter, never stored")
+
+
+def case_rng_normal(small, iters):
+    from ..ops import aux
+    n = (1 << 26) if small else (1 << 28)
+    ms = _time(lambda: aux.rng_fill(n, "normal", 0.0, 1.0, seed=1), iters)
+    return dict(shape=[n], ms=ms, bytes=4 * n, note="write-only; includes the output allocation")
+
+
+def case_layernorm_bwd(small, iters):
+    from ..ops import aux
+    T, Dm = (32768, 4096) if small else (131072, 4096)
+    x, g = _bf(T, Dm, grad=True), _bf(T, Dm)
+    w = torch.ones(Dm, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    y = aux.layernorm_train(x, w, None, 1e-5)
+    ms = _time(lambda: torch.autograd.grad(y, (x, w), g, retain_graph=True), iters)
+    return dict(shape=[T, Dm], ms=ms, bytes=T * Dm * 2 * 3, note="reads x, dy (second pass mostly from L2 / L1), writes dx")
+
+
+def case_block_top2(small, iters):
+    from ..ops import aux
+    n = (1 << 26) if small else (1 << 28)
+    x = torch.randn(n, device="cuda")
+    ms = _time(lambda: aux.block_top2(x), iters)
+    return dict(shape=[n], ms=ms, bytes=4 * n * 3, note="reads x, writes kept and residual")
 
 
 CASES = {k[5:]: v for k, v in list(globals().items()) if k.startswith("case_")}

@@ -144,6 +144,28 @@ int sx_gemm_bf16_comm(const SxGemmArgs* args, const SxGemmCommArgs* comm, cudaSt
 // AR1: small all-reduce (sum) of fp32 values through the peers' buffers; n <= 4096. In place on peers->buf[rank].
 int sx_allreduce_small(const SxPeers* peers, int n, int channel, unsigned epoch, int* status, cudaStream_t stream);
 
+// ------------------------------------------------------------------ RNG, dropout, LayerNorm backward, FM / ARC steps
+// Philox4x32-10 keyed by `seed`; element i of stream `offset` is the same whatever the launch geometry.
+// mode 0 uniform [a, b), 1 normal(mean a, std b), 2 bernoulli(p = a) as 0 / 1. `out` 16-byte aligned.
+int sx_rng_fill(float* out, long long n, int mode, float a, float b, unsigned long long seed, unsigned long long offset, cudaStream_t stream);
+// bf16, n % 8 == 0: y = x * keep / (1 - p). Backward is the same call on dy with the same (seed, offset).
+int sx_dropout(const void* x, void* y, long long n, float p, unsigned long long seed, unsigned long long offset, cudaStream_t stream);
+// LayerNorm backward: x, dy, dx bf16 [rows, cols]; gamma fp32; mean / rstd fp32 [rows] from sx_layernorm_fwd;
+// partials fp32 [sx_layernorm_bwd_blocks(rows), 2, cols] scratch; dgamma_dbeta fp32 [2, cols]. cols % 8 == 0, <= 8192.
+int sx_layernorm_bwd_blocks(long long rows);
+int sx_layernorm_bwd(const void* x, const void* dy, const float* gamma, const float* mean, const float* rstd, void* dx,
+                     float* partials, float* dgamma_dbeta, long long rows, int cols, cudaStream_t stream);
+// Gradient compression (fp32): int8 with one scale per 256 values (n % 256 == 0); top-2 of every 32 values with the
+// dropped part in `residual` (optional; n % 32 == 0); weighted sum of up to 16 equally sized buffers (n % 4 == 0).
+int sx_fm_quant_int8(const float* x, void* q, float* scales, long long n, cudaStream_t stream);
+int sx_fm_dequant_int8(const void* q, const float* scales, float* y, long long n, cudaStream_t stream);
+int sx_fm_block_top2(const float* x, float* kept, float* residual, long long n, cudaStream_t stream);
+int sx_fm_weighted_avg(const float* const* inputs, const float* weights, int count, float* out, long long n, cudaStream_t stream);
+// Adversarial steps (fp32, n % 4 == 0). mode 0 FGSM, 1 PGD step with projection onto the eps-ball around x0,
+// 2 sine obfuscation x + eps * sin(100 x), 3 Gaussian smoothing sample x + eps * N(0, 1).
+int sx_arc_step(const float* x, const float* g, const float* x0, float* out, long long n, int mode, float eps, float alpha,
+                float lo, float hi, unsigned long long seed, unsigned long long offset, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

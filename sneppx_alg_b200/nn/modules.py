@@ -56,7 +56,19 @@ class Embedding(Module):
 
 
 class Dropout(tnn.Dropout, Module):
-    pass
+    """Inverted dropout. On bf16 CUDA activations the keep-mask is a function of (seed, call counter, element index)
+    that backward recomputes, so no mask tensor is stored between the passes (``ops.aux.dropout``)."""
+
+    def __init__(self, p=0.5, inplace=False, seed=0):
+        super().__init__(p, inplace)
+        self.seed, self.calls = seed, 0
+
+    def forward(self, x):
+        if self.training and self.p > 0 and x.is_cuda and x.dtype == torch.bfloat16 and x.numel() % 8 == 0:
+            from ..ops import aux
+            self.calls += 1
+            return aux.dropout(x, self.p, self.seed, self.calls)
+        return super().forward(x)
 
 
 class LayerNorm(Module):
@@ -152,7 +164,7 @@ class TransformerBlock(Module):
         self.ln2 = LayerNorm(d_model, dtype=dtype, device=device)
         self.ff1 = Linear(d_model, d_ff, dtype=dtype, device=device)
         self.ff2 = Linear(d_ff, d_model, dtype=dtype, device=device)
-        self.drop = tnn.Dropout(dropout)
+        self.drop = Dropout(dropout)
 
     def forward(self, x):
         x = x + self.drop(self.attn(self.ln1(x)))
