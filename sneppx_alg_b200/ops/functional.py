@@ -323,6 +323,23 @@ def attention(q, k, v, causal=True, window=0, scale=None):
     return attention_reference(q, k, v, causal, window, scale)
 
 
+@torch.no_grad()
+def attention_with_lse(q, k, v, causal=True, window=0, scale=None):
+    """Forward only: (o [B,Sq,Hq,D], lse [B,Hq,Sq] natural log). The pair lets partial results over disjoint key
+    sets be merged (ring / split-KV attention)."""
+    D = q.shape[-1]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    if not (_native(q) and D == 128):
+        return attention_reference(q, k, v, causal, window, scale, return_lse=True)
+    B, Sq, Hq, _ = q.shape
+    q, k, v = [t if _head_view_ok(t, D) else t.contiguous() for t in (q, k, v)]
+    o = torch.empty(B, Sq, Hq, D, dtype=q.dtype, device=q.device)
+    lse = torch.empty(B, Hq, Sq, dtype=torch.float32, device=q.device)
+    a = _attn_args(q, k, v, o, lse, causal, window, scale, k.shape[2] // v.shape[2])
+    _lib.call("sx_attn_fwd", C.byref(a), stream())
+    return o, lse
+
+
 def differential_attention(q, k, v, lam, causal=True, scale=None):
     """softmax(Q1 K1^T) V - lam * softmax(Q2 K2^T) V  (kernel/attention/differential_attention.c:25-27 states
     the intent). q, k: [B, S, 2H, D] with heads ordered (h0a, h0b, h1a, h1b, ..); v: [B, S, H, D]."""

@@ -37,3 +37,12 @@ def test_fused_expert_parallel_two_gpus():
            "127.0.0.1", "--master-port", "29621", os.path.join(HERE, "mp_ep_check.py")]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+def test_context_parallel_two_gpus():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29631", os.path.join(HERE, "mp_cp_gpu_check.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, NCCL_NVLS_ENABLE="0"))
+    assert r.returncode == 0 and "CP_GPU_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
