@@ -98,6 +98,8 @@ def serve_main(argv=None):
     ap.add_argument("--tls-certfile", default=None)
     ap.add_argument("--tls-keyfile", default=None)
     ap.add_argument("--dry-run", action="store_true", help="build the app and exit (used by tests)")
+    ap.add_argument("--front-end", choices=["fastapi", "native"], default="fastapi",
+                    help="native: the C++ HTTP server with the /v1/health, /v1/models, /v1/generate surface")
     a = ap.parse_args(argv)
     from .serving.server import create_app
     device, dtype = _device_dtype()
@@ -115,6 +117,21 @@ def serve_main(argv=None):
         tok.load(a.tokenizer)
         spec["tokenizer"] = tok
     keys = set(a.api_keys.split(",")) if (a.auth_mode == "api_key" and a.api_keys) else None
+    if a.front_end == "native":
+        import time
+        from .serving.native_http import TextEngine, serve_engine
+        eng = TextEngine(model, spec.get("tokenizer"), a.model_id, **spec["engine_kwargs"])
+        srv = serve_engine(eng, {a.model_id: {"config": a.model_config}}, token=(sorted(keys)[0] if keys else ""),
+                           port=0 if a.dry_run else a.port, workers=max(a.workers, 2))
+        print(json.dumps({"front_end": "native", "port": srv.port}), flush=True)
+        try:
+            while not a.dry_run:
+                time.sleep(1.0)
+        except KeyboardInterrupt:
+            pass
+        srv.stop()
+        eng.stop()
+        return 0
     app = create_app({a.model_id: spec}, a.model_id, api_keys=keys, admin_key=a.admin_key)
     if a.dry_run:
         print(json.dumps({"routes": sorted({r.path for r in app.routes})}))
