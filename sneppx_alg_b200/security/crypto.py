@@ -117,3 +117,76 @@ class GuardedBuffer:
         rc = _L().sx_guarded_free(self.ptr)
         self.ptr = None
         return rc
+
+
+# ------------------------------------------------------------------------------- csrc/host/crypto_ext.cpp
+def _hash(fn, data: bytes, n: int) -> bytes:
+    out = _buf(n)
+    getattr(_L(), fn)(data, C.c_size_t(len(data)), out)
+    return out.raw
+
+
+def sha512(data: bytes) -> bytes:
+    return _hash("sx_sha512", data, 64)
+
+
+def sha3_256(data: bytes) -> bytes:
+    return _hash("sx_sha3_256", data, 32)
+
+
+def sha3_512(data: bytes) -> bytes:
+    return _hash("sx_sha3_512", data, 64)
+
+
+def shake256(data: bytes, length: int) -> bytes:
+    out = _buf(length)
+    _L().sx_shake256(data, C.c_size_t(len(data)), out, C.c_size_t(length))
+    return out.raw
+
+
+def blake2b(data: bytes, digest_size: int = 64, key: bytes = b"") -> bytes:
+    out = _buf(digest_size)
+    if _L().sx_blake2b(data, C.c_size_t(len(data)), key, C.c_size_t(len(key)), out, C.c_size_t(digest_size)):
+        raise ValueError("digest_size must be 1..64 and the key at most 64 bytes")
+    return out.raw
+
+
+def aes256_gcm_encrypt(key: bytes, iv: bytes, plaintext: bytes, aad: bytes = b"") -> bytes:
+    """AES-256-GCM with a 96-bit IV: returns ciphertext || 16-byte tag."""
+    if len(key) != 32 or len(iv) != 12:
+        raise ValueError("key must be 32 bytes and iv 12 bytes")
+    ct, tag = _buf(max(len(plaintext), 1)), _buf(16)
+    _L().sx_aes256_gcm_encrypt(key, iv, aad, C.c_size_t(len(aad)), plaintext, C.c_size_t(len(plaintext)), ct, tag)
+    return ct.raw[:len(plaintext)] + tag.raw
+
+
+def aes256_gcm_decrypt(key: bytes, iv: bytes, sealed: bytes, aad: bytes = b"") -> bytes:
+    if len(key) != 32 or len(iv) != 12 or len(sealed) < 16:
+        raise ValueError("key must be 32 bytes, iv 12 bytes and the input at least a tag long")
+    ct, tag = sealed[:-16], sealed[-16:]
+    pt = _buf(max(len(ct), 1))
+    if _L().sx_aes256_gcm_decrypt(key, iv, aad, C.c_size_t(len(aad)), ct, C.c_size_t(len(ct)), tag, pt):
+        raise ValueError("authentication failed")
+    return pt.raw[:len(ct)]
+
+
+def ed25519_public_key(seed: bytes) -> bytes:
+    if len(seed) != 32:
+        raise ValueError("seed must be 32 bytes")
+    out = _buf(32)
+    _L().sx_ed25519_public_key(seed, out)
+    return out.raw
+
+
+def ed25519_sign(seed: bytes, message: bytes) -> bytes:
+    if len(seed) != 32:
+        raise ValueError("seed must be 32 bytes")
+    out = _buf(64)
+    _L().sx_ed25519_sign(seed, message, C.c_size_t(len(message)), out)
+    return out.raw
+
+
+def ed25519_verify(public_key: bytes, message: bytes, signature: bytes) -> bool:
+    if len(public_key) != 32 or len(signature) != 64:
+        return False
+    return bool(_L().sx_ed25519_verify(public_key, message, C.c_size_t(len(message)), signature))

@@ -155,17 +155,31 @@ class AuditLogger:
 
 
 # ---- S7 updates
-def sign_update(path: str, key: bytes, version: str) -> dict:
+def sign_update(path: str, key: bytes, version: str, scheme: str = "hmac-sha256") -> dict:
+    """Manifest for an update file. ``hmac-sha256``: `key` is a shared secret. ``ed25519``: `key` is the 32-byte
+    signing seed and the manifest is verified with the public key only."""
     data = open(path, "rb").read()
-    manifest = {"file": os.path.basename(path), "version": version, "sha256": crypto.sha256(data).hex(), "size": len(data)}
-    manifest["signature"] = crypto.hmac_sha256(key, json.dumps(manifest, sort_keys=True).encode()).hex()
+    manifest = {"file": os.path.basename(path), "version": version, "sha256": crypto.sha256(data).hex(), "size": len(data),
+                "scheme": scheme}
+    payload = json.dumps(manifest, sort_keys=True).encode()
+    if scheme == "ed25519":
+        manifest["signature"] = crypto.ed25519_sign(key, payload).hex()
+    elif scheme == "hmac-sha256":
+        manifest["signature"] = crypto.hmac_sha256(key, payload).hex()
+    else:
+        raise ValueError(f"unknown signature scheme {scheme!r}")
     return manifest
 
 
 def verify_update(path: str, manifest: dict, key: bytes, min_version: str = "0") -> bool:
+    """`key`: the shared secret (hmac-sha256) or the signer's 32-byte public key (ed25519)."""
     m = dict(manifest)
     sig = bytes.fromhex(m.pop("signature"))
-    if not crypto.ct_equal(sig, crypto.hmac_sha256(key, json.dumps(m, sort_keys=True).encode())):
+    payload = json.dumps(m, sort_keys=True).encode()
+    if m.get("scheme", "hmac-sha256") == "ed25519":
+        if not crypto.ed25519_verify(key, payload, sig):
+            return False
+    elif not crypto.ct_equal(sig, crypto.hmac_sha256(key, payload)):
         return False
     data = open(path, "rb").read()
     as_tuple = lambda v: tuple(int(x) for x in re.findall(r"\d+", v))  # noqa: E731
