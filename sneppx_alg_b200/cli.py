@@ -353,7 +353,7 @@ def onnx_main(argv=None):
 
 
 def hub_main(argv=None):
-    ap = argparse.ArgumentParser(prog="sneppx-hub", description="Local model registry")
+    ap = argparse.ArgumentParser(prog="sneppx-hub", description="Local model registry and registry-service client")
     ap.add_argument("--root", default="~/.sneppx/hub")
     sub = ap.add_subparsers(dest="cmd", required=True)
     sub.add_parser("list")
@@ -374,9 +374,94 @@ def hub_main(argv=None):
     cv.add_argument("src")
     cv.add_argument("dst")
     cv.add_argument("--preset", required=True)
+    # verbs against a registry service (hub/registry_server.py); the session token is kept in <root>/session.json
+    sv = sub.add_parser("serve", help="run the registry service")
+    sv.add_argument("--data", default="~/.sneppx/hub-server")
+    sv.add_argument("--port", type=int, default=8090)
+    sv.add_argument("--dry-run", action="store_true")
+    for name in ("register", "login"):
+        rp = sub.add_parser(name)
+        rp.add_argument("url")
+        rp.add_argument("username")
+        rp.add_argument("password")
+    sub.add_parser("logout")
+    sub.add_parser("whoami")
+    cr = sub.add_parser("create")
+    cr.add_argument("model_id")
+    cr.add_argument("--description", default="")
+    cr.add_argument("--tags", nargs="*", default=[])
+    cr.add_argument("--private", action="store_true")
+    pu = sub.add_parser("push")
+    pu.add_argument("model_dir")
+    pu.add_argument("model_id")
+    pu.add_argument("--version", default="1.0.0")
+    pu.add_argument("--metric", action="append", default=[], help="name=value")
+    pl = sub.add_parser("pull")
+    pl.add_argument("model_id")
+    pl.add_argument("dest")
+    pl.add_argument("--version", default=None)
+    inf = sub.add_parser("info")
+    inf.add_argument("model_id")
+    rm = sub.add_parser("delete")
+    rm.add_argument("model_id")
+    rs = sub.add_parser("remote-search")
+    rs.add_argument("query", nargs="?", default="")
+    rs.add_argument("--tag", default="")
+    ky = sub.add_parser("key")
+    ky.add_argument("name")
     a = ap.parse_args(argv)
     from .hub.model_hub import Hub, convert_hf_to_sneppx
     hub = Hub(a.root)
+    session_path = os.path.join(hub.root, "session.json")
+    if a.cmd == "serve":
+        import time
+        from .hub.registry_server import serve_hub
+        srv = serve_hub(os.path.expanduser(a.data), 0 if a.dry_run else a.port)
+        print(json.dumps({"hub": f"http://127.0.0.1:{srv.port}"}), flush=True)
+        try:
+            while not a.dry_run:
+                time.sleep(1.0)
+        except KeyboardInterrupt:
+            pass
+        srv.stop()
+        return 0
+    if a.cmd in ("register", "login", "logout", "whoami", "create", "push", "pull", "info", "delete", "remote-search", "key"):
+        from .hub.registry_server import HubClient
+        sess = json.load(open(session_path)) if os.path.exists(session_path) else {}
+        if a.cmd in ("register", "login"):
+            cl = HubClient(a.url)
+            if a.cmd == "register":
+                cl.register(a.username, a.password)
+            json.dump({"url": a.url, "user": a.username, "token": cl.login(a.username, a.password)}, open(session_path, "w"))
+            print(json.dumps({"user": a.username, "url": a.url}))
+            return 0
+        if a.cmd == "logout":
+            if os.path.exists(session_path):
+                os.remove(session_path)
+            return 0
+        if not sess:
+            print("not logged in: run `sneppx-hub login <url> <user> <password>` first", file=sys.stderr)
+            return 1
+        cl = HubClient(sess["url"], sess["token"])
+        if a.cmd == "whoami":
+            out = {"user": sess["user"], "url": sess["url"]}
+        elif a.cmd == "create":
+            out = cl.create_model(a.model_id, a.description, a.tags, a.private)
+        elif a.cmd == "push":
+            metrics = {k: float(v) for k, v in (m.split("=", 1) for m in a.metric)}
+            out = {"uploaded": cl.upload(a.model_dir, a.model_id, a.version, metrics)}
+        elif a.cmd == "pull":
+            out = {"path": cl.download(a.model_id, a.dest, a.version)}
+        elif a.cmd == "info":
+            out = cl.model_info(a.model_id)
+        elif a.cmd == "delete":
+            out = cl.delete_model(a.model_id)
+        elif a.cmd == "remote-search":
+            out = cl.search(a.query, a.tag)
+        else:
+            out = {"key": cl.create_api_key(a.name)}
+        print(json.dumps(out, indent=1))
+        return 0
     if a.cmd == "list":
         print(json.dumps(hub.list_models(), indent=1))
     elif a.cmd == "search":

@@ -1,6 +1,8 @@
 // HTTP/1.1 front-end for the serving API: accept thread + worker pool, route table with {param} segments, Bearer
 // authentication, per-route request / latency counters, static JSON routes and callback routes that hand the request
-// to the embedding process (the Python serving engine registers its handlers as C callbacks).
+// to the embedding process (the Python serving engine registers its handlers as C callbacks). A callback receives the
+// captured path parameters as a JSON object, plus the request's Authorization header under "_authorization" and the
+// raw query string under "_query".
 //
 // Reference counterparts: net/http/http_server.c (routes with {param}, middleware chain, worker threads),
 // net/http/http_auth.c (Bearer check), net/http/http_api.c:326-329 (/v1/health, /v1/models, /v1/models/{id},
@@ -179,6 +181,14 @@ struct Server {
       path_matched = true;
       if (r->method == method) { hit = r; params = p; break; }
     }
+    if (hit && hit->cb && headers.count("authorization")) {  // handlers that do their own per-user authorisation
+      if (params.size() > 1) params += ',';
+      params += "\"_authorization\":\"" + json_escape(headers["authorization"]) + "\"";
+    }
+    if (hit && hit->cb && target.find('?') != std::string::npos) {
+      if (params.size() > 1) params += ',';
+      params += "\"_query\":\"" + json_escape(target.substr(target.find('?') + 1)) + "\"";
+    }
     params += "}";
     if (!hit) { rejected++; respond(fd, path_matched ? 405 : 404, path_matched ? "{\"error\":\"method not allowed\"}" : "{\"error\":\"not found\"}"); return; }
     if (!token.empty() && !hit->is_public) {
@@ -191,7 +201,7 @@ struct Server {
     if (hit->cb) {
       std::vector<char> ob(1 << 16);
       long long n = hit->cb(method.c_str(), path.c_str(), params.c_str(), body.data(), (long long)body.size(), ob.data(), (long long)ob.size(), &st);
-      if (n < 0 && -n <= (64ll << 20)) {
+      if (n < 0 && -n <= (4ll << 30)) {  // same worker thread asks again with room; the callee keeps its result
         ob.resize((size_t)-n);
         st = 200;
         n = hit->cb(method.c_str(), path.c_str(), params.c_str(), body.data(), (long long)body.size(), ob.data(), (long long)ob.size(), &st);

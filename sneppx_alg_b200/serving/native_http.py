@@ -10,6 +10,7 @@ from __future__ import annotations
 
 import ctypes as C
 import json
+import threading
 from typing import Callable, Dict, Optional
 
 from .. import _build
@@ -47,6 +48,7 @@ class NativeHttpServer:
         self._keep = []  # callback objects must outlive the server
         self.port: Optional[int] = None
         self._routes: Dict[str, int] = {}
+        self._held: Dict[int, tuple] = {}  # worker thread id -> (status, body) awaiting a larger buffer
 
     def static(self, method: str, pattern: str, payload, public: bool = False):
         body = payload if isinstance(payload, (bytes, str)) else json.dumps(payload)
@@ -57,6 +59,13 @@ class NativeHttpServer:
     def route(self, method: str, pattern: str, public: bool = False):
         def deco(fn: Callable):
             def cb(_m, _p, params, body, blen, out, cap, status):
+                held = self._held.pop(threading.get_ident(), None)
+                if held is not None:  # second call for a response that did not fit: hand over what the first call made
+                    status[0], data = held
+                    if len(data) > cap:
+                        return -len(data)
+                    C.memmove(out, data, len(data))
+                    return len(data)
                 try:
                     res = fn(json.loads(params.decode()), C.string_at(body, blen) if blen else b"")
                     if isinstance(res, tuple):
@@ -67,6 +76,7 @@ class NativeHttpServer:
                 except Exception as e:  # a handler bug must not take the server thread down
                     status[0], data = 500, json.dumps({"error": f"{type(e).__name__}: {e}"}).encode()
                 if len(data) > cap:
+                    self._held[threading.get_ident()] = (status[0], data)  # the handler must not run twice
                     return -len(data)
                 C.memmove(out, data, len(data))
                 return len(data)

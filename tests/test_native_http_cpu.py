@@ -57,8 +57,11 @@ def test_large_bodies_handler_errors_and_concurrency():
     def echo(params, body):
         return {"name": params["name"], "n": len(body)}
 
+    calls = []
+
     @srv.route("GET", "/big")
     def big(_p, _b):
+        calls.append(1)
         return b"x" * 300000  # larger than the first response buffer: the server asks again with room
 
     @srv.route("GET", "/boom")
@@ -74,7 +77,7 @@ def test_large_bodies_handler_errors_and_concurrency():
         assert json.loads(_req(port, "POST", "/echo/a%20b/size", b"z" * 50000)[1]) == {"name": "a%20b", "n": 50000}
         assert _req(port, "POST", "/echo/a/size", b"z" * 70000)[0] == 413
         st, body = _req(port, "GET", "/big")
-        assert st == 200 and len(body) == 300000
+        assert st == 200 and len(body) == 300000 and len(calls) == 1  # the handler ran once
         st, body = _req(port, "GET", "/boom")
         assert st == 500 and b"RuntimeError" in body
         assert _req(port, "GET", "/teapot") == (403, b'{"error": "no"}')
