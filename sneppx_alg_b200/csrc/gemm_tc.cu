@@ -269,18 +269,27 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
     const long long sub_bytes = (long long)p.cm.sub_rows * p.cm.row_bytes;
     bool ok = true;
     int copy_uses = 0;  // pieces issued so far by this CTA (gives ring slot and mbarrier parity)
-    for (int rr = 1; rr < pt.world && ok; ++rr) {
-      const int r = (pt.rank + rr) % pt.world;
-      if (threadIdx.x == 0)
-        s_ok = wait_flag_sys(pt.pad[pt.rank] + p.cm.sig_channel * SX_PAD_STRIDE + r, p.cm.epoch, pt.timeout_ns, p.status);
-      __syncthreads();
-      ok = s_ok != 0;
-      __syncthreads();
-      if (!ok) break;
+    // Work items are (source rank, sub-block) pairs in the order the MMA CTAs consume them (nearest rank first), dealt
+    // round-robin to the copy CTAs: every copy CTA has work from the start, also when a chunk has fewer sub-blocks
+    // than there are copy CTAs (8 ranks x 1024 rows: 4 to 8 sub-blocks per rank).
+    const int items = (pt.world - 1) * subs;
+    unsigned seen = 0;  // ranks whose "chunk complete" signal this CTA has already observed
+    for (int it = blockIdx.x; it < items && ok; it += p.cm.n_copy) {
+      const int r = (pt.rank + 1 + it / subs) % pt.world;
+      const int sub = it % subs;
+      if (!((seen >> r) & 1u)) {
+        if (threadIdx.x == 0)
+          s_ok = wait_flag_sys(pt.pad[pt.rank] + p.cm.sig_channel * SX_PAD_STRIDE + r, p.cm.epoch, pt.timeout_ns, p.status);
+        __syncthreads();
+        ok = s_ok != 0;
+        __syncthreads();
+        if (!ok) break;
+        seen |= 1u << r;
+      }
       // One thread drives bulk copies peer -> shared -> local through a ring of 32 KB pieces in the (otherwise
       // unused) tile staging area, NBUF pieces in flight per CTA, so that a handful of CTAs keep NVLink full.
       constexpr int PIECE = 32768, NBUF = 4;
-      for (int sub = blockIdx.x; sub < subs && ok; sub += p.cm.n_copy) {
+      {
         const long long off = ((long long)r * p.cm.chunk_rows + (long long)sub * p.cm.sub_rows) * p.cm.row_bytes;
         const uint8_t* src = reinterpret_cast<const uint8_t*>(pt.buf[r]) + off;
         uint8_t* dst = p.cm.full + off;

@@ -71,7 +71,8 @@ class FusedTP:
         if k not in self._gather:
             buf = self.sg.alloc(rows_total * cols, dtype)
             sub = 256 if (rows_total // self.world) % 256 == 0 else 128
-            flags = torch.zeros(self.world * max(1, (rows_total // self.world) // sub), dtype=torch.int32,
+            # sized for the finest sub-block (128 rows): ag_gemm may signal at a finer grain than `sub`
+            flags = torch.zeros(self.world * max(1, (rows_total // self.world) // 128), dtype=torch.int32,
                                 device=self.sg.device)
             self._gather[k] = (buf, flags, sub)
         return self._gather[k]
@@ -87,6 +88,10 @@ class FusedTP:
         full = buf.tensor.view(rows, K)
         full[self.rank * rows_s: (self.rank + 1) * rows_s].copy_(x_shard)
         self._ag_epoch += 1
+        if not gather_b and self.world > 2 and rows_s % 128 == 0:
+            # many ranks, short chunks: 128-row sub-blocks give the copy CTAs (world - 1) * rows_s / 128 work items to
+            # share and let a tile start as soon as its own 128 rows are in
+            sub = 128
         if gather_b:
             act = w
             out = torch.empty(act.shape[0], rows, dtype=act.dtype, device=act.device)
