@@ -1,0 +1,91 @@
+"""Serving benchmark: N concurrent requests through the continuous-batching engine (the engine behind ``/v1/generate``),
+reporting output tokens per second and time to first token.
+
+``python -m sneppx_alg_b200.benchmarks.serving [--model llama3-8b] [--requests 64] [--prompt-len 2048] [--new-tokens 256]
+[--quantize none|fp8|int4] [--out file.json]``
+
+The default workload is the serving configuration of the baseline list: 64 concurrent requests, prompts of 2048
+random token ids, 256 greedy decode tokens each, random-init weights (the reference's ``benchmarks/serving_benchmark.py``
+compares static and continuous batching on a dummy model that returns random logits; here the model is real). All
+requests are submitted at time zero; TTFT of a request is measured from submission to its first sampled token, so it
+includes the queueing behind earlier prefills. One GPU; the prompts are distinct, so the prefix cache gives no help.
+Timing is wall clock around ``run_until_done`` with a device synchronisation on both sides (the loop reads one token
+id per request back every step, which is part of serving).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+import time
+
+import torch
+
+
+def run(model, requests=64, prompt_len=2048, new_tokens=256, max_prefill_tokens=16384, block_size=16, seed=0) -> dict:
+    from ..serving.llm_engine import LLMEngine, SamplingParams
+    cfg = model.config
+    dev = next(model.parameters()).device
+    blocks = requests * ((prompt_len + new_tokens + block_size - 1) // block_size) + 64
+    eng = LLMEngine(model, num_blocks=blocks, block_size=block_size, max_batch_size=requests,
+                    max_prefill_tokens=max_prefill_tokens, enable_prefix_cache=False)
+    g = torch.Generator().manual_seed(seed)
+    prompts = [torch.randint(0, cfg.vocab_size, (prompt_len,), generator=g).tolist() for _ in range(requests)]
+    sp = SamplingParams(max_new_tokens=new_tokens)
+    with torch.no_grad():
+        # warm-up: one short request through prefill and a few decode steps (allocations, kernel loading)
+        eng.generate([prompts[0][: min(prompt_len, 128)]], SamplingParams(max_new_tokens=4))
+        eng.finished.clear()
+        eng.stats = {k: 0 for k in eng.stats}
+        if dev.type == "cuda":
+            torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        ids = [eng.submit(p, sp) for p in prompts]
+        eng.run_until_done()
+        if dev.type == "cuda":
+            torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+    done = [eng.finished[i] for i in ids]
+    ttft = sorted(r.first_token_time - r.arrival for r in done)
+    out_tokens = sum(len(r.output) for r in done)
+    pct = lambda q: ttft[min(len(ttft) - 1, int(q * len(ttft)))]  # noqa: E731
+    return {"metric": "serving output tokens/sec", "value": out_tokens / dt, "unit": "tokens/s", "requests": requests,
+            "prompt_len": prompt_len, "new_tokens": new_tokens, "seconds": dt, "output_tokens": out_tokens,
+            "prefill_tokens": eng.stats["prefill_tokens"], "engine_steps": eng.stats["steps"],
+            "ttft_p50_s": pct(0.5), "ttft_p95_s": pct(0.95), "ttft_min_s": ttft[0],
+            "total_tokens_per_s": (out_tokens + eng.stats["prefill_tokens"]) / dt}
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
+    ap.add_argument("--model", default="llama3-8b")
+    ap.add_argument("--requests", type=int, default=64)
+    ap.add_argument("--prompt-len", type=int, default=2048)
+    ap.add_argument("--new-tokens", type=int, default=256)
+    ap.add_argument("--quantize", choices=["none", "fp8", "int4"], default="none")
+    ap.add_argument("--max-prefill-tokens", type=int, default=16384)
+    ap.add_argument("--out", default=None)
+    a = ap.parse_args(argv)
+    from ..models import create_model
+    cuda = torch.cuda.is_available()
+    dev = torch.device("cuda", 0) if cuda else torch.device("cpu")
+    torch.manual_seed(0)
+    model = create_model(a.model, dtype=torch.bfloat16 if cuda else torch.float32, device=dev).eval()
+    model.config.max_position_embeddings = max(model.config.max_position_embeddings, a.prompt_len + a.new_tokens)
+    if a.quantize != "none":
+        from ..ops.quant import quantize_model_
+        quantize_model_(model, a.quantize)
+    r = run(model, a.requests, a.prompt_len, a.new_tokens, a.max_prefill_tokens)
+    r["config"] = {"model": a.model, "weights": "bf16" if a.quantize == "none" else a.quantize, "kv_cache": "bf16" if cuda else "fp32",
+                   "parallelism": "1 GPU" if cuda else "cpu", "data": "random token ids, random-init weights"}
+    if cuda:
+        from ..ops import check_status
+        check_status()
+    print(json.dumps(r), flush=True)
+    if a.out:
+        json.dump(r, open(a.out, "w"), indent=1)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

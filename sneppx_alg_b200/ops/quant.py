@@ -209,6 +209,16 @@ class QuantizedLinear(torch.nn.Module):
         if self.mode == "fp8" and self.fp8_activations and x.is_cuda and x.dtype == torch.bfloat16 \
                 and x.numel() // x.shape[-1] <= 256 and _lib.available():
             return gemm_fp8(x, self.qweight, self.scales, self.bias)
+        rows = x.numel() // x.shape[-1]
+        if rows > 256 and x.is_cuda and x.dtype == torch.bfloat16 and _lib.available():
+            # prefill-size inputs: expanding the weight once (a bandwidth-bound pass over N x K) and running the bf16
+            # tensor-core GEMM beats expanding it inside the GEMM, whose converter warps cap it far below the MMA rate
+            from .gemm import gemm
+            w = dequant_fp8(self.qweight, self.scales, "128x128") if self.mode == "fp8" else dequant_int4(self.qweight, self.scales)
+            y = gemm(x.reshape(rows, x.shape[-1]), w)
+            if self.bias is not None:
+                y = y + self.bias.to(y.dtype)
+            return y.view(*x.shape[:-1], self.out_features)
         return gemm_dequant(x, self.qweight, self.scales, self.mode, self.bias)
 
 

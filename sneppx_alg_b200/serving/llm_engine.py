@@ -158,11 +158,18 @@ class LLMEngine:
         bs = self.cache.block_size
         return (len(req.prompt) + req.params.max_new_tokens + bs - 1) // bs
 
-    def _emit(self, req: Request, logits_row):
+    @staticmethod
+    def _plain_greedy(req: Request) -> bool:
+        return not req.params.do_sample and req.params.repetition_penalty == 1.0
+
+    def _emit(self, req: Request, logits_row, tok: Optional[int] = None):
+        """`tok`: token already chosen for this row (the batched greedy path picks all rows with one argmax and one
+        device-to-host copy instead of one per request)."""
         p = req.params
-        hist = torch.tensor(req.tokens, device=logits_row.device).unsqueeze(0)
-        lg = apply_repetition_penalty(logits_row.unsqueeze(0), hist, p.repetition_penalty)
-        tok = int(sample_from_logits(lg, p.do_sample, p.temperature, p.top_k, p.top_p, self.generator)[0])
+        if tok is None:
+            hist = torch.tensor(req.tokens, device=logits_row.device).unsqueeze(0)
+            lg = apply_repetition_penalty(logits_row.unsqueeze(0), hist, p.repetition_penalty)
+            tok = int(sample_from_logits(lg, p.do_sample, p.temperature, p.top_k, p.top_p, self.generator)[0])
         now = time.perf_counter()
         if req.first_token_time is None:
             req.first_token_time = now
@@ -192,14 +199,15 @@ class LLMEngine:
             budget -= n
             self.stats["prefill_tokens"] += n
             self.running[req.req_id] = req
-            self._emit(req, logits[0])
+            self._emit(req, logits[0], int(logits[0].argmax()) if self._plain_greedy(req) else None)
         active = [r for r in self.running.values() if r.output]
         if active:
             ids = [r.req_id for r in active]
             logits = self.runner.decode(ids, [r.output[-1] for r in active])
             self.stats["decode_tokens"] += len(active)
-            for r, row in zip(active, logits):
-                self._emit(r, row)
+            greedy = logits.argmax(dim=-1).tolist() if any(self._plain_greedy(r) for r in active) else None
+            for i, (r, row) in enumerate(zip(active, logits)):
+                self._emit(r, row, greedy[i] if greedy is not None and self._plain_greedy(r) else None)
 
     def run_until_done(self, max_steps: int = 1_000_000):
         n = 0

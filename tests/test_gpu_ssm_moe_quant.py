@@ -211,3 +211,23 @@ def test_gemm_fp8_block_scaled():
         assert (y2.float() - full).abs().max() / full.abs().max() < 8e-2
     from sneppx_alg_b200 import ops
     ops.check_status()
+
+
+@pytest.mark.parametrize("mode", ["fp8", "int4"])
+@pytest.mark.parametrize("rows", [64, 300, 2048])
+def test_quantized_linear_all_input_sizes(mode, rows):
+    """Decode-size inputs take the fp8 x fp8 / in-GEMM dequant paths, prefill-size inputs expand the weight once and
+    use the bf16 GEMM; all must agree with the dequantised-weight product."""
+    torch.manual_seed(0)
+    lin = torch.nn.Linear(512, 384, bias=True, device="cuda", dtype=torch.bfloat16)
+    ql = quant.QuantizedLinear.from_linear(lin, mode)
+    x = torch.randn(2, rows // 2, 512, device="cuda", dtype=torch.bfloat16)
+    y = ql(x)
+    if mode == "fp8":
+        w = quant.dequant_fp8(ql.qweight.view(torch.float8_e4m3fn), ql.scales, "128x128", torch.float32)
+    else:
+        w = quant.dequant_int4(ql.qweight, ql.scales, torch.float32)
+    ref = x.float() @ w.t() + lin.bias.float()
+    assert y.shape == (2, rows // 2, 384)
+    # the fp8 x fp8 path also rounds the activations to e4m3 (3 mantissa bits)
+    assert _rel(y, ref) < (6e-2 if (mode == "fp8" and rows <= 256) else 2e-2)
