@@ -157,3 +157,99 @@ class LlamaStage(torch.nn.Module):
         tgt = torch.full_like(labels, -100)
         tgt[:, :-1] = labels[:, 1:]
         return ops.linear_cross_entropy(hn, self.head_weight_fn(), tgt)
+
+
+# ---------------------------------------------------------------------------------------------- interleaved 1F1B
+def interleaved_schedule(rank: int, num_ranks: int, num_chunks: int, num_microbatches: int) -> List[tuple]:
+    """Steps ("F" | "B", chunk, micro-batch) of one rank under interleaved 1F1B: each rank holds `num_chunks` model
+    chunks; virtual stage s = chunk * num_ranks + rank. Micro-batches advance in groups of `num_ranks`, chunk by chunk,
+    which shrinks the pipeline bubble by the number of chunks. `num_microbatches` must be a multiple of `num_ranks`."""
+    P, v, M = num_ranks, num_chunks, num_microbatches
+    if M % P:
+        raise ValueError("interleaved schedule needs num_microbatches to be a multiple of the number of ranks")
+    total = M * v
+
+    def fwd(k):
+        return (k // P) % v, (k // (P * v)) * P + k % P
+
+    def bwd(k):
+        c, i = fwd(k)
+        return v - 1 - c, i
+
+    warm = min((P - rank - 1) * 2 + (v - 1) * P, total)
+    steps = [("F",) + fwd(k) for k in range(warm)]
+    f, b = warm, 0
+    while f < total:
+        steps.append(("F",) + fwd(f))
+        steps.append(("B",) + bwd(b))
+        f += 1
+        b += 1
+    while b < total:
+        steps.append(("B",) + bwd(b))
+        b += 1
+    return steps
+
+
+class InterleavedPipelineStage:
+    """Interleaved pipeline over `num_chunks` model chunks per rank. ``chunks[c]`` is the module of virtual stage
+    ``c * P + rank``; the very first virtual stage takes ``inputs``, the very last ``(hidden, labels) -> loss``.
+
+    Messages carry a tag derived from (direction, virtual stage, micro-batch): transports that match on tags (gloo)
+    pair them regardless of posting order. Sends are asynchronous and receives are posted when their step comes up, so
+    the only waits are the data dependencies of the schedule."""
+
+    def __init__(self, chunks: List[torch.nn.Module], group=None, hidden_shape=None, dtype=None, device=None):
+        self.chunks = list(chunks)
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank = dist.get_rank(self.group)
+        self.P = dist.get_world_size(self.group)
+        self.v = len(self.chunks)
+        self.hidden_shape, self.dtype, self.device = hidden_shape, dtype, device
+        self.right = dist.get_global_rank(self.group, (self.rank + 1) % self.P)
+        self.left = dist.get_global_rank(self.group, (self.rank - 1) % self.P)
+
+    def _tag(self, backward: bool, vstage: int, mb: int) -> int:
+        return (1 << 20) * int(backward) + vstage * 1024 + mb
+
+    def forward_backward(self, inputs, labels, num_microbatches: int, loss_scale: Optional[float] = None):
+        P, v, M = self.P, self.v, num_microbatches
+        last_vs = P * v - 1
+        scale = loss_scale if loss_scale is not None else 1.0 / M
+        saved, sends, losses = {}, [], []
+        for kind, c, i in interleaved_schedule(self.rank, P, v, M):
+            vs = c * P + self.rank
+            if kind == "F":
+                if vs == 0:
+                    x = inputs[i]
+                else:
+                    x = torch.empty(self.hidden_shape, dtype=self.dtype, device=self.device)
+                    dist.recv(x, src=self.left, group=self.group, tag=self._tag(False, vs, i))
+                    x.requires_grad_(True)
+                if vs == last_vs:
+                    out = self.chunks[c](x, labels[i])
+                    losses.append(out.detach())
+                else:
+                    out = self.chunks[c](x)
+                    sends.append(dist.isend(out.detach().contiguous(), dst=self.right, group=self.group,
+                                            tag=self._tag(False, vs + 1, i)))
+                saved[(c, i)] = (x, out)
+            else:
+                x, out = saved.pop((c, i))
+                if vs == last_vs:
+                    (out * scale).backward()
+                else:
+                    g = torch.empty_like(out)
+                    dist.recv(g, src=self.right, group=self.group, tag=self._tag(True, vs, i))
+                    out.backward(g)
+                if vs != 0:
+                    sends.append(dist.isend(x.grad.contiguous(), dst=self.left, group=self.group,
+                                            tag=self._tag(True, vs - 1, i)))
+        for w in sends:
+            w.wait()
+        return torch.stack(losses).mean() if losses else None
+
+
+def split_layers_interleaved(num_layers: int, num_ranks: int, num_chunks: int) -> List[List[range]]:
+    """Layer ranges per rank and chunk: virtual stage c * num_ranks + r gets the (c * num_ranks + r)-th slice."""
+    slices = split_layers(num_layers, num_ranks * num_chunks)
+    return [[slices[c * num_ranks + r] for c in range(num_chunks)] for r in range(num_ranks)]
