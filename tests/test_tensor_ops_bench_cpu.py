@@ -1,0 +1,19 @@
+"""Tensor micro-benchmark list and the regression checker with the reference's thresholds."""
+import copy
+
+from sneppx_alg_b200.benchmarks import tensor_ops
+
+
+def test_benchmark_rows_and_regression_thresholds():
+    res = tensor_ops.run("cpu", scale_runs=0.02)
+    names = [r["op"] for r in res["results"]]
+    assert names == [p[0] for p in tensor_ops.PUBLISHED] and all(r["min_ms"] <= r["mean_ms"] <= r["max_ms"] for r in res["results"])
+    assert all(r["vs_published"] > 0 for r in res["results"] if r["published_ms"])
+    ok, rows = tensor_ops.compare(res, res)
+    assert ok and all(abs(r["change"]) < 1e-12 for r in rows)
+    worse = copy.deepcopy(res)
+    for r in worse["results"]:
+        r["min_ms"] *= 1.12  # over the 10 % GEMM / algorithm and 5 % allocator limits, under the 15 % autodiff limit
+    ok, rows = tensor_ops.compare(res, worse)
+    flagged = {r["category"] for r in rows if r["regressed"]}
+    assert not ok and flagged == {"gemm", "allocator", "algorithms"}
