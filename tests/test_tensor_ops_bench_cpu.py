@@ -17,3 +17,10 @@ def test_benchmark_rows_and_regression_thresholds():
     ok, rows = tensor_ops.compare(res, worse)
     flagged = {r["category"] for r in rows if r["regressed"]}
     assert not ok and flagged == {"gemm", "allocator", "algorithms"}
+
+
+def test_tiny_hybrid_parity_config_trains():
+    from sneppx_alg_b200.benchmarks import tiny_hybrid
+    r = tiny_hybrid.run("cpu", steps=2, warmup=1, batch=1, seq=128)
+    assert r["params"] == 22512480 and 10.0 < r["ce_loss"][0] < 10.8   # ln(32000) = 10.37 at initialisation
+    assert r["ce_loss"][-1] < r["ce_loss"][0] - 0.5
