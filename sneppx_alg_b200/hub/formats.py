@@ -102,3 +102,44 @@ def save_npz(path, tensors):
 def load_npz(path):
     with np.load(path) as z:
         return {k: torch.from_numpy(z[k]) for k in z.files}
+
+
+def save_npy(path, tensor):
+    np.save(path, tensor.detach().cpu().numpy() if tensor.dtype != torch.bfloat16 else tensor.detach().float().cpu().numpy())
+
+
+def load_npy(path):
+    return torch.from_numpy(np.load(path, allow_pickle=False))
+
+
+def save_pth(path, state_dict: Dict[str, torch.Tensor]):
+    """PyTorch ``.pth`` state dict (zip archive with a pickle of tensor stubs; fs/format/pth_format.c reads the same
+    subset: tensors only, no arbitrary objects)."""
+    torch.save({k: v.detach().cpu() for k, v in state_dict.items()}, path)
+
+
+def load_pth(path, device="cpu") -> Dict[str, torch.Tensor]:
+    """Loads a ``.pth`` / ``.pt`` state dict with the restricted unpickler (tensors and plain containers only); a
+    checkpoint that wraps the weights under ``state_dict`` / ``model`` is unwrapped."""
+    obj = torch.load(path, map_location=device, weights_only=True)
+    for key in ("state_dict", "model", "model_state_dict"):
+        if isinstance(obj, dict) and key in obj and isinstance(obj[key], dict):
+            obj = obj[key]
+    if not isinstance(obj, dict) or not all(torch.is_tensor(v) for v in obj.values()):
+        raise ValueError(f"{path} does not hold a tensor state dict")
+    return obj
+
+
+def load_any(path, device="cpu") -> Dict[str, torch.Tensor]:
+    """Dispatch on the file extension: .safetensors, .sneppx, .pth / .pt / .bin, .npz."""
+    p = path.lower()
+    if p.endswith(".safetensors"):
+        return load_safetensors(path, device)[0]
+    if p.endswith(".sneppx"):
+        from ..checkpoint.sneppx_format import load_tensors
+        return load_tensors(path)[0]
+    if p.endswith((".pth", ".pt", ".bin")):
+        return load_pth(path, device)
+    if p.endswith(".npz"):
+        return load_npz(path)
+    raise ValueError(f"unknown weight file type: {path}")

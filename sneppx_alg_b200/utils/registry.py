@@ -99,3 +99,64 @@ class EvalMonitor:
             return False
         mean = sum(base) / len(base)
         return (v < mean * (1 - self.tol)) if self.hib else (v > mean * (1 + self.tol))
+
+
+class AIGateway:
+    """Routes a request to one of several named providers (callables) with weighted selection, per-provider rate
+    limits, fall-back to the next provider on failure and per-provider usage accounting (the reference's
+    ``mlflow_like.py`` gateway: named routes in front of model endpoints)."""
+
+    def __init__(self):
+        self.routes = {}
+
+    def add_route(self, route: str, provider: str, fn, weight: float = 1.0, rate_limit_per_s: float = 0.0):
+        self.routes.setdefault(route, []).append({"provider": provider, "fn": fn, "weight": float(weight), "rate": rate_limit_per_s,
+                                                  "tokens": rate_limit_per_s, "stamp": None, "calls": 0, "failures": 0})
+
+    def _admit(self, p, now):
+        if p["rate"] <= 0:
+            return True
+        if p["stamp"] is not None:
+            p["tokens"] = min(p["rate"], p["tokens"] + (now - p["stamp"]) * p["rate"])
+        p["stamp"] = now
+        if p["tokens"] >= 1.0:
+            p["tokens"] -= 1.0
+            return True
+        return False
+
+    def query(self, route: str, payload, request_id: str = "", now: Optional[float] = None):
+        """Providers are tried in an order fixed by the request id (weighted, so the same id maps to the same first
+        choice); a provider that is over its rate or raises is skipped. Returns (provider name, result)."""
+        import hashlib
+        import time
+        ps = self.routes.get(route)
+        if not ps:
+            raise KeyError(f"unknown route {route}")
+        now = time.monotonic() if now is None else now
+        h = int.from_bytes(hashlib.sha256(request_id.encode()).digest()[:8], "big") / 2 ** 64
+        order, pool = [], list(ps)
+        while pool:
+            tot = sum(p["weight"] for p in pool)
+            acc, pick = 0.0, pool[-1]
+            for p in pool:
+                acc += p["weight"] / tot
+                if h < acc:
+                    pick = p
+                    break
+            order.append(pick)
+            pool.remove(pick)
+        errors = []
+        for p in order:
+            if not self._admit(p, now):
+                errors.append(f"{p['provider']}: rate limited")
+                continue
+            try:
+                p["calls"] += 1
+                return p["provider"], p["fn"](payload)
+            except Exception as e:  # fall back to the next provider
+                p["failures"] += 1
+                errors.append(f"{p['provider']}: {e}")
+        raise RuntimeError("all providers failed: " + "; ".join(errors))
+
+    def usage(self, route: str):
+        return {p["provider"]: {"calls": p["calls"], "failures": p["failures"]} for p in self.routes.get(route, [])}
