@@ -110,3 +110,19 @@ def batch_generate(model, prompts: List[torch.Tensor], max_new_tokens=32, pad_to
             results[k] = row
         i = j
     return results
+
+
+def make_stop_fn(tokenizer, stop_strings, window: int = 64):
+    """Stop predicate for ``SamplingParams.stop_fn``: true once the decoded tail of the output contains one of
+    `stop_strings` (only the last `window` tokens are decoded each step)."""
+    stops = [s for s in (stop_strings or []) if s]
+    if not stops:
+        return None
+    return lambda out: any(s in tokenizer.decode(out[-window:]) for s in stops)
+
+
+def truncate_at_stop(text: str, stop_strings) -> str:
+    """Cuts `text` before the earliest occurrence of any stop string (the reference's generate() does the same
+    after decoding, generation.py:244-534)."""
+    cut = min((text.find(s) for s in (stop_strings or []) if s and s in text), default=-1)
+    return text if cut < 0 else text[:cut]

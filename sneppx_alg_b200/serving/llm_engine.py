@@ -33,6 +33,7 @@ class SamplingParams:
     repetition_penalty: float = 1.0
     eos_token_id: Optional[int] = None
     stop_token_ids: tuple = ()
+    stop_fn: Optional[Callable[[List[int]], bool]] = None   # called with the output so far; True ends the request
 
 
 @dataclass(order=True)
@@ -176,7 +177,8 @@ class LLMEngine:
         req.output.append(tok)
         if req.on_token:
             req.on_token(req.req_id, tok)
-        stop = (p.eos_token_id is not None and tok == p.eos_token_id) or tok in p.stop_token_ids
+        stop = (p.eos_token_id is not None and tok == p.eos_token_id) or tok in p.stop_token_ids \
+            or (p.stop_fn is not None and p.stop_fn(req.output))
         if stop or len(req.output) >= p.max_new_tokens:
             req.finish_time = now
             self.cache.free_sequence(req.req_id, req.tokens)

@@ -156,13 +156,15 @@ class TextEngine:
         chk = self.filter.check(prompt)
         if not chk.allowed:
             raise HTTPError(400, "prompt rejected: " + "; ".join(chk.reasons))
-        sampling.pop("stop_strings", None)
+        from .generation import make_stop_fn, truncate_at_stop
+        stops = sampling.pop("stop_strings", None)
         ids = self.tok.encode(chk.sanitized)
-        rid, ev = self.worker.submit(ids, SamplingParams(max_new_tokens=max_new_tokens, **sampling))
+        sp = SamplingParams(max_new_tokens=max_new_tokens, stop_fn=make_stop_fn(self.tok, stops), **sampling)
+        rid, ev = self.worker.submit(ids, sp)
         if not ev.wait(timeout=600):
             raise HTTPError(503, "generation timed out")
         req = self.worker.result(rid)
-        text = self.verifier.verify(self.tok.decode(req.output)).sanitized
+        text = self.verifier.verify(truncate_at_stop(self.tok.decode(req.output), stops)).sanitized
         return {"generated_text": text, "token_ids": req.output, "prompt_tokens": len(ids), "completion_tokens": len(req.output),
                 "total_tokens": len(ids) + len(req.output), "model": self.model_id, "created": int(time.time())}
 

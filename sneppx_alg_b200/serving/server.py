@@ -137,9 +137,12 @@ def create_app(models: Dict[str, dict], default_model: Optional[str] = None, api
         return SamplingParams(max_new_tokens=r.max_new_tokens, do_sample=r.do_sample, temperature=r.temperature,
                               top_k=r.top_k, top_p=r.top_p, repetition_penalty=getattr(r, "repetition_penalty", 1.0))
 
-    async def run_one(mid: str, prompt: str, sp: SamplingParams):
+    async def run_one(mid: str, prompt: str, sp: SamplingParams, stop_strings=None):
         if mid not in workers:
             raise HTTPException(404, f"unknown model '{mid}'")
+        if stop_strings:
+            from .generation import make_stop_fn
+            sp.stop_fn = make_stop_fn(toks[mid], stop_strings)
         chk = prompt_filter.check(prompt)
         if not chk.allowed:
             raise HTTPException(400, {"error": "prompt rejected", "reasons": chk.reasons})
@@ -148,7 +151,11 @@ def create_app(models: Dict[str, dict], default_model: Optional[str] = None, api
         rid, ev = workers[mid].submit(ids, sp)
         await asyncio.get_running_loop().run_in_executor(None, ev.wait)
         req = workers[mid].result(rid)
-        text = verifier.verify(toks[mid].decode(req.output)).sanitized
+        text = toks[mid].decode(req.output)
+        if stop_strings:
+            from .generation import truncate_at_stop
+            text = truncate_at_stop(text, stop_strings)
+        text = verifier.verify(text).sanitized
         metrics.record(time.perf_counter() - t0, True, len(ids), len(req.output),
                        (req.first_token_time - req.arrival) if req.first_token_time else None)
         return {"generated_text": text, "token_ids": req.output, "prompt_tokens": len(ids),
@@ -203,7 +210,7 @@ def create_app(models: Dict[str, dict], default_model: Optional[str] = None, api
     @app.post("/v1/generate")
     async def generate_ep(r: GenerateRequest, authorization: Optional[str] = Header(None)):
         auth(authorization)
-        return await run_one(r.model or default_model, r.prompt, params_of(r))
+        return await run_one(r.model or default_model, r.prompt, params_of(r), r.stop_strings)
 
     @app.post("/v1/generate/batch")
     async def generate_batch(r: BatchRequest, authorization: Optional[str] = Header(None)):

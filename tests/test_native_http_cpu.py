@@ -108,6 +108,13 @@ def test_text_engine_behind_native_front_end():
         out = json.loads(body)
         assert st == 200 and out["completion_tokens"] == 5 and out["prompt_tokens"] == 5 and out["model"] == "tiny"
         assert len(out["token_ids"]) == 5 and out["total_tokens"] == 10
+        # a stop string taken from the middle of a longer greedy continuation ends the request early and is cut off
+        long = json.loads(_req(srv.port, "POST", "/v1/generate", json.dumps({"prompt": "hello", "max_new_tokens": 12}).encode())[1])
+        text = long["generated_text"]
+        stop = text[4:6]
+        cut = json.loads(_req(srv.port, "POST", "/v1/generate", json.dumps(
+            {"prompt": "hello", "max_new_tokens": 12, "stop_strings": [stop]}).encode())[1])
+        assert cut["generated_text"] == text[:text.find(stop)] and cut["completion_tokens"] < 12
     finally:
         srv.stop()
         eng.stop()
