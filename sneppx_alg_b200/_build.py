@@ -145,6 +145,25 @@ def build_host(force: bool = False, verbose: bool = False) -> Path:
     return lib
 
 
+SANITIZE_FLAGS = ["-O1", "-g", "-std=c++17", "-fPIC", "-pthread", "-fsanitize=address,undefined", "-fno-omit-frame-pointer"]
+
+
+def build_host_sanitized(verbose: bool = False) -> Path:
+    """AddressSanitizer + UndefinedBehaviorSanitizer build of the host runtime (``libsneppx_host_asan.so``). Run the
+    host-side tests against it with
+    ``LD_PRELOAD=$(g++ -print-file-name=libasan.so) ASAN_OPTIONS=detect_leaks=0 SX_HOST_LIB=<path> python -m pytest ...``
+    (the reference's ``scripts/run_sanitizers.sh`` does the same for its C tests)."""
+    LIBDIR.mkdir(parents=True, exist_ok=True)
+    lib = LIBDIR / "libsneppx_host_asan.so"
+    cxx = shutil.which("g++") or shutil.which("c++")
+    if cxx is None:
+        raise RuntimeError("g++ not found")
+    srcs = host_sources()
+    objs = _compile_objects(cxx, SANITIZE_FLAGS + ["-I", str(CSRC / "host")], srcs, host_headers(), "host_asan", verbose)
+    _run([cxx, "-shared", "-o", str(lib), *map(str, objs), "-pthread", "-fsanitize=address,undefined"])
+    return lib
+
+
 def build_all(force: bool = False, verbose: bool = False):
     return build_cuda(force, verbose), build_host(force, verbose)
 
@@ -168,6 +187,10 @@ def load_host() -> ctypes.CDLL:
     global _host_lib
     with _lock:
         if _host_lib is None:
+            override = os.environ.get("SX_HOST_LIB")   # e.g. the sanitizer build from build_host_sanitized()
+            if override:
+                _host_lib = ctypes.CDLL(override)
+                return _host_lib
             lib = LIBDIR / "libsneppx_host.so"
             try:
                 lib = build_host()

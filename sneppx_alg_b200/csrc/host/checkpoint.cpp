@@ -140,10 +140,24 @@ void* sx_ckpt_open(const char* path) {
   r->f = f;
   bool ok = fread(&r->h, sizeof(Header), 1, f) == 1 && r->h.magic_lo == kMagicLo && r->h.magic_hi == kMagicHi &&
             r->h.version <= kVersion && r->h.num_tensors < (1u << 24);
+  // every size and offset below comes from the file: check it against the file's length before trusting it
+  uint64_t file_size = 0;
+  if (ok) {
+    long cur = ftell(f);
+    ok = cur >= 0 && fseek(f, 0, SEEK_END) == 0;
+    long end = ok ? ftell(f) : -1;
+    ok = ok && end >= 0 && fseek(f, cur, SEEK_SET) == 0;
+    file_size = ok ? (uint64_t)end : 0;
+  }
+  auto in_file = [&](uint64_t off, uint64_t len) { return off <= file_size && len <= file_size - off; };
+  ok = ok && in_file(sizeof(Header), (uint64_t)r->h.num_tensors * sizeof(Record));
   if (ok) {
     r->recs.resize(r->h.num_tensors);
     ok = r->h.num_tensors == 0 || fread(r->recs.data(), sizeof(Record), r->h.num_tensors, f) == r->h.num_tensors;
   }
+  for (size_t i = 0; ok && i < r->recs.size(); ++i)
+    ok = r->recs[i].ndim <= 8 && in_file(r->recs[i].data_offset, r->recs[i].data_size);
+  ok = ok && in_file(r->h.metadata_offset, r->h.metadata_size);
   if (ok && r->h.metadata_size) {
     r->meta.resize(r->h.metadata_size);
     ok = fseek(f, (long)r->h.metadata_offset, SEEK_SET) == 0 && fread(&r->meta[0], 1, r->h.metadata_size, f) == r->h.metadata_size;

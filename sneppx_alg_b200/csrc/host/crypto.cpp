@@ -168,7 +168,7 @@ void car(gf o) {
     o[i] += (1LL << 16);
     const int64_t c = o[i] >> 16;
     o[(i + 1) * (i < 15)] += c - 1 + 37 * (c - 1) * (i == 15);
-    o[i] -= c << 16;
+    o[i] -= c * 65536;  // not c << 16: shifting a negative value is undefined before C++20
   }
 }
 void sel(gf p, gf q, int b) {

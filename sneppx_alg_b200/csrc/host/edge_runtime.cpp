@@ -102,11 +102,18 @@ void* sx_edge_load(const char* path) {
     fclose(f);
     return nullptr;
   }
+  long here = ftell(f);
+  fseek(f, 0, SEEK_END);
+  const long file_end = ftell(f);
+  fseek(f, here, SEEK_SET);
   EdgeModel* m = new EdgeModel();
   for (uint32_t i = 0; i < n; ++i) {
     Op op;
     if (fread(&op.code, 4, 1, f) != 1 || fread(&op.rows, 4, 1, f) != 1 || fread(&op.cols, 4, 1, f) != 1) break;
+    if (op.code < 1 || op.code > 3) break;
     const size_t cnt = op.code == 1 ? (size_t)op.rows * op.cols : (op.code == 3 ? op.cols : 0);
+    const long left = file_end - ftell(f);
+    if (left < 0 || cnt > (size_t)left / 4) break;  // the weights must be in the file: no allocation from a bare header
     op.w.resize(cnt);
     if (cnt && fread(op.w.data(), 4, cnt, f) != cnt) break;
     m->ops.push_back(std::move(op));
@@ -131,12 +138,20 @@ int sx_edge_run(void* h, const float* x, int batch, int in_dim, float* y, float*
     } else if (op.code == 2) {
       sx_edge_relu(cur.data(), cur.size());
     } else if (op.code == 3) {
+      if ((int)op.cols != dim) return -1;
       for (int b = 0; b < batch; ++b)
         for (int j = 0; j < dim; ++j) cur[(size_t)b * dim + j] += op.w[j];
     }
   }
   memcpy(y, cur.data(), cur.size() * sizeof(float));
   return dim;
+}
+// widest activation row the model produces for inputs of `in_dim` columns (the caller sizes `y` with it)
+int sx_edge_max_width(void* h, int in_dim) {
+  int w = in_dim;
+  for (auto& op : static_cast<EdgeModel*>(h)->ops)
+    if (op.code == 1 && (int)op.cols > w) w = (int)op.cols;
+  return w;
 }
 void sx_edge_free(void* h) { delete static_cast<EdgeModel*>(h); }
 }

@@ -348,12 +348,12 @@ SX_EXPORT long long sx_decompress(const void* in, long long nbytes, float* y, lo
   const uint8_t* p = (const uint8_t*)in;
   if (nbytes < 16) return -1;
   uint32_t id, block; uint64_t n; memcpy(&id, p, 4); memcpy(&block, p + 4, 4); memcpy(&n, p + 8, 8);
-  if ((long long)n > cap || block == 0) return -2;
+  if (cap < 0 || n > (uint64_t)cap || block == 0 || block > 65536) return -2;  // header fields come from untrusted bytes
   size_t k = 16;
-  if (id == C_NONE) { if ((size_t)nbytes < k + 4 * n) return -1; memcpy(y, p + k, 4 * n); return (long long)n; }
+  if (id == C_NONE) { if (n > ((size_t)nbytes - k) / 4) return -1; memcpy(y, p + k, 4 * n); return (long long)n; }
   if (id == C_SPARSE) {
     uint64_t cnt; if (nbytes < 24) return -1; memcpy(&cnt, p + k, 8); k += 8;
-    if ((size_t)nbytes < k + 8 * cnt) return -1;
+    if (cnt > ((size_t)nbytes - k) / 8) return -1;  // written as a division: 8 * cnt can wrap
     std::fill(y, y + n, 0.0f);
     for (uint64_t i = 0; i < cnt; ++i, k += 8) { uint32_t idx; memcpy(&idx, p + k, 4); if (idx >= n) return -1; memcpy(&y[idx], p + k + 4, 4); }
     return (long long)n;
@@ -362,7 +362,7 @@ SX_EXPORT long long sx_decompress(const void* in, long long nbytes, float* y, lo
   const int mant = id == C_BFP8 ? 6 : 2;
   for (uint64_t b0 = 0; b0 < n; b0 += block) {
     size_t len = (size_t)std::min<uint64_t>(block, n - b0);
-    if ((size_t)nbytes < k + 1 + (id == C_BFP8 ? len : (block + 1) / 2)) return -1;
+    if ((size_t)nbytes < k + 1 + (id == C_BFP8 ? len : ((size_t)block + 1) / 2)) return -1;
     int e = (int8_t)p[k++];
     float s = std::ldexp(1.0f, e - mant);
     if (id == C_BFP8) { for (size_t i = 0; i < len; ++i) y[b0 + i] = (float)(int8_t)p[k++] * s; }

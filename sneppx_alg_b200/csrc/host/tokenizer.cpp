@@ -107,11 +107,15 @@ int sx_tok_load(void* h, const char* path) {
   if (!f) return -1;
   size_t n = 0;
   int ver = 0;
-  if (fscanf(f, "sneppx-bpe %d %zu", &ver, &n) != 2) { fclose(f); return -2; }
-  t->merges.resize(n);
-  for (size_t i = 0; i < n; ++i)
-    if (fscanf(f, "%d %d", &t->merges[i].first, &t->merges[i].second) != 2) { fclose(f); return -3; }
+  if (fscanf(f, "sneppx-bpe %d %zu", &ver, &n) != 2 || n > (1u << 22)) { fclose(f); return -2; }
+  std::vector<std::pair<int, int>> merges(n);
+  for (size_t i = 0; i < n; ++i) {
+    // merge i creates token 256 + i out of two tokens that already exist
+    if (fscanf(f, "%d %d", &merges[i].first, &merges[i].second) != 2 || merges[i].first < 0 || merges[i].second < 0 ||
+        merges[i].first >= 256 + (int)i || merges[i].second >= 256 + (int)i) { fclose(f); return -3; }
+  }
   fclose(f);
+  t->merges.swap(merges);
   t->rebuild();
   return 0;
 }

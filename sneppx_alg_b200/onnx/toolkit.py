@@ -243,6 +243,17 @@ class Model:
 
     @classmethod
     def parse(cls, buf: bytes) -> "Model":
+        """Decodes a serialized ModelProto; any structural problem (truncated field, wrong wire type, bad UTF-8, a
+        tensor whose data does not match its dims) is reported as ``ValueError``."""
+        try:
+            return cls._parse(buf)
+        except ValueError:
+            raise
+        except (AttributeError, TypeError, IndexError, KeyError, struct.error, OverflowError, MemoryError) as e:
+            raise ValueError(f"malformed ONNX model: {type(e).__name__}: {e}") from None
+
+    @classmethod
+    def _parse(cls, buf: bytes) -> "Model":
         m = cls(Graph())
         for num, _, v in parse_message(buf):
             if num == 1:

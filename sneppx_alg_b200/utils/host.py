@@ -39,6 +39,7 @@ def _L():
         L.sx_factory_search.argtypes = [C.c_char_p, C.c_char_p, C.c_int]
         L.sx_edge_load.argtypes = [C.c_char_p]
         L.sx_edge_run.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
+        L.sx_edge_max_width.argtypes = [C.c_void_p, C.c_int]
         L.sx_oracle_ssd.argtypes = [C.c_void_p] * 7 + [C.c_int] * 6
         L.sx_oracle_router.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
         L.sx_oracle_adamw.argtypes = [C.c_void_p] * 4 + [C.c_longlong] + [C.c_float] * 5 + [C.c_int]
@@ -154,6 +155,7 @@ class EdgeModel:
 
     def run(self, x: np.ndarray, max_width: int = 4096) -> np.ndarray:
         x = np.ascontiguousarray(x, dtype=np.float32)
+        max_width = max(max_width, _L().sx_edge_max_width(self._h, x.shape[1]))  # never smaller than the model needs
         y = np.zeros((x.shape[0], max_width), dtype=np.float32)
         d = _L().sx_edge_run(self._h, x.ctypes.data, x.shape[0], x.shape[1], y.ctypes.data, None)
         if d < 0:

@@ -1,0 +1,102 @@
+"""Malformed input never crashes a parser: random and mutated byte strings through the native codecs (WebSocket, MQTT,
+compression streams, checkpoint reader, tokenizer, edge model loader) and the Python ones (safetensors, hub container,
+ONNX). Each must return normally or raise a Python exception. Worth running against the sanitizer build of the host
+library (``_build.build_host_sanitized``)."""
+import os
+import random
+import struct
+
+import numpy as np
+import pytest
+import torch
+
+from sneppx_alg_b200.utils import mm, net
+
+CLEAN = (ValueError, KeyError, IndexError, OSError, RuntimeError, EOFError, OverflowError, UnicodeDecodeError, AssertionError,
+         TypeError, BufferError, MemoryError, struct.error)
+
+
+def _mutations(seed_bytes, rng, n):
+    for _ in range(n):
+        b = bytearray(seed_bytes)
+        for _ in range(rng.randint(1, 6)):
+            op = rng.randint(0, 3)
+            if op == 0 and b:
+                b[rng.randrange(len(b))] = rng.randrange(256)
+            elif op == 1 and b:
+                del b[rng.randrange(len(b)):rng.randrange(len(b)) + rng.randint(1, 8)]
+            elif op == 2:
+                at = rng.randrange(len(b) + 1)
+                b[at:at] = bytes(rng.randrange(256) for _ in range(rng.randint(1, 8)))
+            elif b:
+                b = b[: rng.randrange(len(b))]
+        yield bytes(b)
+    for _ in range(n // 4):
+        yield bytes(rng.randrange(256) for _ in range(rng.randint(0, 64)))
+
+
+def _survives(fn, data):
+    try:
+        fn(data)
+    except CLEAN:
+        pass
+
+
+def test_native_wire_codecs_survive_garbage():
+    rng = random.Random(1)
+    ws = net.ws_encode(b"payload" * 30, opcode=2, mask_key=0x01020304)
+    for d in _mutations(ws, rng, 300):
+        _survives(net.ws_decode, d)
+    pkt = net.mqtt_publish("a/b/c", b"x" * 40, qos=1, packet_id=7)
+    for d in _mutations(pkt, rng, 300):
+        _survives(net.mqtt_parse, d)
+    x = np.random.default_rng(0).standard_normal(200).astype(np.float32)
+    for codec in ("bfp8", "bfp4", "sparse", "none"):
+        s = mm.compress(x, codec, threshold=0.5)
+        for d in _mutations(s, rng, 150):
+            _survives(lambda b: mm.decompress(b, 200), d)
+
+
+def test_checkpoint_and_weight_file_readers_survive_garbage(tmp_path):
+    from sneppx_alg_b200.checkpoint.sneppx_format import load_tensors, save_tensors, validate_checkpoint
+    from sneppx_alg_b200.hub import formats
+    rng = random.Random(2)
+    good = tmp_path / "ok.sneppx"
+    save_tensors(str(good), {"w": torch.randn(4, 5), "b": torch.arange(3).float()}, {"step": 7})
+    seeds = {"sneppx": good.read_bytes()}
+    formats.save_safetensors(str(tmp_path / "ok.safetensors"), {"w": torch.randn(2, 3)})
+    seeds["safetensors"] = (tmp_path / "ok.safetensors").read_bytes()
+    formats.save_hub_container(str(tmp_path / "ok.hub"), {"w": torch.randn(2, 3)}, {"name": "m"})
+    seeds["hub"] = (tmp_path / "ok.hub").read_bytes()
+    loaders = {"sneppx": lambda p: (validate_checkpoint(p), load_tensors(p)), "safetensors": formats.load_safetensors,
+               "hub": formats.load_hub_container}
+    for kind, seed in seeds.items():
+        for i, d in enumerate(_mutations(seed, rng, 120)):
+            p = tmp_path / f"bad_{kind}.bin"
+            p.write_bytes(d)
+            _survives(loaders[kind], str(p))
+
+
+def test_tokenizer_edge_and_onnx_loaders_survive_garbage(tmp_path):
+    from sneppx_alg_b200.onnx import toolkit
+    from sneppx_alg_b200.utils.host import BPETokenizer, EdgeModel, write_edge_model
+    rng = random.Random(3)
+    tok = BPETokenizer()
+    tok.train("the quick brown fox jumps over the lazy dog " * 20, 300)
+    tp = tmp_path / "tok.bin"
+    tok.save(str(tp))
+    for d in _mutations(tp.read_bytes(), rng, 120):
+        p = tmp_path / "bad_tok.bin"
+        p.write_bytes(d)
+        _survives(lambda q: BPETokenizer().load(q).encode("hello fox"), str(p))
+    ep = tmp_path / "m.edge"
+    write_edge_model(str(ep), [("matmul", np.ones((4, 3), np.float32)), ("bias", np.zeros(3, np.float32)), ("relu",)])
+    for d in _mutations(ep.read_bytes(), rng, 120):
+        p = tmp_path / "bad.edge"
+        p.write_bytes(d)
+        _survives(lambda q: EdgeModel(q).run(np.ones((2, 4), np.float32), max_width=64), str(p))
+    lin = torch.nn.Linear(4, 3)
+    model = toolkit.export_module(lin, torch.randn(2, 4))
+    blob = model.serialize() if hasattr(model, "serialize") else model.to_bytes()
+    for d in _mutations(blob, rng, 200):
+        _survives(lambda b: toolkit.check_model(toolkit.Model.parse(b)), d)
