@@ -128,13 +128,85 @@ class LlamaPagedRunner:
         return ops.linear(h[:, -1], m.head_weight()).float()
 
 
+class _Slots:
+    def __init__(self, n):
+        self.num_free = n
+
+
+class StateCache:
+    """Admission bookkeeping for models whose per-sequence memory is a fixed-size recurrent state (Mamba-2 / HSS):
+    one slot per running sequence instead of KV blocks. Offers the few calls the engine makes on a cache."""
+
+    block_size = 1 << 30   # any request needs one "block"
+
+    def __init__(self, max_sequences: int, on_free=None):
+        self.pool = _Slots(max_sequences)
+        self._live, self._on_free = set(), on_free
+
+    def add_sequence(self, seq_id, prompt):
+        self.pool.num_free -= 1
+        self._live.add(seq_id)
+        return 0   # no prefix reuse: the state after a prefix is not kept
+
+    def free_sequence(self, seq_id, tokens=None):
+        if seq_id in self._live:
+            self._live.discard(seq_id)
+            self.pool.num_free += 1
+            if self._on_free:
+                self._on_free(seq_id)
+
+
+class StatefulRunner:
+    """Runs any model that follows the generation contract ``forward(input_ids, past_key_values, use_cache) ->
+    {"logits", "past_key_values"}`` with a per-layer state of tensors batched along dim 0 (``Mamba2ForCausalLM``: a
+    list of {"conv", "ssm"} dicts). Prefill runs one sequence; decode stacks the states of all running sequences,
+    advances them together by one token, and splits them again."""
+
+    def __init__(self, model):
+        self.model = model
+        self.states = {}
+
+    def release(self, seq_id):
+        self.states.pop(seq_id, None)
+
+    @torch.no_grad()
+    def prefill(self, seq_id: int, tokens: List[int], start: int):
+        dev = next(self.model.parameters()).device
+        ids = torch.tensor(tokens[start:], dtype=torch.long, device=dev).unsqueeze(0)
+        out = self.model(ids, use_cache=True)
+        self.states[seq_id] = out["past_key_values"]
+        return out["logits"][:, -1].float()
+
+    @staticmethod
+    def _stack(states):
+        first = states[0]
+        return [{k: (None if first[li][k] is None else torch.cat([s[li][k] for s in states], dim=0)) for k in first[li]}
+                for li in range(len(first))]
+
+    @torch.no_grad()
+    def decode(self, seq_ids: List[int], last_tokens: List[int]):
+        dev = next(self.model.parameters()).device
+        batched = self._stack([self.states[s] for s in seq_ids])
+        ids = torch.tensor(last_tokens, dtype=torch.long, device=dev).unsqueeze(1)
+        out = self.model(ids, past_key_values=batched, use_cache=True)
+        new = out["past_key_values"]
+        for b, s in enumerate(seq_ids):
+            self.states[s] = [{k: (None if v is None else v[b:b + 1].clone()) for k, v in layer.items()} for layer in new]
+        return out["logits"][:, -1].float()
+
+
 class LLMEngine:
     def __init__(self, model, num_blocks=2048, block_size=16, max_batch_size=32, max_prefill_tokens=8192,
                  policy="fcfs", enable_prefix_cache=True, runner=None):
         cfg = model.config
         p = next(model.parameters())
-        self.cache = PagedKVCache(cfg.num_hidden_layers, num_blocks, block_size, cfg.num_key_value_heads, cfg.head_dim,
-                                  dtype=p.dtype, device=p.device, enable_prefix_cache=enable_prefix_cache)
+        if runner is None and getattr(cfg, "architecture", "transformer") == "mamba2":
+            runner = StatefulRunner(model)   # recurrent-state models: no KV cache, one state slot per sequence
+        if isinstance(runner, StatefulRunner):
+            self.cache = StateCache(max_batch_size, on_free=runner.release)
+        else:
+            self.cache = PagedKVCache(cfg.num_hidden_layers, num_blocks, block_size, cfg.num_key_value_heads, cfg.head_dim,
+                                      dtype=p.dtype, device=p.device, enable_prefix_cache=enable_prefix_cache)
         self.runner = runner or LlamaPagedRunner(model, self.cache)
         self.max_batch_size, self.max_prefill_tokens, self.policy = max_batch_size, max_prefill_tokens, policy
         self.waiting: List[Request] = []

@@ -60,3 +60,28 @@ def test_sampling_filters():
     model = _model()
     outs = batch_generate(model, [torch.tensor([1, 2, 3]), torch.tensor([4, 5])], max_new_tokens=3)
     assert len(outs[0]) == 6 and len(outs[1]) == 5
+
+
+def test_engine_serves_recurrent_state_models():
+    """Mamba-2 through the continuous-batching engine: tokens equal the model's own greedy decoding from a full
+    re-forward at every step, for requests of different lengths that join and leave the batch at different times."""
+    import torch
+    from sneppx_alg_b200.models import ModelConfig, build_model
+    from sneppx_alg_b200.serving.llm_engine import LLMEngine, SamplingParams, StatefulRunner
+    torch.manual_seed(0)
+    cfg = ModelConfig(architecture="mamba2", hidden_size=32, num_hidden_layers=2, vocab_size=96, ssm_state_size=8,
+                      ssm_conv_kernel=4, ssm_expand=2, ssm_head_dim=8, ssm_ngroups=1, ssm_chunk_size=8, rms_norm_eps=1e-5)
+    model = build_model(cfg).eval()
+    prompts = [[5, 9, 33, 2, 7], [11, 12], [70, 3, 3, 8, 1, 2, 90, 4, 6]]
+    lens = [6, 3, 4]
+    eng = LLMEngine(model, max_batch_size=2)   # two slots for three requests: the third joins when one finishes
+    assert isinstance(eng.runner, StatefulRunner)
+    ids = [eng.submit(p, SamplingParams(max_new_tokens=n)) for p, n in zip(prompts, lens)]
+    eng.run_until_done()
+    for rid, p, n in zip(ids, prompts, lens):
+        seq = list(p)
+        with torch.no_grad():
+            for _ in range(n):
+                seq.append(int(model(torch.tensor([seq]))["logits"][0, -1].argmax()))
+        assert eng.finished[rid].output == seq[len(p):]
+    assert eng.runner.states == {} and eng.cache.pool.num_free == 2
