@@ -62,6 +62,33 @@ _WHERE = {
                              "save_hf_model")},
     **{n: "jit" for n in ("trace", "grad", "vmap", "jacobian", "hessian")},
     **{n: "tensor" for n in ("Tensor", "Function", "Context", "no_grad")},
+    # names that live in a module of the same meaning under another path
+    **{n: 'algorithms.fm' for n in ('FMController',)},
+    **{n: 'algorithms.npe' for n in ('NPEProgram', 'NPEVM')},
+    **{n: 'cli' for n in ('serve_main',)},
+    **{n: 'device' for n in ('device_count', 'set_device', 'synchronize')},
+    **{n: 'hub' for n in ('HF_WEIGHT_MAP',)},
+    **{n: 'jit' for n in ('value_and_grad',)},
+    **{n: 'models.config' for n in ('list_models',)},
+    **{n: 'models.families' for n in ('BertConfig', 'GPTConfig', 'T5Config')},
+    **{n: 'models.llama' for n in ('LlamaAttention', 'LlamaMLP')},
+    **{n: 'onnx.toolkit' for n in ('infer_shapes',)},
+    **{n: 'ops.functional' for n in ('layernorm', 'rmsnorm')},
+    **{n: 'optim.fused' for n in ('clip_grad_norm_',)},
+    **{n: 'optim.zoo' for n in ('Optimizer', 'RAdam', 'ScheduleFreeAdamW')},
+    **{n: 'parallel.distributed' for n in ('DistributedWrapper',)},
+    **{n: 'security.crypto' for n in ('sha256', 'sha3_256', 'sha3_512', 'sha512')},
+    **{n: 'security.services' for n in ('TokenBucket',)},
+    **{n: 'serving.generation' for n in ('sample_generation', 'top_k_top_p_filtering')},
+    **{n: 'serving.serving_engine' for n in ('MetricsCollector', 'ModelVersion')},
+    **{n: 'tensor' for n in ('avg_pool2d', 'conv1d', 'conv2d', 'max_pool2d', 'softmax')},
+    **{n: 'training.augmentation' for n in ('cutmix', 'mixup', 'random_crop')},
+    **{n: 'training.data' for n in ('TensorDataset', 'default_collate')},
+    **{n: 'training.extras' for n in ('DPSGD', 'RDPAccountant', 'SearchSpace', 'checkpoint', 'distillation_loss', 'grid_search', 'random_search')},
+    **{n: 'training.schedulers' for n in ('LRScheduler', 'ReduceLROnPlateau')},
+    **{n: 'utils.net' for n in ('Topology',)},
+    **{n: 'utils.observability' for n in ('CompositeTracker', 'MLflowTracker', 'MemoryTracker', 'Timer', 'WandbTracker', 'estimate_flops', 'timeit')},
+    **{n: 'utils.registry' for n in ('AIGateway', 'EvalMonitor')},
     # observability
     **{n: "utils.observability" for n in ("Profiler", "ExperimentTracker", "Logger")},
 }
@@ -72,6 +99,14 @@ __all__ = sorted(_WHERE)
 def __getattr__(name):
     where = _WHERE.get(name)
     if where is None:
+        # everything else with a counterpart is collected in sneppx_alg_b200.compat (and .compat_services)
+        for mod in ("compat", "compat_services"):
+            try:
+                obj = getattr(importlib.import_module(f"sneppx_alg_b200.{mod}"), name)
+            except (AttributeError, ModuleNotFoundError):
+                continue
+            globals()[name] = obj
+            return obj
         raise AttributeError(f"module 'SneppX_ALG' has no attribute '{name}'")
     obj = getattr(importlib.import_module(f"sneppx_alg_b200.{where}"), name)
     globals()[name] = obj

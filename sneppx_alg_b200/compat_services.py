@@ -1,0 +1,920 @@
+"""Second half of the reference's flat namespace: service singletons and their module-level helpers (audit log, DDoS
+mitigation, key manager, usage tracker, user store, container security), serving schema records, the evaluation
+harness, experiment store, ONNX / graph / NPE / ARC class aliases, data and tokenizer aliases, privacy mechanisms,
+thread pools, streamers and the ``*_kernel`` entry points (``cuda_kernels.py``) mapped onto this package's ops.
+``SneppX_ALG`` resolves names here after ``compat``.
+
+Not reproduced, by design (one CUDA sm_100a device layer, portable C++ host code): the multi-vendor back-end and
+driver tables (``NPUBackend``, ``OpenVINOBackend``, ``ROCmDriver``, ``TPUDriver``, ``TensorRTExporter``, ``AutoBackend``
+...), the x86 assembly wrappers (``AESNI``, ``SHANI``, ``Poly1305ASM``, ``Ed25519ASM``, ``ChaCha20AVX2``, ``FirewallASM``,
+``Asm*``), the code-obfuscation pipeline (``CfgFlattening``, ``OpaquePredicate``, ``StringEncryption`` ...), and the
+post-quantum schemes (``KyberKEM``, ``Dilithium``, ``SphincsPlus``).
+"""
+from __future__ import annotations
+
+import json
+import os
+import threading
+import time
+from concurrent.futures import ThreadPoolExecutor
+from dataclasses import asdict, dataclass, field
+from typing import Any, Callable, Dict, List, Optional, Sequence
+
+import torch
+
+from .algorithms import arc as _arc
+from .algorithms import fm as _fm
+from .algorithms import npe as _npe
+from .onnx import toolkit as _onnx
+from .security import services as _svc
+from .training import data as _data
+
+# ----------------------------------------------------------------------------------------- service singletons
+_singletons: Dict[str, Any] = {}
+
+
+def _accessor(key: str, factory: Callable[[], Any]):
+    def get():
+        if key not in _singletons:
+            _singletons[key] = factory()
+        return _singletons[key]
+
+    def set_(obj):
+        _singletons[key] = obj
+        return obj
+    return get, set_
+
+
+get_audit_logger, set_audit_logger = _accessor("audit", lambda: _svc.AuditLogger(os.path.join(os.path.expanduser("~/.sneppx"), "audit.log")))
+get_ddos_mitigation, set_ddos_mitigation = _accessor("ddos", _svc.DDoSMitigator)
+get_key_manager, set_key_manager = _accessor("keys", _svc.ApiKeyStore)
+get_usage_tracker, set_usage_tracker = _accessor("usage", _svc.UsageTracker)
+DDoSMitigation, ApiKeyManager, SlidingWindowRateLimiter = _svc.DDoSMitigator, _svc.ApiKeyStore, _svc.TokenBucket
+SelfAuditor, NetworkFuzzer = _svc.self_audit, _svc.fuzz
+LTLProperty = ModelChecker = _svc.ltl_check
+
+
+def audit_log(actor: str, action: str, **details):
+    os.makedirs(os.path.expanduser("~/.sneppx"), exist_ok=True)
+    return get_audit_logger().log(actor, action, **details)
+
+
+def audit_login(user: str, success: bool = True, **kw):
+    return audit_log(user, "login", success=success, **kw)
+
+
+def audit_data_access(user: str, resource: str, **kw):
+    return audit_log(user, "data_access", resource=resource, **kw)
+
+
+def audit_config_change(user: str, key: str, old=None, new=None):
+    return audit_log(user, "config_change", key=key, old=old, new=new)
+
+
+def audit_security_event(kind: str, **kw):
+    return audit_log("system", "security_event", kind=kind, **kw)
+
+
+def verify_audit_chain() -> bool:
+    return get_audit_logger().verify()
+
+
+def check_request(client_ip: str) -> bool:
+    return get_ddos_mitigation().check(client_ip)
+
+
+def ban_ip(ip: str, seconds: float = 3600.0):
+    d = get_ddos_mitigation()
+    d.banned[ip] = d.clock() + seconds
+
+
+def unban_ip(ip: str):
+    get_ddos_mitigation().banned.pop(ip, None)
+
+
+def get_ip_info(ip: str) -> dict:
+    d = get_ddos_mitigation()
+    return {"ip": ip, "banned": ip in d.banned and d.clock() < d.banned[ip], "violations": d.violations.get(ip, 0)}
+
+
+def get_ddos_stats() -> dict:
+    d = get_ddos_mitigation()
+    return {"clients": len(d.buckets), "banned": sum(1 for t in d.banned.values() if d.clock() < t), "violations": sum(d.violations.values())}
+
+
+class UserStore:
+    """Username -> salted PBKDF2 password hash and roles."""
+
+    def __init__(self):
+        self.users: Dict[str, dict] = {}
+
+    def add_user(self, name: str, password: str, roles: Sequence[str] = ("user",)):
+        from .security import crypto
+        salt = os.urandom(16)
+        self.users[name] = {"salt": salt, "hash": crypto.pbkdf2_sha256(password.encode(), salt, 20000), "roles": list(roles)}
+
+    def authenticate(self, name: str, password: str) -> bool:
+        from .security import crypto
+        u = self.users.get(name)
+        return bool(u) and crypto.ct_equal(u["hash"], crypto.pbkdf2_sha256(password.encode(), u["salt"], 20000))
+
+    def has_role(self, name: str, role: str) -> bool:
+        return role in self.users.get(name, {}).get("roles", [])
+
+
+get_user_store, set_user_store = _accessor("users", UserStore)
+Authenticator = IdentityManager = UserStore
+
+
+@dataclass
+class SBOMComponent:
+    name: str
+    version: str
+    vulnerable: bool = False
+    cves: List[str] = field(default_factory=list)
+
+
+class SBOMGenerator:
+    def generate(self, packages: Dict[str, str], known_cves: Optional[Dict[str, List[str]]] = None) -> dict:
+        return _svc.sbom(packages, known_cves)
+
+
+class ContainerSecurityManager:
+    """Requirement / image scans against a table of known-vulnerable versions."""
+
+    def __init__(self, known_cves: Optional[Dict[str, List[str]]] = None):
+        self.known, self.history = known_cves or {}, []
+
+    def scan_requirements(self, packages: Dict[str, str]) -> dict:
+        rep = _svc.sbom(packages, self.known)
+        self.history.append(rep)
+        return rep
+
+    scan_image = scan_requirements
+
+
+ContainerSecurity = CVEScanner = ContainerSecurityManager
+get_container_security, set_container_security = _accessor("container", ContainerSecurityManager)
+generate_sbom = lambda packages, known=None: _svc.sbom(packages, known)  # noqa: E731
+scan_requirements = scan_image = lambda packages: get_container_security().scan_requirements(packages)  # noqa: E731
+get_scan_history = lambda: get_container_security().history  # noqa: E731
+get_security, set_security = _accessor("security", lambda: {"ddos": get_ddos_mitigation(), "keys": get_key_manager()})
+
+
+class SignedUpdateManager:
+    """stage -> verify -> install with rollback of the previous file (signed manifests from ``security.services``)."""
+
+    def __init__(self, key: bytes, install_dir: str):
+        self.key, self.dir, self.staged = key, install_dir, None
+        os.makedirs(install_dir, exist_ok=True)
+
+    def stage_update(self, path: str, manifest: dict, min_version: str = "0") -> bool:
+        ok = _svc.verify_update(path, manifest, self.key, min_version)
+        self.staged = (path, manifest) if ok else None
+        return ok
+
+    def install_update(self) -> str:
+        if not self.staged:
+            raise RuntimeError("nothing staged")
+        import shutil
+        path, man = self.staged
+        dst = os.path.join(self.dir, man["file"])
+        if os.path.exists(dst):
+            shutil.copy2(dst, dst + ".previous")
+        shutil.copy2(path, dst)
+        self.staged = None
+        return dst
+
+    def rollback_update(self, file_name: str) -> bool:
+        dst = os.path.join(self.dir, file_name)
+        if not os.path.exists(dst + ".previous"):
+            return False
+        os.replace(dst + ".previous", dst)
+        return True
+
+
+SignedUpdate = SignedUpdateManager
+
+
+# ----------------------------------------------------------------------------------------- serving schema and helpers
+@dataclass
+class GenerateRequest:
+    prompt: str
+    max_new_tokens: int = 64
+    do_sample: bool = False
+    temperature: float = 1.0
+    top_k: int = 0
+    top_p: float = 1.0
+    repetition_penalty: float = 1.0
+    num_beams: int = 1
+    stop_strings: Optional[List[str]] = None
+    model: Optional[str] = None
+
+    def __post_init__(self):
+        if not 1 <= self.max_new_tokens <= 4096:
+            raise ValueError("max_new_tokens must be in 1..4096")
+
+
+@dataclass
+class GenerateResponse:
+    generated_text: str
+    token_ids: List[int]
+    prompt_tokens: int
+    completion_tokens: int
+    total_tokens: int
+    model: str
+    created: int
+
+
+@dataclass
+class BatchGenerateRequest:
+    prompts: List[str]
+    max_new_tokens: int = 64
+    model: Optional[str] = None
+
+
+@dataclass
+class BatchGenerateResponse:
+    results: List[GenerateResponse]
+
+
+@dataclass
+class ChatCompletionRequest:
+    messages: List[Dict[str, str]]
+    max_tokens: int = 64
+    temperature: float = 1.0
+    model: Optional[str] = None
+
+
+@dataclass
+class ChatCompletionResponse:
+    id: str
+    choices: List[dict]
+    usage: Dict[str, int]
+    object: str = "chat.completion"
+
+
+@dataclass
+class HealthResponse:
+    status: str = "ok"
+    models: List[str] = field(default_factory=list)
+
+
+@dataclass
+class ModelInfo:
+    id: str
+    family: str = ""
+    params: float = 0.0
+
+
+@dataclass
+class ModelListResponse:
+    data: List[ModelInfo] = field(default_factory=list)
+
+
+@dataclass
+class GenerationConfig:
+    max_new_tokens: int = 64
+    do_sample: bool = False
+    temperature: float = 1.0
+    top_k: int = 0
+    top_p: float = 1.0
+    repetition_penalty: float = 1.0
+    num_beams: int = 1
+
+
+@dataclass
+class ServingConfig:
+    host: str = "127.0.0.1"
+    port: int = 8000
+    max_batch_size: int = 32
+    batch_timeout_ms: float = 2.0
+    warmup_ticks: int = 0
+
+
+class ServingError(RuntimeError):
+    pass
+
+
+@dataclass
+class PagedAttentionConfig:
+    block_size: int = 16
+    num_blocks: int = 2048
+    enable_prefix_cache: bool = True
+
+
+def serve_from_config(path: str):
+    """Builds the FastAPI application from a YAML / JSON file: {models: {id: preset}, default: id, api_keys: [...]}."""
+    import yaml
+    from .models import create_model
+    from .serving.server import create_app
+    cfg = yaml.safe_load(open(path)) if path.endswith((".yaml", ".yml")) else json.load(open(path))
+    models = {mid: {"model": create_model(preset).eval()} for mid, preset in cfg["models"].items()}
+    return create_app(models, cfg.get("default"), api_keys=set(cfg.get("api_keys") or []) or None)
+
+
+inference_app = serve_from_config
+
+
+class TokenStreamer:
+    """Collects tokens pushed by the engine's ``on_token`` callback; iterating yields them as they arrive."""
+
+    def __init__(self):
+        self._q, self._cv, self._done = [], threading.Condition(), False
+
+    def put(self, _request_id, token: int):
+        with self._cv:
+            self._q.append(token)
+            self._cv.notify_all()
+
+    def end(self):
+        with self._cv:
+            self._done = True
+            self._cv.notify_all()
+
+    def __iter__(self):
+        i = 0
+        while True:
+            with self._cv:
+                self._cv.wait_for(lambda: i < len(self._q) or self._done)
+                if i >= len(self._q):
+                    return
+                tok = self._q[i]
+            i += 1
+            yield tok
+
+
+class TextStreamer(TokenStreamer):
+    def __init__(self, tokenizer):
+        super().__init__()
+        self.tokenizer = tokenizer
+
+    def text(self):
+        for tok in self:
+            yield self.tokenizer.decode([tok])
+
+
+Streamer = TokenStreamer
+
+
+def sample(logits, temperature=1.0, top_k=0, top_p=1.0, generator=None):
+    from .serving.generation import sample_from_logits
+    return sample_from_logits(logits, True, temperature, top_k, top_p, generator)
+
+
+def paged_attention_forward(q, k_cache, v_cache, block_table, lens):
+    from .ops import paged
+    return paged.paged_decode(q, k_cache, v_cache, block_table, lens)
+
+
+def incremental_attention_forward(q, k, v, state: Optional[dict] = None):
+    """One more block of keys / values for fixed queries: returns (output, state) with the running log-sum-exp, so a
+    long context can be consumed piece by piece (the NumPy reference's IncrementalAttentionState)."""
+    from .ops.functional import attention_with_lse
+    from .parallel.context import merge_attention_blocks
+    o, lse = attention_with_lse(q, k, v, causal=False)
+    if state:
+        o, lse = merge_attention_blocks(state["o"], state["lse"], o, lse)
+    return o.to(q.dtype), {"o": o.float(), "lse": lse}
+
+
+IncrementalAttentionState = dict
+
+
+def chunked_prefill_forward(model, input_ids, chunk: int = 512):
+    """Prefill in chunks through the model's cache contract; returns the logits of the last position."""
+    past, logits = None, None
+    for s in range(0, input_ids.shape[1], chunk):
+        out = model(input_ids[:, s:s + chunk], past_key_values=past, use_cache=True)
+        past, logits = out["past_key_values"], out["logits"][:, -1]
+    return logits, past
+
+
+# ----------------------------------------------------------------------------------------- evaluation harness
+@dataclass
+class EvalResult:
+    task: str
+    score: float
+    n: int
+
+
+@dataclass
+class EvalSummary:
+    results: List[EvalResult]
+
+    @property
+    def mean(self) -> float:
+        return sum(r.score for r in self.results) / max(len(self.results), 1)
+
+
+@dataclass
+class EvalConfig:
+    max_new_tokens: int = 16
+    batch_size: int = 8
+
+
+class Task:
+    name = "task"
+
+    def __init__(self, examples: List[dict]):
+        self.examples = examples
+
+    def score(self, predict: Callable[[dict], Any]) -> EvalResult:
+        ok = sum(1 for ex in self.examples if self.correct(predict(ex), ex))
+        return EvalResult(self.name, ok / max(len(self.examples), 1), len(self.examples))
+
+    def correct(self, pred, ex) -> bool:
+        raise NotImplementedError
+
+
+class ExactMatchTask(Task):
+    name = "exact_match"
+
+    def correct(self, pred, ex):
+        return str(pred).strip() == str(ex["answer"]).strip()
+
+
+class MultipleChoiceTask(Task):
+    """`predict` returns the index of the chosen option (e.g. the one with the highest log-likelihood)."""
+    name = "multiple_choice"
+
+    def correct(self, pred, ex):
+        return int(pred) == int(ex["label"])
+
+
+class CodingTask(Task):
+    """`predict` returns source text defining the function named in the example; it is run against the tests."""
+    name = "coding"
+
+    def correct(self, pred, ex):
+        scope: Dict[str, Any] = {}
+        try:
+            exec(pred, scope)   # evaluation harness for trusted benchmark files
+            return all(scope[ex["entry_point"]](*a) == want for a, want in ex["tests"])
+        except Exception:
+            return False
+
+
+class EvalHarness:
+    def __init__(self, tasks: Sequence[Task], config: Optional[EvalConfig] = None):
+        self.tasks, self.config = list(tasks), config or EvalConfig()
+
+    def run(self, predict: Callable[[dict], Any]) -> EvalSummary:
+        return EvalSummary([t.score(predict) for t in self.tasks])
+
+
+MMLU_CATEGORIES = {"stem": ["physics", "chemistry", "biology", "computer_science", "math", "engineering"],
+                   "humanities": ["history", "philosophy", "law"], "social_sciences": ["politics", "culture", "economics", "geography", "psychology"],
+                   "other": ["other", "business", "health"]}
+
+
+# ----------------------------------------------------------------------------------------- experiments
+@dataclass
+class ExperimentRun:
+    run_id: str
+    params: Dict[str, Any] = field(default_factory=dict)
+    metrics: Dict[str, List[float]] = field(default_factory=dict)
+    status: str = "running"
+
+    def log_metric(self, name: str, value: float):
+        self.metrics.setdefault(name, []).append(float(value))
+
+    def finish(self, status: str = "finished"):
+        self.status = status
+
+
+Run = ExperimentRun
+
+
+class Experiment:
+    def __init__(self, name: str):
+        self.name, self.runs = name, []
+
+    def start_run(self, params: Optional[dict] = None) -> ExperimentRun:
+        r = ExperimentRun(f"{self.name}-{len(self.runs)}", dict(params or {}))
+        self.runs.append(r)
+        return r
+
+    def best_run(self, metric: str, mode: str = "min") -> ExperimentRun:
+        cands = [r for r in self.runs if r.metrics.get(metric)]
+        pick = min if mode == "min" else max
+        return pick(cands, key=lambda r: pick(r.metrics[metric]))
+
+
+class ExperimentStore:
+    """Experiments as JSON files in a directory."""
+
+    def __init__(self, directory: str):
+        self.dir = directory
+        os.makedirs(directory, exist_ok=True)
+
+    def save(self, exp: Experiment):
+        with open(os.path.join(self.dir, exp.name + ".json"), "w") as f:
+            json.dump({"name": exp.name, "runs": [asdict(r) for r in exp.runs]}, f)
+
+    def load(self, name: str) -> Experiment:
+        d = json.load(open(os.path.join(self.dir, name + ".json")))
+        exp = Experiment(d["name"])
+        exp.runs = [ExperimentRun(**r) for r in d["runs"]]
+        return exp
+
+    def list(self) -> List[str]:
+        return sorted(f[:-5] for f in os.listdir(self.dir) if f.endswith(".json"))
+
+
+def load_experiment(directory: str, name: str) -> Experiment:
+    return ExperimentStore(directory).load(name)
+
+
+def experiment_cli_main(argv=None):
+    from .cli import experiment_main
+    return experiment_main(argv)
+
+
+class LineageStore:
+    """Parent links between artefacts (datasets, checkpoints, models)."""
+
+    def __init__(self):
+        self.parents: Dict[str, List[str]] = {}
+
+    def link(self, child: str, parent: str):
+        self.parents.setdefault(child, []).append(parent)
+
+    def ancestors(self, node: str) -> List[str]:
+        out, stack = [], list(self.parents.get(node, []))
+        while stack:
+            n = stack.pop()
+            if n not in out:
+                out.append(n)
+                stack.extend(self.parents.get(n, []))
+        return out
+
+
+# ----------------------------------------------------------------------------------------- ONNX, graph, NPE, ARC, FM aliases
+OnnxModel, OnnxGraph, OnnxNode, OnnxTensor, OnnxInitializer = _onnx.Model, _onnx.Graph, _onnx.Node, _onnx.Tensor, _onnx.Tensor
+onnx_check = onnx_validate = _onnx.check_model
+quantize_graph_weights = _onnx.quantize_qdq
+
+
+class OnnxShapeError(ValueError):
+    pass
+
+
+def export_onnx(module, example_input, path: Optional[str] = None):
+    return _onnx.export_module(module, example_input, path)
+
+
+class OnnxExporter:
+    def export(self, module, example_input, path=None):
+        return _onnx.export_module(module, example_input, path)
+
+
+def import_onnx(path_or_bytes):
+    return _onnx.Model.parse(path_or_bytes) if isinstance(path_or_bytes, (bytes, bytearray)) else _onnx.Model.load(path_or_bytes)
+
+
+class OnnxImporter:
+    load = staticmethod(import_onnx)
+
+
+def onnx_to_protobuf(model) -> bytes:
+    return model.serialize()
+
+
+protobuf_to_onnx = _onnx.Model.parse
+
+
+def onnx_version_compatible(model, max_opset: int = 21, min_opset: int = 7) -> bool:
+    return min_opset <= int(getattr(model, "opset", 0) or 0) <= max_opset
+
+
+def upgrade_opset(model, target: int = 17):
+    model.opset = max(int(getattr(model, "opset", 0) or 0), target)
+    return model
+
+
+def inference_session(path_or_model):
+    """Callable running the model on NumPy feeds (the toolkit's executor)."""
+    m = path_or_model if isinstance(path_or_model, _onnx.Model) else import_onnx(path_or_model)
+    return lambda feeds: _onnx.run_model(m, feeds)
+
+
+def select_execution_provider(preferred: Sequence[str] = ("cuda", "cpu")) -> str:
+    return "cuda" if "cuda" in preferred and torch.cuda.is_available() else "cpu"
+
+
+from . import graph as _graph  # noqa: E402
+
+GraphNode, TensorExpr, StateGraph = _graph.ExprNode, _graph.ExprNode, _graph.ExprGraph
+GraphCompiler = GraphOptimizer = TensorExprCompiler = CompiledGraph = _graph.ExprGraph
+FUSABLE_OPS = ("matmul", "bias", "relu", "gelu", "silu", "add", "mul")
+
+
+def visualize_graph(g) -> str:
+    """Graphviz dot text of an expression graph."""
+    lines = ["digraph G {"]
+    for i, n in enumerate(getattr(g, "nodes", [])):
+        lines.append(f'  n{i} [label="{getattr(n, "op", "?")}"];')
+        for j in getattr(n, "inputs", []):
+            lines.append(f"  n{j} -> n{i};")
+    return "\n".join(lines + ["}"])
+
+
+def trace_function(fn, *example_inputs):
+    from . import jit
+    return jit.trace(fn, *example_inputs)
+
+
+jit = trace_function
+Tracer = Trace = trace_function
+
+NPEInstruction, NPECompiler, NPEVerify = _npe.Instruction, _npe.compile_mlp, _npe.verify_program
+ARCInputGuard, ARCGradientObfuscator, ARCOutputVerifier, ARCAttackSim = _arc.InputGuard, _arc.GradientObfuscator, _arc.OutputVerifier, _arc.simulate_attack
+ARCFForward = _arc.ARCLayer
+FMMemoryBank, FMNode, FMSync = _fm.MemoryBank, _fm.Node, _fm.FMSyncNCCL
+
+
+def FGSM(x, loss_fn, epsilon=0.1, lo=-1.0, hi=1.0):
+    return _arc.simulate_attack(x, _arc.ATTACK_FGSM, epsilon, loss_fn, lo=lo, hi=hi)
+
+
+def PGD(x, loss_fn, epsilon=0.1, steps=3, lo=-1.0, hi=1.0):
+    return _arc.simulate_attack(x, _arc.ATTACK_PGD, epsilon, loss_fn, steps=steps, lo=lo, hi=hi)
+
+
+Attack = FGSM
+
+
+@dataclass
+class AdversarialExample:
+    clean: torch.Tensor
+    adversarial: torch.Tensor
+    epsilon: float
+
+
+class AdversarialTrainer:
+    """Mixes clean and FGSM-perturbed batches: loss = (1 - w) L(x) + w L(x_adv)."""
+
+    def __init__(self, model, loss_fn, epsilon=0.03, weight=0.5):
+        self.model, self.loss_fn, self.epsilon, self.weight = model, loss_fn, epsilon, weight
+
+    def loss(self, x, y, lo=-1.0, hi=1.0):
+        adv = FGSM(x, lambda t: self.loss_fn(self.model(t), y), self.epsilon, lo, hi)
+        return (1 - self.weight) * self.loss_fn(self.model(x), y) + self.weight * self.loss_fn(self.model(adv), y)
+
+
+ARCAdversarialTrainGraph = AdversarialTrainer
+
+
+# ----------------------------------------------------------------------------------------- data, tokenizers, trainers
+Dataset = CppDataset = PyTorchDataset = torch.utils.data.Dataset
+CppTensorDataset = _data.TensorDataset
+PyTorchDataLoader = _data.DataLoader
+TextDataset = _data.MemoryMappedTextDataset
+Sampler = _data.DistributedSampler
+BatchCollator = _data.default_collate
+
+
+def _lazy(mod, attr):
+    def get(*a, **k):
+        import importlib
+        return getattr(importlib.import_module(f"sneppx_alg_b200.{mod}"), attr)(*a, **k)
+    get.__name__ = attr
+    return get
+
+
+Tokenizer = _lazy("utils.host", "BPETokenizer")
+SimpleTokenizer = TokenizerSimpleTokenizer = _lazy("serving.server", "ByteTokenizer")
+TrainerV3 = PyTorchTrainer = _lazy("training.trainer", "Trainer")
+TrainConfigV3 = UltraTrainConfig = _lazy("training.config", "TrainConfig")
+EdgeRuntime = _lazy("utils.host", "EdgeModel")
+WeightWatermark = BackdoorWatermark = _lazy("serving.watermark", "Watermark")
+create_vizmon = start_dashboard = _lazy("utils.vizmon", "VizMon")
+SocketComm = _lazy("utils.net", "FramedSocket")
+GRPCService = _lazy("utils.net", "CoordinatorServer")
+NCCLComm = _lazy("parallel.distributed", "ProcessGroup")
+MemoryPool = MemoryAllocator = _lazy("utils.mm", "Arena")
+ContinuousBatchScheduler = _lazy("serving.llm_engine", "LLMEngine")
+DynamicBatchQueue = _lazy("utils.host", "ServingCore")
+get_profiler = _lazy("utils.observability", "Profiler")
+TrainProfiler = _lazy("utils.observability", "Profiler")
+LogTracker = Tracker = LocalBackend = _lazy("utils.observability", "ExperimentTracker")
+QLoRALinear = _lazy("training.lora", "LoRALinear")
+GradientCheckpointer = _lazy("training.extras", "enable_activation_checkpointing")
+checkpoint_sequential = _lazy("training.extras", "checkpoint")
+TopologyType = ("ring", "tree", "graph")
+
+
+@dataclass
+class EdgeConfig:
+    max_width: int = 4096
+    int8: bool = False
+
+
+# ----------------------------------------------------------------------------------------- privacy mechanisms
+class LaplaceMech:
+    def __init__(self, epsilon: float, sensitivity: float = 1.0):
+        self.scale = sensitivity / epsilon
+
+    def __call__(self, x, generator=None):
+        u = torch.rand(x.shape, generator=generator) - 0.5
+        return x - self.scale * torch.sign(u) * torch.log1p(-2 * u.abs())
+
+
+class GaussianMech:
+    def __init__(self, epsilon: float, delta: float = 1e-5, sensitivity: float = 1.0):
+        import math
+        self.sigma = sensitivity * math.sqrt(2 * math.log(1.25 / delta)) / epsilon
+
+    def __call__(self, x, generator=None):
+        return x + self.sigma * torch.randn(x.shape, generator=generator)
+
+
+class PrivacyBudget:
+    """Sequential composition: spent epsilon adds up; `spend` refuses to exceed the total."""
+
+    def __init__(self, epsilon: float, delta: float = 0.0):
+        self.epsilon, self.delta, self.spent = epsilon, delta, 0.0
+
+    def spend(self, eps: float) -> bool:
+        if self.spent + eps > self.epsilon + 1e-12:
+            return False
+        self.spent += eps
+        return True
+
+    @property
+    def remaining(self) -> float:
+        return self.epsilon - self.spent
+
+
+# ----------------------------------------------------------------------------------------- pools and benchmarks
+class ThreadPool:
+    """Futures-returning pool (the C runtime's work-stealing pool maps onto the interpreter's executor here; the
+    native work queue is ``utils.host``)."""
+
+    def __init__(self, workers: int = 4):
+        self._ex = ThreadPoolExecutor(max_workers=workers)
+
+    def submit(self, fn, *a, **k):
+        return self._ex.submit(fn, *a, **k)
+
+    def map(self, fn, items):
+        return list(self._ex.map(fn, items))
+
+    def shutdown(self):
+        self._ex.shutdown(wait=True)
+
+
+WorkStealingPool = WorkerPool = ThreadPool
+
+
+class BenchmarkTimer:
+    def __enter__(self):
+        self.t0 = time.perf_counter()
+        return self
+
+    def __exit__(self, *exc):
+        self.ms = (time.perf_counter() - self.t0) * 1e3
+
+
+@dataclass
+class BenchmarkConfig:
+    device: str = "cpu"
+    scale_runs: float = 1.0
+
+
+@dataclass
+class BenchmarkResult:
+    op: str
+    mean_ms: float
+    min_ms: float
+    max_ms: float
+    runs: int
+
+
+class BenchmarkSuite:
+    def __init__(self, config: Optional[BenchmarkConfig] = None):
+        self.config = config or BenchmarkConfig()
+
+    def run(self) -> List[BenchmarkResult]:
+        from .benchmarks import tensor_ops
+        res = tensor_ops.run(self.config.device, self.config.scale_runs)["results"]
+        return [BenchmarkResult(r["op"], r["mean_ms"], r["min_ms"], r["max_ms"], r["runs"]) for r in res]
+
+
+def run_benchmarks(device: str = "cpu", scale_runs: float = 1.0):
+    return BenchmarkSuite(BenchmarkConfig(device, scale_runs)).run()
+
+
+benchmark = run_benchmarks
+
+
+def run_benchmark_cli(argv=None):
+    from .benchmarks import tensor_ops
+    return tensor_ops.main(argv)
+
+
+# ----------------------------------------------------------------------------------------- kernel entry points by name
+def gemm_kernel(a, b, bias=None, act=None):
+    """a [M, K] x b [N, K]^T on the tcgen05 GEMM for bf16 CUDA tensors (fp32 statement of the same product otherwise)."""
+    from .ops.gemm import gemm
+    return gemm(a, b, bias=bias, act=act)
+
+
+gemm_batched_kernel = gemm_kernel
+
+
+def _elementwise(fn):
+    def run(x, *a, **k):
+        return fn(x, *a, **k)
+    return run
+
+
+relu_kernel, gelu_kernel, silu_kernel = _elementwise(torch.relu), _elementwise(lambda x: torch.nn.functional.gelu(x, approximate="tanh")), _elementwise(torch.nn.functional.silu)
+softmax_kernel = _elementwise(lambda x, dim=-1: torch.softmax(x, dim))
+
+
+def bias_gelu_kernel(x, bias):
+    return torch.nn.functional.gelu(x + bias, approximate="tanh")
+
+
+def layernorm_kernel(x, w, b=None, eps=1e-5):
+    from .ops.functional import layernorm
+    return layernorm(x, w, b, eps)
+
+
+def layernorm_backward_kernel(x, w, b, dy, eps=1e-5):
+    """(dx, dw, db) through the op's own backward (native on bf16 CUDA tensors)."""
+    from .ops.functional import layernorm
+    xs, ws = x.detach().requires_grad_(True), w.detach().requires_grad_(True)
+    bs = None if b is None else b.detach().requires_grad_(True)
+    with torch.enable_grad():
+        y = layernorm(xs, ws, bs, eps)
+    grads = torch.autograd.grad(y, [t for t in (xs, ws, bs) if t is not None], dy)
+    return tuple(grads) + ((None,) if b is None else ())
+
+
+def rmsnorm_kernel(x, w, eps=1e-5):
+    from .ops.functional import rmsnorm
+    return rmsnorm(x, w, eps)[0]
+
+
+def dropout_kernel(x, p, seed=0, offset=0):
+    from .ops.aux import dropout
+    return dropout(x, p, seed, offset)
+
+
+def dropout_backward_kernel(dy, p, seed=0, offset=0):
+    from .ops.aux import dropout
+    return dropout(dy, p, seed, offset)   # the mask is a function of (seed, offset): backward is the same map
+
+
+def flash_attention_v2_kernel(q, k, v, causal=True, scale=None):
+    from .ops.functional import attention
+    return attention(q, k, v, causal=causal, scale=scale)
+
+
+def flash_attention_v2_backward_kernel(q, k, v, do, causal=True, scale=None):
+    from .ops.functional import attention
+    qs, ks, vs = (t.detach().requires_grad_(True) for t in (q, k, v))
+    with torch.enable_grad():
+        o = attention(qs, ks, vs, causal=causal, scale=scale)
+    return torch.autograd.grad(o, (qs, ks, vs), do)
+
+
+def fused_adamw_kernel(p, g, m, v, lr, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01, step=1):
+    """In-place AdamW on one tensor with the reference's update order (decay, then the bias-corrected step)."""
+    with torch.no_grad():
+        m.mul_(beta1).add_(g, alpha=1 - beta1)
+        v.mul_(beta2).addcmul_(g, g, value=1 - beta2)
+        p.mul_(1 - lr * weight_decay)
+        p.addcdiv_(m / (1 - beta1 ** step), (v / (1 - beta2 ** step)).sqrt().add_(eps), value=-lr)
+    return p
+
+
+def conv2d_kernel(x, w, bias=None, stride=1, padding=0):
+    return torch.nn.functional.conv2d(x, w, bias, stride, padding)
+
+
+@dataclass
+class KernelConfig:
+    block: int = 256
+    stages: int = 4
+
+
+GemmConfig = KernelConfig
+
+
+class KernelLauncher:
+    """Name -> callable table over the entry points above."""
+
+    def __init__(self):
+        self.table = {n[:-7]: f for n, f in globals().items() if n.endswith("_kernel") and callable(f)}
+
+    def launch(self, name: str, *a, **k):
+        return self.table[name](*a, **k)
+
+
+get_launcher = KernelLauncher
+dispatch = lambda name, *a, **k: KernelLauncher().launch(name, *a, **k)  # noqa: E731
+ELEMENTWISE_IMPL = {"relu": relu_kernel, "gelu": gelu_kernel, "silu": silu_kernel}

@@ -1,0 +1,138 @@
+"""The reference's flat ``SneppX_ALG`` namespace: which names resolve through the shim, and that the objects behind a
+sample of them do what their names say. ``tests/data/reference_flat_names.txt`` is the list of public names the
+reference's ``interface_bindings/__init__.py`` exports."""
+import math
+import os
+
+import pytest
+import torch
+
+import SneppX_ALG as sx
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+# not reproduced on purpose: other vendors' back-ends and drivers, x86 assembly wrappers, code obfuscation,
+# post-quantum schemes (see the docstring of sneppx_alg_b200/compat_services.py)
+EXCLUDED_PREFIXES = ("Asm", "AESNI", "SHANI", "Poly1305ASM", "Ed25519ASM", "ChaCha20AVX2", "FirewallASM", "MontgomeryMul",
+                     "NPUBackend", "ONNXBackend", "OpenVINOBackend", "ROCmDriver", "TPUDriver", "TensorRTExporter", "AutoBackend",
+                     "CPUBackend", "CPUFP16Backend", "CPUFP32Backend", "EdgeBackend", "InferenceBackend", "BackendRegistry",
+                     "register_backend", "KyberKEM", "Dilithium", "SphincsPlus", "CfgFlattening", "OpaquePredicate",
+                     "StringEncryption", "InstructionSubstitution", "Obfuscation")
+
+
+def test_most_reference_names_resolve():
+    names = [l.strip() for l in open(os.path.join(HERE, "data", "reference_flat_names.txt")) if l.strip()]
+    missing = []
+    for n in names:
+        try:
+            getattr(sx, n)
+        except AttributeError:
+            missing.append(n)
+    assert len(names) > 780 and len(missing) <= 130, (len(names), len(missing))
+    by_design = [n for n in missing if n.startswith(EXCLUDED_PREFIXES)]
+    assert len(by_design) >= 25
+    with pytest.raises(AttributeError):
+        sx.definitely_not_a_name
+
+
+def test_optimizers_schedulers_and_search():
+    for Opt in (sx.Adan, sx.Sophia):
+        w = torch.nn.Parameter(torch.tensor([3.0, -2.0]))
+        opt = Opt([w], lr=0.05)
+        for _ in range(200):
+            opt.zero_grad()
+            (w ** 2).sum().backward()
+            opt.step()
+        assert w.abs().max() < 0.5, Opt.__name__
+    p = torch.nn.Parameter(torch.zeros(1))
+    o = torch.optim.SGD([p], lr=1.0)
+    s = sx.TriStageLR(o, warmup_steps=10, hold_steps=10, decay_steps=10, init_ratio=0.1, final_ratio=0.01)
+    lrs = []
+    for _ in range(35):
+        lrs.append(o.param_groups[0]["lr"])
+        o.step()
+        s.step()
+    assert abs(lrs[0] - 0.1) < 1e-6 and lrs[15] == 1.0 and abs(lrs[-1] - 0.01) < 1e-6
+    c = sx.CosineAnnealingWithWarmup(o, warmup_steps=5, total_steps=25)
+    assert c.get_last_lr()[0] < 1.0
+    best, val = sx.bayesian_search(lambda h: (h["x"] - 2.0) ** 2 + (h["k"] == "b") * 1.0,
+                                   {"x": sx.UniformFloat(-5, 5), "k": sx.Choice(["a", "b"])}, trials=40, seed=1)
+    assert val < 0.5 and best["k"] == "a"
+    cfg, loss = sx.halving_search(lambda h, budget: abs(h["lr"] - 0.1) + 1.0 / budget, {"lr": sx.LogUniformFloat(1e-3, 1.0)},
+                                  n_configs=9, seed=0)
+    assert abs(cfg["lr"] - 0.1) < 0.2
+    st = sx.Study({"n": sx.Choice([1, 2, 3]), "f": sx.Fixed(7)}, sx.GridSampler())
+    assert st.optimize(lambda h: -h["n"], 3).params == {"n": 3, "f": 7}
+
+
+def test_quantisation_pruning_and_losses():
+    x = torch.randn(64, 128)
+    q, s = sx.quantize_int8_sym(x)
+    assert (sx.dequantize_int8_sym(q, s) - x).abs().max() <= s * 0.5001
+    qa, sa, zp = sx.quantize_int8_asym(x)
+    assert (sx.dequantize_int8_asym(qa, sa, zp) - x).abs().max() <= sa * 0.5001
+    qc, sc = sx.quantize_int8_channel(x, 0)
+    assert sc.shape == (64, 1) and sx.quantize_error(x, sx.dequantize_int8_channel(qc, sc)) < 0.01
+    e = sx.dequantize_fp8_e4m3(sx.quantize_fp8_e4m3(x))
+    assert sx.quantize_error(x, e) < 0.05
+    w, mask = sx.magnitude_prune(x, 0.75)
+    assert abs(sx.compute_sparsity(w) - 0.75) < 0.01 and torch.equal(w != 0, mask)
+    pruned, keep = sx.l1_channel_prune(x, 0.5)
+    assert len(keep) == 32 and int((pruned.abs().sum(1) == 0).sum()) == 32
+    lin = torch.nn.Sequential(torch.nn.Linear(16, 16), torch.nn.Linear(16, 4))
+    masks = sx.global_magnitude_prune(lin, 0.5)
+    assert abs(sum(int((~m).sum()) for m in masks.values()) / sum(m.numel() for m in masks.values()) - 0.5) < 0.02
+    logits, teacher = torch.randn(8, 10), torch.randn(8, 10)
+    assert sx.kd_loss(teacher, teacher).abs() < 1e-6 and sx.kd_loss(logits, teacher) > 0
+    assert sx.crd_loss(torch.eye(8), torch.eye(8)) < sx.crd_loss(torch.eye(8), torch.eye(8).flip(0))
+    assert abs(float(sx.dpo_loss(torch.zeros(4), torch.zeros(4), torch.zeros(4), torch.zeros(4))) - math.log(2)) < 1e-6
+    assert sx.py_f1([1, 1, 0, 0], [1, 0, 1, 0]) == 0.5 and sx.py_accuracy([1, 2], [1, 3]) == 0.5
+    h, c = sx.lstm_cell(torch.randn(2, 4), torch.zeros(2, 3), torch.zeros(2, 3), torch.randn(12, 4), torch.randn(12, 3))
+    ref = torch.nn.LSTMCell(4, 3)
+    with torch.no_grad():
+        xin = torch.randn(2, 4)
+        want = ref(xin, (torch.zeros(2, 3), torch.zeros(2, 3)))
+        got = sx.lstm_cell(xin, torch.zeros(2, 3), torch.zeros(2, 3), ref.weight_ih, ref.weight_hh, ref.bias_ih, ref.bias_hh)
+    assert torch.allclose(got[0], want[0], atol=1e-6) and torch.allclose(got[1], want[1], atol=1e-6)
+
+
+def test_services_eval_experiments_and_streaming(tmp_path):
+    assert sx.check_request("10.0.0.1")
+    sx.ban_ip("10.0.0.1", 60)
+    assert not sx.check_request("10.0.0.1") and sx.get_ip_info("10.0.0.1")["banned"]
+    sx.unban_ip("10.0.0.1")
+    assert sx.check_request("10.0.0.1")
+    us = sx.UserStore()
+    us.add_user("ann", "pw123456", roles=("admin",))
+    assert us.authenticate("ann", "pw123456") and not us.authenticate("ann", "nope") and us.has_role("ann", "admin")
+    h = sx.EvalHarness([sx.ExactMatchTask([{"q": "1+1", "answer": "2"}, {"q": "2+2", "answer": "4"}]),
+                        sx.MultipleChoiceTask([{"label": 1}, {"label": 0}]),
+                        sx.CodingTask([{"entry_point": "inc", "tests": [((1,), 2), ((5,), 6)]}])])
+    summ = h.run(lambda ex: "2" if ex.get("q") == "1+1" else ("def inc(x):\n    return x + 1" if "entry_point" in ex else 1))
+    assert [r.score for r in summ.results] == [0.5, 0.5, 1.0] and abs(summ.mean - 2 / 3) < 1e-9
+    exp = sx.Experiment("sweep")
+    for lr, loss in ((0.1, 2.0), (0.01, 1.0)):
+        r = exp.start_run({"lr": lr})
+        r.log_metric("loss", loss)
+        r.finish()
+    store = sx.ExperimentStore(str(tmp_path))
+    store.save(exp)
+    assert sx.load_experiment(str(tmp_path), "sweep").best_run("loss").params == {"lr": 0.01} and store.list() == ["sweep"]
+    st = sx.TokenStreamer()
+    for t in (5, 6, 7):
+        st.put(0, t)
+    st.end()
+    assert list(st) == [5, 6, 7]
+    f = tmp_path / "pkg.bin"
+    f.write_bytes(b"v1")
+    from sneppx_alg_b200.security.services import sign_update
+    mgr = sx.SignedUpdateManager(b"key", str(tmp_path / "inst"))
+    assert mgr.stage_update(str(f), sign_update(str(f), b"key", "1.0")) and mgr.install_update().endswith("pkg.bin")
+    f.write_bytes(b"v2")
+    assert mgr.stage_update(str(f), sign_update(str(f), b"key", "1.1")) and mgr.install_update()
+    assert mgr.rollback_update("pkg.bin") and open(tmp_path / "inst" / "pkg.bin", "rb").read() == b"v1"
+    assert not mgr.stage_update(str(f), sign_update(str(f), b"other", "2.0"))
+    b = sx.PrivacyBudget(1.0)
+    assert b.spend(0.6) and not b.spend(0.6) and abs(b.remaining - 0.4) < 1e-12
+    g = sx.GaussianMech(1.0, 1e-5)(torch.zeros(20000), torch.Generator().manual_seed(0))
+    assert abs(float(g.std()) - g.new_tensor(math.sqrt(2 * math.log(1.25e5))).item()) < 0.1
+    assert sx.gemm_kernel(torch.eye(4), torch.eye(4)).shape == (4, 4) and sx.KernelLauncher().launch("relu", torch.tensor([-1.0, 2.0])).tolist() == [0.0, 2.0]
