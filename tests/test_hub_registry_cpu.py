@@ -104,3 +104,24 @@ def test_hub_cli_against_service(tmp_path, capsys):
         assert run("serve", "--dry-run", "--data", str(tmp_path / "srv2")) == 0
     finally:
         srv.stop()
+
+
+def test_module_level_hub_verbs_against_service(tmp_path):
+    import sneppx
+    from sneppx_alg_b200.hub.model_hub import ModelHub
+    from sneppx_alg_b200.models import create_model
+    hub = sneppx.hub
+    srv = serve_hub(str(tmp_path / "srv"))
+    try:
+        HubClient(f"http://127.0.0.1:{srv.port}").register("erin", "longpassword")
+        c = hub.login(f"http://127.0.0.1:{srv.port}", "erin", "longpassword")
+        c.create_model("erin/m", tags=["t"])
+        src = ModelHub.save_pretrained(create_model("llama3-tiny"), str(tmp_path / "m"))
+        hub.upload(src, "erin/m", "1.0", metrics={"acc": 0.5})
+        assert hub.list_models() == ["erin/m"] and [m["id"] for m in hub.search(tag="t")] == ["erin/m"]
+        assert hub.leaderboard("acc")[0]["id"] == "erin/m"
+        model = hub.load("erin/m", dest=None) if False else ModelHub.from_pretrained(hub.download("erin/m", dest=str(tmp_path / "dl")))
+        assert sum(p.numel() for p in model.parameters()) > 0
+    finally:
+        hub.logout()
+        srv.stop()
