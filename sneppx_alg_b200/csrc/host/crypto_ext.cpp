@@ -458,3 +458,54 @@ SX_EXPORT int sx_ed25519_verify(const void* pub32, const void* msg, size_t len, 
   pt_encode(pt_add(pt_mul(base_point(), sig + 32), pt_mul(negA, k)), enc);  // S B - k A must equal R
   return memcmp(enc, sig, 32) == 0;
 }
+
+// ------------------------------------------------------------------------------------------------ Schnorr proof of knowledge
+// Non-interactive proof (Fiat-Shamir) that the prover knows x with P = x B on the Ed25519 group: R = k B,
+// c = SHA-512(R || P || context) mod L, s = k + c x mod L; the proof is R || s. The nonce k is derived from the secret and
+// the context (deterministic, never reused across contexts). Reference counterpart: drivers/zk/zk_proof.c.
+namespace {
+void schnorr_challenge(const uint8_t R[32], const uint8_t P[32], const uint8_t* ctx, size_t len, uint8_t c[32]) {
+  std::vector<uint8_t> buf(R, R + 32);
+  buf.insert(buf.end(), P, P + 32);
+  buf.insert(buf.end(), ctx, ctx + len);
+  uint8_t h[64];
+  sha512(buf.data(), buf.size(), h);
+  sc_reduce(h, 64, c);
+}
+}  // namespace
+
+// secret: any 32 bytes (reduced mod L). Writes the public point P = x B.
+SX_EXPORT void sx_schnorr_public(const void* secret32, void* pub32) {
+  uint8_t x[32];
+  sc_reduce((const uint8_t*)secret32, 32, x);
+  pt_encode(pt_mul(base_point(), x), (uint8_t*)pub32);
+}
+
+SX_EXPORT void sx_schnorr_prove(const void* secret32, const void* context, size_t len, void* proof64) {
+  uint8_t x[32], P[32], k[32], c[32], h[64];
+  sc_reduce((const uint8_t*)secret32, 32, x);
+  pt_encode(pt_mul(base_point(), x), P);
+  std::vector<uint8_t> buf((const uint8_t*)secret32, (const uint8_t*)secret32 + 32);
+  buf.insert(buf.end(), (const uint8_t*)context, (const uint8_t*)context + len);
+  const char* tag = "sneppx-schnorr-nonce";
+  buf.insert(buf.end(), tag, tag + 20);
+  sha512(buf.data(), buf.size(), h);
+  sc_reduce(h, 64, k);
+  uint8_t* out = (uint8_t*)proof64;
+  pt_encode(pt_mul(base_point(), k), out);
+  schnorr_challenge(out, P, (const uint8_t*)context, len, c);
+  sc_muladd(c, x, k, out + 32);
+}
+
+// 1 = the proof shows knowledge of the discrete logarithm of `pub32` for this context
+SX_EXPORT int sx_schnorr_verify(const void* pub32, const void* context, size_t len, const void* proof64) {
+  const uint8_t* pr = (const uint8_t*)proof64;
+  if (ge_bytes(pr + 32, ORDER_L, 32)) return 0;
+  Pt P;
+  if (!pt_decode((const uint8_t*)pub32, P)) return 0;
+  uint8_t c[32], enc[32];
+  schnorr_challenge(pr, (const uint8_t*)pub32, (const uint8_t*)context, len, c);
+  Pt negP{fe_neg(P.X), P.Y, P.Z, fe_neg(P.T)};
+  pt_encode(pt_add(pt_mul(base_point(), pr + 32), pt_mul(negP, c)), enc);  // s B - c P must equal R
+  return memcmp(enc, pr, 32) == 0;
+}

@@ -190,3 +190,25 @@ def ed25519_verify(public_key: bytes, message: bytes, signature: bytes) -> bool:
     if len(public_key) != 32 or len(signature) != 64:
         return False
     return bool(_L().sx_ed25519_verify(public_key, message, C.c_size_t(len(message)), signature))
+
+
+def schnorr_public(secret: bytes) -> bytes:
+    """P = x B on the Ed25519 group for a 32-byte secret (reduced modulo the group order)."""
+    out = _buf(32)
+    _L().sx_schnorr_public(secret, out)
+    return out.raw
+
+
+def schnorr_prove(secret: bytes, context: bytes = b"") -> bytes:
+    """64-byte non-interactive proof of knowledge of `secret` for ``schnorr_public(secret)``, bound to `context`."""
+    if len(secret) != 32:
+        raise ValueError("secret must be 32 bytes")
+    out = _buf(64)
+    _L().sx_schnorr_prove(secret, context, C.c_size_t(len(context)), out)
+    return out.raw
+
+
+def schnorr_verify(public: bytes, proof: bytes, context: bytes = b"") -> bool:
+    if len(public) != 32 or len(proof) != 64:
+        return False
+    return bool(_L().sx_schnorr_verify(public, context, C.c_size_t(len(context)), proof))

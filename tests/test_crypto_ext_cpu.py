@@ -89,3 +89,23 @@ def test_signed_update_with_public_key(tmp_path):
     assert not verify_update(str(f), man, pub)
     man2 = sign_update(str(f), b"shared", "1.0")
     assert verify_update(str(f), man2, b"shared") and not verify_update(str(f), man2, b"other")
+
+
+def test_schnorr_proof_of_knowledge():
+    x = os.urandom(32)
+    P = c.schnorr_public(x)
+    proof = c.schnorr_prove(x, b"session-42")
+    assert c.schnorr_verify(P, proof, b"session-42")
+    assert not c.schnorr_verify(P, proof, b"session-43")                       # bound to its context
+    assert not c.schnorr_verify(c.schnorr_public(os.urandom(32)), proof, b"session-42")
+    bad = bytearray(proof)
+    bad[50] ^= 1
+    assert not c.schnorr_verify(P, bytes(bad), b"session-42")
+    assert c.schnorr_prove(x, b"a") != c.schnorr_prove(x, b"b") and c.schnorr_prove(x, b"a") == c.schnorr_prove(x, b"a")
+    # the secret clamped by Ed25519 key expansion gives that key pair's public key: same group, same base point
+    import hashlib
+    seed = os.urandom(32)
+    a = bytearray(hashlib.sha512(seed).digest()[:32])
+    a[0] &= 248
+    a[31] = (a[31] & 127) | 64
+    assert c.schnorr_public(bytes(a)) == c.ed25519_public_key(seed)
