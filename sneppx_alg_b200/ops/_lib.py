@@ -55,10 +55,7 @@ def lib() -> C.CDLL:
     if _lib is None:
         with _lock:
             if _lib is None:
-                L = _build.load_cuda()
-                for name in dir(L):
-                    pass
-                _lib = L
+                _lib = _build.load_cuda()
     return _lib
 
 
