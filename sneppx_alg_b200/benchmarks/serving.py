@@ -3,6 +3,7 @@ reporting output tokens per second and time to first token.
 
 ``python -m sneppx_alg_b200.benchmarks.serving [--model llama3-8b] [--requests 64] [--prompt-len 2048] [--new-tokens 256]
 [--quantize none|fp8|int4] [--out file.json]``
+Under ``torch.distributed.run`` with N ranks the engine runs tensor-parallel over all of them (``TPLlamaPagedRunner``).
 
 The default workload is the serving configuration of the baseline list: 64 concurrent requests, prompts of 2048
 random token ids, 256 greedy decode tokens each, random-init weights (the reference's ``benchmarks/serving_benchmark.py``
@@ -22,13 +23,13 @@ import time
 import torch
 
 
-def run(model, requests=64, prompt_len=2048, new_tokens=256, max_prefill_tokens=16384, block_size=16, seed=0) -> dict:
+def run(model, requests=64, prompt_len=2048, new_tokens=256, max_prefill_tokens=16384, block_size=16, seed=0, tp_group=None) -> dict:
     from ..serving.llm_engine import LLMEngine, SamplingParams
     cfg = model.config
     dev = next(model.parameters()).device
     blocks = requests * ((prompt_len + new_tokens + block_size - 1) // block_size) + 64
     eng = LLMEngine(model, num_blocks=blocks, block_size=block_size, max_batch_size=requests,
-                    max_prefill_tokens=max_prefill_tokens, enable_prefix_cache=False)
+                    max_prefill_tokens=max_prefill_tokens, enable_prefix_cache=False, tp_group=tp_group)
     g = torch.Generator().manual_seed(seed)
     prompts = [torch.randint(0, cfg.vocab_size, (prompt_len,), generator=g).tolist() for _ in range(requests)]
     sp = SamplingParams(max_new_tokens=new_tokens)
@@ -66,18 +67,39 @@ def main(argv=None):
     ap.add_argument("--max-prefill-tokens", type=int, default=16384)
     ap.add_argument("--out", default=None)
     a = ap.parse_args(argv)
+    import os
     from ..models import create_model
     cuda = torch.cuda.is_available()
-    dev = torch.device("cuda", 0) if cuda else torch.device("cpu")
+    world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local) if cuda else torch.device("cpu")
+    tp_group = None
+    if world > 1:   # under torchrun: tensor parallelism over all ranks (every rank runs the same scheduler)
+        import torch.distributed as dist
+        if cuda:
+            torch.cuda.set_device(local)
+        dist.init_process_group("nccl" if cuda else "gloo", **({"device_id": dev} if cuda else {}))
+        tp_group = dist.group.WORLD
     torch.manual_seed(0)
-    model = create_model(a.model, dtype=torch.bfloat16 if cuda else torch.float32, device=dev).eval()
+    spec = a.model
+    if spec.endswith(".json"):   # a model configuration file instead of a preset name
+        from ..models import ModelConfig
+        spec = ModelConfig.from_json(spec)
+    model = create_model(spec, dtype=torch.bfloat16 if cuda else torch.float32, device=dev).eval()
     model.config.max_position_embeddings = max(model.config.max_position_embeddings, a.prompt_len + a.new_tokens)
     if a.quantize != "none":
         from ..ops.quant import quantize_model_
         quantize_model_(model, a.quantize)
-    r = run(model, a.requests, a.prompt_len, a.new_tokens, a.max_prefill_tokens)
+    r = run(model, a.requests, a.prompt_len, a.new_tokens, a.max_prefill_tokens, tp_group=tp_group)
     r["config"] = {"model": a.model, "weights": "bf16" if a.quantize == "none" else a.quantize, "kv_cache": "bf16" if cuda else "fp32",
-                   "parallelism": "1 GPU" if cuda else "cpu", "data": "random token ids, random-init weights"}
+                   "parallelism": (f"tp{world}" if world > 1 else "1 GPU") if cuda else (f"cpu tp{world}" if world > 1 else "cpu"),
+                   "data": "random token ids, random-init weights"}
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+        if rank != 0:
+            dist.destroy_process_group()
+            return 0
     if cuda:
         from ..ops import check_status
         check_status()

@@ -128,6 +128,55 @@ class LlamaPagedRunner:
         return ops.linear(h[:, -1], m.head_weight()).float()
 
 
+class TPLlamaPagedRunner(LlamaPagedRunner):
+    """Tensor-parallel form of the paged runner: every rank holds H / tp query heads and Hk / tp key-value heads (and
+    their slice of the paged cache), 1 / tp of the MLP's hidden units, and the replicated embedding, norms and LM
+    head. Two all-reduces per layer (after the attention output projection and after the MLP down projection) make the
+    hidden state identical on all ranks, so every rank runs the same scheduler and samples the same tokens. The
+    projections are slices of the full weights (views, no copy)."""
+
+    def __init__(self, model, cache: PagedKVCache, group=None):
+        import torch.distributed as dist
+        super().__init__(model, cache)
+        self.group = group if group is not None else dist.group.WORLD
+        self.tp, r = dist.get_world_size(self.group), dist.get_rank(self.group)
+        H, Hk, D = self.H, self.Hk, self.D
+        assert H % self.tp == 0 and Hk % self.tp == 0, "query and key-value heads must divide over the tensor-parallel ranks"
+        hl, kl = H // self.tp, Hk // self.tp
+        self.local = []
+        for layer in model.layers:
+            wqkv, wo = layer.attn.qkv_proj.weight, layer.attn.o_proj.weight
+            q = wqkv[r * hl * D:(r + 1) * hl * D]
+            k = wqkv[H * D + r * kl * D: H * D + (r + 1) * kl * D]
+            v = wqkv[(H + Hk) * D + r * kl * D: (H + Hk) * D + (r + 1) * kl * D]
+            gu, dn = layer.mlp.gate_up_proj.weight, layer.mlp.down_proj.weight
+            ff = gu.shape[0] // 2
+            assert ff % self.tp == 0
+            fl = ff // self.tp
+            self.local.append({"qkv": torch.cat([q, k, v]).contiguous(), "o": wo[:, r * hl * D:(r + 1) * hl * D].contiguous(),
+                               "gu": torch.cat([gu[r * fl:(r + 1) * fl], gu[ff + r * fl: ff + (r + 1) * fl]]).contiguous(),
+                               "down": dn[:, r * fl:(r + 1) * fl].contiguous(), "act": layer.mlp.act})
+        self.H, self.Hk = hl, kl
+
+    def _layers(self, x, attn_fn):
+        import torch.distributed as dist
+        m = self.model
+        delta, resid = x, None
+        for li, (layer, w) in enumerate(zip(m.layers, self.local)):
+            if resid is None:
+                h, resid = layer.attn_norm(delta), delta
+            else:
+                h, resid = layer.attn_norm(delta, residual=resid)
+            o = attn_fn(li, ops.linear(h, w["qkv"]))
+            a = ops.linear(o, w["o"])
+            dist.all_reduce(a, group=self.group)
+            h, resid = layer.mlp_norm(a, residual=resid)
+            delta = ops.linear(ops.glu(ops.linear(h, w["gu"]), w["act"]), w["down"])
+            dist.all_reduce(delta, group=self.group)
+        h, _ = m.norm(delta, residual=resid)
+        return h
+
+
 class _Slots:
     def __init__(self, n):
         self.num_free = n
@@ -197,13 +246,19 @@ class StatefulRunner:
 
 class LLMEngine:
     def __init__(self, model, num_blocks=2048, block_size=16, max_batch_size=32, max_prefill_tokens=8192,
-                 policy="fcfs", enable_prefix_cache=True, runner=None):
+                 policy="fcfs", enable_prefix_cache=True, runner=None, tp_group=None):
         cfg = model.config
         p = next(model.parameters())
         if runner is None and getattr(cfg, "architecture", "transformer") == "mamba2":
             runner = StatefulRunner(model)   # recurrent-state models: no KV cache, one state slot per sequence
         if isinstance(runner, StatefulRunner):
             self.cache = StateCache(max_batch_size, on_free=runner.release)
+        elif tp_group is not None:
+            import torch.distributed as dist
+            tp = dist.get_world_size(tp_group)
+            self.cache = PagedKVCache(cfg.num_hidden_layers, num_blocks, block_size, cfg.num_key_value_heads // tp, cfg.head_dim,
+                                      dtype=p.dtype, device=p.device, enable_prefix_cache=enable_prefix_cache)
+            runner = TPLlamaPagedRunner(model, self.cache, tp_group)
         else:
             self.cache = PagedKVCache(cfg.num_hidden_layers, num_blocks, block_size, cfg.num_key_value_heads, cfg.head_dim,
                                       dtype=p.dtype, device=p.device, enable_prefix_cache=enable_prefix_cache)

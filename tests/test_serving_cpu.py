@@ -85,3 +85,13 @@ def test_engine_serves_recurrent_state_models():
                 seq.append(int(model(torch.tensor([seq]))["logits"][0, -1].argmax()))
         assert eng.finished[rid].output == seq[len(p):]
     assert eng.runner.states == {} and eng.cache.pool.num_free == 2
+
+
+def test_tensor_parallel_engine_matches_single_rank_tokens():
+    import os
+    import subprocess
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    r = subprocess.run([sys.executable, os.path.join(here, "mp_tp_serving_check.py"), "2", str(29820 + os.getpid() % 9)],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "TP_SERVING_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
