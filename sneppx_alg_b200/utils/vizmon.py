@@ -1,6 +1,6 @@
-"""vizmon — metrics / timeline store with a small embedded HTTP JSON endpoint (the reference's ``net/http/vizmon.c``
-and Python ``vizmon.py``): scalars, histograms and timeline spans, served at ``/metrics.json`` and ``/timeline.json``
-for a dashboard; no external dependencies."""
+"""vizmon — metrics / graph / timeline store with an embedded HTTP dashboard (the reference's ``net/http/vizmon.c``
+and Python ``vizmon.py``): scalars, histograms, timeline spans and a model graph, served as JSON at ``/metrics.json``,
+``/timeline.json``, ``/graph.json`` and as a self-refreshing page at ``/``; no external dependencies."""
 from __future__ import annotations
 
 import json
@@ -17,6 +17,22 @@ class VizMon:
         self.spans: deque = deque(maxlen=history)
         self.lock = threading.Lock()
         self._srv = None
+        self.graph_nodes, self.graph_edges = [], []
+
+    def set_graph(self, nodes, edges):
+        """nodes: [{"id", "label", ...}], edges: [(src id, dst id)]."""
+        with self.lock:
+            self.graph_nodes, self.graph_edges = list(nodes), [list(e) for e in edges]
+
+    def graph_from_module(self, module, max_depth: int = 2):
+        """Module tree of a ``torch.nn.Module`` down to `max_depth` as the dashboard graph."""
+        nodes, edges = [{"id": "", "label": type(module).__name__}], []
+        for name, m in module.named_modules():
+            if name and name.count(".") < max_depth:
+                nodes.append({"id": name, "label": f"{name.split('.')[-1]}: {type(m).__name__}",
+                              "params": sum(p.numel() for p in m.parameters(recurse=False))})
+                edges.append((name.rsplit(".", 1)[0] if "." in name else "", name))
+        self.set_graph(nodes, edges)
 
     def scalar(self, name, value, step=None):
         with self.lock:
@@ -58,7 +74,16 @@ class VizMon:
 
             def do_GET(self):
                 snap = mon.snapshot()
-                body = {"/metrics.json": snap["scalars"], "/timeline.json": snap["spans"]}.get(self.path)
+                if self.path in ("/", "/index.html"):
+                    page = _PAGE.encode()
+                    self.send_response(200)
+                    self.send_header("Content-Type", "text/html; charset=utf-8")
+                    self.send_header("Content-Length", str(len(page)))
+                    self.end_headers()
+                    self.wfile.write(page)
+                    return
+                body = {"/metrics.json": snap["scalars"], "/timeline.json": snap["spans"],
+                        "/graph.json": {"nodes": mon.graph_nodes, "edges": mon.graph_edges}}.get(self.path)
                 if body is None:
                     self.send_response(404)
                     self.end_headers()
@@ -77,3 +102,18 @@ class VizMon:
         if self._srv:
             self._srv.shutdown()
             self._srv = None
+
+
+_PAGE = """<!doctype html><html><head><meta charset="utf-8"><title>sneppx vizmon</title>
+<style>body{font:13px monospace;margin:16px;background:#111;color:#ddd}svg{background:#1b1b1b;margin:4px 0}
+h3{margin:12px 0 2px}.s{color:#8c8}</style></head><body><h2>sneppx vizmon</h2><div id="m"></div><h3>timeline</h3>
+<div id="t"></div><h3>graph</h3><pre id="g"></pre><script>
+function spark(v){const w=420,h=48;if(!v.length)return"";const ys=v.map(p=>p[1]),lo=Math.min(...ys),hi=Math.max(...ys);
+const pts=v.map((p,i)=>(i*(w-4)/Math.max(v.length-1,1)+2)+","+(h-2-(hi>lo?(p[1]-lo)/(hi-lo):.5)*(h-4))).join(" ");
+return`<svg width="${w}" height="${h}"><polyline fill="none" stroke="#6cf" points="${pts}"/></svg>`}
+async function tick(){const m=await(await fetch("/metrics.json")).json();let s="";
+for(const k in m){const v=m[k];s+=`<h3>${k} <span class=s>${v.length?v[v.length-1][1].toPrecision(5):""}</span></h3>`+spark(v)}
+document.getElementById("m").innerHTML=s;const t=await(await fetch("/timeline.json")).json();
+document.getElementById("t").innerHTML=t.slice(-12).map(x=>`${x.name}: ${((x.end-x.start)*1e3).toFixed(2)} ms`).join("<br>");
+const g=await(await fetch("/graph.json")).json();document.getElementById("g").textContent=g.nodes.map(n=>n.id.split(".").map(_=>"  ").join("")+n.label).join("\n")}
+tick();setInterval(tick,2000)</script></body></html>"""

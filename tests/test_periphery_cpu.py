@@ -93,3 +93,24 @@ def test_hf_round_trip(tmp_path):
     assert torch.allclose(m(ids)["logits"], m2(ids)["logits"], atol=1e-5)
     out = hf.pipeline("text-generation", m2)("hi", max_new_tokens=3)
     assert isinstance(out[0]["generated_text"], str)
+
+
+def test_vizmon_graph_and_dashboard_page():
+    import json
+    import urllib.request
+
+    import torch
+    from sneppx_alg_b200.utils.vizmon import VizMon
+    v = VizMon()
+    for i in range(4):
+        v.scalar("loss", 5.0 - i)
+    v.graph_from_module(torch.nn.Sequential(torch.nn.Linear(2, 3), torch.nn.ReLU()))
+    port = v.serve()
+    try:
+        g = json.load(urllib.request.urlopen(f"http://127.0.0.1:{port}/graph.json"))
+        assert [n["id"] for n in g["nodes"]] == ["", "0", "1"] and g["nodes"][1]["params"] == 9 and g["edges"] == [["", "0"], ["", "1"]]
+        page = urllib.request.urlopen(f"http://127.0.0.1:{port}/").read().decode()
+        assert "<svg" in page and "/metrics.json" in page
+        assert v.histogram("loss", 2)["counts"] == [2, 2]
+    finally:
+        v.stop()
