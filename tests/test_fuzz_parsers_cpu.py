@@ -100,3 +100,42 @@ def test_tokenizer_edge_and_onnx_loaders_survive_garbage(tmp_path):
     blob = model.serialize() if hasattr(model, "serialize") else model.to_bytes()
     for d in _mutations(blob, rng, 200):
         _survives(lambda b: toolkit.check_model(toolkit.Model.parse(b)), d)
+
+
+def test_http_front_end_survives_malformed_requests():
+    """Raw garbage, truncated headers, absurd or non-numeric Content-Length, binary paths and half-open connections must
+    not take the C++ server down: a well-formed request still gets its answer afterwards."""
+    import socket
+    import urllib.request
+
+    from sneppx_alg_b200.serving.native_http import NativeHttpServer
+    srv = NativeHttpServer(max_body=4096)
+
+    @srv.route("POST", "/echo/{x}")
+    def echo(p, b):
+        return {"x": p["x"], "n": len(b)}
+
+    port = srv.start(workers=2)
+    rng = random.Random(7)
+    payloads = [b"", b"\r\n\r\n", b"GET", b"GET / HTTP/1.1\r\n", b"POST /echo/a HTTP/1.1\r\nContent-Length: 99999999999999999999\r\n\r\n",
+                b"POST /echo/a HTTP/1.1\r\nContent-Length: -5\r\n\r\nabc", b"POST /echo/a HTTP/1.1\r\nContent-Length: abc\r\n\r\n",
+                b"POST /echo/a HTTP/1.1\r\nContent-Length: 100\r\n\r\nshort", b"\x00\xff" * 500, b"GET /" + b"A" * 70000 + b" HTTP/1.1\r\n\r\n",
+                b"POST /echo/%00%ff\"\\ HTTP/1.1\r\nContent-Length: 1\r\n\r\nx", b"GET /metrics/native HTTP/9.9\r\n" + b"X: y\r\n" * 2000 + b"\r\n"]
+    payloads += [bytes(rng.randrange(256) for _ in range(rng.randint(1, 300))) for _ in range(40)]
+    try:
+        for p in payloads:
+            s = socket.create_connection(("127.0.0.1", port), timeout=5)
+            try:
+                s.sendall(p)
+                s.shutdown(socket.SHUT_WR)
+                s.settimeout(8)
+                while s.recv(4096):
+                    pass
+            except OSError:
+                pass
+            finally:
+                s.close()
+        req = urllib.request.Request(f"http://127.0.0.1:{port}/echo/ok", data=b"12345", method="POST")
+        assert urllib.request.urlopen(req, timeout=10).read() == b'{"x": "ok", "n": 5}'
+    finally:
+        srv.stop()
