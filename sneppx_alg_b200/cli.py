@@ -122,7 +122,7 @@ def serve_main(argv=None):
         from .serving.native_http import TextEngine, serve_engine
         eng = TextEngine(model, spec.get("tokenizer"), a.model_id, **spec["engine_kwargs"])
         srv = serve_engine(eng, {a.model_id: {"config": a.model_config}}, token=(sorted(keys)[0] if keys else ""),
-                           port=0 if a.dry_run else a.port, workers=max(a.workers, 2))
+                           port=0 if a.dry_run else a.port, workers=max(a.workers, 2), host=a.host)
         print(json.dumps({"front_end": "native", "port": srv.port}), flush=True)
         try:
             while not a.dry_run:

@@ -266,7 +266,8 @@ SX_EXPORT int sx_http_add_route(void* h, const char* method, const char* pattern
   return (int)s->routes.size() - 1;
 }
 
-SX_EXPORT int sx_http_start(void* h, int port, int workers) {
+// `host`: dotted IPv4 address to bind ("0.0.0.0" for all interfaces); nullptr or "" binds the loopback interface.
+SX_EXPORT int sx_http_start_on(void* h, const char* host, int port, int workers) {
   auto* s = (Server*)h;
   s->lfd = ::socket(AF_INET, SOCK_STREAM, 0);
   if (s->lfd < 0) return -1;
@@ -275,6 +276,7 @@ SX_EXPORT int sx_http_start(void* h, int port, int workers) {
   sockaddr_in a{};
   a.sin_family = AF_INET;
   a.sin_addr.s_addr = htonl(INADDR_LOOPBACK);
+  if (host && *host && inet_pton(AF_INET, host, &a.sin_addr) != 1) { ::close(s->lfd); s->lfd = -1; return -1; }
   a.sin_port = htons((uint16_t)port);
   if (::bind(s->lfd, (sockaddr*)&a, sizeof a) || ::listen(s->lfd, 128)) { ::close(s->lfd); s->lfd = -1; return -1; }
   socklen_t l = sizeof a;
@@ -284,6 +286,8 @@ SX_EXPORT int sx_http_start(void* h, int port, int workers) {
   s->acceptor = std::thread([s] { s->accept_loop(); });
   return s->port;
 }
+
+SX_EXPORT int sx_http_start(void* h, int port, int workers) { return sx_http_start_on(h, nullptr, port, workers); }
 
 SX_EXPORT void sx_http_stop(void* h) {
   auto* s = (Server*)h;

@@ -26,6 +26,7 @@ def _L():
         L.sx_http_create.argtypes = [C.c_char_p, C.c_longlong]
         L.sx_http_add_route.argtypes = [C.c_void_p, C.c_char_p, C.c_char_p, C.c_int, C.c_char_p, _CB]
         L.sx_http_start.argtypes = [C.c_void_p, C.c_int, C.c_int]
+        L.sx_http_start_on.argtypes = [C.c_void_p, C.c_char_p, C.c_int, C.c_int]
         L.sx_http_stop.argtypes = [C.c_void_p]
         L.sx_http_route_hits.argtypes = [C.c_void_p, C.c_int]
         L.sx_http_route_hits.restype = C.c_longlong
@@ -88,10 +89,11 @@ class NativeHttpServer:
             return fn
         return deco
 
-    def start(self, port: int = 0, workers: int = 4) -> int:
-        p = _L().sx_http_start(self._h, port, workers)
+    def start(self, port: int = 0, workers: int = 4, host: str = "127.0.0.1") -> int:
+        """Binds `host` (dotted IPv4; "0.0.0.0" for every interface) and starts the accept and worker threads."""
+        p = _L().sx_http_start_on(self._h, host.encode(), port, workers)
         if p < 0:
-            raise OSError(f"cannot bind port {port}")
+            raise OSError(f"cannot bind {host}:{port}")
         self.port = p
         return p
 
@@ -104,7 +106,8 @@ class NativeHttpServer:
             self._h = None
 
 
-def serve_engine(engine, models: Dict[str, dict], token: str = "", port: int = 0, workers: int = 4) -> NativeHttpServer:
+def serve_engine(engine, models: Dict[str, dict], token: str = "", port: int = 0, workers: int = 4,
+                 host: str = "127.0.0.1") -> NativeHttpServer:
     """Starts the REST surface of the reference's C API in front of `engine`. ``models``: id -> description."""
     srv = NativeHttpServer(token)
     srv.static("GET", "/v1/health", {"status": "ok"}, public=True)
@@ -132,7 +135,7 @@ def serve_engine(engine, models: Dict[str, dict], token: str = "", port: int = 0
         kw = {k: req[k] for k in ("do_sample", "temperature", "top_k", "top_p", "repetition_penalty", "stop_strings") if k in req}
         return engine.generate(req["prompt"], max_new_tokens=n, **kw)
 
-    srv.start(port, workers)
+    srv.start(port, workers, host)
     return srv
 
 
