@@ -56,18 +56,20 @@ class Embedding(Module):
 
 
 class Dropout(tnn.Dropout, Module):
-    """Inverted dropout. On bf16 CUDA activations the keep-mask is a function of (seed, call counter, element index)
-    that backward recomputes, so no mask tensor is stored between the passes (``ops.aux.dropout``)."""
+    """Inverted dropout. On bf16 CUDA activations the keep-mask is a function of (seed, stream offset, element index)
+    that backward recomputes, so no mask tensor is stored between the passes (``ops.aux.dropout``). The stream offset
+    of a call is drawn from PyTorch's CPU generator: ``torch.manual_seed`` makes runs repeatable, and activation
+    checkpointing, which restores that generator before it re-runs a forward, gets the same mask again."""
 
     def __init__(self, p=0.5, inplace=False, seed=0):
         super().__init__(p, inplace)
-        self.seed, self.calls = seed, 0
+        self.seed = seed
 
     def forward(self, x):
         if self.training and self.p > 0 and x.is_cuda and x.dtype == torch.bfloat16 and x.numel() % 8 == 0:
             from ..ops import aux
-            self.calls += 1
-            return aux.dropout(x, self.p, self.seed, self.calls)
+            offset = int(torch.randint(0, 2 ** 31 - 1, (1,)).item())
+            return aux.dropout(x, self.p, self.seed, offset)
         return super().forward(x)
 
 
