@@ -1257,3 +1257,18 @@ class ModelHasher:
             h.update(n.encode())
             h.update(p.detach().cpu().contiguous().view(torch.uint8).numpy().tobytes())
         return h.hexdigest()
+
+
+class Argon2:
+    """Argon2id password hashing with a random salt; ``hash`` returns salt || tag, ``verify`` recomputes it."""
+
+    def __init__(self, time_cost: int = 2, memory_kib: int = 19456, lanes: int = 1, length: int = 32):
+        self.t, self.m, self.p, self.n = time_cost, memory_kib, lanes, length
+
+    def hash(self, password: bytes, salt: Optional[bytes] = None) -> bytes:
+        import os
+        salt = salt or os.urandom(16)
+        return salt + _c.argon2id(password, salt, self.t, self.m, self.p, self.n)
+
+    def verify(self, password: bytes, stored: bytes) -> bool:
+        return _c.ct_equal(self.hash(password, stored[:16]), stored)

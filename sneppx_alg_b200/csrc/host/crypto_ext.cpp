@@ -509,3 +509,101 @@ SX_EXPORT int sx_schnorr_verify(const void* pub32, const void* context, size_t l
   pt_encode(pt_add(pt_mul(base_point(), pr + 32), pt_mul(negP, c)), enc);  // s B - c P must equal R
   return memcmp(enc, pr, 32) == 0;
 }
+
+// ------------------------------------------------------------------------------------------------ Argon2id (RFC 9106)
+// Memory-hard password hashing, version 0x13, type id (data-independent addressing in the first half of the first
+// pass, data-dependent afterwards). Lanes are filled one after another inside a slice (no threads).
+namespace {
+
+typedef uint64_t A2Block[128];
+
+void a2_le32(std::vector<uint8_t>& v, uint32_t x) { for (int i = 0; i < 4; ++i) v.push_back((uint8_t)(x >> (8 * i))); }
+
+// variable-length hash H' of RFC 9106 section 3.3
+void a2_hprime(const uint8_t* in, size_t inlen, uint8_t* out, uint32_t T) {
+  std::vector<uint8_t> buf;
+  a2_le32(buf, T);
+  buf.insert(buf.end(), in, in + inlen);
+  if (T <= 64) { blake2b(buf.data(), buf.size(), nullptr, 0, out, T); return; }
+  uint8_t v[64];
+  blake2b(buf.data(), buf.size(), nullptr, 0, v, 64);
+  const uint32_t r = (T + 31) / 32 - 2;
+  memcpy(out, v, 32);
+  for (uint32_t i = 1; i < r; ++i) { uint8_t nx[64]; blake2b(v, 64, nullptr, 0, nx, 64); memcpy(v, nx, 64); memcpy(out + 32 * i, v, 32); }
+  blake2b(v, 64, nullptr, 0, out + 32 * r, T - 32 * r);
+}
+
+inline void a2_gb(uint64_t& a, uint64_t& b, uint64_t& c, uint64_t& d) {
+  auto mix = [](uint64_t x, uint64_t y) { return x + y + 2 * (uint64_t)(uint32_t)x * (uint64_t)(uint32_t)y; };
+  a = mix(a, b); d = rotr64(d ^ a, 32); c = mix(c, d); b = rotr64(b ^ c, 24);
+  a = mix(a, b); d = rotr64(d ^ a, 16); c = mix(c, d); b = rotr64(b ^ c, 63);
+}
+inline void a2_p(uint64_t* v[16]) {
+  a2_gb(*v[0], *v[4], *v[8], *v[12]); a2_gb(*v[1], *v[5], *v[9], *v[13]); a2_gb(*v[2], *v[6], *v[10], *v[14]); a2_gb(*v[3], *v[7], *v[11], *v[15]);
+  a2_gb(*v[0], *v[5], *v[10], *v[15]); a2_gb(*v[1], *v[6], *v[11], *v[12]); a2_gb(*v[2], *v[7], *v[8], *v[13]); a2_gb(*v[3], *v[4], *v[9], *v[14]);
+}
+// out = G(x, y) (xor_into: out ^= G(x, y), the second and later passes)
+void a2_g(const A2Block x, const A2Block y, A2Block out, bool xor_into) {
+  A2Block r, z;
+  for (int i = 0; i < 128; ++i) z[i] = r[i] = x[i] ^ y[i];
+  for (int row = 0; row < 8; ++row) { uint64_t* v[16]; for (int i = 0; i < 16; ++i) v[i] = &z[16 * row + i]; a2_p(v); }
+  for (int col = 0; col < 8; ++col) { uint64_t* v[16]; for (int i = 0; i < 8; ++i) { v[2 * i] = &z[16 * i + 2 * col]; v[2 * i + 1] = &z[16 * i + 2 * col + 1]; } a2_p(v); }
+  for (int i = 0; i < 128; ++i) out[i] = (xor_into ? out[i] : 0) ^ z[i] ^ r[i];
+}
+
+}  // namespace
+
+// m_kib: memory in KiB (>= 8 * lanes). Returns 0, or -1 on bad parameters.
+SX_EXPORT int sx_argon2id(const void* pwd, size_t pwdlen, const void* salt, size_t saltlen, const void* secret, size_t secretlen,
+                          const void* ad, size_t adlen, uint32_t t_cost, uint32_t m_kib, uint32_t lanes, void* out, uint32_t outlen) {
+  if (lanes < 1 || t_cost < 1 || outlen < 4 || m_kib < 8 * lanes || saltlen < 8) return -1;
+  const uint32_t mprime = 4 * lanes * (m_kib / (4 * lanes)), q = mprime / lanes, seg = q / 4;
+  std::vector<uint8_t> h0in;
+  a2_le32(h0in, lanes); a2_le32(h0in, outlen); a2_le32(h0in, m_kib); a2_le32(h0in, t_cost); a2_le32(h0in, 0x13); a2_le32(h0in, 2);
+  auto field = [&](const void* p, size_t n) { a2_le32(h0in, (uint32_t)n); h0in.insert(h0in.end(), (const uint8_t*)p, (const uint8_t*)p + n); };
+  field(pwd, pwdlen); field(salt, saltlen); field(secret, secretlen); field(ad, adlen);
+  uint8_t h0[72];
+  blake2b(h0in.data(), h0in.size(), nullptr, 0, h0, 64);
+  std::vector<uint64_t> mem((size_t)mprime * 128);
+  auto B = [&](uint32_t lane, uint32_t col) { return &mem[((size_t)lane * q + col) * 128]; };
+  for (uint32_t l = 0; l < lanes; ++l)
+    for (uint32_t c = 0; c < 2; ++c) {
+      for (int i = 0; i < 4; ++i) { h0[64 + i] = (uint8_t)(c >> (8 * i)); h0[68 + i] = (uint8_t)(l >> (8 * i)); }
+      a2_hprime(h0, 72, (uint8_t*)B(l, c), 1024);
+    }
+  A2Block zero = {0}, input, addr;
+  for (uint32_t pass = 0; pass < t_cost; ++pass)
+    for (uint32_t s = 0; s < 4; ++s)
+      for (uint32_t l = 0; l < lanes; ++l) {
+        const bool indep = pass == 0 && s < 2;
+        uint32_t start = (pass == 0 && s == 0) ? 2 : 0;
+        auto next_addresses = [&] { ++input[6]; A2Block tmp; a2_g(zero, input, tmp, false); a2_g(zero, tmp, addr, false); };
+        if (indep) {
+          memset(input, 0, sizeof input);
+          input[0] = pass; input[1] = l; input[2] = s; input[3] = mprime; input[4] = t_cost; input[5] = 2;
+          if (start) next_addresses();
+        }
+        for (uint32_t idx = start; idx < seg; ++idx) {
+          const uint32_t j = s * seg + idx, prev = j ? j - 1 : q - 1;
+          uint64_t rnd;
+          if (indep) { if (idx % 128 == 0) next_addresses(); rnd = addr[idx % 128]; }
+          else rnd = B(l, prev)[0];
+          const uint32_t j1 = (uint32_t)rnd, j2 = (uint32_t)(rnd >> 32);
+          const uint32_t ref_lane = (pass == 0 && s == 0) ? l : j2 % lanes;
+          const bool same = ref_lane == l;
+          uint32_t area;
+          if (pass == 0) area = s == 0 ? idx - 1 : (same ? s * seg + idx - 1 : s * seg - (idx == 0 ? 1 : 0));
+          else area = same ? q - seg + idx - 1 : q - seg - (idx == 0 ? 1 : 0);
+          const uint64_t x = ((uint64_t)j1 * j1) >> 32, y = ((uint64_t)area * x) >> 32;
+          const uint32_t zz = area - 1 - (uint32_t)y;
+          const uint32_t first = (pass != 0 && s != 3) ? (s + 1) * seg : 0;
+          const uint32_t ref = (first + zz) % q;
+          a2_g(B(l, prev), B(ref_lane, ref), B(l, j), pass > 0);
+        }
+      }
+  A2Block fin;
+  memcpy(fin, B(0, q - 1), sizeof fin);
+  for (uint32_t l = 1; l < lanes; ++l) for (int i = 0; i < 128; ++i) fin[i] ^= B(l, q - 1)[i];
+  a2_hprime((const uint8_t*)fin, 1024, (uint8_t*)out, outlen);
+  return 0;
+}

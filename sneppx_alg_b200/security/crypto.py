@@ -212,3 +212,15 @@ def schnorr_verify(public: bytes, proof: bytes, context: bytes = b"") -> bool:
     if len(public) != 32 or len(proof) != 64:
         return False
     return bool(_L().sx_schnorr_verify(public, context, C.c_size_t(len(context)), proof))
+
+
+def argon2id(password: bytes, salt: bytes, time_cost: int = 3, memory_kib: int = 65536, lanes: int = 4, length: int = 32,
+             secret: bytes = b"", ad: bytes = b"") -> bytes:
+    """Argon2id (RFC 9106, version 0x13): memory-hard password hash / key derivation."""
+    out = _buf(length)
+    rc = _L().sx_argon2id(password, C.c_size_t(len(password)), salt, C.c_size_t(len(salt)), secret, C.c_size_t(len(secret)),
+                          ad, C.c_size_t(len(ad)), C.c_uint32(time_cost), C.c_uint32(memory_kib), C.c_uint32(lanes), out,
+                          C.c_uint32(length))
+    if rc:
+        raise ValueError("argon2id: need lanes >= 1, time_cost >= 1, length >= 4, memory_kib >= 8 * lanes, salt of 8+ bytes")
+    return out.raw

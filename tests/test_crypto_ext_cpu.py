@@ -109,3 +109,17 @@ def test_schnorr_proof_of_knowledge():
     a[0] &= 248
     a[31] = (a[31] & 127) | 64
     assert c.schnorr_public(bytes(a)) == c.ed25519_public_key(seed)
+
+
+def test_argon2id_rfc_vector_and_independent_implementation():
+    k = c.argon2id(b"\x01" * 32, b"\x02" * 16, 3, 32, 4, 32, secret=b"\x03" * 8, ad=b"\x04" * 12)
+    assert k.hex() == "0d640df58d78766c08c037a34a8b53c9d01ef0452d75b65eb52520e96b01e659"   # RFC 9106 section 5.3
+    Argon2id = pytest.importorskip("cryptography.hazmat.primitives.kdf.argon2").Argon2id
+    for t, m, p, n in ((1, 8, 1, 16), (2, 64, 2, 32), (3, 100, 3, 80), (1, 256, 4, 200)):
+        pwd, salt = os.urandom(13), os.urandom(16)
+        want = Argon2id(salt=salt, length=n, iterations=t, lanes=p, memory_cost=m).derive(pwd)
+        assert c.argon2id(pwd, salt, t, m, p, n) == want, (t, m, p, n)
+    with pytest.raises(ValueError):
+        c.argon2id(b"x", b"short", 1, 8, 1)
+    with pytest.raises(ValueError):
+        c.argon2id(b"x", b"longenoughsalt", 1, 4, 1)
