@@ -1272,3 +1272,14 @@ class Argon2:
 
     def verify(self, password: bytes, stored: bytes) -> bool:
         return _c.ct_equal(self.hash(password, stored[:16]), stored)
+
+
+class Poly1305:
+    def __init__(self, key: bytes):
+        self.key = key
+
+    def tag(self, message: bytes) -> bytes:
+        return _c.poly1305(self.key, message)
+
+    def verify(self, message: bytes, tag: bytes) -> bool:
+        return _c.ct_equal(self.tag(message), tag)

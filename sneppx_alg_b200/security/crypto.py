@@ -224,3 +224,12 @@ def argon2id(password: bytes, salt: bytes, time_cost: int = 3, memory_kib: int =
     if rc:
         raise ValueError("argon2id: need lanes >= 1, time_cost >= 1, length >= 4, memory_kib >= 8 * lanes, salt of 8+ bytes")
     return out.raw
+
+
+def poly1305(key: bytes, message: bytes) -> bytes:
+    """One-time authenticator (RFC 8439 section 2.5): 16-byte tag under a 32-byte one-time key."""
+    if len(key) != 32:
+        raise ValueError("key must be 32 bytes")
+    out = _buf(16)
+    _L().sx_poly1305(key, message, C.c_size_t(len(message)), out)
+    return out.raw

@@ -123,3 +123,14 @@ def test_argon2id_rfc_vector_and_independent_implementation():
         c.argon2id(b"x", b"short", 1, 8, 1)
     with pytest.raises(ValueError):
         c.argon2id(b"x", b"longenoughsalt", 1, 4, 1)
+
+
+def test_poly1305_rfc_vector():
+    key = bytes.fromhex("85d6be7857556d337f4452fe42d506a80103808afb0db2fd4abff6af4149f51b")
+    msg = b"Cryptographic Forum Research Group"
+    assert c.poly1305(key, msg).hex() == "a8061dc1305136c6c22b8baf0c0127a9"   # RFC 8439 section 2.5.2
+    import SneppX_ALG as sx
+    assert sx.Poly1305(key).verify(msg, bytes.fromhex("a8061dc1305136c6c22b8baf0c0127a9"))
+    a = sx.Argon2(1, 64, 1)
+    stored = a.hash(b"pw")
+    assert a.verify(b"pw", stored) and not a.verify(b"px", stored)
