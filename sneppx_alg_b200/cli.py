@@ -480,8 +480,86 @@ def hub_main(argv=None):
     return 0
 
 
+# ----------------------------------------------------------------------------- tools
+def tools_main(argv=None):
+    """Small utilities in the place of the reference's ``tools/`` programs: config generator, data explorer, model
+    converter, benchmarking suite, security auditor."""
+    ap = argparse.ArgumentParser(prog="sneppx-tools", description=tools_main.__doc__.split("\n")[0])
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    cg = sub.add_parser("config", help="write a training configuration template")
+    cg.add_argument("out")
+    cg.add_argument("--model", default="llama3-8b")
+    de = sub.add_parser("data", help="statistics of a text file or a token file (.npy / .bin of int32)")
+    de.add_argument("path")
+    de.add_argument("--top", type=int, default=10)
+    cv = sub.add_parser("convert", help="convert a weight file between .safetensors / .sneppx / .pth / .npz")
+    cv.add_argument("src")
+    cv.add_argument("dst")
+    be = sub.add_parser("bench", help="tensor micro-benchmarks (the reference's published list)")
+    be.add_argument("--device", default="cpu")
+    be.add_argument("--out", default=None)
+    au = sub.add_parser("audit", help="security self-audit of a serving configuration file")
+    au.add_argument("config")
+    a = ap.parse_args(argv)
+    if a.cmd == "config":
+        from .models import config_from_name
+        from .training.config import TrainConfig
+        cfg = TrainConfig().to_dict()
+        cfg["model"] = config_from_name(a.model).to_dict()
+        with open(a.out, "w") as f:
+            if a.out.endswith((".yaml", ".yml")):
+                import yaml
+                yaml.safe_dump(cfg, f, sort_keys=False)
+            else:
+                json.dump(cfg, f, indent=1)
+        print(a.out)
+    elif a.cmd == "data":
+        import collections
+        import numpy as np
+        if a.path.endswith((".npy", ".bin")):
+            ids = np.load(a.path) if a.path.endswith(".npy") else np.fromfile(a.path, dtype=np.int32)
+            ids = ids.reshape(-1)
+            vals, counts = np.unique(ids, return_counts=True)
+            order = np.argsort(-counts)[: a.top]
+            out = {"tokens": int(ids.size), "distinct": int(vals.size), "min": int(ids.min()), "max": int(ids.max()),
+                   "top": [[int(vals[i]), int(counts[i])] for i in order]}
+        else:
+            text = open(a.path, encoding="utf-8", errors="replace").read()
+            words = text.split()
+            out = {"bytes": len(text.encode()), "lines": text.count("\n") + 1, "words": len(words),
+                   "distinct_words": len(set(words)), "top": collections.Counter(words).most_common(a.top)}
+        print(json.dumps(out, indent=1))
+    elif a.cmd == "convert":
+        from .checkpoint.sneppx_format import save_tensors
+        from .hub import formats
+        sd = formats.load_any(a.src)
+        d = a.dst.lower()
+        if d.endswith(".safetensors"):
+            formats.save_safetensors(a.dst, {k: v.contiguous() for k, v in sd.items()})
+        elif d.endswith(".sneppx"):
+            save_tensors(a.dst, sd, {"source": os.path.basename(a.src)})
+        elif d.endswith((".pth", ".pt")):
+            formats.save_pth(a.dst, sd)
+        elif d.endswith(".npz"):
+            formats.save_npz(a.dst, sd)
+        else:
+            print(f"unknown target format: {a.dst}", file=sys.stderr)
+            return 2
+        print(json.dumps({"tensors": len(sd), "dst": a.dst}))
+    elif a.cmd == "bench":
+        from .benchmarks import tensor_ops
+        return tensor_ops.main(["--device", a.device] + (["--out", a.out] if a.out else []))
+    elif a.cmd == "audit":
+        from .security.services import self_audit
+        cfg = json.load(open(a.config)) if a.config.endswith(".json") else __import__("yaml").safe_load(open(a.config))
+        findings = self_audit(cfg)
+        print(json.dumps({"findings": findings}, indent=1))
+        return 1 if findings else 0
+    return 0
+
+
 COMMANDS = {"train": train_main, "serve": serve_main, "eval": eval_main, "quantize": quantize_main, "rlhf": rlhf_main,
-            "experiment": experiment_main, "onnx": onnx_main, "hub": hub_main}
+            "experiment": experiment_main, "onnx": onnx_main, "hub": hub_main, "tools": tools_main}
 
 
 def main(argv=None):

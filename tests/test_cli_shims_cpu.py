@@ -75,3 +75,32 @@ def test_serve_cli_dry_run_and_hub_cli(tmp_path, capsys):
     routes = json.loads(capsys.readouterr().out.strip().splitlines()[-1])["routes"]
     assert "/v1/generate" in routes and "/v1/chat/completions" in routes and "/v1/health" in routes
     assert cli.main(["hub", "--root", str(tmp_path / "hub"), "list"]) == 0
+
+
+def test_tools_cli(tmp_path, capsys):
+    import json
+
+    import numpy as np
+    import torch
+    from sneppx_alg_b200.cli import tools_main
+    from sneppx_alg_b200.hub import formats
+    assert tools_main(["config", str(tmp_path / "train.json"), "--model", "llama3-8b"]) == 0
+    cfg = json.load(open(tmp_path / "train.json"))
+    assert cfg["model"]["hidden_size"] == 4096 and "optimizer" in cfg
+    np.save(tmp_path / "ids.npy", np.array([1, 1, 2, 3, 3, 3], dtype=np.int32))
+    capsys.readouterr()
+    assert tools_main(["data", str(tmp_path / "ids.npy"), "--top", "1"]) == 0
+    assert json.loads(capsys.readouterr().out)["top"] == [[3, 3]]
+    (tmp_path / "t.txt").write_text("a b a\nc")
+    assert tools_main(["data", str(tmp_path / "t.txt")]) == 0
+    assert json.loads(capsys.readouterr().out)["distinct_words"] == 3
+    sd = {"w": torch.randn(3, 4), "b": torch.zeros(4)}
+    formats.save_safetensors(str(tmp_path / "m.safetensors"), sd)
+    for ext in ("sneppx", "pth", "npz"):
+        assert tools_main(["convert", str(tmp_path / "m.safetensors"), str(tmp_path / f"m.{ext}")]) == 0
+        assert torch.equal(formats.load_any(str(tmp_path / f"m.{ext}"))["w"], sd["w"])
+    assert tools_main(["convert", str(tmp_path / "m.safetensors"), str(tmp_path / "m.xyz")]) == 2
+    (tmp_path / "serve.json").write_text(json.dumps({"api_keys_required": True, "max_prompt_chars": 1000, "audit_log": "a.log"}))
+    assert tools_main(["audit", str(tmp_path / "serve.json")]) == 0
+    (tmp_path / "bad.json").write_text(json.dumps({"bind": "0.0.0.0"}))
+    assert tools_main(["audit", str(tmp_path / "bad.json")]) == 1
