@@ -1283,3 +1283,18 @@ class Poly1305:
 
     def verify(self, message: bytes, tag: bytes) -> bool:
         return _c.ct_equal(self.tag(message), tag)
+
+
+class Blake3:
+    def __init__(self, key: Optional[bytes] = None):
+        self.key, self._buf = key, b""
+
+    def update(self, data: bytes):
+        self._buf += data
+        return self
+
+    def digest(self, length: int = 32) -> bytes:
+        return _c.blake3(self._buf, length, self.key)
+
+    def hexdigest(self, length: int = 32) -> str:
+        return self.digest(length).hex()

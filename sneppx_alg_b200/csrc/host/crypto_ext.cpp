@@ -607,3 +607,115 @@ SX_EXPORT int sx_argon2id(const void* pwd, size_t pwdlen, const void* salt, size
   a2_hprime((const uint8_t*)fin, 1024, (uint8_t*)out, outlen);
   return 0;
 }
+
+// ------------------------------------------------------------------------------------------------ BLAKE3
+// Hash and keyed-hash modes with extendable output: 1024-byte chunks of 64-byte blocks, a binary tree of chaining
+// values merged with a stack, and the root node re-compressed per 64-byte output block.
+namespace {
+
+const uint32_t B3_IV[8] = {0x6A09E667u, 0xBB67AE85u, 0x3C6EF372u, 0xA54FF53Au, 0x510E527Fu, 0x9B05688Cu, 0x1F83D9ABu, 0x5BE0CD19u};
+const int B3_PERM[16] = {2, 6, 3, 10, 7, 0, 4, 13, 1, 11, 12, 5, 9, 14, 15, 8};
+enum { B3_CHUNK_START = 1, B3_CHUNK_END = 2, B3_PARENT = 4, B3_ROOT = 8, B3_KEYED = 16 };
+
+inline uint32_t rotr32(uint32_t x, int n) { return (x >> n) | (x << (32 - n)); }
+
+void b3_compress(const uint32_t cv[8], const uint32_t block[16], uint64_t counter, uint32_t block_len, uint32_t flags, uint32_t out[16]) {
+  uint32_t s[16] = {cv[0], cv[1], cv[2], cv[3], cv[4], cv[5], cv[6], cv[7], B3_IV[0], B3_IV[1], B3_IV[2], B3_IV[3],
+                    (uint32_t)counter, (uint32_t)(counter >> 32), block_len, flags};
+  uint32_t m[16];
+  memcpy(m, block, sizeof m);
+  auto g = [&](int a, int b, int c, int d, uint32_t mx, uint32_t my) {
+    s[a] = s[a] + s[b] + mx; s[d] = rotr32(s[d] ^ s[a], 16); s[c] = s[c] + s[d]; s[b] = rotr32(s[b] ^ s[c], 12);
+    s[a] = s[a] + s[b] + my; s[d] = rotr32(s[d] ^ s[a], 8); s[c] = s[c] + s[d]; s[b] = rotr32(s[b] ^ s[c], 7);
+  };
+  for (int r = 0; r < 7; ++r) {
+    g(0, 4, 8, 12, m[0], m[1]); g(1, 5, 9, 13, m[2], m[3]); g(2, 6, 10, 14, m[4], m[5]); g(3, 7, 11, 15, m[6], m[7]);
+    g(0, 5, 10, 15, m[8], m[9]); g(1, 6, 11, 12, m[10], m[11]); g(2, 7, 8, 13, m[12], m[13]); g(3, 4, 9, 14, m[14], m[15]);
+    uint32_t t[16];
+    for (int i = 0; i < 16; ++i) t[i] = m[B3_PERM[i]];
+    memcpy(m, t, sizeof m);
+  }
+  for (int i = 0; i < 8; ++i) { out[i] = s[i] ^ s[i + 8]; out[i + 8] = s[i + 8] ^ cv[i]; }
+}
+
+struct B3Output { uint32_t cv[8], block[16]; uint64_t counter; uint32_t block_len, flags; };
+
+void b3_words(const uint8_t* p, size_t n, uint32_t w[16]) {
+  uint8_t buf[64] = {0};
+  memcpy(buf, p, n);
+  for (int i = 0; i < 16; ++i) w[i] = (uint32_t)buf[4 * i] | (uint32_t)buf[4 * i + 1] << 8 | (uint32_t)buf[4 * i + 2] << 16 | (uint32_t)buf[4 * i + 3] << 24;
+}
+
+// the last block of a chunk is returned uncompressed (it may turn out to be the root)
+B3Output b3_chunk(const uint32_t key[8], const uint8_t* p, size_t len, uint64_t index, uint32_t base) {
+  B3Output o;
+  memcpy(o.cv, key, 32);
+  const size_t nb = len ? (len + 63) / 64 : 1;
+  for (size_t b = 0; b < nb; ++b) {
+    const size_t off = 64 * b, bl = b + 1 < nb ? 64 : len - off;
+    uint32_t w[16];
+    b3_words(p + off, bl, w);
+    const uint32_t fl = base | (b == 0 ? B3_CHUNK_START : 0) | (b + 1 == nb ? B3_CHUNK_END : 0);
+    if (b + 1 < nb) { uint32_t out[16]; b3_compress(o.cv, w, index, 64, fl, out); memcpy(o.cv, out, 32); }
+    else { memcpy(o.block, w, 64); o.counter = index; o.block_len = (uint32_t)bl; o.flags = fl; }
+  }
+  return o;
+}
+
+void b3_cv_of(const B3Output& o, uint32_t cv[8]) {
+  uint32_t out[16];
+  b3_compress(o.cv, o.block, o.counter, o.block_len, o.flags, out);
+  memcpy(cv, out, 32);
+}
+
+B3Output b3_parent(const uint32_t left[8], const uint32_t right[8], const uint32_t key[8], uint32_t base) {
+  B3Output o;
+  memcpy(o.cv, key, 32);
+  memcpy(o.block, left, 32);
+  memcpy(o.block + 8, right, 32);
+  o.counter = 0; o.block_len = 64; o.flags = base | B3_PARENT;
+  return o;
+}
+
+}  // namespace
+
+// key32 == nullptr: plain hash; otherwise the keyed mode. Any output length (extendable output).
+SX_EXPORT void sx_blake3(const void* msg, size_t len, const void* key32, void* out, size_t outlen) {
+  uint32_t key[8];
+  uint32_t base = 0;
+  if (key32) { uint32_t w[16]; b3_words((const uint8_t*)key32, 32, w); memcpy(key, w, 32); base = B3_KEYED; }
+  else memcpy(key, B3_IV, 32);
+  const uint8_t* p = (const uint8_t*)msg;
+  const size_t chunks = len ? (len + 1023) / 1024 : 1;
+  std::vector<std::vector<uint32_t>> stack;
+  for (size_t c = 0; c + 1 < chunks; ++c) {
+    uint32_t cv[8];
+    b3_cv_of(b3_chunk(key, p + 1024 * c, 1024, c, base), cv);
+    size_t total = c + 1;   // chunks completed so far: merge one level per trailing zero bit
+    while ((total & 1) == 0) {
+      uint32_t merged[8];
+      b3_cv_of(b3_parent(stack.back().data(), cv, key, base), merged);
+      stack.pop_back();
+      memcpy(cv, merged, 32);
+      total >>= 1;
+    }
+    stack.emplace_back(cv, cv + 8);
+  }
+  B3Output o = b3_chunk(key, p + 1024 * (chunks - 1), len - 1024 * (chunks - 1), chunks - 1, base);
+  while (!stack.empty()) {
+    uint32_t cv[8];
+    b3_cv_of(o, cv);
+    o = b3_parent(stack.back().data(), cv, key, base);
+    stack.pop_back();
+  }
+  uint8_t* dst = (uint8_t*)out;
+  for (uint64_t blk = 0; outlen; ++blk) {
+    uint32_t w[16];
+    b3_compress(o.cv, o.block, blk, o.block_len, o.flags | B3_ROOT, w);
+    uint8_t bytes[64];
+    for (int i = 0; i < 16; ++i) for (int j = 0; j < 4; ++j) bytes[4 * i + j] = (uint8_t)(w[i] >> (8 * j));
+    const size_t n = outlen < 64 ? outlen : 64;
+    memcpy(dst, bytes, n);
+    dst += n; outlen -= n;
+  }
+}

@@ -233,3 +233,12 @@ def poly1305(key: bytes, message: bytes) -> bytes:
     out = _buf(16)
     _L().sx_poly1305(key, message, C.c_size_t(len(message)), out)
     return out.raw
+
+
+def blake3(data: bytes, length: int = 32, key: bytes = None) -> bytes:
+    """BLAKE3 hash (or keyed hash with a 32-byte key) with any output length."""
+    if key is not None and len(key) != 32:
+        raise ValueError("key must be 32 bytes")
+    out = _buf(length)
+    _L().sx_blake3(data, C.c_size_t(len(data)), key, out, C.c_size_t(length))
+    return out.raw

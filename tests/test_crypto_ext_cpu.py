@@ -134,3 +134,16 @@ def test_poly1305_rfc_vector():
     a = sx.Argon2(1, 64, 1)
     stored = a.hash(b"pw")
     assert a.verify(b"pw", stored) and not a.verify(b"px", stored)
+
+
+def test_blake3_against_published_vector_and_independent_implementation():
+    assert c.blake3(b"").hex() == "af1349b9f5f9a1a6a0404dea36dcc9499bcb25c9adc112b7cc9a93cae41f3262"
+    b3 = pytest.importorskip("blake3")
+    key = bytes(range(32))
+    for n in (1, 63, 64, 65, 1023, 1024, 1025, 2049, 3073, 5000, 8193, 31744):   # block, chunk and tree boundaries
+        m = bytes(i % 251 for i in range(n))
+        assert c.blake3(m) == b3.blake3(m).digest()
+        assert c.blake3(m, 131) == b3.blake3(m).digest(131)
+        assert c.blake3(m, 32, key) == b3.blake3(m, key=key).digest()
+    with pytest.raises(ValueError):
+        c.blake3(b"x", key=b"short")
