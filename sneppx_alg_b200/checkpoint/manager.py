@@ -13,7 +13,7 @@ import os
 import pickle
 import random
 import re
-from typing import Any, Dict, List, Optional
+from typing import Dict, List, Optional
 
 import numpy as np
 import torch

@@ -10,7 +10,7 @@ from __future__ import annotations
 import ctypes
 import math
 import random as _random
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Any, Callable, Dict, List, Optional, Sequence
 
 import torch

@@ -13,7 +13,6 @@ from typing import Optional
 
 import torch
 import torch.nn as tnn
-import torch.nn.functional as F
 
 from ..nn.modules import Embedding, Linear, Module, RMSNorm
 from ..ops import functional as ops

@@ -15,7 +15,6 @@ import torch
 import torch.nn as tnn
 import torch.nn.functional as F
 
-from ..ops import functional as ops
 from ..ops import ssm
 from .modules import LayerNorm, Linear, Module, RMSNorm
 

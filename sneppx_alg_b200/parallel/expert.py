@@ -17,9 +17,8 @@ import torch.distributed as dist
 
 from ..ops import _lib
 from ..ops import moe as moe_ops
-from ..ops.functional import glu, glu_reference
+from ..ops.functional import glu
 from ..ops.gemm import gemm
-from .symm import SxPeers
 
 CH_PLAN, CH_DISP_SIG, CH_DISP_DONE, CH_COMB_SIG, CH_COMB_DONE = 48, 49, 50, 51, 52
 

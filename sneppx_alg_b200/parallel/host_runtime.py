@@ -5,7 +5,6 @@ fault-tolerance glue of kernel/distributed/checkpoint.c:382-457 / interface_bind
 from __future__ import annotations
 
 import ctypes as C
-import time
 from typing import Callable, Dict, List, Optional
 
 import numpy as np

@@ -9,7 +9,7 @@ last stage ``(hidden, labels) -> loss``. Hidden activations are single tensors o
 """
 from __future__ import annotations
 
-from typing import Callable, List, Optional
+from typing import List, Optional
 
 import torch
 import torch.distributed as dist

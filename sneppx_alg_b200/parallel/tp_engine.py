@@ -9,7 +9,7 @@ include/neural_core/architecture/distributed.h:45-50) and no code that combines 
 """
 from __future__ import annotations
 
-from typing import List, Optional, Tuple
+from typing import Tuple
 
 import torch
 import torch.distributed as dist

@@ -2,7 +2,6 @@
 single-process engine when there is one rank."""
 from __future__ import annotations
 
-import torch
 import torch.distributed as dist
 
 from ..training.engine import TrainEngine

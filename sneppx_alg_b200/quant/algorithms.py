@@ -5,7 +5,6 @@ tensors live there; the serving-path kernels (fp8 1x128 / 128x128, int4 group-12
 from __future__ import annotations
 
 import enum
-import math
 
 import torch
 

@@ -13,8 +13,6 @@ import time
 import uuid
 from typing import Dict, List, Optional
 
-import torch
-
 from ..security.ai_filter import OutputVerifier, PromptFilter
 from .llm_engine import LLMEngine, SamplingParams
 from .serving_engine import MetricsCollector, ServingEngine
@@ -73,7 +71,7 @@ class EngineWorker:
 def create_app(models: Dict[str, dict], default_model: Optional[str] = None, api_keys: Optional[set] = None,
                admin_key: Optional[str] = None):
     """models: {model_id: {"model": LlamaForCausalLM, "tokenizer": obj with encode/decode (optional), "engine_kwargs": {...}}}"""
-    from fastapi import FastAPI, Header, HTTPException, Request
+    from fastapi import FastAPI, Header, HTTPException
     from fastapi.responses import PlainTextResponse, StreamingResponse
     from pydantic import BaseModel, Field
 

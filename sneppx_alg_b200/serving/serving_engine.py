@@ -6,7 +6,6 @@ from __future__ import annotations
 
 import hashlib
 import os
-import random
 import threading
 import time
 from collections import deque

@@ -8,7 +8,7 @@ import copy
 import itertools
 import math
 import random
-from typing import Callable, Dict, Iterable, List
+from typing import Callable, Dict, Iterable
 
 import torch
 import torch.nn.functional as F

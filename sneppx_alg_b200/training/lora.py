@@ -4,13 +4,12 @@ from __future__ import annotations
 
 import copy
 import math
-from typing import Callable, List, Optional
+from typing import Callable
 
 import torch
 import torch.nn as tnn
 import torch.nn.functional as F
 
-from ..ops import functional as ops
 
 NF4 = torch.tensor([-1.0, -0.6961928009986877, -0.5250730514526367, -0.39491748809814453, -0.28444138169288635,
                     -0.18477343022823334, -0.09105003625154495, 0.0, 0.07958029955625534, 0.16093020141124725,
