@@ -7,8 +7,8 @@ thread pools, streamers and the ``*_kernel`` entry points (``cuda_kernels.py``) 
 Not reproduced, by design (one CUDA sm_100a device layer, portable C++ host code): the multi-vendor back-end and
 driver tables (``NPUBackend``, ``OpenVINOBackend``, ``ROCmDriver``, ``TPUDriver``, ``TensorRTExporter``, ``AutoBackend``
 ...), the x86 assembly wrappers (``AESNI``, ``SHANI``, ``Poly1305ASM``, ``Ed25519ASM``, ``ChaCha20AVX2``, ``FirewallASM``,
-``Asm*``), the code-obfuscation pipeline (``CfgFlattening``, ``OpaquePredicate``, ``StringEncryption`` ...), and the
-post-quantum schemes (``KyberKEM``, ``Dilithium``, ``SphincsPlus``).
+``Asm*``), control-flow flattening of native code (``CfgFlattening``; the obfuscation passes here work on NPE bytecode,
+``security/obfuscation.py``), and the post-quantum schemes (``KyberKEM``, ``Dilithium``, ``SphincsPlus``).
 """
 from __future__ import annotations
 
@@ -1628,3 +1628,16 @@ class RemoteAPIAuditBackend(_svc.AuditLogger):
 
 
 EdgeDevice = HardwareProbe
+
+
+def _obf(attr):
+    def get(*a, **k):
+        from .security import obfuscation
+        return getattr(obfuscation, attr)(*a, **k)
+    get.__name__ = attr
+    return get
+
+
+ObfuscationPipeline, ObfuscationConfig = _obf("ObfuscationPipeline"), _obf("ObfuscationConfig")
+InstructionSubstitution, OpaquePredicate = _obf("substitute_instructions"), _obf("insert_opaque_predicates")
+StringEncryption = _obf("seal_program")

@@ -15,8 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 EXCLUDED_PREFIXES = ("Asm", "AESNI", "SHANI", "Poly1305ASM", "Ed25519ASM", "ChaCha20AVX2", "FirewallASM", "MontgomeryMul",
                      "NPUBackend", "ONNXBackend", "OpenVINOBackend", "ROCmDriver", "TPUDriver", "TensorRTExporter", "AutoBackend",
                      "CPUBackend", "CPUFP16Backend", "CPUFP32Backend", "EdgeBackend", "InferenceBackend", "BackendRegistry",
-                     "register_backend", "KyberKEM", "Dilithium", "SphincsPlus", "CfgFlattening", "OpaquePredicate",
-                     "StringEncryption", "InstructionSubstitution", "Obfuscation")
+                     "register_backend", "KyberKEM", "Dilithium", "SphincsPlus", "CfgFlattening")
 
 
 def test_most_reference_names_resolve():
@@ -27,9 +26,9 @@ def test_most_reference_names_resolve():
             getattr(sx, n)
         except AttributeError:
             missing.append(n)
-    assert len(names) > 780 and len(missing) <= 40, (len(names), missing)
+    assert len(names) > 780 and len(missing) <= 32, (len(names), missing)
     by_design = [n for n in missing if n.startswith(EXCLUDED_PREFIXES)]
-    assert len(by_design) >= 25
+    assert len(by_design) >= 20
     with pytest.raises(AttributeError):
         sx.definitely_not_a_name
 
