@@ -148,19 +148,22 @@ def build_host(force: bool = False, verbose: bool = False) -> Path:
 SANITIZE_FLAGS = ["-O1", "-g", "-std=c++17", "-fPIC", "-pthread", "-fsanitize=address,undefined", "-fno-omit-frame-pointer"]
 
 
-def build_host_sanitized(verbose: bool = False) -> Path:
-    """AddressSanitizer + UndefinedBehaviorSanitizer build of the host runtime (``libsneppx_host_asan.so``). Run the
-    host-side tests against it with
-    ``LD_PRELOAD=$(g++ -print-file-name=libasan.so) ASAN_OPTIONS=detect_leaks=0 SX_HOST_LIB=<path> python -m pytest ...``
-    (the reference's ``scripts/run_sanitizers.sh`` does the same for its C tests)."""
+def build_host_sanitized(verbose: bool = False, kind: str = "address") -> Path:
+    """Sanitizer build of the host runtime. ``kind="address"``: AddressSanitizer + UndefinedBehaviorSanitizer
+    (``libsneppx_host_asan.so``); ``kind="thread"``: ThreadSanitizer (``libsneppx_host_tsan.so``). Run the host-side
+    tests against it with ``LD_PRELOAD=$(g++ -print-file-name=libasan.so) ASAN_OPTIONS=detect_leaks=0
+    SX_HOST_LIB=<path> python -m pytest ...`` (``libtsan.so`` and ``TSAN_OPTIONS=report_signal_unsafe=0`` for the thread
+    build); the reference's ``scripts/run_sanitizers.sh`` does the same for its C tests."""
     LIBDIR.mkdir(parents=True, exist_ok=True)
-    lib = LIBDIR / "libsneppx_host_asan.so"
+    tag, san = ("tsan", "thread") if kind == "thread" else ("asan", "address,undefined")
+    lib = LIBDIR / f"libsneppx_host_{tag}.so"
     cxx = shutil.which("g++") or shutil.which("c++")
     if cxx is None:
         raise RuntimeError("g++ not found")
     srcs = host_sources()
-    objs = _compile_objects(cxx, SANITIZE_FLAGS + ["-I", str(CSRC / "host")], srcs, host_headers(), "host_asan", verbose)
-    _run([cxx, "-shared", "-o", str(lib), *map(str, objs), "-pthread", "-fsanitize=address,undefined"])
+    flags = [f if not f.startswith("-fsanitize=") else f"-fsanitize={san}" for f in SANITIZE_FLAGS]
+    objs = _compile_objects(cxx, flags + ["-I", str(CSRC / "host")], srcs, host_headers(), f"host_{tag}", verbose)
+    _run([cxx, "-shared", "-o", str(lib), *map(str, objs), "-pthread", f"-fsanitize={san}"])
     return lib
 
 
