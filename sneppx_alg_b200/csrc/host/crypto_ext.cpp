@@ -153,6 +153,7 @@ int blake2b(const uint8_t* msg, size_t len, const uint8_t* key, size_t keylen, u
 SX_EXPORT void sx_sha512(const void* msg, size_t len, void* out64) { sha512((const uint8_t*)msg, len, (uint8_t*)out64); }
 SX_EXPORT void sx_sha3_256(const void* msg, size_t len, void* out32) { keccak((const uint8_t*)msg, len, 136, 0x06, (uint8_t*)out32, 32); }
 SX_EXPORT void sx_sha3_512(const void* msg, size_t len, void* out64) { keccak((const uint8_t*)msg, len, 72, 0x06, (uint8_t*)out64, 64); }
+SX_EXPORT void sx_shake128(const void* msg, size_t len, void* out, size_t outlen) { keccak((const uint8_t*)msg, len, 168, 0x1F, (uint8_t*)out, outlen); }
 SX_EXPORT void sx_shake256(const void* msg, size_t len, void* out, size_t outlen) { keccak((const uint8_t*)msg, len, 136, 0x1F, (uint8_t*)out, outlen); }
 SX_EXPORT int sx_blake2b(const void* msg, size_t len, const void* key, size_t keylen, void* out, size_t outlen) {
   return blake2b((const uint8_t*)msg, len, (const uint8_t*)key, keylen, (uint8_t*)out, outlen);

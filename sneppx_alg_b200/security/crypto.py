@@ -242,3 +242,61 @@ def blake3(data: bytes, length: int = 32, key: bytes = None) -> bytes:
     out = _buf(length)
     _L().sx_blake3(data, C.c_size_t(len(data)), key, out, C.c_size_t(length))
     return out.raw
+
+
+def shake128(data: bytes, length: int) -> bytes:
+    out = _buf(length)
+    _L().sx_shake128(data, C.c_size_t(len(data)), out, C.c_size_t(length))
+    return out.raw
+
+
+# ------------------------------------------------------------------------------------------ post-quantum
+_MLKEM_K = {512: 2, 768: 3, 1024: 4}
+
+
+def mlkem_sizes(level: int = 768):
+    """(encapsulation key, decapsulation key, ciphertext) lengths in bytes for ML-KEM-512 / 768 / 1024."""
+    ek, dk, ct = C.c_int(), C.c_int(), C.c_int()
+    if level not in _MLKEM_K or _L().sx_mlkem_sizes(_MLKEM_K[level], C.byref(ek), C.byref(dk), C.byref(ct)) != 0:
+        raise ValueError("level must be 512, 768 or 1024")
+    return ek.value, dk.value, ct.value
+
+
+def mlkem_keygen(level: int = 768, seed: bytes = None):
+    """ML-KEM (FIPS 203) key pair -> (encapsulation key, decapsulation key). `seed` is the 64-byte d || z of the
+    standard's internal key generation (fresh randomness when omitted)."""
+    import os
+    seed = os.urandom(64) if seed is None else seed
+    if len(seed) != 64:
+        raise ValueError("seed must be 64 bytes (d || z)")
+    n_ek, n_dk, _ = mlkem_sizes(level)
+    ek, dk = _buf(n_ek), _buf(n_dk)
+    _L().sx_mlkem_keygen(_MLKEM_K[level], seed[:32], seed[32:], ek, dk)
+    return ek.raw, dk.raw
+
+
+def mlkem_encaps(ek: bytes, level: int = 768, message: bytes = None):
+    """-> (shared secret of 32 bytes, ciphertext). `message` is the 32-byte randomness of the standard's internal
+    encapsulation (fresh when omitted). Raises on a key of the wrong length or with out-of-range coefficients."""
+    import os
+    n_ek, _, n_ct = mlkem_sizes(level)
+    if len(ek) != n_ek:
+        raise ValueError(f"encapsulation key must be {n_ek} bytes")
+    message = os.urandom(32) if message is None else message
+    if len(message) != 32:
+        raise ValueError("message must be 32 bytes")
+    ct, ss = _buf(n_ct), _buf(32)
+    if _L().sx_mlkem_encaps(_MLKEM_K[level], ek, message, ct, ss) != 0:
+        raise ValueError("encapsulation key fails the modulus check")
+    return ss.raw, ct.raw
+
+
+def mlkem_decaps(dk: bytes, ct: bytes, level: int = 768) -> bytes:
+    """Shared secret for a ciphertext. A forged or damaged ciphertext gives an unrelated pseudo-random secret
+    (implicit rejection), not an error."""
+    _, n_dk, n_ct = mlkem_sizes(level)
+    if len(dk) != n_dk or len(ct) != n_ct:
+        raise ValueError(f"decapsulation key must be {n_dk} bytes and the ciphertext {n_ct} bytes")
+    ss = _buf(32)
+    _L().sx_mlkem_decaps(_MLKEM_K[level], dk, ct, ss)
+    return ss.raw
