@@ -1236,6 +1236,8 @@ class SipHash:
 
 
 DRBG = EntropyPool = _c.HmacDrbg
+KyberKEM, Dilithium, SphincsPlus = _c.KyberKEM, _c.Dilithium, _c.SphincsPlus
+MontgomeryMul = _c.MontgomeryMul
 SecureAllocator = _c.GuardedBuffer
 
 

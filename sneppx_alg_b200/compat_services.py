@@ -7,8 +7,8 @@ thread pools, streamers and the ``*_kernel`` entry points (``cuda_kernels.py``) 
 Not reproduced, by design (one CUDA sm_100a device layer, portable C++ host code): the multi-vendor back-end and
 driver tables (``NPUBackend``, ``OpenVINOBackend``, ``ROCmDriver``, ``TPUDriver``, ``TensorRTExporter``, ``AutoBackend``
 ...), the x86 assembly wrappers (``AESNI``, ``SHANI``, ``Poly1305ASM``, ``Ed25519ASM``, ``ChaCha20AVX2``, ``FirewallASM``,
-``Asm*``), control-flow flattening of native code (``CfgFlattening``; the obfuscation passes here work on NPE bytecode,
-``security/obfuscation.py``), and the post-quantum schemes (``KyberKEM``, ``Dilithium``, ``SphincsPlus``).
+``Asm*``) and control-flow flattening of native code (``CfgFlattening``; the obfuscation passes here work on NPE
+bytecode, ``security/obfuscation.py``).
 """
 from __future__ import annotations
 
@@ -1641,3 +1641,9 @@ def _obf(attr):
 ObfuscationPipeline, ObfuscationConfig = _obf("ObfuscationPipeline"), _obf("ObfuscationConfig")
 InstructionSubstitution, OpaquePredicate = _obf("substitute_instructions"), _obf("insert_opaque_predicates")
 StringEncryption = _obf("seal_program")
+
+
+# ---------------------------------------------------------------------------------------------- late additions
+from .utils.net import RDMA  # noqa: E402,F401
+
+ABOOTPartition = _svc.ABSlots

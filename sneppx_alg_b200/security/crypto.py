@@ -300,3 +300,185 @@ def mlkem_decaps(dk: bytes, ct: bytes, level: int = 768) -> bytes:
     ss = _buf(32)
     _L().sx_mlkem_decaps(_MLKEM_K[level], dk, ct, ss)
     return ss.raw
+
+
+_MLDSA_LEVELS = (44, 65, 87)
+
+
+def mldsa_sizes(level: int = 65):
+    """(public key, private key, signature) lengths in bytes for ML-DSA-44 / 65 / 87."""
+    pk, sk, sig = C.c_int(), C.c_int(), C.c_int()
+    if level not in _MLDSA_LEVELS or _L().sx_mldsa_sizes(level, C.byref(pk), C.byref(sk), C.byref(sig)) != 0:
+        raise ValueError("level must be 44, 65 or 87")
+    return pk.value, sk.value, sig.value
+
+
+def mldsa_keygen(level: int = 65, seed: bytes = None):
+    """ML-DSA (FIPS 204) key pair from a 32-byte seed -> (public key, private key)."""
+    import os
+    seed = os.urandom(32) if seed is None else seed
+    if len(seed) != 32:
+        raise ValueError("seed must be 32 bytes")
+    n_pk, n_sk, _ = mldsa_sizes(level)
+    pk, sk = _buf(n_pk), _buf(n_sk)
+    _L().sx_mldsa_keygen(level, seed, pk, sk)
+    return pk.raw, sk.raw
+
+
+def mldsa_sign(sk: bytes, message: bytes, level: int = 65, context: bytes = b"", deterministic: bool = False) -> bytes:
+    """Signature of `message` (pure ML-DSA with a context string of at most 255 bytes). Hedged with 32 fresh random
+    bytes unless `deterministic`."""
+    import os
+    _, n_sk, n_sig = mldsa_sizes(level)
+    if len(sk) != n_sk or len(context) > 255:
+        raise ValueError(f"private key must be {n_sk} bytes and the context at most 255 bytes")
+    rnd = bytes(32) if deterministic else os.urandom(32)
+    sig = _buf(n_sig)
+    if _L().sx_mldsa_sign(level, sk, message, C.c_size_t(len(message)), context, C.c_size_t(len(context)), rnd, sig) != 0:
+        raise RuntimeError("ML-DSA signing failed")
+    return sig.raw
+
+
+def mldsa_verify(pk: bytes, message: bytes, signature: bytes, level: int = 65, context: bytes = b"") -> bool:
+    n_pk, _, n_sig = mldsa_sizes(level)
+    if len(pk) != n_pk or len(signature) != n_sig or len(context) > 255:
+        return False
+    return _L().sx_mldsa_verify(level, pk, message, C.c_size_t(len(message)), context, C.c_size_t(len(context)), signature) == 1
+
+
+_SLH_VARIANTS = {"128f": 0, "128s": 1}
+
+
+def slhdsa_sizes(variant: str = "128f"):
+    """(public key, private key, signature) lengths for SLH-DSA-SHAKE-128f / 128s."""
+    pk, sk, sig = C.c_int(), C.c_int(), C.c_int()
+    if variant not in _SLH_VARIANTS or _L().sx_slhdsa_sizes(_SLH_VARIANTS[variant], C.byref(pk), C.byref(sk), C.byref(sig)) != 0:
+        raise ValueError("variant must be '128f' or '128s'")
+    return pk.value, sk.value, sig.value
+
+
+def slhdsa_keygen(variant: str = "128f", seed: bytes = None):
+    """SLH-DSA (FIPS 205, SHAKE) key pair from the 48-byte SK.seed || SK.prf || PK.seed -> (public key, private key)."""
+    import os
+    seed = os.urandom(48) if seed is None else seed
+    if len(seed) != 48:
+        raise ValueError("seed must be 48 bytes")
+    n_pk, n_sk, _ = slhdsa_sizes(variant)
+    pk, sk = _buf(n_pk), _buf(n_sk)
+    _L().sx_slhdsa_keygen(_SLH_VARIANTS[variant], seed, pk, sk)
+    return pk.raw, sk.raw
+
+
+def slhdsa_sign(sk: bytes, message: bytes, variant: str = "128f", context: bytes = b"", deterministic: bool = False) -> bytes:
+    import os
+    _, n_sk, n_sig = slhdsa_sizes(variant)
+    if len(sk) != n_sk or len(context) > 255:
+        raise ValueError(f"private key must be {n_sk} bytes and the context at most 255 bytes")
+    sig = _buf(n_sig)
+    rnd = None if deterministic else os.urandom(16)
+    if _L().sx_slhdsa_sign(_SLH_VARIANTS[variant], sk, message, C.c_size_t(len(message)), context, C.c_size_t(len(context)), rnd, sig) != 0:
+        raise RuntimeError("SLH-DSA signing failed")
+    return sig.raw
+
+
+def slhdsa_verify(pk: bytes, message: bytes, signature: bytes, variant: str = "128f", context: bytes = b"") -> bool:
+    n_pk, _, n_sig = slhdsa_sizes(variant)
+    if len(pk) != n_pk or len(signature) != n_sig or len(context) > 255:
+        return False
+    return _L().sx_slhdsa_verify(_SLH_VARIANTS[variant], pk, message, C.c_size_t(len(message)), context,
+                                 C.c_size_t(len(context)), signature) == 1
+
+
+class KyberKEM:
+    """ML-KEM behind the reference's class shape (``crypto_kem.py:17-54``): ``keypair() -> (pk, sk)``,
+    ``encapsulate(pk) -> (ciphertext, shared secret)``, ``decapsulate(sk, ciphertext) -> shared secret``."""
+    MODE_ML_KEM_512, MODE_ML_KEM_768, MODE_ML_KEM_1024 = 512, 768, 1024
+
+    def __init__(self, mode: int = 1024):
+        self.mode = mode
+
+    def keypair(self, seed: bytes = None):
+        return mlkem_keygen(self.mode, None if seed is None else sha3_512(seed))
+
+    def encapsulate(self, pk: bytes):
+        ss, ct = mlkem_encaps(pk, self.mode)
+        return ct, ss
+
+    def decapsulate(self, sk: bytes, ct: bytes):
+        return mlkem_decaps(sk, ct, self.mode)
+
+
+class Dilithium:
+    """ML-DSA behind the reference's class shape (``crypto_sign.py:93-131``); modes 2 / 3 / 5 are ML-DSA-44 / 65 / 87."""
+    MODE_ML_DSA_44, MODE_ML_DSA_65, MODE_ML_DSA_87 = 2, 3, 5
+    _LEVEL = {2: 44, 3: 65, 5: 87}
+
+    def __init__(self, mode: int = 2):
+        self.mode, self.level = mode, self._LEVEL[mode]
+
+    def keypair(self, seed: bytes = None):
+        return mldsa_keygen(self.level, None if seed is None else sha3_256(seed))
+
+    def sign(self, sk: bytes, msg: bytes) -> bytes:
+        return mldsa_sign(sk, msg, self.level)
+
+    def verify(self, pk: bytes, msg: bytes, sig: bytes) -> bool:
+        return mldsa_verify(pk, msg, sig, self.level)
+
+
+class SphincsPlus:
+    """SLH-DSA-SHAKE behind the reference's class shape (``crypto_sign.py:136-168``); variants "128f" and "128s"."""
+
+    def __init__(self, variant: str = "128f"):
+        self.variant = variant
+
+    def keypair(self, seed: bytes = None):
+        return slhdsa_keygen(self.variant, None if seed is None else shake256(seed, 48))
+
+    def sign(self, sk: bytes, msg: bytes) -> bytes:
+        return slhdsa_sign(sk, msg, self.variant)
+
+    def verify(self, pk: bytes, msg: bytes, sig: bytes) -> bool:
+        return slhdsa_verify(pk, msg, sig, self.variant)
+
+
+class MontgomeryMul:
+    """Montgomery modular multiplication for an odd modulus (the reference's ``MontgomeryMul``, ``crypto_asm.py:147``,
+    is ``a * b * inv % mod``). ``to_mont`` / ``from_mont`` convert, ``mont_mul`` multiplies two Montgomery-form values
+    with one reduction (no division by the modulus), ``pow`` is square-and-multiply in that form."""
+
+    def __init__(self, modulus: int = None):
+        if modulus is not None:
+            if modulus % 2 == 0 or modulus < 3:
+                raise ValueError("modulus must be odd and >= 3")
+            self.n = modulus
+            self.bits = modulus.bit_length()
+            self.r_mask = (1 << self.bits) - 1
+            self.n_prime = (-pow(modulus, -1, 1 << self.bits)) & self.r_mask
+            self.r2 = pow(1 << self.bits, 2, modulus)
+
+    def _redc(self, t: int) -> int:
+        m = ((t & self.r_mask) * self.n_prime) & self.r_mask
+        u = (t + m * self.n) >> self.bits
+        return u - self.n if u >= self.n else u
+
+    def to_mont(self, a: int) -> int:
+        return self._redc((a % self.n) * self.r2)
+
+    def from_mont(self, a: int) -> int:
+        return self._redc(a)
+
+    def mont_mul(self, a: int, b: int) -> int:
+        return self._redc(a * b)
+
+    def pow(self, base: int, exponent: int) -> int:
+        x, acc = self.to_mont(base), self.to_mont(1)
+        while exponent:
+            if exponent & 1:
+                acc = self.mont_mul(acc, x)
+            x = self.mont_mul(x, x)
+            exponent >>= 1
+        return self.from_mont(acc)
+
+    def mul(self, a: int, b: int, mod: int, inv: int = 1) -> int:
+        return (a * b * inv) % mod

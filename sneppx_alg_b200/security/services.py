@@ -157,13 +157,16 @@ class AuditLogger:
 # ---- S7 updates
 def sign_update(path: str, key: bytes, version: str, scheme: str = "hmac-sha256") -> dict:
     """Manifest for an update file. ``hmac-sha256``: `key` is a shared secret. ``ed25519``: `key` is the 32-byte
-    signing seed and the manifest is verified with the public key only."""
+    signing seed and the manifest is verified with the public key only. ``ml-dsa-65``: `key` is the ML-DSA private
+    key (post-quantum signature, FIPS 204), verified with its public key."""
     data = open(path, "rb").read()
     manifest = {"file": os.path.basename(path), "version": version, "sha256": crypto.sha256(data).hex(), "size": len(data),
                 "scheme": scheme}
     payload = json.dumps(manifest, sort_keys=True).encode()
     if scheme == "ed25519":
         manifest["signature"] = crypto.ed25519_sign(key, payload).hex()
+    elif scheme == "ml-dsa-65":
+        manifest["signature"] = crypto.mldsa_sign(key, payload, 65, context=b"sneppx-update").hex()
     elif scheme == "hmac-sha256":
         manifest["signature"] = crypto.hmac_sha256(key, payload).hex()
     else:
@@ -172,12 +175,15 @@ def sign_update(path: str, key: bytes, version: str, scheme: str = "hmac-sha256"
 
 
 def verify_update(path: str, manifest: dict, key: bytes, min_version: str = "0") -> bool:
-    """`key`: the shared secret (hmac-sha256) or the signer's 32-byte public key (ed25519)."""
+    """`key`: the shared secret (hmac-sha256) or the signer's public key (ed25519: 32 bytes; ml-dsa-65: 1952 bytes)."""
     m = dict(manifest)
     sig = bytes.fromhex(m.pop("signature"))
     payload = json.dumps(m, sort_keys=True).encode()
     if m.get("scheme", "hmac-sha256") == "ed25519":
         if not crypto.ed25519_verify(key, payload, sig):
+            return False
+    elif m.get("scheme") == "ml-dsa-65":
+        if not crypto.mldsa_verify(key, payload, sig, 65, context=b"sneppx-update"):
             return False
     elif not crypto.ct_equal(sig, crypto.hmac_sha256(key, payload)):
         return False
@@ -291,3 +297,57 @@ class UsageTracker:
 
     def report(self, owner: str) -> dict:
         return dict(self.usage.get(owner, {}))
+
+
+class ABSlots:
+    """A/B slots for atomic updates of a deployed directory (``container_security.py:451-489`` keeps the slot of the
+    boot partition; here the unit is a model / runtime directory): the inactive slot is filled and verified, then one
+    atomic rename of the ``current`` marker makes it live, and ``rollback`` renames it back."""
+
+    def __init__(self, root: str):
+        self.root = root
+        for s in ("_a", "_b"):
+            os.makedirs(os.path.join(root, "slot" + s), exist_ok=True)
+        if not os.path.exists(self._marker):
+            self._write_marker("_a")
+
+    @property
+    def _marker(self) -> str:
+        return os.path.join(self.root, "current")
+
+    def _write_marker(self, slot: str):
+        tmp = self._marker + ".tmp"
+        with open(tmp, "w") as f:
+            f.write(slot)
+            f.flush()
+            os.fsync(f.fileno())
+        os.replace(tmp, self._marker)
+
+    @property
+    def current(self) -> str:
+        return open(self._marker).read().strip()
+
+    @property
+    def inactive_slot(self) -> str:
+        return "_b" if self.current == "_a" else "_a"
+
+    def get_partition_path(self, partition: str = "", slot: Optional[str] = None) -> str:
+        return os.path.join(self.root, "slot" + (slot or self.current), partition)
+
+    def stage(self, name: str, data: bytes) -> str:
+        """Writes a file into the inactive slot."""
+        path = self.get_partition_path(name, self.inactive_slot)
+        os.makedirs(os.path.dirname(path), exist_ok=True)
+        with open(path, "wb") as f:
+            f.write(data)
+        return path
+
+    def switch_slot(self, verify: Optional[Callable[[str], bool]] = None) -> bool:
+        """Makes the inactive slot live if `verify(slot directory)` accepts it (always, when no verifier is given)."""
+        target = self.inactive_slot
+        if verify is not None and not verify(self.get_partition_path("", target)):
+            return False
+        self._write_marker(target)
+        return True
+
+    rollback = switch_slot

@@ -414,3 +414,79 @@ class ServiceDirectory:
             _L().sx_sd_destroy(self._h)
         except Exception:
             pass
+
+
+class RDMA:
+    """One-sided read / write of registered memory regions between processes of one host, over POSIX shared memory.
+
+    The reference's ``RDMA`` (``net_bindings.py:193-225``) is a shell whose ``read`` / ``write`` return 0. Between GPUs
+    the one-sided transport of this framework is NVLink peer memory (``torch.distributed._symmetric_memory`` buffers
+    read and written by the fused kernels); this class gives host memory the same shape: a process registers a region
+    under a key, any other process attaches by key and reads or writes it at an offset with no involvement of the
+    owner. Ordering between writer and reader is the caller's business (a flag word in the region, or the
+    coordinator's barrier), as with real RDMA."""
+
+    def __init__(self):
+        self._regions = {}
+        self._owned = set()
+        self._open = False
+
+    def open(self, device_idx: int = 0) -> bool:
+        self._open = True
+        return True
+
+    def register_memory(self, key: str, nbytes: int = 0, array: Optional[np.ndarray] = None) -> np.ndarray:
+        """Creates the shared region `key` (initialised from `array` when given) and returns a NumPy view of it."""
+        from multiprocessing import shared_memory
+        if not self._open:
+            raise RuntimeError("open() first")
+        nbytes = int(array.nbytes if array is not None else nbytes)
+        shm = shared_memory.SharedMemory(name=key, create=True, size=max(nbytes, 1))
+        self._regions[key] = shm
+        self._owned.add(key)
+        view = np.ndarray((nbytes,), dtype=np.uint8, buffer=shm.buf)
+        if array is not None:
+            view[:] = np.frombuffer(np.ascontiguousarray(array).tobytes(), dtype=np.uint8)
+        return view
+
+    def attach(self, key: str):
+        from multiprocessing import shared_memory
+        if key not in self._regions:
+            self._regions[key] = shared_memory.SharedMemory(name=key)
+        return self._regions[key]
+
+    def read(self, key: str, remote_offset: int, local: np.ndarray, length: Optional[int] = None) -> int:
+        """Copies `length` bytes at `remote_offset` of region `key` into `local`; returns the byte count."""
+        shm = self.attach(key)
+        dst = local.reshape(-1).view(np.uint8)
+        length = dst.nbytes if length is None else int(length)
+        if remote_offset < 0 or remote_offset + length > shm.size or length > dst.nbytes:
+            raise ValueError("read outside the registered region or the local buffer")
+        dst[:length] = np.frombuffer(shm.buf, dtype=np.uint8, count=length, offset=remote_offset)
+        return length
+
+    def write(self, key: str, remote_offset: int, local: np.ndarray, length: Optional[int] = None) -> int:
+        shm = self.attach(key)
+        src = np.ascontiguousarray(local).reshape(-1).view(np.uint8)
+        length = src.nbytes if length is None else int(length)
+        if remote_offset < 0 or remote_offset + length > shm.size or length > src.nbytes:
+            raise ValueError("write outside the registered region or the local buffer")
+        np.frombuffer(shm.buf, dtype=np.uint8, count=length, offset=remote_offset)[:] = src[:length]
+        return length
+
+    def deregister_memory(self, key: Optional[str] = None):
+        for k in ([key] if key else list(self._regions)):
+            shm = self._regions.pop(k, None)
+            if shm is None:
+                continue
+            shm.close()
+            if k in self._owned:
+                self._owned.discard(k)
+                try:
+                    shm.unlink()
+                except FileNotFoundError:
+                    pass
+
+    def close(self):
+        self.deregister_memory()
+        self._open = False

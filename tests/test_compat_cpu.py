@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 EXCLUDED_PREFIXES = ("Asm", "AESNI", "SHANI", "Poly1305ASM", "Ed25519ASM", "ChaCha20AVX2", "FirewallASM", "MontgomeryMul",
                      "NPUBackend", "ONNXBackend", "OpenVINOBackend", "ROCmDriver", "TPUDriver", "TensorRTExporter", "AutoBackend",
                      "CPUBackend", "CPUFP16Backend", "CPUFP32Backend", "EdgeBackend", "InferenceBackend", "BackendRegistry",
-                     "register_backend", "KyberKEM", "Dilithium", "SphincsPlus", "CfgFlattening")
+                     "register_backend", "CfgFlattening")
 
 
 def test_most_reference_names_resolve():
