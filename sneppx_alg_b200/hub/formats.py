@@ -143,3 +143,176 @@ def load_any(path, device="cpu") -> Dict[str, torch.Tensor]:
     if p.endswith(".npz"):
         return load_npz(path)
     raise ValueError(f"unknown weight file type: {path}")
+
+
+class HierarchicalFile:
+    """Single-file hierarchical store: groups, n-dimensional datasets and attributes addressed by ``/a/b/c`` paths
+    (the API of the reference's HDF5-like format, ``fs/format/hdf5_format.h:31-115``: open / create_group /
+    dataset_exists / read_dataset / write_dataset / read_attribute / write_attribute / list_children; its body keeps
+    the tree in memory only).
+
+    Layout: ``SXH5`` magic, version, the byte offset of the index (u64), then dataset payloads appended on 64-byte
+    boundaries, then a JSON index {path: {"kind", "dtype", "shape", "offset", "nbytes", "attrs"}}. Appending rewrites
+    only the index; replaced datasets leave their old payload behind until ``repack``. Datasets are read through a
+    memory map, so opening a file of any size costs the index only."""
+
+    MAGIC = b"SXH5"
+
+    def __init__(self, path: str, mode: str = "r"):
+        import os
+        if mode not in ("r", "w", "a"):
+            raise ValueError("mode must be 'r', 'w' or 'a'")
+        self.path, self.mode, self._dirty = path, mode, False
+        if mode == "w" or (mode == "a" and not os.path.exists(path)):
+            self.index = {"/": {"kind": "group", "attrs": {}}}
+            with open(path, "wb") as f:
+                f.write(self.MAGIC + struct.pack("<IQ", 1, 16))
+            self._end = 16
+            self._dirty = True
+        else:
+            with open(path, "rb") as f:
+                head = f.read(16)
+                if len(head) != 16 or head[:4] != self.MAGIC:
+                    raise ValueError("not a hierarchical store file")
+                _, off = struct.unpack("<IQ", head[4:])
+                size = f.seek(0, 2)
+                if off < 16 or off > size:
+                    raise ValueError("index offset outside the file")
+                f.seek(off)
+                try:
+                    self.index = json.loads(f.read().decode())
+                except Exception as e:
+                    raise ValueError("corrupt index") from e
+            for p, e in self.index.items():
+                if e.get("kind") == "dataset" and e["offset"] + e["nbytes"] > off:
+                    raise ValueError(f"dataset {p} extends past the data region")
+            self._end = off
+
+    # ---- tree
+    @staticmethod
+    def _norm(path: str) -> str:
+        parts = [p for p in path.split("/") if p]
+        return "/" + "/".join(parts)
+
+    def create_group(self, path: str):
+        self._writable()
+        parts = [p for p in path.split("/") if p]
+        for i in range(1, len(parts) + 1):
+            p = "/" + "/".join(parts[:i])
+            e = self.index.setdefault(p, {"kind": "group", "attrs": {}})
+            if e["kind"] != "group":
+                raise ValueError(f"{p} is a dataset")
+        self._dirty = True
+
+    def exists(self, path: str) -> bool:
+        return self._norm(path) in self.index
+
+    def dataset_exists(self, path: str) -> bool:
+        return self.index.get(self._norm(path), {}).get("kind") == "dataset"
+
+    def list_children(self, path: str = "/"):
+        base = self._norm(path).rstrip("/") + "/"
+        return sorted({p[len(base):].split("/")[0] for p in self.index if p.startswith(base) and p != base and p != "/"})
+
+    def _writable(self):
+        if self.mode == "r":
+            raise PermissionError("file opened read-only")
+
+    # ---- datasets
+    def write_dataset(self, path: str, data):
+        self._writable()
+        a = data.detach().cpu().numpy() if isinstance(data, torch.Tensor) and data.dtype != torch.bfloat16 else data
+        bf16 = isinstance(a, torch.Tensor)
+        if bf16:                                                       # bfloat16 has no NumPy dtype: store the bit pattern
+            a = a.detach().cpu().view(torch.int16).numpy()
+        a = np.ascontiguousarray(a)
+        p = self._norm(path)
+        if "/" in p[1:]:
+            self.create_group(p.rsplit("/", 1)[0])
+        if self.index.get(p, {}).get("kind") == "group":
+            raise ValueError(f"{p} is a group")
+        off = (self._end + 63) // 64 * 64
+        with open(self.path, "r+b") as f:
+            f.seek(off)
+            f.write(a.tobytes())
+        self.index[p] = {"kind": "dataset", "dtype": "bfloat16" if bf16 else a.dtype.str, "shape": list(a.shape), "offset": off,
+                         "nbytes": a.nbytes, "attrs": self.index.get(p, {}).get("attrs", {})}
+        self._end = off + a.nbytes
+        self._dirty = True
+
+    def read_dataset(self, path: str, as_tensor: bool = False):
+        e = self.index.get(self._norm(path))
+        if e is None or e["kind"] != "dataset":
+            raise KeyError(path)
+        self.flush()
+        bf16 = e["dtype"] == "bfloat16"
+        dt = np.dtype("<i2") if bf16 else np.dtype(e["dtype"])
+        if e["nbytes"] == 0:
+            a = np.zeros(e["shape"], dtype=dt)
+        else:
+            a = np.memmap(self.path, dtype=dt, mode="r", offset=e["offset"], shape=tuple(e["shape"]))
+        if bf16:
+            return torch.from_numpy(np.array(a)).view(torch.bfloat16)
+        return torch.from_numpy(np.array(a)) if as_tensor else a
+
+    # ---- attributes (JSON values, or bytes stored as hex)
+    def write_attribute(self, path: str, name: str, value):
+        self._writable()
+        p = self._norm(path)
+        if p not in self.index:
+            self.create_group(p)
+        self.index[p]["attrs"][name] = {"hex": value.hex()} if isinstance(value, (bytes, bytearray)) else {"json": value}
+        self._dirty = True
+
+    def read_attribute(self, path: str, name: str):
+        v = self.index[self._norm(path)]["attrs"][name]
+        return bytes.fromhex(v["hex"]) if "hex" in v else v["json"]
+
+    # ---- whole-model helpers
+    def write_state_dict(self, state: Dict[str, torch.Tensor], root: str = "/"):
+        for k, v in state.items():
+            self.write_dataset(self._norm(root) + "/" + k.replace(".", "/"), v)
+
+    def read_state_dict(self, root: str = "/") -> Dict[str, torch.Tensor]:
+        base = self._norm(root).rstrip("/") + "/"
+        return {p[len(base):].replace("/", "."): self.read_dataset(p, as_tensor=True)
+                for p, e in self.index.items() if e["kind"] == "dataset" and p.startswith(base)}
+
+    def repack(self):
+        """Rewrites the file without the payloads that replaced datasets left behind."""
+        self._writable()
+        import os
+        live = {p: np.array(self.read_dataset(p)) if e["dtype"] != "bfloat16" else self.read_dataset(p)
+                for p, e in self.index.items() if e["kind"] == "dataset"}
+        tmp = HierarchicalFile(self.path + ".repack", "w")
+        for p, e in self.index.items():
+            if e["kind"] == "group":
+                tmp.create_group(p)
+        for p, a in live.items():
+            tmp.write_dataset(p, a)
+        for p, e in self.index.items():
+            tmp.index[p]["attrs"] = e["attrs"]
+        tmp._dirty = True
+        tmp.close()
+        os.replace(self.path + ".repack", self.path)
+        self.index, self._end, self._dirty = tmp.index, tmp._end, False
+
+    def flush(self):
+        if self._dirty and self.mode != "r":
+            blob = json.dumps(self.index).encode()
+            with open(self.path, "r+b") as f:
+                f.seek(self._end)
+                f.write(blob)
+                f.truncate()
+                f.seek(4)
+                f.write(struct.pack("<IQ", 1, self._end))
+            self._dirty = False
+
+    def close(self):
+        self.flush()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()

@@ -51,3 +51,53 @@ def test_gateway_weights_fallback_and_rate_limit():
         gw4.query("r", 1)
     with pytest.raises(KeyError):
         gw4.query("nope", 1)
+
+
+def test_hierarchical_file_groups_datasets_attributes(tmp_path):
+    import numpy as np
+    from sneppx_alg_b200.hub.formats import HierarchicalFile
+    path = str(tmp_path / "store.sxh5")
+    w = torch.randn(5, 7)
+    b16 = torch.randn(4, 3).bfloat16()
+    with HierarchicalFile(path, "w") as f:
+        f.create_group("/model/layers/0")
+        f.write_dataset("/model/layers/0/weight", w)
+        f.write_dataset("/model/layers/0/scale", b16)
+        f.write_dataset("/stats/steps", np.arange(10, dtype=np.int64))
+        f.write_dataset("/stats/empty", np.zeros((0, 4), dtype=np.float32))
+        f.write_attribute("/model", "arch", {"d_model": 64, "layers": 2})
+        f.write_attribute("/model/layers/0/weight", "digest", b"\x01\x02")
+        assert np.array_equal(f.read_dataset("/stats/steps"), np.arange(10))      # readable before close
+    with HierarchicalFile(path, "r") as f:
+        assert f.list_children("/") == ["model", "stats"] and f.list_children("/model/layers/0") == ["scale", "weight"]
+        assert f.dataset_exists("/model/layers/0/weight") and not f.dataset_exists("/model/layers") and f.exists("/model/layers")
+        assert torch.equal(f.read_dataset("/model/layers/0/weight", as_tensor=True), w)
+        assert torch.equal(f.read_dataset("/model/layers/0/scale"), b16)
+        assert f.read_dataset("/stats/empty").shape == (0, 4)
+        assert f.read_attribute("/model", "arch")["d_model"] == 64
+        assert f.read_attribute("/model/layers/0/weight", "digest") == b"\x01\x02"
+        with pytest.raises(PermissionError):
+            f.write_dataset("/x", w)
+        with pytest.raises(KeyError):
+            f.read_dataset("/model")
+    import os
+    with HierarchicalFile(path, "a") as f:                                         # append + replace + repack
+        f.write_dataset("/model/layers/0/weight", w * 2)
+        f.write_state_dict({"head.weight": w, "head.bias": torch.zeros(7)}, root="/extra")
+    grown = os.path.getsize(path)
+    with HierarchicalFile(path, "a") as f:
+        assert torch.equal(f.read_dataset("/model/layers/0/weight", as_tensor=True), w * 2)
+        sd = f.read_state_dict("/extra")
+        assert set(sd) == {"head.weight", "head.bias"} and torch.equal(sd["head.weight"], w)
+        f.repack()
+        assert f.read_attribute("/model", "arch")["layers"] == 2
+        assert torch.equal(f.read_dataset("/model/layers/0/scale"), b16)
+    assert os.path.getsize(path) < grown
+    # damaged files are reported, not trusted
+    raw = bytearray(open(path, "rb").read())
+    open(path, "wb").write(bytes(raw[:8]) + (10 ** 12).to_bytes(8, "little") + bytes(raw[16:]))
+    with pytest.raises(ValueError):
+        HierarchicalFile(path, "r")
+    open(path, "wb").write(b"nope")
+    with pytest.raises(ValueError):
+        HierarchicalFile(path, "r")

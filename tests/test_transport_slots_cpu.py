@@ -65,3 +65,62 @@ def test_montgomery_multiplication():
     with pytest.raises(ValueError):
         crypto.MontgomeryMul(100)
     assert crypto.MontgomeryMul().mul(3, 4, 7, 1) == 5
+
+
+def test_secure_multiplexed_streams():
+    import threading
+    from sneppx_alg_b200.utils.net import FramedSocket, SecureStreamConnection, close_listener
+    lfd, port = FramedSocket.listen(0)
+    out = {}
+
+    def server():
+        c = SecureStreamConnection.accept(lfd, psk=b"cluster-secret")
+        out["a"] = c.stream_recv(0)
+        big = b""
+        while True:
+            part = c.stream_recv(2)
+            if part is None:
+                break
+            big += part
+        out["big"] = big
+        out["b"] = c.stream_recv(0)                       # queued while stream 2 was being drained
+        sid = c.stream_open()
+        c.stream_send(sid, b"reply on " + str(sid).encode())
+        out["server"] = c
+    t = threading.Thread(target=server)
+    t.start()
+    c = SecureStreamConnection.dial("127.0.0.1", port, psk=b"cluster-secret")
+    s0, s2 = c.stream_open(), c.stream_open()
+    assert (s0, s2) == (0, 2)
+    payload = os.urandom(300_000)
+    c.stream_send(s0, b"hello")
+    c.stream_send(s2, payload[:100_000], chunk=65536)
+    c.stream_send(s0, b"second")
+    c.stream_send(s2, payload[100_000:], chunk=65536)
+    c.stream_close(s2)
+    assert c.stream_recv(1) == b"reply on 1"
+    t.join(30)
+    assert out["a"] == b"hello" and out["b"] == b"second" and out["big"] == payload
+    # a frame altered on the wire fails authentication at the receiver
+    srv = out["server"]
+    c.sock.send_message(b"\x00\x00\x00\x00\x00" + b"x" * 40)
+    with pytest.raises(ConnectionError):
+        srv.stream_recv(0)
+    c.close(); srv.close()
+
+    # a peer with another pre-shared key is turned away during the handshake
+    res = {}
+
+    def server2():
+        try:
+            SecureStreamConnection.accept(lfd, psk=b"cluster-secret")
+            res["ok"] = True
+        except ConnectionError:
+            res["ok"] = False
+    t = threading.Thread(target=server2)
+    t.start()
+    with pytest.raises(ConnectionError):
+        SecureStreamConnection.dial("127.0.0.1", port, timeout_ms=2000, psk=b"wrong")
+    t.join(30)
+    assert res["ok"] is False
+    close_listener(lfd)
