@@ -131,7 +131,7 @@ def load_pth(path, device="cpu") -> Dict[str, torch.Tensor]:
 
 
 def load_any(path, device="cpu") -> Dict[str, torch.Tensor]:
-    """Dispatch on the file extension: .safetensors, .sneppx, .pth / .pt / .bin, .npz."""
+    """Dispatch on the file extension: .safetensors, .sneppx, .pth / .pt / .bin, .npz, .gguf, .sxh5."""
     p = path.lower()
     if p.endswith(".safetensors"):
         return load_safetensors(path, device)[0]
@@ -142,6 +142,12 @@ def load_any(path, device="cpu") -> Dict[str, torch.Tensor]:
         return load_pth(path, device)
     if p.endswith(".npz"):
         return load_npz(path)
+    if p.endswith(".gguf"):
+        from .model_card import load_gguf
+        return load_gguf(path)[0]
+    if p.endswith(".sxh5"):
+        with HierarchicalFile(path, "r") as f:
+            return f.read_state_dict("/")
     raise ValueError(f"unknown weight file type: {path}")
 
 
