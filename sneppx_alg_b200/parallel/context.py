@@ -247,3 +247,71 @@ def cp_ssd_scan(x, dt, A, Bm, Cm, D=None, chunk=64, group=None, mode: str = "par
     # ranks whose output does not use the gathered states (rank 0, and every rank for its successors' entries) still
     # have to take part in the backward collective that returns the other ranks' state gradients
     return y + (packed.sum() * 0).to(y.dtype)
+
+
+# ----------------------------------------------------------------------------------------------- Ulysses
+def _a2a(x, group):
+    x = x.contiguous()                 # before empty_like: a permuted view would hand its strides to the output
+    out = torch.empty_like(x)
+    dist.all_to_all_single(out, x, group=group)
+    return out
+
+
+class _SeqToHead(torch.autograd.Function):
+    """[B, S/w, H, D] sharded by sequence -> [B, S, H/w, D] sharded by heads, one all-to-all; backward is the inverse."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return _seq_to_head(x, group)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _head_to_seq(g, ctx.group), None
+
+
+class _HeadToSeq(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return _head_to_seq(x, group)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _seq_to_head(g, ctx.group), None
+
+
+def _seq_to_head(x, group):
+    w = _world(group)[0]
+    B, Sl, H, D = x.shape
+    send = x.reshape(B, Sl, w, H // w, D).permute(2, 0, 1, 3, 4)            # [head chunk = destination, B, Sl, H/w, D]
+    recv = _a2a(send, group)                                                # [source = sequence chunk, B, Sl, H/w, D]
+    return recv.permute(1, 0, 2, 3, 4).reshape(B, w * Sl, H // w, D)
+
+
+def _head_to_seq(x, group):
+    w = _world(group)[0]
+    B, S, Hl, D = x.shape
+    send = x.reshape(B, w, S // w, Hl, D).permute(1, 0, 2, 3, 4)            # [sequence chunk = destination, B, Sl, H/w, D]
+    recv = _a2a(send, group)                                                # [source = head chunk, B, Sl, H/w, D]
+    return recv.permute(1, 2, 0, 3, 4).reshape(B, S // w, w * Hl, D)
+
+
+def ulysses_attention(q, k, v, causal: bool = True, scale: Optional[float] = None, group=None):
+    """Sequence parallelism by head exchange (DeepSpeed-Ulysses): q, k, v arrive sharded along the sequence
+    ([B, S/w, H, D], contiguous layout); one all-to-all per tensor turns them into full-sequence tensors holding H/w
+    heads, attention runs locally with no further communication, and one all-to-all returns the output to sequence
+    shards. Traffic per rank is 4 x (S/w) x H x D elements regardless of S, against the (w-1)/w x S x Hkv x D x 2 of the
+    all-gather form, so it wins when Hkv is not much smaller than H; it needs H (and Hkv, after repetition) divisible
+    by w. The reference has only the unused ``sequence_parallel`` flag (include/neural_core/architecture/distributed.h)."""
+    w = _world(group)[0]
+    if w == 1:
+        return F_.attention(q, k, v, causal=causal, scale=scale)
+    Hq, Hk = q.shape[2], k.shape[2]
+    if Hq % w:
+        raise ValueError(f"{Hq} query heads cannot be split over {w} ranks")
+    if Hk % w:                                      # grouped KV heads that do not divide: expand to one per query head
+        k, v = k.repeat_interleave(Hq // Hk, dim=2), v.repeat_interleave(Hq // Hk, dim=2)
+    qh, kh, vh = (_SeqToHead.apply(t, group) for t in (q, k, v))
+    o = F_.attention(qh, kh, vh, causal=causal, scale=scale)
+    return _HeadToSeq.apply(o, group)
