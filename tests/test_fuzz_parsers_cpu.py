@@ -139,3 +139,65 @@ def test_http_front_end_survives_malformed_requests():
         assert urllib.request.urlopen(req, timeout=10).read() == b'{"x": "ok", "n": 5}'
     finally:
         srv.stop()
+
+
+def test_gguf_and_hierarchical_store_survive_garbage(tmp_path):
+    from sneppx_alg_b200.hub.formats import HierarchicalFile
+    from sneppx_alg_b200.hub.model_card import ModelCard, load_gguf, save_gguf
+    rng = random.Random(11)
+    good = str(tmp_path / "g.gguf")
+    save_gguf(good, {"a.weight": torch.randn(4, 32), "b": torch.randn(8).half()}, {"general.name": "x", "list": [1, 2, 3]})
+    seed = open(good, "rb").read()
+    p = str(tmp_path / "m.gguf")
+
+    def gguf(d):
+        open(p, "wb").write(d)
+        for t in load_gguf(p)[0].values():
+            t.float().sum()
+    for d in _mutations(seed, rng, 400):
+        _survives(gguf, d)
+
+    hgood = str(tmp_path / "h.sxh5")
+    with HierarchicalFile(hgood, "w") as f:
+        f.write_dataset("/g/w", torch.randn(6, 5))
+        f.write_attribute("/g", "k", {"a": 1})
+    hseed = open(hgood, "rb").read()
+    hp = str(tmp_path / "m.sxh5")
+
+    def hier(d):
+        open(hp, "wb").write(d)
+        with HierarchicalFile(hp, "r") as f:
+            for path, e in list(f.index.items()):
+                if isinstance(e, dict) and e.get("kind") == "dataset":
+                    np.asarray(f.read_dataset(path)).sum()
+            f.list_children("/")
+    for d in _mutations(hseed, rng, 400):
+        _survives(hier, d)
+
+    card = ModelCard(name="n", version="1", architecture="a").to_json().encode()
+    for d in _mutations(card, rng, 300):
+        _survives(lambda b: ModelCard.from_json(b.decode("utf-8", "replace")).validate(), d)
+
+
+def test_post_quantum_verifiers_reject_garbage():
+    from sneppx_alg_b200.security import crypto
+    rng = random.Random(12)
+    pk, sk = crypto.mldsa_keygen(44, seed=bytes(32))
+    sig = crypto.mldsa_sign(sk, b"m", 44, deterministic=True)
+    for d in _mutations(sig, rng, 60):
+        assert not crypto.mldsa_verify(pk, b"m", d, 44) or d == sig
+    for _ in range(40):
+        junk = bytes(rng.randrange(256) for _ in range(len(sig)))
+        assert not crypto.mldsa_verify(pk, b"m", junk, 44)
+        assert not crypto.mldsa_verify(bytes(rng.randrange(256) for _ in range(len(pk))), b"m", sig, 44)
+    ek, dk = crypto.mlkem_keygen(512, seed=bytes(64))
+    _, n_dk, n_ct = crypto.mlkem_sizes(512)
+    for _ in range(40):
+        assert len(crypto.mlkem_decaps(dk, bytes(rng.randrange(256) for _ in range(n_ct)), 512)) == 32
+        assert len(crypto.mlkem_decaps(bytes(rng.randrange(256) for _ in range(n_dk)), bytes(n_ct), 512)) == 32
+    spk, ssk = crypto.slhdsa_keygen("128f", seed=bytes(48))
+    ssig = crypto.slhdsa_sign(ssk, b"m", deterministic=True)
+    for _ in range(5):
+        junk = bytearray(ssig)
+        junk[rng.randrange(len(junk))] ^= 1 << rng.randrange(8)
+        assert not crypto.slhdsa_verify(spk, b"m", bytes(junk))
