@@ -182,3 +182,36 @@ void sx_threadpool_destroy(void* h) {
   delete tp;
 }
 }
+
+
+// ---------------------------------------------------------------------------------------------- conv2d backward
+// The same index arithmetic as the CUDA kernels (shared header), run serially: oracle for their tests and the CPU path.
+#include "../conv2d_bwd_body.h"
+
+namespace {
+struct LoadHost { const float* p; float operator()(long long i) const { return p[i]; } };
+}
+
+extern "C" int sx_oracle_conv2d_bwd(const float* x, const float* w, const float* dy, float* dx, float* dw, float* db, int N, int C,
+                                    int H, int W, int K, int R, int S, int stride, int pad) {
+  if (N < 1 || C < 1 || H < 1 || W < 1 || K < 1 || R < 1 || S < 1 || stride < 1 || pad < 0 || H + 2 * pad < R || W + 2 * pad < S) return -1;
+  SxConvDims d{N, C, H, W, K, R, S, (H + 2 * pad - R) / stride + 1, (W + 2 * pad - S) / stride + 1, stride, pad};
+  LoadHost ldy{dy}, lw{w}, lx{x};
+  if (dx)
+    for (int n = 0; n < N; ++n) for (int c = 0; c < C; ++c) for (int h = 0; h < H; ++h) for (int ww = 0; ww < W; ++ww)
+      dx[(((long long)n * C + c) * H + h) * W + ww] = sx_conv2d_dx_at(d, ldy, lw, n, c, h, ww);
+  if (dw)
+    for (int e = 0; e < K * C * R * S; ++e) {
+      const int s = e % S, r = (e / S) % R, c = (e / (S * R)) % C, k = e / (S * R * C);
+      float acc = 0.f;                     // 256 interleaved partial sums, as the kernel's 256 threads form them
+      for (int t = 0; t < 256; ++t) acc += sx_conv2d_dw_partial(d, ldy, lx, k, c, r, s, t, 256);
+      dw[e] = acc;
+    }
+  if (db)
+    for (int k = 0; k < K; ++k) {
+      float acc = 0.f;
+      for (int t = 0; t < 256; ++t) acc += sx_conv2d_db_partial(d, ldy, k, t, 256);
+      db[k] = acc;
+    }
+  return 0;
+}

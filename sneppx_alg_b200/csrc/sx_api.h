@@ -166,6 +166,11 @@ int sx_fm_weighted_avg(const float* const* inputs, const float* weights, int cou
 int sx_arc_step(const float* x, const float* g, const float* x0, float* out, long long n, int mode, float eps, float alpha,
                 float lo, float hi, unsigned long long seed, unsigned long long offset, cudaStream_t stream);
 
+// conv2d backward: x [N,C,H,W], w [K,C,R,S], dy [N,K,OH,OW] (fp32, or bf16 with is_bf16), contiguous; fp32 gradients
+// dx / dw / db, any of which may be null to skip it.
+int sx_conv2d_bwd(const void* x, const void* w, const void* dy, float* dx, float* dw, float* db, int N, int C, int H, int W,
+                  int K, int R, int S, int stride, int pad, int is_bf16, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
