@@ -70,7 +70,7 @@ def host_sources():
 
 
 def host_headers():
-    return sorted((CSRC / "host").glob("*.h")) + sorted((CSRC / "host").glob("*.hpp")) + [CSRC / "conv2d_bwd_body.h"]
+    return sorted((CSRC / "host").glob("*.h")) + sorted((CSRC / "host").glob("*.hpp")) + [CSRC / "conv2d_bwd_body.h", CSRC / "npe_body.h"]
 
 
 def _run(cmd):

@@ -313,6 +313,56 @@ class VM:
         return result if result is not None else last
 
 
+    # ---- single-launch interpreter (csrc/npe_interp.cu; the host library runs the same instruction code on CPU)
+    def _encoded(self):
+        import numpy as np
+        rows = [[int(i.opcode), i.dest, i.a, i.b, i.immediate, i.shape_a[0], i.shape_a[1], i.shape_b[0]] for i in self.program.instructions]
+        return np.ascontiguousarray(np.array(rows, dtype=np.int32).reshape(len(rows), 8))
+
+    def plan_rows(self, in_width: int):
+        """(code, widest register, output width) from the interpreter's planner; code 0 means the program can run
+        there, -3 that it uses an instruction the interpreter leaves to ``run`` (ATTENTION, BRANCH, ...)."""
+        import ctypes as C
+        from .. import _build
+        L = _build.load_host()
+        prog = self._encoded()
+        maxw, out_w = C.c_int(0), C.c_int(0)
+        rc = L.sx_oracle_npe_plan(C.c_void_p(prog.ctypes.data), C.c_int(len(prog)), C.c_longlong(self.program.memory.numel()),
+                                  C.c_int(in_width), C.byref(maxw), C.byref(out_w))
+        return rc, maxw.value, out_w.value
+
+    def run_rows(self, x: torch.Tensor) -> torch.Tensor:
+        """The whole program in one call per batch: every row of x [..., width] goes through the interpreter with its
+        registers on chip. Inference only (no autograd). Raises NotImplementedError for programs the planner refuses
+        with -3 and ValueError for malformed ones."""
+        import ctypes as C
+        from .. import _build
+        from ..ops import _lib
+        width = x.shape[-1]
+        rc, _, out_w = self.plan_rows(width)
+        if rc == -3:
+            raise NotImplementedError("program uses instructions outside the row interpreter")
+        if rc != 0:
+            raise ValueError(f"program does not pass the interpreter's planner (code {rc})")
+        prog = self._encoded()
+        xf = x.detach().reshape(-1, width).float().contiguous()
+        mem = self.program.memory.detach().float().contiguous()
+        out = torch.empty(xf.shape[0], out_w, dtype=torch.float32, device=x.device)
+        if x.is_cuda:
+            dev_prog = torch.from_numpy(prog).to(x.device)
+            _lib.call("sx_npe_run", C.c_void_p(prog.ctypes.data), _lib.ptr(dev_prog), C.c_int(len(prog)), _lib.ptr(mem),
+                      C.c_longlong(mem.numel()), _lib.ptr(xf), C.c_longlong(xf.shape[0]), C.c_int(width), _lib.ptr(out),
+                      C.c_int(out_w), _lib.stream())
+        else:
+            L = _build.load_host()
+            rc = L.sx_oracle_npe_run(C.c_void_p(prog.ctypes.data), C.c_int(len(prog)), C.c_void_p(mem.data_ptr()), C.c_longlong(mem.numel()),
+                                     C.c_void_p(xf.data_ptr()), C.c_longlong(xf.shape[0]), C.c_int(width), C.c_void_p(out.data_ptr()),
+                                     C.c_int(out_w))
+            if rc != 0:
+                raise RuntimeError(f"interpreter failed with code {rc}")
+        return out.reshape(*x.shape[:-1], out_w).to(x.dtype)
+
+
 class NPELayer(Module):
     """A compiled program as an ``nn`` module: parameters are the program memory; the fused program is built once."""
 

@@ -215,3 +215,37 @@ extern "C" int sx_oracle_conv2d_bwd(const float* x, const float* w, const float*
     }
   return 0;
 }
+
+
+// ---------------------------------------------------------------------------------------------- NPE interpreter
+// The instruction semantics of the interpreter kernel (shared header), one thread per row.
+#include <vector>
+#include "../npe_body.h"
+
+namespace {
+struct NpeHostCtx {
+  int tid() const { return 0; }
+  int nthreads() const { return 1; }
+  void sync() const {}
+  float sum(float v) const { return v; }
+  float max(float v) const { return v; }
+};
+}
+
+extern "C" int sx_oracle_npe_plan(const int* prog8, int n, long long mem_size, int in_w, int* maxw, int* out_w) {
+  if (n < 0 || n > 4096 || in_w < 1) return -1;
+  return sx_npe_plan((const SxNpeIns*)prog8, n, mem_size, in_w, maxw, out_w);
+}
+
+extern "C" int sx_oracle_npe_run(const int* prog8, int n, const float* mem, long long mem_size, const float* x, long long rows, int in_w,
+                                 float* out, int out_w_expected) {
+  int maxw = 0, out_w = 0;
+  const int rc = sx_oracle_npe_plan(prog8, n, mem_size, in_w, &maxw, &out_w);
+  if (rc != 0) return rc;
+  if (out_w != out_w_expected || rows < 1) return -2;
+  std::vector<float> slots((size_t)(SX_NPE_REGS + 1) * maxw);
+  NpeHostCtx ctx;
+  for (long long r = 0; r < rows; ++r)
+    sx_npe_exec_row((const SxNpeIns*)prog8, n, mem, x + r * in_w, in_w, out + r * out_w, slots.data(), maxw, ctx);
+  return 0;
+}

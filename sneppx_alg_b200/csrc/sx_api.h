@@ -171,6 +171,12 @@ int sx_arc_step(const float* x, const float* g, const float* x0, float* out, lon
 int sx_conv2d_bwd(const void* x, const void* w, const void* dy, float* dx, float* dw, float* db, int N, int C, int H, int W,
                   int K, int R, int S, int stride, int pad, int is_bf16, cudaStream_t stream);
 
+// NPE bytecode interpreter: instruction table [n, 8] int32 (op, dest, a, b, immediate, rows, cols, bias register);
+// program memory and x / out fp32. The planner returns 0, -1 malformed, -2 shapes do not fit, -3 unsupported opcode.
+int sx_npe_plan_program(const int* prog8, int n, long long mem_size, int in_w, int* maxw, int* out_w);
+int sx_npe_run(const int* prog_host, const int* prog_dev, int n, const float* mem, long long mem_size, const float* x, long long rows,
+               int in_w, float* out, int out_w_expected, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
