@@ -4,7 +4,7 @@ time whole NumPy ops; here every case is one native sm_100a kernel).
 ``python -m sneppx_alg_b200.benchmarks.kernels <case> [--small] [--iters N] [--out file.json]``
 
 Cases: gemm, gemm_wgrad, attn_fwd, attn_bwd, rmsnorm, glu, rope, ce, adamw, sumsq, paged_decode, gemm_dq_fp8,
-gemm_dq_int4, gemm_fp8, gemm_fp8_prefill, conv1d, conv1d_bwd, ssd_fwd, ssd_bwd, router, quant_fp8, dropout, rng_normal, layernorm_bwd, block_top2, all.  ``--small`` picks a problem that still exceeds L2 but holds well
+gemm_dq_int4, gemm_fp8, gemm_fp8_prefill, conv1d, conv1d_bwd, ssd_fwd, ssd_bwd, router, quant_fp8, dropout, rng_normal, layernorm_bwd, block_top2, conv2d_bwd, npe_interp, all.  ``--small`` picks a problem that still exceeds L2 but holds well
 under 2 GB so that one launch can be captured by a profiler in seconds.  Timing: CUDA events on the launching
 stream after 3 warm-up launches; inputs are larger than L2 or rotated between iterations.  Fractions are against the
 measured copy bandwidth / cuBLAS bf16 throughput in ``MEASURED_PEAKS.json`` when that file is present at the
@@ -311,6 +311,30 @@ def case_block_top2(small, iters):
     x = torch.randn(n, device="cuda")
     ms = _time(lambda: aux.block_top2(x), iters)
     return dict(shape=[n], ms=ms, bytes=4 * n * 3, note="reads x, writes kept and residual")
+
+
+def case_conv2d_bwd(small, iters):
+    from ..ops import conv
+    N, C, H, K = (32, 64, 56, 64) if small else (128, 64, 56, 64)
+    x, w, dy = _bf(N, C, H, H), _bf(K, C, 3, 3), _bf(N, K, H, H)
+    ms = _time(lambda: conv.conv2d_backward(x, w, dy, 1, 1), iters)
+    return dict(shape=[N, C, H, H, K, 3, 3], ms=ms, bytes=2 * (x.numel() + dy.numel()) + 4 * x.numel(), flops=2 * 2 * N * K * C * 9 * H * H,
+                note="direct SIMT kernels (dx, dw, db); flops = dgrad + wgrad, fraction is against the tensor-core peak they do not use")
+
+
+def case_npe_interp(small, iters):
+    from ..algorithms import npe
+    dim, hidden, rows = 256, 1024, (1 << 16) if small else (1 << 18)
+    prog = npe.compile_mlp(dim, hidden, device="cuda")
+    with torch.no_grad():
+        prog.memory.normal_(0, dim ** -0.5)
+    vm = npe.VM(npe.NPEConfig())
+    vm.load(prog)
+    vm.optimize()
+    x = torch.randn(rows, dim, device="cuda")
+    ms = _time(lambda: vm.run_rows(x), iters)
+    return dict(shape=[rows, dim, hidden], ms=ms, bytes=4 * rows * dim * 2, flops=2 * 2 * rows * dim * hidden,
+                note="whole MLP program in one launch, registers in shared memory, weights re-read from L2 per row")
 
 
 CASES = {k[5:]: v for k, v in list(globals().items()) if k.startswith("case_")}
