@@ -497,23 +497,52 @@ class SecureStreamConnection:
     listener / dial / stream_open / stream_send / stream_recv; its body opens no socket).
 
     Not the QUIC wire protocol: the carrier is one framed TCP connection. What it keeps of QUIC's shape is what callers
-    use: a key agreement when the connection opens (ephemeral X25519, HKDF-SHA256, one key per direction), every frame
+    use: a key agreement when the connection opens (ephemeral X25519, optionally combined with ML-KEM-768 so that the
+    session keys also resist an attacker with a quantum computer; HKDF-SHA256, one key per direction), every frame
     sealed with ChaCha20-Poly1305 under a per-direction counter nonce (replayed, reordered or altered frames fail
     authentication), and any number of streams multiplexed on the connection so that a large transfer on one stream
     does not have to finish before a message on another is read."""
 
-    def __init__(self, sock: FramedSocket, initiator: bool, psk: bytes = b""):
+    def __init__(self, sock: FramedSocket, initiator: bool, psk: bytes = b"", post_quantum: bool = False):
+        try:
+            self._handshake(sock, initiator, psk, post_quantum)
+        except Exception:
+            sock.close()                      # the peer must not be left waiting for the rest of a failed handshake
+            raise
+
+    def _handshake(self, sock, initiator, psk, post_quantum):
         import os
         from collections import defaultdict, deque
         from ..security import crypto
         self._crypto, self.sock = crypto, sock
         secret = os.urandom(32)
         mine = crypto.x25519(secret)
-        sock.send_message(mine)
-        theirs = sock.recv_message(64)
-        if len(theirs) != 32:
-            raise ConnectionError("bad handshake")
-        shared = crypto.x25519(secret, theirs)
+        kem_secret = b""
+        if post_quantum and initiator:
+            # hybrid key agreement: the initiator adds an ML-KEM-768 encapsulation key, the acceptor answers with a
+            # ciphertext; the session keys depend on both the X25519 and the ML-KEM secrets
+            ek, dk = crypto.mlkem_keygen(768)
+            sock.send_message(mine + ek)
+            reply = sock.recv_message(4096)
+            if len(reply) != 32 + crypto.mlkem_sizes(768)[2]:
+                raise ConnectionError("bad handshake")
+            theirs, kem_secret = reply[:32], crypto.mlkem_decaps(dk, reply[32:], 768)
+        elif post_quantum:
+            hello = sock.recv_message(4096)
+            if len(hello) != 32 + crypto.mlkem_sizes(768)[0]:
+                raise ConnectionError("bad handshake")
+            theirs = hello[:32]
+            try:
+                kem_secret, ct = crypto.mlkem_encaps(hello[32:], 768)
+            except ValueError as e:
+                raise ConnectionError("bad handshake") from e
+            sock.send_message(mine + ct)
+        else:
+            sock.send_message(mine)
+            theirs = sock.recv_message(64)
+            if len(theirs) != 32:
+                raise ConnectionError("bad handshake")
+        shared = crypto.x25519(secret, theirs) + kem_secret
         first, second = (mine, theirs) if initiator else (theirs, mine)
         okm = crypto.hkdf_sha256(shared + psk, salt=first + second, info=b"sneppx-stream", length=64)
         self._send_key, self._recv_key = (okm[:32], okm[32:]) if initiator else (okm[32:], okm[:32])
@@ -528,12 +557,16 @@ class SecureStreamConnection:
             raise ConnectionError("key confirmation failed")
 
     @classmethod
-    def dial(cls, host: str, port: int, timeout_ms: int = 5000, psk: bytes = b""):
-        return cls(FramedSocket.connect(host, port, timeout_ms), True, psk)
+    def dial(cls, host: str, port: int, timeout_ms: int = 5000, psk: bytes = b"", post_quantum: bool = False):
+        sock = FramedSocket.connect(host, port, timeout_ms)
+        sock.set_timeout(timeout_ms)
+        return cls(sock, True, psk, post_quantum)
 
     @classmethod
-    def accept(cls, listen_fd: int, timeout_ms: int = 5000, psk: bytes = b""):
-        return cls(FramedSocket.accept(listen_fd, timeout_ms), False, psk)
+    def accept(cls, listen_fd: int, timeout_ms: int = 5000, psk: bytes = b"", post_quantum: bool = False):
+        sock = FramedSocket.accept(listen_fd, timeout_ms)
+        sock.set_timeout(timeout_ms)
+        return cls(sock, False, psk, post_quantum)
 
     def _send_frame(self, stream_id: int, kind: int, body: bytes):
         nonce = self._send_ctr.to_bytes(12, "little")

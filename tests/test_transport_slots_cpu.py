@@ -124,3 +124,41 @@ def test_secure_multiplexed_streams():
     t.join(30)
     assert res["ok"] is False
     close_listener(lfd)
+
+
+def test_hybrid_post_quantum_handshake():
+    import threading
+    from sneppx_alg_b200.utils.net import FramedSocket, SecureStreamConnection, close_listener
+    lfd, port = FramedSocket.listen(0)
+    out = {}
+
+    def server():
+        c = SecureStreamConnection.accept(lfd, post_quantum=True)
+        out["msg"] = c.stream_recv(0)
+        c.stream_send(c.stream_open(), b"pong")
+        out["c"] = c
+    t = threading.Thread(target=server)
+    t.start()
+    c = SecureStreamConnection.dial("127.0.0.1", port, post_quantum=True)
+    c.stream_send(c.stream_open(), b"ping")
+    assert c.stream_recv(1) == b"pong"
+    t.join(30)
+    assert out["msg"] == b"ping"
+    c.close(); out["c"].close()
+
+    # a classical-only initiator does not get through to a hybrid acceptor
+    res = {}
+
+    def server2():
+        try:
+            SecureStreamConnection.accept(lfd, timeout_ms=2000, post_quantum=True)
+            res["ok"] = True
+        except ConnectionError:
+            res["ok"] = False
+    t = threading.Thread(target=server2)
+    t.start()
+    with pytest.raises(ConnectionError):
+        SecureStreamConnection.dial("127.0.0.1", port, timeout_ms=2000)
+    t.join(30)
+    assert res["ok"] is False
+    close_listener(lfd)
