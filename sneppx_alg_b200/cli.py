@@ -492,9 +492,29 @@ def tools_main(argv=None):
     de = sub.add_parser("data", help="statistics of a text file or a token file (.npy / .bin of int32)")
     de.add_argument("path")
     de.add_argument("--top", type=int, default=10)
-    cv = sub.add_parser("convert", help="convert a weight file between .safetensors / .sneppx / .pth / .npz")
+    cv = sub.add_parser("convert", help="convert a weight file between .safetensors / .sneppx / .pth / .npz / .gguf / .sxh5")
     cv.add_argument("src")
     cv.add_argument("dst")
+    cv.add_argument("--q8", action="store_true", help="store matrices as 8-bit blocks when the target is .gguf")
+    cd = sub.add_parser("card", help="write a model card (JSON, or Markdown for a .md target) for a preset or a saved model")
+    cd.add_argument("model")
+    cd.add_argument("out")
+    cd.add_argument("--name", default=None)
+    cd.add_argument("--version", default="1.0.0")
+    cd.add_argument("--license", default="")
+    kg = sub.add_parser("keygen", help="signing key pair (ed25519 or post-quantum ml-dsa-65) written as <prefix>.pub / <prefix>.key")
+    kg.add_argument("prefix")
+    kg.add_argument("--scheme", default="ml-dsa-65", choices=["ed25519", "ml-dsa-65"])
+    sg = sub.add_parser("sign", help="signed manifest for a file (update package, weight file)")
+    sg.add_argument("file")
+    sg.add_argument("key")
+    sg.add_argument("--scheme", default="ml-dsa-65", choices=["ed25519", "ml-dsa-65"])
+    sg.add_argument("--version", default="1.0.0")
+    sg.add_argument("--out", default=None)
+    vf = sub.add_parser("verify", help="check a file against its signed manifest; exit code 0 when it is authentic")
+    vf.add_argument("file")
+    vf.add_argument("manifest")
+    vf.add_argument("pub")
     be = sub.add_parser("bench", help="tensor micro-benchmarks (the reference's published list)")
     be.add_argument("--device", default="cpu")
     be.add_argument("--out", default=None)
@@ -542,10 +562,53 @@ def tools_main(argv=None):
             formats.save_pth(a.dst, sd)
         elif d.endswith(".npz"):
             formats.save_npz(a.dst, sd)
+        elif d.endswith(".gguf"):
+            from .hub.model_card import save_gguf
+            save_gguf(a.dst, sd, {"general.name": os.path.basename(a.src)}, q8_0=a.q8)
+        elif d.endswith(".sxh5"):
+            with formats.HierarchicalFile(a.dst, "w") as f:
+                f.write_state_dict(sd)
         else:
             print(f"unknown target format: {a.dst}", file=sys.stderr)
             return 2
         print(json.dumps({"tensors": len(sd), "dst": a.dst}))
+    elif a.cmd == "card":
+        from .hub.model_card import ModelCard
+        model = _model_from_spec(a.model)
+        card = ModelCard.from_model(model, a.name or os.path.basename(a.model.rstrip("/")), a.version, license=a.license,
+                                    model_type="causal-lm")
+        ok, errors = card.validate()
+        if not ok:
+            print("; ".join(errors), file=sys.stderr)
+            return 1
+        with open(a.out, "w") as f:
+            f.write(card.to_markdown() if a.out.endswith(".md") else card.to_json())
+        print(a.out)
+    elif a.cmd == "keygen":
+        from .security import crypto
+        if a.scheme == "ed25519":
+            key = os.urandom(32)
+            pub = crypto.ed25519_public_key(key)
+        else:
+            pub, key = crypto.mldsa_keygen(65)
+        with open(a.prefix + ".pub", "wb") as f:
+            f.write(pub)
+        fd = os.open(a.prefix + ".key", os.O_WRONLY | os.O_CREAT | os.O_TRUNC, 0o600)     # private key: owner only
+        with os.fdopen(fd, "wb") as f:
+            f.write(key)
+        print(json.dumps({"scheme": a.scheme, "public": a.prefix + ".pub", "private": a.prefix + ".key", "public_bytes": len(pub)}))
+    elif a.cmd == "sign":
+        from .security.services import sign_update
+        manifest = sign_update(a.file, open(a.key, "rb").read(), a.version, scheme=a.scheme)
+        out = a.out or a.file + ".manifest.json"
+        with open(out, "w") as f:
+            json.dump(manifest, f, indent=1)
+        print(out)
+    elif a.cmd == "verify":
+        from .security.services import verify_update
+        ok = verify_update(a.file, json.load(open(a.manifest)), open(a.pub, "rb").read())
+        print(json.dumps({"authentic": bool(ok)}))
+        return 0 if ok else 1
     elif a.cmd == "bench":
         from .benchmarks import tensor_ops
         return tensor_ops.main(["--device", a.device] + (["--out", a.out] if a.out else []))

@@ -96,7 +96,7 @@ def test_tools_cli(tmp_path, capsys):
     assert json.loads(capsys.readouterr().out)["distinct_words"] == 3
     sd = {"w": torch.randn(3, 4), "b": torch.zeros(4)}
     formats.save_safetensors(str(tmp_path / "m.safetensors"), sd)
-    for ext in ("sneppx", "pth", "npz"):
+    for ext in ("sneppx", "pth", "npz", "gguf", "sxh5"):
         assert tools_main(["convert", str(tmp_path / "m.safetensors"), str(tmp_path / f"m.{ext}")]) == 0
         assert torch.equal(formats.load_any(str(tmp_path / f"m.{ext}"))["w"], sd["w"])
     assert tools_main(["convert", str(tmp_path / "m.safetensors"), str(tmp_path / "m.xyz")]) == 2
@@ -104,3 +104,29 @@ def test_tools_cli(tmp_path, capsys):
     assert tools_main(["audit", str(tmp_path / "serve.json")]) == 0
     (tmp_path / "bad.json").write_text(json.dumps({"bind": "0.0.0.0"}))
     assert tools_main(["audit", str(tmp_path / "bad.json")]) == 1
+
+
+def test_tools_card_keygen_sign_verify(tmp_path, capsys):
+    import stat
+    from sneppx_alg_b200.cli import tools_main
+    from sneppx_alg_b200.hub.model_card import ModelCard
+    assert tools_main(["card", "llama3-tiny", str(tmp_path / "card.json"), "--license", "apache-2.0"]) == 0
+    card = ModelCard.load(str(tmp_path / "card.json"))
+    assert card.name == "llama3-tiny" and card.num_parameters > 0 and card.license == "apache-2.0"
+    assert tools_main(["card", "llama3-tiny", str(tmp_path / "card.md")]) == 0
+    assert open(tmp_path / "card.md").read().startswith("# llama3-tiny 1.0.0")
+    pkg = tmp_path / "update.bin"
+    pkg.write_bytes(os.urandom(2048))
+    for scheme in ("ml-dsa-65", "ed25519"):
+        prefix = str(tmp_path / scheme)
+        assert tools_main(["keygen", prefix, "--scheme", scheme]) == 0
+        assert stat.S_IMODE(os.stat(prefix + ".key").st_mode) == 0o600
+        assert tools_main(["sign", str(pkg), prefix + ".key", "--scheme", scheme, "--version", "2.1.0"]) == 0
+        manifest = str(pkg) + ".manifest.json"
+        assert json.load(open(manifest))["scheme"] == scheme
+        assert tools_main(["verify", str(pkg), manifest, prefix + ".pub"]) == 0
+        other = str(tmp_path / (scheme + "-other"))
+        tools_main(["keygen", other, "--scheme", scheme])
+        assert tools_main(["verify", str(pkg), manifest, other + ".pub"]) == 1
+    pkg.write_bytes(b"changed")
+    assert tools_main(["verify", str(pkg), str(pkg) + ".manifest.json", str(tmp_path / "ed25519.pub")]) == 1
