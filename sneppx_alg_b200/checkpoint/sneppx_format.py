@@ -198,3 +198,61 @@ class AsyncSaver:
         if self._h:
             _lib().sx_ckpt_saver_destroy(self._h)
             self._h = None
+
+
+# ---- the C trainer's raw checkpoint (kernel/train/trainer.c:269-353): u32 magic 0x41524958, u32 version 2, u64 step,
+# u64 tensor count, then per tensor u32 ndim, u64 shape[ndim], u64 element count, fp32 data. Unnamed, in parameter order.
+RAW_MAGIC, RAW_VERSION = 0x41524958, 2
+
+
+def save_raw_trainer_checkpoint(path: str, step: int, tensors) -> None:
+    """`tensors`: parameters in model order (a list, or the values of a state dict); stored as fp32."""
+    import struct
+    vals = list(tensors.values()) if isinstance(tensors, dict) else list(tensors)
+    with open(path, "wb") as f:
+        f.write(struct.pack("<IIQQ", RAW_MAGIC, RAW_VERSION, int(step), len(vals)))
+        for t in vals:
+            t = t.detach().float().cpu().contiguous()
+            if t.dim() > 8:
+                raise ValueError("the raw trainer format holds at most 8 dimensions")
+            f.write(struct.pack("<I", t.dim()) + struct.pack(f"<{t.dim()}Q", *t.shape) + struct.pack("<Q", t.numel()))
+            f.write(t.numpy().tobytes())
+
+
+def load_raw_trainer_checkpoint(path: str):
+    """-> (step, [fp32 tensors in file order]). Version 1 files carry the step only."""
+    import struct
+    import numpy as np
+    data = open(path, "rb").read()
+    if len(data) < 16 or struct.unpack_from("<I", data, 0)[0] != RAW_MAGIC:
+        raise ValueError("not a raw trainer checkpoint")
+    version, step = struct.unpack_from("<IQ", data, 4)
+    if version not in (1, 2):
+        raise ValueError(f"unsupported raw trainer checkpoint version {version}")
+    if version == 1:
+        return step, []
+    if len(data) < 24:
+        raise ValueError("raw trainer checkpoint truncated")
+    (count,) = struct.unpack_from("<Q", data, 16)
+    pos, out = 24, []
+    if count > len(data):
+        raise ValueError("tensor count larger than the file")
+    for _ in range(count):
+        if pos + 4 > len(data):
+            raise ValueError("raw trainer checkpoint truncated")
+        (nd,) = struct.unpack_from("<I", data, pos)
+        pos += 4
+        if nd > 8 or pos + 8 * nd + 8 > len(data):
+            raise ValueError("bad tensor record")
+        shape = struct.unpack_from(f"<{nd}Q", data, pos)
+        pos += 8 * nd
+        (n,) = struct.unpack_from("<Q", data, pos)
+        pos += 8
+        want = 1
+        for d in shape:
+            want *= d
+        if n != want or pos + 4 * n > len(data):
+            raise ValueError("tensor data does not match its shape or the file length")
+        out.append(torch.from_numpy(np.frombuffer(data, dtype="<f4", count=n, offset=pos).reshape(shape).copy()))
+        pos += 4 * n
+    return step, out

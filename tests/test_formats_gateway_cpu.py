@@ -101,3 +101,25 @@ def test_hierarchical_file_groups_datasets_attributes(tmp_path):
     open(path, "wb").write(b"nope")
     with pytest.raises(ValueError):
         HierarchicalFile(path, "r")
+
+
+def test_raw_trainer_checkpoint_round_trip_and_damage(tmp_path):
+    import struct
+    from sneppx_alg_b200.checkpoint.sneppx_format import load_raw_trainer_checkpoint, save_raw_trainer_checkpoint
+    p = str(tmp_path / "trainer.ckpt")
+    params = [torch.randn(4, 3), torch.randn(5).bfloat16(), torch.tensor(2.5), torch.zeros(0, 2)]
+    save_raw_trainer_checkpoint(p, 1234, params)
+    raw = open(p, "rb").read()
+    assert struct.unpack_from("<IIQQ", raw, 0) == (0x41524958, 2, 1234, 4)
+    assert struct.unpack_from("<IQQQ", raw, 24) == (2, 4, 3, 12)                 # first record: ndim, shape, element count
+    step, back = load_raw_trainer_checkpoint(p)
+    assert step == 1234 and len(back) == 4 and all(torch.equal(b, q.float()) for b, q in zip(back, params))
+    save_raw_trainer_checkpoint(p, 7, {"a": params[0]})
+    assert load_raw_trainer_checkpoint(p)[1][0].shape == (4, 3)
+    open(p, "wb").write(struct.pack("<IIQ", 0x41524958, 1, 99))
+    assert load_raw_trainer_checkpoint(p) == (99, [])
+    for bad in (raw[:10], raw[:40], b"XXXX" + raw[4:], raw[:16] + struct.pack("<Q", 1 << 50) + raw[24:],
+                raw[:24] + struct.pack("<I", 9) + raw[28:], raw[:44] + struct.pack("<Q", 13) + raw[52:]):
+        open(p, "wb").write(bad)
+        with pytest.raises(ValueError):
+            load_raw_trainer_checkpoint(p)
