@@ -156,8 +156,11 @@ class HSSModel(Module):
         self.layers = tnn.ModuleList(layers)
 
     def forward(self, x):
+        from ..utils.observability import bench_marker
+        bench_marker("HSS forward start")
         for layer in self.layers:
             x = layer(x)
+        bench_marker("HSS forward done")
         return x
 
     def num_params_per_layer(self):

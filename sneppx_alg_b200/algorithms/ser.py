@@ -131,9 +131,12 @@ class SERModel(Module):
         self.layers = tnn.ModuleList([SERLayer(cfg, dtype=dtype, device=device) for _ in range(cfg.num_layers)])
 
     def forward(self, x):
+        from ..utils.observability import bench_marker
         aux = 0.0
         for layer in self.layers:
+            bench_marker("SER layer forward start")
             x = layer(x)
+            bench_marker("SER layer forward done")
             aux = aux + layer.aux_loss
         self.aux_loss = aux
         return x

@@ -208,3 +208,26 @@ class CompositeTracker:
 
 def make_tracker(kind="local", **kw):
     return {"local": ExperimentTracker, "wandb": WandbTracker, "mlflow": MLflowTracker}.get(kind, ExperimentTracker)(**kw)
+
+
+
+def bench_marker(text: str):
+    """``[BENCH] <text>`` on stderr when the environment has ``SNEPPX_BENCH=1``: the start / done markers that the
+    reference's HSS and SER forwards print for its external bench tool (algorithms/hss/core/forward.c:143,174,
+    algorithms/ser/core/forward_layer.c:32). Silent otherwise, so that training loops pay one dictionary lookup."""
+    import os
+    import sys
+    if os.environ.get("SNEPPX_BENCH") == "1":
+        print(f"[BENCH] {text}", file=sys.stderr, flush=True)
+
+
+def parse_bench_markers(stderr_text: str):
+    """Pairs ``[BENCH] X start`` / ``[BENCH] X done`` lines of a captured stderr into [(X, count)] in first-seen order."""
+    seen, order = {}, []
+    for line in stderr_text.splitlines():
+        if line.startswith("[BENCH] ") and line.endswith(" done"):
+            name = line[8:-5]
+            if name not in seen:
+                order.append(name)
+            seen[name] = seen.get(name, 0) + 1
+    return [(n, seen[n]) for n in order]

@@ -24,3 +24,20 @@ def test_tiny_hybrid_parity_config_trains():
     r = tiny_hybrid.run("cpu", steps=2, warmup=1, batch=1, seq=128)
     assert r["params"] == 22512480 and 10.0 < r["ce_loss"][0] < 10.8   # ln(32000) = 10.37 at initialisation
     assert r["ce_loss"][-1] < r["ce_loss"][0] - 0.5
+
+
+def test_bench_markers_on_stderr(monkeypatch, capsys):
+    import torch
+    from sneppx_alg_b200.algorithms.hss import HSSModel
+    from sneppx_alg_b200.algorithms.ser import SERModel
+    from sneppx_alg_b200.utils.observability import parse_bench_markers
+    hss = HSSModel(input_dim=8, output_dim=8, state_dim=4, num_layers=1, seq_len=6)
+    ser = SERModel(input_dim=8, hidden_dim=16, output_dim=8, num_experts=4, top_k=2, num_layers=2)
+    x = torch.randn(2, 6, 8)
+    hss(x); ser(x)
+    assert "[BENCH]" not in capsys.readouterr().err                      # silent unless asked
+    monkeypatch.setenv("SNEPPX_BENCH", "1")
+    hss(x); ser(x)
+    err = capsys.readouterr().err
+    assert "[BENCH] HSS forward start\n[BENCH] HSS forward done" in err
+    assert parse_bench_markers(err) == [("HSS forward", 1), ("SER layer forward", 2)]
