@@ -346,7 +346,7 @@ class VM:
             raise ValueError(f"program does not pass the interpreter's planner (code {rc})")
         prog = self._encoded()
         xf = x.detach().reshape(-1, width).float().contiguous()
-        mem = self.program.memory.detach().float().contiguous()
+        mem = self.program.memory.detach().to(x.device).float().contiguous()     # the kernel dereferences it on x's device
         out = torch.empty(xf.shape[0], out_w, dtype=torch.float32, device=x.device)
         if x.is_cuda:
             dev_prog = torch.from_numpy(prog).to(x.device)

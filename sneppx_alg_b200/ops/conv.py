@@ -35,6 +35,8 @@ def conv2d_backward(x: torch.Tensor, w: torch.Tensor, dy: torch.Tensor, stride: 
     OH, OW = (H + 2 * padding - R) // stride + 1, (W + 2 * padding - S) // stride + 1
     if C2 != Cc or tuple(dy.shape) != (N, K, OH, OW):
         raise ValueError(f"shapes do not fit: x {tuple(x.shape)}, w {tuple(w.shape)}, dy {tuple(dy.shape)}, expected dy {(N, K, OH, OW)}")
+    if not (x.device == w.device == dy.device):
+        raise ValueError("x, w and dy must live on one device")
     if not (x.dtype == w.dtype == dy.dtype) or x.dtype not in (torch.float32, torch.bfloat16):
         raise TypeError("x, w and dy must share one dtype, fp32 or bf16")
     x, w, dy = x.contiguous(), w.contiguous(), dy.contiguous()
