@@ -504,11 +504,11 @@ def tools_main(argv=None):
     cd.add_argument("--license", default="")
     kg = sub.add_parser("keygen", help="signing key pair (ed25519 or post-quantum ml-dsa-65) written as <prefix>.pub / <prefix>.key")
     kg.add_argument("prefix")
-    kg.add_argument("--scheme", default="ml-dsa-65", choices=["ed25519", "ml-dsa-65"])
+    kg.add_argument("--scheme", default="ml-dsa-65", choices=["ed25519", "ml-dsa-65", "slh-dsa-128f"])
     sg = sub.add_parser("sign", help="signed manifest for a file (update package, weight file)")
     sg.add_argument("file")
     sg.add_argument("key")
-    sg.add_argument("--scheme", default="ml-dsa-65", choices=["ed25519", "ml-dsa-65"])
+    sg.add_argument("--scheme", default="ml-dsa-65", choices=["ed25519", "ml-dsa-65", "slh-dsa-128f"])
     sg.add_argument("--version", default="1.0.0")
     sg.add_argument("--out", default=None)
     vf = sub.add_parser("verify", help="check a file against its signed manifest; exit code 0 when it is authentic")
@@ -589,6 +589,8 @@ def tools_main(argv=None):
         if a.scheme == "ed25519":
             key = os.urandom(32)
             pub = crypto.ed25519_public_key(key)
+        elif a.scheme == "slh-dsa-128f":
+            pub, key = crypto.slhdsa_keygen("128f")
         else:
             pub, key = crypto.mldsa_keygen(65)
         with open(a.prefix + ".pub", "wb") as f:

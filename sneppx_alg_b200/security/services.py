@@ -158,7 +158,8 @@ class AuditLogger:
 def sign_update(path: str, key: bytes, version: str, scheme: str = "hmac-sha256") -> dict:
     """Manifest for an update file. ``hmac-sha256``: `key` is a shared secret. ``ed25519``: `key` is the 32-byte
     signing seed and the manifest is verified with the public key only. ``ml-dsa-65``: `key` is the ML-DSA private
-    key (post-quantum signature, FIPS 204), verified with its public key."""
+    key (post-quantum signature, FIPS 204), verified with its public key. ``slh-dsa-128f``: the hash-based
+    SLH-DSA private key (FIPS 205; 17 KB signatures, security resting on SHAKE-256 alone)."""
     data = open(path, "rb").read()
     manifest = {"file": os.path.basename(path), "version": version, "sha256": crypto.sha256(data).hex(), "size": len(data),
                 "scheme": scheme}
@@ -167,6 +168,8 @@ def sign_update(path: str, key: bytes, version: str, scheme: str = "hmac-sha256"
         manifest["signature"] = crypto.ed25519_sign(key, payload).hex()
     elif scheme == "ml-dsa-65":
         manifest["signature"] = crypto.mldsa_sign(key, payload, 65, context=b"sneppx-update").hex()
+    elif scheme == "slh-dsa-128f":
+        manifest["signature"] = crypto.slhdsa_sign(key, payload, "128f", context=b"sneppx-update").hex()
     elif scheme == "hmac-sha256":
         manifest["signature"] = crypto.hmac_sha256(key, payload).hex()
     else:
@@ -184,6 +187,9 @@ def verify_update(path: str, manifest: dict, key: bytes, min_version: str = "0")
             return False
     elif m.get("scheme") == "ml-dsa-65":
         if not crypto.mldsa_verify(key, payload, sig, 65, context=b"sneppx-update"):
+            return False
+    elif m.get("scheme") == "slh-dsa-128f":
+        if not crypto.slhdsa_verify(key, payload, sig, "128f", context=b"sneppx-update"):
             return False
     elif not crypto.ct_equal(sig, crypto.hmac_sha256(key, payload)):
         return False

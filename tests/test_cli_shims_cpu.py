@@ -117,7 +117,7 @@ def test_tools_card_keygen_sign_verify(tmp_path, capsys):
     assert open(tmp_path / "card.md").read().startswith("# llama3-tiny 1.0.0")
     pkg = tmp_path / "update.bin"
     pkg.write_bytes(os.urandom(2048))
-    for scheme in ("ml-dsa-65", "ed25519"):
+    for scheme in ("ml-dsa-65", "ed25519", "slh-dsa-128f"):
         prefix = str(tmp_path / scheme)
         assert tools_main(["keygen", prefix, "--scheme", scheme]) == 0
         assert stat.S_IMODE(os.stat(prefix + ".key").st_mode) == 0o600

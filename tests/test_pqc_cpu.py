@@ -125,8 +125,11 @@ def test_signed_update_with_post_quantum_signature(tmp_path):
     manifest = services.sign_update(str(f), sk, "1.4.0", scheme="ml-dsa-65")
     assert services.verify_update(str(f), manifest, pk, min_version="1.0")
     assert not services.verify_update(str(f), manifest, crypto.mldsa_keygen(65)[0])
+    spk, ssk = crypto.slhdsa_keygen("128f")
+    hashed = services.sign_update(str(f), ssk, "1.4.0", scheme="slh-dsa-128f")
+    assert services.verify_update(str(f), hashed, spk) and not services.verify_update(str(f), hashed, crypto.slhdsa_keygen("128f")[0])
     f.write_bytes(b"tampered")
-    assert not services.verify_update(str(f), manifest, pk)
+    assert not services.verify_update(str(f), manifest, pk) and not services.verify_update(str(f), hashed, spk)
 
 
 def test_hybrid_key_exchange_x25519_mlkem():
