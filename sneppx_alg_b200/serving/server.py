@@ -189,6 +189,16 @@ def create_app(models: Dict[str, dict], default_model: Optional[str] = None, api
         cfg = models[model_id]["model"].config
         return {"id": model_id, "config": cfg.to_dict(), "versions": control.list_models().get(model_id, {})}
 
+    @app.get("/v1/models/{model_id}/card")
+    def get_model_card(model_id: str):
+        """Model card of a served model: the one passed in its spec (``card``), else one derived from the module."""
+        if model_id not in workers:
+            raise HTTPException(404, "unknown model")
+        from dataclasses import asdict
+        from ..hub.model_card import ModelCard
+        card = models[model_id].get("card") or ModelCard.from_model(models[model_id]["model"], model_id, model_type="causal-lm")
+        return asdict(card)
+
     @app.get("/v1/models/{model_id}/versions")
     def get_versions(model_id: str):
         return control.list_models().get(model_id, {})

@@ -30,6 +30,9 @@ def test_rest_endpoints():
     assert "sneppx_requests_total" in c.get("/metrics").text
     assert c.get("/v1/models").json()["data"][0]["id"] == "tiny"
     assert c.get("/v1/models/nope").status_code == 404
+    card = c.get("/v1/models/tiny/card").json()
+    assert card["name"] == "tiny" and card["num_layers"] == 1 and card["hidden_size"] == 32 and card["num_parameters"] > 0
+    assert c.get("/v1/models/nope/card").status_code == 404
 
 
 def test_control_plane_and_filters():
