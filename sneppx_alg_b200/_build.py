@@ -179,9 +179,13 @@ def load_cuda() -> ctypes.CDLL:
             lib = LIBDIR / "libsneppx_b200.so"
             try:
                 lib = build_cuda()
-            except RuntimeError:
+            except RuntimeError as e:
                 if not lib.exists():
                     raise
+                import warnings
+                warnings.warn(f"sneppx_alg_b200: rebuilding the CUDA library FAILED ({e}); loading the existing "
+                              f"{lib.name}, which was built from OLDER sources", RuntimeWarning, stacklevel=2)
+                print(f"[sneppx_alg_b200] WARNING: stale {lib} in use, rebuild failed: {e}", file=sys.stderr, flush=True)
             _cuda_lib = ctypes.CDLL(str(lib), mode=ctypes.RTLD_GLOBAL)
         return _cuda_lib
 

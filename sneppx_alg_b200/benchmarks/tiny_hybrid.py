@@ -6,7 +6,7 @@
 
 Reports the loss trajectory (it must fall from about ln(32000) = 10.37) and the step time. The reference's pieces of
 this configuration are its C HSS and SER cores (dense-A LTI scan, biased MLP experts); their forward-only timings on
-the survey box are the closest published comparison (HSS forward seq 512, 6 layers: 186.7 ms; SER forward 128 tokens,
+an 8-vCPU Xeon (2.7 GHz, gcc -O3, one thread) are the closest published comparison (HSS forward seq 512, 6 layers: 186.7 ms; SER forward 128 tokens,
 32 experts: 21.5 ms) and there is no reference training step for this model.
 """
 from __future__ import annotations

@@ -34,23 +34,38 @@ def _flatten_state(prefix, obj, tensors, meta):
     return {"__pickle__": pickle.dumps(obj).hex()}
 
 
-def _unflatten_state(node, tensors):
+class UntrustedCheckpoint(RuntimeError):
+    """The file holds a pickled Python object and the caller did not declare the file trusted."""
+
+
+def _unflatten_state(node, tensors, trusted=False):
     if isinstance(node, dict):
         if "__tensor__" in node:
             return tensors[node["__tensor__"]]
         if "__pickle__" in node:
+            if not trusted:
+                raise UntrustedCheckpoint("checkpoint holds a pickled object; load it with trusted=True only if you "
+                                          "wrote the file yourself (unpickling runs code from the file)")
             return pickle.loads(bytes.fromhex(node["__pickle__"]))
-        return {k: _unflatten_state(v, tensors) for k, v in node.items()}
+        return {k: _unflatten_state(v, tensors, trusted) for k, v in node.items()}
     if isinstance(node, list):
-        return [_unflatten_state(v, tensors) for v in node]
+        return [_unflatten_state(v, tensors, trusted) for v in node]
     return node
 
 
 class CheckpointManager:
     def __init__(self, directory: str, keep_last: int = 3, keep_best: int = 1, metric: str = "loss", mode: str = "min",
-                 save_format: str = "binary", async_save: bool = False):
+                 save_format: str = "binary", async_save: bool = False, rank: int = 0, world_size: int = 1,
+                 barrier_fn=None, trusted: bool = False):
+        """``world_size > 1`` makes the manager sharded: every rank writes its own
+        ``checkpoint_{step}_rank_{rank}`` file between two barriers, a step counts as saved only when every rank's
+        file exists and validates, and a loaded shard must carry the loading rank's number. ``trusted`` allows
+        pickled nodes (arbitrary Python objects in the state) to be loaded; leave it off for files from elsewhere."""
         self.dir, self.keep_last, self.keep_best = directory, keep_last, keep_best
         self.metric, self.mode, self.format = metric, mode, save_format
+        self.rank, self.world = rank, world_size
+        self.barrier_fn = barrier_fn or (lambda: None)
+        self.trusted = trusted or save_format != "binary"   # a pickle-format manager reads back its own pickles
         os.makedirs(directory, exist_ok=True)
         self.best: List[tuple] = []
         self.saver = AsyncSaver() if async_save and save_format == "binary" else None
@@ -58,33 +73,57 @@ class CheckpointManager:
     def _ext(self):
         return ".sneppx" if self.format == "binary" else ".ckpt"
 
+    def _suffix(self, rank=None):
+        return f"_rank_{self.rank if rank is None else rank}" if self.world > 1 else ""
+
     @staticmethod
     def _rng_state():
-        st = {"python": random.getstate(), "numpy": np.random.get_state(), "torch": torch.get_rng_state()}
+        """Generator states as plain data (ints, floats, tensors): nothing in it needs unpickling."""
+        ver, keys, gauss = random.getstate()
+        name, nkeys, pos, has_gauss, cached = np.random.get_state()
+        st = {"python": {"version": int(ver), "keys": torch.tensor(list(keys), dtype=torch.int64), "gauss": gauss},
+              "numpy": {"name": str(name), "keys": torch.from_numpy(np.asarray(nkeys, dtype=np.int64).copy()),
+                        "pos": int(pos), "has_gauss": int(has_gauss), "cached": float(cached)},
+              "torch": torch.get_rng_state()}
         if torch.cuda.is_available():
-            st["cuda"] = torch.cuda.get_rng_state_all()
+            st["cuda"] = list(torch.cuda.get_rng_state_all())
         return st
 
     @staticmethod
     def _set_rng_state(st):
-        random.setstate(st["python"])
-        np.random.set_state(st["numpy"])
-        torch.set_rng_state(st["torch"])
+        py, npst = st["python"], st["numpy"]
+        if isinstance(py, dict):
+            random.setstate((int(py["version"]), tuple(int(x) for x in py["keys"].tolist()), py["gauss"]))
+            np.random.set_state((npst["name"], npst["keys"].numpy().astype(np.uint32), int(npst["pos"]),
+                                 int(npst["has_gauss"]), float(npst["cached"])))
+        else:   # tuple forms, as returned by random.getstate() / numpy.random.get_state()
+            random.setstate(py)
+            np.random.set_state(npst)
+        torch.set_rng_state(st["torch"].cpu().to(torch.uint8))
         if "cuda" in st and torch.cuda.is_available():
-            torch.cuda.set_rng_state_all(st["cuda"])
+            try:
+                torch.cuda.set_rng_state_all([t.cpu().to(torch.uint8) for t in st["cuda"]])
+            except (RuntimeError, IndexError):   # saved on a box with a different number of GPUs
+                pass
 
     def save(self, step: int, model_state: dict, optimizer_state: Optional[dict] = None, epoch: int = 0,
              metrics: Optional[dict] = None, config: Optional[dict] = None, scaler_state: Optional[dict] = None,
              extra: Optional[dict] = None) -> str:
         state = {"step": step, "epoch": epoch, "best_metric": self.best[0][0] if self.best else None, "config": config,
                  "model_state": model_state, "optimizer_state": optimizer_state,
-                 "rng": pickle.dumps(self._rng_state()).hex(),
+                 "rng": self._rng_state(),
                  "scaler_state": scaler_state, "metrics": metrics or {}, "extra": extra}
-        path = os.path.join(self.dir, f"checkpoint_{step}{self._ext()}")
+        state["shard_rank"], state["shard_world"] = self.rank, self.world
+        path = os.path.join(self.dir, f"checkpoint_{step}{self._suffix()}{self._ext()}")
+        self.barrier_fn()
         self._write(path, state)
+        if self.world > 1:
+            if self.saver:
+                self.saver.wait()     # the closing barrier must mean "every rank's file is on disk"
+            self.barrier_fn()
         if metrics and self.metric in metrics and self.keep_best > 0:
             val = float(metrics[self.metric])
-            bpath = os.path.join(self.dir, f"best_{step}_{self.metric}={val:.6g}{self._ext()}")
+            bpath = os.path.join(self.dir, f"best_{step}_{self.metric}={val:.6g}{self._suffix()}{self._ext()}")
             self._write(bpath, state)
             self.best.append((val, bpath))
             self.best.sort(key=lambda t: t[0], reverse=self.mode == "max")
@@ -116,25 +155,44 @@ class CheckpointManager:
             self._remove(p)
 
     def list_checkpoints(self):
+        """(step, this rank's path), oldest first; sharded: only steps for which every rank's file exists."""
         out = []
         for p in glob.glob(os.path.join(self.dir, "checkpoint_*")):
+            if self.world > 1:
+                m = re.search(rf"checkpoint_(\d+)_rank_{self.rank}\.(sneppx|ckpt)$", p)
+                if m and all(os.path.exists(os.path.join(self.dir, f"checkpoint_{m.group(1)}_rank_{r}.{m.group(2)}"))
+                             for r in range(self.world)):
+                    out.append((int(m.group(1)), p))
+                continue
             m = re.search(r"checkpoint_(\d+)\.(sneppx|ckpt)$", p)
             if m:
                 out.append((int(m.group(1)), p))
         return sorted(out)
 
-    def load(self, path: str, restore_rng: bool = True) -> dict:
+    def load(self, path: str, restore_rng: bool = True, trusted: Optional[bool] = None) -> dict:
+        trusted = self.trusted if trusted is None else trusted
         if self.saver:
             self.saver.wait()
         if path.endswith(".sneppx"):
             tensors, meta = load_tensors(path)
-            state = _unflatten_state(meta["state_tree"], tensors)
+            state = _unflatten_state(meta["state_tree"], tensors, trusted)
         else:
+            if not trusted:
+                raise UntrustedCheckpoint(".ckpt files are Python pickles; pass trusted=True for files you wrote")
             with open(path, "rb") as f:
                 state = pickle.load(f)
+        if self.world > 1 or state.get("shard_world", 1) not in (None, 1):
+            if int(state.get("shard_world") or 1) != self.world:
+                raise ValueError(f"checkpoint written by {state.get('shard_world')} ranks, loading with {self.world}")
+            if int(state.get("shard_rank") or 0) != self.rank:
+                raise ValueError(f"shard of rank {state.get('shard_rank')} loaded by rank {self.rank}")
         if restore_rng and state.get("rng"):
             rng = state["rng"]
-            self._set_rng_state(pickle.loads(bytes.fromhex(rng)) if isinstance(rng, str) else rng)
+            if isinstance(rng, str):      # older files carried the generator states as a pickle
+                if not trusted:
+                    raise UntrustedCheckpoint("generator state in this file is a pickle; pass trusted=True")
+                rng = pickle.loads(bytes.fromhex(rng))
+            self._set_rng_state(rng)
         return state
 
     def load_latest(self, **kw) -> Optional[dict]:

@@ -446,13 +446,33 @@ class CodingTask(Task):
     """`predict` returns source text defining the function named in the example; it is run against the tests."""
     name = "coding"
 
+    timeout_s = 10.0
+
     def correct(self, pred, ex):
-        scope: Dict[str, Any] = {}
+        """Model-written code never runs inside this process: a child interpreter (isolated mode, no site
+        packages, empty environment, scratch working directory) loads the source, runs the tests and prints a
+        JSON verdict; a crash, a hang past ``timeout_s`` or anything but ``true`` on the last line counts as wrong."""
+        import json as _json
+        import subprocess
+        import sys
+        import tempfile
+        driver = ("import json,sys\n"
+                  "job=json.load(sys.stdin)\n"
+                  "scope={}\n"
+                  "exec(job['src'],scope)\n"
+                  "f=scope[job['entry']]\n"
+                  "print(json.dumps(all(f(*a)==w for a,w in job['tests'])))\n")
         try:
-            exec(pred, scope)   # evaluation harness for trusted benchmark files
-            return all(scope[ex["entry_point"]](*a) == want for a, want in ex["tests"])
-        except Exception:
+            job = _json.dumps({"src": str(pred), "entry": ex["entry_point"], "tests": [[list(a), w] for a, w in ex["tests"]]})
+        except (TypeError, ValueError):
             return False
+        try:
+            with tempfile.TemporaryDirectory() as tmp:
+                r = subprocess.run([sys.executable, "-I", "-S", "-c", driver], input=job, capture_output=True, text=True,
+                                   timeout=self.timeout_s, cwd=tmp, env={})
+        except (subprocess.TimeoutExpired, OSError):
+            return False
+        return r.returncode == 0 and r.stdout.strip().splitlines()[-1:] == ["true"]
 
 
 class EvalHarness:

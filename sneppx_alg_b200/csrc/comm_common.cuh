@@ -101,7 +101,9 @@ __device__ __forceinline__ bool wait_all(const PeerTable& pt, int channel, uint3
     if (!wait_flag_sys(pt.pad[pt.rank] + channel * SX_PAD_STRIDE + threadIdx.x, epoch, pt.timeout_ns, status)) s_ok = 0;
   }
   __syncthreads();
-  return s_ok != 0;
+  const bool ok = s_ok != 0;
+  __syncthreads();  // every thread has read s_ok before a following wait_all may set it again
+  return ok;
 }
 
 __device__ __forceinline__ uint4 ld_peer_v4(const void* p) {

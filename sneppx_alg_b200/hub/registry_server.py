@@ -399,6 +399,10 @@ class HubClient:
         version = version or sorted(info["versions"])[-1]
         os.makedirs(dest, exist_ok=True)
         for name, meta in info["versions"][version]["files"].items():
+            # file names come from the server: accept plain names only, never a path that could leave `dest`
+            if (not name or os.path.basename(name) != name or name.startswith(".") or "\\" in name or "\x00" in name
+                    or name in (os.curdir, os.pardir)):
+                raise RuntimeError(f"registry sent an unsafe file name: {name!r}")
             data = self._call("GET", f"/api/models/{model_id}/versions/{version}/files/{urllib.parse.quote(name)}", raw=True)
             if hashlib.sha256(data).hexdigest() != meta["sha256"]:
                 raise RuntimeError(f"checksum mismatch for {name}")

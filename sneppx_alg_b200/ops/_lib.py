@@ -104,6 +104,39 @@ def check_status(device=None, reset: bool = True) -> None:
         raise KernelTimeout(f"sneppx kernel status {code}: {STATUS_NAMES.get(code, 'unknown')}")
 
 
+class StatusPoll:
+    """Non-blocking check of the status word: ``arm(stream)`` queues a 4-byte copy of the word into pinned host
+    memory behind whatever the stream holds; ``check()`` raises KernelTimeout if an armed copy that has completed
+    shows a code. A step calls ``check()`` on entry (reads the previous step's copy, which has landed by then)
+    and ``arm()`` after its last launch, so a wait that ran out surfaces one step later without any
+    host-device synchronisation on the hot path."""
+
+    def __init__(self, device=None):
+        self.word = status_word(device)
+        self.host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self.event = None
+
+    def arm(self, stream=None):
+        st = stream if stream is not None else torch.cuda.current_stream(self.word.device)
+        with torch.cuda.stream(st):
+            self.host.copy_(self.word[0:1], non_blocking=True)
+            self.event = torch.cuda.Event()
+            self.event.record(st)
+
+    def check(self, wait: bool = False):
+        if self.event is None:
+            return
+        if wait:
+            self.event.synchronize()
+        elif not self.event.query():
+            return
+        self.event = None
+        code = int(self.host[0])
+        if code != 0:
+            self.word.zero_()
+            raise KernelTimeout(f"sneppx kernel status {code}: {STATUS_NAMES.get(code, 'unknown')}")
+
+
 def call(name: str, *args) -> None:
     global launch_count
     fn = getattr(lib(), name)

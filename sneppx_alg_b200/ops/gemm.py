@@ -108,12 +108,17 @@ def gemm(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=None, c=None, beta
     b, N, Kb, ldb, sB = prep(b, b_mn)
     assert K == Kb, f"reduction mismatch {K} vs {Kb}"
     if K % 8 != 0 or lda % 8 != 0 or ldb % 8 != 0:
-        r = gemm_reference(a, b, a_mn=a_mn, b_mn=b_mn, c=c, beta=beta, alpha=alpha, bias=bias, act=act,
-                           out_dtype=out_dtype, tile_group=tile_group, k_ranges=k_ranges)
-        if out is not None:
-            out.copy_(r)
-            return out
-        return r
+        # TMA needs 16-byte row pitches. K-major operands of a plain GEMM are zero-padded along K to the next
+        # multiple of 8 (zeros add nothing to the sum) and run on the tensor-core kernel; layouts that cannot be
+        # padded that way are refused rather than quietly sent to a library GEMM.
+        if a_mn or b_mn or tile_group is not None or k_ranges is not None or a.dim() != 2 or b.dim() != 2:
+            raise ValueError(f"gemm: K={K}, lda={lda}, ldb={ldb} must be multiples of 8 elements for this layout; "
+                             "pad the operands")
+        Kp = (K + 7) // 8 * 8
+        a = torch.nn.functional.pad(a, (0, Kp - K))
+        b = torch.nn.functional.pad(b, (0, Kp - K))
+        return gemm(a, b, c=c, beta=beta, alpha=alpha, bias=bias, act=act, out=out, out_dtype=out_dtype,
+                    sm_limit=sm_limit, force_bn=force_bn)
     batch = 1
     k_total = 0
     if k_ranges is not None:
@@ -246,4 +251,7 @@ def bmm(a, b):
         if not b3.is_contiguous():
             b3 = b3.contiguous()
         return _BmmFn.apply(a3, b3).reshape(*lead, a.shape[-2], b.shape[-1])
-    return torch.matmul(a, b)
+    if _use_kernel(a, b):
+        raise ValueError(f"bmm: inner sizes {a.shape[-1]} and {b.shape[-1]} must be multiples of 8 for the tensor-core "
+                         "kernel; pad the operands")
+    return torch.matmul(a, b)      # CPU tensors and dtypes the kernels do not cover (fp32 oracles)

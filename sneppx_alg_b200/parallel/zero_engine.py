@@ -150,6 +150,7 @@ class ZeroEngine:
             self.comm_stream = torch.cuda.Stream(device=dev)
             self.gather_events = [None] * len(self.bounds)
             self._ready_count = 0
+            self._status_poll = _lib.StatusPoll(dev)
             self._install_hooks()
             torch.cuda.synchronize()
             dist.barrier(self.group)
@@ -252,6 +253,9 @@ class ZeroEngine:
         return self._step_fused(input_ids, labels, **kw) if self.fused else self._step_library(input_ids, labels, **kw)
 
     def _step_fused(self, input_ids, labels, **kw):
+        # A bounded device wait that ran out in the previous step left stale gradients / parameters behind:
+        # stop here instead of training on them (KernelTimeout; the context stays usable).
+        self._status_poll.check()
         self.step_count += 1
         self.fp.begin_step()
         if self.efp is not None:
@@ -292,7 +296,13 @@ class ZeroEngine:
             done.record(cs)
             torch.cuda.current_stream().wait_event(done)
         self._prefetch_params()
+        self._status_poll.arm(cs)
         return loss.detach()
+
+    def check_status(self):
+        """Blocking form of the per-step check (e.g. before a checkpoint is written)."""
+        if self.fused:
+            self._status_poll.check(wait=True)
 
     def _expert_update(self, coef):
         p16 = self.efp.flat if self.efp.flat.dtype != torch.float32 else None
@@ -357,7 +367,14 @@ class ZeroEngine:
         return sd
 
     def load_state_dict(self, sd):
+        """Restore this rank's shard and rebuild everything derived from it: the bf16 parameter shard peers gather
+        from and the full bf16 parameter buffer the model runs on (gathered from all ranks), so that the first
+        step after a resume runs on the restored weights."""
         assert sd["world"] == self.world, "use checkpoint.reshard to change the world size"
+        if "rank" in sd and int(sd["rank"]) != self.rank:
+            raise ValueError(f"checkpoint shard of rank {int(sd['rank'])} given to rank {self.rank}")
+        if "bounds" in sd and [tuple(int(x) for x in b) for b in sd["bounds"]] != [tuple(b) for b in self.bounds]:
+            raise ValueError("checkpoint bucket layout differs from this engine's")
         self.step_count = int(sd["step"])
         self.master.copy_(sd["master"])
         self.m.copy_(sd["m"])
@@ -367,3 +384,25 @@ class ZeroEngine:
             self.e_m.copy_(sd["e_m"])
             self.e_v.copy_(sd["e_v"])
             self.efp.flat.copy_(self.e_master)
+        self._refresh_params_from_master()
+
+    def _refresh_params_from_master(self):
+        w = self.world
+        if self.fused:
+            self.pshard.tensor.copy_(self.master)
+            torch.cuda.synchronize()
+            dist.barrier(self.group)          # every rank's shard is in place before anyone pulls
+            self._prefetch_params()
+            self.comm_stream.synchronize()
+            torch.cuda.current_stream().wait_stream(self.comm_stream)
+            self.gather_events = [None] * len(self.bounds)
+            dist.barrier(self.group)
+            return
+        self.pshard_local.copy_(self.master)
+        for bi, (b0, b1) in enumerate(self.bounds):
+            sz = (b1 - b0) // w
+            src = self.pshard_local[self.shard_off[bi]: self.shard_off[bi] + sz].contiguous()
+            if w > 1:
+                dist.all_gather_into_tensor(self.fp.flat[b0:b1], src, group=self.group)
+            else:
+                self.fp.flat[b0:b1].copy_(src)

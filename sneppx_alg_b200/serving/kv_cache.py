@@ -5,6 +5,7 @@ storage living on the GPU in the layout the decode kernel reads ([blocks, block_
 from __future__ import annotations
 
 import hashlib
+from collections import OrderedDict
 from typing import Dict, List, Optional, Tuple
 
 import torch
@@ -17,8 +18,11 @@ class KVBlockPool:
         self.num_blocks = num_blocks
         self.free: List[int] = list(range(num_blocks - 1, -1, -1))
         self.ref = [0] * num_blocks
+        self.reclaim = None     # callable(n) -> blocks freed; set by the cache that owns prefix entries
 
     def allocate(self) -> int:
+        if not self.free and self.reclaim is not None:
+            self.reclaim(1)
         if not self.free:
             raise MemoryError("KV block pool exhausted")
         b = self.free.pop()
@@ -42,12 +46,15 @@ class KVBlockPool:
 
 
 class PrefixCache:
-    """Maps a hash of (all tokens up to the end of a full block) to the block that holds their K/V."""
+    """Maps a hash of (all tokens up to the end of a full block) to the block that holds their K/V. Entries are
+    kept in least-recently-used order; the cache never pins more than ``max_entries`` blocks (by default half of
+    the pool) and gives blocks back on demand (``evict``) when the pool runs short."""
 
-    def __init__(self, pool: KVBlockPool, block_size: int, max_entries: int = 4096):
+    def __init__(self, pool: KVBlockPool, block_size: int, max_entries: Optional[int] = None):
+        if max_entries is None:
+            max_entries = max(1, min(4096, pool.num_blocks // 2))
         self.pool, self.block_size, self.max_entries = pool, block_size, max_entries
-        self.table: Dict[bytes, int] = {}
-        self.order: List[bytes] = []
+        self.table: "OrderedDict[bytes, int]" = OrderedDict()
 
     @staticmethod
     def _hash(prev: bytes, chunk) -> bytes:
@@ -64,6 +71,7 @@ class PrefixCache:
             b = self.table.get(key)
             if b is None:
                 break
+            self.table.move_to_end(key)
             blocks.append(self.pool.share(b))
             keys.append(key)
             prev = key
@@ -73,13 +81,31 @@ class PrefixCache:
         prev = b""
         for j, i in enumerate(range(0, len(tokens) - len(tokens) % self.block_size, self.block_size)):
             key = self._hash(prev, tokens[i: i + self.block_size])
-            if key not in self.table and j < len(block_ids):
-                if len(self.order) >= self.max_entries:
-                    old = self.order.pop(0)
-                    self.pool.release(self.table.pop(old))
+            if key in self.table:
+                self.table.move_to_end(key)
+            elif j < len(block_ids):
+                if len(self.table) >= self.max_entries:
+                    _, old = self.table.popitem(last=False)
+                    self.pool.release(old)
                 self.table[key] = self.pool.share(block_ids[j])
-                self.order.append(key)
             prev = key
+
+    def evictable(self) -> int:
+        """Blocks that only the cache still holds."""
+        return sum(1 for b in self.table.values() if self.pool.ref[b] == 1)
+
+    def evict(self, n: int) -> int:
+        """Give back up to ``n`` blocks that no running sequence shares, least recently used first."""
+        freed = 0
+        for key in list(self.table):
+            if freed >= n:
+                break
+            b = self.table[key]
+            if self.pool.ref[b] == 1:
+                del self.table[key]
+                self.pool.release(b)
+                freed += 1
+        return freed
 
 
 class PagedKVCache:
@@ -93,6 +119,19 @@ class PagedKVCache:
         self.tables: Dict[int, List[int]] = {}
         self.lens: Dict[int, int] = {}
         self.prefix = PrefixCache(self.pool, block_size) if enable_prefix_cache else None
+        if self.prefix is not None:
+            self.pool.reclaim = self.prefix.evict
+
+    def available_blocks(self) -> int:
+        """Free blocks plus those the prefix cache would give back."""
+        return self.pool.num_free + (self.prefix.evictable() if self.prefix is not None else 0)
+
+    def make_room(self, n: int) -> bool:
+        """Evict prefix entries until ``n`` blocks are free; False if that is not possible."""
+        short = n - self.pool.num_free
+        if short > 0 and self.prefix is not None:
+            self.prefix.evict(short)
+        return self.pool.num_free >= n
 
     # ---- sequences
     def add_sequence(self, seq_id: int, tokens=None) -> int:

@@ -192,6 +192,12 @@ class StateCache:
         self.pool = _Slots(max_sequences)
         self._live, self._on_free = set(), on_free
 
+    def available_blocks(self):
+        return self.pool.num_free
+
+    def make_room(self, n):
+        return self.pool.num_free >= n
+
     def add_sequence(self, seq_id, prompt):
         self.pool.num_free -= 1
         self._live.add(seq_id)
@@ -269,7 +275,8 @@ class LLMEngine:
         self.finished: Dict[int, Request] = {}
         self._ids = itertools.count()
         self.generator = None
-        self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "cached_prefix_tokens": 0, "steps": 0}
+        self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "cached_prefix_tokens": 0, "steps": 0, "rejected": 0}
+        self.failed: Dict[int, str] = {}
 
     # ------------------------------------------------------------------ API
     def submit(self, prompt: List[int], params: Optional[SamplingParams] = None, priority: int = 0, on_token=None) -> int:
@@ -285,6 +292,20 @@ class LLMEngine:
     def _blocks_needed(self, req: Request) -> int:
         bs = self.cache.block_size
         return (len(req.prompt) + req.params.max_new_tokens + bs - 1) // bs
+
+    def _committed(self) -> int:
+        """Blocks the running sequences may still claim before they finish (admission keeps these in hand, so a
+        decode step never finds the pool empty)."""
+        tables = getattr(self.cache, "tables", None)
+        if tables is None:
+            return 0
+        return sum(max(0, self._blocks_needed(r) - len(tables.get(r.req_id, ()))) for r in self.running.values())
+
+    def _fail(self, req: Request, why: str):
+        req.finish_time = time.perf_counter()
+        self.failed[req.req_id] = why
+        self.finished[req.req_id] = req
+        self.stats["rejected"] += 1
 
     @staticmethod
     def _plain_greedy(req: Request) -> bool:
@@ -318,7 +339,15 @@ class LLMEngine:
         budget = self.max_prefill_tokens
         while self.waiting and len(self.running) < self.max_batch_size and budget > 0:
             req = self.waiting[0]
-            if self._blocks_needed(req) > self.cache.pool.num_free:
+            need = self._blocks_needed(req) + self._committed()
+            if need > self.cache.available_blocks() or not self.cache.make_room(need):
+                total = getattr(self.cache.pool, "num_blocks", None)
+                if not self.running and (total is None or self._blocks_needed(req) > total
+                                         or need > self.cache.available_blocks()):
+                    # nothing will ever free more room for it: fail it instead of waiting forever
+                    heapq.heappop(self.waiting)
+                    self._fail(req, "request needs more KV blocks than the pool can ever provide")
+                    continue
                 break
             heapq.heappop(self.waiting)
             cached = self.cache.add_sequence(req.req_id, req.prompt)

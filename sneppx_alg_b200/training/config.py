@@ -17,7 +17,7 @@ DEFAULTS: Dict[str, Any] = {
     "amp": {"enabled": True, "dtype": "bfloat16", "loss_scale": "dynamic"},
     "logging": {"dir": "runs", "tracker": "local", "level": "info"},
     "checkpoint": {"dir": "checkpoints", "save_every": 0, "keep_last": 3, "keep_best": 1, "resume_from": None,
-                   "format": "binary", "async": True, "metric": "loss", "mode": "min"},
+                   "format": "binary", "async": True, "metric": "loss", "mode": "min", "trusted": False},
     "distributed": {"enabled": False, "backend": "nccl", "zero_stage": 0, "tensor_parallel_size": 1,
                     "pipeline_parallel_size": 1, "expert_parallel_size": 1, "num_microbatches": 1,
                     "bucket_size_mb": 25, "overlap_comm": True, "fused_collectives": True},
@@ -52,6 +52,9 @@ class _Section:
 
     def __getitem__(self, k):
         return self._d[k]
+
+    def __setitem__(self, k, v):
+        self._d[k] = v
 
     def get(self, k, default=None):
         return self._d.get(k, default)

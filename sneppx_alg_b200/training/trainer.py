@@ -68,8 +68,16 @@ class Trainer:
         self.scheduler = get_scheduler(s.name, sched_target, base_lr=o.lr, total_steps=s.total_steps or c.training.max_steps,
                                        warmup_steps=s.warmup_steps, min_lr=s.min_lr)
         ck = c.checkpoint
+        # A ZeRO engine's state is this rank's shard: every rank then saves its own file (between barriers) and a
+        # resume only accepts a step that every rank wrote.
+        sharded = self.engine is not None and getattr(self.engine, "world", 1) > 1
         self.ckpt = CheckpointManager(ck.dir, ck.keep_last, ck.keep_best, ck.metric, ck.mode, ck.format,
-                                      async_save=bool(ck.get("async", False))) if ck.save_every or ck.resume_from else None
+                                      async_save=bool(ck.get("async", False)),
+                                      rank=self.engine.rank if sharded else 0,
+                                      world_size=self.engine.world if sharded else 1,
+                                      barrier_fn=(lambda: dist.barrier(self.engine.group)) if sharded else None,
+                                      trusted=bool(ck.get("trusted", False))) \
+            if ck.save_every or ck.resume_from else None
 
     # ------------------------------------------------------------------ steps
     def train_step(self, batch) -> float:
@@ -128,6 +136,8 @@ class Trainer:
         return sd
 
     def save_checkpoint(self, metrics=None):
+        if self.engine is not None and hasattr(self.engine, "check_status"):
+            self.engine.check_status()      # never write a checkpoint after a device wait gave up
         sd = self.state_dict()
         return self.ckpt.save(self.step_count, sd.get("model") or {}, sd.get("optimizer") or sd.get("engine"),
                               self.epoch, metrics, self.cfg.to_dict(), extra={"scheduler": sd["scheduler"]})

@@ -125,3 +125,19 @@ def test_module_level_hub_verbs_against_service(tmp_path):
     finally:
         hub.logout()
         srv.stop()
+
+
+def test_client_refuses_server_supplied_paths(tmp_path, monkeypatch):
+    """A registry that answers with a file name containing a path must not make the client write outside `dest`."""
+    import hashlib
+
+    from sneppx_alg_b200.hub.registry_server import HubClient
+    c = HubClient.__new__(HubClient)
+    evil = b"x"
+    info = {"versions": {"1": {"files": {"../escape.txt": {"sha256": hashlib.sha256(evil).hexdigest()}}}}}
+    monkeypatch.setattr(c, "model_info", lambda mid: info, raising=False)
+    monkeypatch.setattr(c, "_call", lambda *a, **k: evil, raising=False)
+    import pytest
+    with pytest.raises(RuntimeError, match="unsafe file name"):
+        c.download("m", str(tmp_path / "dl"))
+    assert not (tmp_path / "escape.txt").exists()

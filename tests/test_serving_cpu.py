@@ -95,3 +95,26 @@ def test_tensor_parallel_engine_matches_single_rank_tokens():
     r = subprocess.run([sys.executable, os.path.join(here, "mp_tp_serving_check.py"), "2", str(29820 + os.getpid() % 9)],
                        capture_output=True, text=True, timeout=600)
     assert r.returncode == 0 and "TP_SERVING_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
+
+
+def test_prefix_cache_gives_blocks_back_under_pressure():
+    """A pool mostly pinned by cached prefixes must still admit new requests (entries nobody shares are evicted,
+    least recently used first), never run dry in the middle of a generation, and fail a request that can never
+    fit instead of spinning."""
+    model = _model()
+    g = torch.Generator().manual_seed(3)
+    eng = LLMEngine(model, num_blocks=24, block_size=4, max_batch_size=4)
+    assert eng.cache.prefix.max_entries <= 12          # capped at a fraction of the pool
+    ref_prompts = [torch.randint(0, 97, (17 + i,), generator=g).tolist() for i in range(8)]
+    refs = [generate(model, torch.tensor([p]), max_new_tokens=6)[0, len(p):].tolist() for p in ref_prompts]
+    # eight different prompts of ~6 blocks each through a 24-block pool: the cache fills, then has to yield
+    outs = eng.generate(ref_prompts, SamplingParams(max_new_tokens=6))
+    assert outs == refs
+    assert not eng.failed
+    assert eng.cache.pool.num_free + len(eng.cache.prefix.table) == 24
+    # a request larger than the whole pool is rejected at once; the engine goes idle instead of looping
+    rid = eng.submit(list(range(90)) + [1] * 30, SamplingParams(max_new_tokens=8))
+    done = eng.run_until_done(max_steps=50)
+    assert rid in eng.failed and rid in done and not eng.has_work()
+    # and the engine still serves afterwards
+    assert eng.generate(ref_prompts[:1], SamplingParams(max_new_tokens=6))[0] == refs[0]

@@ -89,3 +89,64 @@ def test_partition_range_reference_rule():
     # first n % w ranks get one extra element
     assert [partition_range(10, 4, r) for r in range(4)] == [(0, 3), (3, 6), (6, 8), (8, 10)]
     assert [partition_range(8, 4, r) for r in range(4)] == [(0, 2), (2, 4), (4, 6), (6, 8)]
+
+
+def _resume_worker(rank, world, port, ckdir, q):
+    """Uninterrupted run of 4 steps against: 2 steps, save through the Trainer, new model + Trainer, resume, 2 steps."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from sneppx_alg_b200.training.config import TrainConfig
+    from sneppx_alg_b200.training.trainer import Trainer
+
+    def batch(step):     # ranks see different data, so a resume that mixed up shards would show
+        return torch.randint(0, 256, (2, 16), generator=torch.Generator().manual_seed(10 * step + rank))
+
+    def make(seed):
+        torch.manual_seed(seed)
+        cfg = TrainConfig()
+        cfg.optimizer.lr, cfg.training.max_grad_norm = 1e-2, 1.0
+        cfg.checkpoint.dir, cfg.checkpoint.save_every, cfg.checkpoint["async"] = ckdir, 1000, False
+        cfg.logging.tracker = "none"
+        cfg.distributed.zero_stage = 3
+        return Trainer(build_model(_cfg()), cfg)
+
+    whole = make(0)
+    ref = [float(whole.train_step(batch(s))) for s in range(4)]
+    first = make(0)
+    got = [float(first.train_step(batch(s))) for s in range(2)]
+    path = first.save_checkpoint({"loss": got[-1]})
+    assert f"_rank_{rank}" in os.path.basename(path)
+    second = make(123)                      # different initial weights: only a real restore can reproduce the run
+    state = second.ckpt.load_latest()
+    assert state is not None and int(state["shard_rank"]) == rank
+    second.load_checkpoint(state)
+    got += [float(second.train_step(batch(s))) for s in range(2, 4)]
+    # a shard of the other rank is refused
+    other = os.path.join(ckdir, os.path.basename(path).replace(f"_rank_{rank}", f"_rank_{1 - rank}"))
+    try:
+        second.ckpt.load(other, restore_rng=False)
+        refused = False
+    except ValueError:
+        refused = True
+    q.put((rank, ref, got, refused))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_zero_resume_restores_parameters_and_keeps_every_shard(tmp_path):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + os.getpid() % 2000 + 11
+    procs = [ctx.Process(target=_resume_worker, args=(r, 2, port, str(tmp_path), q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=180) for _ in range(2)]
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    for rank, ref, got, refused in res:
+        assert max(abs(a - b) for a, b in zip(ref, got)) < 1e-5, (rank, ref, got)
+        assert refused
+    files = sorted(os.listdir(tmp_path))
+    assert any("_rank_0" in f for f in files) and any("_rank_1" in f for f in files)

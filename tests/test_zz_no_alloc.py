@@ -1,8 +1,9 @@
 """The allocation-free gradient-norm entry point, called through its exported C symbol.
 
 Callers that cannot reserve device memory (a fixed memory plan, a capture region, a no-new-allocations
-policy) use ``sx_grad_sumsq_noalloc``; it must give what the regular entry point ``sx_grad_sumsq`` gives, on
-repeated calls, because both share one built-in scratch array per device that keeps the previous call's data.
+policy) use ``sx_grad_sumsq_noalloc``; it must give what the regular entry point ``sx_grad_sumsq`` gives (that one
+works in a buffer its caller allocates). It is checked on repeated calls because every call of the allocation-free
+entry point works in the same built-in per-device scratch array, which still holds the previous call's data.
 This file sorts last so that a run stopping at the first failure has already run everything else.
 """
 import ctypes as C
