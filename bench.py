@@ -3,7 +3,10 @@
 seq 4096, micro-batch 1 per GPU, AdamW beta 0.9/0.95 wd 0.1), synthetic token ids, random-init weights.
 
     python bench.py --gpus N --steps K --warmup W          # N > 1: launched by torch.distributed.run
-    python bench.py --impl reference ...                    # the unmodified reference, if it can run this config
+    python bench.py --impl reference ...                    # the unmodified reference, driven through its own API
+    python bench.py --impl library ...                      # PyTorch library ops + NCCL only, overlapped like FSDP
+    python bench.py --model deepseek-v2-lite --ep --micro-batch 2      # SER MoE, expert parallel + ZeRO-1
+    python bench.py --model mamba2-2.7b --seq 8192 --tp 2              # Mamba-2, tensor parallel x data parallel
 
 Rank 0 prints one JSON line. ``value`` is whole-job tokens/s from CUDA-event timing (max over ranks);
 ``e2e`` repeats the measurement through the public engine API with the per-step host->device copy of the
@@ -36,6 +39,8 @@ def parse():
     ap.add_argument("--ep", action="store_true", help="expert parallelism over all ranks (SER MoE models): experts are "
                     "sharded, the other parameters use ZeRO-1")
     ap.add_argument("--zero-stage", type=int, default=3)
+    ap.add_argument("--tp", type=int, default=1, help="tensor-parallel size (Mamba-2 models): ranks form world/tp "
+                    "data-parallel replicas of tp consecutive ranks; ignored on one GPU")
     return ap.parse_args()
 
 
@@ -86,37 +91,53 @@ class ClockSampler:
 
 
 def run_reference(args):
-    """The reference's own code path. Its CUDA/NCCL layers do not build and its Python API is NumPy on
-    CPU with no working Transformer backward, so the named config cannot run; say so and exit 0."""
+    """Runs the unmodified reference (``baseline/_ref``) through its own public API in a child process
+    (``baseline/reference_probe.py``) and reports what happened. The named config cannot run on it: its Llama class
+    raises in forward, its generic Transformer "trains" without any parameter receiving a gradient, its tensors are
+    NumPy arrays on the host whatever ``.cuda()`` says, and its collectives return their input. The line carries
+    the captured observations, not a canned text."""
     ref_dir = os.path.join(REPO, "baseline", "_ref")
-    why = None
+    probe = os.path.join(REPO, "baseline", "reference_probe.py")
+    out = {"impl": "reference"}
     if not os.path.isdir(os.path.join(ref_dir, "SneppX_ALG")):
-        why = "reference not installed under baseline/_ref (offline pip install of the reference source tree not done on this box)"
+        out["unavailable"] = ("reference not installed under baseline/_ref (offline pip install of the reference source "
+                              "tree not done on this box)")
+        print(json.dumps(out))
+        return 0
+    rank = int(os.environ.get("RANK", "0"))
+    obs, err = None, None
+    try:
+        env = {k: v for k, v in os.environ.items() if k not in ("PYTHONPATH",)}
+        r = subprocess.run([sys.executable, probe], capture_output=True, text=True, timeout=600, cwd=ref_dir, env=env)
+        lines = [ln for ln in r.stdout.strip().splitlines() if ln.startswith("{")]
+        obs = json.loads(lines[-1]) if lines else None
+        if obs is None:
+            err = (r.stderr or r.stdout).strip().splitlines()[-1:] or ["no output"]
+    except Exception as e:  # noqa: BLE001
+        err = [f"{type(e).__name__}: {e}"]
+    if obs is None:
+        out["unavailable"] = f"reference probe failed: {err[0]}"
     else:
-        sys.path.insert(0, ref_dir)
-        try:
-            import SneppX_ALG  # noqa: F401
-            why = ("reference installs but cannot run this config: its Python API is NumPy-on-CPU only (no GPU "
-                   "execution, collectives are identity stubs) and backward through its Transformer raises a "
-                   "matmul shape error; its CUDA/NCCL C layers do not compile")
-        except Exception as e:  # noqa: BLE001
-            why = f"reference import failed: {type(e).__name__}: {e}"
-    print(json.dumps({"impl": "reference", "unavailable": why}))
+        tt = obs.get("transformer_train")
+        trains = isinstance(tt, dict) and tt.get("params_changed_by_adamw_step", 0) > 0
+        out["unavailable"] = (
+            "the unmodified reference cannot run Llama-3-8B-shape bf16 ZeRO-3 training on GPUs: "
+            f"LlamaForCausalLM forward -> {obs.get('llama_forward')}; generic Transformer step "
+            f"{'updates' if trains else 'updates no'} parameters "
+            f"({tt.get('params_with_grad_after_backward') if isinstance(tt, dict) else tt} of "
+            f"{tt.get('params') if isinstance(tt, dict) else '?'} got a gradient); Tensor.cuda() keeps data in "
+            f"{obs.get('cuda_tensor', {}).get('storage_type') if isinstance(obs.get('cuda_tensor'), dict) else obs.get('cuda_tensor')}; "
+            f"all_reduce changed values: {obs.get('collectives', {}).get('all_reduce_changed_values') if isinstance(obs.get('collectives'), dict) else obs.get('collectives')}; "
+            "its CUDA / NCCL C layers do not compile")
+        out["observed"] = obs
+    if rank == 0:
+        print(json.dumps(out))
     return 0
 
 
-def run_library(args):
-    """The same step stated with PyTorch library ops only (cuBLAS through nn.functional.linear, SDPA attention,
-    F.rms_norm, F.cross_entropy, NCCL reduce-scatter / all-gather over flat buffers, torch's fused AdamW on fp32 master
-    shards): the comparator this repository can actually run on the box, since the reference cannot run the config.
-    Same model shape, dtype recipe (bf16 weights / activations / gradients, fp32 master + moments), clipping and
-    timing rules as the main arm; none of this repository's kernels are on the path."""
-    import math
-
+def _dist_setup():
     import torch
     import torch.distributed as dist
-    import torch.nn.functional as F
-
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -125,103 +146,20 @@ def run_library(args):
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
-    from sneppx_alg_b200.models import config_from_name
-    cfg = config_from_name(args.model)
-    if cfg.architecture != "transformer":
-        print(json.dumps({"impl": "library", "unavailable": "library arm covers the dense decoder config only"}))
-        return 0
-    L = args.layers or cfg.num_hidden_layers
-    d, H, Hk, D, Fd, V = cfg.hidden_size, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, \
-        cfg.intermediate_size, cfg.vocab_size
-    torch.manual_seed(1234)
-    shapes = [("emb", (V, d))]
-    for i in range(L):
-        shapes += [(f"{i}.n1", (d,)), (f"{i}.qkv", ((H + 2 * Hk) * D, d)), (f"{i}.o", (d, H * D)), (f"{i}.n2", (d,)),
-                   (f"{i}.gu", (2 * Fd, d)), (f"{i}.down", (d, Fd))]
-    shapes += [("nf", (d,)), ("head", (V, d))]
-    unit = 256 * world
-    offs, off = {}, 0
-    for n, sh in shapes:
-        offs[n] = off
-        off += (math.prod(sh) + 255) // 256 * 256
-    total = (off + unit - 1) // unit * unit
-    flat = torch.empty(total, dtype=torch.bfloat16, device=dev)
-    grad = torch.zeros(total, dtype=torch.bfloat16, device=dev)
-    P = {}
-    for n, sh in shapes:
-        v = flat[offs[n]: offs[n] + math.prod(sh)].view(sh)
-        if len(sh) == 1:
-            v.fill_(1.0)
-        else:
-            v.normal_(0.0, 0.02)
-        p = torch.nn.Parameter(v)
-        p.grad = grad[offs[n]: offs[n] + math.prod(sh)].view(sh)
-        P[n] = p
-    if world > 1:
-        dist.broadcast(flat, 0)
-    sz = total // world
-    master = flat[rank * sz: (rank + 1) * sz].float()
-    CH = 1 << 28
-    chunks = []
-    for c0 in range(0, sz, CH):
-        mp = torch.nn.Parameter(master[c0: c0 + CH])
-        chunks.append((c0, mp, torch.optim.AdamW([mp], lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, fused=True)))
-    gshard = torch.empty(sz, dtype=torch.bfloat16, device=dev) if world > 1 else None
-    S = args.seq
-    inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, D, 2, device=dev, dtype=torch.float32) / D))
-    ang = torch.outer(torch.arange(S, device=dev, dtype=torch.float32), inv)
-    cos, sin = ang.cos()[None, :, None, :], ang.sin()[None, :, None, :]
+    return world, rank, local_rank, dev
 
-    def rope(x):
-        x1, x2 = x[..., : D // 2].float(), x[..., D // 2:].float()
-        return torch.cat((x1 * cos - x2 * sin, x2 * cos + x1 * sin), -1).to(x.dtype)
 
-    def forward_loss(ids):
-        B = ids.shape[0]
-        x = F.embedding(ids, P["emb"])
-        for i in range(L):
-            h = F.rms_norm(x, (d,), P[f"{i}.n1"], cfg.rms_norm_eps)
-            qkv = F.linear(h, P[f"{i}.qkv"])
-            q = rope(qkv[..., : H * D].view(B, S, H, D)).transpose(1, 2)
-            k = rope(qkv[..., H * D:(H + Hk) * D].view(B, S, Hk, D)).transpose(1, 2)
-            v = qkv[..., (H + Hk) * D:].view(B, S, Hk, D).transpose(1, 2)
-            a = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
-            x = x + F.linear(a.transpose(1, 2).reshape(B, S, H * D), P[f"{i}.o"])
-            h = F.rms_norm(x, (d,), P[f"{i}.n2"], cfg.rms_norm_eps)
-            g, u = F.linear(h, P[f"{i}.gu"]).chunk(2, -1)
-            x = x + F.linear(F.silu(g) * u, P[f"{i}.down"])
-        x = F.rms_norm(x, (d,), P["nf"], cfg.rms_norm_eps)
-        logits = F.linear(x[:, :-1], P["head"])
-        return F.cross_entropy(logits.reshape(-1, V).float(), ids[:, 1:].reshape(-1))
-
-    def step(ids):
-        grad.zero_()
-        loss = forward_loss(ids)
-        loss.backward()
-        if world > 1:
-            dist.reduce_scatter_tensor(gshard, grad, op=dist.ReduceOp.AVG)
-            g = gshard
-        else:
-            g = grad
-        ss = torch.linalg.vector_norm(g, dtype=torch.float32).pow(2)
-        if world > 1:
-            dist.all_reduce(ss)
-        nrm = ss.sqrt()
-        coef = torch.clamp(1.0 / (nrm + 1e-6), max=1.0)
-        for c0, mp, opt in chunks:
-            mp.grad = g[c0: c0 + CH].float() * coef
-            opt.step()
-            mp.grad = None
-        flat[rank * sz: (rank + 1) * sz].copy_(master)
-        if world > 1:
-            dist.all_gather_into_tensor(flat, flat[rank * sz: (rank + 1) * sz].clone())
-        return loss.detach()
-
-    B = args.micro_batch
-    gen = torch.Generator().manual_seed(100 + rank)
+def measure(args, world, rank, local_rank, dev, step, vocab, B, S, data_seed, launches=None, check=None):
+    """Warm-up, the device-timed region (inputs resident on the device) and the end-to-end region (every step copies
+    its batch from pinned host memory and reads the loss back), each bracketed by barrier + synchronize and timed with
+    CUDA events; returns max-over-ranks milliseconds. ``step(ids) -> loss tensor``."""
+    import torch
+    import torch.distributed as dist
+    gen = torch.Generator().manual_seed(data_seed)
     n_batches = args.warmup + 2 * args.steps + 2
-    host = [torch.randint(0, V, (B, S), generator=gen, dtype=torch.int64).pin_memory() for _ in range(n_batches)]
+    host = [torch.randint(0, vocab, (B, S), generator=gen, dtype=torch.int64).pin_memory() for _ in range(n_batches)]
     devb = [h.to(dev, non_blocking=True) for h in host]
+    torch.cuda.synchronize()
 
     def sync():
         if world > 1:
@@ -232,9 +170,12 @@ def run_library(args):
     for _ in range(args.warmup):
         step(devb[it])
         it += 1
+    if check:
+        check()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    l0 = launches() if launches else 0
     sync()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -244,6 +185,7 @@ def run_library(args):
     e1.record()
     sync()
     ms = e0.elapsed_time(e1)
+    n_launch = (launches() - l0) if launches else 0
     f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     f0.record()
     last = 0.0
@@ -254,23 +196,71 @@ def run_library(args):
     sync()
     ms_e2e = f0.elapsed_time(f1)
     clocks = sampler.stop() if rank == 0 else None
-    t = torch.tensor([ms, ms_e2e], device=dev, dtype=torch.float64)
+    if check:
+        check()
+    peak = torch.cuda.max_memory_allocated(dev) / 2 ** 30
+    t = torch.tensor([ms, ms_e2e, peak], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, ms_e2e = t.tolist()
-    tokens = B * S * world * args.steps
+    ms, ms_e2e, peak = t.tolist()
+    return {"ms": ms, "ms_e2e": ms_e2e, "last": last, "clocks": clocks, "launches": n_launch, "peak_gib": peak}
+
+
+def model_label(cfg, args):
+    name = f"{cfg.name}-shape".replace("llama3-8B", "llama3-8b")
+    return name if not args.layers else f"{name}-{args.layers}L(debug, invalid)"
+
+
+def result_line(args, world, dp, res, B, S, impl, model, parallelism, launches, extra_cfg=None):
+    tokens = B * S * dp * args.steps
+    line = {
+        "metric": "train tokens/sec", "value": tokens / (res["ms"] / 1e3), "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": res["ms"] / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic token ids, random-init weights",
+        "impl": impl,
+        "config": {"model": model, "global_batch": B * dp, "seq_len": S, "parallelism": parallelism,
+                   "optimizer": "AdamW b=(0.9,0.95) wd=0.1 fp32 master+moments, clip 1.0",
+                   "l2": "per-step working set (GBs of weights and activations) far exceeds the 126 MB L2",
+                   "peak_memory_gib_per_gpu": round(res["peak_gib"], 2)},
+        "e2e": {"value": tokens / (res["ms_e2e"] / 1e3), "unit": "tokens/s", "ms_per_step": res["ms_e2e"] / args.steps,
+                "h2d_bytes_per_step": B * S * 8, "d2h_bytes_per_step": 4, "last_loss": res["last"]},
+        "gpu_launches": launches, "clocks": res["clocks"]}
+    if extra_cfg:
+        line["config"].update(extra_cfg)
+    return line
+
+
+def run_library(args):
+    """The same step stated with PyTorch library ops only (cuBLAS through F.linear / einsum, SDPA attention, F.rms_norm,
+    F.conv1d, F.cross_entropy, NCCL reduce-scatter / all-gather / all-to-all, torch's fused AdamW on fp32 master
+    shards), with the communication overlapped the way stock FSDP does it: the comparator this repository can actually
+    run on the box, since the reference cannot run the config. Same model shapes, dtype recipe, clipping and timing
+    rules as the main arm; none of this repository's kernels are on the path (``benchmarks/library_arm.py``)."""
+    import torch
+    import torch.distributed as dist
+    world, rank, local_rank, dev = _dist_setup()
+    from sneppx_alg_b200.benchmarks import library_arm
+    from sneppx_alg_b200.models import config_from_name
+    cfg = config_from_name(args.model)
+    torch.manual_seed(1234)
+    tp = args.tp if world > 1 else 1
+    model, engine, par, dp, tp_group = library_arm.build(args.model, cfg, dev, world, rank, layers=args.layers, tp=tp,
+                                                         ep=args.ep)
+    B, S = args.micro_batch, args.seq
+    dp_rank = rank // tp if tp_group is not None else rank
+    def step(ids):
+        loss = engine.step(ids)
+        if tp_group is not None:      # each tensor-parallel rank holds its token rows' share of the mean loss
+            loss = loss.clone()
+            dist.all_reduce(loss, group=tp_group)
+        return loss
+
+    res = measure(args, world, rank, local_rank, dev, step, cfg.vocab_size, B, S, 100 + dp_rank)
     if rank == 0:
-        print(json.dumps({
-            "metric": "train tokens/sec", "value": tokens / (ms / 1e3), "unit": "tokens/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic token ids, random-init weights",
-            "impl": "library (PyTorch ops: cuBLAS, SDPA, NCCL, torch fused AdamW; none of this repository's kernels)",
-            "config": {"model": "llama3-8b-shape" if not args.layers else f"llama3-8b-shape-{args.layers}L(debug, invalid)",
-                       "global_batch": B * world, "seq_len": S, "parallelism": f"zero-dp{world} (flat reduce-scatter / all-gather)",
-                       "optimizer": "AdamW b=(0.9,0.95) wd=0.1 fp32 master+moments, clip 1.0"},
-            "e2e": {"value": tokens / (ms_e2e / 1e3), "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
-                    "h2d_bytes_per_step": B * S * 8, "d2h_bytes_per_step": 4, "last_loss": last},
-            "gpu_launches": 0, "clocks": clocks}))
+        print(json.dumps(result_line(
+            args, world, dp, res, B, S,
+            "library (PyTorch ops: cuBLAS, SDPA, NCCL, torch fused AdamW; none of this repository's kernels)",
+            model_label(cfg, args), par, 0)))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -286,15 +276,7 @@ def main():
 
     import torch
     import torch.distributed as dist
-
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
+    world, rank, local_rank, dev = _dist_setup()
 
     from sneppx_alg_b200.models import config_from_name, build_model
     from sneppx_alg_b200.ops import _lib, check_status
@@ -305,99 +287,53 @@ def main():
         cfg.num_hidden_layers = cfg.num_layers = args.layers
     cfg.max_position_embeddings = max(args.seq, 8)
     torch.manual_seed(1234)
-    if args.ep and world > 1:
+    arch = getattr(cfg, "architecture", "transformer")
+    B, S, V = args.micro_batch, args.seq, cfg.vocab_size
+    dp, dp_rank, extra = world, rank, {}
+    kw = dict(lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, max_grad_norm=1.0)
+    if arch == "mamba2" and world > 1 and args.tp > 1:
+        # tensor parallel x data parallel: in_proj all-gather -> GEMM, out_proj GEMM -> reduce-scatter (fused kernels)
+        from sneppx_alg_b200.parallel.tp import TPContext
+        from sneppx_alg_b200.parallel.tp_engine import TPDPEngine, make_tp_dp_groups
+        from sneppx_alg_b200.parallel.tp_mamba import TPMamba2ForCausalLM
+        tp_group, dp_group, tp_rank, dp_rank = make_tp_dp_groups(args.tp)
+        dp = world // args.tp
+        full = build_model(cfg, dtype=torch.bfloat16, device=dev)
+        model = TPMamba2ForCausalLM(full, TPContext(group=tp_group))
+        for layer in full.layers:      # the unsharded mixers are no longer needed
+            layer.mixer = None
+        del full
+        torch.cuda.empty_cache()
+        engine = TPDPEngine(model, tp_group, dp_group, **kw)
+        parallelism = f"tp{args.tp}xdp{dp}"
+    elif args.ep and world > 1:
         from sneppx_alg_b200.models.deepseek import DeepSeekV2ForCausalLM
         model = DeepSeekV2ForCausalLM(cfg, dtype=torch.bfloat16, device=dev, ep_group=dist.group.WORLD)
-        stage = 1
+        engine = make_engine(model, zero_stage=1, **kw)
+        parallelism = f"ep{world}+zero1"
     else:
         model = build_model(cfg, dtype=torch.bfloat16, device=dev)
-        stage = args.zero_stage
-    engine = make_engine(model, zero_stage=stage, lr=3e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1,
-                         max_grad_norm=1.0)
-    B, S, V = args.micro_batch, args.seq, cfg.vocab_size
-    gen = torch.Generator().manual_seed(100 + rank)
-    n_batches = args.warmup + 2 * args.steps + 2
-    host = [torch.randint(0, V, (B, S), generator=gen, dtype=torch.int64).pin_memory() for _ in range(n_batches)]
-    dev_batches = [h.to(dev, non_blocking=True) for h in host]
-    torch.cuda.synchronize()
+        engine = make_engine(model, zero_stage=args.zero_stage, **kw)
+        parallelism = f"zero{args.zero_stage}-dp{world}"
 
-    def sync():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
+    def step(ids):
+        return engine.step(ids, ids)
 
-    it = 0
-    for _ in range(args.warmup):
-        engine.step(dev_batches[it], dev_batches[it])
-        it += 1
-    check_status()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-    # ---- device-timed region: inputs resident on the device
-    launches0 = _lib.launch_count
-    sync()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(args.steps):
-        loss = engine.step(dev_batches[it], dev_batches[it])
-        it += 1
-    e1.record()
-    sync()
-    ms = e0.elapsed_time(e1)
-    launches = _lib.launch_count - launches0
-    # ---- end-to-end region: pinned host batch -> device every step, loss read back every step
-    sync()
-    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    f0.record()
-    last = 0.0
-    for _ in range(args.steps):
-        ids = host[it].to(dev, non_blocking=True)
-        last = float(engine.step(ids, ids).item())
-        it += 1
-    f1.record()
-    sync()
-    ms_e2e = f0.elapsed_time(f1)
-    clocks = sampler.stop() if rank == 0 else None
-    check_status()
-    t = torch.tensor([ms, ms_e2e], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, ms_e2e = t.tolist()
-    tokens = B * S * world * args.steps
-    ep_note = None
+    res = measure(args, world, rank, local_rank, dev, step, V, B, S, 100 + dp_rank,
+                  launches=lambda: _lib.launch_count, check=check_status)
     if args.ep and world > 1:
-        # capacity-factor expert parallelism: report how many routed (token, expert) entries were over capacity
         from sneppx_alg_b200.parallel import expert as _ep
         d = torch.tensor([float(_ep.dropped_entries())], device=dev, dtype=torch.float64)
         dist.all_reduce(d)
         n_moe = sum(1 for m in model.modules() if hasattr(m, "ep_group") and hasattr(m, "router"))
         routed = float(B * S * world) * cfg.num_experts_per_token * max(n_moe, 1) * (args.warmup + 2 * args.steps)
-        ep_note = {"capacity_factor": float(os.environ.get("SX_EP_CAPACITY", "2.0")),
-                   "dropped_fraction_of_routed_entries": float(d.item()) / routed}
-    value = tokens / (ms / 1e3)
-    e2e = tokens / (ms_e2e / 1e3)
+        extra["expert_parallel"] = {"policy": _ep.policy_name(), "experts": _ep.expert_dtype_name(),
+                                    "dropped_fraction_of_routed_entries": float(d.item()) / routed}
     if rank == 0:
-        line = {
-            "metric": "train tokens/sec", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic token ids, random-init weights",
-            "impl": "ours",
-            "config": {"model": (f"{cfg.name}-shape" if not args.layers else f"{cfg.name}-shape-{args.layers}L(debug, invalid)")
-                       .replace("llama3-8B", "llama3-8b"),
-                       "global_batch": B * world, "seq_len": S,
-                       "parallelism": (f"ep{world}+zero1" if (args.ep and world > 1) else f"zero{stage}-dp{world}"),
-                       "optimizer": "AdamW b=(0.9,0.95) wd=0.1 fp32 master+moments",
-                       "l2": "per-step working set (>= 16 GB of weights) far exceeds the 126 MB L2"},
-            "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / args.steps,
-                    "h2d_bytes_per_step": B * S * 8, "d2h_bytes_per_step": 4, "last_loss": last},
-            "gpu_launches": launches,
-            "clocks": clocks,
-        }
-        if ep_note:
-            line["config"]["expert_parallel"] = ep_note
-        print(json.dumps(line))
+        print(json.dumps(result_line(args, world, dp, res, B, S, "ours", model_label(cfg, args), parallelism,
+                                     res["launches"], extra)))
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
     return 0
 

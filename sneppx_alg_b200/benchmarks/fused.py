@@ -4,13 +4,17 @@ Run one process per GPU, e.g.
 ``python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 -m sneppx_alg_b200.benchmarks.fused``
 
 For each path the roofline time is the slower of FLOPs / measured GEMM peak and bytes that must cross NVLink / link
-bandwidth (770 GB/s per direction per GPU measured on this pool, 900 nominal).  Times are CUDA-event times on each
-rank, maximum over ranks; rank 0 prints one JSON line per case.
+bandwidth. The link bandwidth is measured at the start of the run (``benchmarks/link.py``: every rank pulling 256 MiB
+from its neighbour with 16-byte peer loads at the same time) and printed; 900 GB/s per direction per GPU is nominal.
+Times are CUDA-event times on each rank, maximum over ranks; rank 0 prints one JSON line per case.
 
 Cases
   ag_gemm    all-gather of activation rows -> GEMM (TP column-parallel in_proj / QKV)
   gemm_rs    GEMM -> reduce-scatter of output rows (TP row-parallel o_proj / down_proj)
-  zero_ag    ZeRO-3 parameter all-gather (pull kernel) of a 1 GiB bf16 bucket
+  zero_ag    ZeRO-3 parameter all-gather of a 1 GiB bf16 bucket: pull kernel over peer loads, and (NVLS) one multimem.st
+             push per rank
+  zero_rs_adamw  ZeRO gradient reduce-scatter + AdamW in one kernel: peer loads, and (NVLS) multimem.ld_reduce
+  wgather_gemm   ZeRO-3 weight all-gather fused into the consuming GEMM (B rows pulled by the GEMM's copy CTAs)
   allreduce  small all-reduce (norms / loss / router statistics)
 """
 from __future__ import annotations
@@ -22,7 +26,7 @@ import os
 import torch
 import torch.distributed as dist
 
-NVLINK_GBS = 770.0
+NVLINK_GBS = 770.0     # replaced by the measured figure at the start of main()
 
 
 def _peaks():
@@ -72,6 +76,14 @@ def main(argv=None):
     group = dist.group.WORLD
     tf, src = _peaks()
     res = []
+    global NVLINK_GBS
+    if world > 1:
+        from .link import measure_link_gbs
+        NVLINK_GBS = measure_link_gbs(sg, group=group)
+        if rank == 0:
+            print(json.dumps({"case": "link_bandwidth", "world": world, "GBps_per_direction_per_gpu": NVLINK_GBS,
+                              "how": "256 MiB of 16-byte peer loads from the next rank, all ranks at once",
+                              "nominal": 900.0}), flush=True)
     T, d, ff = a.tokens, a.d, a.ff
     rows = T // world
     bf = dict(device="cuda", dtype=torch.bfloat16)
@@ -82,7 +94,7 @@ def main(argv=None):
         roof = max(t_compute, t_link)
         r = {"case": name, "world": world, "shape": shape, "ms": ms, "library_ms": ms_lib, "speedup_vs_library": ms_lib / ms,
              "roofline_ms": roof, f"frac_of_roofline_{src}": roof / ms, "bound": "compute" if t_compute >= t_link else "nvlink",
-             "note": note}
+             "link_GBps_used": NVLINK_GBS, "note": note}
         res.append(r)
         if rank == 0:
             print(json.dumps(r), flush=True)
@@ -114,6 +126,26 @@ def main(argv=None):
     ms = _time(lambda: sg.allgather_pull(shard, full, n * 2, grid=48), a.iters, group)
     ms_lib = _time(lambda: dist.all_gather_into_tensor(lib_out, shard.tensor, group=group), a.iters, group)
     report("zero_ag", [world * n], ms, ms_lib, 0.0, (world - 1) * n * 2, "pull kernel over peer loads")
+    full_s = sg.alloc(world * n, torch.bfloat16)
+    if full_s.multicast_ptr and world > 1:
+        ms = _time(lambda: sg.allgather_mc(shard.tensor, full_s, 0, n * 2, 7, sg.next_epoch(7), grid=32), a.iters, group)
+        report("zero_ag_nvls", [world * n], ms, ms_lib, 0.0, world * n * 2,
+               "one multimem.st push per rank; link bytes = the whole buffer arriving from the switch")
+        ok_mc = bool(torch.equal(full_s.tensor[rank * n: rank * n + 4096], shard.tensor[:4096]))
+        if not ok_mc:
+            raise RuntimeError("multicast all-gather delivered wrong data")
+
+    # ---- ZeRO-3 weight all-gather fused into the consuming GEMM: act [T/world.., d] x (gathered W [ff2, d])^T
+    if world > 1:
+        n_w = (2 * ff) // world // 256 * 256
+        w_shard = torch.randn(n_w, d, **bf) * 0.02
+        act = torch.randn(rows * world if rows * world <= 8192 else 8192, d, **bf)
+        ms = _time(lambda: tp.ag_gemm(w_shard, act, key="bench_f2", gather_b=True), a.iters, group)
+        w_full = torch.empty(world * n_w, d, **bf)
+        ms_lib = _time(lambda: (dist.all_gather_into_tensor(w_full, w_shard, group=group), torch.matmul(act, w_full.t())),
+                       a.iters, group)
+        report("wgather_gemm", [act.shape[0], world * n_w, d], ms, ms_lib, 2.0 * act.shape[0] * world * n_w * d,
+               (world - 1) * n_w * d * 2, "gate_up weight sharded by rows (ZeRO-3); library = all_gather + cuBLAS")
 
 
     # ---- ZeRO reduce-scatter + AdamW in one kernel: every rank holds a full bf16 gradient bucket
@@ -131,7 +163,7 @@ def main(argv=None):
         partials = torch.zeros(4096, device="cuda")
         state = {"e": 0}
 
-        def fused_rs_adamw():
+        def fused_rs_adamw(nvls=False):
             state["e"] += 1
             sg.signal(2, state["e"])
             za = SxZeroArgs()
@@ -142,7 +174,8 @@ def main(argv=None):
             za.lr, za.beta1, za.beta2, za.eps, za.wd, za.step, za.max_norm = 1e-4, 0.9, 0.95, 1e-8, 0.1, 5, 0.0
             za.ready_channel, za.ready_epoch = 2, state["e"]
             za.done_channel, za.done_epoch = 3, state["e"]
-            za.mode, za.grid = 3, _lib.lib().sx_zero_grid_default()
+            za.mode, za.grid = 3, (64 if nvls else _lib.lib().sx_zero_grid_default())
+            za.mc_buf = gbuf.multicast_ptr if nvls else None
             za.status = _lib.status_word(sg.device).data_ptr()
             _lib.call("sx_zero_step", C.byref(za), _lib.stream())
 
@@ -161,6 +194,11 @@ def main(argv=None):
         # bytes: every rank reads (world-1) remote shards of bf16 grads; HBM side 28 B per owned parameter
         report("zero_rs_adamw", [nb], ms, ms_lib, 0.0, (world - 1) * sz * 2,
                "peer loads of the other ranks' slices, reduce, AdamW, bf16 shadow write in one pass")
+        if gbuf.multicast_ptr:
+            ms = _time(lambda: fused_rs_adamw(True), a.iters, group)
+            report("zero_rs_adamw_nvls", [nb], ms, ms_lib, 0.0, nb * 2,
+                   "multimem.ld_reduce (sum in the switch), AdamW, bf16 shadow write; link bytes = the whole bucket "
+                   "leaving every GPU towards the switch")
 
     # ---- expert-parallel SER layer (DeepSeek-V2-Lite shape: d 2048, 64 experts of d_ff 1408, top-6, 2 shared)
     if world > 1 and 64 % world == 0:
@@ -175,11 +213,9 @@ def main(argv=None):
                 dist.broadcast(prm, 0)
         xm = torch.randn(Tm, dm, **bf)
         gm = torch.randn(Tm, dm, **bf)
-        orig = ep.ep_experts_forward
 
         def run(fused):
-            ep.ep_experts_forward = lambda *aa, _f=fused: orig(*aa, fused=_f)
-            import sneppx_alg_b200.nn.moe  # noqa: F401  (the layer resolves the function at call time)
+            ep.FORCE_FUSED = fused
             xx = xm.detach().requires_grad_(True)
             y = layer(xx)
             y.backward(gm)
@@ -188,7 +224,7 @@ def main(argv=None):
 
         ms = _time(lambda: run(True), a.iters, group)
         ms_lib = _time(lambda: run(False), a.iters, group)
-        ep.ep_experts_forward = orig
+        ep.FORCE_FUSED = None
         flops = 3 * 2.0 * Tm * k * 3 * dm * dff + 3 * 2.0 * Tm * 2 * 3 * dm * dff      # routed + shared experts, fwd + bwd
         link = 2 * 2 * Tm * k * dm * 2 * (world - 1) / world                              # dispatch + combine, fwd + bwd
         report("ep_moe_fwd_bwd", [Tm, dm, dff, E, k], ms, ms_lib, flops, link,

@@ -54,6 +54,7 @@ struct ZeroParams {
   uint32_t done_epoch;
   int mode;
   int* status;
+  const __nv_bfloat16* mc;   // NVLS multicast view of the gradient buffer (nullptr: peer loads)
 };
 
 __device__ __forceinline__ void adamw1(float& p, float& m, float& v, float g, const ZeroParams& z) {
@@ -63,10 +64,16 @@ __device__ __forceinline__ void adamw1(float& p, float& m, float& v, float g, co
   p -= z.lr * (m / z.bc1) / (sqrtf(v / z.bc2) + z.eps);
 }
 
-// Sum of the same 8 bf16 gradients over all ranks, in rank order.
+// Sum of the same 8 bf16 gradients over all ranks: one in-switch reduction (NVLS) when the buffer has a multicast
+// mapping, else `world` peer loads summed in rank order.
 __device__ __forceinline__ void reduce8(const ZeroParams& z, long long elem, float (&acc)[8]) {
 #pragma unroll
   for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+  if (z.mc) {
+    const uint4 v = multimem_ld_reduce_bf16x8(z.mc + elem);
+    acc_bf16x8(acc, v);
+    return;
+  }
   uint4 v[SX_MAX_RANKS];
 #pragma unroll
   for (int r = 0; r < SX_MAX_RANKS; ++r)
@@ -222,6 +229,70 @@ __global__ void __launch_bounds__(512) allgather_pull_kernel(PeerTable pt, uint8
   }
 }
 
+// NVLS all-gather: my shard -> multicast address of my slot in every rank's full buffer.
+__global__ void __launch_bounds__(512) allgather_mc_kernel(PeerTable pt, const uint8_t* __restrict__ src, uint8_t* mc_dst,
+                                                          long long shard_bytes, int channel, uint32_t epoch,
+                                                          int* status) {
+  const long long nvec = shard_bytes >> 4;
+  constexpr int U = 4;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; i0 < nvec; i0 += stride * U) {
+    uint4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < nvec) v[u] = *reinterpret_cast<const uint4*>(src + (i << 4));
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < nvec) multimem_st_v4(mc_dst + (i << 4), v[u]);
+    }
+  }
+  __shared__ int s_last;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    uint32_t* counter = pt.pad[pt.rank] + (SX_PAD_CHANNELS - 1) * SX_PAD_STRIDE + 1;  // local CTA counter
+    const uint32_t prev = atomicAdd(counter, 1u);
+    s_last = (prev + 1 == gridDim.x);
+    if (s_last) *counter = 0;
+  }
+  __syncthreads();
+  if (s_last) {
+    signal_all(pt, channel, epoch);
+    wait_all(pt, channel, epoch, status);
+  }
+}
+
+// Link probes (benchmarks only): every thread moves 16 bytes per step.
+__global__ void __launch_bounds__(512) link_probe_kernel(PeerTable pt, int kind, int peer, const uint8_t* mc,
+                                                        uint8_t* local, long long bytes) {
+  const long long nvec = bytes >> 4;
+  constexpr int U = 4;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  uint8_t* remote = reinterpret_cast<uint8_t*>(pt.buf[peer]);
+  for (long long i0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; i0 < nvec; i0 += stride * U) {
+    uint4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i >= nvec) continue;
+      if (kind == 0) v[u] = ld_peer_v4(remote + (i << 4));
+      else if (kind == 2) v[u] = multimem_ld_reduce_bf16x8(mc + (i << 4));
+      else v[u] = *reinterpret_cast<const uint4*>(local + (i << 4));
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i >= nvec) continue;
+      if (kind == 0 || kind == 2) *reinterpret_cast<uint4*>(local + (i << 4)) = v[u];
+      else if (kind == 1) st_peer_v4(remote + (i << 4), v[u]);
+      else multimem_st_v4(const_cast<uint8_t*>(mc) + (i << 4), v[u]);
+    }
+  }
+}
+
 // In-place sum over ranks of n fp32 values held at the start of each rank's buffer: every rank reads all peers'
 // inputs (after a barrier), then writes its own result after a second barrier.
 __global__ void __launch_bounds__(1024) allreduce_small_kernel(PeerTable pt, int n, int channel, uint32_t epoch,
@@ -269,6 +340,7 @@ extern "C" int sx_zero_step(const SxZeroArgs* a, cudaStream_t st) {
   z.norm_channel = a->norm_channel; z.norm_epoch = a->norm_epoch;
   z.done_channel = a->done_channel; z.done_epoch = a->done_epoch;
   z.mode = a->mode; z.status = a->status;
+  z.mc = reinterpret_cast<const __nv_bfloat16*>(a->mc_buf);
   const int grid = a->grid > 0 ? a->grid : sx_zero_grid_default();
   zero_step_kernel<<<grid, 256, 0, st>>>(z);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
@@ -279,6 +351,23 @@ extern "C" int sx_allgather_pull(const SxPeers* peers, void* dst, long long shar
   if ((shard_bytes % 16) || (src_off % 16)) return -1;
   allgather_pull_kernel<<<grid > 0 ? grid : 64, 512, 0, st>>>(to_table(peers), (uint8_t*)dst, shard_bytes, src_off,
                                                              channel, epoch, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+extern "C" int sx_allgather_mc(const SxPeers* peers, const void* src_shard, void* mc_dst, long long shard_bytes,
+                               int channel, unsigned epoch, int grid, int* status, cudaStream_t st) {
+  if ((shard_bytes % 16) || !mc_dst || ((uintptr_t)mc_dst % 16) || ((uintptr_t)src_shard % 16)) return -1;
+  allgather_mc_kernel<<<grid > 0 ? grid : 32, 512, 0, st>>>(to_table(peers), (const uint8_t*)src_shard, (uint8_t*)mc_dst,
+                                                           shard_bytes, channel, epoch, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
+
+extern "C" int sx_link_probe(const SxPeers* peers, int kind, int peer, const void* mc, void* local, long long bytes,
+                             int grid, cudaStream_t st) {
+  if ((bytes % 16) || kind < 0 || kind > 3 || peer < 0 || peer >= peers->world) return -1;
+  if ((kind == 2 || kind == 3) && !mc) return -2;
+  link_probe_kernel<<<grid > 0 ? grid : 64, 512, 0, st>>>(to_table(peers), kind, peer, (const uint8_t*)mc, (uint8_t*)local,
+                                                         bytes);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

@@ -97,6 +97,9 @@ typedef struct SxZeroArgs {
   int mode;
   int grid;                  // CTAs to use (0: default)
   int* status;
+  const void* mc_buf;        // optional: NVLS multicast mapping of the gradient buffer (same layout as peers.buf[r]).
+                             // When set, modes 1 and 3 read each 16 bytes with ONE multimem.ld_reduce (the switch sums
+                             // the ranks' values in fp32 and returns bf16) instead of `world` peer loads.
 } SxZeroArgs;
 int sx_zero_grid_default(void);
 int sx_zero_step(const SxZeroArgs* args, cudaStream_t stream);
@@ -107,6 +110,19 @@ int sx_signal_peers(const SxPeers* peers, int channel, unsigned epoch, cudaStrea
 // Waits for `epoch` on `channel` from every rank first when channel >= 0.
 int sx_allgather_pull(const SxPeers* peers, void* dst, long long shard_bytes, long long src_offset_bytes, int channel,
                       unsigned epoch, int grid, int* status, cudaStream_t stream);
+
+// F2 (push form, NVLS): every rank stores its shard ONCE to the multicast mapping of the full-size symmetric buffer
+// (multimem.st: the switch delivers it to all ranks), then the grid's last CTA signals `channel` = `epoch` to every rank
+// and waits for every rank's signal, so when the kernel ends on a rank, all shards have landed in its copy.
+// mc_dst: multicast address of this rank's slot in the full buffer. Callers must make sure no rank still reads the old
+// contents of the buffer when any rank starts pushing (the ZeRO engine's optimizer kernel ends with such a barrier).
+int sx_allgather_mc(const SxPeers* peers, const void* src_shard, void* mc_dst, long long shard_bytes, int channel,
+                    unsigned epoch, int grid, int* status, cudaStream_t stream);
+// Link micro-benchmark kernels: move / reduce `bytes` through peer loads, peer stores, multimem.ld_reduce or multimem.st.
+//   kind 0: pull   dst_local <- peers.buf[peer]          kind 1: push   peers.buf[peer] <- src_local
+//   kind 2: NVLS ld_reduce over mc (bf16 sum) -> dst_local  kind 3: NVLS multimem.st  mc <- src_local
+int sx_link_probe(const SxPeers* peers, int kind, int peer, const void* mc, void* local, long long bytes, int grid,
+                  cudaStream_t stream);
 
 // F2 / F3 / F4: GEMM with a collective fused into the same kernel.
 //   mode 1  all-gather A rows -> GEMM   (TP column-parallel / sequence-parallel input; F3)

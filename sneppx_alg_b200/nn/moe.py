@@ -54,10 +54,12 @@ class SERMoE(Module):
         if self.capacity_factor and self.capacity_factor > 0:
             cap = int(math.ceil(self.capacity_factor * T * self.k / self.E))
             idx, w = moe_ops.enforce_capacity(idx, w, self.E, cap)
-        base = self.shared(x2) if self.shared is not None else None
         if self.ep_world > 1:
-            from ..parallel.expert import ep_experts_forward
-            y = ep_experts_forward(self, x2, idx, w, base)
-        else:
-            y = moe_ops.experts_forward(x2, idx, w, self.w1, self.w2, base, self.act)
+            from ..parallel.expert import ep_experts_forward, ep_plan
+            plan = ep_plan(self, x2, idx)        # plan kernels first; the shared experts run while the host reads its size
+            base = self.shared(x2) if self.shared is not None else None
+            y = ep_experts_forward(self, x2, idx, w, base, plan=plan)
+            return y.view(shape)
+        base = self.shared(x2) if self.shared is not None else None
+        y = moe_ops.experts_forward(x2, idx, w, self.w1, self.w2, base, self.act)
         return y.view(shape)

@@ -2,7 +2,11 @@
 
 Experts are split contiguously over the ranks of the EP group (expert e lives on rank e // E_local; the reference
 assigns round-robin ``i % ep``, kernel/distributed/expert_parallel.c:53-62 - contiguous blocks keep each owner's
-weights one stacked tensor). Fused path: the routing plan is exchanged through peer stores, the dispatch all-to-all
+weights one stacked tensor). By default no routed row is ever dropped: the owners' receive buffers (shared by all
+layers) hold the worst case, and each layer's activations are sized by the row count of its actual routing, which the
+host reads back (4 bytes, behind an event that only waits for the plan kernels) while the shared experts run. Setting
+``SX_EP_CAPACITY`` (or ``cap_mult``) switches to capacity-factor routing without the read-back: rows past
+``cap_mult`` times the fair share are dropped and counted. Fused path: the routing plan is exchanged through peer stores, the dispatch all-to-all
 runs inside the grouped-GEMM kernel (dispatch CTAs push rows into the owners' buffers while GEMM CTAs consume tiles
 as their arrival counters fill), and the combine all-to-all is a peer-load gather fused with the top-k weighted
 sum. Library path (CPU / ``fused=False``): ``all_to_all_single`` around the local grouped GEMMs.
@@ -29,14 +33,17 @@ class EPWorkspace:
     def __init__(self, sg, T, k, d, E, cap_mult=None):
         self.sg, self.world, self.rank = sg, sg.world, sg.rank
         self.E, self.E_local = E, E // sg.world
-        # Capacity factor: an owner accepts up to cap_mult times its fair share of routed rows (never more than every
-        # row of every rank); rows routed past it are dropped, as in capacity-factor MoE training, and counted in
-        # ``dropped``. The reference has no capacity limit because its experts run on the token's own rank
-        # (kernel/distributed/expert_parallel.c:70-110).
-        if cap_mult is None:
-            cap_mult = float(os.environ.get("SX_EP_CAPACITY", "2.0"))
+        # No-drop (default): an owner can be sent every routed row of every rank, so its buffers hold world * T * k
+        # rows (plus padding of each expert segment to 128). Capacity factor (cap_mult given or SX_EP_CAPACITY set):
+        # an owner accepts up to cap_mult times its fair share; rows routed past it are dropped, as in
+        # capacity-factor MoE training, and counted in ``dropped``. The reference has no limit because its experts
+        # run on the token's own rank (kernel/distributed/expert_parallel.c:70-110).
+        if cap_mult is None and os.environ.get("SX_EP_CAPACITY"):
+            cap_mult = float(os.environ["SX_EP_CAPACITY"])
         self.cap_mult = cap_mult
-        rows = min(sg.world * T * k, int(cap_mult * T * k)) + self.E_local * 128
+        self.nodrop = cap_mult is None
+        rows = sg.world * T * k if self.nodrop else min(sg.world * T * k, int(cap_mult * T * k))
+        rows += self.E_local * 128
         self.max_rows = (rows + 127) // 128 * 128
         self.max_tiles = self.max_rows // 128
         dev = sg.device
@@ -65,6 +72,7 @@ class EPPlan:
     def __init__(self, ws: EPWorkspace, idx):
         T, k = idx.shape
         dev = idx.device
+        self.ws = ws
         self.T, self.k, self.E = T, k, ws.E_local
         self.max_rows, self.max_tiles = ws.max_rows, ws.max_tiles
         i32 = lambda *s: torch.empty(*s, dtype=torch.int32, device=dev)
@@ -80,18 +88,35 @@ class EPPlan:
                   _lib.ptr(self.expected_a), _lib.ptr(self.total_rows), C.c_int(ws.max_tiles), _lib.ptr(self.dest_rank),
                   _lib.ptr(self.dest_row), _lib.ptr(ws.dropped), ws.status(), _lib.stream())
         self.valid = self.expected_a - prev       # rows that will arrive per tile for this routing
+        self._rows = None if ws.nodrop else ws.max_rows
+        if ws.nodrop:
+            # rows this rank's experts receive for this routing: read back behind an event that waits for the plan
+            # kernels only, so work queued after this point (the shared experts) keeps the GPU busy meanwhile
+            self._host = torch.empty(1, dtype=torch.int32).pin_memory()
+            self._host.copy_(self.total_rows, non_blocking=True)
+            self._event = torch.cuda.Event()
+            self._event.record()
+
+    @property
+    def rows(self) -> int:
+        """Rows (a multiple of 128) of this rank's expert-sorted buffers that this routing uses."""
+        if self._rows is None:
+            self._event.synchronize()
+            self._rows = max(128, min(int(self._host[0]), self.ws.max_rows))
+        return self._rows
 
 
 def _dispatch_gemm(ws, plan, x, w, rows_buf, arrive, expected, scale, b_mn):
     """Push routed rows of ``x`` to their owners and multiply the local expert-sorted rows by ``w`` (one kernel)."""
-    rows_buf.tensor.zero_()
     d = x.shape[1]
-    a_full = rows_buf.tensor.view(ws.max_rows, d)
+    R = plan.rows
+    rows_buf.tensor[: R * d].zero_()
+    a_full = rows_buf.tensor[: R * d].view(R, d)
     N = w.shape[2] if b_mn else w.shape[1]
-    out = torch.empty(ws.max_rows, N, dtype=x.dtype, device=x.device)
+    out = torch.empty(R, N, dtype=x.dtype, device=x.device)
     g = _lib.SxGemmArgs()
     g.A, g.B, g.D = a_full.data_ptr(), w.data_ptr(), out.data_ptr()
-    g.M, g.N, g.K, g.batch = ws.max_rows, N, d, 1
+    g.M, g.N, g.K, g.batch = R, N, d, 1
     g.lda, g.ldb, g.ldd = d, w.stride(1), N
     g.strideB = w.stride(0)
     g.a_mn, g.b_mn = 0, int(b_mn)
@@ -137,7 +162,7 @@ class _EPExpertsFn(torch.autograd.Function):
         h1, xs_view = _dispatch_gemm(ws, plan, x, W1, ws.rows_a, ws.arrive_a, plan.expected_a, None, False)
         xs = xs_view.clone()
         hm = glu(h1, act)
-        out_view = ws.out.tensor.view(ws.max_rows, ws.d)
+        out_view = ws.out.tensor[: plan.rows * ws.d].view(plan.rows, ws.d)
         gemm(hm, W2, tile_group=plan.tile_group, out=out_view)
         y, _ = _combine(ws, plan, w, base, None)
         ctx.save_for_backward(xs, h1, hm, w, W1, W2)
@@ -150,7 +175,7 @@ class _EPExpertsFn(torch.autograd.Function):
         ws, plan, act = ctx.ws, ctx.plan, ctx.act
         dy = dy.contiguous()
         # expert outputs again (the shared output buffer has been reused since), for d(gate weights)
-        out_view = ws.out.tensor.view(ws.max_rows, ws.d)
+        out_view = ws.out.tensor[: plan.rows * ws.d].view(plan.rows, ws.d)
         gemm(hm, W2, tile_group=plan.tile_group, out=out_view)
         _, dw = _combine(ws, plan, None, None, dy, want_y=False, want_dw=True)
         ws.cum_b += plan.valid
@@ -225,10 +250,35 @@ def dropped_entries(reset=False) -> int:
     return n
 
 
-def ep_experts_forward(layer, x, idx, w, base, fused=None):
-    use_fused = (x.is_cuda and x.dtype == torch.bfloat16 and _lib.available()) if fused is None else fused
-    if not use_fused:
-        return _library_forward(layer, x, idx, w, base)
+def policy_name() -> str:
+    for ws in _WORKSPACES.values():
+        return "no-drop" if ws.nodrop else f"capacity factor {ws.cap_mult}"
+    return "no-drop" if not os.environ.get("SX_EP_CAPACITY") else f"capacity factor {os.environ['SX_EP_CAPACITY']}"
+
+
+def expert_dtype_name() -> str:
+    return "bf16"
+
+
+FORCE_FUSED = None     # tests set True / False to pin the path of every layer; None: fused for CUDA bf16 tensors
+
+
+def _use_fused(x, fused):
+    if fused is None:
+        fused = FORCE_FUSED
+    return (x.is_cuda and x.dtype == torch.bfloat16 and _lib.available()) if fused is None else fused
+
+
+def ep_plan(layer, x, idx, fused=None):
+    """Start the routing plan of a fused expert-parallel layer (launches only; returns None on the library path).
+    Call it before queueing work that does not depend on the routing (the shared experts), then pass the plan to
+    ``ep_experts_forward``."""
+    if not _use_fused(x, fused):
+        return None
+    return EPPlan(_workspace(layer, x, idx), idx)
+
+
+def _workspace(layer, x, idx):
     ws = getattr(layer, "_ep_ws", None)
     if ws is None:
         from .symm import SymmGroup
@@ -236,5 +286,13 @@ def ep_experts_forward(layer, x, idx, w, base, fused=None):
         if key not in _WORKSPACES:
             _WORKSPACES[key] = EPWorkspace(SymmGroup(layer.ep_group), x.shape[0], idx.shape[1], x.shape[1], layer.E)
         ws = layer._ep_ws = _WORKSPACES[key]
-    plan = EPPlan(ws, idx)
+    return ws
+
+
+def ep_experts_forward(layer, x, idx, w, base, fused=None, plan=None):
+    if not _use_fused(x, fused):
+        return _library_forward(layer, x, idx, w, base)
+    ws = _workspace(layer, x, idx)
+    if plan is None:
+        plan = EPPlan(ws, idx)
     return _EPExpertsFn.apply(x, w, layer.w1, layer.w2, base, ws, plan, layer.act)

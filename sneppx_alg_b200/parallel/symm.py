@@ -35,7 +35,7 @@ class SxZeroArgs(C.Structure):
         ("step", C.c_int), ("max_norm", C.c_float), ("norm_out", C.c_void_p),
         ("ready_channel", C.c_int), ("ready_epoch", C.c_uint), ("norm_channel", C.c_int), ("norm_epoch", C.c_uint),
         ("done_channel", C.c_int), ("done_epoch", C.c_uint), ("mode", C.c_int), ("grid", C.c_int),
-        ("status", C.c_void_p),
+        ("status", C.c_void_p), ("mc_buf", C.c_void_p),
     ]
 
 
@@ -106,6 +106,17 @@ class SymmGroup:
         p = self.peers(src)
         _lib.call("sx_allgather_pull", C.byref(p), C.c_void_p(dst.data_ptr()), C.c_longlong(shard_bytes),
                   C.c_longlong(src_offset_bytes), C.c_int(channel), C.c_uint(epoch), C.c_int(grid),
+                  C.c_void_p(_lib.status_word(self.device).data_ptr()), stream or _lib.stream())
+
+    def allgather_mc(self, src: torch.Tensor, dst: SymmBuffer, dst_offset_bytes: int, shard_bytes: int, channel: int,
+                     epoch: int, grid: int = 32, stream=None):
+        """NVLS all-gather: store ``src`` (this rank's shard) once to the multicast mapping of ``dst`` at
+        ``dst_offset_bytes + rank * shard_bytes``; ends with a barrier over the group on ``channel``."""
+        assert dst.multicast_ptr, "buffer has no multicast mapping"
+        p = self.peers(dst)
+        _lib.call("sx_allgather_mc", C.byref(p), C.c_void_p(src.data_ptr()),
+                  C.c_void_p(dst.multicast_ptr + dst_offset_bytes + self.rank * shard_bytes), C.c_longlong(shard_bytes),
+                  C.c_int(channel), C.c_uint(epoch), C.c_int(grid),
                   C.c_void_p(_lib.status_word(self.device).data_ptr()), stream or _lib.stream())
 
     def allreduce_small(self, buf: SymmBuffer, n: int, channel: int = 56, stream=None):

@@ -21,6 +21,7 @@ Library path (``fused=False``, also CPU/gloo): ``reduce_scatter`` / ``all_reduce
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import List
 
 import torch
@@ -49,7 +50,7 @@ def _find_layer_list(model):
 
 class ZeroEngine:
     def __init__(self, model, zero_stage=3, lr=1e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1,
-                 max_grad_norm=1.0, group=None, fused=None, comm_grid=0, timeout_s=5.0):
+                 max_grad_norm=1.0, group=None, fused=None, comm_grid=0, timeout_s=5.0, nvls=None):
         self.model = model
         self.group = group if group is not None else dist.group.WORLD
         self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
@@ -63,7 +64,13 @@ class ZeroEngine:
         dev = params[0].device
         self.device = dev
         self.fused = (dev.type == "cuda" and params[0].dtype == torch.bfloat16) if fused is None else fused
-        # ---- buckets: one per repeated layer (in forward order), the rest last
+        # NVLS (in-switch reduction / multicast stores) for the gradient reduce-scatter and the parameter
+        # all-gather; needs a multicast mapping of the symmetric buffers, else the peer-load kernels run.
+        if nvls is None:
+            nvls = os.environ.get("SX_ZERO_NVLS", "0") == "1"
+        self.nvls = bool(nvls) and self.fused
+        # ---- buckets: one per repeated layer (in forward order), then what runs before the layers (embedding) and
+        # what runs after them (final norm, head): the last group's gradients are complete first in backward
         layers = _find_layer_list(model)
         bucket_params: List[List[torch.nn.Parameter]] = []
         taken = set()
@@ -76,8 +83,23 @@ class ZeroEngine:
                     bucket_params.append(ps)
                     self.bucket_modules.append(layer)
         rest = [p for p in params if id(p) not in taken]
-        self.rest_index = len(bucket_params)
-        if rest:
+        self.rest_index = len(bucket_params)      # first of the non-layer buckets
+        self.post_index = None
+        if rest and layers is not None:
+            # parameters registered after the layer list are used after it in forward (final norm, untied head)
+            order = [id(p) for _, p in model.named_parameters()]
+            layer_ids = {id(p) for l in layers for p in l.parameters()}
+            first_layer = min((i for i, q in enumerate(order) if q in layer_ids), default=len(order))
+            pos = {q: i for i, q in enumerate(order)}
+            pre = [p for p in rest if pos.get(id(p), 0) < first_layer]
+            post = [p for p in rest if pos.get(id(p), 0) >= first_layer]
+            if pre and post:
+                bucket_params.append(pre)
+                self.post_index = len(bucket_params)
+                bucket_params.append(post)
+            else:
+                bucket_params.append(rest)
+        elif rest:
             bucket_params.append(rest)
         ordered = [p for b in bucket_params for p in b]
         self.sg = None
@@ -90,11 +112,12 @@ class ZeroEngine:
 
             def alloc(n, dt):
                 # FlatParams asks for the parameter buffer first, then the gradient buffer. Gradients must be
-                # peer-readable (owners pull their slice from every rank); gathered parameters are local.
+                # peer-readable (owners pull their slice from every rank); gathered parameters are local, unless
+                # they are filled by multicast stores (NVLS), which need the symmetric mapping too.
                 calls.append(n)
-                if len(calls) == 2:
+                if len(calls) == 2 or (len(calls) == 1 and self.nvls):
                     b = self.sg.alloc(n, dt)
-                    self._symm["grad"] = b
+                    self._symm["grad" if len(calls) == 2 else "param"] = b
                     b.tensor.zero_()
                     return b.tensor
                 return torch.zeros(n, dtype=dt, device=dev)
@@ -147,6 +170,11 @@ class ZeroEngine:
             # one extra slot after the per-bucket partials carries the sum of squares of the local expert gradients
             self.partials = torch.zeros(len(self.bounds) * self.grid + 1, dtype=torch.float32, device=dev)
             self.norm_out = torch.zeros(4, dtype=torch.float32, device=dev)
+            if self.nvls and not (self._symm["grad"].multicast_ptr and self._symm["param"].multicast_ptr):
+                self.nvls = False          # no multicast mapping on this system: peer loads
+            if self.nvls and comm_grid == 0:
+                self.grid = 64             # one in-switch reduction per 16 bytes: few CTAs keep the links busy
+                self.partials = torch.zeros(len(self.bounds) * self.grid + 1, dtype=torch.float32, device=dev)
             self.comm_stream = torch.cuda.Stream(device=dev)
             self.gather_events = [None] * len(self.bounds)
             self._ready_count = 0
@@ -179,6 +207,25 @@ class ZeroEngine:
 
         for bi, mod in enumerate(self.bucket_modules):
             mod.register_forward_pre_hook(pre_hook_factory(bi))
+        if self.post_index is not None and self.bucket_modules:
+            pi = self.post_index
+
+            def after_last_layer(mod, args, out):
+                # what follows the layers (final norm, head) needs its gathered parameters now; and its gradients
+                # are complete as soon as backward has produced the gradient of this output
+                ev = eng.gather_events[pi]
+                if ev is not None:
+                    torch.cuda.current_stream().wait_event(ev)
+                    eng.gather_events[pi] = None
+                if torch.is_grad_enabled() and eng.stage >= 2:
+                    outs = out if isinstance(out, (tuple, list)) else (out,)
+                    for o in outs:
+                        if torch.is_tensor(o) and o.requires_grad:
+                            o.register_hook(lambda g: eng._bucket_ready(pi))
+                            break
+                return None
+
+            self.bucket_modules[-1].register_forward_hook(after_last_layer)
 
     def _launch_reduce(self, bi):
         """Called when bucket ``bi`` holds this rank's complete gradients (stream-ordered on the compute stream)."""
@@ -209,6 +256,8 @@ class ZeroEngine:
         a.partial_offset = bi * self.grid
         a.ready_channel, a.ready_epoch = 0, epoch
         a.mode = 1
+        if self.nvls:
+            a.mc_buf = self._symm["grad"].multicast_ptr
         _lib.call("sx_zero_step", C.byref(a), sptr)
 
     def _bucket_ready(self, bi):
@@ -230,21 +279,30 @@ class ZeroEngine:
         return a
 
     def _prefetch_params(self):
-        """Pull every bucket's shards into the full bf16 buffer on the comm stream, in forward order."""
+        """Refill the full bf16 parameter buffer from the owners' shards on the comm stream, in forward order:
+        what runs before the layers, the layers, what runs after them. Peer-load pull kernels, or (NVLS) one
+        multicast store of this rank's shard per bucket."""
         cs = self.comm_stream
         sptr = C.c_void_p(cs.cuda_stream)
         es = self.fp.flat.element_size()
-        order = [self.rest_index] + list(range(len(self.bucket_modules))) if self.rest_index < len(self.bounds) \
-            else list(range(len(self.bucket_modules)))
+        nl = len(self.bucket_modules)
+        tail = list(range(nl, len(self.bounds)))
+        pre = [b for b in tail if b != self.post_index]
+        order = pre + list(range(nl)) + ([self.post_index] if self.post_index is not None else [])
         for bi in order:
             b0, b1 = self.bounds[bi]
             sz = (b1 - b0) // self.world
-            self.sg.allgather_pull(self.pshard, self.fp.flat[b0:b1], sz * es, self.shard_off[bi] * es, grid=48,
-                                   stream=sptr)
+            if self.nvls:
+                src = self.pshard.tensor[self.shard_off[bi]: self.shard_off[bi] + sz]
+                self.sg.allgather_mc(src, self._symm["param"], b0 * es, sz * es, 6, self.sg.next_epoch(6), grid=32,
+                                     stream=sptr)
+            else:
+                self.sg.allgather_pull(self.pshard, self.fp.flat[b0:b1], sz * es, self.shard_off[bi] * es, grid=48,
+                                       stream=sptr)
             ev = torch.cuda.Event()
             ev.record(cs)
-            if bi == self.rest_index:
-                torch.cuda.current_stream().wait_event(ev)   # embeddings / head / final norm: needed first and last
+            if bi in pre or not self.bucket_modules:
+                torch.cuda.current_stream().wait_event(ev)   # embeddings: needed first
             else:
                 self.gather_events[bi] = ev
 

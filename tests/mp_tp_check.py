@@ -65,13 +65,29 @@ def main():
         full_dx = dh @ wc.detach()
         dist.all_reduce(full_dx)
         worst = max(worst, rel(x_s.grad, full_dx[rank * rs: (rank + 1) * rs]))
+    # F2: the weight is sharded by rows over the ranks (ZeRO-3); the GEMM pulls the other ranks' rows itself.
+    # y = act [M, K] x W^T with W [N, K] = concatenation of every rank's shard, against an fp32 matmul.
+    ftp = tp.fused
+    worst_f2 = 0.0
+    for it in range(2):
+        torch.manual_seed(500 + it)                     # the same activation on every rank
+        act = torch.randn(384, d, device=dev, dtype=torch.bfloat16)
+        torch.manual_seed(900 + 10 * it + rank)
+        w_shard = (torch.randn(256, d, device=dev) * 0.05).to(torch.bfloat16)
+        y, _ = ftp.ag_gemm(w_shard, act, key="f2", gather_b=True)
+        ws = [torch.empty_like(w_shard) for _ in range(world)]
+        dist.all_gather(ws, w_shard)
+        ref = act.float() @ torch.cat(ws, 0).float().t()
+        worst_f2 = max(worst_f2, rel(y, ref))
+    worst = max(worst, worst_f2)
     torch.cuda.synchronize()
     check_status()
     ok = worst < 4e-2
     t = torch.tensor([int(ok)], device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MIN)
     if rank == 0:
-        print(f"tp world {world}: worst rel err {worst:.3e} ->", "OK" if t.item() else "MISMATCH")
+        print(f"tp world {world}: worst rel err {worst:.3e} (weight-gather GEMM {worst_f2:.3e}) ->",
+              "OK" if t.item() else "MISMATCH")
     dist.destroy_process_group()
     sys.exit(0 if t.item() else 1)
 

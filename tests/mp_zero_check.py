@@ -1,5 +1,7 @@
 """Worker for the multi-GPU ZeRO test: run under torch.distributed.run, one rank per GPU.
-Compares the fused (peer-memory) ZeRO path with the torch.distributed library path on the same model/data."""
+Compares the fused (peer-memory) ZeRO path with (a) an fp32 PyTorch oracle (the same model in fp32 on plain torch
+ops, gradients averaged with an fp32 all-reduce, torch.optim.AdamW, clip_grad_norm_) and (b) the torch.distributed
+library path of the engine, on the same model and data."""
 import copy
 import os
 import sys
@@ -25,13 +27,26 @@ def main():
     base = build_model(cfg, dtype=torch.bfloat16, device=dev)
     lib_model = copy.deepcopy(base)
     fused = ZeroEngine(base, zero_stage=stage, lr=1e-3, fused=True)
+    oracle = copy.deepcopy(lib_model).float()
     lib = ZeroEngine(lib_model, zero_stage=stage, lr=1e-3, fused=False)
-    worst = 0.0
+    opt = torch.optim.AdamW(oracle.parameters(), lr=1e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    worst, worst_o, worst_n = 0.0, 0.0, 0.0
     for step in range(4):
         ids = torch.randint(0, cfg.vocab_size, (2, 256), generator=torch.Generator().manual_seed(10 * step + rank)).to(dev)
         lf = fused.step(ids, ids).item()
         ll = lib.step(ids, ids).item()
         worst = max(worst, abs(lf - ll))
+        opt.zero_grad(set_to_none=True)
+        lo = oracle(ids, labels=ids)["loss"]
+        lo.backward()
+        for q in oracle.parameters():
+            dist.all_reduce(q.grad)
+            q.grad /= world
+        no = float(torch.nn.utils.clip_grad_norm_(oracle.parameters(), 1.0))
+        opt.step()
+        worst_o = max(worst_o, abs(lf - lo.item()))
+        torch.cuda.synchronize()
+        worst_n = max(worst_n, abs(float(fused.last_norm[1]) - no) / max(no, 1.0))
     torch.cuda.synchronize()
     check_status()
     # after the last step the gathered parameters are refreshed asynchronously; wait for them
@@ -39,11 +54,16 @@ def main():
     pf, pl = fused.fp.flat.float(), lib.fp.flat.float()
     rel = (pf - pl).abs().max().item() / (pl.abs().max().item() + 1e-6)
     nf, nl = float(fused.last_norm[1]), float(lib.last_norm[1])
-    ok = worst < 0.05 and rel < 2e-2 and abs(nf - nl) < 2e-2 * max(nl, 1.0)
+    rel_o = 0.0
+    for (_, pa), (_, pb) in zip(base.named_parameters(), oracle.named_parameters()):
+        rel_o = max(rel_o, (pa.float() - pb).abs().max().item() / (pb.abs().max().item() + 1e-6))
+    ok = worst < 0.05 and rel < 2e-2 and abs(nf - nl) < 2e-2 * max(nl, 1.0) and worst_o < 0.05 and rel_o < 3e-2 \
+        and worst_n < 3e-2
     t = torch.tensor([int(ok)], device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MIN)
     if rank == 0:
-        print(f"zero stage {stage} world {world}: loss diff {worst:.4f} param rel {rel:.2e} norm {nf:.4f}/{nl:.4f} ->",
+        print(f"zero stage {stage} world {world}: vs fp32 oracle loss diff {worst_o:.4f} param rel {rel_o:.2e} norm rel "
+              f"{worst_n:.2e}; vs library loss diff {worst:.4f} param rel {rel:.2e} norm {nf:.4f}/{nl:.4f} ->",
               "OK" if t.item() else "MISMATCH")
     dist.destroy_process_group()
     sys.exit(0 if t.item() else 1)
