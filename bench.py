@@ -39,6 +39,8 @@ def parse():
     ap.add_argument("--ep", action="store_true", help="expert parallelism over all ranks (SER MoE models): experts are "
                     "sharded, the other parameters use ZeRO-1")
     ap.add_argument("--zero-stage", type=int, default=3)
+    ap.add_argument("--fp8-experts", action="store_true", help="SER MoE models: forward expert GEMMs in block-scaled "
+                    "fp8 (e4m3 data, 1x128 activation and 128x128 weight scales); backward stays bf16")
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel size (Mamba-2 models): ranks form world/tp "
                     "data-parallel replicas of tp consecutive ranks; ignored on one GPU")
     return ap.parse_args()
@@ -286,6 +288,8 @@ def main():
     if args.layers:
         cfg.num_hidden_layers = cfg.num_layers = args.layers
     cfg.max_position_embeddings = max(args.seq, 8)
+    if args.fp8_experts:
+        cfg.expert_fp8 = True
     torch.manual_seed(1234)
     arch = getattr(cfg, "architecture", "transformer")
     B, S, V = args.micro_batch, args.seq, cfg.vocab_size
@@ -327,7 +331,7 @@ def main():
         dist.all_reduce(d)
         n_moe = sum(1 for m in model.modules() if hasattr(m, "ep_group") and hasattr(m, "router"))
         routed = float(B * S * world) * cfg.num_experts_per_token * max(n_moe, 1) * (args.warmup + 2 * args.steps)
-        extra["expert_parallel"] = {"policy": _ep.policy_name(), "experts": _ep.expert_dtype_name(),
+        extra["expert_parallel"] = {"policy": _ep.policy_name(), "experts": _ep.expert_dtype_name(model),
                                     "dropped_fraction_of_routed_entries": float(d.item()) / routed}
     if rank == 0:
         print(json.dumps(result_line(args, world, dp, res, B, S, "ours", model_label(cfg, args), parallelism,

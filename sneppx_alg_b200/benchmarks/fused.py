@@ -174,7 +174,7 @@ def main(argv=None):
             za.lr, za.beta1, za.beta2, za.eps, za.wd, za.step, za.max_norm = 1e-4, 0.9, 0.95, 1e-8, 0.1, 5, 0.0
             za.ready_channel, za.ready_epoch = 2, state["e"]
             za.done_channel, za.done_epoch = 3, state["e"]
-            za.mode, za.grid = 3, (64 if nvls else _lib.lib().sx_zero_grid_default())
+            za.mode, za.grid = 3, _lib.lib().sx_zero_grid_default()
             za.mc_buf = gbuf.multicast_ptr if nvls else None
             za.status = _lib.status_word(sg.device).data_ptr()
             _lib.call("sx_zero_step", C.byref(za), _lib.stream())

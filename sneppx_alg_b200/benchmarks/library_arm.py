@@ -137,6 +137,8 @@ class _MoE(nn.Module):
     experts split contiguously over the EP ranks, shared experts on every rank. No token is dropped: the
     all-to-all carries exactly the routed rows (split sizes are read back to the host, as NCCL needs them)."""
 
+    grouped_mm = True       # use torch._grouped_mm for the expert projections while it works on this device
+
     def __init__(self, cfg, dtype, device, ep_group=None):
         super().__init__()
         d, ff = cfg.hidden_size, cfg.moe_intermediate_size
@@ -176,15 +178,26 @@ class _MoE(nn.Module):
         eid = torch.arange(El, device=x.device).repeat(w_).repeat_interleave(recv_ce.reshape(-1), output_size=sum(rc))
         perm = torch.argsort(eid, stable=True)
         xs = recv_x[perm]
-        sizes = recv_ce.sum(0).tolist()
-        outs = []
-        for e, chunk in enumerate(xs.split(sizes)):
-            if chunk.shape[0] == 0:
-                outs.append(chunk)
-                continue
-            g, u = F.linear(chunk, self.w1[e]).chunk(2, -1)
-            outs.append(F.linear(F.silu(g) * u, self.w2[e]))
-        ys = torch.empty_like(xs).index_copy(0, perm, torch.cat(outs))
+        per_expert = recv_ce.sum(0)
+        ys_sorted = None
+        if _MoE.grouped_mm and hasattr(torch, "_grouped_mm"):
+            # one grouped GEMM per projection over the expert-sorted rows (row offsets stay on the device)
+            try:
+                offs = per_expert.cumsum(0).to(torch.int32)
+                g, u = torch._grouped_mm(xs, self.w1.transpose(1, 2), offs=offs).chunk(2, -1)
+                ys_sorted = torch._grouped_mm(F.silu(g) * u, self.w2.transpose(1, 2), offs=offs)
+            except (RuntimeError, NotImplementedError):
+                _MoE.grouped_mm = False        # this build / device has no grouped GEMM: loop over the experts
+        if ys_sorted is None:
+            outs = []
+            for chunk, w1e, w2e in zip(xs.split(per_expert.tolist()), self.w1.unbind(0), self.w2.unbind(0)):
+                if chunk.shape[0] == 0:
+                    outs.append(chunk)
+                    continue
+                g, u = F.linear(chunk, w1e).chunk(2, -1)
+                outs.append(F.linear(F.silu(g) * u, w2e))
+            ys_sorted = torch.cat(outs)
+        ys = torch.empty_like(xs).index_copy(0, perm, ys_sorted)
         back = _a2a(ys, sc, rc, self.group)
         y = torch.zeros(T, d, dtype=torch.float32, device=x.device).index_add(
             0, tok, back.float() * w.reshape(-1)[order].unsqueeze(1))

@@ -2,7 +2,10 @@
 reporting output tokens per second and time to first token.
 
 ``python -m sneppx_alg_b200.benchmarks.serving [--model llama3-8b] [--requests 64] [--prompt-len 2048] [--new-tokens 256]
-[--quantize none|fp8|int4] [--out file.json]``
+[--quantize none|fp8|int4] [--http] [--out file.json]``
+``--http`` drives the same workload through the HTTP front-end: the FastAPI application is served by uvicorn on
+127.0.0.1 and every request is a ``POST /v1/generate`` carrying its prompt as token ids, all sent at once from client
+threads; TTFT is the server's figure for each request (submission to first token), throughput is client wall clock.
 Under ``torch.distributed.run`` with N ranks the engine runs tensor-parallel over all of them (``TPLlamaPagedRunner``).
 
 The default workload is the serving configuration of the baseline list: 64 concurrent requests, prompts of 2048
@@ -57,6 +60,77 @@ def run(model, requests=64, prompt_len=2048, new_tokens=256, max_prefill_tokens=
             "total_tokens_per_s": (out_tokens + eng.stats["prefill_tokens"]) / dt}
 
 
+def run_http(model, requests=64, prompt_len=2048, new_tokens=256, max_prefill_tokens=16384, block_size=16, seed=0) -> dict:
+    """The workload of ``run`` sent through ``POST /v1/generate`` of the FastAPI front-end (uvicorn, loopback)."""
+    import http.client
+    import socket
+    import threading
+
+    import uvicorn
+
+    from ..serving.server import create_app
+    cfg = model.config
+    blocks = requests * ((prompt_len + new_tokens + block_size - 1) // block_size) + 64
+    app = create_app({"bench": {"model": model, "engine_kwargs": dict(
+        num_blocks=blocks, block_size=block_size, max_batch_size=requests, max_prefill_tokens=max_prefill_tokens,
+        enable_prefix_cache=False)}})
+    with socket.socket() as sck:
+        sck.bind(("127.0.0.1", 0))
+        port = sck.getsockname()[1]
+    server = uvicorn.Server(uvicorn.Config(app, host="127.0.0.1", port=port, log_level="error"))
+    th = threading.Thread(target=server.run, daemon=True)
+    th.start()
+    t_wait = time.perf_counter()
+    while not server.started:
+        if time.perf_counter() - t_wait > 60:
+            raise RuntimeError("HTTP server did not start")
+        time.sleep(0.05)
+    g = torch.Generator().manual_seed(seed)
+    prompts = [torch.randint(0, cfg.vocab_size, (prompt_len,), generator=g).tolist() for _ in range(requests)]
+
+    def post(ids, n):
+        conn = http.client.HTTPConnection("127.0.0.1", port, timeout=3600)
+        t0 = time.perf_counter()
+        conn.request("POST", "/v1/generate", json.dumps({"prompt_token_ids": ids, "max_new_tokens": n}),
+                     {"Content-Type": "application/json"})
+        resp = conn.getresponse()
+        body = json.loads(resp.read())
+        conn.close()
+        if resp.status != 200:
+            raise RuntimeError(f"HTTP {resp.status}: {body}")
+        return body, time.perf_counter() - t0
+
+    post(prompts[0][: min(prompt_len, 128)], 4)          # warm-up (allocations, kernel loading, graph capture)
+    post(prompts[0][: min(prompt_len, 128)], 4)
+    results = [None] * requests
+
+    def worker(i):
+        results[i] = post(prompts[i], new_tokens)
+
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(requests)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    dt = time.perf_counter() - t0
+    server.should_exit = True
+    th.join(10)
+    for w in app.state.workers.values():
+        w.stop()
+    out_tokens = sum(r[0]["completion_tokens"] for r in results)
+    ttft = sorted(r[0]["ttft_s"] for r in results)
+    lat = sorted(r[1] for r in results)
+    pct = lambda v, q: v[min(len(v) - 1, int(q * len(v)))]  # noqa: E731
+    return {"metric": "serving output tokens/sec", "value": out_tokens / dt, "unit": "tokens/s", "requests": requests,
+            "prompt_len": prompt_len, "new_tokens": new_tokens, "seconds": dt, "output_tokens": out_tokens,
+            "ttft_p50_s": pct(ttft, 0.5), "ttft_p95_s": pct(ttft, 0.95), "ttft_min_s": ttft[0],
+            "latency_p50_s": pct(lat, 0.5), "latency_max_s": lat[-1],
+            "front_end": "HTTP POST /v1/generate (FastAPI on uvicorn, loopback), prompts as token ids"}
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     ap.add_argument("--model", default="llama3-8b")
@@ -65,6 +139,7 @@ def main(argv=None):
     ap.add_argument("--new-tokens", type=int, default=256)
     ap.add_argument("--quantize", choices=["none", "fp8", "int4"], default="none")
     ap.add_argument("--max-prefill-tokens", type=int, default=16384)
+    ap.add_argument("--http", action="store_true", help="send the requests through POST /v1/generate (one GPU)")
     ap.add_argument("--out", default=None)
     a = ap.parse_args(argv)
     import os
@@ -90,7 +165,10 @@ def main(argv=None):
     if a.quantize != "none":
         from ..ops.quant import quantize_model_
         quantize_model_(model, a.quantize)
-    r = run(model, a.requests, a.prompt_len, a.new_tokens, a.max_prefill_tokens, tp_group=tp_group)
+    if a.http and world == 1:
+        r = run_http(model, a.requests, a.prompt_len, a.new_tokens, a.max_prefill_tokens)
+    else:
+        r = run(model, a.requests, a.prompt_len, a.new_tokens, a.max_prefill_tokens, tp_group=tp_group)
     r["config"] = {"model": a.model, "weights": "bf16" if a.quantize == "none" else a.quantize, "kv_cache": "bf16" if cuda else "fp32",
                    "parallelism": (f"tp{world}" if world > 1 else "1 GPU") if cuda else (f"cpu tp{world}" if world > 1 else "cpu"),
                    "data": "random token ids, random-init weights"}

@@ -94,6 +94,40 @@ __global__ void __launch_bounds__(256) zero_step_kernel(const __grid_constant__ 
     if (!wait_all(z.pt, z.ready_channel, z.ready_epoch, z.status)) return;
   }
 
+  if (z.mode == 1 && z.mc) {
+    // NVLS: four in-switch reductions in flight per thread before the first result is used
+    float ss = 0.f;
+    constexpr int U = 4;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; i0 < nvec; i0 += stride * U) {
+      uint4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < nvec) v[u] = multimem_ld_reduce_bf16x8(z.mc + z.elem_offset + i * 8);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * stride;
+        if (i >= nvec) continue;
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        acc_bf16x8(acc, v[u]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          acc[j] *= inv_world;
+          ss += acc[j] * acc[j];
+        }
+        float4* o = reinterpret_cast<float4*>(z.reduced + i * 8);
+        o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+      }
+    }
+    ss = block_sum(ss, red);
+    if (threadIdx.x == 0) z.sumsq_partials[z.partial_offset + blockIdx.x] = ss;
+    return;
+  }
   if (z.mode == 1) {
     float ss = 0.f;
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;

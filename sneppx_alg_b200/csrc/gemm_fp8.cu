@@ -10,6 +10,11 @@
 // with its scale (acc += sw[nb, kb] * sx[token, kb] * partial) while the next k-block runs in the other buffer.
 // Operand tiles are exactly one 128-byte swizzle row wide (128 fp8 = 128 B), loaded by TMA. With split-K several CTAs
 // share a tile's reduction and add fp32 partials into a zeroed workspace that a second kernel converts.
+// Grouped form (SER experts, G2 in fp8): the token rows are expert-sorted with every expert's segment padded to
+// 128 rows; `tile_group[t]` names the expert of token tile t (-1: unused tile, its output rows are zero-filled).
+// The experts' weights are one stacked [E * N, K] tensor (N a multiple of 128, so a 128-row weight tile never
+// straddles two experts) with scales [E * N/128, K/128]; a CTA simply offsets its weight-row and scale-row
+// coordinates by the tile's expert.
 // The reference has e4m3 quantise / dequantise kernels only (kernel/quantization/quantize_cuda.cu,
 // kernel/quantization/quantize_fp8.c); block-scaled fp8 experts are what its DeepSeek-shape preset implies.
 #include "tc_common.cuh"
@@ -32,6 +37,7 @@ struct F8Params {
   long long ldd;
   int M, N, K, kblks, splits;
   int* status;
+  const int* tile_group;   // grouped form: expert of each 128-token tile (BT == 128), else nullptr
 };
 
 template <int BT>
@@ -85,7 +91,10 @@ __global__ void __launch_bounds__(F8_THREADS, 1) gemm_f8_kernel(const __grid_con
   const int nb = blockIdx.x, tb = blockIdx.y, sp = blockIdx.z;
   const int per = (p.kblks + p.splits - 1) / p.splits;
   const int kb0 = sp * per, kb1 = min(p.kblks, kb0 + per);
-  const int nkb = max(kb1 - kb0, 0);
+  const int grp = p.tile_group ? p.tile_group[tb] : 0;
+  const int nkb = grp < 0 ? 0 : max(kb1 - kb0, 0);          // unused tile: no loads, no MMAs, zero output
+  const int w_row0 = grp * (p.tile_group ? p.N : 0) + nb * 128;     // row of the stacked weight tensor
+  const int s_row = grp * (p.tile_group ? (p.N + 127) / 128 : 0) + nb;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -95,7 +104,7 @@ __global__ void __launch_bounds__(F8_THREADS, 1) gemm_f8_kernel(const __grid_con
         if (!mbar_wait(&empty_bar[stage], phase ^ 1, s_abort, p.status, ST_TIMEOUT_PRODUCER)) break;
         uint8_t* sw_ = smem + stage * Cfg::STAGE_BYTES;
         mbar_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
-        tma_load_2d(sw_, &p.tmW, &full_bar[stage], (kb0 + i) * F8_BK, nb * 128);
+        tma_load_2d(sw_, &p.tmW, &full_bar[stage], (kb0 + i) * F8_BK, w_row0);
         tma_load_2d(sw_ + Cfg::W_BYTES, &p.tmX, &full_bar[stage], (kb0 + i) * F8_BK, tb * BT);
         if (++stage == Cfg::STAGES) { stage = 0; phase ^= 1; }
       }
@@ -144,7 +153,7 @@ __global__ void __launch_bounds__(F8_THREADS, 1) gemm_f8_kernel(const __grid_con
     }
     for (int i = 0; i < nkb && ok; ++i) {
       const int buf = i & 1, kb = kb0 + i;
-      const float swv = p.sw[(long long)nb * p.kblks + kb];
+      const float swv = p.sw[(long long)s_row * p.kblks + kb];
       if (!mbar_wait_warp(&tfull[buf], (i >> 1) & 1, s_abort, p.status, ST_TIMEOUT_EPILOGUE)) { ok = false; break; }
       tc_fence_after();
 #pragma unroll
@@ -227,6 +236,36 @@ static int f8_launch(const F8Params& p, dim3 grid, cudaStream_t st) {
 }  // namespace sx
 using namespace sx;
 
+// Grouped form: xq [rows, K] e4m3 expert-sorted rows (segments padded to 128), sx [rows, K/128];
+// wq [E * N, K] e4m3, sw [E * N/128, K/128]; tile_group int32 [rows / 128]; out bf16 [rows, N]. N % 128 == 0.
+extern "C" int sx_gemm_fp8_grouped(const void* xq, long long ldx, const float* sx_, const void* wq, long long ldw,
+                                   const float* sw_, const int* tile_group, int num_experts, void* out, long long ldd,
+                                   int rows, int N, int K, int* status, cudaStream_t st) {
+  if (rows <= 0 || N <= 0) return 0;
+  if (K % 128 || N % 128 || rows % 128 || (ldx % 16) || (ldw % 16) || !tile_group ||
+      (reinterpret_cast<uintptr_t>(xq) & 15) || (reinterpret_cast<uintptr_t>(wq) & 15))
+    return -1;
+  F8Params p;
+  {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)N * (uint64_t)num_experts};
+    uint64_t strides[1] = {(uint64_t)ldw};
+    uint32_t box[2] = {128, 128};
+    int rc = make_tmap(&p.tmW, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, wq, dims, strides, box);
+    if (rc) return rc;
+  }
+  {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)rows};
+    uint64_t strides[1] = {(uint64_t)ldx};
+    uint32_t box[2] = {128, 128};
+    int rc = make_tmap(&p.tmX, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, xq, dims, strides, box);
+    if (rc) return rc;
+  }
+  p.sw = sw_; p.sx = sx_; p.bias = nullptr; p.D = (__nv_bfloat16*)out; p.work = nullptr; p.ldd = ldd;
+  p.M = rows; p.N = N; p.K = K; p.kblks = K / 128; p.status = status; p.splits = 1; p.tile_group = tile_group;
+  dim3 grid(N / 128, rows / 128, 1);
+  return f8_launch<128>(p, grid, st);
+}
+
 // Bytes of fp32 workspace the call needs (0 when no split-K is used for this shape).
 extern "C" long long sx_gemm_fp8_workspace(int M, int N, int K) {
   const int bt = M <= 32 ? 32 : (M <= 64 ? 64 : 128);
@@ -262,7 +301,7 @@ extern "C" int sx_gemm_fp8(const void* xq, long long ldx, const float* sx_, cons
     if (rc) return rc;
   }
   p.sw = sw_; p.sx = sx_; p.bias = bias; p.D = (__nv_bfloat16*)out; p.work = work; p.ldd = ldd;
-  p.M = M; p.N = N; p.K = K; p.kblks = K / 128; p.status = status;
+  p.M = M; p.N = N; p.K = K; p.kblks = K / 128; p.status = status; p.tile_group = nullptr;
   const int nblks = (N + 127) / 128, tblks = (M + bt - 1) / bt;
   const long long ctas = (long long)nblks * tblks;
   int splits = (int)((148 * 2 + ctas - 1) / ctas);

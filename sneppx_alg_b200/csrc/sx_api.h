@@ -193,6 +193,19 @@ int sx_npe_plan_program(const int* prog8, int n, long long mem_size, int in_w, i
 int sx_npe_run(const int* prog_host, const int* prog_dev, int n, const float* mem, long long mem_size, const float* x, long long rows,
                int in_w, float* out, int out_w_expected, cudaStream_t stream);
 
+// Block-scaled fp8 (e4m3) GEMM, y = (xq * sx) (wq * sw)^T: xq [M, K] with fp32 scales sx [M, K/128] (1 x 128 blocks),
+// wq [N, K] with sw [ceil(N/128), K/128] (128 x 128 blocks), bf16 out. `work`: sx_gemm_fp8_workspace bytes (or null).
+long long sx_gemm_fp8_workspace(int M, int N, int K);
+int sx_gemm_fp8(const void* xq, long long ldx, const float* sx, const void* wq, long long ldw, const float* sw,
+                const float* bias, void* out, long long ldd, float* work, int M, int N, int K, int* status,
+                cudaStream_t stream);
+// Grouped form for SER experts: expert-sorted token rows (segments padded to 128 rows) times the stacked expert
+// weights [E * N, K] (N % 128 == 0, scales [E * N/128, K/128]); tile_group[t] is the expert of token tile t
+// (-1: unused tile, its output rows are zero).
+int sx_gemm_fp8_grouped(const void* xq, long long ldx, const float* sx, const void* wq, long long ldw, const float* sw,
+                        const int* tile_group, int num_experts, void* out, long long ldd, int rows, int N, int K,
+                        int* status, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

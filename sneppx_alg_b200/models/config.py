@@ -86,6 +86,7 @@ class ModelConfig:
     router_aux_loss_coef: float = 0.0
     router_z_loss_coef: float = 0.0
     expert_capacity_factor: float = 0.0   # 0: dropless
+    expert_fp8: bool = False              # forward expert GEMMs in block-scaled e4m3 (1x128 / 128x128 scales)
     fp8_experts: bool = False
     # MLA (DeepSeek-V2)
     kv_lora_rank: int = 0

@@ -30,7 +30,7 @@ class DeepSeekLayer(Module):
             self.mlp = SERMoE(d, cfg.moe_intermediate_size, cfg.num_experts, cfg.num_experts_per_token,
                               cfg.num_shared_experts, cfg.expert_capacity_factor, cfg.router_aux_loss_coef,
                               cfg.router_z_loss_coef, dtype=dtype, device=device, init_std=cfg.initializer_range,
-                              ep_group=ep_group)
+                              ep_group=ep_group, expert_fp8=getattr(cfg, "expert_fp8", False))
 
     def forward(self, delta, resid, rope, positions=None, kv_cache=None):
         if resid is None:

@@ -17,11 +17,13 @@ from .modules import Linear, Module, SwiGLU
 class SERMoE(Module):
     def __init__(self, d_model, d_ff, num_experts=8, top_k=2, num_shared_experts=0, capacity_factor=0.0,
                  aux_loss_coef=0.01, z_loss_coef=0.0, act="silu", renorm=True, dtype=None, device=None,
-                 init_std=0.02, ep_group=None):
+                 init_std=0.02, ep_group=None, expert_fp8=False):
         super().__init__()
         self.d_model, self.d_ff, self.E, self.k = d_model, d_ff, num_experts, top_k
         self.capacity_factor, self.aux_coef, self.z_coef = capacity_factor, aux_loss_coef, z_loss_coef
         self.act, self.renorm = act, renorm
+        # forward expert GEMMs in block-scaled fp8 (e4m3 data, 1 x 128 activation / 128 x 128 weight scales)
+        self.expert_fp8 = expert_fp8 and d_model % 128 == 0 and d_ff % 128 == 0
         self.router = Linear(d_model, num_experts, bias=False, dtype=dtype, device=device, init_std=init_std)
         self.ep_group = ep_group
         self.ep_world = 1
@@ -61,5 +63,5 @@ class SERMoE(Module):
             y = ep_experts_forward(self, x2, idx, w, base, plan=plan)
             return y.view(shape)
         base = self.shared(x2) if self.shared is not None else None
-        y = moe_ops.experts_forward(x2, idx, w, self.w1, self.w2, base, self.act)
+        y = moe_ops.experts_forward(x2, idx, w, self.w1, self.w2, base, self.act, fp8=self.expert_fp8)
         return y.view(shape)

@@ -382,6 +382,9 @@ class _CEFn(torch.autograd.Function):
 
 
 def cross_entropy(logits, target, ignore_index=-100):
+    from . import debug as _dbg
+    if _dbg.ENABLED:
+        _dbg.check_indices(target, 0, logits.shape[-1], _dbg.SITE_CE_TARGET, also_ok=ignore_index)
     if logits.is_cuda and logits.dtype in (torch.bfloat16, torch.float32) and _lib.available() and \
             logits.is_contiguous():
         return _CEFn.apply(logits, target, ignore_index)
@@ -446,6 +449,9 @@ class _LinearCEFn(torch.autograd.Function):
 
 def linear_cross_entropy(h, w, target, ignore_index=-100, chunk=2048):
     """Mean next-token CE of logits = h @ w^T, vocab-chunk fused on GPU."""
+    from . import debug as _dbg
+    if _dbg.ENABLED:
+        _dbg.check_indices(target, 0, w.shape[0], _dbg.SITE_CE_TARGET, also_ok=ignore_index)
     if _native(h) and w.shape[0] % 64 == 0 and h.shape[-1] % 64 == 0:
         return _LinearCEFn.apply(h, w, target, ignore_index, chunk)
     logits = F.linear(h, w)

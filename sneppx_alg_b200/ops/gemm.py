@@ -108,17 +108,28 @@ def gemm(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=None, c=None, beta
     b, N, Kb, ldb, sB = prep(b, b_mn)
     assert K == Kb, f"reduction mismatch {K} vs {Kb}"
     if K % 8 != 0 or lda % 8 != 0 or ldb % 8 != 0:
-        # TMA needs 16-byte row pitches. K-major operands of a plain GEMM are zero-padded along K to the next
-        # multiple of 8 (zeros add nothing to the sum) and run on the tensor-core kernel; layouts that cannot be
-        # padded that way are refused rather than quietly sent to a library GEMM.
-        if a_mn or b_mn or tile_group is not None or k_ranges is not None or a.dim() != 2 or b.dim() != 2:
+        # TMA needs 16-byte row pitches. A plain 2-D GEMM is zero-padded along K to the next multiple of 8 (zeros add
+        # nothing to the sum; a copy with a padded pitch also fixes an odd leading dimension) and runs on the
+        # tensor-core kernel; grouped / ranged / batched layouts that cannot be padded that way are refused rather
+        # than quietly sent to a library GEMM.
+        if tile_group is not None or k_ranges is not None or a.dim() != 2 or b.dim() != 2:
             raise ValueError(f"gemm: K={K}, lda={lda}, ldb={ldb} must be multiples of 8 elements for this layout; "
                              "pad the operands")
         Kp = (K + 7) // 8 * 8
-        a = torch.nn.functional.pad(a, (0, Kp - K))
-        b = torch.nn.functional.pad(b, (0, Kp - K))
-        return gemm(a, b, c=c, beta=beta, alpha=alpha, bias=bias, act=act, out=out, out_dtype=out_dtype,
-                    sm_limit=sm_limit, force_bn=force_bn)
+
+        def pad_k(t, mn_major):
+            # K is the row axis of an MN-major operand and the column axis of a K-major one
+            if mn_major:
+                cols = (t.shape[1] + 7) // 8 * 8
+                buf = torch.zeros(Kp, cols, dtype=t.dtype, device=t.device)
+                buf[: t.shape[0], : t.shape[1]] = t
+                return buf[:, : t.shape[1]]
+            buf = torch.zeros(t.shape[0], Kp, dtype=t.dtype, device=t.device)
+            buf[:, : t.shape[1]] = t
+            return buf
+
+        return gemm(pad_k(a, a_mn), pad_k(b, b_mn), a_mn=a_mn, b_mn=b_mn, c=c, beta=beta, alpha=alpha, bias=bias, act=act,
+                    out=out, out_dtype=out_dtype, sm_limit=sm_limit, force_bn=force_bn)
     batch = 1
     k_total = 0
     if k_ranges is not None:
@@ -138,6 +149,13 @@ def gemm(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=None, c=None, beta
         shape = (batch, M, N) if (batch > 1 or a.dim() == 3 or (b.dim() == 3 and tile_group is None) or
                                   k_ranges is not None) else (M, N)
         out = torch.empty(shape, dtype=odt, device=a.device)
+        from . import debug as _dbg
+        if _dbg.ENABLED and tile_group is None and k_ranges is None:
+            _dbg.poison_(out)      # debug-bounds mode: every element must be written by the kernel
+    if tile_group is not None:
+        from . import debug as _dbg
+        if _dbg.ENABLED:
+            _dbg.check_indices(tile_group, -1, b.shape[0], _dbg.SITE_TILE_GROUP)
     assert out.stride(-1) == 1
     ldd = out.stride(-2)
     sD = out.stride(0) if out.dim() == 3 else 0

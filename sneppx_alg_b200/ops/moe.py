@@ -101,6 +101,11 @@ class MoEPlan:
             _lib.call("sx_moe_plan", ptr(counts), ptr(idx.contiguous()), ptr(self.offsets), ptr(cursors),
                       ptr(self.tile_group), ptr(self.k_ranges), ptr(self.slot), ptr(self.row_token), c_int(T), c_int(E),
                       c_int(k), c_int(self.max_tiles), stream())
+            from . import debug as _dbg
+            if _dbg.ENABLED:     # the gather / combine kernels index rows with these
+                _dbg.check_indices(idx, 0, E, _dbg.SITE_TILE_GROUP)
+                _dbg.check_indices(self.slot, -1, self.max_rows, _dbg.SITE_MOE_SLOT)
+                _dbg.check_indices(self.tile_group, -1, E, _dbg.SITE_TILE_GROUP)
         else:
             e = idx.reshape(-1).long()
             ok = e >= 0
@@ -153,8 +158,12 @@ def _combine(ys, plan, w, base):
     return y.to(ys.dtype)
 
 
-def _grouped(a, w, plan, b_mn=False):
-    """Row block i of ``a`` times expert tile_group[i]'s matrix."""
+def _grouped(a, w, plan, b_mn=False, fp8=False):
+    """Row block i of ``a`` times expert tile_group[i]'s matrix. ``fp8``: both operands in block-scaled e4m3
+    (1 x 128 activation scales, 128 x 128 weight scales) on the fp8 tensor-core GEMM (forward GEMMs only)."""
+    if fp8 and not b_mn:
+        from .quant import gemm_fp8_grouped
+        return gemm_fp8_grouped(a, plan.tile_group, w)
     if _native(a):
         return gemm(a, w, tile_group=plan.tile_group, b_mn=b_mn)
     out_dim = w.shape[2] if b_mn else w.shape[1]
@@ -183,11 +192,11 @@ class _ExpertsFn(torch.autograd.Function):
     """y[t] = base[t] + sum_r w[t,r] * Expert_{idx[t,r]}(x[t]) with gated experts W1 [E, 2F, d], W2 [E, d, F]."""
 
     @staticmethod
-    def forward(ctx, x, w, W1, W2, base, plan, act):
+    def forward(ctx, x, w, W1, W2, base, plan, act, fp8=False):
         xs = _gather_rows(x, plan)
-        h1 = _grouped(xs, W1, plan)
+        h1 = _grouped(xs, W1, plan, fp8=fp8)
         hm = glu(h1, act) if _native(h1) else glu_reference(h1, act)
-        ys = _grouped(hm, W2, plan)
+        ys = _grouped(hm, W2, plan, fp8=fp8)
         y = _combine(ys, plan, w, base)
         ctx.save_for_backward(xs, h1, hm, ys, w, W1, W2)
         ctx.plan, ctx.act, ctx.has_base = plan, act, base is not None
@@ -238,13 +247,14 @@ class _ExpertsFn(torch.autograd.Function):
             W._main_grad_written = True
             return None
 
-        return dx, dw, deliver(W1, dW1), deliver(W2, dW2), (dy if ctx.has_base else None), None, None
+        return dx, dw, deliver(W1, dW1), deliver(W2, dW2), (dy if ctx.has_base else None), None, None, None
 
 
-def experts_forward(x, idx, w, W1, W2, base=None, act="silu"):
-    """x [T, d]; idx int32 [T, k] (-1 = dropped); w fp32 [T, k]; returns [T, d]."""
+def experts_forward(x, idx, w, W1, W2, base=None, act="silu", fp8=False):
+    """x [T, d]; idx int32 [T, k] (-1 = dropped); w fp32 [T, k]; returns [T, d]. ``fp8``: the two forward expert GEMMs
+    run in block-scaled e4m3 (the backward GEMMs stay bf16 on the saved bf16 activations: straight-through)."""
     plan = MoEPlan(idx, W1.shape[0])
-    return _ExpertsFn.apply(x, w, W1, W2, base, plan, act)
+    return _ExpertsFn.apply(x, w, W1, W2, base, plan, act, fp8)
 
 
 def moe_reference(x, idx, w, W1, W2, base=None, act="silu"):

@@ -27,6 +27,9 @@ def kv_append_reference(qkv, cos, sin, pos, slot, k_cache, v_cache, Hq, Hkv, D, 
 def kv_append_(qkv, cos, sin, pos, slot, k_cache, v_cache, Hq, Hkv, D, rotate=True):
     """In place: rotate Q and K rows of ``qkv`` [T, (Hq+2Hkv)*D] and scatter K/V into the block pool at ``slot``."""
     if qkv.is_cuda and qkv.dtype == torch.bfloat16 and _lib.available():
+        from . import debug as _dbg
+        if _dbg.ENABLED:
+            _dbg.check_indices(slot, -1, k_cache.shape[0] * k_cache.shape[1], _dbg.SITE_KV_SLOT)
         _lib.call("sx_kv_append", ptr(qkv), c_ll(qkv.stride(0)), ptr(cos), ptr(sin), ptr(pos.to(torch.int32)),
                   ptr(slot.to(torch.int32)), ptr(k_cache), ptr(v_cache), c_int(qkv.shape[0]), c_int(Hq), c_int(Hkv),
                   c_int(D), c_int(int(rotate)), stream())
@@ -58,9 +61,14 @@ def paged_decode(q, k_cache, v_cache, block_table, seq_lens, scale=None):
     scale = scale or 1.0 / math.sqrt(D)
     if q.is_cuda and q.dtype == torch.bfloat16 and _lib.available() and D in (64, 128) and Hq // Hkv <= 8:
         q = q if q.stride(2) == 1 and q.stride(1) == D else q.contiguous()
+        from . import debug as _dbg
+        if _dbg.ENABLED:
+            _dbg.check_indices(block_table, 0, k_cache.shape[0], _dbg.SITE_BLOCK_TABLE)
         max_len = block_table.shape[1] * bs
         ns = _lib.lib().sx_paged_decode_splits2(c_int(max_len), c_int(B * Hkv))
         out = torch.empty(B, Hq, D, dtype=q.dtype, device=q.device)
+        if _dbg.ENABLED:
+            _dbg.poison_(out)
         o_part = torch.empty(B * Hq * ns * D, dtype=torch.float32, device=q.device)
         ml = torch.empty(B * Hq * ns * 2, dtype=torch.float32, device=q.device)
         _lib.call("sx_paged_decode", ptr(q), c_ll(q.stride(0)), ptr(k_cache), ptr(v_cache),

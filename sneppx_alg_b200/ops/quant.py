@@ -157,6 +157,44 @@ def gemm_fp8(x, wq, sw, bias=None, xq=None, sx=None):
     return gemm_fp8_reference(xq, sx, wq, sw, bias).view(*lead, N)
 
 
+def gemm_fp8_grouped_reference(x, tile_group, W):
+    """Oracle of ``gemm_fp8_grouped``: both operands rounded to block-scaled e4m3 (1 x 128 rows of ``x``, 128 x 128
+    blocks of each expert's matrix), de-quantised to fp32, multiplied per 128-row tile with the tile's expert."""
+    E, N, K = W.shape
+    xq, sx = quant_fp8_1x128_reference(x.reshape(-1, K))
+    wq, sw = quant_fp8_128x128_reference(W.reshape(E * N, K))
+    xd = dequant_fp8(xq, sx, "1x128", torch.float32)
+    wd = dequant_fp8(wq, sw, "128x128", torch.float32).view(E, N, K)
+    out = torch.zeros(x.shape[0], N, dtype=torch.float32, device=x.device)
+    tg = tile_group.tolist()
+    for t, e in enumerate(tg[: x.shape[0] // 128]):
+        if e >= 0:
+            out[t * 128:(t + 1) * 128] = xd[t * 128:(t + 1) * 128] @ wd[e].t()
+    return out.to(x.dtype)
+
+
+def gemm_fp8_grouped(x, tile_group, W, wq=None, sw=None):
+    """Expert-sorted rows ``x`` [rows, K] (bf16, segments padded to 128 rows) times the stacked expert matrices
+    ``W`` [E, N, K], tile t using expert ``tile_group[t]`` (-1: output rows zero), with both operands in
+    block-scaled e4m3 on the fp8 tensor-core path (G2 in fp8). ``wq`` / ``sw`` may carry the experts already
+    quantised (``quant_fp8_128x128`` of ``W.view(E * N, K)``). N and K must be multiples of 128."""
+    E, N, K = W.shape
+    rows = x.shape[0]
+    if not (x.is_cuda and x.dtype == torch.bfloat16 and _lib.available()):
+        return gemm_fp8_grouped_reference(x, tile_group, W)
+    if N % 128 or K % 128 or rows % 128:
+        raise ValueError(f"gemm_fp8_grouped: rows {rows}, N {N}, K {K} must be multiples of 128")
+    xq, sx = quant_fp8_1x128(x)
+    if wq is None:
+        wq, sw = quant_fp8_128x128(W.reshape(E * N, K))
+    out = torch.empty(rows, N, dtype=torch.bfloat16, device=x.device)
+    xq_, wq_ = xq.view(torch.uint8), wq.view(torch.uint8)
+    _lib.call("sx_gemm_fp8_grouped", ptr(xq_), c_ll(xq_.stride(0)), ptr(sx.contiguous()), ptr(wq_), c_ll(wq_.stride(0)),
+              ptr(sw.contiguous()), ptr(tile_group), c_int(E), ptr(out), c_ll(out.stride(0)), c_int(rows), c_int(N),
+              c_int(K), ptr(_lib.status_word(x.device)), stream())
+    return out
+
+
 def gemm_dequant(x, qweight, scales, mode="fp8", bias=None):
     """y = x @ dequant(W)^T. x bf16 [.., K]; mode 'fp8': qweight float8_e4m3fn/uint8 [N, K], scales [N/128, K/128];
     mode 'int4': qweight uint8 [N, K/2], scales [N, K/128]. CUDA: weights are expanded to bf16 inside the GEMM."""

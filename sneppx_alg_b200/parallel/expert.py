@@ -88,6 +88,11 @@ class EPPlan:
                   _lib.ptr(self.expected_a), _lib.ptr(self.total_rows), C.c_int(ws.max_tiles), _lib.ptr(self.dest_rank),
                   _lib.ptr(self.dest_row), _lib.ptr(ws.dropped), ws.status(), _lib.stream())
         self.valid = self.expected_a - prev       # rows that will arrive per tile for this routing
+        from ..ops import debug as _dbg
+        if _dbg.ENABLED:     # the dispatch pushes rows to (dest_rank, dest_row) of a peer's buffer
+            _dbg.check_indices(self.dest_rank, -1, ws.world, _dbg.SITE_EP_RANK)
+            _dbg.check_indices(self.dest_row, 0, ws.max_rows, _dbg.SITE_EP_ROW)
+            _dbg.check_indices(self.tile_group, -1, ws.E_local, _dbg.SITE_TILE_GROUP)
         self._rows = None if ws.nodrop else ws.max_rows
         if ws.nodrop:
             # rows this rank's experts receive for this routing: read back behind an event that waits for the plan
@@ -158,12 +163,16 @@ def _combine(ws, plan, w, base, dy, want_y=True, want_dw=False):
 
 class _EPExpertsFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, W1, W2, base, ws, plan, act):
+    def forward(ctx, x, w, W1, W2, base, ws, plan, act, fp8=False):
         h1, xs_view = _dispatch_gemm(ws, plan, x, W1, ws.rows_a, ws.arrive_a, plan.expected_a, None, False)
         xs = xs_view.clone()
         hm = glu(h1, act)
         out_view = ws.out.tensor[: plan.rows * ws.d].view(plan.rows, ws.d)
-        gemm(hm, W2, tile_group=plan.tile_group, out=out_view)
+        if fp8:       # second expert GEMM in block-scaled e4m3 (the first is fused with the dispatch in bf16)
+            from ..ops.quant import gemm_fp8_grouped
+            out_view.copy_(gemm_fp8_grouped(hm, plan.tile_group, W2))
+        else:
+            gemm(hm, W2, tile_group=plan.tile_group, out=out_view)
         y, _ = _combine(ws, plan, w, base, None)
         ctx.save_for_backward(xs, h1, hm, w, W1, W2)
         ctx.ws, ctx.plan, ctx.act, ctx.has_base = ws, plan, act, base is not None
@@ -202,7 +211,7 @@ class _EPExpertsFn(torch.autograd.Function):
             W._main_grad_written = True
             return None
 
-        return dx, dw, deliver(W1, dW1), deliver(W2, dW2), (dy if ctx.has_base else None), None, None, None
+        return dx, dw, deliver(W1, dW1), deliver(W2, dW2), (dy if ctx.has_base else None), None, None, None, None
 
 
 def _library_forward(layer, x, idx, w, base):
@@ -228,7 +237,8 @@ def _library_forward(layer, x, idx, w, base):
     recv_e = torch.empty(sum(rc), dtype=torch.int64, device=x.device)
     dist.all_to_all_single(recv_e, send_e, rc, sc, group=group)
     ones = torch.ones(recv_x.shape[0], 1, dtype=torch.float32, device=x.device)
-    ys = moe_ops.experts_forward(recv_x, recv_e.to(torch.int32).view(-1, 1), ones, layer.w1, layer.w2, None, layer.act)
+    ys = moe_ops.experts_forward(recv_x, recv_e.to(torch.int32).view(-1, 1), ones, layer.w1, layer.w2, None, layer.act,
+                                 fp8=getattr(layer, "expert_fp8", False))
     back = dfn.all_to_all_single(torch.empty(sum(sc), d, dtype=x.dtype, device=x.device), ys, sc, rc, group=group)
     contrib = back.float() * w.reshape(-1)[order].unsqueeze(1)
     y = torch.zeros(T, d, dtype=torch.float32, device=x.device).index_add(0, tok, contrib)
@@ -256,8 +266,10 @@ def policy_name() -> str:
     return "no-drop" if not os.environ.get("SX_EP_CAPACITY") else f"capacity factor {os.environ['SX_EP_CAPACITY']}"
 
 
-def expert_dtype_name() -> str:
-    return "bf16"
+def expert_dtype_name(model=None) -> str:
+    fp8 = model is not None and any(getattr(m, "expert_fp8", False) for m in model.modules())
+    return ("fp8 e4m3 1x128/128x128 forward for the second expert GEMM (the first is fused with the bf16 dispatch), "
+            "bf16 backward") if fp8 else "bf16"
 
 
 FORCE_FUSED = None     # tests set True / False to pin the path of every layer; None: fused for CUDA bf16 tensors
@@ -295,4 +307,4 @@ def ep_experts_forward(layer, x, idx, w, base, fused=None, plan=None):
     ws = _workspace(layer, x, idx)
     if plan is None:
         plan = EPPlan(ws, idx)
-    return _EPExpertsFn.apply(x, w, layer.w1, layer.w2, base, ws, plan, layer.act)
+    return _EPExpertsFn.apply(x, w, layer.w1, layer.w2, base, ws, plan, layer.act, getattr(layer, "expert_fp8", False))

@@ -39,17 +39,32 @@ class SxZeroArgs(C.Structure):
     ]
 
 
-class SymmBuffer:
-    """One symmetric allocation: ``tensor`` is the local view, ``ptrs[r]`` rank r's mapping of the same range."""
+GUARD_BYTES = 256          # canary zone on each side of a symmetric buffer in debug-bounds mode
+CANARY = 0x5A
 
-    def __init__(self, tensor, handle):
+
+class SymmBuffer:
+    """One symmetric allocation: ``tensor`` is the local view, ``ptrs[r]`` rank r's mapping of the same range.
+    With ``guard`` > 0 the allocation carries that many canary bytes before and after the usable range (the
+    pointers and the tensor already point past the leading guard)."""
+
+    def __init__(self, tensor, handle, guard: int = 0, raw=None):
         self.tensor = tensor
         self.handle = handle
-        self.ptrs = [int(p) for p in handle.buffer_ptrs]
+        self.guard, self.raw = guard, raw
+        self.ptrs = [int(p) + guard for p in handle.buffer_ptrs]
         try:
-            self.multicast_ptr = int(handle.multicast_ptr) if handle.has_multicast_support else 0
+            self.multicast_ptr = (int(handle.multicast_ptr) + guard) if handle.has_multicast_support else 0
         except Exception:  # noqa: BLE001
             self.multicast_ptr = 0
+
+    def canaries_intact(self) -> bool:
+        """True when no kernel (local or a peer's) wrote into the guard zones around this buffer."""
+        if not self.guard:
+            return True
+        b = self.raw.view(torch.uint8)
+        g = self.guard
+        return bool((b[:g] == CANARY).all()) and bool((b[-g:] == CANARY).all())
 
 
 class SymmGroup:
@@ -62,6 +77,7 @@ class SymmGroup:
         assert self.world <= 8, "one NVSwitch domain (<= 8 GPUs) per symmetric group"
         self.device = torch.device("cuda", torch.cuda.current_device())
         self.timeout_ns = int(timeout_s * 1e9)
+        self._buffers = []
         try:
             symm_mem.enable_symm_mem_for_group(self.group.group_name)
         except Exception:  # noqa: BLE001  (newer torch enables groups implicitly)
@@ -73,9 +89,29 @@ class SymmGroup:
         self._epochs = {}
 
     def alloc(self, numel: int, dtype) -> SymmBuffer:
+        from ..ops import debug as _dbg
+        if _dbg.ENABLED:
+            # debug-bounds mode: guard zones of canary bytes around every peer-mapped buffer
+            es = torch.empty(0, dtype=dtype).element_size()
+            ge = GUARD_BYTES // es
+            raw = self._sm.empty(numel + 2 * ge, dtype=dtype, device=self.device)
+            h = self._sm.rendezvous(raw, group=self.group)
+            raw.view(torch.uint8)[:GUARD_BYTES].fill_(CANARY)
+            raw.view(torch.uint8)[-GUARD_BYTES:].fill_(CANARY)
+            buf = SymmBuffer(raw[ge: ge + numel], h, guard=GUARD_BYTES, raw=raw)
+            self._buffers.append(buf)
+            return buf
         t = self._sm.empty(numel, dtype=dtype, device=self.device)
         h = self._sm.rendezvous(t, group=self.group)
         return SymmBuffer(t, h)
+
+    def check_canaries(self) -> None:
+        """Debug-bounds mode: raise if any symmetric buffer's guard zone was overwritten."""
+        torch.cuda.synchronize()
+        for i, b in enumerate(self._buffers):
+            if not b.canaries_intact():
+                from ..ops.debug import KernelBoundsError
+                raise KernelBoundsError(f"symmetric buffer {i} ({b.tensor.numel()} x {b.tensor.dtype}): guard zone overwritten")
 
     def next_epoch(self, channel: int) -> int:
         e = self._epochs.get(channel, 0) + 1

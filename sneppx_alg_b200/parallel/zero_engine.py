@@ -172,8 +172,8 @@ class ZeroEngine:
             self.norm_out = torch.zeros(4, dtype=torch.float32, device=dev)
             if self.nvls and not (self._symm["grad"].multicast_ptr and self._symm["param"].multicast_ptr):
                 self.nvls = False          # no multicast mapping on this system: peer loads
-            if self.nvls and comm_grid == 0:
-                self.grid = 64             # one in-switch reduction per 16 bytes: few CTAs keep the links busy
+            if self.nvls and comm_grid == 0 and os.environ.get("SX_ZERO_NVLS_GRID"):
+                self.grid = int(os.environ["SX_ZERO_NVLS_GRID"])
                 self.partials = torch.zeros(len(self.bounds) * self.grid + 1, dtype=torch.float32, device=dev)
             self.comm_stream = torch.cuda.Stream(device=dev)
             self.gather_events = [None] * len(self.bounds)

@@ -105,18 +105,31 @@ class LlamaPagedRunner:
         h = self._layers(m.embedding(ids).unsqueeze(0), attn)
         return ops.linear(h[:, -1], m.head_weight()).float()
 
-    @torch.no_grad()
-    def decode(self, seq_ids: List[int], last_tokens: List[int]):
-        """One token for each running sequence; returns logits [B, V]."""
+    # ------------------------------------------------------------------ decode
+    def enable_graphs(self, max_batch: int, max_len: int):
+        """Capture the decode step into CUDA graphs, one per batch-size bucket (1, 2, 4, .. max_batch): a decode step
+        is some 300 small launches for a few microseconds of work each, so replaying one graph instead of launching
+        them from Python removes most of the step time. Inputs live in one static int32 buffer (token ids, positions,
+        KV slots, sequence lengths, block table of ``max_len`` tokens per sequence) filled with a single host -> device
+        copy per step; padding rows have slot -1 and length 0 and touch nothing."""
+        dev = self.model.embedding.weight.device
+        if dev.type != "cuda":
+            return
+        bs = self.cache.block_size
+        self._g_max_blocks = (max_len + bs - 1) // bs
+        self._g_max_len = self._g_max_blocks * bs
+        self._g_buckets = []
+        b = 1
+        while b < max_batch:
+            self._g_buckets.append(b)
+            b *= 2
+        self._g_buckets.append(max_batch)
+        self._graphs = {}
+        self.model.rope(dev, self._g_max_len)
+
+    def _decode_body(self, B, ids, pos, slots, bt, lens):
         m, H, Hk, D = self.model, self.H, self.Hk, self.D
-        dev = m.embedding.weight.device
-        B = len(seq_ids)
-        pos_list = [self.cache.lens[s] for s in seq_ids]
-        slots = torch.tensor([self.cache.reserve(s, 1)[0] for s in seq_ids], dtype=torch.int32, device=dev)
-        pos = torch.tensor(pos_list, dtype=torch.int32, device=dev)
-        bt, lens = self.cache.block_table_tensor(seq_ids, dev)
-        cos, sin = m.rope(dev, max(pos_list) + 1)
-        ids = torch.tensor(last_tokens, dtype=torch.long, device=dev)
+        cos, sin = m.rope(ids.device, self._g_max_len if getattr(self, "_graphs", None) is not None else int(pos.max()) + 1)
 
         def attn(li, qkv):
             q2 = qkv.view(B, (H + 2 * Hk) * D)
@@ -126,6 +139,68 @@ class LlamaPagedRunner:
 
         h = self._layers(m.embedding(ids).unsqueeze(1), attn)
         return ops.linear(h[:, -1], m.head_weight()).float()
+
+    def _graph_for(self, Bb):
+        g = self._graphs.get(Bb)
+        if g is not None:
+            return g
+        dev = self.model.embedding.weight.device
+        mb = self._g_max_blocks
+        n = 4 * Bb + Bb * mb
+        host = torch.zeros(n, dtype=torch.int32).pin_memory()
+        buf = torch.zeros(n, dtype=torch.int32, device=dev)
+        views = dict(ids=buf[:Bb], pos=buf[Bb:2 * Bb], slots=buf[2 * Bb:3 * Bb], lens=buf[3 * Bb:4 * Bb],
+                     bt=buf[4 * Bb:].view(Bb, mb))
+        # warm-up outside the graph with rows that write nothing (slot -1, length 0), then capture
+        buf[2 * Bb:3 * Bb].fill_(-1)
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                self._decode_body(Bb, views["ids"], views["pos"], views["slots"], views["bt"], views["lens"])
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            out = self._decode_body(Bb, views["ids"], views["pos"], views["slots"], views["bt"], views["lens"])
+        g = self._graphs[Bb] = dict(graph=graph, host=host, buf=buf, out=out, hv=host.numpy())
+        return g
+
+    @torch.no_grad()
+    def decode(self, seq_ids: List[int], last_tokens: List[int]):
+        """One token for each running sequence; returns logits [B, V]."""
+        m = self.model
+        dev = m.embedding.weight.device
+        B = len(seq_ids)
+        pos_list = [self.cache.lens[s] for s in seq_ids]
+        slot_list = [self.cache.reserve(s, 1)[0] for s in seq_ids]
+        graphs = getattr(self, "_graphs", None)
+        if graphs is not None and B <= self._g_buckets[-1] and max(pos_list) + 1 <= self._g_max_len:
+            Bb = next(b for b in self._g_buckets if b >= B)
+            g = self._graph_for(Bb)
+            hv, mb = g["hv"], self._g_max_blocks
+            hv[:4 * Bb] = 0
+            hv[2 * Bb:3 * Bb] = -1
+            hv[:B] = last_tokens
+            hv[Bb:Bb + B] = pos_list
+            hv[2 * Bb:2 * Bb + B] = slot_list
+            hv[3 * Bb:3 * Bb + B] = [p + 1 for p in pos_list]
+            bt = hv[4 * Bb:].reshape(Bb, mb)
+            for i, s in enumerate(seq_ids):
+                t = self.cache.tables[s]
+                bt[i, :len(t)] = t
+            g["buf"].copy_(g["host"], non_blocking=True)
+            g["graph"].replay()
+            return g["out"][:B]
+        slots = torch.tensor(slot_list, dtype=torch.int32, device=dev)
+        pos = torch.tensor(pos_list, dtype=torch.int32, device=dev)
+        bt, lens = self.cache.block_table_tensor(seq_ids, dev)
+        ids = torch.tensor(last_tokens, dtype=torch.long, device=dev)
+        saved, self._graphs = graphs, None          # eager step: rope tables sized by the longest sequence
+        try:
+            return self._decode_body(B, ids, pos, slots, bt, lens)
+        finally:
+            self._graphs = saved
 
 
 class TPLlamaPagedRunner(LlamaPagedRunner):
@@ -252,7 +327,8 @@ class StatefulRunner:
 
 class LLMEngine:
     def __init__(self, model, num_blocks=2048, block_size=16, max_batch_size=32, max_prefill_tokens=8192,
-                 policy="fcfs", enable_prefix_cache=True, runner=None, tp_group=None):
+                 policy="fcfs", enable_prefix_cache=True, runner=None, tp_group=None, cuda_graphs=True,
+                 max_model_len=None):
         cfg = model.config
         p = next(model.parameters())
         if runner is None and getattr(cfg, "architecture", "transformer") == "mamba2":
@@ -269,6 +345,10 @@ class LLMEngine:
             self.cache = PagedKVCache(cfg.num_hidden_layers, num_blocks, block_size, cfg.num_key_value_heads, cfg.head_dim,
                                       dtype=p.dtype, device=p.device, enable_prefix_cache=enable_prefix_cache)
         self.runner = runner or LlamaPagedRunner(model, self.cache)
+        # CUDA-graph decode on one GPU (the tensor-parallel runner's collectives stay outside graphs)
+        if cuda_graphs and p.is_cuda and type(self.runner) is LlamaPagedRunner:
+            limit = max_model_len or min(getattr(cfg, "max_position_embeddings", 4096) or 4096, num_blocks * block_size)
+            self.runner.enable_graphs(max_batch_size, limit)
         self.max_batch_size, self.max_prefill_tokens, self.policy = max_batch_size, max_prefill_tokens, policy
         self.waiting: List[Request] = []
         self.running: Dict[int, Request] = {}

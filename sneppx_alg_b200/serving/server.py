@@ -38,6 +38,7 @@ class EngineWorker:
         self.engine = engine
         self._lock = threading.Lock()
         self._events: Dict[int, threading.Event] = {}
+        self._callbacks: Dict[int, object] = {}
         self._stop = False
         self.thread = threading.Thread(target=self._loop, daemon=True)
         self.thread.start()
@@ -51,14 +52,21 @@ class EngineWorker:
                     for rid in list(self._events):
                         if rid in self.engine.finished:
                             self._events.pop(rid).set()
+                            cb = self._callbacks.pop(rid, None)
+                            if cb is not None:
+                                cb()
             if not work:
                 time.sleep(0.001)
 
-    def submit(self, prompt_ids, params, on_token=None):
+    def submit(self, prompt_ids, params, on_token=None, on_done=None):
+        """``on_done``: called (on the engine thread) when the request has finished; lets an event loop await the
+        result without parking a thread per request."""
         ev = threading.Event()
         with self._lock:
             rid = self.engine.submit(prompt_ids, params, on_token=on_token)
             self._events[rid] = ev
+            if on_done is not None:
+                self._callbacks[rid] = on_done
         return rid, ev
 
     def result(self, rid):
@@ -92,7 +100,8 @@ def create_app(models: Dict[str, dict], default_model: Optional[str] = None, api
     app.state.workers, app.state.metrics, app.state.control = workers, metrics, control
 
     class GenerateRequest(BaseModel):
-        prompt: str
+        prompt: str = ""
+        prompt_token_ids: Optional[List[int]] = None      # already tokenised prompt (takes precedence over `prompt`)
         max_new_tokens: int = Field(64, ge=1, le=4096)
         do_sample: bool = False
         temperature: float = 1.0
@@ -135,20 +144,32 @@ def create_app(models: Dict[str, dict], default_model: Optional[str] = None, api
         return SamplingParams(max_new_tokens=r.max_new_tokens, do_sample=r.do_sample, temperature=r.temperature,
                               top_k=r.top_k, top_p=r.top_p, repetition_penalty=getattr(r, "repetition_penalty", 1.0))
 
-    async def run_one(mid: str, prompt: str, sp: SamplingParams, stop_strings=None):
+    async def run_one(mid: str, prompt: str, sp: SamplingParams, stop_strings=None, token_ids=None):
         if mid not in workers:
             raise HTTPException(404, f"unknown model '{mid}'")
         if stop_strings:
             from .generation import make_stop_fn
             sp.stop_fn = make_stop_fn(toks[mid], stop_strings)
-        chk = prompt_filter.check(prompt)
-        if not chk.allowed:
-            raise HTTPException(400, {"error": "prompt rejected", "reasons": chk.reasons})
         t0 = time.perf_counter()
-        ids = toks[mid].encode(chk.sanitized)
-        rid, ev = workers[mid].submit(ids, sp)
-        await asyncio.get_running_loop().run_in_executor(None, ev.wait)
+        if token_ids is not None:
+            vocab = models[mid]["model"].config.vocab_size
+            if not token_ids or any((not isinstance(t, int)) or t < 0 or t >= vocab for t in token_ids):
+                raise HTTPException(400, {"error": "prompt_token_ids must be non-empty ids inside the vocabulary"})
+            ids = list(token_ids)
+        else:
+            chk = prompt_filter.check(prompt)
+            if not chk.allowed:
+                raise HTTPException(400, {"error": "prompt rejected", "reasons": chk.reasons})
+            ids = toks[mid].encode(chk.sanitized)
+        loop = asyncio.get_running_loop()
+        done = loop.create_future()
+        rid, ev = workers[mid].submit(ids, sp, on_done=lambda: loop.call_soon_threadsafe(
+            lambda: done.done() or done.set_result(None)))
+        await done
+        why = workers[mid].engine.failed.pop(rid, None)
         req = workers[mid].result(rid)
+        if why is not None:
+            raise HTTPException(413, {"error": why})
         text = toks[mid].decode(req.output)
         if stop_strings:
             from .generation import truncate_at_stop
@@ -158,7 +179,8 @@ def create_app(models: Dict[str, dict], default_model: Optional[str] = None, api
                        (req.first_token_time - req.arrival) if req.first_token_time else None)
         return {"generated_text": text, "token_ids": req.output, "prompt_tokens": len(ids),
                 "completion_tokens": len(req.output), "total_tokens": len(ids) + len(req.output), "model": mid,
-                "created": int(time.time())}
+                "created": int(time.time()),
+                "ttft_s": (req.first_token_time - req.arrival) if req.first_token_time else None}
 
     @app.get("/v1/health")
     def health():
@@ -218,7 +240,7 @@ def create_app(models: Dict[str, dict], default_model: Optional[str] = None, api
     @app.post("/v1/generate")
     async def generate_ep(r: GenerateRequest, authorization: Optional[str] = Header(None)):
         auth(authorization)
-        return await run_one(r.model or default_model, r.prompt, params_of(r), r.stop_strings)
+        return await run_one(r.model or default_model, r.prompt, params_of(r), r.stop_strings, r.prompt_token_ids)
 
     @app.post("/v1/generate/batch")
     async def generate_batch(r: BatchRequest, authorization: Optional[str] = Header(None)):

@@ -21,12 +21,13 @@ def main():
     dev = torch.device("cuda", torch.cuda.current_device())
     dist.init_process_group("nccl", device_id=dev)
     stage = int(sys.argv[1]) if len(sys.argv) > 1 else 3
+    nvls = len(sys.argv) > 2 and sys.argv[2] == "nvls"      # in-switch reduction / multicast stores instead of peer loads
     cfg = ModelConfig(hidden_size=512, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2,
                       intermediate_size=1024, vocab_size=2048, max_position_embeddings=256, rms_norm_eps=1e-5)
     torch.manual_seed(0)
     base = build_model(cfg, dtype=torch.bfloat16, device=dev)
     lib_model = copy.deepcopy(base)
-    fused = ZeroEngine(base, zero_stage=stage, lr=1e-3, fused=True)
+    fused = ZeroEngine(base, zero_stage=stage, lr=1e-3, fused=True, nvls=nvls)
     oracle = copy.deepcopy(lib_model).float()
     lib = ZeroEngine(lib_model, zero_stage=stage, lr=1e-3, fused=False)
     opt = torch.optim.AdamW(oracle.parameters(), lr=1e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
@@ -62,7 +63,8 @@ def main():
     t = torch.tensor([int(ok)], device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MIN)
     if rank == 0:
-        print(f"zero stage {stage} world {world}: vs fp32 oracle loss diff {worst_o:.4f} param rel {rel_o:.2e} norm rel "
+        print(f"zero stage {stage} world {world} ({'NVLS multimem' if fused.nvls else 'peer loads'}"
+              f"{', NVLS asked for but no multicast mapping' if nvls and not fused.nvls else ''}): vs fp32 oracle loss diff {worst_o:.4f} param rel {rel_o:.2e} norm rel "
               f"{worst_n:.2e}; vs library loss diff {worst:.4f} param rel {rel:.2e} norm {nf:.4f}/{nl:.4f} ->",
               "OK" if t.item() else "MISMATCH")
     dist.destroy_process_group()

@@ -84,3 +84,47 @@ def test_arc_step_kernels():
     sm = aux.arc_step("smooth", x0, eps=0.25, seed=9, offset=1)
     assert torch.allclose(sm, aux.arc_step_reference("smooth", x0, eps=0.25, seed=9, offset=1), atol=2e-3)
 
+
+
+def test_debug_bounds_mode_catches_bad_indices_without_faulting():
+    """Debug-bounds mode: an out-of-range index is reported by the checking kernel (nothing faults, the context stays
+    usable), poisoned outputs come back fully written, and a clean run records nothing."""
+    from sneppx_alg_b200.ops import debug, moe
+    from sneppx_alg_b200.ops import gemm as gemm_mod
+    debug.enable(True)
+    try:
+        assert debug.read_record() is None
+        torch.manual_seed(0)
+        # clean run through the MoE plan / grouped GEMM / paged path: no record, no NaN left in outputs
+        T, d, E, k, Fd = 300, 128, 4, 2, 64
+        x = torch.randn(T, d, device="cuda", dtype=torch.bfloat16)
+        idx, w, _, _ = moe.route(torch.randn(T, E, device="cuda"), k)
+        W1 = (0.05 * torch.randn(E, 2 * Fd, d, device="cuda")).to(torch.bfloat16)
+        W2 = (0.05 * torch.randn(E, d, Fd, device="cuda")).to(torch.bfloat16)
+        y = moe.experts_forward(x, idx, w, W1, W2)
+        a = torch.randn(256, 128, device="cuda", dtype=torch.bfloat16)
+        b = torch.randn(192, 128, device="cuda", dtype=torch.bfloat16)
+        c = gemm_mod.gemm(a, b)
+        debug.check()
+        assert not torch.isnan(y.float()).any() and not torch.isnan(c.float()).any()
+        # a bad expert index is caught before any kernel indexes with it
+        bad = idx.clone()
+        bad[7, 1] = E + 3
+        debug.check_indices(bad, 0, E, debug.SITE_TILE_GROUP)
+        with pytest.raises(debug.KernelBoundsError, match="element 15 is 7"):
+            debug.check()
+        assert debug.read_record() is None                     # cleared; the context still works
+        tgt = torch.randint(0, 50, (64,), device="cuda")
+        tgt[3] = -100
+        debug.check_indices(tgt, 0, 50, debug.SITE_CE_TARGET, also_ok=-100)
+        debug.check()
+        tgt[5] = 50
+        debug.check_indices(tgt, 0, 50, debug.SITE_CE_TARGET, also_ok=-100)
+        with pytest.raises(debug.KernelBoundsError, match="cross-entropy target"):
+            debug.check()
+        p = torch.empty(1000, device="cuda", dtype=torch.bfloat16)
+        debug.poison_(p)
+        assert torch.isnan(p.float()).all()
+        assert float((a.float() @ b.float().t()).sum()) == float((a.float() @ b.float().t()).sum())
+    finally:
+        debug.enable(False)

@@ -231,3 +231,38 @@ def test_quantized_linear_all_input_sizes(mode, rows):
     assert y.shape == (2, rows // 2, 384)
     # the fp8 x fp8 path also rounds the activations to e4m3 (3 mantissa bits)
     assert _rel(y, ref) < (6e-2 if (mode == "fp8" and rows <= 256) else 2e-2)
+
+
+def test_grouped_fp8_expert_gemm_and_fp8_moe_layer():
+    """Grouped block-scaled fp8 GEMM (expert-sorted rows x stacked expert matrices) against the fp32 product of the
+    de-quantised operands; then the SER layer with fp8 forward expert GEMMs against the fp32 dense oracle."""
+    from sneppx_alg_b200.ops import quant
+    torch.manual_seed(0)
+    E, N, K = 5, 384, 512
+    groups = [0, 0, 3, -1, 4, 1, 1, 1, -1]
+    tg = torch.tensor(groups, dtype=torch.int32, device="cuda")
+    rows = 128 * len(groups)
+    x = torch.randn(rows, K, device="cuda", dtype=torch.bfloat16)
+    W = (torch.randn(E, N, K, device="cuda") * 0.05).to(torch.bfloat16)
+    y = quant.gemm_fp8_grouped(x, tg, W)
+    ref = quant.gemm_fp8_grouped_reference(x.float(), tg, W.float())
+    assert (y.float() - ref.float()).abs().max() / ref.float().abs().max() < 1e-2
+    for t, e in enumerate(groups):       # unused tiles are zero, used ones are not
+        blk = y[t * 128:(t + 1) * 128].float().abs().max().item()
+        assert (blk == 0.0) == (e < 0)
+    ops.check_status()
+    T, d, Ex, k, Fd = 1000, 256, 8, 2, 128
+    xx = torch.randn(T, d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    idx, w, _, _ = moe.route(torch.randn(T, Ex, device="cuda"), k)
+    W1 = (0.05 * torch.randn(Ex, 2 * Fd, d, device="cuda")).to(torch.bfloat16).requires_grad_(True)
+    W2 = (0.05 * torch.randn(Ex, d, Fd, device="cuda")).to(torch.bfloat16).requires_grad_(True)
+    w = w.detach().requires_grad_(True)
+    yy = moe.experts_forward(xx, idx, w, W1, W2, fp8=True)
+    g = torch.randn_like(yy)
+    yy.backward(g)
+    ops.check_status()
+    xr, wr, W1r, W2r = [t.detach().float().requires_grad_(True) for t in (xx, w, W1, W2)]
+    yr = moe.moe_reference(xr, idx, wr, W1r, W2r)
+    yr.backward(g.float())
+    assert _rel(yy, yr) < 8e-2                       # e4m3 rounding of both operands of both GEMMs
+    assert _rel(xx.grad, xr.grad) < 8e-2 and _rel(W1.grad, W1r.grad) < 8e-2 and _rel(W2.grad, W2r.grad) < 8e-2

@@ -10,13 +10,13 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-@pytest.mark.parametrize("stage", [1, 3])
-def test_fused_zero_two_gpus(stage):
+@pytest.mark.parametrize("stage,mode", [(1, "p2p"), (3, "p2p"), (3, "nvls")])
+def test_fused_zero_two_gpus(stage, mode):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
-    port = 29600 + stage
+    port = 29600 + stage + (4 if mode == "nvls" else 0)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
-           "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "mp_zero_check.py"), str(stage)]
+           "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "mp_zero_check.py"), str(stage), mode]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
 
@@ -46,3 +46,21 @@ def test_context_parallel_two_gpus():
            "127.0.0.1", "--master-port", "29631", os.path.join(HERE, "mp_cp_gpu_check.py")]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, NCCL_NVLS_ENABLE="0"))
     assert r.returncode == 0 and "CP_GPU_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
+
+
+def test_tensor_parallel_mamba_two_gpus():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29641", os.path.join(HERE, "mp_tp_mamba_gpu_check.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+def test_pipeline_ulysses_hierarchical_two_gpus():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29651", os.path.join(HERE, "mp_pp_sp_gpu_check.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=dict(os.environ, NCCL_NVLS_ENABLE="0"))
+    assert r.returncode == 0 and "PP_SP_GPU_OK" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]

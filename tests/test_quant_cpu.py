@@ -52,3 +52,27 @@ def test_mx_and_nvfp4():
     y4, e4 = Q.mx_quantize(x, "mxfp4")
     mags = (y4.reshape(-1, 32) / torch.exp2(e4.float()).reshape(-1, 1)).abs().unique()
     assert set(mags.tolist()) <= {0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0}
+
+
+def test_grouped_fp8_reference_and_fp8_moe_on_cpu():
+    """CPU statement of the grouped fp8 expert GEMM: close to the unquantised product, zero rows for unused tiles,
+    and the MoE layer with fp8 forward GEMMs stays close to the plain layer."""
+    import torch
+
+    from sneppx_alg_b200.ops import moe, quant
+    torch.manual_seed(0)
+    E, N, K = 3, 128, 256
+    tg = torch.tensor([2, -1, 0], dtype=torch.int32)
+    x = torch.randn(384, K)
+    W = torch.randn(E, N, K) * 0.05
+    y = quant.gemm_fp8_grouped(x, tg, W)
+    assert y[128:256].abs().max() == 0
+    full = x[:128] @ W[2].t()
+    assert (y[:128] - full).abs().max() / full.abs().max() < 8e-2
+    T, d, Fd, k = 64, 128, 128, 2
+    xx = torch.randn(T, d)
+    idx, w, _, _ = moe.route(torch.randn(T, E), k)
+    W1, W2 = torch.randn(E, 2 * Fd, d) * 0.05, torch.randn(E, d, Fd) * 0.05
+    a = moe.experts_forward(xx, idx, w, W1, W2, fp8=True)
+    b = moe.experts_forward(xx, idx, w, W1, W2)
+    assert (a - b).abs().max() / b.abs().max() < 0.1
