@@ -785,7 +785,9 @@ class ThreadPool:
         self._ex.shutdown(wait=True)
 
 
-WorkStealingPool = WorkerPool = ThreadPool
+from .utils.workpool import Future as PoolFuture, TaskGroup, Workload, WorkStealingPool  # noqa: E402  (native pool)
+
+WorkerPool = WorkStealingPool
 
 
 class BenchmarkTimer:
