@@ -104,8 +104,13 @@ def run_http(model, requests=64, prompt_len=2048, new_tokens=256, max_prefill_to
     post(prompts[0][: min(prompt_len, 128)], 4)
     results = [None] * requests
 
+    errors = []
+
     def worker(i):
-        results[i] = post(prompts[i], new_tokens)
+        try:
+            results[i] = post(prompts[i], new_tokens)
+        except Exception as e:  # noqa: BLE001  (reported after the run)
+            errors.append(f"request {i}: {type(e).__name__}: {e}")
 
     if torch.cuda.is_available():
         torch.cuda.synchronize()
@@ -120,6 +125,8 @@ def run_http(model, requests=64, prompt_len=2048, new_tokens=256, max_prefill_to
     th.join(10)
     for w in app.state.workers.values():
         w.stop()
+    if errors:
+        raise RuntimeError(f"{len(errors)} of {requests} requests failed; first: {errors[0]}")
     out_tokens = sum(r[0]["completion_tokens"] for r in results)
     ttft = sorted(r[0]["ttft_s"] for r in results)
     lat = sorted(r[1] for r in results)

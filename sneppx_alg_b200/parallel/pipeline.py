@@ -38,6 +38,88 @@ class PipelineSchedule:
         return [("F", i) for i in range(num_microbatches)] + [("B", i) for i in range(num_microbatches)]
 
 
+def plan_rounds(schedules: List[List[tuple]], num_ranks: int, num_chunks: int):
+    """Turns the per-rank schedules (lists of (kind, chunk, micro-batch)) into globally agreed communication rounds.
+
+    Every rank runs the same simulation: in a round each rank executes its next step if the message that step
+    consumes was produced in an earlier round; the messages produced in a round are exchanged at the round's end, every
+    rank issuing ONE batch of sends and receives. Both ends of every pair therefore post their operations in the same
+    order, which is what transports without message tags (NCCL matches point-to-point operations of a pair strictly in
+    posting order and runs them one after another) need in order not to dead-lock; opposite-direction transfers of a
+    round travel in one batch and progress together. Returns, per round, (steps executed per rank, messages
+    [(key, src, dst)]), where key = (direction, consuming virtual stage, micro-batch)."""
+    P, v = num_ranks, num_chunks
+    last_vs = P * v - 1
+
+    def consumes(r, step):
+        kind, c, i = step
+        vs = c * P + r
+        if kind == "F":
+            return None if vs == 0 else ("act", vs, i)
+        return None if vs == last_vs else ("grad", vs, i)
+
+    def produces(r, step):
+        kind, c, i = step
+        vs = c * P + r
+        if kind == "F":
+            return None if vs == last_vs else (("act", vs + 1, i), (vs + 1) % P)
+        return None if vs == 0 else (("grad", vs - 1, i), (vs - 1) % P)
+
+    ptr = [0] * P
+    avail = set()
+    rounds = []
+    while any(ptr[r] < len(schedules[r]) for r in range(P)):
+        executed = [None] * P
+        for r in range(P):
+            if ptr[r] < len(schedules[r]):
+                need = consumes(r, schedules[r][ptr[r]])
+                if need is None or need in avail:
+                    executed[r] = schedules[r][ptr[r]]
+        if not any(e is not None for e in executed):
+            raise RuntimeError("pipeline schedule cannot make progress (a step waits for a message nobody sends)")
+        msgs = []
+        for r in range(P):
+            if executed[r] is not None:
+                ptr[r] += 1
+                out = produces(r, executed[r])
+                if out is not None:
+                    msgs.append((out[0], r, out[1]))
+        avail.update(k for k, _, _ in msgs)
+        rounds.append((executed, msgs))
+    return rounds
+
+
+def run_rounds(rounds, rank: int, group, hidden_shape, dtype, device, forward_step, backward_step):
+    """Executes this rank's part of ``plan_rounds``. ``forward_step(chunk, mb, x_or_None) -> tensor to send or None``;
+    ``backward_step(chunk, mb, grad_or_None) -> tensor to send or None``."""
+    inbox = {}
+    P = dist.get_world_size(group)
+    glob = [dist.get_global_rank(group, r) for r in range(P)]
+    for executed, msgs in rounds:
+        outgoing = None
+        step = executed[rank]
+        if step is not None:
+            kind, c, i = step
+            vs = c * P + rank
+            if kind == "F":
+                outgoing = forward_step(c, i, inbox.pop(("act", vs, i), None))
+            else:
+                outgoing = backward_step(c, i, inbox.pop(("grad", vs, i), None))
+        ops, bufs = [], []
+        for key, src, dst in msgs:
+            if src == rank:
+                ops.append(dist.P2POp(dist.isend, outgoing.contiguous(), glob[dst], group))
+            if dst == rank:
+                buf = torch.empty(hidden_shape, dtype=dtype, device=device)
+                bufs.append((key, buf))
+                ops.append(dist.P2POp(dist.irecv, buf, glob[src], group))
+        if ops:
+            for w in dist.batch_isend_irecv(ops):
+                w.wait()
+        for key, buf in bufs:
+            inbox[key] = buf
+
+
 class PipelineStage:
     def __init__(self, stage_module: torch.nn.Module, group=None, hidden_shape=None, dtype=None, device=None,
                  schedule: str = "1f1b"):
@@ -51,62 +133,38 @@ class PipelineStage:
         self.prev = dist.get_global_rank(self.group, self.stage - 1) if not self.first else None
         self.next = dist.get_global_rank(self.group, self.stage + 1) if not self.last else None
 
-    def _recv(self, src):
-        buf = torch.empty(self.hidden_shape, dtype=self.dtype, device=self.device)
-        return buf, dist.irecv(buf, src=src, group=self.group)
-
     def forward_backward(self, inputs: Optional[List[torch.Tensor]], labels: Optional[List[torch.Tensor]],
                          num_microbatches: int, loss_scale: Optional[float] = None):
         """Runs all micro-batches of one step. ``inputs`` on the first stage, ``labels`` on the last. Returns the mean
-        loss on the last stage (None elsewhere). Gradients accumulate in the stage's parameters."""
-        M = num_microbatches
-        sched = (PipelineSchedule.one_f_one_b if self.schedule == "1f1b" else PipelineSchedule.gpipe)(
-            self.stage, self.num_stages, M)
+        loss on the last stage (None elsewhere). Gradients accumulate in the stage's parameters. Activations and
+        gradients move in globally ordered rounds (``plan_rounds``), one batched send / receive per round, so the same
+        code runs on NCCL point-to-point (no tags, strict pairwise order) and on gloo."""
+        M, P = num_microbatches, self.num_stages
+        make = PipelineSchedule.one_f_one_b if self.schedule == "1f1b" else PipelineSchedule.gpipe
+        schedules = [[(k, 0, i) for k, i in make(st, P, M)] for st in range(P)]
+        rounds = plan_rounds(schedules, P, 1)
         scale = loss_scale if loss_scale is not None else 1.0 / M
-        saved_in, saved_out = {}, {}
-        pending_sends = []
-        losses = []
-        # post the first receive early; later ones are posted one step ahead so they overlap with compute
-        next_fwd_recv = self._recv(self.prev) if not self.first else None
-        next_bwd_recv = None
-        fwd_seen = 0
-        for kind, i in sched:
-            if kind == "F":
-                if self.first:
-                    x = inputs[i]
-                else:
-                    buf, work = next_fwd_recv
-                    work.wait()
-                    fwd_seen += 1
-                    next_fwd_recv = self._recv(self.prev) if fwd_seen < M else None
-                    x = buf.requires_grad_(True)
-                if self.last:
-                    out = self.module(x, labels[i])
-                    losses.append(out.detach())
-                    saved_out[i] = out
-                else:
-                    out = self.module(x)
-                    pending_sends.append(dist.isend(out.detach().contiguous(), dst=self.next, group=self.group))
-                    saved_out[i] = out
-                    if next_bwd_recv is None:
-                        next_bwd_recv = self._recv(self.next)
-                saved_in[i] = x
+        saved, losses = {}, []
+
+        def fwd(c, i, x):
+            x = inputs[i] if self.first else x.requires_grad_(True)
+            out = self.module(x, labels[i]) if self.last else self.module(x)
+            saved[i] = (x, out)
+            if self.last:
+                losses.append(out.detach())
+                return None
+            return out.detach()
+
+        def bwd(c, i, g):
+            x, out = saved.pop(i)
+            if self.last:
+                (out * scale).backward()
             else:
-                x, out = saved_in.pop(i), saved_out.pop(i)
-                if self.last:
-                    (out * scale).backward()
-                else:
-                    gbuf, work = next_bwd_recv
-                    work.wait()
-                    next_bwd_recv = self._recv(self.next) if any(k == "B" and j > i for k, j in sched) else None
-                    out.backward(gbuf)
-                if not self.first:
-                    pending_sends.append(dist.isend(x.grad.contiguous(), dst=self.prev, group=self.group))
-        for w in pending_sends:
-            w.wait()
-        if self.last:
-            return torch.stack(losses).mean()
-        return None
+                out.backward(g)
+            return None if self.first else x.grad
+
+        run_rounds(rounds, self.stage, self.group, self.hidden_shape, self.dtype, self.device, fwd, bwd)
+        return torch.stack(losses).mean() if self.last else None
 
 
 def split_layers(num_layers: int, num_stages: int) -> List[range]:
@@ -194,9 +252,8 @@ class InterleavedPipelineStage:
     """Interleaved pipeline over `num_chunks` model chunks per rank. ``chunks[c]`` is the module of virtual stage
     ``c * P + rank``; the very first virtual stage takes ``inputs``, the very last ``(hidden, labels) -> loss``.
 
-    Messages carry a tag derived from (direction, virtual stage, micro-batch): transports that match on tags (gloo)
-    pair them regardless of posting order. Sends are asynchronous and receives are posted when their step comes up, so
-    the only waits are the data dependencies of the schedule."""
+    Messages move in the globally ordered rounds of ``plan_rounds`` (one batched send / receive per round and rank),
+    which needs no message tags and so also runs on NCCL point-to-point."""
 
     def __init__(self, chunks: List[torch.nn.Module], group=None, hidden_shape=None, dtype=None, device=None):
         self.chunks = list(chunks)
@@ -208,44 +265,33 @@ class InterleavedPipelineStage:
         self.right = dist.get_global_rank(self.group, (self.rank + 1) % self.P)
         self.left = dist.get_global_rank(self.group, (self.rank - 1) % self.P)
 
-    def _tag(self, backward: bool, vstage: int, mb: int) -> int:
-        return (1 << 20) * int(backward) + vstage * 1024 + mb
-
     def forward_backward(self, inputs, labels, num_microbatches: int, loss_scale: Optional[float] = None):
         P, v, M = self.P, self.v, num_microbatches
         last_vs = P * v - 1
         scale = loss_scale if loss_scale is not None else 1.0 / M
-        saved, sends, losses = {}, [], []
-        for kind, c, i in interleaved_schedule(self.rank, P, v, M):
+        rounds = plan_rounds([interleaved_schedule(r, P, v, M) for r in range(P)], P, v)
+        saved, losses = {}, []
+
+        def fwd(c, i, x):
             vs = c * P + self.rank
-            if kind == "F":
-                if vs == 0:
-                    x = inputs[i]
-                else:
-                    x = torch.empty(self.hidden_shape, dtype=self.dtype, device=self.device)
-                    dist.recv(x, src=self.left, group=self.group, tag=self._tag(False, vs, i))
-                    x.requires_grad_(True)
-                if vs == last_vs:
-                    out = self.chunks[c](x, labels[i])
-                    losses.append(out.detach())
-                else:
-                    out = self.chunks[c](x)
-                    sends.append(dist.isend(out.detach().contiguous(), dst=self.right, group=self.group,
-                                            tag=self._tag(False, vs + 1, i)))
-                saved[(c, i)] = (x, out)
+            x = inputs[i] if vs == 0 else x.requires_grad_(True)
+            out = self.chunks[c](x, labels[i]) if vs == last_vs else self.chunks[c](x)
+            saved[(c, i)] = (x, out)
+            if vs == last_vs:
+                losses.append(out.detach())
+                return None
+            return out.detach()
+
+        def bwd(c, i, g):
+            vs = c * P + self.rank
+            x, out = saved.pop((c, i))
+            if vs == last_vs:
+                (out * scale).backward()
             else:
-                x, out = saved.pop((c, i))
-                if vs == last_vs:
-                    (out * scale).backward()
-                else:
-                    g = torch.empty_like(out)
-                    dist.recv(g, src=self.right, group=self.group, tag=self._tag(True, vs, i))
-                    out.backward(g)
-                if vs != 0:
-                    sends.append(dist.isend(x.grad.contiguous(), dst=self.left, group=self.group,
-                                            tag=self._tag(True, vs - 1, i)))
-        for w in sends:
-            w.wait()
+                out.backward(g)
+            return None if vs == 0 else x.grad
+
+        run_rounds(rounds, self.rank, self.group, self.hidden_shape, self.dtype, self.device, fwd, bwd)
         return torch.stack(losses).mean() if losses else None
 
 

@@ -175,3 +175,166 @@ def seal_program(prog: Program, key: bytes) -> bytes:
 
 def unseal_program(blob: bytes, key: bytes) -> Program:
     return deserialize_program(crypto.aead_decrypt(key, blob[:12], blob[12:], b"sneppx-npe"))
+
+
+# ----------------------------------------------------------------------------------------------- native-logic obfuscation
+class ObfuscatedRoutine:
+    """A routine written in the small register IR of ``csrc/host/obfvm.cpp`` ("label: movi r0 5 ; cmpi r0 3 ;
+    jg big small"), optionally control-flow flattened, compiled to a bytecode whose opcode encoding is private to
+    this compilation, and run by the native virtual machine. The reference's passes of the same purpose:
+    security/obfuscation/cfg_flatten.cpp, security/obfuscation/vm.cpp."""
+
+    def __init__(self, source: str):
+        import ctypes as C
+        L = self._lib()
+        self._C, self._g = C, L.sx_obf_parse(source.encode())
+        err = L.sx_obf_cfg_error(self._g).decode()
+        if err:
+            L.sx_obf_cfg_free(self._g)
+            self._g = None
+            raise ValueError(err)
+        self._p = None
+
+    @staticmethod
+    def _lib():
+        import ctypes as C
+
+        from .. import _build
+        L = _build.load_host()
+        if not getattr(L, "_obf_ready", False):
+            L.sx_obf_parse.restype = L.sx_obf_compile.restype = C.c_void_p
+            L.sx_obf_parse.argtypes = [C.c_char_p]
+            L.sx_obf_cfg_error.restype = C.c_char_p
+            for f in ("sx_obf_cfg_error", "sx_obf_cfg_free", "sx_obf_cfg_blocks", "sx_obf_program_free", "sx_obf_program_size",
+                      "sx_obf_validate"):
+                getattr(L, f).argtypes = [C.c_void_p]
+            L.sx_obf_program_size.restype = C.c_longlong
+            L.sx_obf_cfg_successors.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int]
+            L.sx_obf_flatten.argtypes = L.sx_obf_compile.argtypes = [C.c_void_p, C.c_ulonglong]
+            L.sx_obf_flatten.restype = None
+            sig = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_longlong]
+            L.sx_obf_run_ir.argtypes = L.sx_obf_execute.argtypes = sig
+            L.sx_obf_program_bytes.argtypes = [C.c_void_p, C.c_void_p]
+            L.sx_obf_program_poke.argtypes = [C.c_void_p, C.c_longlong, C.c_ubyte]
+            L.sx_obf_string_xform.argtypes = [C.c_char_p, C.c_ulonglong, C.c_char_p, C.c_void_p, C.c_size_t]
+            L.sx_obf_string_xform.restype = None
+            L.sx_obf_wipe.argtypes = [C.c_void_p, C.c_size_t]
+            L.sx_obf_debugger_signals.argtypes = [C.c_double]
+            L._obf_ready = True
+        return L
+
+    @property
+    def num_blocks(self) -> int:
+        return self._lib().sx_obf_cfg_blocks(self._g)
+
+    def successors(self, block: int) -> List[int]:
+        out = (self._C.c_int * 4)()
+        n = self._lib().sx_obf_cfg_successors(self._g, block, out, 4)
+        return [int(out[i]) for i in range(max(n, 0))]
+
+    def flatten(self, seed: int = 0) -> "ObfuscatedRoutine":
+        self._lib().sx_obf_flatten(self._g, seed)
+        return self
+
+    def compile(self, seed: int = 0) -> "ObfuscatedRoutine":
+        if self._p:
+            self._lib().sx_obf_program_free(self._p)
+        self._p = self._lib().sx_obf_compile(self._g, seed)
+        if not self._p:
+            raise ValueError("program has an immediate outside 32 bits")
+        return self
+
+    def _run(self, fn, handle, args, step_limit):
+        C = self._C
+        a = (C.c_longlong * max(len(args), 1))(*args)
+        out = (C.c_longlong * 256)()
+        n_out, ret = C.c_int(0), C.c_longlong(0)
+        rc = fn(handle, a, len(args), out, 256, C.byref(n_out), C.byref(ret), step_limit)
+        if rc != 0:
+            raise RuntimeError({-1: "undecodable opcode", -2: "step limit exceeded", -3: "register out of range",
+                                -4: "jump target out of range", -5: "truncated program", -6: "ran off the end"}.get(rc, f"error {rc}"))
+        return int(ret.value), [int(out[i]) for i in range(n_out.value)]
+
+    def run_ir(self, *args, step_limit: int = 1_000_000):
+        """Interpret the control-flow graph directly: (return value, values passed to ``out``)."""
+        return self._run(self._lib().sx_obf_run_ir, self._g, args, step_limit)
+
+    def run(self, *args, step_limit: int = 1_000_000):
+        """Run the compiled bytecode on the virtual machine."""
+        if not self._p:
+            self.compile()
+        return self._run(self._lib().sx_obf_execute, self._p, args, step_limit)
+
+    def bytecode(self) -> bytes:
+        n = self._lib().sx_obf_program_size(self._p)
+        buf = self._C.create_string_buffer(n)
+        self._lib().sx_obf_program_bytes(self._p, buf)
+        return buf.raw
+
+    def poke(self, offset: int, value: int) -> None:
+        self._lib().sx_obf_program_poke(self._p, offset, value)
+
+    def validate(self) -> int:
+        return self._lib().sx_obf_validate(self._p)
+
+    def close(self) -> None:
+        L = self._lib()
+        if self._p:
+            L.sx_obf_program_free(self._p)
+            self._p = None
+        if self._g:
+            L.sx_obf_cfg_free(self._g)
+            self._g = None
+
+
+class StringVault:
+    """String literals kept sealed (ChaCha20 under a vault key and the string's id) and opened one at a time into a
+    buffer that is wiped when the ``with`` block ends (security/obfuscation/string_encrypt.cpp)."""
+
+    def __init__(self, key32: bytes):
+        assert len(key32) == 32
+        self._key, self._items = key32, {}
+
+    def seal(self, name: str, text: str) -> bytes:
+        import ctypes as C
+        raw = text.encode()
+        sid = int.from_bytes(hashlib_sha(name)[:8], "little")
+        out = C.create_string_buffer(len(raw))
+        ObfuscatedRoutine._lib().sx_obf_string_xform(self._key, sid, raw, out, len(raw))
+        self._items[name] = out.raw
+        return out.raw
+
+    def open(self, name: str):
+        import ctypes as C
+        sealed = self._items[name]
+        sid = int.from_bytes(hashlib_sha(name)[:8], "little")
+        buf = C.create_string_buffer(len(sealed))
+        ObfuscatedRoutine._lib().sx_obf_string_xform(self._key, sid, sealed, buf, len(sealed))
+        return _OpenedString(buf)
+
+
+def hashlib_sha(name: str) -> bytes:
+    import hashlib
+    return hashlib.sha256(name.encode()).digest()
+
+
+class _OpenedString:
+    def __init__(self, buf):
+        self._buf = buf
+
+    def __enter__(self):
+        return self._buf.raw.decode()
+
+    def __exit__(self, *exc):
+        ObfuscatedRoutine._lib().sx_obf_wipe(self._buf, len(self._buf))
+
+    @property
+    def wiped(self) -> bool:
+        return not any(self._buf.raw)
+
+
+def debugger_signals(slow_factor: float = 50.0) -> dict:
+    """Signs of being observed: an attached tracer, a preloaded library, a timing probe that ran ``slow_factor`` times
+    slower than its own best (security/obfuscation/debug_detect.cpp)."""
+    bits = ObfuscatedRoutine._lib().sx_obf_debugger_signals(slow_factor)
+    return {"tracer_attached": bool(bits & 1), "ld_preload": bool(bits & 2), "timing_anomaly": bool(bits & 4)}

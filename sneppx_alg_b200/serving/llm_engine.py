@@ -161,7 +161,7 @@ class LlamaPagedRunner:
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
+        with torch.cuda.graph(graph, capture_error_mode="thread_local"):   # other threads (HTTP handlers) may call CUDA
             out = self._decode_body(Bb, views["ids"], views["pos"], views["slots"], views["bt"], views["lens"])
         g = self._graphs[Bb] = dict(graph=graph, host=host, buf=buf, out=out, hv=host.numpy())
         return g

@@ -105,4 +105,13 @@ def main():
 
 
 if __name__ == "__main__":
-    main()
+    try:
+        main()
+    except SystemExit:
+        raise
+    except BaseException:  # noqa: BLE001  (the launcher only keeps the tail of stderr: put the cause on stdout)
+        import traceback
+        print("WORKER ERROR on rank", os.environ.get("RANK"), flush=True)
+        traceback.print_exc(file=sys.stdout)
+        sys.stdout.flush()
+        os._exit(1)

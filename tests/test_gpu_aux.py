@@ -90,7 +90,7 @@ def test_debug_bounds_mode_catches_bad_indices_without_faulting():
     """Debug-bounds mode: an out-of-range index is reported by the checking kernel (nothing faults, the context stays
     usable), poisoned outputs come back fully written, and a clean run records nothing."""
     from sneppx_alg_b200.ops import debug, moe
-    from sneppx_alg_b200.ops import gemm as gemm_mod
+    from sneppx_alg_b200.ops.gemm import gemm as gemm_fn
     debug.enable(True)
     try:
         assert debug.read_record() is None
@@ -104,7 +104,7 @@ def test_debug_bounds_mode_catches_bad_indices_without_faulting():
         y = moe.experts_forward(x, idx, w, W1, W2)
         a = torch.randn(256, 128, device="cuda", dtype=torch.bfloat16)
         b = torch.randn(192, 128, device="cuda", dtype=torch.bfloat16)
-        c = gemm_mod.gemm(a, b)
+        c = gemm_fn(a, b)
         debug.check()
         assert not torch.isnan(y.float()).any() and not torch.isnan(c.float()).any()
         # a bad expert index is caught before any kernel indexes with it
