@@ -28,7 +28,8 @@ class ByteTokenizer:
         return [ord(c) % self.vocab_size for c in text] or [0]
 
     def decode(self, ids: List[int]) -> str:
-        return "".join(chr(i) if 32 <= i < 0x110000 else "?" for i in ids)
+        # code points that cannot be encoded as UTF-8 on their own (surrogates) print as "?" like control characters
+        return "".join(chr(i) if (32 <= i < 0xD800 or 0xE000 <= i < 0x110000) else "?" for i in ids)
 
 
 class EngineWorker:
