@@ -80,16 +80,30 @@ _DT = {np.dtype(v): k for k, v in _NP.items()}
 class Tensor:
     name: str
     data: np.ndarray
+    external: Optional[Dict[str, str]] = None     # {"location", "offset", "length"} when the bytes live in a side file
 
-    def serialize(self) -> bytes:
+    def serialize(self, external: Optional[Dict[str, str]] = None) -> bytes:
         a = np.ascontiguousarray(self.data)
-        out = b"".join(_vi(1, int(d)) for d in a.shape) + _vi(2, _DT[a.dtype]) + _ld(8, self.name.encode()) + _ld(9, a.tobytes())
-        return out
+        out = b"".join(_vi(1, int(d)) for d in a.shape) + _vi(2, _DT[a.dtype]) + _ld(8, self.name.encode())
+        if external is None:
+            return out + _ld(9, a.tobytes())
+        # TensorProto.external_data (field 13, key / value entries) + data_location = EXTERNAL (field 14)
+        for k in ("location", "offset", "length"):
+            out += _ld(13, _ld(1, k.encode()) + _ld(2, str(external[k]).encode()))
+        return out + _vi(14, 1)
 
     @classmethod
     def parse(cls, buf: bytes) -> "Tensor":
         dims, dt, name, raw, floats, ints = [], DT_FLOAT, "", None, [], []
+        ext, location = {}, 0
         for num, wire, v in parse_message(buf):
+            if num == 13:
+                kv = {n_: x for n_, _, x in parse_message(v)}
+                ext[kv.get(1, b"").decode()] = kv.get(2, b"").decode()
+                continue
+            if num == 14:
+                location = v
+                continue
             if num == 1:
                 dims.append(v) if wire == 0 else dims.extend(_unpack_varints(v))
             elif num == 2:
@@ -102,6 +116,10 @@ class Tensor:
                 floats.extend(struct.unpack(f"<{len(v) // 4}f", v) if wire == 2 else struct.unpack("<f", v))
             elif num == 7:
                 ints.extend(_unpack_varints(v) if wire == 2 else [v])
+        if location == 1:        # bytes are in a side file: placeholder of the right shape until they are loaded
+            if "location" not in ext:
+                raise ValueError(f"tensor {name!r} is marked external but names no file")
+            return cls(name, np.zeros(dims, dtype=_NP[dt]), ext)
         if raw is not None:
             arr = np.frombuffer(raw, dtype=_NP[dt]).reshape(dims)
         elif floats:
@@ -233,11 +251,12 @@ class Model:
     ir_version: int = 8
     opset: int = 17
     producer: str = "sneppx"
+    external: Dict[str, Dict[str, str]] = field(default_factory=dict)   # initializers whose bytes are in side files
 
     def serialize(self) -> bytes:
         g = self.graph
         gb = b"".join(_ld(1, n.serialize()) for n in g.nodes) + _ld(2, g.name.encode())
-        gb += b"".join(_ld(5, Tensor(k, v).serialize()) for k, v in g.initializers.items())
+        gb += b"".join(_ld(5, Tensor(k, v).serialize(self.external.get(k))) for k, v in g.initializers.items())
         gb += b"".join(_ld(11, v.serialize()) for v in g.inputs) + b"".join(_ld(12, v.serialize()) for v in g.outputs)
         return _vi(1, self.ir_version) + _ld(2, self.producer.encode()) + _ld(7, gb) + _ld(8, _ld(1, b"") + _vi(2, self.opset))
 
@@ -273,6 +292,8 @@ class Model:
                     elif gn == 5:
                         t = Tensor.parse(gv)
                         m.graph.initializers[t.name] = t.data
+                        if t.external is not None:
+                            m.external[t.name] = t.external
                     elif gn == 11:
                         m.graph.inputs.append(ValueInfo.parse(gv))
                     elif gn == 12:
@@ -448,6 +469,93 @@ def export_module(module, example_input, path: Optional[str] = None) -> Model:
     if path:
         m.save(path)
     return m
+
+
+# ----------------------------------------------------------------------------- external data / runtime adapter
+def save_external_data(m: Model, path: str, data_file: Optional[str] = None, size_threshold: int = 1024) -> List[str]:
+    """Writes ``path`` with every initializer of at least ``size_threshold`` bytes moved into one side file
+    (``<model name>.data`` beside it unless named), 64-byte aligned, referenced by location / offset / length as in
+    the ONNX external-data convention (the reference's onnx/external_data.py:26-55). Returns the moved names."""
+    import os
+    data_file = data_file or os.path.basename(path) + ".data"
+    if os.path.basename(data_file) != data_file:
+        raise ValueError("the data file must sit beside the model (a plain file name)")
+    moved, ext, off = [], {}, 0
+    with open(os.path.join(os.path.dirname(os.path.abspath(path)), data_file), "wb") as f:
+        for name, arr in m.graph.initializers.items():
+            raw = np.ascontiguousarray(arr).tobytes()
+            if len(raw) < size_threshold:
+                continue
+            pad = (-off) % 64
+            f.write(b"\x00" * pad)
+            off += pad
+            f.write(raw)
+            ext[name] = {"location": data_file, "offset": str(off), "length": str(len(raw))}
+            off += len(raw)
+            moved.append(name)
+    out = Model(m.graph, m.ir_version, m.opset, m.producer, ext)
+    out.save(path)
+    return moved
+
+
+def load_external_data(path: str, base_dir: Optional[str] = None) -> Model:
+    """Loads a model and pulls every external initializer in from its side file. File names are taken relative to the
+    model's folder (or ``base_dir``) and may not leave it; offsets and lengths are checked against the file and the
+    tensor's shape (onnx/external_data.py:92-95 of the reference trusts them)."""
+    import os
+    m = Model.load(path)
+    base = os.path.abspath(base_dir or os.path.dirname(os.path.abspath(path)))
+    for name, e in m.external.items():
+        loc = e.get("location", "")
+        full = os.path.abspath(os.path.join(base, loc))
+        if not loc or os.path.isabs(loc) or os.path.commonpath([base, full]) != base:
+            raise ValueError(f"external data of {name!r} points outside the model folder: {loc!r}")
+        arr = m.graph.initializers[name]
+        off, want = int(e.get("offset", 0)), arr.size * arr.dtype.itemsize
+        length = int(e.get("length", want))
+        if off < 0 or length != want or off + length > os.path.getsize(full):
+            raise ValueError(f"external data of {name!r}: offset {off} / length {length} do not fit the file or the shape")
+        with open(full, "rb") as f:
+            f.seek(off)
+            m.graph.initializers[name] = np.frombuffer(f.read(length), dtype=arr.dtype).reshape(arr.shape).copy()
+    m.external = {}
+    return m
+
+
+def has_onnxruntime() -> bool:
+    try:
+        import onnxruntime  # noqa: F401
+        return True
+    except Exception:  # noqa: BLE001
+        return False
+
+
+class OnnxRuntimeSession:
+    """``InferenceSession``-shaped front: runs on onnxruntime when it is installed (or when ``require_ort``), else on
+    this toolkit's own executor, with the same ``get_inputs`` / ``get_outputs`` / ``run`` surface
+    (onnx/runtime/ort_adapter.py:38-73 of the reference)."""
+
+    def __init__(self, model: Model, require_ort: bool = False):
+        self.model, self._sess = model, None
+        if has_onnxruntime():
+            import onnxruntime as ort
+            self._sess = ort.InferenceSession(model.serialize(), providers=["CPUExecutionProvider"])
+        elif require_ort:
+            raise RuntimeError("onnxruntime is not installed")
+        self.backend = "onnxruntime" if self._sess is not None else "sneppx"
+
+    def get_inputs(self) -> List[ValueInfo]:
+        return list(self.model.graph.inputs)
+
+    def get_outputs(self) -> List[ValueInfo]:
+        return list(self.model.graph.outputs)
+
+    def run(self, output_names: Optional[List[str]], inputs: Dict[str, np.ndarray]) -> List[np.ndarray]:
+        if self._sess is not None:
+            return self._sess.run(output_names, inputs)
+        res = run_model(self.model, inputs)
+        names = output_names or [o.name for o in self.model.graph.outputs]
+        return [res[n] for n in names]
 
 
 def main(argv=None):
