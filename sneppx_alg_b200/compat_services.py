@@ -50,8 +50,92 @@ get_ddos_mitigation, set_ddos_mitigation = _accessor("ddos", _svc.DDoSMitigator)
 get_key_manager, set_key_manager = _accessor("keys", _svc.ApiKeyStore)
 get_usage_tracker, set_usage_tracker = _accessor("usage", _svc.UsageTracker)
 DDoSMitigation, ApiKeyManager, SlidingWindowRateLimiter = _svc.DDoSMitigator, _svc.ApiKeyStore, _svc.TokenBucket
-SelfAuditor, NetworkFuzzer = _svc.self_audit, _svc.fuzz
-LTLProperty = ModelChecker = _svc.ltl_check
+
+
+class SelfAuditor:
+    """Configuration audit with a score: ``audit(config)`` lists findings, ``score`` is the share of checks passed."""
+
+    CHECKS = 4
+
+    def __init__(self):
+        self.findings: List[str] = []
+
+    def audit(self, config: dict) -> List[str]:
+        self.findings = _svc.self_audit(config)
+        return self.findings
+
+    @property
+    def score(self) -> float:
+        return 1.0 - len(self.findings) / self.CHECKS
+
+
+class NetworkFuzzer:
+    """Mutation fuzzer bound to a seed corpus; ``run(target)`` returns the crashing inputs of this campaign."""
+
+    def __init__(self, seeds: Sequence[bytes], iterations: int = 200, seed: int = 0):
+        self.seeds, self.iterations, self.seed = list(seeds), iterations, seed
+        self.crashes: List[dict] = []
+
+    def run(self, target: Callable[[bytes], None]) -> List[dict]:
+        self.crashes = _svc.fuzz(target, self.seeds, self.iterations, self.seed)
+        return self.crashes
+
+
+class LTLProperty:
+    """A named temporal property. ``holds_on(trace)`` evaluates it on one finite trace of labelled states;
+    ``holds_in(model)`` checks every infinite run of a ``security.formal.FormalModel``."""
+
+    def __init__(self, formula, name: str = ""):
+        from .security.formal import parse_ltl
+        self.formula = parse_ltl(formula) if isinstance(formula, str) else formula
+        self.name = name or str(formula)
+
+    def holds_on(self, trace: List[dict]) -> bool:
+        return _svc.ltl_check(self._finite(self.formula), trace)
+
+    @staticmethod
+    def _finite(f):
+        if f is True or f is False or f[0] in ("ap",):
+            return ("ap", "__true__") if f is True else (("not", ("ap", "__true__")) if f is False else f)
+        if f[0] == "implies":
+            return ("or", ("not", LTLProperty._finite(f[1])), LTLProperty._finite(f[2]))
+        if f[0] == "release":      # f R g on a finite trace: g holds up to and including the first f (or to the end)
+            a, b = LTLProperty._finite(f[1]), LTLProperty._finite(f[2])
+            return ("or", ("always", b), ("until", b, ("and", a, b)))
+        return (f[0],) + tuple(LTLProperty._finite(x) if isinstance(x, tuple) or x is True or x is False else x for x in f[1:])
+
+    def holds_in(self, model):
+        return model.check_ltl(self.formula)
+
+
+class ModelChecker:
+    """Builds a transition system and checks properties on it (``security.formal.FormalModel`` underneath)."""
+
+    def __init__(self):
+        from .security.formal import FormalModel
+        self.model = FormalModel()
+
+    def add_state(self, state: int, props=(), initial=False, accepting=False, error=False):
+        self.model.add_state(state, props, initial, accepting, error)
+        return self
+
+    def add_transition(self, a: int, b: int, label: str = ""):
+        self.model.add_transition(a, b, label)
+        return self
+
+    def check(self, prop) -> bool:
+        prop = prop if isinstance(prop, LTLProperty) else LTLProperty(prop)
+        return bool(prop.holds_in(self.model))
+
+    def counterexample(self, prop):
+        prop = prop if isinstance(prop, LTLProperty) else LTLProperty(prop)
+        return prop.holds_in(self.model).counterexample
+
+    def deadlocks(self):
+        return self.model.deadlocks()
+
+    def reachable(self, a: int, b: int) -> bool:
+        return self.model.is_reachable(a, b)
 
 
 def audit_log(actor: str, action: str, **details):
@@ -626,7 +710,44 @@ def select_execution_provider(preferred: Sequence[str] = ("cuda", "cpu")) -> str
 from . import graph as _graph  # noqa: E402
 
 GraphNode, TensorExpr, StateGraph = _graph.ExprNode, _graph.ExprNode, _graph.ExprGraph
-GraphCompiler = GraphOptimizer = TensorExprCompiler = CompiledGraph = _graph.ExprGraph
+
+
+class CompiledGraph:
+    """An expression graph bound to its outputs and fusion plan: call it with named inputs."""
+
+    def __init__(self, graph, outputs, fuse: bool = True):
+        self.graph, self.outputs, self.fuse = graph, list(outputs), fuse
+        self.plan = graph.plan_fusions(self.outputs) if fuse else []
+
+    def __call__(self, **feeds):
+        return self.graph.run(self.outputs, feeds, fuse=self.fuse)
+
+    @property
+    def num_fused_groups(self) -> int:
+        return len(self.plan)
+
+
+class GraphOptimizer:
+    """Fusion planner front: ``optimize(graph, outputs)`` returns the fusion groups (matmul + bias + activation chains)
+    and ``memory_saving`` the bytes of intermediates that fusing avoids."""
+
+    def optimize(self, graph, outputs):
+        return graph.plan_fusions(list(outputs))
+
+    def memory_saving(self, graph, outputs, shapes, elem_bytes=2) -> int:
+        return graph.memory_estimate(list(outputs), shapes, elem_bytes, fused=False) - \
+            graph.memory_estimate(list(outputs), shapes, elem_bytes, fused=True)
+
+
+class GraphCompiler:
+    def __init__(self, fuse: bool = True):
+        self.fuse = fuse
+
+    def compile(self, graph, outputs) -> CompiledGraph:
+        return CompiledGraph(graph, outputs, self.fuse)
+
+
+TensorExprCompiler = GraphCompiler
 FUSABLE_OPS = ("matmul", "bias", "relu", "gelu", "silu", "add", "mul")
 
 
@@ -646,7 +767,30 @@ def trace_function(fn, *example_inputs):
 
 
 jit = trace_function
-Tracer = Trace = trace_function
+
+
+class Trace:
+    """What a ``Tracer`` recorded for one function: the captured callable and the example input signature."""
+
+    def __init__(self, fn, compiled, example_inputs):
+        self.fn, self.compiled = fn, compiled
+        self.signature = [(tuple(t.shape), str(t.dtype)) if torch.is_tensor(t) else type(t).__name__ for t in example_inputs]
+
+    def __call__(self, *inputs):
+        return self.compiled(*inputs)
+
+
+class Tracer:
+    """Captures functions into replayable form (a CUDA graph for CUDA inputs, the function itself otherwise) and keeps
+    the traces by name."""
+
+    def __init__(self):
+        self.traces: Dict[str, Trace] = {}
+
+    def trace(self, fn, *example_inputs, name: Optional[str] = None) -> Trace:
+        t = Trace(fn, trace_function(fn, *example_inputs), example_inputs)
+        self.traces[name or getattr(fn, "__name__", f"fn{len(self.traces)}")] = t
+        return t
 
 NPEInstruction, NPECompiler, NPEVerify = _npe.Instruction, _npe.compile_mlp, _npe.verify_program
 ARCInputGuard, ARCGradientObfuscator, ARCOutputVerifier, ARCAttackSim = _arc.InputGuard, _arc.GradientObfuscator, _arc.OutputVerifier, _arc.simulate_attack
@@ -713,13 +857,74 @@ create_vizmon = start_dashboard = _lazy("utils.vizmon", "VizMon")
 SocketComm = _lazy("utils.net", "FramedSocket")
 GRPCService = _lazy("utils.net", "CoordinatorServer")
 NCCLComm = _lazy("parallel.distributed", "ProcessGroup")
-MemoryPool = MemoryAllocator = _lazy("utils.mm", "Arena")
-ContinuousBatchScheduler = _lazy("serving.llm_engine", "LLMEngine")
+MemoryAllocator = _lazy("utils.mm", "Arena")
+
+
+class MemoryPool:
+    """Size-class host memory pool of the native runtime (``sx_pool_*`` in csrc/host/cpu_oracle.cpp): ``alloc`` /
+    ``free`` by address with hit / miss statistics."""
+
+    def __init__(self):
+        import ctypes as C
+
+        from .utils.host import _L as _host
+        self._C, self._L = C, _host()
+        self._L.sx_pool_alloc.argtypes = [C.c_void_p, C.c_size_t]
+        self._L.sx_pool_free.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
+        self._L.sx_pool_stats.argtypes = [C.c_void_p, C.c_void_p]
+        self._h = self._L.sx_pool_create()
+
+    def alloc(self, n: int) -> int:
+        return self._L.sx_pool_alloc(self._h, n) or 0
+
+    def free(self, ptr: int, n: int) -> None:
+        self._L.sx_pool_free(self._h, ptr, n)
+
+    def stats(self) -> dict:
+        out = (self._C.c_longlong * 3)()
+        self._L.sx_pool_stats(self._h, out)
+        return {"allocations": int(out[0]), "reused": int(out[1]), "bytes_live": int(out[2])}
+
+    def close(self) -> None:
+        if self._h:
+            self._L.sx_pool_destroy(self._h)
+            self._h = None
+
+
+class ContinuousBatchScheduler:
+    """Request-level front of the continuous-batching engine with the reference scheduler's verbs
+    (interface_bindings/continuous_batching.py:64-179: ``submit`` / ``get_batch`` / ``step``): requests are queued,
+    ``get_batch`` shows what is running, ``step`` advances every running sequence by one token on the paged engine."""
+
+    def __init__(self, model, max_batch_size: int = 32, **engine_kwargs):
+        from .serving.llm_engine import LLMEngine
+        self.engine = LLMEngine(model, max_batch_size=max_batch_size, **engine_kwargs)
+
+    def submit(self, prompt_tokens: List[int], max_new_tokens: int = 64, priority: int = 0, **sampling) -> int:
+        from .serving.llm_engine import SamplingParams
+        return self.engine.submit(list(prompt_tokens), SamplingParams(max_new_tokens=max_new_tokens, **sampling), priority)
+
+    def get_batch(self) -> List[int]:
+        return list(self.engine.running)
+
+    def step(self) -> Dict[int, List[int]]:
+        """One engine step; returns the requests that finished in it with their output tokens."""
+        before = set(self.engine.finished)
+        self.engine.step()
+        return {rid: self.engine.finished[rid].output for rid in set(self.engine.finished) - before}
+
+    def run(self) -> Dict[int, List[int]]:
+        self.engine.run_until_done()
+        return {rid: r.output for rid, r in self.engine.finished.items()}
+
+    @property
+    def pending(self) -> int:
+        return len(self.engine.waiting)
 DynamicBatchQueue = _lazy("utils.host", "ServingCore")
 get_profiler = _lazy("utils.observability", "Profiler")
 TrainProfiler = _lazy("utils.observability", "Profiler")
 LogTracker = Tracker = LocalBackend = _lazy("utils.observability", "ExperimentTracker")
-QLoRALinear = _lazy("training.lora", "LoRALinear")
+from .training.lora import QLoRALinear  # noqa: E402
 GradientCheckpointer = _lazy("training.extras", "enable_activation_checkpointing")
 checkpoint_sequential = _lazy("training.extras", "checkpoint")
 TopologyType = ("ring", "tree", "graph")

@@ -36,7 +36,8 @@ class LoRALinear(tnn.Module):
         w = base.weight.detach()
         self.out_features, self.in_features = w.shape
         self.r, self.scaling = r, alpha / r
-        self.bias = getattr(base, "bias", None)
+        b = getattr(base, "bias", None)
+        self.bias = tnn.Parameter(b.detach().clone(), requires_grad=False) if b is not None else None   # frozen with W
         self.qbase = quantize_base
         if quantize_base:
             idx, absmax, shape = quantize_nf4(w)
@@ -61,6 +62,24 @@ class LoRALinear(tnn.Module):
         return self.base_weight() + self.scaling * (self.lora_B @ self.lora_A)
 
 
+class QLoRALinear(LoRALinear):
+    """LoRA over a frozen base weight stored in 4-bit NormalFloat with per-block absmax scales: the base takes half a
+    byte per weight (plus scales) and is de-quantised on the fly for every forward; only A and B train
+    (the reference's ``QLoRALinear``, interface_bindings/lora.py:133-175, keeps an int4 base and ``_dequantize_weight``)."""
+
+    def __init__(self, base, r=8, alpha=16.0, dropout=0.0):
+        super().__init__(base, r, alpha, dropout, quantize_base=True)
+
+    @property
+    def base_bytes(self) -> int:
+        return self.w_idx.numel() * self.w_idx.element_size() + self.w_absmax.numel() * self.w_absmax.element_size()
+
+    def quantization_error(self, reference_weight) -> float:
+        """Relative Frobenius error of the stored base against the weight it was made from."""
+        w = reference_weight.detach().float()
+        return float((self.base_weight().float() - w).norm() / (w.norm() + 1e-12))
+
+
 def apply_lora(model, r=8, alpha=16.0, targets=("qkv_proj", "o_proj", "gate_up_proj", "down_proj"), qlora=False):
     """Freeze the model and wrap the targeted linear layers; returns the list of trainable LoRA parameters."""
     for p in model.parameters():
@@ -69,7 +88,7 @@ def apply_lora(model, r=8, alpha=16.0, targets=("qkv_proj", "o_proj", "gate_up_p
     for mod in list(model.modules()):
         for name, child in list(mod.named_children()):
             if name in targets and hasattr(child, "weight") and child.weight.dim() == 2:
-                l = LoRALinear(child, r, alpha, quantize_base=qlora)
+                l = QLoRALinear(child, r, alpha) if qlora else LoRALinear(child, r, alpha)
                 setattr(mod, name, l)
                 params += [l.lora_A, l.lora_B]
     return params

@@ -193,3 +193,49 @@ def test_hardening_probes_and_remote_audit(tmp_path):
     dead = sx.RemoteAPIAuditBackend(str(tmp_path / "b.log"), "http://127.0.0.1:9/none", timeout=0.5)
     dead.log("ann", "login")
     assert dead.failed == 1 and dead.verify()
+
+
+def test_compat_names_are_real_objects_of_the_right_kind():
+    """Names that used to be aliases of a function or of an unrelated class are classes with their own behaviour."""
+    import inspect
+
+    import torch
+
+    import SneppX_ALG as sx
+    for name in ("SelfAuditor", "NetworkFuzzer", "LTLProperty", "ModelChecker", "GraphCompiler", "GraphOptimizer",
+                 "CompiledGraph", "Tracer", "Trace", "MemoryPool", "ContinuousBatchScheduler", "QLoRALinear",
+                 "WorkStealingPool"):
+        assert inspect.isclass(getattr(sx, name)), name
+    assert len({sx.GraphCompiler, sx.GraphOptimizer, sx.CompiledGraph}) == 3 and sx.Tracer is not sx.Trace
+    a = sx.SelfAuditor()
+    assert "API keys are not required" in a.audit({"bind": "0.0.0.0"}) and 0 <= a.score < 1
+    fz = sx.NetworkFuzzer([b"GET / HTTP/1.1"], iterations=50)
+    assert all("input" in c for c in fz.run(lambda b: b.decode("ascii")))
+    p = sx.LTLProperty("G (req -> F ack)", "response")
+    assert p.holds_on([{"req": True}, {}, {"ack": True}]) and not p.holds_on([{"req": True}, {}])
+    mc = sx.ModelChecker().add_state(0, {"req"}, initial=True).add_state(1, {"ack"}).add_transition(0, 1).add_transition(1, 0)
+    assert mc.check(p) and not mc.check("G !ack") and mc.counterexample("G !ack") is not None and mc.reachable(0, 1)
+    from sneppx_alg_b200.graph import ExprGraph
+    g = ExprGraph()
+    x, w, b = g.input("x"), g.const(torch.randn(8, 4)), g.const(torch.randn(8))
+    y = g.unary("relu", g.add(g.matmul(x, w), b))
+    cg = sx.GraphCompiler().compile(g, [y])
+    xin = torch.randn(3, 4)
+    out = cg(x=xin)
+    out = out[0] if isinstance(out, (list, tuple)) else (out[y] if isinstance(out, dict) else out)
+    assert torch.allclose(out, torch.relu(xin @ g.nodes[w].value.t() + g.nodes[b].value), atol=1e-5)
+    assert cg.num_fused_groups >= 1 and len(sx.GraphOptimizer().optimize(g, [y])) >= 1
+    tr = sx.Tracer()
+    t = tr.trace(lambda v: v * 2, torch.ones(3), name="double")
+    assert torch.equal(t(torch.ones(3)), torch.full((3,), 2.0)) and t.signature == [((3,), "torch.float32")] and "double" in tr.traces
+    mp_ = sx.MemoryPool()
+    ptr = mp_.alloc(100)
+    mp_.free(ptr, 100)
+    assert mp_.alloc(100) == ptr and mp_.stats()["reused"] >= 1
+    mp_.close()
+    lin = torch.nn.Linear(64, 32)
+    q = sx.QLoRALinear(lin, r=4)
+    assert q.base_bytes < lin.weight.numel() * 4 / 2 and q.quantization_error(lin.weight) < 0.15
+    xin = torch.randn(2, 64)
+    assert (q(xin) - lin(xin)).abs().max() < 0.5          # B starts at zero: only the 4-bit rounding of the base differs
+    assert [n for n, p_ in q.named_parameters() if p_.requires_grad] == ["lora_A", "lora_B"]
