@@ -72,11 +72,11 @@ def test_loss_recovery_and_forged_packets():
     t.join(40)
     assert out["data"] == payload and dropped[0] > 10 and conn.stats["retransmitted_frames"] > 0
     # a forged short-header packet (right connection id, wrong key) is dropped without effect
-    cli.sock.sendto(b"\x40" + conn.local_cid + b"\x00\x00\x00\x63" + os.urandom(40), cli.address)
+    cli.sock.sendto(b"\x40" + conn.local_cid + b"\x7f\xff\xff\x00" + os.urandom(40), cli.address)
     cli.sock.sendto(b"\xc0\xff", cli.address)                        # truncated long header
     import time
     time.sleep(0.1)
-    assert not conn.closed and 0x63 not in conn.recv_pns            # never accepted: it failed authentication
+    assert not conn.closed and 0x7FFFFF00 not in conn.recv_pns            # never accepted: it failed authentication
     srv.close()
     cli.close()
 
