@@ -343,8 +343,65 @@ __global__ void __launch_bounds__(1024) allreduce_small_kernel(PeerTable pt, int
     reinterpret_cast<float*>(pt.buf[pt.rank])[i] = acc[k];
 }
 
+// One-shot all-reduce of bf16 activations for tensor-parallel layers (decode steps, short prefill chunks): every rank
+// has copied its n values into its symmetric staging buffer (stream-ordered before this launch); each CTA sums its
+// slice over all ranks' staging buffers with 16-byte peer loads (fp32 accumulation, rank order) and writes the local
+// result. The epoch is a counter in device memory that the launch itself advances, so the same launch can sit in a
+// CUDA graph and be replayed; two barriers per call: inputs ready, and everyone done reading (staging reusable).
+__global__ void __launch_bounds__(256) allreduce_bf16_kernel(PeerTable pt, __nv_bfloat16* __restrict__ out, long long n,
+                                                             int channel, uint32_t* epoch_ctr, uint32_t* cta_counter,
+                                                             int* status) {
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(epoch_ctr) + 1;
+  if (blockIdx.x == 0) signal_all(pt, channel, epoch);
+  const bool ok = wait_all(pt, channel, epoch, status);
+  if (ok) {
+    const long long nvec = n >> 3;
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+      uint4 v[SX_MAX_RANKS];
+#pragma unroll
+      for (int r = 0; r < SX_MAX_RANKS; ++r)
+        if (r < pt.world) v[r] = ld_peer_v4(reinterpret_cast<const __nv_bfloat16*>(pt.buf[r]) + i * 8);
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll
+      for (int r = 0; r < SX_MAX_RANKS; ++r)
+        if (r < pt.world) acc_bf16x8(acc, v[r]);
+      bf16x8 o = pack8(acc);
+      *reinterpret_cast<uint4*>(out + i * 8) = *reinterpret_cast<uint4*>(&o);
+    }
+  }
+  __shared__ int s_last;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t prev = atomicAdd(cta_counter, 1u);
+    s_last = (prev + 1 == gridDim.x);
+    if (s_last) *cta_counter = 0;
+  }
+  __syncthreads();
+  if (s_last) {
+    signal_all(pt, channel + 1, epoch);
+    wait_all(pt, channel + 1, epoch, status);
+    if (threadIdx.x == 0) *epoch_ctr = epoch;     // the next launch (or graph replay) uses epoch + 1
+  }
+}
+
 }  // namespace sx
 using namespace sx;
+
+// peers->buf[r]: rank r's bf16 staging buffer holding its n values (n % 8 == 0); out: local bf16 [n] (may alias the
+// local staging buffer's source tensor, not the staging buffer itself); epoch_ctr / cta_counter: local uint32 words,
+// zeroed once. Uses channels `channel` and `channel + 1` of the signal pad.
+extern "C" int sx_allreduce_bf16(const SxPeers* peers, void* out, long long n, int channel, void* epoch_ctr,
+                                 void* cta_counter, int grid, int* status, cudaStream_t st) {
+  if (n % 8 || n <= 0) return -1;
+  long long want = (n / 8 + 255) / 256;
+  if (grid <= 0) grid = (int)(want < 32 ? (want < 1 ? 1 : want) : 32);
+  allreduce_bf16_kernel<<<grid, 256, 0, st>>>(to_table(peers), (__nv_bfloat16*)out, n, channel, (uint32_t*)epoch_ctr,
+                                             (uint32_t*)cta_counter, status);
+  return cudaGetLastError() == cudaSuccess ? 0 : -11;
+}
 
 extern "C" int sx_peer_barrier(const SxPeers* peers, int channel, unsigned epoch, int* status, cudaStream_t st) {
   peer_barrier_kernel<<<1, 32, 0, st>>>(to_table(peers), channel, epoch, status);

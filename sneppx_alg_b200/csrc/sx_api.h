@@ -111,6 +111,12 @@ int sx_signal_peers(const SxPeers* peers, int channel, unsigned epoch, cudaStrea
 int sx_allgather_pull(const SxPeers* peers, void* dst, long long shard_bytes, long long src_offset_bytes, int channel,
                       unsigned epoch, int grid, int* status, cudaStream_t stream);
 
+// One-shot all-reduce of bf16 activations (tensor-parallel decode / short prefill): out = sum over ranks of their
+// staging buffers (peers->buf[r], n values each, n % 8 == 0). The epoch lives in device memory (epoch_ctr, advanced
+// by the launch), so the launch can be captured in a CUDA graph. Channels `channel`, `channel + 1`.
+int sx_allreduce_bf16(const SxPeers* peers, void* out, long long n, int channel, void* epoch_ctr, void* cta_counter,
+                      int grid, int* status, cudaStream_t stream);
+
 // F2 (push form, NVLS): every rank stores its shard ONCE to the multicast mapping of the full-size symmetric buffer
 // (multimem.st: the switch delivers it to all ranks), then the grid's last CTA signals `channel` = `epoch` to every rank
 // and waits for every rank's signal, so when the kernel ends on a rank, all shards have landed in its copy.

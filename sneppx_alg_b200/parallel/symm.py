@@ -155,6 +155,19 @@ class SymmGroup:
                   C.c_int(channel), C.c_uint(epoch), C.c_int(grid),
                   C.c_void_p(_lib.status_word(self.device).data_ptr()), stream or _lib.stream())
 
+    def allreduce_bf16_(self, x: torch.Tensor, staging: SymmBuffer, state: torch.Tensor, channel: int = 40, stream=None):
+        """In-place sum over the group of a contiguous bf16 tensor (numel % 8 == 0, at most the staging size) through
+        peer loads. ``state``: int32 [2] device tensor zeroed once (epoch counter, CTA counter) owned by the caller
+        and used by no other call site at the same time. Safe inside CUDA-graph capture."""
+        n = x.numel()
+        assert x.is_contiguous() and x.dtype == torch.bfloat16 and n % 8 == 0 and n <= staging.tensor.numel()
+        staging.tensor[:n].copy_(x.view(-1))
+        p = self.peers(staging)
+        _lib.call("sx_allreduce_bf16", C.byref(p), C.c_void_p(x.data_ptr()), C.c_longlong(n), C.c_int(channel),
+                  C.c_void_p(state.data_ptr()), C.c_void_p(state.data_ptr() + 4), C.c_int(0),
+                  C.c_void_p(_lib.status_word(self.device).data_ptr()), stream or _lib.stream())
+        return x
+
     def allreduce_small(self, buf: SymmBuffer, n: int, channel: int = 56, stream=None):
         e = self.next_epoch(channel)
         p = self.peers(buf)

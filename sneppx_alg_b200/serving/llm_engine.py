@@ -232,9 +232,26 @@ class TPLlamaPagedRunner(LlamaPagedRunner):
                                "gu": torch.cat([gu[r * fl:(r + 1) * fl], gu[ff + r * fl: ff + (r + 1) * fl]]).contiguous(),
                                "down": dn[:, r * fl:(r + 1) * fl].contiguous(), "act": layer.mlp.act})
         self.H, self.Hk = hl, kl
+        # all-reduce of the layer outputs: this package's peer-load kernel for messages up to 4 MiB (every decode
+        # step, short prefill chunks), NCCL above that. The kernel keeps its epoch on the device: graph-capturable.
+        self._sg = self._stage = None
+        p = model.embedding.weight
+        if p.is_cuda and p.dtype == torch.bfloat16 and dist.get_backend(self.group) == "nccl" and self.tp > 1:
+            from ..parallel.symm import SymmGroup
+            self._sg = SymmGroup(self.group)
+            self._stage = self._sg.alloc(2 << 20, torch.bfloat16)
+            self._ar_state = torch.zeros(2, dtype=torch.int32, device=p.device)
+            torch.cuda.synchronize()
+            dist.barrier(self.group)
+
+    def _all_reduce(self, t):
+        import torch.distributed as dist
+        if self._sg is not None and t.numel() <= self._stage.tensor.numel() and t.numel() % 8 == 0:
+            return self._sg.allreduce_bf16_(t if t.is_contiguous() else t.contiguous(), self._stage, self._ar_state)
+        dist.all_reduce(t, group=self.group)
+        return t
 
     def _layers(self, x, attn_fn):
-        import torch.distributed as dist
         m = self.model
         delta, resid = x, None
         for li, (layer, w) in enumerate(zip(m.layers, self.local)):
@@ -243,11 +260,9 @@ class TPLlamaPagedRunner(LlamaPagedRunner):
             else:
                 h, resid = layer.attn_norm(delta, residual=resid)
             o = attn_fn(li, ops.linear(h, w["qkv"]))
-            a = ops.linear(o, w["o"])
-            dist.all_reduce(a, group=self.group)
+            a = self._all_reduce(ops.linear(o, w["o"]))
             h, resid = layer.mlp_norm(a, residual=resid)
-            delta = ops.linear(ops.glu(ops.linear(h, w["gu"]), w["act"]), w["down"])
-            dist.all_reduce(delta, group=self.group)
+            delta = self._all_reduce(ops.linear(ops.glu(ops.linear(h, w["gu"]), w["act"]), w["down"]))
         h, _ = m.norm(delta, residual=resid)
         return h
 
@@ -345,8 +360,9 @@ class LLMEngine:
             self.cache = PagedKVCache(cfg.num_hidden_layers, num_blocks, block_size, cfg.num_key_value_heads, cfg.head_dim,
                                       dtype=p.dtype, device=p.device, enable_prefix_cache=enable_prefix_cache)
         self.runner = runner or LlamaPagedRunner(model, self.cache)
-        # CUDA-graph decode on one GPU (the tensor-parallel runner's collectives stay outside graphs)
-        if cuda_graphs and p.is_cuda and type(self.runner) is LlamaPagedRunner:
+        # CUDA-graph decode: the single-GPU runner, and the tensor-parallel runner when its all-reduce is the
+        # graph-capturable peer-load kernel
+        if cuda_graphs and p.is_cuda and (type(self.runner) is LlamaPagedRunner or getattr(self.runner, "_sg", None) is not None):
             limit = max_model_len or min(getattr(cfg, "max_position_embeddings", 4096) or 4096, num_blocks * block_size)
             self.runner.enable_graphs(max_batch_size, limit)
         self.max_batch_size, self.max_prefill_tokens, self.policy = max_batch_size, max_prefill_tokens, policy

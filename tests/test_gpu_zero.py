@@ -64,3 +64,12 @@ def test_pipeline_ulysses_hierarchical_two_gpus():
            "127.0.0.1", "--master-port", "29651", os.path.join(HERE, "mp_pp_sp_gpu_check.py")]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=240, env=dict(os.environ, NCCL_NVLS_ENABLE="0"))
     assert r.returncode == 0 and "PP_SP_GPU_OK" in r.stdout, r.stdout[-4000:] + r.stderr[-1500:]
+
+
+def test_tensor_parallel_serving_two_gpus():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29661", os.path.join(HERE, "mp_tp_serving_gpu_check.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=240)
+    assert r.returncode == 0, r.stdout[-4000:] + r.stderr[-1500:]
