@@ -63,5 +63,7 @@ class SERMoE(Module):
             y = ep_experts_forward(self, x2, idx, w, base, plan=plan)
             return y.view(shape)
         base = self.shared(x2) if self.shared is not None else None
-        y = moe_ops.experts_forward(x2, idx, w, self.w1, self.w2, base, self.act, fp8=self.expert_fp8)
+        no_cap = not (self.capacity_factor and self.capacity_factor > 0)      # nothing was dropped: no need to look
+        y = moe_ops.experts_forward(x2, idx, w, self.w1, self.w2, base, self.act, fp8=self.expert_fp8,
+                                    all_valid=True if no_cap else None)
         return y.view(shape)

@@ -82,14 +82,16 @@ def enforce_capacity(idx, w, E, capacity):
 class MoEPlan:
     """Device-side routing metadata: expert segments padded to 128 rows, tile -> expert table, permutation."""
 
-    def __init__(self, idx, E):
+    def __init__(self, idx, E, all_valid=None):
+        """``all_valid``: True when the caller knows that no entry of ``idx`` is -1 (no capacity limit was applied),
+        which saves the device -> host read that finding out would cost; None: look."""
         T, k = idx.shape
         dev = idx.device
         self.T, self.k, self.E = T, k, E
         self.max_rows = (T * k + E * 127 + 127) // 128 * 128
         self.max_tiles = self.max_rows // 128
         valid = idx >= 0
-        if idx.is_cuda and _lib.available() and bool(valid.all()):
+        if idx.is_cuda and _lib.available() and (all_valid if all_valid is not None else bool(valid.all())):
             counts = torch.zeros(E, dtype=torch.int32, device=dev)
             counts.scatter_add_(0, idx.reshape(-1).long(), torch.ones(T * k, dtype=torch.int32, device=dev))
             self.offsets = torch.empty(E + 1, dtype=torch.int32, device=dev)
@@ -250,10 +252,10 @@ class _ExpertsFn(torch.autograd.Function):
         return dx, dw, deliver(W1, dW1), deliver(W2, dW2), (dy if ctx.has_base else None), None, None, None
 
 
-def experts_forward(x, idx, w, W1, W2, base=None, act="silu", fp8=False):
+def experts_forward(x, idx, w, W1, W2, base=None, act="silu", fp8=False, all_valid=None):
     """x [T, d]; idx int32 [T, k] (-1 = dropped); w fp32 [T, k]; returns [T, d]. ``fp8``: the two forward expert GEMMs
     run in block-scaled e4m3 (the backward GEMMs stay bf16 on the saved bf16 activations: straight-through)."""
-    plan = MoEPlan(idx, W1.shape[0])
+    plan = MoEPlan(idx, W1.shape[0], all_valid)
     return _ExpertsFn.apply(x, w, W1, W2, base, plan, act, fp8)
 
 
