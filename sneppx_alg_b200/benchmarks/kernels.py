@@ -161,7 +161,17 @@ def case_paged_decode(small, iters):
     q = _bf(B, Hq, D)
     with torch.no_grad():
         ms = _time(lambda: paged.paged_decode(q, kc, vc, tables, lens), iters)
-    return dict(shape=[B, Hq, Hkv, D, L], ms=ms, bytes=2 * 2 * B * L * Hkv * D)
+        old = os.environ.get("SX_PAGED_TC")
+        os.environ["SX_PAGED_TC"] = "0"
+        try:
+            ms_simt = _time(lambda: paged.paged_decode(q, kc, vc, tables, lens), iters)
+        finally:
+            if old is None:
+                del os.environ["SX_PAGED_TC"]
+            else:
+                os.environ["SX_PAGED_TC"] = old
+    return dict(shape=[B, Hq, Hkv, D, L], ms=ms, bytes=2 * 2 * B * L * Hkv * D, lib_ms=ms_simt,
+                lib="own SIMT kernel (SX_PAGED_TC=0)")
 
 
 def _case_dq(mode, small, iters):

@@ -209,6 +209,12 @@ __global__ void kv_append_kernel(__nv_bfloat16* __restrict__ qkv, long long row_
   }
 }
 
+// Shared with the tensor-core decode kernel (paged_attn_tc.cu).
+void paged_merge_launch(const float* o_part, const float* ml_part, void* out, long long out_row_stride, int B, int Hq,
+                        int D, int nsplit, cudaStream_t st) {
+  paged_merge_kernel<<<dim3(B, Hq), D, 0, st>>>(o_part, ml_part, (__nv_bfloat16*)out, out_row_stride, Hq, D, nsplit);
+}
+
 }  // namespace sx
 using namespace sx;
 
@@ -243,7 +249,7 @@ extern "C" int sx_paged_decode(const void* q, long long q_row_stride, const void
     if (G == 1) SX_PD(64, 1); else if (G == 2) SX_PD(64, 2); else if (G <= 4) SX_PD(64, 4); else SX_PD(64, 8);
   }
 #undef SX_PD
-  paged_merge_kernel<<<dim3(B, Hq), D, 0, st>>>(o_part, ml_part, (__nv_bfloat16*)out, out_row_stride, Hq, D, nsplit);
+  paged_merge_launch(o_part, ml_part, out, out_row_stride, B, Hq, D, nsplit, st);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }
 

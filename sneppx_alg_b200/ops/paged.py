@@ -2,6 +2,7 @@
 from __future__ import annotations
 
 import math
+import os
 
 import torch
 
@@ -55,6 +56,12 @@ def paged_decode_reference(q, k_cache, v_cache, block_table, seq_lens, scale=Non
     return out.to(q.dtype)
 
 
+def _use_tc(D, bs, G) -> bool:
+    """Tensor-core decode kernel: head size 128, block size a divisor of 128 (>= 8), at most 8 query heads per KV
+    head. ``SX_PAGED_TC=0`` selects the SIMT kernel."""
+    return D == 128 and bs >= 8 and 128 % bs == 0 and G <= 8 and os.environ.get("SX_PAGED_TC", "1") != "0"
+
+
 def paged_decode(q, k_cache, v_cache, block_table, seq_lens, scale=None):
     B, Hq, D = q.shape
     bs, Hkv = k_cache.shape[1], k_cache.shape[2]
@@ -65,12 +72,23 @@ def paged_decode(q, k_cache, v_cache, block_table, seq_lens, scale=None):
         if _dbg.ENABLED:
             _dbg.check_indices(block_table, 0, k_cache.shape[0], _dbg.SITE_BLOCK_TABLE)
         max_len = block_table.shape[1] * bs
-        ns = _lib.lib().sx_paged_decode_splits2(c_int(max_len), c_int(B * Hkv))
+        tc = _use_tc(D, bs, Hq // Hkv) and k_cache.is_contiguous() and v_cache.is_contiguous()
+        if tc:
+            ns = _lib.lib().sx_paged_decode_tc_splits(c_int(max_len), c_int(B * Hkv))
+        else:
+            ns = _lib.lib().sx_paged_decode_splits2(c_int(max_len), c_int(B * Hkv))
         out = torch.empty(B, Hq, D, dtype=q.dtype, device=q.device)
         if _dbg.ENABLED:
             _dbg.poison_(out)
         o_part = torch.empty(B * Hq * ns * D, dtype=torch.float32, device=q.device)
         ml = torch.empty(B * Hq * ns * 2, dtype=torch.float32, device=q.device)
+        if tc:
+            _lib.call("sx_paged_decode_tc", ptr(q), c_ll(q.stride(0)), ptr(k_cache), ptr(v_cache),
+                      c_ll(k_cache.shape[0]), ptr(block_table.to(torch.int32).contiguous()),
+                      ptr(seq_lens.to(torch.int32).contiguous()), ptr(out), c_ll(out.stride(0)), ptr(o_part), ptr(ml),
+                      c_int(B), c_int(Hq), c_int(Hkv), c_int(D), c_int(bs), c_int(block_table.shape[1]), c_int(ns),
+                      c_float(scale), ptr(_lib.status_word(q.device)), stream())
+            return out
         _lib.call("sx_paged_decode", ptr(q), c_ll(q.stride(0)), ptr(k_cache), ptr(v_cache),
                   ptr(block_table.to(torch.int32).contiguous()), ptr(seq_lens.to(torch.int32).contiguous()), ptr(out),
                   c_ll(out.stride(0)), ptr(o_part), ptr(ml), c_int(B), c_int(Hq), c_int(Hkv), c_int(D), c_int(bs),

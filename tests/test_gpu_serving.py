@@ -53,6 +53,47 @@ def test_kv_append_and_paged_decode():
     assert _rel(out, ref) < 2e-2
 
 
+@pytest.mark.parametrize("Hq,Hkv,bs", [(32, 8, 16), (8, 8, 16), (16, 2, 32), (12, 4, 8), (8, 2, 128)])
+def test_paged_decode_tensor_core(Hq, Hkv, bs, monkeypatch):
+    """Tensor-core decode kernel against the fp32 reference and against the SIMT kernel; cache rows that belong to no
+    sequence hold NaN, so any read past a sequence's end that reaches the output fails the test."""
+    import random
+    torch.manual_seed(1)
+    D = 128
+    lens = [1, 15, 128, 129, 700, 2304, 0, 1000]
+    B = len(lens)
+    need = sum((n + bs - 1) // bs for n in lens)
+    kc = torch.full((need + 3, bs, Hkv, D), float("nan"), device="cuda", dtype=torch.bfloat16)
+    vc = torch.full_like(kc, float("nan"))
+    order = list(range(need + 3))
+    random.Random(3).shuffle(order)
+    width = max((n + bs - 1) // bs for n in lens) + 2
+    tables = torch.zeros(B, width, dtype=torch.int32)
+    nxt = 0
+    for b, n in enumerate(lens):
+        nb = (n + bs - 1) // bs
+        blocks = order[nxt: nxt + nb]
+        nxt += nb
+        tables[b, :nb] = torch.tensor(blocks, dtype=torch.int32)
+        if n:
+            k = torch.randn(n, Hkv, D, device="cuda", dtype=torch.bfloat16)
+            v = torch.randn(n, Hkv, D, device="cuda", dtype=torch.bfloat16)
+            idx = torch.tensor(blocks, device="cuda").repeat_interleave(bs)[:n] * bs + torch.arange(n, device="cuda") % bs
+            kc.view(-1, Hkv, D)[idx] = k
+            vc.view(-1, Hkv, D)[idx] = v
+    q = (torch.randn(B, Hq, D, device="cuda") * 1.5).to(torch.bfloat16)
+    sl = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    assert paged._use_tc(D, bs, Hq // Hkv)
+    out = paged.paged_decode(q, kc, vc, tables.cuda(), sl)
+    ops.check_status()
+    ref = paged.paged_decode_reference(q.float(), kc.float(), vc.float(), tables.cuda(), sl)
+    assert torch.isfinite(out.float()).all()
+    assert _rel(out, ref) < 2e-2
+    monkeypatch.setenv("SX_PAGED_TC", "0")
+    simt = paged.paged_decode(q, kc, vc, tables.cuda(), sl)
+    assert _rel(out, simt) < 2e-2
+
+
 @pytest.mark.parametrize("mode", ["fp8", "int4"])
 @pytest.mark.parametrize("M,N,K", [(64, 512, 1024), (300, 1000, 256), (2048, 4096, 4096)])
 def test_dequant_gemm(mode, M, N, K):
