@@ -3,7 +3,7 @@ time whole NumPy ops; here every case is one native sm_100a kernel).
 
 ``python -m sneppx_alg_b200.benchmarks.kernels <case> [--small] [--iters N] [--out file.json]``
 
-Cases: gemm, gemm_wgrad, attn_fwd, attn_bwd, rmsnorm, glu, rope, ce, adamw, sumsq, paged_decode, gemm_dq_fp8,
+Cases: gemm, gemm_decode, gemm_wgrad, attn_fwd, attn_bwd, rmsnorm, glu, rope, ce, adamw, sumsq, paged_decode, gemm_dq_fp8,
 gemm_dq_int4, gemm_fp8, gemm_fp8_prefill, conv1d, conv1d_bwd, ssd_fwd, ssd_bwd, router, quant_fp8, dropout, rng_normal, layernorm_bwd, block_top2, conv2d_bwd, npe_interp, all.  ``--small`` picks a problem that still exceeds L2 but holds well
 under 2 GB so that one launch can be captured by a profiler in seconds.  Timing: CUDA events on the launching
 stream after 3 warm-up launches; inputs are larger than L2 or rotated between iterations.  Fractions are against the
@@ -148,6 +148,59 @@ def case_sumsq(small, iters):
     g = torch.randn(n, device="cuda", dtype=torch.bfloat16)
     ms = _time(lambda: grad_norm_([g]), iters)
     return dict(shape=[n], ms=ms, bytes=2 * n)
+
+
+def _graph_time(fn, iters):
+    """Device time of ``fn`` (a sequence of launches) replayed from a CUDA graph: no host time between launches."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        fn()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        fn()
+    return _time(g.replay, iters)
+
+
+def case_gemm_decode(small, iters):
+    """The four weight GEMMs of one Llama-3-8B decoder layer (and the LM head) at 64 rows of activations: weight
+    streaming, so the fraction is of copy bandwidth. Every shape has several weight copies that are used in turn (more
+    than L2 holds together), and the launches are replayed from a CUDA graph so that host time is not in the figure."""
+    from ..ops.gemm import gemm
+    M = 64
+    shapes = [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336)] + ([] if small else [(128256, 4096)])
+    copies = [max(2, min(8, (320 << 20) // (2 * n * k))) for n, k in shapes]
+    ws = [[_bf(n, k) for _ in range(c)] for (n, k), c in zip(shapes, copies)]
+    xs = [_bf(M, k) for _, k in shapes]
+    outs = [torch.empty(M, n, device="cuda", dtype=torch.bfloat16) for n, _ in shapes]
+    rounds = max(copies)
+
+    def ours():
+        for i in range(rounds):
+            for w, x, o in zip(ws, xs, outs):
+                gemm(x, w[i % len(w)], out=o)
+
+    def lib():
+        for i in range(rounds):
+            for w, x, o in zip(ws, xs, outs):
+                torch.matmul(x, w[i % len(w)].t(), out=o)
+
+    ms = _graph_time(ours, iters) / rounds
+    ms_lib = _graph_time(lib, iters) / rounds
+    per, per_lib = {}, {}
+    for (n, k), w, x, o in zip(shapes, ws, xs, outs):
+        def one(f):
+            def run():
+                for wi in w:
+                    f(wi)
+            return _graph_time(run, iters) / len(w) * 1e3
+        per[f"{n}x{k}"] = round(one(lambda wi: gemm(x, wi, out=o)), 1)
+        per_lib[f"{n}x{k}"] = round(one(lambda wi: torch.matmul(x, wi.t(), out=o)), 1)
+    byt = sum(2 * n * k + 2 * M * k + 2 * M * n for n, k in shapes)
+    return dict(shape=[M, shapes], ms=ms, bytes=byt, flops=sum(2 * M * n * k for n, k in shapes), lib_ms=ms_lib,
+                lib="cuBLAS", per_shape_us=per, per_shape_us_lib=per_lib)
 
 
 def case_paged_decode(small, iters):

@@ -1013,9 +1013,14 @@ static int launch_cfg2_any(const GemmKernelParams& kp, int am, int bm, int sms, 
 
 }  // namespace sx
 
+extern "C" int sx_gemm_skinny_ok(const SxGemmArgs* a);
+extern "C" int sx_gemm_skinny(const SxGemmArgs* a, cudaStream_t st);
+
 static int gemm_launch(const SxGemmArgs* a, const SxGemmCommArgs* cm, cudaStream_t st) {
   using namespace sx;
   if (a->M <= 0 || a->N <= 0 || a->batch <= 0) return 0;
+  // decode-sized products stream the weight on the cluster split-K kernel (gemm_skinny.cu)
+  if (!cm && sx_gemm_skinny_ok(a)) return sx_gemm_skinny(a, st);
   if ((a->lda % 8) || (a->ldb % 8) || (reinterpret_cast<uintptr_t>(a->A) & 15) ||
       (reinterpret_cast<uintptr_t>(a->B) & 15))
     return -1;

@@ -1,7 +1,7 @@
 // A3 on the tensor cores: paged decode attention for head size 128 with the query heads of one KV head as the
 // N dimension of tcgen05 MMAs ("swap A/B": the 128 cached positions of a tile are the M rows).
 //
-// One CTA owns (sequence b, KV head hk, split) and walks its 128-position tiles of the block pool:
+// A work item is (sequence b, KV head hk, split); a CTA walks the 128-position tiles of its items in the block pool:
 //   S^T = K_tile Q^T        M=128 positions, N=16 (query heads of this KV head, padded), K=D; fp32 in TMEM
 //   P^T = exp2(S^T - m)     one cached position per thread (TMEM lane == position): G exponentials per thread
 //                           instead of 128, the running max per head shared through shared memory
@@ -24,9 +24,9 @@ constexpr int PT_MAX_G = 8;
 constexpr int PT_STAGES = 3;
 constexpr int PT_THREADS = 192;  // warps 0-3: softmax / epilogue (TMEM lane quadrants 0-3), warp 4: MMA, warp 5: TMA
 constexpr int PT_KV_BYTES = PT_BN * PT_D * 2;          // one K or V tile
-constexpr int PT_Q_BYTES = PT_NQ * PT_D * 2;           // 4 KB: Q rows, then the same size again for P^T
-constexpr int PT_OFF_P = PT_Q_BYTES;
-constexpr int PT_OFF_ST = 2 * PT_Q_BYTES;              // stages: [K tile][V tile]
+constexpr int PT_Q_BYTES = PT_NQ * PT_D * 2;           // 4 KB: two buffers of Q rows, then the same size for P^T
+constexpr int PT_OFF_P = 2 * PT_Q_BYTES;
+constexpr int PT_OFF_ST = 3 * PT_Q_BYTES + 1024;       // stages: [K tile][V tile], 1024-byte aligned
 constexpr int PT_OFF_BAR = PT_OFF_ST + PT_STAGES * 2 * PT_KV_BYTES;
 constexpr int PT_SMEM = PT_OFF_BAR + 1024 + 1024;
 constexpr int PT_TMEM_COLS = 32;                       // S^T at +0, O^T at +16
@@ -38,7 +38,7 @@ struct PagedTcParams {
   float* o_part;
   float* ml_part;
   int* status;
-  int Hq, Hkv, block_size, max_blocks, nsplit;
+  int B, Hq, Hkv, block_size, max_blocks, nsplit;
   float scale_log2;
 };
 
@@ -51,17 +51,42 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
       : "memory");
 }
 
+struct PtItem {
+  int b, hk, split, len, t0, n_steps;
+};
+
+// Work item `item` of the (split, KV head, sequence) space, sequences fastest so that neighbouring CTAs hold different
+// sequences; its tile range comes from the sequence length on the device.
+__device__ __forceinline__ PtItem pt_item(const PagedTcParams& p, int item) {
+  PtItem w;
+  w.b = item % p.B;
+  const int rest = item / p.B;
+  w.hk = rest % p.Hkv;
+  w.split = rest / p.Hkv;
+  w.len = p.seq_lens[w.b];
+  const int tiles = (w.len + PT_BN - 1) / PT_BN;
+  const int per = (tiles + p.nsplit - 1) / p.nsplit;
+  w.t0 = w.split * per;
+  const int t1 = min(tiles, w.t0 + per);
+  w.n_steps = t1 > w.t0 ? t1 - w.t0 : 0;
+  return w;
+}
+
+// Persistent: one CTA per SM walks items blockIdx.x, blockIdx.x + gridDim.x, ...; the TMA warp runs ahead across item
+// boundaries (the stage ring and every barrier phase are counted over the CTA's whole life), so the cache stream does
+// not stop while an item's result is written out.
 __global__ void __launch_bounds__(PT_THREADS, 1) paged_decode_tc_kernel(const __grid_constant__ PagedTcParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sQ = smem;
+  uint8_t* sQ = smem;                      // two Q buffers
   uint8_t* sP = smem + PT_OFF_P;
   uint8_t* sSt = smem + PT_OFF_ST;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PT_OFF_BAR);
-  uint64_t* q_full = bars;                 // 1
-  uint64_t* full = bars + 1;               // [PT_STAGES]
-  uint64_t* empty = bars + 1 + PT_STAGES;  // [PT_STAGES]
-  uint64_t* s_full = bars + 1 + 2 * PT_STAGES;
+  uint64_t* q_full = bars;                 // [2]
+  uint64_t* q_empty = bars + 2;            // [2]
+  uint64_t* full = bars + 4;               // [PT_STAGES]
+  uint64_t* empty = bars + 4 + PT_STAGES;  // [PT_STAGES]
+  uint64_t* s_full = bars + 4 + 2 * PT_STAGES;
   uint64_t* p_full = s_full + 1;           // 4 arrivals (one per softmax warp)
   uint64_t* o_done = s_full + 2;
   uint64_t* red_bar = s_full + 3;          // 4 arrivals: per-warp maxima / sums are in shared memory
@@ -70,17 +95,14 @@ __global__ void __launch_bounds__(PT_THREADS, 1) paged_decode_tc_kernel(const __
   float (*s_red)[4][PT_MAX_G] = reinterpret_cast<float (*)[4][PT_MAX_G]>(smem + PT_OFF_BAR + 256);  // [2][4][G]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int b = blockIdx.x, hk = blockIdx.y, split = blockIdx.z;
   const int G = p.Hq / p.Hkv;
-  const int len = p.seq_lens[b];
-  const int tiles = (len + PT_BN - 1) / PT_BN;
-  const int per = (tiles + p.nsplit - 1) / p.nsplit;
-  const int t0 = split * per;
-  const int t1 = min(tiles, t0 + per);
-  const int n_steps = t1 > t0 ? t1 - t0 : 0;
+  const int n_items = p.B * p.Hkv * p.nsplit;
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&q_full[i], 1);
+      mbar_init(&q_empty[i], 1);
+    }
     for (int i = 0; i < PT_STAGES; ++i) {
       mbar_init(&full[i], 1);
       mbar_init(&empty[i], 1);
@@ -112,20 +134,28 @@ __global__ void __launch_bounds__(PT_THREADS, 1) paged_decode_tc_kernel(const __
 
   if (warp == 5) {
     // ------------------------------------------------------------ TMA producer (whole warp: one box per lane)
-    if (n_steps > 0) {
+    const int bs = p.block_size;
+    const int nchunk = PT_BN / bs;       // cache blocks per tile
+    const int n_box = nchunk * 4;        // (K, V) x 2 slabs
+    uint32_t gt = 0, qi = 0;             // tiles / non-empty items so far
+    bool ok = true;
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+      const PtItem w = pt_item(p, item);
+      if (w.n_steps == 0) continue;
+      const int qb = qi & 1;
+      if (!mbar_wait_warp(&q_empty[qb], ((qi >> 1) & 1) ^ 1, s_abort, p.status, ST_TIMEOUT_PRODUCER)) break;
       if (lane == 0) {
-        mbar_expect_tx(q_full, PT_Q_BYTES);
-        tma5(sQ, &p.tmQ, q_full, hk * G, 0, 0, b);   // 16 head rows from head hk*G on; rows past Hq are zero-filled
+        mbar_expect_tx(&q_full[qb], PT_Q_BYTES);
+        // 16 head rows from head hk*G on; rows past Hq are zero-filled
+        tma5(sQ + qb * PT_Q_BYTES, &p.tmQ, &q_full[qb], w.hk * G, 0, 0, w.b);
       }
-      const int* tbl = p.block_table + (long long)b * p.max_blocks;
-      const int bs = p.block_size;
-      const int nchunk = PT_BN / bs;       // cache blocks per tile
-      const int n_box = nchunk * 4;        // (K, V) x 2 slabs
-      for (int j = 0; j < n_steps; ++j) {
-        const int s = j % PT_STAGES;
-        const uint32_t ph = (j / PT_STAGES) & 1;
-        const int kv0 = (t0 + j) * PT_BN;
-        if (!mbar_wait_warp(&empty[s], ph ^ 1, s_abort, p.status, ST_TIMEOUT_PRODUCER)) break;
+      ++qi;
+      const int* tbl = p.block_table + (long long)w.b * p.max_blocks;
+      for (int j = 0; j < w.n_steps; ++j, ++gt) {
+        const int s = gt % PT_STAGES;
+        const uint32_t ph = (gt / PT_STAGES) & 1;
+        const int kv0 = (w.t0 + j) * PT_BN;
+        if (!mbar_wait_warp(&empty[s], ph ^ 1, s_abort, p.status, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
         if (lane == 0) mbar_expect_tx(&full[s], 2 * PT_KV_BYTES);
         __syncwarp();
         uint8_t* st = sSt + s * 2 * PT_KV_BYTES;
@@ -135,166 +165,188 @@ __global__ void __launch_bounds__(PT_THREADS, 1) paged_decode_tc_kernel(const __
           const int i = rem >> 1, c = rem & 1;
           const int pos = kv0 + i * bs;
           // blocks past the end of the sequence are masked; any valid block keeps the tile finite
-          const int blk = pos < len ? tbl[pos / bs] : tbl[0];
-          tma5(st + which * PT_KV_BYTES + c * (PT_BN * 128) + i * bs * 128, which ? &p.tmV : &p.tmK, &full[s], 0, c, hk,
-               blk);
+          const int blk = pos < w.len ? tbl[pos / bs] : tbl[0];
+          tma5(st + which * PT_KV_BYTES + c * (PT_BN * 128) + i * bs * 128, which ? &p.tmV : &p.tmK, &full[s], 0, c,
+               w.hk, blk);
         }
       }
     }
   } else if (warp == 4) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0 && n_steps > 0) {
+    if (lane == 0) {
       constexpr uint32_t idesc_qk = umma_idesc_f16(PT_BN, PT_NQ, 1, 0, 0);   // A = K tile (K-major), B = Q (K-major)
       constexpr uint32_t idesc_pv = umma_idesc_f16(PT_D, PT_NQ, 1, 1, 0);    // A = V tile (MN-major), B = P^T (K-major)
-      const uint32_t q0 = smem_u32(sQ), p0 = smem_u32(sP);
-      bool ok = mbar_wait(q_full, 0, s_abort, p.status, ST_TIMEOUT_MMA);
-      for (int j = 0; j < n_steps && ok; ++j) {
-        const int s = j % PT_STAGES;
-        if (!mbar_wait(&full[s], (j / PT_STAGES) & 1, s_abort, p.status, ST_TIMEOUT_MMA)) break;
-        tc_fence_after();
-        const uint32_t k0 = smem_u32(sSt + s * 2 * PT_KV_BYTES), v0 = k0 + PT_KV_BYTES;
+      const uint32_t p0 = smem_u32(sP);
+      uint32_t gt = 0, qi = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+        const PtItem w = pt_item(p, item);
+        if (w.n_steps == 0) continue;
+        const int qb = qi & 1;
+        const uint32_t q0 = smem_u32(sQ + qb * PT_Q_BYTES);
+        if (!mbar_wait(&q_full[qb], (qi >> 1) & 1, s_abort, p.status, ST_TIMEOUT_MMA)) break;
+        for (int j = 0; j < w.n_steps; ++j, ++gt) {
+          const int s = gt % PT_STAGES;
+          if (!mbar_wait(&full[s], (gt / PT_STAGES) & 1, s_abort, p.status, ST_TIMEOUT_MMA)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t k0 = smem_u32(sSt + s * 2 * PT_KV_BYTES), v0 = k0 + PT_KV_BYTES;
 #pragma unroll
-        for (int c = 0; c < PT_D / 64; ++c)
+          for (int c = 0; c < PT_D / 64; ++c)
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma_f16_ss(tS, umma_desc_sw128(k0 + c * (PT_BN * 128) + k * 32, 16, 1024),
-                        umma_desc_sw128(q0 + c * (PT_NQ * 128) + k * 32, 16, 1024), idesc_qk, (c | k) ? 1u : 0u);
-        umma_commit(s_full);
-        if (!mbar_wait(p_full, j & 1, s_abort, p.status, ST_TIMEOUT_MMA)) break;
-        tc_fence_after();
+            for (int k = 0; k < 4; ++k)
+              umma_f16_ss(tS, umma_desc_sw128(k0 + c * (PT_BN * 128) + k * 32, 16, 1024),
+                          umma_desc_sw128(q0 + c * (PT_NQ * 128) + k * 32, 16, 1024), idesc_qk, (c | k) ? 1u : 0u);
+          umma_commit(s_full);
+          if (!mbar_wait(p_full, gt & 1, s_abort, p.status, ST_TIMEOUT_MMA)) { ok = false; break; }
+          tc_fence_after();
 #pragma unroll
-        for (int k = 0; k < PT_BN / 16; ++k)
-          umma_f16_ss(tO, umma_desc_sw128(v0 + k * 2048, PT_BN * 128, 1024),
-                      umma_desc_sw128(p0 + (k >> 2) * (PT_NQ * 128) + (k & 3) * 32, 16, 1024), idesc_pv,
-                      (j | k) ? 1u : 0u);
-        umma_commit(&empty[s]);
-        if (j + 1 == n_steps) umma_commit(o_done);
+          for (int k = 0; k < PT_BN / 16; ++k)
+            umma_f16_ss(tO, umma_desc_sw128(v0 + k * 2048, PT_BN * 128, 1024),
+                        umma_desc_sw128(p0 + (k >> 2) * (PT_NQ * 128) + (k & 3) * 32, 16, 1024), idesc_pv,
+                        (j | k) ? 1u : 0u);
+          umma_commit(&empty[s]);
+          if (j + 1 == w.n_steps) {
+            umma_commit(o_done);
+            umma_commit(&q_empty[qb]);
+          }
+        }
+        ++qi;
       }
     }
   } else {
     // ------------------------------------------------------------ softmax + epilogue: thread t <-> position t / dim t
     const int t = threadIdx.x;
     const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
-    float m[PT_MAX_G], l[PT_MAX_G];
-#pragma unroll
-    for (int g = 0; g < PT_MAX_G; ++g) { m[g] = -INFINITY; l[g] = 0.f; }
     // P^T rows of heads >= G stay zero for the whole kernel
     *reinterpret_cast<uint4*>(sP + t * 32) = make_uint4(0, 0, 0, 0);
     *reinterpret_cast<uint4*>(sP + t * 32 + 16) = make_uint4(0, 0, 0, 0);
     const uint32_t p_off = (t >> 6) * (PT_NQ * 128) + ((t & 7) << 1);   // slab and byte inside the 16-byte chunk
     const int p_chunk = (t & 63) >> 3;
     bool ok = true;
-    uint32_t red_phase = 0;
-    for (int j = 0; j < n_steps && ok; ++j) {
-      const int kv0 = (t0 + j) * PT_BN;
-      const bool valid = kv0 + t < len;
-      if (!mbar_wait_warp(s_full, j & 1, s_abort, p.status, ST_TIMEOUT_EPILOGUE)) { ok = false; break; }
-      tc_fence_after();
-      uint32_t r[16];
-      tmem_ld16(tS + lane_addr, r);
-      tmem_ld_wait();
-      float sc[PT_MAX_G];
-#pragma unroll
-      for (int g = 0; g < PT_MAX_G; ++g) {
-        sc[g] = (valid && g < G) ? __uint_as_float(r[g]) * p.scale_log2 : -INFINITY;
-        float v = sc[g];
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-        if (lane == 0) s_red[j & 1][warp][g] = v;
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(red_bar);
-      if (!mbar_wait_warp(red_bar, red_phase, s_abort, p.status, ST_TIMEOUT_EPILOGUE)) { ok = false; break; }
-      red_phase ^= 1;
-      float alpha[PT_MAX_G];
-      bool rescale = false;
-#pragma unroll
-      for (int g = 0; g < PT_MAX_G; ++g) {
-        const float mx = fmaxf(fmaxf(s_red[j & 1][0][g], s_red[j & 1][1][g]),
-                               fmaxf(s_red[j & 1][2][g], s_red[j & 1][3][g]));
-        alpha[g] = 1.f;
-        if ((mx > m[g] + 8.f || m[g] == -INFINITY) && mx != -INFINITY) {
-          if (m[g] == -INFINITY) alpha[g] = 0.f;
-          else { alpha[g] = exp2f(m[g] - mx); rescale = true; }
-          m[g] = mx;
+    uint32_t gt = 0, qi = 0, rc = 0;    // tiles, non-empty items, uses of red_bar so far
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+      const PtItem w = pt_item(p, item);
+      const long long row0 = ((long long)w.b * p.Hq + (long long)w.hk * G) * p.nsplit + w.split;   // + g * nsplit
+      if (w.n_steps == 0) {
+        for (int g = 0; g < G; ++g) {
+          const long long idx = row0 + (long long)g * p.nsplit;
+          p.o_part[idx * PT_D + t] = 0.f;
+          if (t == 0) { p.ml_part[idx * 2] = -INFINITY; p.ml_part[idx * 2 + 1] = 0.f; }
         }
+        continue;
       }
+      float m[PT_MAX_G], l[PT_MAX_G];
 #pragma unroll
-      for (int g = 0; g < PT_MAX_G; ++g) {
-        if (g < G) {
-          const float pv = valid ? exp2f(sc[g] - m[g]) : 0.f;
-          const __nv_bfloat16 pb = __float2bfloat16_rn(pv);
-          // the row sum uses the rounded value so that l matches what the P V product sees
-          l[g] = fmaf(l[g], alpha[g], __bfloat162float(pb));
-          *reinterpret_cast<__nv_bfloat16*>(sP + p_off + g * 128 + ((p_chunk ^ (g & 7)) << 4)) = pb;
-        }
-      }
-      // s_full(j) completed after P V of step j-1 (in-order tensor pipe): O^T and P^T are ours until p_full
-      if (j > 0 && rescale) {
-        uint32_t o[16];
-        tmem_ld16(tO + lane_addr, o);
+      for (int g = 0; g < PT_MAX_G; ++g) { m[g] = -INFINITY; l[g] = 0.f; }
+      for (int j = 0; j < w.n_steps && ok; ++j, ++gt) {
+        const int kv0 = (w.t0 + j) * PT_BN;
+        const bool valid = kv0 + t < w.len;
+        if (!mbar_wait_warp(s_full, gt & 1, s_abort, p.status, ST_TIMEOUT_EPILOGUE)) { ok = false; break; }
+        tc_fence_after();
+        uint32_t r[16];
+        tmem_ld16(tS + lane_addr, r);
         tmem_ld_wait();
+        float sc[PT_MAX_G];
 #pragma unroll
-        for (int g = 0; g < PT_MAX_G; ++g) o[g] = __float_as_uint(__uint_as_float(o[g]) * alpha[g]);
-        tmem_st16(tO + lane_addr, o);
-        tmem_st_wait();
-      }
-      if (kv0 + PT_BN > len) {
-        // last tile of the sequence: rows past the end may hold anything (0 * NaN would poison O), clear their V rows
-        const int s = j % PT_STAGES;
-        if (!mbar_wait_warp(&full[s], (j / PT_STAGES) & 1, s_abort, p.status, ST_TIMEOUT_EPILOGUE)) { ok = false; break; }
-        if (!valid) {
-          uint8_t* vrow = sSt + s * 2 * PT_KV_BYTES + PT_KV_BYTES + t * 128;
+        for (int g = 0; g < PT_MAX_G; ++g) {
+          sc[g] = (valid && g < G) ? __uint_as_float(r[g]) * p.scale_log2 : -INFINITY;
+          float v = sc[g];
 #pragma unroll
-          for (int c = 0; c < PT_D / 64; ++c)
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-              *reinterpret_cast<uint4*>(vrow + c * (PT_BN * 128) + i * 16) = make_uint4(0, 0, 0, 0);
+          for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+          if (lane == 0) s_red[rc & 1][warp][g] = v;
         }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(red_bar);
+        if (!mbar_wait_warp(red_bar, rc & 1, s_abort, p.status, ST_TIMEOUT_EPILOGUE)) { ok = false; break; }
+        float alpha[PT_MAX_G];
+        bool rescale = false;
+#pragma unroll
+        for (int g = 0; g < PT_MAX_G; ++g) {
+          const float mx = fmaxf(fmaxf(s_red[rc & 1][0][g], s_red[rc & 1][1][g]),
+                                 fmaxf(s_red[rc & 1][2][g], s_red[rc & 1][3][g]));
+          alpha[g] = 1.f;
+          if ((mx > m[g] + 8.f || m[g] == -INFINITY) && mx != -INFINITY) {
+            if (m[g] == -INFINITY) alpha[g] = 0.f;
+            else { alpha[g] = exp2f(m[g] - mx); rescale = true; }
+            m[g] = mx;
+          }
+        }
+        ++rc;
+#pragma unroll
+        for (int g = 0; g < PT_MAX_G; ++g) {
+          if (g < G) {
+            const float pv = valid ? exp2f(sc[g] - m[g]) : 0.f;
+            const __nv_bfloat16 pb = __float2bfloat16_rn(pv);
+            // the row sum uses the rounded value so that l matches what the P V product sees
+            l[g] = fmaf(l[g], alpha[g], __bfloat162float(pb));
+            *reinterpret_cast<__nv_bfloat16*>(sP + p_off + g * 128 + ((p_chunk ^ (g & 7)) << 4)) = pb;
+          }
+        }
+        // s_full of this tile completed after P V of the previous one (in-order tensor pipe): O^T and P^T are ours
+        if (j > 0 && rescale) {
+          uint32_t o[16];
+          tmem_ld16(tO + lane_addr, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int g = 0; g < PT_MAX_G; ++g) o[g] = __float_as_uint(__uint_as_float(o[g]) * alpha[g]);
+          tmem_st16(tO + lane_addr, o);
+          tmem_st_wait();
+        }
+        if (kv0 + PT_BN > w.len) {
+          // last tile of the sequence: rows past the end may hold anything (0 * NaN would poison O), clear their V rows
+          const int s = gt % PT_STAGES;
+          if (!mbar_wait_warp(&full[s], (gt / PT_STAGES) & 1, s_abort, p.status, ST_TIMEOUT_EPILOGUE)) { ok = false; break; }
+          if (!valid) {
+            uint8_t* vrow = sSt + s * 2 * PT_KV_BYTES + PT_KV_BYTES + t * 128;
+#pragma unroll
+            for (int c = 0; c < PT_D / 64; ++c)
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                *reinterpret_cast<uint4*>(vrow + c * (PT_BN * 128) + i * 16) = make_uint4(0, 0, 0, 0);
+          }
+        }
+        fence_proxy_async_smem();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(p_full);
       }
-      fence_proxy_async_smem();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(p_full);
-    }
-    // ---- epilogue: partial result of this split for the merge kernel
-    const long long row0 = ((long long)b * p.Hq + (long long)hk * G) * p.nsplit + split;   // + g * nsplit
-    if (n_steps == 0) {
-      for (int g = 0; g < G; ++g) {
-        const long long idx = row0 + (long long)g * p.nsplit;
-        p.o_part[idx * PT_D + t] = 0.f;
-        if (t == 0) { p.ml_part[idx * 2] = -INFINITY; p.ml_part[idx * 2 + 1] = 0.f; }
-      }
-    } else if (ok) {
-      // total row sums: every thread holds the partial sum of its own positions
+      if (!ok) break;
+      // ---- partial result of this item for the merge kernel. Total row sums: every thread holds the partial sum of
+      // its own positions.
 #pragma unroll
       for (int g = 0; g < PT_MAX_G; ++g) {
         float v = l[g];
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-        if (lane == 0) s_red[n_steps & 1][warp][g] = v;
+        if (lane == 0) s_red[rc & 1][warp][g] = v;
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(red_bar);
-      if (mbar_wait_warp(red_bar, red_phase, s_abort, p.status, ST_TIMEOUT_EPILOGUE) &&
-          mbar_wait_warp(o_done, 0, s_abort, p.status, ST_TIMEOUT_EPILOGUE)) {
-        tc_fence_after();
-        uint32_t o[16];
-        tmem_ld16(tO + lane_addr, o);
-        tmem_ld_wait();
+      if (!mbar_wait_warp(red_bar, rc & 1, s_abort, p.status, ST_TIMEOUT_EPILOGUE) ||
+          !mbar_wait_warp(o_done, qi & 1, s_abort, p.status, ST_TIMEOUT_EPILOGUE)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      uint32_t o[16];
+      tmem_ld16(tO + lane_addr, o);
+      tmem_ld_wait();
+      // the next item's first P V (which overwrites O^T) waits for this thread's next p_full arrival
+      tc_fence_before();
 #pragma unroll
-        for (int g = 0; g < PT_MAX_G; ++g) {
-          if (g < G) {
-            const long long idx = row0 + (long long)g * p.nsplit;
-            p.o_part[idx * PT_D + t] = __uint_as_float(o[g]);
-            if (t == 0) {
-              const int x = n_steps & 1;
-              p.ml_part[idx * 2] = m[g] * 0.6931471805599453f;   // natural-log units for the merge
-              p.ml_part[idx * 2 + 1] = s_red[x][0][g] + s_red[x][1][g] + s_red[x][2][g] + s_red[x][3][g];
-            }
+      for (int g = 0; g < PT_MAX_G; ++g) {
+        if (g < G) {
+          const long long idx = row0 + (long long)g * p.nsplit;
+          p.o_part[idx * PT_D + t] = __uint_as_float(o[g]);
+          if (t == 0) {
+            const int x = rc & 1;
+            p.ml_part[idx * 2] = m[g] * 0.6931471805599453f;   // natural-log units for the merge
+            p.ml_part[idx * 2 + 1] = s_red[x][0][g] + s_red[x][1][g] + s_red[x][2][g] + s_red[x][3][g];
           }
         }
       }
+      ++rc;
+      ++qi;
     }
   }
 
@@ -313,18 +365,17 @@ void paged_merge_launch(const float* o_part, const float* ml_part, void* out, lo
 }  // namespace sx
 using namespace sx;
 
-// Splits for the tensor-core kernel: one CTA per SM, so pick the split count that minimises
-// waves x (tiles per split + fixed cost of a CTA, about two tiles).
+// Splits for the tensor-core kernel. It is persistent (one CTA per SM walks the (split, KV head, sequence) items), so
+// splits only set the granularity: items of about six tiles keep the SMs evenly loaded, and there are at least two
+// items per SM when the batch is small.
 extern "C" int sx_paged_decode_tc_splits(int max_len, int ctas_per_split) {
   const int tiles = (max_len + PT_BN - 1) / PT_BN;
-  int best = 1;
-  long long best_cost = -1;
-  for (int s = 1; s <= 32 && s <= (tiles > 1 ? tiles : 1); ++s) {
-    const long long waves = ((long long)ctas_per_split * s + 147) / 148;
-    const long long cost = waves * ((tiles + s - 1) / s + 2);
-    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = s; }
-  }
-  return best;
+  const int by_size = (tiles + 5) / 6;
+  const int by_fill = (2 * 148 + ctas_per_split - 1) / (ctas_per_split > 0 ? ctas_per_split : 1);
+  int s = by_size > by_fill ? by_size : by_fill;
+  if (s > tiles) s = tiles;
+  if (s > 32) s = 32;
+  return s < 1 ? 1 : s;
 }
 
 // Same contract as sx_paged_decode (o_part: fp32 [B, Hq, nsplit, D], ml_part: fp32 [B, Hq, nsplit, 2] scratch);
@@ -360,7 +411,7 @@ extern "C" int sx_paged_decode_tc(const void* q, long long q_row_stride, const v
   p.o_part = o_part;
   p.ml_part = ml_part;
   p.status = status;
-  p.Hq = Hq; p.Hkv = Hkv; p.block_size = block_size; p.max_blocks = max_blocks; p.nsplit = nsplit;
+  p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.block_size = block_size; p.max_blocks = max_blocks; p.nsplit = nsplit;
   p.scale_log2 = scale * 1.4426950408889634f;
   static bool set = false;
   if (!set) {
@@ -369,7 +420,14 @@ extern "C" int sx_paged_decode_tc(const void* q, long long q_row_stride, const v
       return -10;
     set = true;
   }
-  paged_decode_tc_kernel<<<dim3(B, Hkv, nsplit), PT_THREADS, PT_SMEM, st>>>(p);
+  static int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+  }
+  const long long items = (long long)B * Hkv * nsplit;
+  paged_decode_tc_kernel<<<(unsigned)(items < sms ? items : sms), PT_THREADS, PT_SMEM, st>>>(p);
   paged_merge_launch(o_part, ml_part, out, out_row_stride, B, Hq, D, nsplit, st);
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }

@@ -1,4 +1,6 @@
 """tcgen05 GEMM (G1/G2) against an fp32 PyTorch reference of the same op."""
+import ctypes
+
 import pytest
 import torch
 
@@ -24,6 +26,43 @@ def test_gemm_layouts(M, N, K, a_mn, b_mn):
     ref = gemm_reference(a, b, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32)
     ops.check_status()
     assert _rel(d, ref) < 1e-2
+
+
+@pytest.mark.parametrize("M", [1, 7, 16, 33, 64, 100, 128])
+@pytest.mark.parametrize("N,K", [(128, 256), (1000, 520), (4096, 4096), (6144, 4096), (4096, 14336), (50048, 1024)])
+def test_gemm_decode_sized_cluster_split_k(M, N, K):
+    """Decode-sized products go to the cluster split-K kernel: every cluster size from 1 to 8, ragged N and K tails,
+    activation rows that do not divide by the cluster size."""
+    from sneppx_alg_b200.ops import _lib
+    torch.manual_seed(M * 7 + N)
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.1
+    args = _lib.SxGemmArgs()
+    args.M, args.N, args.K, args.batch = M, N, K, 1
+    assert _lib.lib().sx_gemm_skinny_ok(ctypes.byref(args)) == 1
+    d = gemm(a, b)
+    ref = gemm_reference(a, b, out_dtype=torch.float32)
+    ops.check_status()
+    assert _rel(d, ref) < 1e-2
+    # same values on a second call (the reduction order over the cluster is fixed)
+    assert torch.equal(d, gemm(a, b))
+
+
+def test_gemm_decode_sized_epilogue_and_strided_out():
+    torch.manual_seed(5)
+    M, N, K = 48, 1536, 2048
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.1
+    bias = torch.randn(N, device="cuda", dtype=torch.float32)
+    for act in (None, "silu", "gelu", "relu"):
+        d = gemm(a, b, alpha=0.5, bias=bias, act=act, out_dtype=torch.float32)
+        ref = gemm_reference(a, b, alpha=0.5, bias=bias, act=act, out_dtype=torch.float32)
+        assert _rel(d, ref) < 1e-2
+    wide = torch.zeros(M, N + 64, device="cuda", dtype=torch.bfloat16)
+    gemm(a, b, out=wide[:, 32: 32 + N])
+    ops.check_status()
+    assert _rel(wide[:, 32: 32 + N], gemm_reference(a, b, out_dtype=torch.float32)) < 1e-2
+    assert float(wide[:, :32].abs().max()) == 0.0 and float(wide[:, 32 + N:].abs().max()) == 0.0
 
 
 def test_gemm_epilogue_bias_beta_act_fp32out():
