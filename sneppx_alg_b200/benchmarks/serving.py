@@ -60,8 +60,20 @@ def run(model, requests=64, prompt_len=2048, new_tokens=256, max_prefill_tokens=
             "total_tokens_per_s": (out_tokens + eng.stats["prefill_tokens"]) / dt}
 
 
-def run_http(model, requests=64, prompt_len=2048, new_tokens=256, max_prefill_tokens=16384, block_size=16, seed=0) -> dict:
-    """The workload of ``run`` sent through ``POST /v1/generate`` of the FastAPI front-end (uvicorn, loopback)."""
+def _engine_kwargs(requests, prompt_len, new_tokens, max_prefill_tokens, block_size, tp_group=None):
+    blocks = requests * ((prompt_len + new_tokens + block_size - 1) // block_size) + 64
+    kw = dict(num_blocks=blocks, block_size=block_size, max_batch_size=requests, max_prefill_tokens=max_prefill_tokens,
+              enable_prefix_cache=False)
+    if tp_group is not None:
+        kw["tp_group"] = tp_group
+    return kw
+
+
+def run_http(model, requests=64, prompt_len=2048, new_tokens=256, max_prefill_tokens=16384, block_size=16, seed=0,
+             tp_group=None) -> dict:
+    """The workload of ``run`` sent through ``POST /v1/generate`` of the FastAPI front-end (uvicorn, loopback). With
+    ``tp_group`` this is the leader's side of tensor-parallel serving; the other ranks run ``serving.server.tp_follow``
+    with the same engine arguments."""
     import http.client
     import socket
     import threading
@@ -70,10 +82,8 @@ def run_http(model, requests=64, prompt_len=2048, new_tokens=256, max_prefill_to
 
     from ..serving.server import create_app
     cfg = model.config
-    blocks = requests * ((prompt_len + new_tokens + block_size - 1) // block_size) + 64
-    app = create_app({"bench": {"model": model, "engine_kwargs": dict(
-        num_blocks=blocks, block_size=block_size, max_batch_size=requests, max_prefill_tokens=max_prefill_tokens,
-        enable_prefix_cache=False)}})
+    app = create_app({"bench": {"model": model, "engine_kwargs": _engine_kwargs(
+        requests, prompt_len, new_tokens, max_prefill_tokens, block_size, tp_group)}})
     with socket.socket() as sck:
         sck.bind(("127.0.0.1", 0))
         port = sck.getsockname()[1]
@@ -146,7 +156,8 @@ def main(argv=None):
     ap.add_argument("--new-tokens", type=int, default=256)
     ap.add_argument("--quantize", choices=["none", "fp8", "int4"], default="none")
     ap.add_argument("--max-prefill-tokens", type=int, default=16384)
-    ap.add_argument("--http", action="store_true", help="send the requests through POST /v1/generate (one GPU)")
+    ap.add_argument("--http", action="store_true",
+                    help="send the requests through POST /v1/generate (under torchrun: rank 0 serves, the others mirror)")
     ap.add_argument("--out", default=None)
     a = ap.parse_args(argv)
     import os
@@ -172,8 +183,13 @@ def main(argv=None):
     if a.quantize != "none":
         from ..ops.quant import quantize_model_
         quantize_model_(model, a.quantize)
-    if a.http and world == 1:
-        r = run_http(model, a.requests, a.prompt_len, a.new_tokens, a.max_prefill_tokens)
+    if a.http and world > 1 and rank != 0:
+        from ..serving.server import tp_follow
+        with torch.no_grad():
+            tp_follow(model, _engine_kwargs(a.requests, a.prompt_len, a.new_tokens, a.max_prefill_tokens, 16, tp_group))
+        r = {}
+    elif a.http:
+        r = run_http(model, a.requests, a.prompt_len, a.new_tokens, a.max_prefill_tokens, tp_group=tp_group)
     else:
         r = run(model, a.requests, a.prompt_len, a.new_tokens, a.max_prefill_tokens, tp_group=tp_group)
     r["config"] = {"model": a.model, "weights": "bf16" if a.quantize == "none" else a.quantize, "kv_cache": "bf16" if cuda else "fp32",

@@ -77,6 +77,105 @@ class EngineWorker:
         self._stop = True
 
 
+class TPEngineWorker(EngineWorker):
+    """Tensor-parallel form of the worker. Every rank of ``group`` owns an ``LLMEngine`` over its shard of the model;
+    the engines only stay consistent if all of them see the same requests in the same order and step together. The
+    leader (group rank 0) takes submissions from the HTTP handlers; once per loop iteration it broadcasts the new
+    ones (a three-word header, then the pickled prompts and sampling parameters when there are any) and every rank
+    submits them and takes one engine step. The other ranks run ``follow()``, which returns when the leader stops.
+    Requests with a ``stop_fn`` are refused: the callable lives on the leader only."""
+
+    def __init__(self, engine: LLMEngine, group):
+        import torch.distributed as dist
+        self.group = group
+        self.leader = dist.get_rank(group) == 0
+        self.src = dist.get_global_rank(group, 0)
+        self.dev = next(engine.runner.model.parameters()).device
+        self._pending: list = []
+        self._next_rid = 0
+        if self.leader:
+            super().__init__(engine)     # starts the loop thread
+        else:
+            self.engine, self._stop = engine, False
+            self._lock, self._events, self._callbacks = threading.Lock(), {}, {}
+
+    def _exchange(self, items, stop):
+        import pickle
+
+        import torch
+        import torch.distributed as dist
+        payload = pickle.dumps(items) if (self.leader and items) else b""
+        hdr = torch.tensor([len(items), len(payload), int(stop)] if self.leader else [0, 0, 0], dtype=torch.int64,
+                           device=self.dev)
+        dist.broadcast(hdr, self.src, group=self.group)
+        n, nbytes, stop = hdr.tolist()
+        if nbytes:
+            if self.leader:
+                buf = torch.frombuffer(bytearray(payload), dtype=torch.uint8).to(self.dev)
+            else:
+                buf = torch.empty(nbytes, dtype=torch.uint8, device=self.dev)
+            dist.broadcast(buf, self.src, group=self.group)
+            if not self.leader:
+                items = pickle.loads(buf.cpu().numpy().tobytes())    # from a rank of the same job
+        return items if n else [], bool(stop)
+
+    def _loop(self):
+        from dataclasses import asdict
+        if self.dev.type == "cuda":
+            import torch
+            torch.cuda.set_device(self.dev)      # the leader's loop runs on a thread of its own
+        while True:
+            with self._lock:
+                new, self._pending = self._pending, []
+                stop = self._stop
+            items, stop = self._exchange([(p, asdict(sp)) for p, sp, _, _ in new] if self.leader else [], stop)
+            with self._lock:
+                for i, (prompt, pd) in enumerate(items):
+                    pd["stop_token_ids"] = tuple(pd.get("stop_token_ids", ()))
+                    rid = self.engine.submit(prompt, SamplingParams(**pd), on_token=new[i][2] if self.leader else None)
+                    if self.leader and rid != new[i][3]:
+                        raise RuntimeError("request ids of the tensor-parallel engines diverged")
+                if stop:
+                    return
+                work = self.engine.has_work()
+                if work:
+                    self.engine.step()
+                    for rid in list(self._events):
+                        if rid in self.engine.finished or rid in self.engine.failed:
+                            self._events.pop(rid).set()
+                            cb = self._callbacks.pop(rid, None)
+                            if cb is not None:
+                                cb()
+            if not work and self.leader:
+                time.sleep(0.002)
+
+    follow = _loop
+
+    def submit(self, prompt_ids, params, on_token=None, on_done=None):
+        if params.stop_fn is not None:
+            raise ValueError("stop strings / stop_fn are not supported by tensor-parallel serving")
+        ev = threading.Event()
+        with self._lock:
+            rid = self._next_rid
+            self._next_rid += 1
+            self._pending.append((list(prompt_ids), params, on_token, rid))
+            self._events[rid] = ev
+            if on_done is not None:
+                self._callbacks[rid] = on_done
+        return rid, ev
+
+    def stop(self):
+        self._stop = True
+        if self.leader:
+            self.thread.join(30)
+
+
+def tp_follow(model, engine_kwargs: dict):
+    """What the ranks other than group rank 0 run while rank 0 serves HTTP: build the same engine and mirror it."""
+    eng = LLMEngine(model, **engine_kwargs)
+    TPEngineWorker(eng, engine_kwargs["tp_group"]).follow()
+
+
 def create_app(models: Dict[str, dict], default_model: Optional[str] = None, api_keys: Optional[set] = None,
                admin_key: Optional[str] = None):
     """models: {model_id: {"model": LlamaForCausalLM, "tokenizer": obj with encode/decode (optional), "engine_kwargs": {...}}}"""
@@ -94,7 +193,8 @@ def create_app(models: Dict[str, dict], default_model: Optional[str] = None, api
     default_model = default_model or next(iter(models))
     for mid, spec in models.items():
         eng = LLMEngine(spec["model"], **spec.get("engine_kwargs", {}))
-        workers[mid] = EngineWorker(eng)
+        tpg = spec.get("engine_kwargs", {}).get("tp_group")
+        workers[mid] = TPEngineWorker(eng, tpg) if tpg is not None else EngineWorker(eng)
         toks[mid] = spec.get("tokenizer") or ByteTokenizer(spec["model"].config.vocab_size)
         control.register_model(mid, "v1", handler=lambda *a, **k: None)
         control.deploy(mid, "v1", 1.0)

@@ -97,6 +97,17 @@ def test_tensor_parallel_engine_matches_single_rank_tokens():
     assert r.returncode == 0 and "TP_SERVING_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
 
 
+def test_tensor_parallel_serving_over_http_matches_single_rank_tokens():
+    """Rank 0 serves POST /v1/generate, rank 1 mirrors it (requests broadcast once per engine step)."""
+    import os
+    import subprocess
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    r = subprocess.run([sys.executable, os.path.join(here, "mp_tp_http_check.py"), "2", str(29840 + os.getpid() % 9)],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "TP_HTTP_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-4000:]
+
+
 def test_prefix_cache_gives_blocks_back_under_pressure():
     """A pool mostly pinned by cached prefixes must still admit new requests (entries nobody shares are evicted,
     least recently used first), never run dry in the middle of a generation, and fail a request that can never
