@@ -11,7 +11,9 @@
 // issue order, which is what makes the S/P aliasing safe. The running max is only refreshed when
 // it grew by more than 2^8, so rescaling O in TMEM is rare. Causal / sliding-window masks, GQA head
 // mapping and the differential-attention V mapping (two score heads share one V head) are index
-// arithmetic; nothing is materialised.
+// arithmetic; nothing is materialised. An optional block mask (one byte per 128 x 128 score tile, per head or
+// shared) removes whole tiles from the walk: a step whose tile is masked for both query tiles is neither loaded nor
+// multiplied (block-sparse / flex-attention patterns at tile granularity).
 // Takes the place of the reference's SIMT flash-attention forward, GQA and block-sparse kernels
 // (kernel/cuda/attention_cuda.cu:37-328, 498-573, 1154-1230) and its empty "v3" kernel (:1262-1286).
 #include <limits.h>
@@ -35,6 +37,9 @@ struct AttnFwdParams {
   int v_head_div;  // V head = (K head) / v_head_div
   int causal, window;  // window <= 0: unlimited
   float scale_log2;    // softmax scale * log2(e)
+  const uint8_t* block_mask;   // optional [B or 1][Hq or 1][q tiles][kv tiles], non-zero = tile takes part
+  long long bm_batch_stride, bm_head_stride;
+  int bm_kv_tiles;
 };
 
 template <int D>
@@ -65,7 +70,7 @@ __device__ __forceinline__ void kv_range(const AttnFwdParams& p, int q0, int& lo
   if (hi < lo) hi = lo;
 }
 
-template <int D>
+template <int D, bool MASK>
 __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_constant__ AttnFwdParams p) {
   using Cfg = AttnCfg<D>;
   extern __shared__ uint8_t smem_raw[];
@@ -101,7 +106,25 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
 #pragma unroll
   for (int x = 0; x < 2; ++x)
     if (hi[x] > lo[x]) { jlo = min(jlo, lo[x]); jhi = max(jhi, hi[x]); }
-  const int n_steps = jhi > jlo ? jhi - jlo : 0;
+  // tile X takes part in the step of kv tile jt?
+  const uint8_t* bm = MASK ? p.block_mask + b * p.bm_batch_stride + head * p.bm_head_stride : nullptr;
+  auto on = [&](int x, int jt) -> bool {
+    if (jt < lo[x] || jt >= hi[x]) return false;
+    if constexpr (!MASK) return true;
+    else return bm[(long long)(pair * 2 + x) * p.bm_kv_tiles + jt] != 0;
+  };
+  // next kv tile after jt that any of the two tiles takes part in (-1: none)
+  auto next_step = [&](int jt) -> int {
+    if constexpr (!MASK) {
+      return jt + 1 < jhi ? jt + 1 : -1;   // without a mask every tile of the union range is taken
+    } else {
+      for (++jt; jt < jhi; ++jt)
+        if (on(0, jt) || on(1, jt)) return jt;
+      return -1;
+    }
+  };
+  const int first_step = jhi > jlo ? next_step(jlo - 1) : -1;
+  const int n_steps = first_step >= 0 ? 1 : 0;   // only "are there any" is used below
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -140,10 +163,11 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
       mbar_expect_tx(q_full, 2 * Cfg::Q_BYTES);
       tma5(sQ, &p.tmQ, q_full, q0, head, b);
       tma5(sQ + Cfg::Q_BYTES, &p.tmQ, q_full, q0 + ATT_BM, head, b);
-      for (int j = 0; j < n_steps; ++j) {
+      int j = 0;   // steps taken so far
+      for (int jt = first_step; jt >= 0; jt = next_step(jt), ++j) {
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
-        const int kv0 = (jlo + j) * ATT_BN;
+        const int kv0 = jt * ATT_BN;
         if (!mbar_wait(&k_empty[s], ph ^ 1, s_abort, p.status, ST_TIMEOUT_PRODUCER)) break;
         mbar_expect_tx(&k_full[s], Cfg::KV_BYTES);
         tma5(sK + s * Cfg::KV_BYTES, &p.tmK, &k_full[s], kv0, kv_head, b);
@@ -157,7 +181,6 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
     if (lane == 0 && n_steps > 0) {
       constexpr uint32_t idesc_qk = umma_idesc_f16(ATT_BM, ATT_BN, 1, 0, 0);
       constexpr uint32_t idesc_pv = umma_idesc_f16(ATT_BM, D, 1, 0, 1);
-      auto active = [&](int x, int j) { return jlo + j >= lo[x] && jlo + j < hi[x]; };
       auto issue_qk = [&](int x, int j) {
         const uint32_t a0 = smem_u32(sQ + x * Cfg::Q_BYTES), b0 = smem_u32(sK + (j & 1) * Cfg::KV_BYTES);
         const uint32_t d = tmem_base + x * 256;
@@ -169,25 +192,29 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
                         umma_desc_sw128(b0 + c * (ATT_BN * 128) + k * 32, 16, 1024), idesc_qk, (c | k) ? 1u : 0u);
         umma_commit(&s_full[x]);
       };
-      // number of steps each tile has taken part in so far (gives barrier parities and accumulate flags)
-      int cnt[2] = {0, 0};
+      // steps each tile takes part in: total, and so far (gives barrier parities and accumulate flags)
+      int total[2] = {0, 0}, cnt[2] = {0, 0};
+      for (int jt = first_step; jt >= 0; jt = next_step(jt))
+        for (int x = 0; x < 2; ++x) total[x] += on(x, jt) ? 1 : 0;
       bool ok = mbar_wait(q_full, 0, s_abort, p.status, ST_TIMEOUT_MMA);
       if (ok) ok = mbar_wait(&k_full[0], 0, s_abort, p.status, ST_TIMEOUT_MMA);
       if (ok) {
         tc_fence_after();
         for (int x = 0; x < 2; ++x)
-          if (active(x, 0)) issue_qk(x, 0);
+          if (on(x, first_step)) issue_qk(x, 0);
         umma_commit(&k_empty[0]);
       }
-      for (int j = 0; j < n_steps && ok; ++j) {
-        const bool more = j + 1 < n_steps;
+      int j = 0;   // steps taken so far; K / V ring slot and phase follow it
+      for (int jt = first_step; jt >= 0 && ok; ++j) {
+        const int nxt = next_step(jt);
+        const bool more = nxt >= 0;
         if (!mbar_wait(&v_full[j & 1], (j >> 1) & 1, s_abort, p.status, ST_TIMEOUT_MMA)) { ok = false; break; }
         if (more && !mbar_wait(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, s_abort, p.status, ST_TIMEOUT_MMA)) {
           ok = false;
           break;
         }
         for (int x = 0; x < 2 && ok; ++x) {
-          if (active(x, j)) {
+          if (on(x, jt)) {
             if (!mbar_wait(&p_full[x], cnt[x] & 1, s_abort, p.status, ST_TIMEOUT_MMA)) { ok = false; break; }
             tc_fence_after();
             const uint32_t b0 = smem_u32(sV + (j & 1) * Cfg::KV_BYTES);
@@ -197,12 +224,13 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
               umma_f16_ts(dO, aP + k * 8, umma_desc_sw128(b0 + k * 2048, ATT_BN * 128, 1024), idesc_pv,
                           (cnt[x] | k) ? 1u : 0u);
             ++cnt[x];
-            if (!(more && active(x, j + 1))) umma_commit(&o_done[x]);  // last step of this tile
+            if (cnt[x] == total[x]) umma_commit(&o_done[x]);  // last step of this tile
           }
-          if (more && active(x, j + 1)) issue_qk(x, j + 1);
+          if (more && on(x, nxt)) issue_qk(x, j + 1);
         }
         umma_commit(&v_empty[j & 1]);
         if (more) umma_commit(&k_empty[(j + 1) & 1]);
+        jt = nxt;
       }
     }
   } else {
@@ -215,15 +243,17 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
     const uint32_t lane_addr = static_cast<uint32_t>(qd * 32) << 16;
     const uint32_t tS = tmem_base + x * 256 + lane_addr;
     const uint32_t tO = tS + 128;
-    const int n_mine = hi[x] - lo[x];
+    int n_mine = 0;   // steps this tile takes part in
+    for (int jt = lo[x]; jt < hi[x]; ++jt) n_mine += on(x, jt) ? 1 : 0;
     float m_used = -INFINITY;  // running (possibly stale) max, log2 domain
     float l = 0.f;
     bool ok = true;
     int hi_k = p.Skv - 1;  // last visible key index for this row
     if (p.causal) hi_k = min(hi_k, q_idx + offset);
     const int lo_k = p.window > 0 ? q_idx + offset - p.window + 1 : INT_MIN;
-    for (int j = 0; j < n_mine && ok; ++j) {
-      const int kv0 = (lo[x] + j) * ATT_BN;
+    for (int jt = lo[x], j = 0; jt < hi[x] && ok; ++jt) {
+      if (!on(x, jt)) continue;
+      const int kv0 = jt * ATT_BN;
       if (!mbar_wait_warp(&s_full[x], j & 1, s_abort, p.status, ST_TIMEOUT_EPILOGUE)) { ok = false; break; }
       tc_fence_after();
       const int qt0 = q0 + x * ATT_BM;
@@ -284,6 +314,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 1) attn_fwd_kernel(const __grid_c
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[x]);
+      ++j;
     }
     if (ok && n_mine > 0) {
       if (mbar_wait_warp(&o_done[x], 0, s_abort, p.status, ST_TIMEOUT_EPILOGUE)) {
@@ -364,23 +395,33 @@ extern "C" int sx_attn_fwd(const SxAttnArgs* a, cudaStream_t st) {
   p.v_head_div = a->v_head_div > 0 ? a->v_head_div : 1;
   p.causal = a->causal; p.window = a->window;
   p.scale_log2 = a->scale * 1.4426950408889634f;
+  p.block_mask = (const uint8_t*)a->block_mask;
+  p.bm_batch_stride = a->bm_batch_stride;
+  p.bm_head_stride = a->bm_head_stride;
+  p.bm_kv_tiles = (a->Skv + ATT_BN - 1) / ATT_BN;
   dim3 grid((a->Sq + 2 * ATT_BM - 1) / (2 * ATT_BM), a->Hq, a->B);
   if (a->D == 128) {
     static bool set = false;
     if (!set) {
-      if (cudaFuncSetAttribute(attn_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      if (cudaFuncSetAttribute(attn_fwd_kernel<128, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               AttnCfg<128>::SMEM_BYTES) != cudaSuccess ||
+          cudaFuncSetAttribute(attn_fwd_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                AttnCfg<128>::SMEM_BYTES) != cudaSuccess) return -10;
       set = true;
     }
-    attn_fwd_kernel<128><<<grid, ATT_THREADS, AttnCfg<128>::SMEM_BYTES, st>>>(p);
+    if (p.block_mask) attn_fwd_kernel<128, true><<<grid, ATT_THREADS, AttnCfg<128>::SMEM_BYTES, st>>>(p);
+    else attn_fwd_kernel<128, false><<<grid, ATT_THREADS, AttnCfg<128>::SMEM_BYTES, st>>>(p);
   } else {
     static bool set = false;
     if (!set) {
-      if (cudaFuncSetAttribute(attn_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      if (cudaFuncSetAttribute(attn_fwd_kernel<64, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               AttnCfg<64>::SMEM_BYTES) != cudaSuccess ||
+          cudaFuncSetAttribute(attn_fwd_kernel<64, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                AttnCfg<64>::SMEM_BYTES) != cudaSuccess) return -10;
       set = true;
     }
-    attn_fwd_kernel<64><<<grid, ATT_THREADS, AttnCfg<64>::SMEM_BYTES, st>>>(p);
+    if (p.block_mask) attn_fwd_kernel<64, true><<<grid, ATT_THREADS, AttnCfg<64>::SMEM_BYTES, st>>>(p);
+    else attn_fwd_kernel<64, false><<<grid, ATT_THREADS, AttnCfg<64>::SMEM_BYTES, st>>>(p);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -11;
 }

@@ -8,6 +8,10 @@
 // their fp32 partial tiles in shared memory and reduce them through distributed shared memory (CTA r sums and writes
 // the activation rows m = r, r + S, ...): deterministic, no workspace, no atomics. S is chosen so that tiles x S fills
 // the machine in one wave where it can. Two CTAs fit on an SM, each with 3-5 TMA stages in flight.
+// The kernel is launched with programmatic stream serialisation: it may become resident while the kernel before it on
+// the stream is still running, sets up its barriers and TMEM, and (when the caller says that the weight is not
+// produced by earlier kernels: flags bit 0) starts the weight loads of its first stages; everything that depends on
+// the predecessor - the activation loads and every store - comes after griddepcontrol.wait.
 // (Role in the reference: the batched matmul of its inference engine's decode step, csrc/inference/engine.cpp.)
 #include <stdlib.h>
 #include "tc_common.cuh"
@@ -28,7 +32,7 @@ struct SkinnyParams {
   const float* bias;
   int* status;
   long long ldd;
-  int M, N, K, Mpad, stages, tmem_cols, out_fp32, act;
+  int M, N, K, Mpad, stages, tmem_cols, out_fp32, act, flags;
   float alpha;
 };
 
@@ -42,6 +46,12 @@ __device__ __forceinline__ uint32_t cluster_size() {
   asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
   return r;
 }
+// Blocks until every kernel this launch depends on has completed and its writes are visible (no-op for a launch
+// without a programmatic dependency).
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Lets the next kernel on the stream start its own prologue (it still waits for this one before reading its results).
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
@@ -111,7 +121,16 @@ __global__ void __launch_bounds__(SK_THREADS, 2) gemm_skinny_kernel(const __grid
 
   if (warp == 5) {
     if (lane == 0) {
-      for (int i = 0; i < nk; ++i) {
+      // weight tiles of the first ring pass may be fetched before the predecessor kernel has finished
+      const int pre = (p.flags & 1) ? min(nk, p.stages) : 0;
+      for (int i = 0; i < pre; ++i) {
+        mbar_expect_tx(&full[i], stage_bytes);
+        tma_load_2d(sStages + i * stage_bytes, &p.tmW, &full[i], (kb0 + i) * SK_BK, n0);
+      }
+      griddep_wait();
+      for (int i = 0; i < pre; ++i)
+        tma_load_2d(sStages + i * stage_bytes + SK_A_BYTES, &p.tmX, &full[i], (kb0 + i) * SK_BK, 0);
+      for (int i = pre; i < nk; ++i) {
         const int s = i % p.stages;
         if (!mbar_wait(&empty[s], ((i / p.stages) & 1) ^ 1, s_abort, p.status, ST_TIMEOUT_PRODUCER)) break;
         mbar_expect_tx(&full[s], stage_bytes);
@@ -165,7 +184,9 @@ __global__ void __launch_bounds__(SK_THREADS, 2) gemm_skinny_kernel(const __grid
 
   // every thread of every CTA of the cluster takes part in both cluster barriers, whatever happened above
   if (S > 1) cluster_sync_all();
+  griddep_launch_dependents();
   if (warp < 4) {
+    griddep_wait();   // stores (and the bias read) come after the predecessor kernel
     // CTA r owns the activation rows m = r, r + S, ...: sum the S partial tiles (fixed order) and write the row out.
     // Thread layout: 32 float4 column groups x 4 row slots.
     const int q = threadIdx.x & 31, slot = threadIdx.x >> 5;
@@ -280,6 +301,7 @@ extern "C" int sx_gemm_skinny(const SxGemmArgs* a, cudaStream_t st) {
   p.tmem_cols = p.Mpad <= 32 ? 32 : (p.Mpad <= 64 ? 64 : 128);
   p.D = a->D; p.bias = a->bias; p.status = a->status; p.ldd = a->ldd;
   p.M = a->M; p.N = a->N; p.K = a->K; p.out_fp32 = a->out_fp32; p.act = a->act; p.alpha = a->alpha;
+  p.flags = a->flags;
   const int smem = stages * stage_bytes + 1024 + 1024;
   static int smem_set = 0;
   if (smem_set < smem) {
@@ -300,13 +322,20 @@ extern "C" int sx_gemm_skinny(const SxGemmArgs* a, cudaStream_t st) {
   cfg.blockDim = dim3(SK_THREADS, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = S;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  static int pdl = -1;
+  if (pdl < 0) {
+    const char* e = getenv("SX_GEMM_PDL");   // 0: plain stream order (measurement aid)
+    pdl = e ? atoi(e) : 1;
+  }
+  cfg.numAttrs = pdl ? 2 : 1;
   if (cudaLaunchKernelEx(&cfg, gemm_skinny_kernel, p) != cudaSuccess) return -11;
   return 0;
 }

@@ -18,6 +18,7 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const __nv_bfloat16* _
                                                           __nv_bfloat16* __restrict__ y,
                                                           __nv_bfloat16* __restrict__ res_out,
                                                           float* __restrict__ rstd, int d, float eps) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // a dependent launch may start its prologue
   __shared__ float red[33];
   const long long row = blockIdx.x;
   const __nv_bfloat16* xr = x + row * d;
@@ -250,6 +251,7 @@ __device__ __forceinline__ float gate_act_grad(float g, int act) {
 
 __global__ void glu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ h, long long T,
                                int F, int act) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // a dependent launch may start its prologue
   const int fv = F >> 3;
   const long long total = T * fv;
   for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;

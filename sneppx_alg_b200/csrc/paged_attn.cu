@@ -156,6 +156,7 @@ __global__ void __launch_bounds__(PA_TILE) paged_decode_kernel(
 
 __global__ void paged_merge_kernel(const float* __restrict__ o_part, const float* __restrict__ ml_part,
                                    __nv_bfloat16* __restrict__ out, long long out_row_stride, int Hq, int D, int nsplit) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // a dependent launch may start its prologue
   const int b = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
   const long long base = ((long long)b * Hq + h) * nsplit;
   float m = -INFINITY;

@@ -31,6 +31,8 @@ typedef struct SxGemmArgs {
   int* status;
   int sm_limit;  // cap on CTAs (0: one per SM)
   int force_bn;  // 0 auto, 128 or 256
+  int flags;     // bit 0: B is not written by any kernel launched before this one on the stream (a weight at
+                 // inference time), so a kernel may start fetching it before its predecessor has finished
 } SxGemmArgs;
 int sx_gemm_bf16(const SxGemmArgs* args, cudaStream_t stream);
 
@@ -53,6 +55,10 @@ typedef struct SxAttnArgs {
   int causal, window;
   float scale;
   int* status;
+  // forward only: optional byte per 128 x 128 score tile, [B or 1][Hq or 1][ceil(Sq/128)][ceil(Skv/128)]; a zero
+  // byte removes the tile. Strides in bytes (0 = shared over the batch / the heads).
+  const void* block_mask;
+  long long bm_batch_stride, bm_head_stride;
 } SxAttnArgs;
 int sx_attn_fwd(const SxAttnArgs* args, cudaStream_t stream);
 int sx_attn_bwd(const SxAttnArgs* args, cudaStream_t stream);

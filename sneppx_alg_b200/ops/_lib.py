@@ -25,7 +25,7 @@ class SxGemmArgs(C.Structure):
         ("alpha", c_float), ("beta", c_float),
         ("tile_group", c_void_p), ("num_groups", c_int),
         ("k_ranges", c_void_p), ("k_total", c_int),
-        ("status", c_void_p), ("sm_limit", c_int), ("force_bn", c_int),
+        ("status", c_void_p), ("sm_limit", c_int), ("force_bn", c_int), ("flags", c_int),
     ]
 
 
@@ -41,6 +41,7 @@ class SxAttnArgs(C.Structure):
         ("B", c_int), ("Sq", c_int), ("Skv", c_int), ("Hq", c_int), ("Hk", c_int), ("D", c_int),
         ("v_head_div", c_int), ("causal", c_int), ("window", c_int), ("scale", c_float),
         ("status", c_void_p),
+        ("block_mask", c_void_p), ("bm_batch_stride", c_ll), ("bm_head_stride", c_ll),
     ]
 
 

@@ -323,6 +323,67 @@ def attention(q, k, v, causal=True, window=0, scale=None):
     return attention_reference(q, k, v, causal, window, scale)
 
 
+def _expand_block_mask(block_mask, B, H, Sq, Skv, block=128):
+    bm = block_mask.bool()
+    while bm.dim() < 4:
+        bm = bm.unsqueeze(0)
+    bm = bm.expand(B if bm.shape[0] != 1 else 1, H if bm.shape[1] != 1 else 1, bm.shape[2], bm.shape[3])
+    return bm.repeat_interleave(block, dim=2)[:, :, :Sq].repeat_interleave(block, dim=3)[..., :Skv]
+
+
+def block_sparse_attention_reference(q, k, v, block_mask, causal=False, window=0, scale=None):
+    """fp32 reference of ``block_sparse_attention``: tiles of 128 x 128 scores whose mask entry is False are removed."""
+    B, Sq, Hq, D = q.shape
+    Skv, Hk, Hv = k.shape[1], k.shape[2], v.shape[2]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    qf = q.float().permute(0, 2, 1, 3)
+    kf = k.float().permute(0, 2, 1, 3).repeat_interleave(Hq // Hk, dim=1)
+    vf = v.float().permute(0, 2, 1, 3).repeat_interleave(Hq // Hv, dim=1)
+    s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+    off = Skv - Sq
+    qi = torch.arange(Sq, device=q.device).view(-1, 1) + off
+    ki = torch.arange(Skv, device=q.device).view(1, -1)
+    drop = ~_expand_block_mask(block_mask.to(q.device), B, Hq, Sq, Skv)
+    if causal:
+        drop = drop | (ki > qi)
+    if window and window > 0:
+        drop = drop | (ki < qi - window + 1)
+    s = s.masked_fill(drop, float("-inf"))
+    p = torch.nan_to_num(torch.softmax(s, dim=-1), nan=0.0)
+    return torch.matmul(p, vf).permute(0, 2, 1, 3).to(q.dtype)
+
+
+@torch.no_grad()
+def block_sparse_attention(q, k, v, block_mask, causal=False, window=0, scale=None):
+    """Forward-only attention with a tile-level mask: ``block_mask`` [ceil(Sq/128), ceil(Skv/128)] (optionally with
+    leading head and batch dimensions of size 1 or H / B), True where the 128 x 128 score tile takes part. Masked tiles
+    are neither loaded nor multiplied by the kernel; causal / window masks still apply inside the tiles that remain.
+    Query rows without any visible key give zeros. (Reference: kernel/algorithms/flex_attention.c:29-247 block masks,
+    kernel/cuda/attention_cuda.cu:1154-1230 block-sparse kernel.)"""
+    D = q.shape[-1]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    B, Sq, Hq, _ = q.shape
+    Skv = k.shape[1]
+    nq, nk = (Sq + 127) // 128, (Skv + 127) // 128
+    assert block_mask.shape[-2:] == (nq, nk), f"block_mask must end in [{nq}, {nk}]"
+    if not (_native(q) and D in (64, 128)):
+        return block_sparse_attention_reference(q, k, v, block_mask, causal, window, scale)
+    bm = block_mask.to(device=q.device)
+    while bm.dim() < 4:
+        bm = bm.unsqueeze(0)
+    assert bm.shape[0] in (1, B) and bm.shape[1] in (1, Hq)
+    bm = bm.to(torch.uint8).contiguous()
+    q, k, v = [t if _head_view_ok(t, D) else t.contiguous() for t in (q, k, v)]
+    o = torch.empty(B, Sq, Hq, D, dtype=q.dtype, device=q.device)
+    lse = torch.empty(B, Hq, Sq, dtype=torch.float32, device=q.device)
+    a = _attn_args(q, k, v, o, lse, causal, window, scale, k.shape[2] // v.shape[2])
+    a.block_mask = bm.data_ptr()
+    a.bm_batch_stride = bm.stride(0) if bm.shape[0] > 1 else 0
+    a.bm_head_stride = bm.stride(1) if bm.shape[1] > 1 else 0
+    _lib.call("sx_attn_fwd", C.byref(a), stream())
+    return o
+
+
 @torch.no_grad()
 def attention_with_lse(q, k, v, causal=True, window=0, scale=None):
     """Forward only: (o [B,Sq,Hq,D], lse [B,Hq,Sq] natural log). The pair lets partial results over disjoint key

@@ -9,6 +9,9 @@ from __future__ import annotations
 
 import ctypes as C
 
+import contextlib
+import threading
+
 import torch
 
 from . import _lib
@@ -52,6 +55,25 @@ def gemm_reference(a, b, *, a_mn=False, b_mn=False, c=None, beta=0.0, alpha=1.0,
     if c is not None and beta != 0.0:
         d = d + beta * c.float()
     return _act_ref(d, act).to(out_dtype)
+
+
+class _Static(threading.local):
+    on = False
+
+
+_static = _Static()
+
+
+@contextlib.contextmanager
+def static_weights(on: bool = True):
+    """Inside this block the second operand of every ``gemm`` / ``linear`` call is declared static: no kernel launched
+    earlier on the stream writes it (weights at inference time). Decode-sized products then start fetching the weight
+    while the kernel before them is still running (programmatic dependent launch)."""
+    old, _static.on = _static.on, on
+    try:
+        yield
+    finally:
+        _static.on = old
 
 
 def _use_kernel(*ts) -> bool:
@@ -186,6 +208,7 @@ def gemm(a, b, *, a_mn=False, b_mn=False, out=None, out_dtype=None, c=None, beta
     args.status = _lib.status_word(a.device).data_ptr()
     args.sm_limit = sm_limit
     args.force_bn = force_bn
+    args.flags = 1 if _static.on else 0
     _lib.call("sx_gemm_bf16", C.byref(args), _lib.stream())
     return out
 

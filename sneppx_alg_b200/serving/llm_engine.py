@@ -137,8 +137,10 @@ class LlamaPagedRunner:
             q = q2[:, : H * D].view(B, H, D)
             return paged.paged_decode(q, self.cache.k[li], self.cache.v[li], bt, lens).reshape(B, 1, H * D)
 
-        h = self._layers(m.embedding(ids).unsqueeze(1), attn)
-        return ops.linear(h[:, -1], m.head_weight()).float()
+        from ..ops.gemm import static_weights
+        with static_weights():     # weights are not written while serving: decode GEMMs may prefetch them early
+            h = self._layers(m.embedding(ids).unsqueeze(1), attn)
+            return ops.linear(h[:, -1], m.head_weight()).float()
 
     def _graph_for(self, Bb):
         g = self._graphs.get(Bb)
