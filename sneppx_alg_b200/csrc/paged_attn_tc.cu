@@ -9,9 +9,7 @@
 // K and V tiles are gathered by TMA straight from the paged cache: one box per (cache block, 64-wide slab), placed so
 // that the tile in shared memory has the same swizzled layout as a contiguous load. The cache is read once for all
 // query heads of the KV head and there are no shuffles on the score path, which is what bounded the SIMT kernel
-// (paged_attn.cu). S^T and P^T are double-buffered and the MMA warp issues the score MMA of tile j+1 before it waits
-// for the softmax of tile j (QK(0), QK(1), PV(0), QK(2), PV(1), ...), so the per-tile chain MMA -> softmax -> MMA is
-// off the critical path and the kernel is bound by the TMA stream. Splits are merged by paged_merge_kernel.
+// (paged_attn.cu); here the kernel is bound by the TMA stream. Splits are merged by paged_merge_kernel.
 // Serves the role of the reference's paged decode kernels (kernel/cuda/attention_cuda.cu:602-690).
 #include "tc_common.cuh"
 #include "tmap.h"
@@ -26,12 +24,12 @@ constexpr int PT_MAX_G = 8;
 constexpr int PT_STAGES = 3;
 constexpr int PT_THREADS = 192;  // warps 0-3: softmax / epilogue (TMEM lane quadrants 0-3), warp 4: MMA, warp 5: TMA
 constexpr int PT_KV_BYTES = PT_BN * PT_D * 2;          // one K or V tile
-constexpr int PT_Q_BYTES = PT_NQ * PT_D * 2;           // 4 KB: two buffers of Q rows, then two of P^T
+constexpr int PT_Q_BYTES = PT_NQ * PT_D * 2;           // 4 KB: two buffers of Q rows, then the same size for P^T
 constexpr int PT_OFF_P = 2 * PT_Q_BYTES;
-constexpr int PT_OFF_ST = 4 * PT_Q_BYTES;              // stages: [K tile][V tile], 1024-byte aligned
+constexpr int PT_OFF_ST = 3 * PT_Q_BYTES + 1024;       // stages: [K tile][V tile], 1024-byte aligned
 constexpr int PT_OFF_BAR = PT_OFF_ST + PT_STAGES * 2 * PT_KV_BYTES;
 constexpr int PT_SMEM = PT_OFF_BAR + 1024 + 1024;
-constexpr int PT_TMEM_COLS = 64;                       // S^T buffers at +0 and +16, O^T at +32
+constexpr int PT_TMEM_COLS = 32;                       // S^T at +0, O^T at +16
 
 struct PagedTcParams {
   CUtensorMap tmQ, tmK, tmV;
@@ -57,15 +55,14 @@ struct PtItem {
   int b, hk, split, len, t0, n_steps;
 };
 
-// Work item `item` of the (split, sequence, KV head) space, KV heads fastest: CTAs that run at the same time read
-// the heads of the same cache rows, which are adjacent in memory. The tile range comes from the sequence length on
-// the device.
+// Work item `item` of the (split, KV head, sequence) space, sequences fastest so that neighbouring CTAs hold different
+// sequences; its tile range comes from the sequence length on the device.
 __device__ __forceinline__ PtItem pt_item(const PagedTcParams& p, int item) {
   PtItem w;
-  w.hk = item % p.Hkv;
-  const int rest = item / p.Hkv;
-  w.b = rest % p.B;
-  w.split = rest / p.B;
+  w.b = item % p.B;
+  const int rest = item / p.B;
+  w.hk = rest % p.Hkv;
+  w.split = rest / p.Hkv;
   w.len = p.seq_lens[w.b];
   const int tiles = (w.len + PT_BN - 1) / PT_BN;
   const int per = (tiles + p.nsplit - 1) / p.nsplit;
@@ -73,32 +70,6 @@ __device__ __forceinline__ PtItem pt_item(const PagedTcParams& p, int item) {
   const int t1 = min(tiles, w.t0 + per);
   w.n_steps = t1 > w.t0 ? t1 - w.t0 : 0;
   return w;
-}
-
-// Position of a role in the CTA's tile sequence: item, tile j of it, tiles (gt) and non-empty items (qi) before it.
-struct PtCur {
-  int item, j;
-  PtItem w;
-  uint32_t gt, qi;
-  bool valid;
-};
-__device__ __forceinline__ void pt_next_item(const PagedTcParams& p, PtCur& c, int n_items) {
-  for (c.item += gridDim.x; c.item < n_items; c.item += gridDim.x) {
-    c.w = pt_item(p, c.item);
-    if (c.w.n_steps > 0) { c.j = 0; c.valid = true; return; }
-  }
-  c.valid = false;
-}
-__device__ __forceinline__ void pt_cur_init(const PagedTcParams& p, PtCur& c, int n_items) {
-  c.item = (int)blockIdx.x - (int)gridDim.x;
-  c.j = 0; c.gt = 0; c.qi = 0;
-  pt_next_item(p, c, n_items);
-}
-__device__ __forceinline__ void pt_cur_advance(const PagedTcParams& p, PtCur& c, int n_items) {
-  ++c.gt;
-  if (c.j + 1 < c.w.n_steps) { ++c.j; return; }
-  ++c.qi;
-  pt_next_item(p, c, n_items);
 }
 
 // Persistent: one CTA per SM walks items blockIdx.x, blockIdx.x + gridDim.x, ...; the TMA warp runs ahead across item
@@ -115,12 +86,11 @@ __global__ void __launch_bounds__(PT_THREADS, 1) paged_decode_tc_kernel(const __
   uint64_t* q_empty = bars + 2;            // [2]
   uint64_t* full = bars + 4;               // [PT_STAGES]
   uint64_t* empty = bars + 4 + PT_STAGES;  // [PT_STAGES]
-  uint64_t* s_full = bars + 4 + 2 * PT_STAGES;   // [2]: score buffer gt & 1 holds S^T of tile gt
-  uint64_t* p_full = s_full + 2;           // [2], 4 arrivals each (one per softmax warp)
-  uint64_t* o_done = s_full + 4;
-  uint64_t* red_bar = s_full + 5;          // 4 arrivals: per-warp maxima / sums are in shared memory
-  uint64_t* pv_done = s_full + 6;          // one phase per tile: its P V product has completed
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_full + 7);
+  uint64_t* s_full = bars + 4 + 2 * PT_STAGES;
+  uint64_t* p_full = s_full + 1;           // 4 arrivals (one per softmax warp)
+  uint64_t* o_done = s_full + 2;
+  uint64_t* red_bar = s_full + 3;          // 4 arrivals: per-warp maxima / sums are in shared memory
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_full + 4);
   volatile int* s_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float (*s_red)[4][PT_MAX_G] = reinterpret_cast<float (*)[4][PT_MAX_G]>(smem + PT_OFF_BAR + 256);  // [2][4][G]
 
@@ -137,13 +107,10 @@ __global__ void __launch_bounds__(PT_THREADS, 1) paged_decode_tc_kernel(const __
       mbar_init(&full[i], 1);
       mbar_init(&empty[i], 1);
     }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&s_full[i], 1);
-      mbar_init(&p_full[i], 4);
-    }
+    mbar_init(s_full, 1);
+    mbar_init(p_full, 4);
     mbar_init(o_done, 1);
     mbar_init(red_bar, 4);
-    mbar_init(pv_done, 1);
     *s_abort = 0;
     mbar_fence_init();
     tma_prefetch_desc(&p.tmQ);
@@ -155,7 +122,7 @@ __global__ void __launch_bounds__(PT_THREADS, 1) paged_decode_tc_kernel(const __
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tS = tmem_base, tO = tmem_base + 32;
+  const uint32_t tS = tmem_base, tO = tmem_base + 16;
 
   auto tma5 = [](void* dst, const CUtensorMap* m, uint64_t* bar, int c1, int c2, int c3, int c4) {
     asm volatile(
@@ -189,19 +156,18 @@ __global__ void __launch_bounds__(PT_THREADS, 1) paged_decode_tc_kernel(const __
         const uint32_t ph = (gt / PT_STAGES) & 1;
         const int kv0 = (w.t0 + j) * PT_BN;
         if (!mbar_wait_warp(&empty[s], ph ^ 1, s_abort, p.status, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
-        // cache blocks past the end of the sequence are not fetched: their score rows are masked and their V rows
-        // are cleared by the softmax warps, whatever the stage held before
-        const int live = min(nchunk, (w.len - kv0 + bs - 1) / bs);
-        if (lane == 0) mbar_expect_tx(&full[s], live * bs * 512);
+        if (lane == 0) mbar_expect_tx(&full[s], 2 * PT_KV_BYTES);
         __syncwarp();
         uint8_t* st = sSt + s * 2 * PT_KV_BYTES;
         for (int t = lane; t < n_box; t += 32) {
           const int which = t / (nchunk * 2);   // 0: K, 1: V
           const int rem = t - which * nchunk * 2;
           const int i = rem >> 1, c = rem & 1;
-          if (i < live)
-            tma5(st + which * PT_KV_BYTES + c * (PT_BN * 128) + i * bs * 128, which ? &p.tmV : &p.tmK, &full[s], 0, c,
-                 w.hk, tbl[(kv0 + i * bs) / bs]);
+          const int pos = kv0 + i * bs;
+          // blocks past the end of the sequence are masked; any valid block keeps the tile finite
+          const int blk = pos < w.len ? tbl[pos / bs] : tbl[0];
+          tma5(st + which * PT_KV_BYTES + c * (PT_BN * 128) + i * bs * 128, which ? &p.tmV : &p.tmK, &full[s], 0, c,
+               w.hk, blk);
         }
       }
     }
@@ -210,53 +176,41 @@ __global__ void __launch_bounds__(PT_THREADS, 1) paged_decode_tc_kernel(const __
     if (lane == 0) {
       constexpr uint32_t idesc_qk = umma_idesc_f16(PT_BN, PT_NQ, 1, 0, 0);   // A = K tile (K-major), B = Q (K-major)
       constexpr uint32_t idesc_pv = umma_idesc_f16(PT_D, PT_NQ, 1, 1, 0);    // A = V tile (MN-major), B = P^T (K-major)
+      const uint32_t p0 = smem_u32(sP);
+      uint32_t gt = 0, qi = 0;
       bool ok = true;
-      // score MMA of the tile at cursor c into score buffer c.gt & 1
-      auto issue_qk = [&](const PtCur& c) -> bool {
-        const int qb = c.qi & 1;
-        if (c.j == 0 && !mbar_wait(&q_full[qb], (c.qi >> 1) & 1, s_abort, p.status, ST_TIMEOUT_MMA)) return false;
-        const int s = c.gt % PT_STAGES;
-        if (!mbar_wait(&full[s], (c.gt / PT_STAGES) & 1, s_abort, p.status, ST_TIMEOUT_MMA)) return false;
-        tc_fence_after();
-        const uint32_t k0 = smem_u32(sSt + s * 2 * PT_KV_BYTES), q0 = smem_u32(sQ + qb * PT_Q_BYTES);
-        const uint32_t d = tS + (c.gt & 1) * 16;
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+        const PtItem w = pt_item(p, item);
+        if (w.n_steps == 0) continue;
+        const int qb = qi & 1;
+        const uint32_t q0 = smem_u32(sQ + qb * PT_Q_BYTES);
+        if (!mbar_wait(&q_full[qb], (qi >> 1) & 1, s_abort, p.status, ST_TIMEOUT_MMA)) break;
+        for (int j = 0; j < w.n_steps; ++j, ++gt) {
+          const int s = gt % PT_STAGES;
+          if (!mbar_wait(&full[s], (gt / PT_STAGES) & 1, s_abort, p.status, ST_TIMEOUT_MMA)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t k0 = smem_u32(sSt + s * 2 * PT_KV_BYTES), v0 = k0 + PT_KV_BYTES;
 #pragma unroll
-        for (int cc = 0; cc < PT_D / 64; ++cc)
+          for (int c = 0; c < PT_D / 64; ++c)
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma_f16_ss(d, umma_desc_sw128(k0 + cc * (PT_BN * 128) + k * 32, 16, 1024),
-                        umma_desc_sw128(q0 + cc * (PT_NQ * 128) + k * 32, 16, 1024), idesc_qk, (cc | k) ? 1u : 0u);
-        umma_commit(&s_full[c.gt & 1]);
-        return true;
-      };
-      PtCur cq, cv;   // the score MMAs run one tile ahead of the P V MMAs
-      pt_cur_init(p, cq, n_items);
-      pt_cur_init(p, cv, n_items);
-      if (cq.valid) {
-        ok = issue_qk(cq);
-        pt_cur_advance(p, cq, n_items);
-      }
-      while (ok && cv.valid) {
-        if (cq.valid) {
-          if (!issue_qk(cq)) break;
-          pt_cur_advance(p, cq, n_items);
+            for (int k = 0; k < 4; ++k)
+              umma_f16_ss(tS, umma_desc_sw128(k0 + c * (PT_BN * 128) + k * 32, 16, 1024),
+                          umma_desc_sw128(q0 + c * (PT_NQ * 128) + k * 32, 16, 1024), idesc_qk, (c | k) ? 1u : 0u);
+          umma_commit(s_full);
+          if (!mbar_wait(p_full, gt & 1, s_abort, p.status, ST_TIMEOUT_MMA)) { ok = false; break; }
+          tc_fence_after();
+#pragma unroll
+          for (int k = 0; k < PT_BN / 16; ++k)
+            umma_f16_ss(tO, umma_desc_sw128(v0 + k * 2048, PT_BN * 128, 1024),
+                        umma_desc_sw128(p0 + (k >> 2) * (PT_NQ * 128) + (k & 3) * 32, 16, 1024), idesc_pv,
+                        (j | k) ? 1u : 0u);
+          umma_commit(&empty[s]);
+          if (j + 1 == w.n_steps) {
+            umma_commit(o_done);
+            umma_commit(&q_empty[qb]);
+          }
         }
-        const int s = cv.gt % PT_STAGES, x = cv.gt & 1;
-        if (!mbar_wait(&p_full[x], (cv.gt >> 1) & 1, s_abort, p.status, ST_TIMEOUT_MMA)) break;
-        tc_fence_after();
-        const uint32_t v0 = smem_u32(sSt + s * 2 * PT_KV_BYTES) + PT_KV_BYTES, p0 = smem_u32(sP + x * PT_Q_BYTES);
-#pragma unroll
-        for (int k = 0; k < PT_BN / 16; ++k)
-          umma_f16_ss(tO, umma_desc_sw128(v0 + k * 2048, PT_BN * 128, 1024),
-                      umma_desc_sw128(p0 + (k >> 2) * (PT_NQ * 128) + (k & 3) * 32, 16, 1024), idesc_pv,
-                      (cv.j | k) ? 1u : 0u);
-        umma_commit(&empty[s]);
-        umma_commit(pv_done);
-        if (cv.j + 1 == cv.w.n_steps) {
-          umma_commit(o_done);
-          umma_commit(&q_empty[cv.qi & 1]);
-        }
-        pt_cur_advance(p, cv, n_items);
+        ++qi;
       }
     }
   } else {
@@ -264,8 +218,8 @@ __global__ void __launch_bounds__(PT_THREADS, 1) paged_decode_tc_kernel(const __
     const int t = threadIdx.x;
     const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
     // P^T rows of heads >= G stay zero for the whole kernel
-#pragma unroll
-    for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(sP + t * 64 + i * 16) = make_uint4(0, 0, 0, 0);
+    *reinterpret_cast<uint4*>(sP + t * 32) = make_uint4(0, 0, 0, 0);
+    *reinterpret_cast<uint4*>(sP + t * 32 + 16) = make_uint4(0, 0, 0, 0);
     const uint32_t p_off = (t >> 6) * (PT_NQ * 128) + ((t & 7) << 1);   // slab and byte inside the 16-byte chunk
     const int p_chunk = (t & 63) >> 3;
     bool ok = true;
@@ -287,11 +241,10 @@ __global__ void __launch_bounds__(PT_THREADS, 1) paged_decode_tc_kernel(const __
       for (int j = 0; j < w.n_steps && ok; ++j, ++gt) {
         const int kv0 = (w.t0 + j) * PT_BN;
         const bool valid = kv0 + t < w.len;
-        const int x = gt & 1;   // score / P^T buffer of this tile
-        if (!mbar_wait_warp(&s_full[x], (gt >> 1) & 1, s_abort, p.status, ST_TIMEOUT_EPILOGUE)) { ok = false; break; }
+        if (!mbar_wait_warp(s_full, gt & 1, s_abort, p.status, ST_TIMEOUT_EPILOGUE)) { ok = false; break; }
         tc_fence_after();
         uint32_t r[16];
-        tmem_ld16(tS + x * 16 + lane_addr, r);
+        tmem_ld16(tS + lane_addr, r);
         tmem_ld_wait();
         float sc[PT_MAX_G];
 #pragma unroll
@@ -326,15 +279,11 @@ __global__ void __launch_bounds__(PT_THREADS, 1) paged_decode_tc_kernel(const __
             const __nv_bfloat16 pb = __float2bfloat16_rn(pv);
             // the row sum uses the rounded value so that l matches what the P V product sees
             l[g] = fmaf(l[g], alpha[g], __bfloat162float(pb));
-            *reinterpret_cast<__nv_bfloat16*>(sP + x * PT_Q_BYTES + p_off + g * 128 + ((p_chunk ^ (g & 7)) << 4)) = pb;
+            *reinterpret_cast<__nv_bfloat16*>(sP + p_off + g * 128 + ((p_chunk ^ (g & 7)) << 4)) = pb;
           }
         }
-        // The score MMA of this tile was issued after P V of tile gt - 2, so this P^T buffer is free; O^T is still
-        // being accumulated into by P V of tile gt - 1, which has to finish before O^T is rescaled. (P V of this tile
-        // cannot start before the p_full arrival below, so pv_done is at most one phase ahead: the parity is exact.)
+        // s_full of this tile completed after P V of the previous one (in-order tensor pipe): O^T and P^T are ours
         if (j > 0 && rescale) {
-          if (!mbar_wait_warp(pv_done, (gt - 1) & 1, s_abort, p.status, ST_TIMEOUT_EPILOGUE)) { ok = false; break; }
-          tc_fence_after();
           uint32_t o[16];
           tmem_ld16(tO + lane_addr, o);
           tmem_ld_wait();
@@ -359,7 +308,7 @@ __global__ void __launch_bounds__(PT_THREADS, 1) paged_decode_tc_kernel(const __
         fence_proxy_async_smem();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&p_full[x]);
+        if (lane == 0) mbar_arrive(p_full);
       }
       if (!ok) break;
       // ---- partial result of this item for the merge kernel. Total row sums: every thread holds the partial sum of
