@@ -1,7 +1,8 @@
 """Worker for the 2-GPU tensor-parallel serving test (run under torch.distributed.run): the TP engine (peer-load
 all-reduce kernel, CUDA-graph decode) against the single-GPU engine on the same bf16 model: first-token logits agree
-within bf16 reduction noise and the greedy continuations agree on almost every token (a different summation order can
-flip an argmax between two nearly equal logits)."""
+within bf16 reduction noise, and wherever a greedy continuation leaves the single-GPU one the two candidate tokens are a
+near tie in the single-GPU engine's own logits for that prefix (a different summation order can flip an argmax
+between two nearly equal logits; everything after such a flip differs legitimately)."""
 import os
 import sys
 
@@ -39,9 +40,21 @@ def main():
     l_tp = eng.runner.prefill(10_000, prompts[2], 0)
     rel = (l_ref - l_tp).abs().max().item() / (l_ref.abs().max().item() + 1e-6)
     agree = sum(a == b for w, o in zip(want, got) for a, b in zip(w, o)) / sum(len(w) for w in want)
+    # first divergence of every sequence: the single-GPU logits for that prefix must hold the two tokens within noise
+    ties_ok, sid = True, 20_000
+    for pr, w, o in zip(prompts, want, got):
+        i = next((j for j, (a, b) in enumerate(zip(w, o)) if a != b), None)
+        if i is None:
+            continue
+        sid += 1
+        ref.cache.add_sequence(sid, None)
+        lg = ref.runner.prefill(sid, pr + w[:i], 0)[0]
+        ref.cache.free_sequence(sid)
+        gap = (lg[w[i]] - lg[o[i]]).abs().item() / (lg.abs().max().item() + 1e-6)
+        ties_ok = ties_ok and gap < 3e-2
     torch.cuda.synchronize()
     check_status()
-    ok = rel < 3e-2 and agree >= 0.9 and graphs >= 1 and all(len(o) == 24 for o in got)
+    ok = rel < 3e-2 and ties_ok and agree >= 0.3 and graphs >= 1 and all(len(o) == 24 for o in got)
     t = torch.tensor([int(ok)], device=dev)
     dist.all_reduce(t, op=dist.ReduceOp.MIN)
     same = torch.tensor([hash(tuple(map(tuple, got))) % (1 << 30)], device=dev)
@@ -50,7 +63,7 @@ def main():
     dist.all_reduce(hi, op=dist.ReduceOp.MAX)
     ranks_agree = bool(lo.item() == hi.item())           # every rank must sample the same tokens
     if rank == 0:
-        print(f"tp serving world {world}: logits rel err {rel:.3e}, token agreement with 1 GPU {agree:.3f}, decode graphs {graphs}, "
+        print(f"tp serving world {world}: logits rel err {rel:.3e}, token agreement with 1 GPU {agree:.3f} (divergences are near ties: {ties_ok}), decode graphs {graphs}, "
               f"ranks agree {ranks_agree} ->", "OK" if (t.item() and ranks_agree) else "MISMATCH", flush=True)
     dist.barrier()
     dist.destroy_process_group()
