@@ -151,10 +151,12 @@ def _dist_setup():
     return world, rank, local_rank, dev
 
 
-def measure(args, world, rank, local_rank, dev, step, vocab, B, S, data_seed, launches=None, check=None):
+def measure(args, world, rank, local_rank, dev, step, vocab, B, S, data_seed, launches=None, check=None, drain=None):
     """Warm-up, the device-timed region (inputs resident on the device) and the end-to-end region (every step copies
     its batch from pinned host memory and reads the loss back), each bracketed by barrier + synchronize and timed with
-    CUDA events; returns max-over-ranks milliseconds. ``step(ids) -> loss tensor``."""
+    CUDA events; returns max-over-ranks milliseconds. ``step(ids) -> loss tensor``. ``drain``: makes the timing stream
+    wait for work the engine still has in flight on its own streams (deferred parameter updates), called before each
+    closing event so that the timed region holds all the work of its steps."""
     import torch
     import torch.distributed as dist
     gen = torch.Generator().manual_seed(data_seed)
@@ -184,6 +186,8 @@ def measure(args, world, rank, local_rank, dev, step, vocab, B, S, data_seed, la
     for _ in range(args.steps):
         step(devb[it])
         it += 1
+    if drain:
+        drain()
     e1.record()
     sync()
     ms = e0.elapsed_time(e1)
@@ -194,6 +198,8 @@ def measure(args, world, rank, local_rank, dev, step, vocab, B, S, data_seed, la
     for _ in range(args.steps):
         last = float(step(host[it].to(dev, non_blocking=True)).item())
         it += 1
+    if drain:
+        drain()
     f1.record()
     sync()
     ms_e2e = f0.elapsed_time(f1)
@@ -324,7 +330,7 @@ def main():
         return engine.step(ids, ids)
 
     res = measure(args, world, rank, local_rank, dev, step, V, B, S, 100 + dp_rank,
-                  launches=lambda: _lib.launch_count, check=check_status)
+                  launches=lambda: _lib.launch_count, check=check_status, drain=getattr(engine, "finish", None))
     if args.ep and world > 1:
         from sneppx_alg_b200.parallel import expert as _ep
         d = torch.tensor([float(_ep.dropped_entries())], device=dev, dtype=torch.float64)

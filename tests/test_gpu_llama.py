@@ -37,6 +37,28 @@ def test_llama_step_matches_fp32_oracle():
     assert last < first
 
 
+def test_overlapped_optimizer_gives_the_same_parameters():
+    """Per-bucket AdamW on a side stream (the next forward waits bucket by bucket) against the single-stream step:
+    identical losses and bit-identical master weights after several steps."""
+    torch.manual_seed(0)
+    cfg = ModelConfig(hidden_size=512, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2,
+                      intermediate_size=1024, vocab_size=2048, max_position_embeddings=256, rms_norm_eps=1e-5)
+    base = build_model(cfg).to("cuda", torch.bfloat16)
+    a = TrainEngine(copy.deepcopy(base), lr=1e-3, weight_decay=0.1, max_grad_norm=1.0, overlap_optimizer=False)
+    b = TrainEngine(copy.deepcopy(base), lr=1e-3, weight_decay=0.1, max_grad_norm=1.0, overlap_optimizer=True)
+    assert b._opt_stream is not None and len(b._ranges) == cfg.num_hidden_layers + 2
+    assert b._ranges[0][0] == 0 and b._ranges[-1][1] == b.fp.total
+    assert all(x[1] == y[0] for x, y in zip(b._ranges, b._ranges[1:]))
+    for step in range(5):
+        ids = torch.randint(0, cfg.vocab_size, (2, 256), generator=torch.Generator().manual_seed(step)).cuda()
+        la, lb = a.step(ids, ids), b.step(ids, ids)
+        assert la.item() == lb.item()
+    sa, sb = a.state_dict(), b.state_dict()     # state_dict waits for the updates in flight
+    assert torch.equal(sa["master"], sb["master"]) and torch.equal(sa["m"], sb["m"]) and torch.equal(sa["v"], sb["v"])
+    assert torch.equal(a.fp.flat, b.fp.flat)
+    ops.check_status()
+
+
 def test_llama_generate_cached_equals_uncached():
     torch.manual_seed(0)
     cfg = ModelConfig(hidden_size=256, num_hidden_layers=2, num_attention_heads=2, num_key_value_heads=1,
