@@ -33,30 +33,50 @@ class ByteTokenizer:
 
 
 class EngineWorker:
-    """Owns one LLMEngine and steps it on a background thread; HTTP handlers submit and await futures."""
+    """Owns one LLMEngine and steps it on a background thread; HTTP handlers submit and await futures. Submissions
+    only append to a list under a lock that is never held across an engine step (a handler running on the event loop
+    must not wait for a step, and an unfair lock would let the stepping thread starve it); the stepping thread moves
+    them into the engine at the start of its next iteration, so request ids are handed out here."""
 
     def __init__(self, engine: LLMEngine):
         self.engine = engine
         self._lock = threading.Lock()
         self._events: Dict[int, threading.Event] = {}
         self._callbacks: Dict[int, object] = {}
+        self._pending: list = []
+        self._next_rid = 0
         self._stop = False
         self.thread = threading.Thread(target=self._loop, daemon=True)
         self.thread.start()
 
+    def _fire_finished(self):
+        with self._lock:
+            done = [rid for rid in self._events if rid in self.engine.finished or rid in self.engine.failed]
+            fired = [(self._events.pop(rid), self._callbacks.pop(rid, None)) for rid in done]
+        for ev, cb in fired:
+            ev.set()
+            if cb is not None:
+                cb()
+
     def _loop(self):
+        try:
+            dev = next(self.engine.runner.model.parameters()).device
+            if dev.type == "cuda":
+                import torch
+                torch.cuda.set_device(dev)       # a new thread starts on device 0
+        except (AttributeError, StopIteration):
+            pass
         while not self._stop:
             with self._lock:
-                work = self.engine.has_work()
-                if work:
-                    self.engine.step()
-                    for rid in list(self._events):
-                        if rid in self.engine.finished:
-                            self._events.pop(rid).set()
-                            cb = self._callbacks.pop(rid, None)
-                            if cb is not None:
-                                cb()
-            if not work:
+                new, self._pending = self._pending, []
+            for prompt, sp, on_token, rid in new:
+                got = self.engine.submit(prompt, sp, on_token=on_token)
+                if got != rid:
+                    raise RuntimeError("request ids diverged: something else submitted to this engine")
+            if self.engine.has_work():
+                self.engine.step()
+                self._fire_finished()
+            else:
                 time.sleep(0.001)
 
     def submit(self, prompt_ids, params, on_token=None, on_done=None):
@@ -64,7 +84,9 @@ class EngineWorker:
         result without parking a thread per request."""
         ev = threading.Event()
         with self._lock:
-            rid = self.engine.submit(prompt_ids, params, on_token=on_token)
+            rid = self._next_rid
+            self._next_rid += 1
+            self._pending.append((list(prompt_ids), params, on_token, rid))
             self._events[rid] = ev
             if on_done is not None:
                 self._callbacks[rid] = on_done
@@ -129,24 +151,17 @@ class TPEngineWorker(EngineWorker):
                 new, self._pending = self._pending, []
                 stop = self._stop
             items, stop = self._exchange([(p, asdict(sp)) for p, sp, _, _ in new] if self.leader else [], stop)
-            with self._lock:
-                for i, (prompt, pd) in enumerate(items):
-                    pd["stop_token_ids"] = tuple(pd.get("stop_token_ids", ()))
-                    rid = self.engine.submit(prompt, SamplingParams(**pd), on_token=new[i][2] if self.leader else None)
-                    if self.leader and rid != new[i][3]:
-                        raise RuntimeError("request ids of the tensor-parallel engines diverged")
-                if stop:
-                    return
-                work = self.engine.has_work()
-                if work:
-                    self.engine.step()
-                    for rid in list(self._events):
-                        if rid in self.engine.finished or rid in self.engine.failed:
-                            self._events.pop(rid).set()
-                            cb = self._callbacks.pop(rid, None)
-                            if cb is not None:
-                                cb()
-            if not work and self.leader:
+            for i, (prompt, pd) in enumerate(items):
+                pd["stop_token_ids"] = tuple(pd.get("stop_token_ids", ()))
+                rid = self.engine.submit(prompt, SamplingParams(**pd), on_token=new[i][2] if self.leader else None)
+                if self.leader and rid != new[i][3]:
+                    raise RuntimeError("request ids of the tensor-parallel engines diverged")
+            if stop:
+                return
+            if self.engine.has_work():
+                self.engine.step()
+                self._fire_finished()
+            elif self.leader:
                 time.sleep(0.002)
 
     follow = _loop
@@ -154,15 +169,7 @@ class TPEngineWorker(EngineWorker):
     def submit(self, prompt_ids, params, on_token=None, on_done=None):
         if params.stop_fn is not None:
             raise ValueError("stop strings / stop_fn are not supported by tensor-parallel serving")
-        ev = threading.Event()
-        with self._lock:
-            rid = self._next_rid
-            self._next_rid += 1
-            self._pending.append((list(prompt_ids), params, on_token, rid))
-            self._events[rid] = ev
-            if on_done is not None:
-                self._callbacks[rid] = on_done
-        return rid, ev
+        return super().submit(prompt_ids, params, on_token=on_token, on_done=on_done)
 
     def stop(self):
         self._stop = True
