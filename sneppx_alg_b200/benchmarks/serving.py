@@ -69,12 +69,58 @@ def _engine_kwargs(requests, prompt_len, new_tokens, max_prefill_tokens, block_s
     return kw
 
 
+def _http_clients(port, prompts, new_tokens, warm, conn):
+    """Client side of ``run_http`` in a process of its own (threads in the server's process would share its
+    interpreter lock with the thread that launches kernels and trickle their requests out over seconds): one thread
+    per request, all released together when the parent says go."""
+    import http.client
+    import threading
+
+    def post(ids, n):
+        c = http.client.HTTPConnection("127.0.0.1", port, timeout=3600)
+        t0 = time.perf_counter()
+        c.request("POST", "/v1/generate", json.dumps({"prompt_token_ids": ids, "max_new_tokens": n}),
+                  {"Content-Type": "application/json"})
+        resp = c.getresponse()
+        body = json.loads(resp.read())
+        c.close()
+        if resp.status != 200:
+            raise RuntimeError(f"HTTP {resp.status}: {body}")
+        return body, time.perf_counter() - t0
+
+    try:
+        for _ in range(2):                      # warm-up (allocations, kernel loading, graph capture)
+            post(warm, 4)
+        bodies = [json.dumps({"prompt_token_ids": p, "max_new_tokens": new_tokens}) for p in prompts]
+        del bodies
+        conn.send("ready")
+        conn.recv()                             # go
+        results, errors = [None] * len(prompts), []
+
+        def worker(i):
+            try:
+                body, dt = post(prompts[i], new_tokens)
+                results[i] = (body["completion_tokens"], body["ttft_s"], dt)
+            except Exception as e:  # noqa: BLE001  (reported after the run)
+                errors.append(f"request {i}: {type(e).__name__}: {e}")
+
+        t0 = time.perf_counter()
+        threads = [threading.Thread(target=worker, args=(i,)) for i in range(len(prompts))]
+        for t in threads:
+            t.start()
+        for t in threads:
+            t.join()
+        conn.send({"seconds": time.perf_counter() - t0, "results": results, "errors": errors})
+    except Exception as e:  # noqa: BLE001
+        conn.send({"seconds": 0.0, "results": [], "errors": [f"client process: {type(e).__name__}: {e}"]})
+
+
 def run_http(model, requests=64, prompt_len=2048, new_tokens=256, max_prefill_tokens=16384, block_size=16, seed=0,
              tp_group=None) -> dict:
-    """The workload of ``run`` sent through ``POST /v1/generate`` of the FastAPI front-end (uvicorn, loopback). With
-    ``tp_group`` this is the leader's side of tensor-parallel serving; the other ranks run ``serving.server.tp_follow``
-    with the same engine arguments."""
-    import http.client
+    """The workload of ``run`` sent through ``POST /v1/generate`` of the FastAPI front-end (uvicorn, loopback) by a
+    client process. With ``tp_group`` this is the leader's side of tensor-parallel serving; the other ranks run
+    ``serving.server.tp_follow`` with the same engine arguments."""
+    import multiprocessing as mp
     import socket
     import threading
 
@@ -97,55 +143,36 @@ def run_http(model, requests=64, prompt_len=2048, new_tokens=256, max_prefill_to
         time.sleep(0.05)
     g = torch.Generator().manual_seed(seed)
     prompts = [torch.randint(0, cfg.vocab_size, (prompt_len,), generator=g).tolist() for _ in range(requests)]
-
-    def post(ids, n):
-        conn = http.client.HTTPConnection("127.0.0.1", port, timeout=3600)
-        t0 = time.perf_counter()
-        conn.request("POST", "/v1/generate", json.dumps({"prompt_token_ids": ids, "max_new_tokens": n}),
-                     {"Content-Type": "application/json"})
-        resp = conn.getresponse()
-        body = json.loads(resp.read())
-        conn.close()
-        if resp.status != 200:
-            raise RuntimeError(f"HTTP {resp.status}: {body}")
-        return body, time.perf_counter() - t0
-
-    post(prompts[0][: min(prompt_len, 128)], 4)          # warm-up (allocations, kernel loading, graph capture)
-    post(prompts[0][: min(prompt_len, 128)], 4)
-    results = [None] * requests
-
-    errors = []
-
-    def worker(i):
-        try:
-            results[i] = post(prompts[i], new_tokens)
-        except Exception as e:  # noqa: BLE001  (reported after the run)
-            errors.append(f"request {i}: {type(e).__name__}: {e}")
-
+    ctx = mp.get_context("spawn")
+    parent, child = ctx.Pipe()
+    proc = ctx.Process(target=_http_clients, args=(port, prompts, new_tokens, prompts[0][: min(prompt_len, 128)], child),
+                       daemon=True)
+    proc.start()
+    msg = parent.recv()                          # "ready" after the warm-up requests, or an error record
+    if msg != "ready":
+        raise RuntimeError(f"HTTP client process failed: {msg}")
     if torch.cuda.is_available():
         torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    threads = [threading.Thread(target=worker, args=(i,)) for i in range(requests)]
-    for t in threads:
-        t.start()
-    for t in threads:
-        t.join()
-    dt = time.perf_counter() - t0
+    parent.send("go")
+    out = parent.recv()
+    proc.join(30)
     server.should_exit = True
     th.join(10)
     for w in app.state.workers.values():
         w.stop()
-    if errors:
-        raise RuntimeError(f"{len(errors)} of {requests} requests failed; first: {errors[0]}")
-    out_tokens = sum(r[0]["completion_tokens"] for r in results)
-    ttft = sorted(r[0]["ttft_s"] for r in results)
-    lat = sorted(r[1] for r in results)
+    if out["errors"]:
+        raise RuntimeError(f"{len(out['errors'])} of {requests} requests failed; first: {out['errors'][0]}")
+    dt = out["seconds"]
+    out_tokens = sum(r[0] for r in out["results"])
+    ttft = sorted(r[1] for r in out["results"])
+    lat = sorted(r[2] for r in out["results"])
     pct = lambda v, q: v[min(len(v) - 1, int(q * len(v)))]  # noqa: E731
     return {"metric": "serving output tokens/sec", "value": out_tokens / dt, "unit": "tokens/s", "requests": requests,
             "prompt_len": prompt_len, "new_tokens": new_tokens, "seconds": dt, "output_tokens": out_tokens,
             "ttft_p50_s": pct(ttft, 0.5), "ttft_p95_s": pct(ttft, 0.95), "ttft_min_s": ttft[0],
             "latency_p50_s": pct(lat, 0.5), "latency_max_s": lat[-1],
-            "front_end": "HTTP POST /v1/generate (FastAPI on uvicorn, loopback), prompts as token ids"}
+            "front_end": "HTTP POST /v1/generate (FastAPI on uvicorn, loopback; clients in their own process), "
+                         "prompts as token ids"}
 
 
 def main(argv=None):
