@@ -123,11 +123,14 @@ def serve_engine(engine, models: Dict[str, dict], token: str = "", port: int = 0
     def _generate(_params, body):
         try:
             req = json.loads(body or b"{}")
-        except ValueError:
+        except (ValueError, RecursionError):      # RecursionError: thousands of nested brackets
             raise HTTPError(400, "body is not JSON")
-        if not isinstance(req.get("prompt"), str):
+        if not isinstance(req, dict) or not isinstance(req.get("prompt"), str):
             raise HTTPError(400, "prompt (string) is required")
-        n = int(req.get("max_new_tokens", 32))
+        try:
+            n = int(req.get("max_new_tokens", 32))
+        except (TypeError, ValueError, OverflowError):
+            raise HTTPError(400, "max_new_tokens must be an integer")
         if not 0 < n <= 4096:
             raise HTTPError(400, "max_new_tokens must be in 1..4096")
         if req.get("model") and req["model"] not in models:

@@ -103,7 +103,7 @@ class TPEngineWorker(EngineWorker):
     """Tensor-parallel form of the worker. Every rank of ``group`` owns an ``LLMEngine`` over its shard of the model;
     the engines only stay consistent if all of them see the same requests in the same order and step together. The
     leader (group rank 0) takes submissions from the HTTP handlers; once per loop iteration it broadcasts the new
-    ones (a three-word header, then the pickled prompts and sampling parameters when there are any) and every rank
+    ones (a three-word header, then the prompts and sampling parameters as JSON when there are any) and every rank
     submits them and takes one engine step. The other ranks run ``follow()``, which returns when the leader stops.
     Requests with a ``stop_fn`` are refused: the callable lives on the leader only."""
 
@@ -122,11 +122,9 @@ class TPEngineWorker(EngineWorker):
             self._lock, self._events, self._callbacks = threading.Lock(), {}, {}
 
     def _exchange(self, items, stop):
-        import pickle
-
         import torch
         import torch.distributed as dist
-        payload = pickle.dumps(items) if (self.leader and items) else b""
+        payload = json.dumps(items).encode() if (self.leader and items) else b""
         hdr = torch.tensor([len(items), len(payload), int(stop)] if self.leader else [0, 0, 0], dtype=torch.int64,
                            device=self.dev)
         dist.broadcast(hdr, self.src, group=self.group)
@@ -138,7 +136,7 @@ class TPEngineWorker(EngineWorker):
                 buf = torch.empty(nbytes, dtype=torch.uint8, device=self.dev)
             dist.broadcast(buf, self.src, group=self.group)
             if not self.leader:
-                items = pickle.loads(buf.cpu().numpy().tobytes())    # from a rank of the same job
+                items = json.loads(buf.cpu().numpy().tobytes().decode())
         return items if n else [], bool(stop)
 
     def _loop(self):
