@@ -277,36 +277,82 @@ class _AttnFn(torch.autograd.Function):
     def backward(ctx, do):
         q, k, v, o, lse = ctx.saved_tensors
         causal, window, scale, v_head_div = ctx.meta
-        B, Sq, Hq, D = q.shape
-        Skv, Hk = k.shape[1], k.shape[2]
-        if v_head_div > 1:
-            v_use = v.repeat_interleave(v_head_div, dim=2)
-        else:
-            v_use = v
-        do = do if _head_view_ok(do, D) else do.contiguous()
-        # dQ|dK|dV written into one fused buffer so that a fused QKV projection gets a contiguous grad
-        dqkv = torch.empty(B, max(Sq, Skv), (Hq + 2 * Hk) * D, dtype=q.dtype, device=q.device) if Sq == Skv else None
-        if dqkv is not None:
-            dq = dqkv[..., : Hq * D].view(B, Sq, Hq, D)
-            dk = dqkv[..., Hq * D: (Hq + Hk) * D].view(B, Skv, Hk, D)
-            dv = dqkv[..., (Hq + Hk) * D:].view(B, Skv, Hk, D)
-        else:
-            dq = torch.empty(B, Sq, Hq, D, dtype=q.dtype, device=q.device)
-            dk = torch.empty(B, Skv, Hk, D, dtype=q.dtype, device=q.device)
-            dv = torch.empty(B, Skv, Hk, D, dtype=q.dtype, device=q.device)
-        a = _attn_args(q, k, v_use, o, lse, causal, window, scale, 1)
-        dq_acc = torch.empty(B, Hq, (Sq + 63) // 64 * 64, D, dtype=torch.float32, device=q.device)  # tiled by the kernel
-        delta = torch.empty(B, Hq, Sq, dtype=torch.float32, device=q.device)
-        a.dO, a.dQ, a.dK, a.dV = do.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
-        a.dq_accum, a.delta = dq_acc.data_ptr(), delta.data_ptr()
-        a.do_row_stride = do.stride(1)
-        a.dq_row_stride, a.dk_row_stride, a.dv_row_stride = dq.stride(1), dk.stride(1), dv.stride(1)
-        a.dq_batch_stride, a.dk_batch_stride, a.dv_batch_stride = dq.stride(0), dk.stride(0), dv.stride(0)
-        assert dq.stride(0) == Sq * dq.stride(1)
-        _lib.call("sx_attn_bwd", C.byref(a), stream())
-        if v_head_div > 1:
-            dv = dv.view(B, Skv, Hk // v_head_div, v_head_div, D).sum(3)
+        dq, dk, dv = attention_backward(q, k, v, o, lse, do, causal, window, scale)
         return dq, dk, dv, None, None, None
+
+
+def attention_backward_reference(q, k, v, o, lse, do, causal=True, window=0, scale=None):
+    """fp32 gradients of attention given the forward's output and log-sum-exp. ``o`` and ``lse`` may be those of a
+    softmax over MORE keys than ``k`` holds (ring / split-KV attention): the result is then this key block's share
+    of dQ and its own dK, dV."""
+    B, Sq, Hq, D = q.shape
+    Skv, Hk, Hv = k.shape[1], k.shape[2], v.shape[2]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    qf = q.float().permute(0, 2, 1, 3)
+    kf = k.float().permute(0, 2, 1, 3).repeat_interleave(Hq // Hk, dim=1)
+    vf = v.float().permute(0, 2, 1, 3).repeat_interleave(Hq // Hv, dim=1)
+    dof = do.float().permute(0, 2, 1, 3)
+    s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+    off = Skv - Sq
+    qi = torch.arange(Sq, device=q.device).view(-1, 1) + off
+    ki = torch.arange(Skv, device=q.device).view(1, -1)
+    mask = torch.zeros(Sq, Skv, dtype=torch.bool, device=q.device)
+    if causal:
+        mask |= ki > qi
+    if window and window > 0:
+        mask |= ki < qi - window + 1
+    p = torch.exp(s - lse.float().unsqueeze(-1)).masked_fill(mask, 0.0)
+    p = torch.nan_to_num(p, nan=0.0, posinf=0.0)
+    delta = (dof * o.float().permute(0, 2, 1, 3)).sum(-1, keepdim=True)
+    dv = torch.matmul(p.transpose(-1, -2), dof)
+    ds = p * (torch.matmul(dof, vf.transpose(-1, -2)) - delta)
+    dq = torch.matmul(ds, kf) * scale
+    dk = torch.matmul(ds.transpose(-1, -2), qf) * scale
+    dk = dk.view(B, Hk, Hq // Hk, Skv, D).sum(2)
+    dv = dv.view(B, Hv, Hq // Hv, Skv, D).sum(2)
+    return (dq.permute(0, 2, 1, 3).to(q.dtype), dk.permute(0, 2, 1, 3).to(k.dtype), dv.permute(0, 2, 1, 3).to(v.dtype))
+
+
+def attention_backward(q, k, v, o, lse, do, causal=True, window=0, scale=None):
+    """(dQ, dK, dV) of flash attention from its saved output and log-sum-exp (natural log, [B, Hq, Sq]). Also the
+    per-block step of ring attention backward: with the final ``o`` / ``lse`` of a softmax over all key blocks it
+    returns this block's contribution."""
+    B, Sq, Hq, D = q.shape
+    Skv, Hk = k.shape[1], k.shape[2]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    if not (_native(q) and D == 128):
+        return attention_backward_reference(q, k, v, o, lse, do, causal, window, scale)
+    v_head_div = Hk // v.shape[2]
+    q, k, v, o = [t if _head_view_ok(t, D) else t.contiguous() for t in (q, k, v, o)]
+    lse = lse.contiguous()
+    if v_head_div > 1:
+        v_use = v.repeat_interleave(v_head_div, dim=2)
+    else:
+        v_use = v
+    do = do if _head_view_ok(do, D) else do.contiguous()
+    # dQ|dK|dV written into one fused buffer so that a fused QKV projection gets a contiguous grad
+    dqkv = torch.empty(B, max(Sq, Skv), (Hq + 2 * Hk) * D, dtype=q.dtype, device=q.device) if Sq == Skv else None
+    if dqkv is not None:
+        dq = dqkv[..., : Hq * D].view(B, Sq, Hq, D)
+        dk = dqkv[..., Hq * D: (Hq + Hk) * D].view(B, Skv, Hk, D)
+        dv = dqkv[..., (Hq + Hk) * D:].view(B, Skv, Hk, D)
+    else:
+        dq = torch.empty(B, Sq, Hq, D, dtype=q.dtype, device=q.device)
+        dk = torch.empty(B, Skv, Hk, D, dtype=q.dtype, device=q.device)
+        dv = torch.empty(B, Skv, Hk, D, dtype=q.dtype, device=q.device)
+    a = _attn_args(q, k, v_use, o, lse, causal, window, scale, 1)
+    dq_acc = torch.empty(B, Hq, (Sq + 63) // 64 * 64, D, dtype=torch.float32, device=q.device)  # tiled by the kernel
+    delta = torch.empty(B, Hq, Sq, dtype=torch.float32, device=q.device)
+    a.dO, a.dQ, a.dK, a.dV = do.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+    a.dq_accum, a.delta = dq_acc.data_ptr(), delta.data_ptr()
+    a.do_row_stride = do.stride(1)
+    a.dq_row_stride, a.dk_row_stride, a.dv_row_stride = dq.stride(1), dk.stride(1), dv.stride(1)
+    a.dq_batch_stride, a.dk_batch_stride, a.dv_batch_stride = dq.stride(0), dk.stride(0), dv.stride(0)
+    assert dq.stride(0) == Sq * dq.stride(1)
+    _lib.call("sx_attn_bwd", C.byref(a), stream())
+    if v_head_div > 1:
+        dv = dv.view(B, Skv, Hk // v_head_div, v_head_div, D).sum(3)
+    return dq, dk, dv
 
 
 def attention(q, k, v, causal=True, window=0, scale=None):

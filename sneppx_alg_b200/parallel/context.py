@@ -4,7 +4,8 @@
   of the gather is a reduce-scatter of dK / dV) and the local queries run through the flash-attention kernel with the
   bottom-right causal alignment (query i sees keys <= i + Skv - Sq), so a rank only reads the keys it can see.
   ``layout="zigzag"`` gives rank r the chunks r and 2w-1-r, which equalises causal work over ranks.
-* ``ring_attention_forward``: inference-only ring variant: K/V blocks travel rank to rank and the per-block outputs
+* ``ring_attention``: ring variant with a backward pass (dK / dV accumulators travel with their blocks);
+  ``ring_attention_forward``: the inference-only form: K/V blocks travel rank to rank and the per-block outputs
   are merged with their log-sum-exp (no full-sequence K/V is ever resident).
 * ``cp_ssd_scan``: Mamba-2 scan over a sharded sequence. Pass 1 scans every shard from a zero state (in parallel) and
   yields the shard's final state and total decay; the [H, P, N] states are all-gathered (a few hundred KB) and each
@@ -141,6 +142,71 @@ def ring_attention_forward(q, k, v, causal: bool = True, scale: Optional[float] 
         ob, lb = F_.attention_with_lse(q, kb, vb, causal=False, scale=scale)
         o, lse = merge_attention_blocks(o, lse, ob, lb)
     return o.to(q.dtype)
+
+
+def _ring_rotate(tensors, group):
+    """Every tensor goes to rank r + 1 and is replaced by the one arriving from rank r - 1 (one batched exchange)."""
+    w, r = _world(group)
+    send_to, recv_from = (r + 1) % w, (r - 1) % w
+    src = [t.contiguous() for t in tensors]
+    dst = [torch.empty_like(t) for t in src]
+    ops = [dist.P2POp(dist.isend, t, send_to, group) for t in src] + [dist.P2POp(dist.irecv, t, recv_from, group) for t in dst]
+    for req in dist.batch_isend_irecv(ops):
+        req.wait()
+    return dst
+
+
+class _RingAttention(torch.autograd.Function):
+    """Ring attention with a backward pass (contiguous layout). Forward: K/V blocks travel around the ring and the
+    per-block results are merged through their log-sum-exps. Backward: the blocks travel again, each together with
+    an accumulator for its dK / dV; every rank adds the contribution of its queries (computed from the FINAL output
+    and log-sum-exp, so that the block probabilities are those of the full softmax) and after ``world`` rotations
+    every accumulator is back on the rank that owns the block."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, causal, scale, group):
+        w, r = _world(group)
+        o, lse = F_.attention_with_lse(q, k, v, causal=causal, scale=scale)
+        o = o.float()
+        kb, vb = k.contiguous(), v.contiguous()
+        for s in range(1, w):
+            kb, vb = _ring_rotate([kb, vb], group)
+            if causal and (r - s) % w > r:
+                continue
+            ob, lb = F_.attention_with_lse(q, kb, vb, causal=False, scale=scale)
+            o, lse = merge_attention_blocks(o, lse, ob, lb)
+        o = o.to(q.dtype)
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.meta = (causal, scale, group)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, lse = ctx.saved_tensors
+        causal, scale, group = ctx.meta
+        w, r = _world(group)
+        do = do.contiguous()
+        dq = torch.zeros_like(q, dtype=torch.float32)
+        kb, vb = k.contiguous(), v.contiguous()
+        dkb, dvb = torch.zeros_like(k, dtype=torch.float32), torch.zeros_like(v, dtype=torch.float32)
+        for s in range(w):
+            if not (causal and (r - s) % w > r):
+                dq_b, dk_b, dv_b = F_.attention_backward(q, kb, vb, o, lse, do, causal=causal and s == 0, window=0,
+                                                         scale=scale)
+                dq += dq_b.float()
+                dkb += dk_b.float()
+                dvb += dv_b.float()
+            if s + 1 < w:
+                kb, vb, dkb, dvb = _ring_rotate([kb, vb, dkb, dvb], group)
+            elif w > 1:
+                dkb, dvb = _ring_rotate([dkb, dvb], group)      # the last hop brings the accumulators home
+        return dq.to(q.dtype), dkb.to(k.dtype), dvb.to(v.dtype), None, None, None
+
+
+def ring_attention(q, k, v, causal: bool = True, scale: Optional[float] = None, group=None):
+    """Ring attention for training over a sequence sharded in contiguous blocks: q, k, v are this rank's
+    [B, S / world, H, D] shards; returns this rank's output shard, differentiable in q, k and v."""
+    return _RingAttention.apply(q, k, v, causal, scale, group)
 
 
 # ------------------------------------------------------------------------------------------------ Mamba-2 / SSD

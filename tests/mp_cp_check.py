@@ -52,6 +52,20 @@ def _run(rank, world, port):
     ring_nc = cp.ring_attention_forward(q[:, sl], k[:, sl], v[:, sl], causal=False)
     assert torch.allclose(ring_nc, F_.attention_reference(q, k, v, causal=False)[:, sl], atol=1e-5), "ring non-causal"
 
+    # ring attention with its backward pass (dK / dV accumulators travel with the blocks), causal and not
+    for causal, (o_ref, grads) in ((True, (ref, (qr.grad, kr.grad, vr.grad))), (False, (None, None))):
+        if o_ref is None:
+            qn, kn, vn = (t.clone().requires_grad_(True) for t in (q, k, v))
+            o_ref = F_.attention_reference(qn, kn, vn, causal=False)
+            o_ref.backward(go)
+            grads = (qn.grad, kn.grad, vn.grad)
+        ql, kl, vl = (t[:, sl].clone().requires_grad_(True) for t in (q, k, v))
+        out = cp.ring_attention(ql, kl, vl, causal=causal)
+        out.backward(go[:, sl])
+        assert torch.allclose(out, o_ref[:, sl].detach(), atol=1e-5), f"ring forward causal={causal}"
+        for g, full_g, name in zip((ql.grad, kl.grad, vl.grad), grads, "qkv"):
+            assert torch.allclose(g, full_g[:, sl], atol=2e-5), f"ring backward d{name} causal={causal}"
+
     # SSD scan, both modes, with gradients
     H, P, G, N, L = 4, 8, 2, 8, 16 * world
     x = torch.randn(B, L, H, P)

@@ -45,6 +45,10 @@ def main():
     worst = max(worst, rel(out, zz(ref)), rel(ql.grad, zz(qr.grad)), rel(kl.grad, zz(kr.grad)), rel(vl.grad, zz(vr.grad)))
     ring = cp.ring_attention_forward(q[:, sl], k[:, sl], v[:, sl], causal=True)
     worst = max(worst, rel(ring, ref[:, sl]))
+    ql, kl, vl = (t[:, sl].clone().requires_grad_(True) for t in (q, k, v))
+    out = cp.ring_attention(ql, kl, vl, causal=True)       # ring form with its backward pass
+    out.backward(go[:, sl])
+    worst = max(worst, rel(out, ref[:, sl]), rel(ql.grad, qr.grad[:, sl]), rel(kl.grad, kr.grad[:, sl]), rel(vl.grad, vr.grad[:, sl]))
     assert worst < 3e-2, f"context-parallel attention error {worst}"
 
     H, P, G, N, L = 8, 64, 2, 128, 512 * world
