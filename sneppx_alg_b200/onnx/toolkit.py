@@ -365,12 +365,27 @@ OPS = {
 }
 
 
+def _eval_node(n: "Node", env: dict) -> None:
+    """Runs one node on ``env``. Empty input names are optional inputs that were left out (passed as None unless they
+    trail); an operator returns one array, or a tuple that is bound to the node's outputs in order."""
+    ins = [env[i] if i else None for i in n.inputs]
+    while ins and ins[-1] is None:
+        ins.pop()
+    attrs = n.attrs if len(n.outputs) <= 1 else dict(n.attrs, _n_outputs=len(n.outputs))
+    out = OPS[n.op_type](attrs, ins)
+    if isinstance(out, tuple):
+        for name, val in zip(n.outputs, out):
+            if name:
+                env[name] = val
+    else:
+        env[n.outputs[0]] = out
+
+
 def run_model(m: Model, feeds: Dict[str, np.ndarray]) -> Dict[str, np.ndarray]:
     env = dict(m.graph.initializers)
     env.update(feeds)
     for n in m.graph.nodes:
-        out = OPS[n.op_type](n.attrs, [env[i] for i in n.inputs if i])
-        env[n.outputs[0]] = out
+        _eval_node(n, env)
     return {o.name: env[o.name] for o in m.graph.outputs}
 
 
@@ -384,8 +399,10 @@ def infer_shapes(m: Model, input_shapes: Optional[Dict[str, tuple]] = None) -> D
     env.update(feeds)
     shapes = {k: tuple(v.shape) for k, v in env.items()}
     for n in m.graph.nodes:
-        env[n.outputs[0]] = OPS[n.op_type](n.attrs, [env[i] for i in n.inputs if i])
-        shapes[n.outputs[0]] = tuple(np.shape(env[n.outputs[0]]))
+        _eval_node(n, env)
+        for o in n.outputs:
+            if o in env:
+                shapes[o] = tuple(np.shape(env[o]))
     return shapes
 
 
@@ -396,7 +413,10 @@ def optimize(m: Model) -> Model:
     kept = []
     for n in g.nodes:
         if n.op_type in OPS and all((i in const) for i in n.inputs if i) and (n.inputs or n.op_type == "Constant"):
-            const[n.outputs[0]] = np.asarray(OPS[n.op_type](n.attrs, [const[i] for i in n.inputs if i]))
+            _eval_node(n, const)
+            for o in n.outputs:
+                if o in const:
+                    const[o] = np.asarray(const[o])
         else:
             kept.append(n)
     needed = {o.name for o in g.outputs}
