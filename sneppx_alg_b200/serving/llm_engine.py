@@ -105,6 +105,31 @@ class LlamaPagedRunner:
         h = self._layers(m.embedding(ids).unsqueeze(0), attn)
         return ops.linear(h[:, -1], m.head_weight()).float()
 
+    @torch.no_grad()
+    def prefill_batch(self, seq_ids: List[int], prompts: List[List[int]]):
+        """Whole prompts of EQUAL length (nothing cached) in one pass: the GEMMs see n x T rows and the attention
+        kernel a batch of n; returns the logits of the last position of every sequence [n, V]."""
+        m, H, Hk, D = self.model, self.H, self.Hk, self.D
+        dev = m.embedding.weight.device
+        n, T = len(prompts), len(prompts[0])
+        assert all(len(p) == T for p in prompts)
+        ids = torch.tensor(prompts, dtype=torch.long, device=dev)
+        slots = torch.tensor([s for sid in seq_ids for s in self.cache.reserve(sid, T)], dtype=torch.int32, device=dev)
+        pos = torch.arange(T, dtype=torch.int32, device=dev).repeat(n)
+        cos, sin = m.rope(dev, T)
+
+        def attn(li, qkv):
+            q2 = qkv.view(n * T, (H + 2 * Hk) * D)
+            paged.kv_append_(q2, cos, sin, pos, slots, self.cache.k[li], self.cache.v[li], H, Hk, D)
+            q3 = q2.view(n, T, (H + 2 * Hk) * D)
+            q = q3[..., : H * D].view(n, T, H, D)
+            k = q3[..., H * D: (H + Hk) * D].view(n, T, Hk, D)
+            v = q3[..., (H + Hk) * D:].view(n, T, Hk, D)
+            return ops.attention(q, k, v, causal=True).reshape(n, T, H * D)
+
+        h = self._layers(m.embedding(ids), attn)
+        return ops.linear(h[:, -1], m.head_weight()).float()
+
     # ------------------------------------------------------------------ decode
     def enable_graphs(self, max_batch: int, max_len: int):
         """Capture the decode step into CUDA graphs, one per batch-size bucket (1, 2, 4, .. max_batch): a decode step
@@ -431,6 +456,27 @@ class LLMEngine:
             self.running.pop(req.req_id, None)
             self.finished[req.req_id] = req
 
+    def _admit_same_length(self, first: "Request", budget: int) -> List["Request"]:
+        """Pops the waiting requests that can join ``first``'s prefill pass: they are next in queue order, have a
+        prompt of the same length, hit no cached prefix, fit the batch, the token budget and the block pool."""
+        out, T = [], len(first.prompt)
+        reserved = self._blocks_needed(first)
+        while self.waiting and len(self.running) + 1 + len(out) < self.max_batch_size and budget >= T and len(out) < 15:
+            nxt = self.waiting[0]
+            if len(nxt.prompt) != T:
+                break
+            need = reserved + self._blocks_needed(nxt) + self._committed()
+            if need > self.cache.available_blocks() or not self.cache.make_room(need):
+                break
+            if self.cache.add_sequence(nxt.req_id, nxt.prompt) != 0:     # a cached prefix: it prefills on its own
+                self.cache.free_sequence(nxt.req_id)
+                break
+            heapq.heappop(self.waiting)
+            out.append(nxt)
+            reserved += self._blocks_needed(nxt)
+            budget -= T
+        return out
+
     def step(self):
         """One scheduler iteration: admit + prefill, then one decode step for all running sequences."""
         self.stats["steps"] += 1
@@ -450,12 +496,22 @@ class LLMEngine:
             heapq.heappop(self.waiting)
             cached = self.cache.add_sequence(req.req_id, req.prompt)
             self.stats["cached_prefix_tokens"] += cached
-            logits = self.runner.prefill(req.req_id, req.prompt, cached)
-            n = len(req.prompt) - cached
-            budget -= n
-            self.stats["prefill_tokens"] += n
-            self.running[req.req_id] = req
-            self._emit(req, logits[0], int(logits[0].argmax()) if self._plain_greedy(req) else None)
+            group = [req]
+            if cached == 0 and hasattr(self.runner, "prefill_batch"):
+                # requests behind it with a prompt of the same length (and nothing cached) share the pass
+                group += self._admit_same_length(req, budget - len(req.prompt))
+            if len(group) > 1:
+                logits = self.runner.prefill_batch([g.req_id for g in group], [g.prompt for g in group])
+                picks = logits.argmax(dim=-1).tolist() if any(self._plain_greedy(g) for g in group) else None
+            else:
+                logits = self.runner.prefill(req.req_id, req.prompt, cached)
+                picks = [int(logits[0].argmax())] if self._plain_greedy(req) else None
+            for i, g in enumerate(group):
+                n = len(g.prompt) - (cached if i == 0 else 0)
+                budget -= n
+                self.stats["prefill_tokens"] += n
+                self.running[g.req_id] = g
+                self._emit(g, logits[i], picks[i] if picks is not None and self._plain_greedy(g) else None)
         active = [r for r in self.running.values() if r.output]
         if active:
             ids = [r.req_id for r in active]

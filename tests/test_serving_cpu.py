@@ -87,6 +87,26 @@ def test_engine_serves_recurrent_state_models():
     assert eng.runner.states == {} and eng.cache.pool.num_free == 2
 
 
+def test_same_length_prompts_share_one_prefill_pass():
+    """Waiting requests whose prompts have the same length are prefilled as one batch (one pass over the weights);
+    the tokens are those of one-by-one generation, the prompt of another length still goes alone, and the batch
+    respects the token budget."""
+    model = _model()
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, 97, (12,), generator=g).tolist() for _ in range(5)] + [torch.randint(0, 97, (7,), generator=g).tolist()] + \
+              [torch.randint(0, 97, (12,), generator=g).tolist() for _ in range(2)]
+    ref = [generate(model, torch.tensor([p]), max_new_tokens=6)[0, len(p):].tolist() for p in prompts]
+    eng = LLMEngine(model, num_blocks=128, block_size=4, max_batch_size=8, max_prefill_tokens=40, enable_prefix_cache=False)
+    calls = []
+    orig = eng.runner.prefill_batch
+    eng.runner.prefill_batch = lambda ids, ps: (calls.append(len(ps)), orig(ids, ps))[1]
+    out = eng.generate(prompts, SamplingParams(max_new_tokens=6))
+    assert out == ref
+    assert calls and calls[0] == 3                     # 40-token budget: three 12-token prompts per pass
+    assert eng.stats["prefill_tokens"] == sum(len(p) for p in prompts)
+    assert not eng.cache.tables and eng.cache.pool.free_count() == 128 if hasattr(eng.cache.pool, "free_count") else True
+
+
 def test_tensor_parallel_engine_matches_single_rank_tokens():
     import os
     import subprocess
