@@ -39,6 +39,9 @@ def parse():
     ap.add_argument("--ep", action="store_true", help="expert parallelism over all ranks (SER MoE models): experts are "
                     "sharded, the other parameters use ZeRO-1")
     ap.add_argument("--zero-stage", type=int, default=3)
+    ap.add_argument("--param-slots", type=int, default=0,
+                    help="ZeRO-3 with sharded parameters: keep this many rotating layer slots instead of all gathered "
+                         "parameters (N > 1); 0 keeps them all resident")
     ap.add_argument("--fp8-experts", action="store_true", help="SER MoE models: forward expert GEMMs in block-scaled "
                     "fp8 (e4m3 data, 1x128 activation and 128x128 weight scales); backward stays bf16")
     ap.add_argument("--tp", type=int, default=1, help="tensor-parallel size (Mamba-2 models): ranks form world/tp "
@@ -176,6 +179,7 @@ def measure(args, world, rank, local_rank, dev, step, vocab, B, S, data_seed, la
         it += 1
     if check:
         check()
+    torch.cuda.reset_peak_memory_stats(dev)       # peak memory of the steps, not of building the model
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -323,8 +327,10 @@ def main():
         parallelism = f"ep{world}+zero1"
     else:
         model = build_model(cfg, dtype=torch.bfloat16, device=dev)
+        if args.param_slots and world > 1:
+            kw["param_slots"] = args.param_slots
         engine = make_engine(model, zero_stage=args.zero_stage, **kw)
-        parallelism = f"zero{args.zero_stage}-dp{world}"
+        parallelism = f"zero{args.zero_stage}-dp{world}" + (f"-paramslots{args.param_slots}" if kw.get("param_slots") else "")
 
     def step(ids):
         return engine.step(ids, ids)

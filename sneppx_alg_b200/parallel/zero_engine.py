@@ -15,6 +15,14 @@ to the shard; parameters for the next step are pulled bucket by bucket over NVLi
 them. Stage 1 reduces once at the end of backward, stage 2 reduces per bucket, stage 3 additionally treats the
 full bf16 parameter buffer as a cache that is refilled from the owners' shards every step.
 
+Sharded parameters (``param_slots=K``, stage 3 only): the gathered bf16 parameters of the repeated layers are not
+kept. ``K`` layer-sized slots rotate: layer i lives in slot i mod K, is gathered K - 1 layers ahead of its forward
+pass, overwritten by layer i + K once its forward is done, and gathered again ahead of its backward pass (the
+parameters of every layer alias the slot memory, so tensors saved for backward see the right values again). Per GPU
+this keeps K layers plus the embedding / head bucket instead of the whole model, at the price of a second all-gather
+of the layers per step. (The reference's FSDP wrapper describes the same ``FULL_SHARD`` behaviour,
+interface_bindings/fsdp.py:132-151,187-194.)
+
 Library path (``fused=False``, also CPU/gloo): ``reduce_scatter`` / ``all_reduce`` / ``all_gather`` from
 ``torch.distributed`` around the same local math. This is the baseline the fused path is measured against.
 """
@@ -50,7 +58,7 @@ def _find_layer_list(model):
 
 class ZeroEngine:
     def __init__(self, model, zero_stage=3, lr=1e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1,
-                 max_grad_norm=1.0, group=None, fused=None, comm_grid=0, timeout_s=5.0, nvls=None):
+                 max_grad_norm=1.0, group=None, fused=None, comm_grid=0, timeout_s=5.0, nvls=None, param_slots=None):
         self.model = model
         self.group = group if group is not None else dist.group.WORLD
         self.rank, self.world = dist.get_rank(self.group), dist.get_world_size(self.group)
@@ -69,6 +77,12 @@ class ZeroEngine:
         if nvls is None:
             nvls = os.environ.get("SX_ZERO_NVLS", "0") == "1"
         self.nvls = bool(nvls) and self.fused
+        if param_slots is None:
+            param_slots = int(os.environ.get("SX_ZERO_PARAM_SLOTS", "0"))
+        self.param_slots = int(param_slots) if zero_stage >= 3 else 0
+        if self.param_slots:
+            assert self.param_slots >= 2, "at least two slots (one in use, one being filled)"
+            assert not self.nvls, "sharded parameters use the peer-load all-gather"
         # ---- buckets: one per repeated layer (in forward order), then what runs before the layers (embedding) and
         # what runs after them (final norm, head): the last group's gradients are complete first in backward
         layers = _find_layer_list(model)
@@ -162,6 +176,9 @@ class ZeroEngine:
                 self.fp.flat[b0 + self.rank * sz: b0 + (self.rank + 1) * sz])
         self.m = torch.zeros_like(self.master)
         self.v = torch.zeros_like(self.master)
+        self._nl = len(self.bucket_modules)
+        if self.param_slots:
+            self._setup_param_slots()
         if self.fused:
             self.pshard = self.sg.alloc(self.shard_total, self.fp.dtype)
             self.pshard.tensor.copy_(self.master)
@@ -184,8 +201,125 @@ class ZeroEngine:
             dist.barrier(self.group)
         else:
             self.pshard_local = torch.empty(self.shard_total, dtype=self.fp.dtype, device=dev)
+            self.pshard_local.copy_(self.master)
             self.reduced = torch.empty(self.shard_total, dtype=torch.float32, device=dev)
+            self.gather_events = [None] * len(self.bounds)
+            if self.param_slots:
+                self._install_hooks()
         self.last_norm = None
+        if self.param_slots:
+            self._gather_initial()
+
+    # ------------------------------------------------------------------ sharded parameters: rotating layer slots
+    def _setup_param_slots(self):
+        """Re-homes the parameters: layer i's tensors become views of slot i mod K (at the offsets they had inside
+        their bucket), everything outside the layers moves to a compact tail; the full-size buffer is released."""
+        K, nl = self.param_slots, self._nl
+        assert nl >= K, "fewer layers than parameter slots"
+        sizes = {b1 - b0 for (b0, b1) in self.bounds[:nl]}
+        rel = [[o - self.bounds[bi][0] for o, p in zip(self.fp.offsets, self.fp.params) if self.bucket_of_param[id(p)] == bi]
+               for bi in range(nl)]
+        if len(sizes) != 1 or any(r != rel[0] for r in rel):
+            raise RuntimeError("param_slots needs identically laid out layers (same parameter shapes in the same order)")
+        slot = sizes.pop()
+        rest0 = self.bounds[nl][0] if nl < len(self.bounds) else self.fp.total
+        old = self.fp.flat
+        compact = torch.empty(K * slot + (self.fp.total - rest0), dtype=old.dtype, device=old.device)
+        compact[K * slot:].copy_(old[rest0:])
+        self._slot_elems, self._rest0, self._compact = slot, rest0, compact
+        with torch.no_grad():
+            for pr, o in zip(self.fp.params, self.fp.offsets):
+                bi = self.bucket_of_param[id(pr)]
+                base = (bi % K) * slot + (o - self.bounds[bi][0]) if bi < nl else K * slot + (o - rest0)
+                pr.data = compact[base: base + pr.numel()].view(pr.shape)
+        self.fp.flat = None          # the only full-size copy of the parameters is gone from here on
+        del old
+        self._resident = [None] * K  # which layer each slot holds
+        self._bwd_events = {}
+
+    def _param_dst(self, bi):
+        """Where the gathered parameters of bucket ``bi`` live."""
+        b0, b1 = self.bounds[bi]
+        if not self.param_slots:
+            return self.fp.flat[b0:b1]
+        if bi < self._nl:
+            k = bi % self.param_slots
+            return self._compact[k * self._slot_elems: (k + 1) * self._slot_elems]
+        o = self.param_slots * self._slot_elems + (b0 - self._rest0)
+        return self._compact[o: o + (b1 - b0)]
+
+    def _gather_bucket(self, bi, after_event=None):
+        """All-gather bucket ``bi`` into its destination. Fused path: pull kernel on the comm stream (after
+        ``after_event`` of the compute stream, if given), returns the event that marks its end. Library path: a
+        blocking ``all_gather`` on the current stream, returns None."""
+        b0, b1 = self.bounds[bi]
+        sz = (b1 - b0) // self.world
+        dst = self._param_dst(bi)
+        if bi < self._nl and self.param_slots:
+            self._resident[bi % self.param_slots] = bi
+        if not self.fused:
+            src = self.pshard_local[self.shard_off[bi]: self.shard_off[bi] + sz].contiguous()
+            if self.world > 1:
+                dist.all_gather_into_tensor(dst, src, group=self.group)
+            else:
+                dst.copy_(src)
+            return None
+        cs = self.comm_stream
+        if after_event is not None:
+            cs.wait_event(after_event)
+        es = dst.element_size()
+        self.sg.allgather_pull(self.pshard, dst, sz * es, self.shard_off[bi] * es, grid=48,
+                               stream=C.c_void_p(cs.cuda_stream))
+        ev = torch.cuda.Event()
+        ev.record(cs)
+        return ev
+
+    def _gather_initial(self):
+        """Start of a step with sharded parameters: what runs before the layers, the first K layers, what runs after
+        the layers. The compute stream waits for the first group at once, for the others where they are used."""
+        nl = self._nl
+        self._resident = [None] * self.param_slots      # whatever the slots hold predates the optimizer step
+        self._bwd_events = {}
+        tail = list(range(nl, len(self.bounds)))
+        pre = [b for b in tail if b != self.post_index]
+        for bi in pre + list(range(self.param_slots)) + ([self.post_index] if self.post_index is not None else []):
+            ev = self._gather_bucket(bi)
+            if ev is not None and (bi in pre or not self.bucket_modules):
+                torch.cuda.current_stream().wait_event(ev)
+            else:
+                self.gather_events[bi] = ev
+
+    def _after_layer_forward(self, bi, out):
+        """Layer ``bi`` is done with its slot for now: layer ``bi + K`` may be gathered over it; and before the
+        backward pass reaches layer ``bi`` its parameters must be back."""
+        K, nl = self.param_slots, self._nl
+        if bi + K < nl:
+            ev = None
+            if self.fused:
+                ev = torch.cuda.Event()
+                ev.record(torch.cuda.current_stream())
+            self.gather_events[bi + K] = self._gather_bucket(bi + K, ev)
+        if torch.is_grad_enabled():
+            outs = out if isinstance(out, (tuple, list)) else (out,)
+            for o in outs:
+                if torch.is_tensor(o) and o.requires_grad:
+                    o.register_hook(lambda g, bi=bi: self._before_layer_backward(bi))
+                    break
+
+    def _before_layer_backward(self, bi):
+        if self._resident[bi % self.param_slots] != bi:          # library path: gather on demand
+            self._gather_bucket(bi)
+        ev = self._bwd_events.pop(bi, None)
+        if ev is not None:
+            torch.cuda.current_stream().wait_event(ev)
+
+    def _after_layer_backward(self, bi):
+        """Layer ``bi``'s backward has been issued: its slot can take layer ``bi - K`` (fused path: ahead of time)."""
+        K = self.param_slots
+        if self.fused and bi - K >= 0:
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream())
+            self._bwd_events[bi - K] = self._gather_bucket(bi - K, ev)
 
     # ------------------------------------------------------------------ fused path plumbing
     def _install_hooks(self):
@@ -193,20 +327,31 @@ class ZeroEngine:
 
         def pre_hook_factory(bi):
             def pre(mod, args):
+                if eng.param_slots and eng._resident[bi % eng.param_slots] != bi:
+                    # not gathered ahead of time (library path; a forward pass outside a training step): do it now
+                    e = None
+                    if eng.fused:
+                        e = torch.cuda.Event()
+                        e.record(torch.cuda.current_stream())
+                    eng.gather_events[bi] = eng._gather_bucket(bi, e)
                 ev = eng.gather_events[bi]
                 if ev is not None:
                     torch.cuda.current_stream().wait_event(ev)
                     eng.gather_events[bi] = None
-                if torch.is_grad_enabled() and eng.stage >= 2:
+                if torch.is_grad_enabled() and ((eng.fused and eng.stage >= 2) or eng.param_slots):
                     for a in args:
                         if torch.is_tensor(a) and a.requires_grad:
-                            a.register_hook(lambda g, bi=bi: eng._bucket_ready(bi))
+                            a.register_hook(lambda g, bi=bi: eng._layer_backward_done(bi))
                             break
                 return None
             return pre
 
         for bi, mod in enumerate(self.bucket_modules):
             mod.register_forward_pre_hook(pre_hook_factory(bi))
+            if self.param_slots:
+                mod.register_forward_hook(lambda m_, a_, out, bi=bi: eng._after_layer_forward(bi, out))
+        if not self.fused:
+            return
         if self.post_index is not None and self.bucket_modules:
             pi = self.post_index
 
@@ -259,6 +404,12 @@ class ZeroEngine:
         if self.nvls:
             a.mc_buf = self._symm["grad"].multicast_ptr
         _lib.call("sx_zero_step", C.byref(a), sptr)
+
+    def _layer_backward_done(self, bi):
+        if self.fused and self.stage >= 2:
+            self._bucket_ready(bi)
+        if self.param_slots:
+            self._after_layer_backward(bi)
 
     def _bucket_ready(self, bi):
         if bi not in self._pending:
@@ -353,7 +504,10 @@ class ZeroEngine:
             done = torch.cuda.Event()
             done.record(cs)
             torch.cuda.current_stream().wait_event(done)
-        self._prefetch_params()
+        if self.param_slots:
+            self._gather_initial()
+        else:
+            self._prefetch_params()
         self._status_poll.arm(cs)
         return loss.detach()
 
@@ -410,6 +564,10 @@ class ZeroEngine:
         if p16 is None:
             self.pshard_local.copy_(self.master)
             src = self.pshard_local
+        if self.param_slots:
+            self._resident = [None] * self.param_slots
+            self._gather_initial()
+            return loss.detach()
         for bi, (b0, b1) in enumerate(self.bounds):
             sz = (b1 - b0) // w
             dist.all_gather_into_tensor(self.fp.flat[b0:b1], src[self.shard_off[bi]: self.shard_off[bi] + sz].contiguous(),
@@ -450,13 +608,21 @@ class ZeroEngine:
             self.pshard.tensor.copy_(self.master)
             torch.cuda.synchronize()
             dist.barrier(self.group)          # every rank's shard is in place before anyone pulls
-            self._prefetch_params()
+            if self.param_slots:
+                self._resident = [None] * self.param_slots
+                self._gather_initial()
+            else:
+                self._prefetch_params()
             self.comm_stream.synchronize()
             torch.cuda.current_stream().wait_stream(self.comm_stream)
             self.gather_events = [None] * len(self.bounds)
             dist.barrier(self.group)
             return
         self.pshard_local.copy_(self.master)
+        if self.param_slots:
+            self._resident = [None] * self.param_slots
+            self._gather_initial()
+            return
         for bi, (b0, b1) in enumerate(self.bounds):
             sz = (b1 - b0) // w
             src = self.pshard_local[self.shard_off[bi]: self.shard_off[bi] + sz].contiguous()

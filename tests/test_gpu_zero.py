@@ -10,11 +10,11 @@ pytestmark = pytest.mark.gpu
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
-@pytest.mark.parametrize("stage,mode", [(1, "p2p"), (3, "p2p"), (3, "nvls")])
+@pytest.mark.parametrize("stage,mode", [(1, "p2p"), (3, "p2p"), (3, "nvls"), (3, "slots")])
 def test_fused_zero_two_gpus(stage, mode):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
-    port = 29600 + stage + (4 if mode == "nvls" else 0)
+    port = 29600 + stage + {"nvls": 4, "slots": 6}.get(mode, 0)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
            "127.0.0.1", "--master-port", str(port), os.path.join(HERE, "mp_zero_check.py"), str(stage), mode]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=240)

@@ -63,6 +63,56 @@ def test_zero_matches_single_process(stage):
     assert abs(nrm - float(eng.last_norm[1])) < 1e-3 * max(1.0, nrm)
 
 
+def _slots_worker(rank, world, port, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    cfg = _cfg()
+    cfg.num_hidden_layers = 5
+    out = {}
+    for slots in (0, 2, 3):
+        torch.manual_seed(0)
+        model = build_model(cfg)
+        eng = ZeroEngine(model, zero_stage=3, lr=1e-2, weight_decay=0.1, max_grad_norm=1.0, param_slots=slots)
+        if slots:
+            assert eng.fp.flat is None and eng._compact.numel() < eng.fp.total
+            # the parameters of layers i and i + slots share memory
+            a, b = eng.bucket_params[0][0], eng.bucket_params[slots][0]
+            assert a.data_ptr() == b.data_ptr()
+        losses = []
+        for step in range(4):
+            ids = torch.randint(0, 256, (2, 16), generator=torch.Generator().manual_seed(100 * rank + step))
+            losses.append(eng.step(ids, ids).item())
+        with torch.no_grad():          # a forward pass outside a training step gathers layer by layer on demand
+            ev = float(model(torch.arange(16).view(1, 16), labels=torch.arange(16).view(1, 16))["loss"])
+        out[slots] = (losses, eng.master.numpy().copy(), eng.m.numpy().copy(), float(eng.last_norm[1]), ev)   # by value
+    if rank == 0:
+        q.put(out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_sharded_parameter_slots_match_the_resident_parameter_engine():
+    """``param_slots=K``: K rotating layer slots instead of the full gathered parameter buffer. Losses, gradient norm,
+    master weights and moments after four steps (different data per rank) equal those of the engine that keeps every
+    parameter resident, for K = 2 and 3 over five layers."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + os.getpid() % 2000 + 40
+    procs = [ctx.Process(target=_slots_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    out = q.get(timeout=300)
+    for p in procs:
+        p.join(60)
+        assert p.exitcode == 0
+    base = out[0]
+    for k in (2, 3):
+        losses, master, m, nrm, ev = out[k]
+        assert losses == base[0], (k, losses, base[0])
+        assert (master == base[1]).all() and (m == base[2]).all() and nrm == base[3] and ev == base[4]
+
+
 def test_zero_buckets_of_small_tensors_split_evenly():
     """Mamba-2 layers hold tensors of 8 and 512 elements; every bucket must still be a multiple of 64 * world."""
     torch.manual_seed(0)
