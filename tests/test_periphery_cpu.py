@@ -37,7 +37,8 @@ def test_jit_and_tensor_api():
     assert torch.allclose(jit.vmap(lambda r: r.sum())(torch.ones(3, 4)), torch.full((3,), 4.0))
     assert jit.jacobian(lambda r: r * 2)(v).shape == (2, 2)
     fn = lambda a: a + 1  # noqa: E731
-    assert jit.trace(fn, v) is fn                         # CPU: no capture
+    traced = jit.trace(fn, v)                             # CPU: a replayed tape, no CUDA-graph capture
+    assert torch.equal(traced(v * 2), fn(v * 2)) and traced.traces == 1
     x = torch.tensor([0.113, -0.5], requires_grad=True)
     T.fake_quant(x, 4).sum().backward()
     assert torch.allclose(x.grad, torch.ones(2))           # straight-through
