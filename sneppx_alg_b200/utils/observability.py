@@ -176,24 +176,140 @@ class ExperimentTracker:
 
 
 class WandbTracker(ExperimentTracker):
-    """Uses wandb when importable, otherwise behaves like the local tracker."""
+    """Weights & Biases. With the ``wandb`` package importable the run is also opened there in offline mode; in every
+    case an offline-run directory in wandb's layout is written (``wandb/offline-run-<time>-<id>/files`` with
+    ``config.yaml``, ``wandb-history.jsonl`` - one JSON object per logged step with ``_step`` / ``_timestamp`` /
+    ``_runtime`` - and ``wandb-summary.json`` holding the last value of every metric), next to the local files."""
 
     def start_run(self, run_name=None, params=None):
+        import secrets
         try:
             import wandb  # noqa: F401
-            self._wandb = wandb.init(project=self.experiment, name=run_name, config=params, mode="offline")
+            os.makedirs(self.dir, exist_ok=True)
+            self._wandb = wandb.init(project=self.experiment, name=run_name, config=params, mode="offline", dir=self.dir)
         except Exception:  # noqa: BLE001
             self._wandb = None
-        return super().start_run(run_name, params)
+        rid = super().start_run(run_name, params)
+        self.wandb_id = secrets.token_hex(4)
+        self._t0 = time.time()
+        self.wandb_dir = os.path.join(self.dir, "wandb", f"offline-run-{time.strftime('%Y%m%d_%H%M%S')}-{self.wandb_id}", "files")
+        os.makedirs(self.wandb_dir, exist_ok=True)
+        with open(os.path.join(self.wandb_dir, "config.yaml"), "w") as f:
+            f.write("wandb_version: 1\n\n")
+            for k, v in (params or {}).items():
+                f.write(f"{k}:\n  desc: null\n  value: {json.dumps(v, default=str)}\n")
+        self._summary, self._wstep = {}, 0
+        return rid
 
     def log_metrics(self, metrics, step=None):
         if getattr(self, "_wandb", None):
             self._wandb.log(metrics, step=step)
         super().log_metrics(metrics, step)
+        self._wstep = step if step is not None else self._wstep + 1
+        row = {k: float(v) for k, v in metrics.items()}
+        now = time.time()
+        row.update(_step=self._wstep, _timestamp=now, _runtime=now - self._t0)
+        with open(os.path.join(self.wandb_dir, "wandb-history.jsonl"), "a") as f:
+            f.write(json.dumps(row) + "\n")
+        self._summary.update(row)
+        with open(os.path.join(self.wandb_dir, "wandb-summary.json"), "w") as f:
+            json.dump(self._summary, f)
+
+    def end_run(self):
+        if getattr(self, "_wandb", None):
+            self._wandb.finish()
+        super().end_run()
 
 
 class MLflowTracker(ExperimentTracker):
-    pass
+    """Writes MLflow's file-store layout under ``<dir>/mlruns`` (what ``mlflow ui --backend-store-uri <dir>/mlruns``
+    reads): ``<experiment id>/meta.yaml``, and per run ``meta.yaml``, ``params/<key>`` (the value as text),
+    ``metrics/<key>`` (one ``<timestamp ms> <value> <step>`` line per logged point), ``tags/<key>`` and ``artifacts/``.
+    The local JSONL files of the base tracker are written as well."""
+
+    def _experiment_dir(self):
+        root = os.path.join(self.dir, "mlruns")
+        os.makedirs(root, exist_ok=True)
+        for d in sorted(os.listdir(root)):
+            meta = os.path.join(root, d, "meta.yaml")
+            if os.path.exists(meta) and f"name: {self.experiment}\n" in open(meta).read():
+                return os.path.join(root, d), d
+        ids = [int(d) for d in os.listdir(root) if d.isdigit()]
+        eid = str(max(ids) + 1 if ids else 0)
+        path = os.path.join(root, eid)
+        os.makedirs(path)
+        with open(os.path.join(path, "meta.yaml"), "w") as f:
+            f.write(f"artifact_location: {path}\ncreation_time: {int(time.time() * 1000)}\nexperiment_id: '{eid}'\n"
+                    f"last_update_time: {int(time.time() * 1000)}\nlifecycle_stage: active\nname: {self.experiment}\n")
+        return path, eid
+
+    def start_run(self, run_name=None, params=None):
+        import uuid
+        rid = super().start_run(run_name, None)
+        exp_dir, eid = self._experiment_dir()
+        self.mlflow_run_id = uuid.uuid4().hex
+        self.mlflow_dir = os.path.join(exp_dir, self.mlflow_run_id)
+        for sub in ("params", "metrics", "tags", "artifacts"):
+            os.makedirs(os.path.join(self.mlflow_dir, sub))
+        self._start_ms = int(time.time() * 1000)
+        self._write_meta("RUNNING", None)
+        self.set_tags({"mlflow.runName": rid, "mlflow.source.type": "LOCAL", "mlflow.user": os.environ.get("USER", "unknown")})
+        self._eid = eid
+        if params:
+            self.log_params(params)
+        return rid
+
+    def _write_meta(self, status, end_ms):
+        names = {"RUNNING": 1, "FINISHED": 3, "FAILED": 4}
+        with open(os.path.join(self.mlflow_dir, "meta.yaml"), "w") as f:
+            f.write(f"artifact_uri: {os.path.join(self.mlflow_dir, 'artifacts')}\nend_time: {end_ms if end_ms else 'null'}\n"
+                    f"entry_point_name: ''\nexperiment_id: '{getattr(self, '_eid', '0')}'\nlifecycle_stage: active\n"
+                    f"run_id: {self.mlflow_run_id}\nrun_uuid: {self.mlflow_run_id}\nsource_name: ''\nsource_type: 4\n"
+                    f"source_version: ''\nstart_time: {self._start_ms}\nstatus: {names[status]}\ntags: []\nuser_id: "
+                    f"{os.environ.get('USER', 'unknown')}\n")
+
+    @staticmethod
+    def _safe_key(k: str) -> str:
+        import re
+        return re.sub(r"[^A-Za-z0-9_./ -]", "_", str(k)).strip("/").replace("..", "_") or "_"
+
+    def set_tags(self, tags: dict):
+        for k, v in tags.items():
+            path = os.path.join(self.mlflow_dir, "tags", self._safe_key(k))
+            os.makedirs(os.path.dirname(path), exist_ok=True)
+            with open(path, "w") as f:
+                f.write(str(v))
+
+    def log_params(self, params: dict):
+        super().log_params(params)
+        for k, v in params.items():
+            path = os.path.join(self.mlflow_dir, "params", self._safe_key(k))
+            os.makedirs(os.path.dirname(path), exist_ok=True)
+            with open(path, "w") as f:
+                f.write(str(v))
+
+    def log_metrics(self, metrics, step=None):
+        super().log_metrics(metrics, step)
+        ts = int(time.time() * 1000)
+        for k, v in metrics.items():
+            path = os.path.join(self.mlflow_dir, "metrics", self._safe_key(k))
+            os.makedirs(os.path.dirname(path), exist_ok=True)
+            with open(path, "a") as f:
+                f.write(f"{ts} {float(v)} {int(step) if step is not None else 0}\n")
+
+    def log_artifact(self, path: str):
+        import shutil
+        super().log_artifact(path)
+        shutil.copy(path, os.path.join(self.mlflow_dir, "artifacts"))
+
+    def end_run(self, status: str = "FINISHED"):
+        super().end_run()
+        self._write_meta(status, int(time.time() * 1000))
+
+    def read_metric(self, key: str):
+        """[(timestamp ms, value, step)] of one metric of the current run, as stored."""
+        with open(os.path.join(self.mlflow_dir, "metrics", self._safe_key(key))) as f:
+            return [(int(a), float(b), int(c)) for a, b, c in (line.split() for line in f if line.strip())]
 
 
 class CompositeTracker:
