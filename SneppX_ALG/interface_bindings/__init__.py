@@ -99,8 +99,8 @@ __all__ = sorted(_WHERE)
 def __getattr__(name):
     where = _WHERE.get(name)
     if where is None:
-        # everything else with a counterpart is collected in sneppx_alg_b200.compat (and .compat_services)
-        for mod in ("compat", "compat_services"):
+        # everything else with a counterpart is collected in sneppx_alg_b200.compat_classes, .compat and .compat_services
+        for mod in ("compat_classes", "compat", "compat_services"):
             try:
                 obj = getattr(importlib.import_module(f"sneppx_alg_b200.{mod}"), name)
             except (AttributeError, ModuleNotFoundError):

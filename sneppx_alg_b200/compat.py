@@ -8,6 +8,7 @@ package's modules or on ``torch``, not a placeholder; ``SneppX_ALG`` resolves un
 from __future__ import annotations
 
 import ctypes
+import enum
 import math
 import random as _random
 from dataclasses import dataclass
@@ -23,7 +24,6 @@ from .optim import zoo as _zoo
 from .training import schedulers as _sched
 
 # ----------------------------------------------------------------------------------------- layers (keras / torch style)
-Dense = _nn.Linear
 Flatten = tnn.Flatten
 Softmax = tnn.Softmax
 Conv2D = tnn.Conv2d
@@ -33,7 +33,11 @@ BatchNormalization = tnn.BatchNorm2d
 PyTorchModule, PyTorchLinear, PyTorchEmbedding, PyTorchLayerNorm = _nn.Module, _nn.Linear, _nn.Embedding, _nn.LayerNorm
 PyTorchDropout, PyTorchSequential, PyTorchConv2d, PyTorchParameter, PyTorchTensor = _nn.Dropout, tnn.Sequential, tnn.Conv2d, tnn.Parameter, torch.Tensor
 Param = tnn.Parameter
-LlamaRMSNorm = _nn.RMSNorm
+
+
+class LlamaRMSNorm(_nn.RMSNorm):
+    """RMSNorm under the name the Llama model files use."""
+
 
 
 class Activation(tnn.Module):
@@ -52,14 +56,19 @@ class Activation(tnn.Module):
         return self._FN[self.name](x)
 
 
-class Input:
+class InputSpec:
     """Keras-style input placeholder: records the per-sample shape."""
 
     def __init__(self, shape: Sequence[int], dtype=torch.float32):
         self.shape, self.dtype = tuple(shape), dtype
 
     def example(self, batch: int = 1):
-        return torch.zeros((batch,) + self.shape, dtype=self.dtype)
+        return torch.zeros((batch,) + tuple(d or 1 for d in self.shape), dtype=self.dtype)
+
+
+def Input(shape: Sequence[int], dtype=torch.float32) -> InputSpec:
+    """The input placeholder of a functional model (reference: interface_bindings/keras_api.py:362)."""
+    return InputSpec(shape, dtype)
 
 
 class PatchEmbedding(tnn.Module):
@@ -76,7 +85,6 @@ class PatchEmbedding(tnn.Module):
 
 # ----------------------------------------------------------------------------------------- losses
 MSELoss, BCELoss, CrossEntropyLoss, NLLLoss, KLDivLoss = tnn.MSELoss, tnn.BCELoss, tnn.CrossEntropyLoss, tnn.NLLLoss, tnn.KLDivLoss
-MAELoss = MAE = tnn.L1Loss
 
 
 def kd_loss(student_logits, teacher_logits, T: float = 2.0):
@@ -230,42 +238,62 @@ CosineAnnealingWarmRestarts = torch.optim.lr_scheduler.CosineAnnealingWarmRestar
 CosineLR = torch.optim.lr_scheduler.CosineAnnealingLR
 
 
-def ConstantLRWithWarmup(optimizer, warmup_steps: int):
-    return _lambda_scheduler(optimizer, lambda s: min(1.0, (s + 1) / max(warmup_steps, 1)))
+class _ShapedLR(torch.optim.lr_scheduler.LambdaLR):
+    """A multiplicative schedule given by ``shape(step) -> factor``; subclasses fix the shape from their arguments."""
+
+    def __init__(self, optimizer, shape):
+        self.shape = shape
+        super().__init__(optimizer, shape)
 
 
-def CosineAnnealingWithWarmup(optimizer, warmup_steps: int, total_steps: int, min_ratio: float = 0.0):
-    def f(s):
-        if s < warmup_steps:
-            return (s + 1) / max(warmup_steps, 1)
-        t = min(1.0, (s - warmup_steps) / max(total_steps - warmup_steps, 1))
-        return min_ratio + (1 - min_ratio) * 0.5 * (1 + math.cos(math.pi * t))
-    return _lambda_scheduler(optimizer, f)
+class ConstantLRWithWarmup(_ShapedLR):
+    def __init__(self, optimizer, warmup_steps: int):
+        self.warmup_steps = warmup_steps
+        super().__init__(optimizer, lambda s: min(1.0, (s + 1) / max(warmup_steps, 1)))
 
 
-LinearWarmupCosineDecay = CosineAnnealingWithWarmup
+class CosineAnnealingWithWarmup(_ShapedLR):
+    def __init__(self, optimizer, warmup_steps: int, total_steps: int, min_ratio: float = 0.0):
+        self.warmup_steps, self.total_steps, self.min_ratio = warmup_steps, total_steps, min_ratio
+
+        def f(s):
+            if s < warmup_steps:
+                return (s + 1) / max(warmup_steps, 1)
+            t = min(1.0, (s - warmup_steps) / max(total_steps - warmup_steps, 1))
+            return min_ratio + (1 - min_ratio) * 0.5 * (1 + math.cos(math.pi * t))
+        super().__init__(optimizer, f)
 
 
-def CosineAnnealingWithWarmupRestarts(optimizer, warmup_steps: int, cycle_steps: int, min_ratio: float = 0.0):
-    def f(s):
-        s = s % max(cycle_steps, 1)
-        if s < warmup_steps:
-            return (s + 1) / max(warmup_steps, 1)
-        t = (s - warmup_steps) / max(cycle_steps - warmup_steps, 1)
-        return min_ratio + (1 - min_ratio) * 0.5 * (1 + math.cos(math.pi * t))
-    return _lambda_scheduler(optimizer, f)
+class LinearWarmupCosineDecay(CosineAnnealingWithWarmup):
+    """The reference's second name for linear warm-up followed by cosine decay."""
 
 
-def TriStageLR(optimizer, warmup_steps: int, hold_steps: int, decay_steps: int, init_ratio: float = 0.01, final_ratio: float = 0.01):
+class CosineAnnealingWithWarmupRestarts(_ShapedLR):
+    def __init__(self, optimizer, warmup_steps: int, cycle_steps: int, min_ratio: float = 0.0):
+        self.warmup_steps, self.cycle_steps, self.min_ratio = warmup_steps, cycle_steps, min_ratio
+
+        def f(s):
+            s = s % max(cycle_steps, 1)
+            if s < warmup_steps:
+                return (s + 1) / max(warmup_steps, 1)
+            t = (s - warmup_steps) / max(cycle_steps - warmup_steps, 1)
+            return min_ratio + (1 - min_ratio) * 0.5 * (1 + math.cos(math.pi * t))
+        super().__init__(optimizer, f)
+
+
+class TriStageLR(_ShapedLR):
     """Linear warm-up, hold, exponential decay to final_ratio."""
-    def f(s):
-        if s < warmup_steps:
-            return init_ratio + (1 - init_ratio) * s / max(warmup_steps, 1)
-        if s < warmup_steps + hold_steps:
-            return 1.0
-        t = min(1.0, (s - warmup_steps - hold_steps) / max(decay_steps, 1))
-        return math.exp(math.log(final_ratio) * t)
-    return _lambda_scheduler(optimizer, f)
+
+    def __init__(self, optimizer, warmup_steps: int, hold_steps: int, decay_steps: int, init_ratio: float = 0.01,
+                 final_ratio: float = 0.01):
+        def f(s):
+            if s < warmup_steps:
+                return init_ratio + (1 - init_ratio) * s / max(warmup_steps, 1)
+            if s < warmup_steps + hold_steps:
+                return 1.0
+            t = min(1.0, (s - warmup_steps - hold_steps) / max(decay_steps, 1))
+            return math.exp(math.log(final_ratio) * t)
+        super().__init__(optimizer, f)
 
 
 # ----------------------------------------------------------------------------------------- optimizers by name
@@ -388,8 +416,13 @@ def dequantize_fp8_e5m2(codes):
     return _qa.fp8_decode(codes, _qa.QuantMode.FP8_E5M2)
 
 
-quantize_mx = _qa.mx_quantize
-MX_FORMATS = dict(getattr(_qa, "_MX", {}))
+MX_FORMATS = _qa.MX_FORMATS
+
+
+def quantize_mx(x, fmt: str = "mxfp8", block: int = 32):
+    """Micro-scaling fake quantisation by the short family name ("mxfp8" / "mxfp6" / "mxfp4") or by a full format
+    name of ``MX_FORMATS`` ("mxfp6_e2m3", ...)."""
+    return _qa.mx_quantize_spec(x, fmt, block) if fmt in _qa.MX_FORMATS else _qa.mx_quantize(x, fmt, block)
 
 
 def dequantize_mx(x, fmt: str = "mxfp8"):
@@ -565,7 +598,21 @@ class Fixed:
         return self.value
 
 
-uniform, log_uniform, choice = UniformFloat, LogUniformFloat, lambda *o: Choice(o[0] if len(o) == 1 and isinstance(o[0], (list, tuple)) else o)
+def uniform(low: float, high: float) -> UniformFloat:
+    return UniformFloat(float(low), float(high))
+
+
+def log_uniform(low: float, high: float) -> LogUniformFloat:
+    return LogUniformFloat(float(low), float(high))
+
+
+def int_(low: int, high: int) -> UniformInt:
+    """An integer range of a search space, both ends included (reference: interface_bindings/hpo.py:53)."""
+    return UniformInt(int(low), int(high))
+
+
+def choice(*o) -> Choice:
+    return Choice(o[0] if len(o) == 1 and isinstance(o[0], (list, tuple)) else o)
 
 
 @dataclass
@@ -575,19 +622,51 @@ class Trial:
     value: Optional[float] = None
 
 
-class RandomSampler:
-    def __init__(self, seed: int = 0):
-        self.rng = _random.Random(seed)
+class Sampler:
+    """Base of the search samplers (reference: interface_bindings/hparams.py:173). A sampler is stateless about the
+    space: ``suggest(space, history)`` returns the next parameter set given the trials so far; a sampler bound to a
+    space at construction also answers ``sample()`` and ``total_trials()``."""
+
+    def __init__(self, space: Optional[Dict[str, Any]] = None, seed: int = 42):
+        self.space, self.rng, self._drawn = space, _random.Random(seed), []
+
+    def suggest(self, space: Dict[str, Any], history: List["Trial"]) -> Dict[str, Any]:
+        raise NotImplementedError
+
+    def sample(self) -> Dict[str, Any]:
+        if self.space is None:
+            raise ValueError("this sampler was built without a search space")
+        params = self.suggest(self.space, self._drawn)
+        self._drawn.append(Trial(len(self._drawn), params))
+        return params
+
+    def total_trials(self) -> Optional[int]:
+        """Number of distinct trials when the space is finite, else None."""
+        return None
+
+
+class RandomSampler(Sampler):
+    def __init__(self, seed: int = 0, space: Optional[Dict[str, Any]] = None):
+        super().__init__(space, seed)
 
     def suggest(self, space: Dict[str, Any], history: List[Trial]):
         return {k: v.sample(self.rng) for k, v in space.items()}
 
 
-class GridSampler:
+class GridSampler(Sampler):
     """Cartesian product of ``Choice`` / ``Fixed`` dimensions, in order."""
 
-    def __init__(self):
+    def __init__(self, space: Optional[Dict[str, Any]] = None):
+        super().__init__(space)
         self._grid = None
+
+    def total_trials(self) -> Optional[int]:
+        if self.space is None:
+            return None
+        n = 1
+        for v in self.space.values():
+            n *= len(v.options) if isinstance(v, Choice) else 1
+        return n
 
     def suggest(self, space, history):
         if self._grid is None:
@@ -929,13 +1008,19 @@ from .models import llama as _llama  # noqa: E402
 from .models.deepseek import DeepSeekLayer as DeepSeekV2DecoderLayer  # noqa: E402,F401
 from .nn import attention as _attn  # noqa: E402
 
-LlamaDecoderLayer = MistralDecoderLayer = Qwen2DecoderLayer = _llama.LlamaBlock
-MistralAttention = Qwen2Attention = _llama.LlamaAttention
-MistralMLP = Qwen2MLP = DeepSeekV2MLP = _llama.LlamaMLP
+LlamaDecoderLayer = _llama.LlamaBlock
+MistralDecoderLayer, Qwen2DecoderLayer = _llama.MistralDecoderLayer, _llama.Qwen2DecoderLayer
+MistralAttention, Qwen2Attention = _llama.MistralAttention, _llama.Qwen2Attention
+MistralMLP, Qwen2MLP = _llama.MistralMLP, _llama.Qwen2MLP
+
+
+class DeepSeekV2MLP(_llama.LlamaMLP):
+    """The dense SwiGLU feed-forward of DeepSeek-V2's first layers and of its shared experts."""
+
 DeepSeekV2Attention = _attn.MultiHeadLatentAttention
-LlamaModel, MistralModel, Qwen2Model = _llama.LlamaForCausalLM, _llama.MistralForCausalLM, _llama.Qwen2ForCausalLM
-GPTLMHeadModel, T5Model, ViTBlock = _fam.GPTModel, _fam.T5ForConditionalGeneration, _fam._Block
-SERExpert = _llama.LlamaMLP
+LlamaModel, MistralModel, Qwen2Model = _llama.LlamaModel, _llama.MistralModel, _llama.Qwen2Model
+GPTLMHeadModel, T5Model, ViTBlock = _fam.GPTLMHeadModel, _fam.T5Model, _fam._Block
+MAE, mae_base, mae_large = _fam.MAE, _fam.mae_base, _fam.mae_large
 
 
 def _family_table(family):
@@ -1082,11 +1167,47 @@ def detect_cpu() -> dict:
     return {"arch": platform.machine(), "cores": os.cpu_count(), **{f: f in flags.split() for f in ("sse4_2", "avx2", "avx512f")}}
 
 
-CPUFeatures = detect_cpu
+class CPUFeatures:
+    """Instruction-set features of the host CPU, read from the kernel's flag list once at construction
+    (reference: interface_bindings/asm_bridge.py:17 reads the same bits through cpuid)."""
+
+    NAMES = {"aes_ni": "aes", "sha_ni": "sha_ni", "avx2": "avx2", "avx512f": "avx512f", "sse2": "sse2", "sse4_2": "sse4_2",
+             "bmi2": "bmi2", "adx": "adx"}
+
+    def __init__(self):
+        try:
+            flags = next(l for l in open("/proc/cpuinfo") if l.startswith("flags")).split(":", 1)[1].split()
+        except (OSError, StopIteration):
+            flags = []
+        self._features = {k: v in flags for k, v in self.NAMES.items()}
+
+    def has(self, name: str) -> bool:
+        return bool(self._features.get(name, False))
+
+    def as_dict(self) -> dict:
+        return dict(self._features)
+
+    def __getattr__(self, name):
+        if name.startswith("has_") and name[4:] in self.NAMES:
+            return self._features[name[4:]]
+        raise AttributeError(name)
 CUDAStream = torch.cuda.Stream
 CUDAEvent = torch.cuda.Event
-CUDADeviceProps = DeviceInfo = _device.DeviceProperties
-ComputeCapability = get_device_capability
+class ComputeCapability(enum.Enum):
+    """Named compute-capability levels; ``ComputeCapability.of(i)`` is the newest level device ``i`` reaches."""
+
+    PASCAL = (6, 0)
+    VOLTA = (7, 0)
+    TURING = (7, 5)
+    AMPERE = (8, 0)
+    HOPPER = (9, 0)
+    BLACKWELL = (10, 0)
+
+    @classmethod
+    def of(cls, i: int = 0):
+        cap = tuple(get_device_capability(i))
+        reached = [c for c in cls if c.value <= cap]
+        return reached[-1] if reached else None
 
 
 class CUDADevice:
@@ -1108,7 +1229,7 @@ class CUDADevice:
     synchronize = staticmethod(_device.synchronize)
 
 
-Device = DeviceContext = CUDADriver = CUDADevice
+Device = CUDADevice
 
 
 def get_backend() -> str:
@@ -1119,7 +1240,7 @@ get_kernel_backend = get_algo_backend = get_infra_backend = get_security_backend
 
 int8_t, int16_t, int32_t, int64_t = ctypes.c_int8, ctypes.c_int16, ctypes.c_int32, ctypes.c_int64
 uint8_t, uint16_t, uint32_t, uint64_t = ctypes.c_uint8, ctypes.c_uint16, ctypes.c_uint32, ctypes.c_uint64
-int_, float_t, double_t, size_t, ssize_t = ctypes.c_int, ctypes.c_float, ctypes.c_double, ctypes.c_size_t, ctypes.c_ssize_t
+float_t, double_t, size_t, ssize_t = ctypes.c_float, ctypes.c_double, ctypes.c_size_t, ctypes.c_ssize_t
 void_p, const_char_p = ctypes.c_void_p, ctypes.c_char_p
 
 
@@ -1235,7 +1356,47 @@ class SipHash:
         return _c.siphash24(self.key, data)
 
 
-DRBG = EntropyPool = _c.HmacDrbg
+DRBG = _c.HmacDrbg
+
+
+class EntropyPool:
+    """Collects entropy from several sources (OS randomness, clock jitter, caller-supplied bytes), hashes it into a
+    pool and seeds an HMAC-DRBG from the pool; ``random_bytes`` draws from the DRBG and reseeds it every
+    ``reseed_interval`` calls (reference: interface_bindings/crypto_util.py:149)."""
+
+    def __init__(self, reseed_interval: int = 1024):
+        import hashlib
+        self._h = hashlib.sha512()
+        self._n, self._interval, self._drbg = 0, reseed_interval, None
+        self.collect()
+
+    def add(self, data: bytes):
+        self._h.update(len(data).to_bytes(4, "big") + bytes(data))
+
+    def collect(self):
+        import os
+        import time
+        self.add(os.urandom(48))
+        jitter = bytearray()
+        for _ in range(64):
+            jitter += (time.perf_counter_ns() & 0xFF).to_bytes(1, "big")
+        self.add(bytes(jitter))
+        self.add(os.getpid().to_bytes(4, "big"))
+
+    def _seed(self) -> bytes:
+        d = self._h.digest()
+        self._h.update(d)
+        return d
+
+    def random_bytes(self, n: int) -> bytes:
+        if self._drbg is None:
+            self._drbg = _c.HmacDrbg(self._seed())
+        elif self._n and self._n % self._interval == 0:
+            self.collect()
+            self.add(self._drbg.generate(32))
+            self._drbg = _c.HmacDrbg(self._seed())
+        self._n += 1
+        return self._drbg.generate(n)
 KyberKEM, Dilithium, SphincsPlus = _c.KyberKEM, _c.Dilithium, _c.SphincsPlus
 MontgomeryMul = _c.MontgomeryMul
 SecureAllocator = _c.GuardedBuffer
@@ -1245,7 +1406,6 @@ class ConstantTime:
     equal = staticmethod(_c.ct_equal)
 
 
-ConstantTimeOps = ConstantTime
 
 
 class ModelHasher:

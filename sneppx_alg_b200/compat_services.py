@@ -12,6 +12,7 @@ bytecode, ``security/obfuscation.py``).
 """
 from __future__ import annotations
 
+import enum
 import json
 import os
 import threading
@@ -49,7 +50,7 @@ get_audit_logger, set_audit_logger = _accessor("audit", lambda: _svc.AuditLogger
 get_ddos_mitigation, set_ddos_mitigation = _accessor("ddos", _svc.DDoSMitigator)
 get_key_manager, set_key_manager = _accessor("keys", _svc.ApiKeyStore)
 get_usage_tracker, set_usage_tracker = _accessor("usage", _svc.UsageTracker)
-DDoSMitigation, ApiKeyManager, SlidingWindowRateLimiter = _svc.DDoSMitigator, _svc.ApiKeyStore, _svc.TokenBucket
+DDoSMitigation = _svc.DDoSMitigator
 
 
 class SelfAuditor:
@@ -207,7 +208,6 @@ class UserStore:
 
 
 get_user_store, set_user_store = _accessor("users", UserStore)
-Authenticator = IdentityManager = UserStore
 
 
 @dataclass
@@ -237,7 +237,6 @@ class ContainerSecurityManager:
     scan_image = scan_requirements
 
 
-ContainerSecurity = CVEScanner = ContainerSecurityManager
 get_container_security, set_container_security = _accessor("container", ContainerSecurityManager)
 generate_sbom = lambda packages, known=None: _svc.sbom(packages, known)  # noqa: E731
 scan_requirements = scan_image = lambda packages: get_container_security().scan_requirements(packages)  # noqa: E731
@@ -277,7 +276,6 @@ class SignedUpdateManager:
         return True
 
 
-SignedUpdate = SignedUpdateManager
 
 
 # ----------------------------------------------------------------------------------------- serving schema and helpers
@@ -400,16 +398,24 @@ def serve_from_config(path: str):
 inference_app = serve_from_config
 
 
-class TokenStreamer:
-    """Collects tokens pushed by the engine's ``on_token`` callback; iterating yields them as they arrive."""
+from .compat_classes import Streamer  # noqa: E402
+
+
+class TokenStreamer(Streamer):
+    """Collects tokens pushed by a generation loop (``put(token)``) or by the engine's ``on_token`` callback
+    (``put(request_id, token)``); iterating yields them as they arrive, ``get_tokens`` returns those seen so far."""
 
     def __init__(self):
         self._q, self._cv, self._done = [], threading.Condition(), False
 
-    def put(self, _request_id, token: int):
+    def put(self, *args):
         with self._cv:
-            self._q.append(token)
+            self._q.append(int(args[-1]))
             self._cv.notify_all()
+
+    def get_tokens(self) -> List[int]:
+        with self._cv:
+            return list(self._q)
 
     def end(self):
         with self._cv:
@@ -428,17 +434,6 @@ class TokenStreamer:
             yield tok
 
 
-class TextStreamer(TokenStreamer):
-    def __init__(self, tokenizer):
-        super().__init__()
-        self.tokenizer = tokenizer
-
-    def text(self):
-        for tok in self:
-            yield self.tokenizer.decode([tok])
-
-
-Streamer = TokenStreamer
 
 
 def sample(logits, temperature=1.0, top_k=0, top_p=1.0, generator=None):
@@ -462,7 +457,6 @@ def incremental_attention_forward(q, k, v, state: Optional[dict] = None):
     return o.to(q.dtype), {"o": o.float(), "lse": lse}
 
 
-IncrementalAttentionState = dict
 
 
 def chunked_prefill_forward(model, input_ids, chunk: int = 512):
@@ -587,7 +581,6 @@ class ExperimentRun:
         self.status = status
 
 
-Run = ExperimentRun
 
 
 class Experiment:
@@ -655,7 +648,7 @@ class LineageStore:
 
 
 # ----------------------------------------------------------------------------------------- ONNX, graph, NPE, ARC, FM aliases
-OnnxModel, OnnxGraph, OnnxNode, OnnxTensor, OnnxInitializer = _onnx.Model, _onnx.Graph, _onnx.Node, _onnx.Tensor, _onnx.Tensor
+OnnxModel, OnnxGraph, OnnxNode = _onnx.Model, _onnx.Graph, _onnx.Node
 onnx_check = onnx_validate = _onnx.check_model
 quantize_graph_weights = _onnx.quantize_qdq
 
@@ -709,7 +702,7 @@ def select_execution_provider(preferred: Sequence[str] = ("cuda", "cpu")) -> str
 
 from . import graph as _graph  # noqa: E402
 
-GraphNode, TensorExpr, StateGraph = _graph.ExprNode, _graph.ExprNode, _graph.ExprGraph
+StateGraph = _graph.ExprGraph
 
 
 class CompiledGraph:
@@ -747,7 +740,6 @@ class GraphCompiler:
         return CompiledGraph(graph, outputs, self.fuse)
 
 
-TensorExprCompiler = GraphCompiler
 FUSABLE_OPS = ("matmul", "bias", "relu", "gelu", "silu", "add", "mul")
 
 
@@ -792,21 +784,53 @@ class Tracer:
         self.traces[name or getattr(fn, "__name__", f"fn{len(self.traces)}")] = t
         return t
 
-NPEInstruction, NPECompiler, NPEVerify = _npe.Instruction, _npe.compile_mlp, _npe.verify_program
+NPEInstruction = _npe.Instruction
 ARCInputGuard, ARCGradientObfuscator, ARCOutputVerifier, ARCAttackSim = _arc.InputGuard, _arc.GradientObfuscator, _arc.OutputVerifier, _arc.simulate_attack
-ARCFForward = _arc.ARCLayer
-FMMemoryBank, FMNode, FMSync = _fm.MemoryBank, _fm.Node, _fm.FMSyncNCCL
+FMMemoryBank, FMNode = _fm.MemoryBank, _fm.Node
 
 
-def FGSM(x, loss_fn, epsilon=0.1, lo=-1.0, hi=1.0):
-    return _arc.simulate_attack(x, _arc.ATTACK_FGSM, epsilon, loss_fn, lo=lo, hi=hi)
+class Attack:
+    """An input-space attack with a perturbation budget ``epsilon`` inside the box [lo, hi]. ``attack(x, loss_fn)``
+    (or calling the object) returns the adversarial input; subclasses name the method."""
+
+    kind = _arc.ATTACK_FGSM
+
+    def __init__(self, epsilon=0.1, lo=-1.0, hi=1.0, **extra):
+        self.epsilon, self.lo, self.hi, self.extra = epsilon, lo, hi, extra
+
+    def attack(self, x, loss_fn):
+        return _arc.simulate_attack(x, self.kind, self.epsilon, loss_fn, lo=self.lo, hi=self.hi, **self.extra)
+
+    __call__ = attack
 
 
-def PGD(x, loss_fn, epsilon=0.1, steps=3, lo=-1.0, hi=1.0):
-    return _arc.simulate_attack(x, _arc.ATTACK_PGD, epsilon, loss_fn, steps=steps, lo=lo, hi=hi)
+class FGSM(Attack):
+    """One signed-gradient step of size epsilon."""
 
 
-Attack = FGSM
+class PGD(Attack):
+    """``steps`` projected signed-gradient steps inside the epsilon ball."""
+
+    kind = _arc.ATTACK_PGD
+
+    def __init__(self, epsilon=0.1, steps=3, lo=-1.0, hi=1.0):
+        super().__init__(epsilon, lo, hi, steps=steps)
+
+
+class ARCAttackSim:
+    """Runs a set of attacks against ``loss_fn`` and reports how much each raises the loss."""
+
+    def __init__(self, attacks=None):
+        self.attacks = list(attacks) if attacks is not None else [FGSM(0.05), PGD(0.05, steps=3)]
+
+    def run(self, x, loss_fn):
+        base = float(loss_fn(x))
+        out = {}
+        for a in self.attacks:
+            adv = a(x, loss_fn)
+            out[type(a).__name__] = {"loss": float(loss_fn(adv)), "clean_loss": base,
+                                     "linf": float((adv - x).abs().max())}
+        return out
 
 
 @dataclass
@@ -827,19 +851,48 @@ class AdversarialTrainer:
         return (1 - self.weight) * self.loss_fn(self.model(x), y) + self.weight * self.loss_fn(self.model(adv), y)
 
 
-ARCAdversarialTrainGraph = AdversarialTrainer
 
 
 # ----------------------------------------------------------------------------------------- data, tokenizers, trainers
 Dataset = CppDataset = PyTorchDataset = torch.utils.data.Dataset
 CppTensorDataset = _data.TensorDataset
 PyTorchDataLoader = _data.DataLoader
-TextDataset = _data.MemoryMappedTextDataset
-Sampler = _data.DistributedSampler
-BatchCollator = _data.default_collate
+
+
+class _LateBound(type):
+    """Metaclass of class names that are bound to their implementation at first use (the implementation's module is
+    not imported with this one). Calling the name constructs the implementation; ``isinstance`` / ``issubclass``
+    and attribute access go to it."""
+
+    def _real(cls):
+        r = cls.__dict__.get("_resolved")
+        if r is None:
+            import importlib
+            r = getattr(importlib.import_module(f"sneppx_alg_b200.{cls._mod}"), cls._attr)
+            type.__setattr__(cls, "_resolved", r)
+        return r
+
+    def __call__(cls, *a, **k):
+        return cls._real()(*a, **k)
+
+    def __instancecheck__(cls, obj):
+        return isinstance(obj, cls._real())
+
+    def __subclasscheck__(cls, sub):
+        return issubclass(sub, cls._real())
+
+    def __getattr__(cls, name):
+        if name.startswith("__"):
+            raise AttributeError(name)
+        return getattr(cls._real(), name)
 
 
 def _lazy(mod, attr):
+    """A late-bound class name when ``attr`` is spelled like a class, else a late-bound function."""
+    if attr[:1].isupper():
+        return _LateBound(attr, (), {"_mod": mod, "_attr": attr, "_resolved": None,
+                                     "__doc__": f"``sneppx_alg_b200.{mod}.{attr}``, bound at first use."})
+
     def get(*a, **k):
         import importlib
         return getattr(importlib.import_module(f"sneppx_alg_b200.{mod}"), attr)(*a, **k)
@@ -852,8 +905,6 @@ SimpleTokenizer = TokenizerSimpleTokenizer = _lazy("serving.server", "ByteTokeni
 TrainerV3 = PyTorchTrainer = _lazy("training.trainer", "Trainer")
 TrainConfigV3 = UltraTrainConfig = _lazy("training.config", "TrainConfig")
 EdgeRuntime = _lazy("utils.host", "EdgeModel")
-WeightWatermark = BackdoorWatermark = _lazy("serving.watermark", "Watermark")
-create_vizmon = start_dashboard = _lazy("utils.vizmon", "VizMon")
 SocketComm = _lazy("utils.net", "FramedSocket")
 GRPCService = _lazy("utils.net", "CoordinatorServer")
 NCCLComm = _lazy("parallel.distributed", "ProcessGroup")
@@ -921,13 +972,30 @@ class ContinuousBatchScheduler:
     def pending(self) -> int:
         return len(self.engine.waiting)
 DynamicBatchQueue = _lazy("utils.host", "ServingCore")
-get_profiler = _lazy("utils.observability", "Profiler")
 TrainProfiler = _lazy("utils.observability", "Profiler")
-LogTracker = Tracker = LocalBackend = _lazy("utils.observability", "ExperimentTracker")
 from .training.lora import QLoRALinear  # noqa: E402
-GradientCheckpointer = _lazy("training.extras", "enable_activation_checkpointing")
+class GradientCheckpointer:
+    """Wraps the repeated layers of ``model`` so that their activations are recomputed in backward."""
+
+    def __init__(self, model=None, every: int = 1):
+        self.every, self.wrapped = every, 0
+        if model is not None:
+            self.apply(model)
+
+    def apply(self, model):
+        from .training.extras import enable_activation_checkpointing
+        self.wrapped = enable_activation_checkpointing(model) or 0
+        return model
+
+    @staticmethod
+    def checkpoint(fn, *args):
+        from .training.extras import checkpoint
+        return checkpoint(fn, *args)
 checkpoint_sequential = _lazy("training.extras", "checkpoint")
-TopologyType = ("ring", "tree", "graph")
+class TopologyType(enum.Enum):
+    RING = "ring"
+    TREE = "tree"
+    GRAPH = "graph"
 
 
 @dataclass
@@ -992,7 +1060,6 @@ class ThreadPool:
 
 from .utils.workpool import Future as PoolFuture, TaskGroup, Workload, WorkStealingPool  # noqa: E402  (native pool)
 
-WorkerPool = WorkStealingPool
 
 
 class BenchmarkTimer:
@@ -1129,7 +1196,6 @@ class KernelConfig:
     stages: int = 4
 
 
-GemmConfig = KernelConfig
 
 
 class KernelLauncher:
@@ -1142,7 +1208,6 @@ class KernelLauncher:
         return self.table[name](*a, **k)
 
 
-get_launcher = KernelLauncher
 dispatch = lambda name, *a, **k: KernelLauncher().launch(name, *a, **k)  # noqa: E731
 ELEMENTWISE_IMPL = {"relu": relu_kernel, "gelu": gelu_kernel, "silu": silu_kernel}
 
@@ -1160,7 +1225,6 @@ class AuditSeverity(enum.IntEnum):
     INFO, WARNING, ERROR, CRITICAL = 0, 1, 2, 3
 
 
-Severity = AuditSeverity
 
 
 class AuditAction(str, enum.Enum):
@@ -1261,7 +1325,6 @@ class CVE:
     severity: AuditSeverity = AuditSeverity.WARNING
 
 
-SBOM = dict
 
 
 @dataclass
@@ -1278,7 +1341,6 @@ class TensorDescriptor:
         return n * torch.empty(0, dtype=self.dtype).element_size()
 
 
-TensorRecord = TensorDescriptor
 
 
 @dataclass
@@ -1398,11 +1460,6 @@ def export_audit_log(dest: str) -> int:
     return len(rows)
 
 
-class FileAuditBackend(_svc.AuditLogger):
-    pass
-
-
-AuditBackend = FileAuditBackend
 
 
 class ConnectionTracker:
@@ -1421,7 +1478,6 @@ class ConnectionTracker:
         self.open[client] = max(0, self.open.get(client, 0) - 1)
 
 
-SYNFloodDetector = ConnectionTracker
 _connections = ConnectionTracker()
 release_connection = _connections.release
 
@@ -1529,7 +1585,17 @@ def prune_and_distill(student, teacher, batches, sparsity: float = 0.5, steps: i
     return masks, losses
 
 
-DistillationPruner = prune_and_distill
+class DistillationPruner:
+    """Global magnitude pruning of the student to ``sparsity`` followed by ``steps`` distillation steps against the
+    teacher with the mask re-applied; ``run(batches)`` returns (masks, losses)."""
+
+    def __init__(self, student, teacher, sparsity: float = 0.5, steps: int = 10):
+        self.student, self.teacher, self.sparsity, self.steps = student, teacher, sparsity, steps
+        self.masks, self.losses = None, []
+
+    def run(self, batches):
+        self.masks, self.losses = prune_and_distill(self.student, self.teacher, batches, self.sparsity, self.steps)
+        return self.masks, self.losses
 
 
 class Random:
@@ -1634,7 +1700,6 @@ AlgoHSSModel, AlgoSERModel = _alg("HSSModel"), _alg("SERModel")
 DeepSeekV2Model = _lazy("models.deepseek", "DeepSeekV2ForCausalLM")
 BlockTable = _lazy("serving.kv_cache", "PagedKVCache")
 DataBuffer = _lazy("utils.mm", "Arena")
-FusedNode = _graph.ExprNode
 
 
 class BigNum(int):
@@ -1661,14 +1726,7 @@ class ArchOps:
         return Mamba2Block(x.shape[-1], d_state=d_state, d_conv=d_conv, headdim=min(64, x.shape[-1] * 2)).to(x.dtype)(x)
 
 
-@dataclass
-class MXFormatSpec:
-    name: str
-    element_bits: int
-    block: int = 32
-
-
-MXFormat = MXFormatSpec
+from .quant.algorithms import MX_FORMATS, MXFormat, MXFormatSpec, mx_quantize_spec  # noqa: E402,F401
 
 
 class Preprocessor:
@@ -1854,20 +1912,39 @@ class RemoteAPIAuditBackend(_svc.AuditLogger):
         return h
 
 
-EdgeDevice = HardwareProbe
 
 
-def _obf(attr):
-    def get(*a, **k):
+ObfuscationPipeline = _lazy("security.obfuscation", "ObfuscationPipeline")
+ObfuscationConfig = _lazy("security.obfuscation", "ObfuscationConfig")
+
+
+class _ProgramPass:
+    """One obfuscation pass over an NPE program; ``apply(program, **options)`` returns the transformed program."""
+
+    fn_name = ""
+
+    def __init__(self, **options):
+        self.options = options
+
+    def apply(self, program, **options):
         from .security import obfuscation
-        return getattr(obfuscation, attr)(*a, **k)
-    get.__name__ = attr
-    return get
+        return getattr(obfuscation, self.fn_name)(program, **dict(self.options, **options))
+
+    __call__ = apply
 
 
-ObfuscationPipeline, ObfuscationConfig = _obf("ObfuscationPipeline"), _obf("ObfuscationConfig")
-InstructionSubstitution, OpaquePredicate = _obf("substitute_instructions"), _obf("insert_opaque_predicates")
-StringEncryption = _obf("seal_program")
+class InstructionSubstitution(_ProgramPass):
+    fn_name = "substitute_instructions"
+
+
+class OpaquePredicate(_ProgramPass):
+    fn_name = "insert_opaque_predicates"
+
+
+class StringEncryption(_ProgramPass):
+    """Seals a program (encrypts and authenticates its serialised form)."""
+
+    fn_name = "seal_program"
 
 
 # ---------------------------------------------------------------------------------------------- late additions

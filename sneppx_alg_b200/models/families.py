@@ -112,7 +112,8 @@ class GPTConfig:
 
 
 class GPTModel(Module):
-    """GPT-2 shape: learned positions, pre-LN blocks, tied LM head."""
+    """GPT-2 shape: learned positions, pre-LN blocks, tied LM head. ``hidden_states`` is the stack without the head;
+    ``forward`` applies the tied head (logits, or the loss when labels are given)."""
 
     def __init__(self, cfg: GPTConfig = None, dtype=None, device=None, **kw):
         super().__init__()
@@ -125,16 +126,37 @@ class GPTModel(Module):
                                              device=device) for _ in range(cfg.n_layer)])
         self.ln_f = LayerNorm(d, eps=cfg.layer_norm_eps, dtype=dtype, device=device)
 
-    def forward(self, input_ids, labels=None, **_):
+    def hidden_states(self, input_ids):
         S = input_ids.shape[1]
         x = self.wte(input_ids) + self.wpe(torch.arange(S, device=input_ids.device))[None]
         for layer in self.layers:
             x = layer(x)
-        x = self.ln_f(x)
+        return self.ln_f(x)
+
+    def forward(self, input_ids, labels=None, **_):
+        x = self.hidden_states(input_ids)
         if labels is not None:
             loss = ops.linear_cross_entropy(x[:, :-1].reshape(-1, x.shape[-1]), self.wte.weight, labels[:, 1:].reshape(-1))
             return {"loss": loss}
         return {"logits": ops.linear(x, self.wte.weight)}
+
+
+class GPTLMHeadModel(GPTModel):
+    """GPT-2 with an untied output projection of its own (``lm_head``), initialised from the token embedding."""
+
+    def __init__(self, cfg: GPTConfig = None, dtype=None, device=None, **kw):
+        super().__init__(cfg, dtype, device, **kw)
+        from ..nn.modules import Linear
+        self.lm_head = Linear(self.config.n_embd, self.config.vocab_size, bias=False, dtype=dtype, device=device)
+        with torch.no_grad():
+            self.lm_head.weight.copy_(self.wte.weight)
+
+    def forward(self, input_ids, labels=None, **_):
+        x = self.hidden_states(input_ids)
+        if labels is not None:
+            loss = ops.linear_cross_entropy(x[:, :-1].reshape(-1, x.shape[-1]), self.lm_head.weight, labels[:, 1:].reshape(-1))
+            return {"loss": loss}
+        return {"logits": ops.linear(x, self.lm_head.weight)}
 
 
 GPT2LMHeadModel = GPTModel
@@ -228,18 +250,29 @@ class T5ForConditionalGeneration(Module):
             x = layer(x, bias)
         return self.enc_norm(x)
 
-    def forward(self, input_ids, decoder_input_ids, labels=None):
-        mem = self.encode(input_ids)
+    def decode(self, decoder_input_ids, memory):
         y = self.shared(decoder_input_ids)
         bias = self.decoder[0].self_attn.bias(y.shape[1], y.device)
         for layer in self.decoder:
-            y = layer(y, bias, mem)
-        y = self.dec_norm(y) * (self.config.d_model ** -0.5)
+            y = layer(y, bias, memory)
+        return self.dec_norm(y)
+
+    def forward(self, input_ids, decoder_input_ids, labels=None):
+        y = self.decode(decoder_input_ids, self.encode(input_ids)) * (self.config.d_model ** -0.5)
         logits = ops.linear(y, self.shared.weight)
         out = {"logits": logits}
         if labels is not None:
             out["loss"] = ops.cross_entropy(logits.reshape(-1, logits.shape[-1]), labels.reshape(-1))
         return out
+
+
+class T5Model(T5ForConditionalGeneration):
+    """Encoder-decoder stack without the output projection: ``forward`` returns the decoder's and the encoder's final
+    hidden states (reference: interface_bindings/model_implementations.py:1284)."""
+
+    def forward(self, input_ids, decoder_input_ids):
+        mem = self.encode(input_ids)
+        return {"last_hidden_state": self.decode(decoder_input_ids, mem), "encoder_last_hidden_state": mem}
 
 
 # ----------------------------------------------------------------------------- ViT
@@ -293,3 +326,103 @@ class VisionTransformer(Module):
 
 
 ViTForImageClassification = VisionTransformer
+
+
+# ----------------------------------------------------------------------------- masked autoencoder
+class MAE(Module):
+    """Masked autoencoder for images (He et al. 2021; reference: interface_bindings/vision_transformers.py:651).
+
+    A random ``mask_ratio`` of the patches is dropped; the encoder sees only the kept ones (plus a class token), a
+    lighter decoder gets the encoded tokens back in place with a learned mask token everywhere else and predicts the
+    pixels of every patch; the loss is the mean squared error on the dropped patches only.
+    ``forward(imgs)`` returns ``(loss, pred, mask)`` with pred [B, N, p*p*C] and mask [B, N] (1 = dropped)."""
+
+    def __init__(self, img_size=224, patch_size=16, in_channels=3, embed_dim=768, encoder_depth=12, decoder_depth=8,
+                 num_heads=12, mlp_ratio=4.0, mask_ratio=0.75, decoder_embed_dim=512, decoder_num_heads=None,
+                 norm_pix_loss=False, dtype=None, device=None):
+        super().__init__()
+        assert img_size % patch_size == 0
+        self.patch_size, self.in_channels, self.mask_ratio, self.norm_pix_loss = patch_size, in_channels, mask_ratio, norm_pix_loss
+        self.n_patches = n = (img_size // patch_size) ** 2
+        pd = in_channels * patch_size * patch_size
+        kw = dict(dtype=dtype, device=device)
+        self.patch = Linear(pd, embed_dim, init_std=0.02, **kw)
+        self.cls = tnn.Parameter(torch.zeros(1, 1, embed_dim, **kw))
+        self.pos = tnn.Parameter(torch.randn(1, n + 1, embed_dim, **kw) * 0.02)
+        self.encoder = tnn.ModuleList([_Block(embed_dim, num_heads, int(embed_dim * mlp_ratio), False, True, **kw)
+                                       for _ in range(encoder_depth)])
+        self.enc_norm = LayerNorm(embed_dim, **kw)
+        self.to_decoder = Linear(embed_dim, decoder_embed_dim, init_std=0.02, **kw)
+        self.mask_token = tnn.Parameter(torch.randn(1, 1, decoder_embed_dim, **kw) * 0.02)
+        self.dec_pos = tnn.Parameter(torch.randn(1, n + 1, decoder_embed_dim, **kw) * 0.02)
+        dh = decoder_num_heads or max(1, min(num_heads, decoder_embed_dim // 32))
+        self.decoder = tnn.ModuleList([_Block(decoder_embed_dim, dh, int(decoder_embed_dim * mlp_ratio), False, True, **kw)
+                                       for _ in range(decoder_depth)])
+        self.dec_norm = LayerNorm(decoder_embed_dim, **kw)
+        self.to_pixels = Linear(decoder_embed_dim, pd, init_std=0.02, **kw)
+
+    def patchify(self, img):
+        p = self.patch_size
+        B, C, H, W = img.shape
+        x = img.reshape(B, C, H // p, p, W // p, p).permute(0, 2, 4, 1, 3, 5)
+        return x.reshape(B, (H // p) * (W // p), C * p * p)
+
+    def unpatchify(self, patches):
+        p, C = self.patch_size, self.in_channels
+        B, N, _ = patches.shape
+        g = int(N ** 0.5)
+        x = patches.reshape(B, g, g, C, p, p).permute(0, 3, 1, 4, 2, 5)
+        return x.reshape(B, C, g * p, g * p)
+
+    def random_masking(self, x, mask_ratio=None, noise=None):
+        """Keeps the ``1 - mask_ratio`` patches with the smallest noise. Returns (kept tokens, mask [B, N] with 1 for
+        dropped, restore indices that undo the shuffle)."""
+        B, N, D = x.shape
+        ratio = self.mask_ratio if mask_ratio is None else mask_ratio
+        keep = max(1, int(round(N * (1.0 - ratio))))
+        noise = torch.rand(B, N, device=x.device) if noise is None else noise
+        shuffle = noise.argsort(dim=1)
+        restore = shuffle.argsort(dim=1)
+        kept = x.gather(1, shuffle[:, :keep, None].expand(-1, -1, D))
+        mask = torch.ones(B, N, device=x.device)
+        mask[:, :keep] = 0
+        return kept, mask.gather(1, restore), restore
+
+    def encode(self, imgs, mask_ratio=None, noise=None):
+        x = self.patch(self.patchify(imgs).to(self.patch.weight.dtype)) + self.pos[:, 1:]
+        x, mask, restore = self.random_masking(x, mask_ratio, noise)
+        x = torch.cat([(self.cls + self.pos[:, :1]).expand(x.shape[0], -1, -1), x], dim=1)
+        for layer in self.encoder:
+            x = layer(x)
+        return self.enc_norm(x), mask, restore
+
+    def decode(self, latent, restore):
+        x = self.to_decoder(latent)
+        B, _, D = x.shape
+        N = restore.shape[1]
+        filled = torch.cat([x[:, 1:], self.mask_token.expand(B, N + 1 - x.shape[1], -1).to(x.dtype)], dim=1)
+        filled = filled.gather(1, restore[:, :, None].expand(-1, -1, D))
+        x = torch.cat([x[:, :1], filled], dim=1) + self.dec_pos
+        for layer in self.decoder:
+            x = layer(x)
+        return self.to_pixels(self.dec_norm(x))[:, 1:]
+
+    def reconstruction_loss(self, imgs, pred, mask):
+        target = self.patchify(imgs).float()
+        if self.norm_pix_loss:
+            target = (target - target.mean(-1, keepdim=True)) / (target.var(-1, keepdim=True) + 1e-6).sqrt()
+        per_patch = (pred.float() - target).pow(2).mean(-1)
+        return (per_patch * mask).sum() / mask.sum().clamp_min(1.0)
+
+    def forward(self, imgs, mask_ratio=None, noise=None):
+        latent, mask, restore = self.encode(imgs, mask_ratio, noise)
+        pred = self.decode(latent, restore)
+        return self.reconstruction_loss(imgs, pred, mask), pred, mask
+
+
+def mae_base(**kw) -> MAE:
+    return MAE(**{**dict(embed_dim=768, encoder_depth=12, num_heads=12, decoder_embed_dim=512, decoder_depth=8), **kw})
+
+
+def mae_large(**kw) -> MAE:
+    return MAE(**{**dict(embed_dim=1024, encoder_depth=24, num_heads=16, decoder_embed_dim=512, decoder_depth=8), **kw})

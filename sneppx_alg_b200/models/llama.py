@@ -94,14 +94,14 @@ class KVCache:
 
 
 class LlamaForCausalLM(Module):
-    def __init__(self, cfg: ModelConfig, dtype=None, device=None):
+    def __init__(self, cfg: ModelConfig, dtype=None, device=None, with_head: bool = True):
         super().__init__()
         self.config = cfg
         d = cfg.hidden_size
         self.embedding = Embedding(cfg.vocab_size, d, dtype=dtype, device=device, init_std=cfg.initializer_range)
         self.layers = tnn.ModuleList([LlamaBlock(cfg, dtype, device) for _ in range(cfg.num_hidden_layers)])
         self.norm = RMSNorm(d, cfg.rms_norm_eps, dtype=dtype, device=device)
-        if cfg.tie_word_embeddings:
+        if cfg.tie_word_embeddings or not with_head:
             self.lm_head = None
         else:
             self.lm_head = Linear(d, cfg.vocab_size, bias=False, dtype=dtype, device=device,
@@ -243,6 +243,58 @@ class MistralForCausalLM(LlamaForCausalLM):
 
 
 class Qwen2ForCausalLM(LlamaForCausalLM):
+    pass
+
+
+class LlamaModel(LlamaForCausalLM):
+    """The decoder stack alone (embedding, blocks, final norm): no language-model head is allocated and ``forward``
+    returns the final hidden states (reference: interface_bindings/llama_models.py:230)."""
+
+    def __init__(self, cfg: ModelConfig, dtype=None, device=None):
+        super().__init__(cfg, dtype, device, with_head=False)
+
+    def head_weight(self):
+        raise AttributeError(f"{type(self).__name__} has no language-model head")
+
+    def forward(self, input_ids, attention_mask=None, position_ids=None, past_key_values=None, use_cache=False):
+        if use_cache and past_key_values is None:
+            past_key_values = self.init_kv_cache(input_ids.shape[0], self.config.max_position_embeddings)
+        h = self.hidden_states(input_ids, position_ids, past_key_values)
+        return {"last_hidden_state": h, "past_key_values": past_key_values if use_cache else None}
+
+    def generate(self, *a, **k):
+        raise AttributeError(f"{type(self).__name__} has no language-model head to generate with")
+
+
+class MistralModel(LlamaModel):
+    pass
+
+
+class Qwen2Model(LlamaModel):
+    pass
+
+
+class MistralMLP(LlamaMLP):
+    pass
+
+
+class Qwen2MLP(LlamaMLP):
+    pass
+
+
+class MistralAttention(LlamaAttention):
+    """Llama attention under a Mistral config (``sliding_window`` set in the config selects the windowed kernel)."""
+
+
+class Qwen2Attention(LlamaAttention):
+    """Llama attention under a Qwen2 config (``attention_bias`` set in the config adds the q/k/v biases)."""
+
+
+class MistralDecoderLayer(LlamaBlock):
+    pass
+
+
+class Qwen2DecoderLayer(LlamaBlock):
     pass
 
 

@@ -5,6 +5,8 @@ tensors live there; the serving-path kernels (fp8 1x128 / 128x128, int4 group-12
 from __future__ import annotations
 
 import enum
+import math
+from dataclasses import dataclass
 
 import torch
 
@@ -143,6 +145,68 @@ def _round_to_grid(x, grid):
     g = grid.to(x.device)
     idx = torch.bucketize(x.abs(), (g[1:] + g[:-1]) / 2)
     return g[idx] * x.sign()
+
+
+class MXFormat:
+    """Names of the micro-scaling element formats (reference: interface_bindings/mx_formats.py:37)."""
+
+    MXFP8_E4M3 = "mxfp8_e4m3"
+    MXFP8_E5M2 = "mxfp8_e5m2"
+    MXFP6_E3M2 = "mxfp6_e3m2"
+    MXFP6_E2M3 = "mxfp6_e2m3"
+    MXFP4_E2M1 = "mxfp4_e2m1"
+    NVFP4_E2M1 = "nvfp4_e2m1"
+
+
+@dataclass(frozen=True)
+class MXFormatSpec:
+    """One element format: total bits, exponent / mantissa bits, exponent bias, elements per shared scale (0 = the
+    NVFP4 two-level scaling of ``nvfp4_quantize``) and the largest finite magnitude."""
+
+    name: str
+    bits: int
+    exp_bits: int
+    mant_bits: int
+    bias: int
+    block_size: int
+    max_value: float
+
+    @property
+    def emax(self) -> int:
+        """Exponent of the largest binade, the amount the shared scale is shifted down by."""
+        return int(math.floor(math.log2(self.max_value)))
+
+    def grid(self) -> torch.Tensor:
+        """Every non-negative finite value of the format, ascending (sub-normals included)."""
+        m = 2 ** self.mant_bits
+        vals = {k / m * 2.0 ** (1 - self.bias) for k in range(m)}
+        vals |= {(1 + k / m) * 2.0 ** (e - self.bias) for e in range(1, 2 ** self.exp_bits) for k in range(m)}
+        return torch.tensor(sorted(v for v in vals if v <= self.max_value))
+
+
+MX_FORMATS = {
+    MXFormat.MXFP8_E4M3: MXFormatSpec("mxfp8_e4m3", 8, 4, 3, 7, 32, 448.0),
+    MXFormat.MXFP8_E5M2: MXFormatSpec("mxfp8_e5m2", 8, 5, 2, 15, 32, 57344.0),
+    MXFormat.MXFP6_E3M2: MXFormatSpec("mxfp6_e3m2", 6, 3, 2, 3, 32, 28.0),
+    MXFormat.MXFP6_E2M3: MXFormatSpec("mxfp6_e2m3", 6, 2, 3, 1, 32, 7.5),
+    MXFormat.MXFP4_E2M1: MXFormatSpec("mxfp4_e2m1", 4, 2, 1, 1, 32, 6.0),
+    MXFormat.NVFP4_E2M1: MXFormatSpec("nvfp4_e2m1", 4, 2, 1, 1, 0, 6.0),
+}
+
+
+def mx_quantize_spec(x, fmt: str = MXFormat.MXFP8_E4M3, block: int = None):
+    """``mx_quantize`` for any entry of ``MX_FORMATS`` by name (NVFP4 goes to ``nvfp4_quantize``). The element
+    rounding is to the nearest value of the format's grid, ties away from the smaller neighbour's midpoint."""
+    spec = MX_FORMATS[fmt]
+    if spec.block_size == 0:
+        return nvfp4_quantize(x, block or 16)
+    block = block or spec.block_size
+    g = x.float().reshape(-1, block)
+    amax = g.abs().amax(-1, keepdim=True).clamp_min(2.0 ** -126)
+    e = torch.floor(torch.log2(amax)) - spec.emax
+    s = torch.exp2(e)
+    y = _round_to_grid((g / s).clamp(-spec.max_value, spec.max_value), spec.grid())
+    return (y * s).reshape(x.shape).to(x.dtype), e.squeeze(-1).to(torch.int8).reshape(*x.shape[:-1], -1)
 
 
 def mx_quantize(x, fmt="mxfp8", block=32):

@@ -58,6 +58,7 @@ class IdentityManager:
     def __init__(self, window_s: float = 1.0, limit: int = 1000, clock: Callable[[], float] = time.time):
         self.clock = clock
         self.pinned: Dict[bytes, dict] = {}
+        self.devices: Dict[str, dict] = {}
         self.revoked: set = set()
         self.ocsp_cache: Dict[bytes, Tuple[bool, float]] = {}
         self.ocsp_hits = self.ocsp_misses = 0
@@ -96,6 +97,33 @@ class IdentityManager:
 
     def clear(self) -> None:
         self.pinned.clear()
+
+    # ---- device registry: identities by Ed25519 key (reference: interface_bindings/s4_network.py:53)
+    def register(self, device_id: str, public_key: bytes, metadata: Optional[dict] = None) -> None:
+        if len(public_key) != 32:
+            raise ValueError("an Ed25519 public key has 32 bytes")
+        fp = crypto.sha256(bytes(public_key))
+        self.devices[device_id] = {"public_key": bytes(public_key), "metadata": dict(metadata or {}),
+                                   "fingerprint": fp.hex(), "registered": self.clock()}
+        self.pin(fp, subject=device_id)
+
+    def lookup(self, device_id: str) -> Optional[dict]:
+        rec = self.devices.get(device_id)
+        return dict(rec) if rec and not self.is_revoked(bytes.fromhex(rec["fingerprint"])) else None
+
+    def revoke(self, device_id: str) -> bool:
+        rec = self.devices.get(device_id)
+        if rec is None or self.is_revoked(bytes.fromhex(rec["fingerprint"])):
+            return False
+        self.add_revocation(bytes.fromhex(rec["fingerprint"]))
+        return True
+
+    def verify_identity(self, device_id: str, challenge: bytes, signature: bytes) -> bool:
+        """True when ``signature`` is the registered, unrevoked device's Ed25519 signature over ``challenge``."""
+        rec = self.lookup(device_id)
+        if rec is None or len(signature) != 64:
+            return False
+        return crypto.ed25519_verify(rec["public_key"], challenge, signature)
 
     # ---- revocation / OCSP-style cache
     def add_revocation(self, fingerprint: bytes) -> None:

@@ -164,4 +164,8 @@ def get_scheduler(name, target, **kw):
     return LRScheduler(target, name, **kw)
 
 
-CosineAnnealingLR = lambda opt, T_max, eta_min=0.0: LRScheduler(opt, "cosine", total_steps=T_max, min_lr=eta_min)  # noqa: E731
+class CosineAnnealingLR(LRScheduler):
+    """Cosine decay from the base rate to ``eta_min`` over ``T_max`` steps (torch's argument names)."""
+
+    def __init__(self, opt, T_max, eta_min=0.0):
+        super().__init__(opt, "cosine", total_steps=T_max, min_lr=eta_min)

@@ -144,9 +144,15 @@ def test_audit_backends_and_small_services(tmp_path):
     assert db.verify()
     db.db.execute("update audit set rec = replace(rec, 'ann', 'eve') where id = 2")
     assert not db.verify()
-    fa = sx.FileAuditBackend(str(tmp_path / "audit.log"))
-    fa.log("bob", "data_access", resource="weights")
-    assert fa.verify()
+    assert issubclass(sx.FileAuditBackend, sx.AuditBackend)
+    fa = sx.FileAuditBackend(str(tmp_path / "audit"), max_file_size=400, max_files=3)
+    for i in range(20):
+        fa.write(sx.AuditEvent(f"u{i % 2}", "login", details={"n": i}))
+    kept = fa.query()
+    assert 0 < len(kept) < 20 and kept[-1]["details"] == {"n": 19} and fa.verify_chain()      # rotation dropped the oldest files
+    assert {r["actor"] for r in fa.query(actor="u1")} == {"u1"} and fa.query(action="logout") == []
+    assert len([f for f in os.listdir(tmp_path / "audit") if f.endswith(".gz")]) == 3
+    fa.close()
     ct = sx.ConnectionTracker(max_per_client=2)
     assert ct.acquire("a") and ct.acquire("a") and not ct.acquire("a")
     ct.release("a")
@@ -239,3 +245,286 @@ def test_compat_names_are_real_objects_of_the_right_kind():
     xin = torch.randn(2, 64)
     assert (q(xin) - lin(xin)).abs().max() < 0.5          # B starts at zero: only the 4-bit rounding of the base differs
     assert [n for n, p_ in q.named_parameters() if p_.requires_grad] == ["lora_A", "lora_B"]
+
+
+def test_names_resolve_to_objects_of_the_reference_kind():
+    """A reference class name resolves to a class, a reference function name to a function (kinds listed from the
+    reference's sources), and these pairs of reference classes are not one object here."""
+    import inspect
+    for cls_name in ("Tracker", "LogTracker", "LocalBackend", "BatchCollator", "CPUFeatures", "ComputeCapability", "NPECompiler",
+                     "NPEVerify", "WeightWatermark", "BackdoorWatermark", "SimpleTokenizer", "GradientCheckpointer", "TopologyType",
+                     "FGSM", "PGD", "DistillationPruner", "TriStageLR", "CosineAnnealingLR", "StringEncryption", "UltraTrainConfig"):
+        assert inspect.isclass(getattr(sx, cls_name)), cls_name
+    for fn_name in ("Input", "create_vizmon", "start_dashboard", "get_profiler", "get_launcher", "int_", "uniform", "log_uniform"):
+        assert inspect.isfunction(getattr(sx, fn_name)), fn_name
+    for a, b in (("SlidingWindowRateLimiter", "TokenBucket"), ("SYNFloodDetector", "ConnectionTracker"), ("DRBG", "EntropyPool"),
+                 ("LlamaModel", "LlamaForCausalLM"), ("GPTModel", "GPTLMHeadModel"), ("T5Model", "T5ForConditionalGeneration"),
+                 ("MAE", "MAELoss"), ("Streamer", "TokenStreamer"), ("OnnxTensor", "OnnxInitializer"), ("Run", "ExperimentRun"),
+                 ("SignedUpdate", "SignedUpdateManager"), ("ApiKeyManager", "ApiKeyStore"), ("Severity", "AuditSeverity"),
+                 ("MXFormat", "MXFormatSpec"), ("CVEScanner", "ContainerSecurity"), ("SBOM", "IncrementalAttentionState"),
+                 ("Authenticator", "UserStore"), ("IdentityManager", "UserStore"), ("EdgeDevice", "HardwareProbe"),
+                 ("TensorRecord", "TensorDescriptor"), ("GraphNode", "FusedNode"), ("WorkerPool", "WorkStealingPool")):
+        assert getattr(sx, a) is not getattr(sx, b), (a, b)
+    assert issubclass(sx.TokenStreamer, sx.Streamer) and issubclass(sx.LogTracker, sx.Tracker)
+    assert isinstance(sx.SimpleTokenizer(300), sx.SimpleTokenizer)          # late-bound names answer isinstance
+
+
+def test_traffic_limits_identities_and_keys():
+    now = [0.0]
+    rl = sx.SlidingWindowRateLimiter(3, 10.0, clock=lambda: now[0])
+    assert [rl.check("a") for _ in range(4)] == [True, True, True, False] and rl.check("b") and rl.get_count("a") == 3
+    now[0] = 10.5
+    assert rl.get_count("a") == 0 and rl.check("a")
+    syn = sx.SYNFloodDetector(threshold=5, window=1.0, clock=lambda: now[0])
+    assert [syn.record_syn() for _ in range(6)] == [False] * 5 + [True] and syn.get_rate() == 6.0
+    now[0] += 2.0
+    assert syn.get_rate() == 0.0
+    from sneppx_alg_b200.security import crypto
+    im = sx.IdentityManager()
+    seed = bytes(range(32))
+    im.register("edge-1", crypto.ed25519_public_key(seed), {"site": "lab"})
+    sig = crypto.ed25519_sign(seed, b"challenge")
+    assert im.verify_identity("edge-1", b"challenge", sig) and not im.verify_identity("edge-1", b"other", sig)
+    assert im.lookup("edge-1")["metadata"] == {"site": "lab"} and im.revoke("edge-1") and not im.revoke("edge-1")
+    assert im.lookup("edge-1") is None and not im.verify_identity("edge-1", b"challenge", sig)
+    mgr = sx.ApiKeyManager(cache_ttl=0.0, clock=lambda: now[0])
+    k = mgr.create_key("svc", "pro", expires_in_days=1.0, user_id="u7")
+    assert mgr.validate_key(k["key"])["rate_limit_rpm"] == 600 and mgr.validate_key("nope") is None
+    auth = sx.Authenticator(sx.AuthConfig("api_key"), mgr)
+    assert auth.authenticate("Bearer " + k["key"])["owner"] == "u7" and auth.authenticate("Basic x") is None
+    now[0] += 2 * 86400.0
+    assert mgr.validate_key(k["key"]) is None                                  # expired
+    k2 = mgr.create_key("svc2")
+    assert mgr.revoke_key(k2["id"]) and mgr.validate_key(k2["key"]) is None and len(mgr.list_keys(True)) == 2
+    bearer = sx.Authenticator(sx.AuthConfig("bearer", ["t1", "t2"], "root"))
+    assert bearer.authenticate("bearer t2")["admin"] is False and bearer.authenticate("Bearer root")["admin"] and \
+        bearer.authenticate("Bearer t3") is None
+
+
+def test_supply_chain_records_and_signed_updates(tmp_path):
+    from sneppx_alg_b200.security.pentest import Advisory
+    sbom = sx.SBOM.from_packages({"numpy": "1.20.0", "torch": "2.1.0"}, name="img")
+    doc = sbom.to_cyclonedx_json()
+    assert doc["bomFormat"] == "CycloneDX" and [c["purl"] for c in doc["components"]] == ["pkg:pypi/numpy@1.20.0", "pkg:pypi/torch@2.1.0"]
+    scanner = sx.CVEScanner(cache_dir=str(tmp_path), advisories=[Advisory("CVE-X-1", "numpy", "<1.22", 7.5)])
+    hits = scanner.scan_sbom(sbom)
+    assert len(hits) == 1 and os.path.exists(tmp_path / "cve_cache.json") and scanner.scan_package("numpy", "1.26.0") == []
+    cs = sx.ContainerSecurity()
+    cs.register_sbom("img", cs.generate_sbom([{"name": "numpy", "version": "1.20.0"}]))
+    cs.add_vulnerability("img", {"package": "numpy", "severity": 7.5})
+    cs.add_vulnerability("img", {"package": "absent", "severity": 9.9})
+    assert len(cs.scan_cves("img")) == 1 and cs.is_compliant("img", {"max_severity": 8.0}) and \
+        not cs.is_compliant("img", {"max_severity": 5.0}) and not cs.is_compliant("img", {"forbidden_packages": ["numpy"]})
+    assert sx.Severity.from_cvss(9.1) is sx.Severity.CRITICAL and sx.Severity.from_cvss(4.0) is sx.Severity.MEDIUM
+    su = sx.SignedUpdate()
+    sig, pk = su.sign_update(b"pkg-bytes", b"\x07" * 32)
+    su.register_update("u1", {"data": b"pkg-bytes", "signature": sig, "public_key": pk, "sha256": su.hash_package(b"pkg-bytes")})
+    su.register_update("u2", {"data": b"tampered", "signature": sig, "public_key": pk})
+    assert su.apply("u1") and su.status("u1") == "applied" and not su.apply("u2") and su.status("u2") == "failed"
+    assert su.rollback("u1") and su.status("u1") == "rolled_back" and su.status("zz") is None
+
+
+def test_watermarks_trackers_and_collation(tmp_path, capsys):
+    torch.manual_seed(0)
+    net = torch.nn.Sequential(torch.nn.Linear(16, 32), torch.nn.ReLU(), torch.nn.Linear(32, 4))
+    wm = sx.WeightWatermark("owner-key", strength=0.05, ratio=0.1)
+    assert not wm.detect(net)[0]
+    info = wm.embed(net)
+    assert info["0.weight"] == {"selected": 51, "total": 512}
+    marked, score = wm.detect(net)
+    assert marked and score > 0.99 and not sx.WeightWatermark("other-key", 0.05, 0.1).detect(net)[0]
+    bd = sx.BackdoorWatermark("owner-key", (16,), target_label=2, num_keys=32, threshold=0.9)
+    assert not bd.verify(net)[0]
+    hist = bd.train(net, torch.optim.Adam(net.parameters(), lr=0.05), epochs=60)
+    assert hist[-1] < hist[0] and bd.verify(net) == (True, 1.0)
+    t = sx.LogTracker()
+    t.start_run("exp", "r1", params={"lr": 0.1})
+    t.log_metrics({"loss": 1.5}, step=3)
+    t.log_metric("loss", 1.0, step=4)
+    t.set_tag("k", "v")
+    t.end_run()
+    out = capsys.readouterr().out
+    assert "[step 3] loss=1.5" in out and t.run.status == "finished" and t.run.metrics["loss"] == [(3, 1.5), (4, 1.0)]
+    be = sx.LocalBackend(str(tmp_path / "runs"))
+    be.save(t.run)
+    back = be.load(t.run.run_id)
+    assert back.metrics == t.run.metrics and back.tags == {"k": "v"} and [r.run_id for r in be.list_runs("exp")] == [t.run.run_id]
+    assert be.list_runs("other") == []
+    be.delete_run(t.run.run_id)
+    assert be.load(t.run.run_id) is None
+    silent = sx.Tracker()
+    silent.log_metric("x", 1.0)                                                # no run: nothing happens, nothing raises
+    assert silent.run is None
+    with sx.Run("exp", params={"a": 1}) as r:
+        r.log_metric("loss", 2.0, 0).log_metric("loss", 1.0, 1).add_tag("t").add_tag("t")
+    assert r.status == "finished" and r.metric_history("loss") == [2.0, 1.0] and r.tags == ["t"]
+    assert sx.Run.load(r.save(str(tmp_path / "r"))).metric_history("loss") == [2.0, 1.0]
+    try:
+        with sx.Run("exp") as bad:
+            raise ValueError("boom")
+    except ValueError:
+        pass
+    assert bad.status == "failed" and "boom" in bad.error
+    col = sx.BatchCollator(padding_value=-1)
+    x, y = col([(torch.tensor([1, 2, 3]), torch.tensor([1])), (torch.tensor([4]), torch.tensor([0]))])
+    assert x.tolist() == [[1, 2, 3], [4, -1, -1]] and y.tolist() == [[1], [0]]
+    assert sx.BatchCollator(0, max_length=2)([[5, 6, 7], [8]]).tolist() == [[5, 6], [8, 0]]
+    ds = sx.TextDataset(["abc", "de"], sx.SimpleTokenizer(300), max_length=4)
+    inp, tgt = ds[0]
+    assert len(ds) == 2 and inp.shape == (4,) and torch.equal(inp[1:], tgt[:-1])
+    ts = sx.TextStreamer(sx.SimpleTokenizer(300), print_fn=(pieces := []).append)
+    for tok in sx.SimpleTokenizer(300).encode("héllo"):
+        ts.put(tok)
+    assert "".join(pieces) == "héllo" and all("�" not in p for p in pieces)
+
+
+def test_graph_nodes_tensor_expressions_and_npe_front_end():
+    x = sx.GraphNode.input_("x")
+    w = sx.GraphNode.parameter(torch.randn(4, 3), "w")
+    y = sx.GraphNode.clip(((x @ w) + 1.0).relu().tanh() * 2.0, -1.5, 1.5)
+    xin = torch.randn(5, 4)
+    want = (torch.tanh(torch.relu(xin @ w.value + 1.0)) * 2.0).clamp(-1.5, 1.5)
+    assert torch.allclose(y.evaluate({"x": xin}), want)
+    from sneppx_alg_b200.compat_classes import elementwise_clusters
+    clusters = elementwise_clusters(y)
+    assert len(clusters) == 1 and [m.op for m in clusters[0].members] == ["add", "relu", "tanh", "mul", "clip"]
+    mm = clusters[0].external_inputs[0]
+    ext = {id(i): i.value for i in clusters[0].external_inputs if i.op == "constant"}
+    ext[id(mm)] = xin @ w.value
+    assert torch.allclose(clusters[0].run(ext), want)
+    with pytest.raises(ValueError):
+        sx.FusedNode([x @ w])
+    a = sx.TensorExpr.parameter(torch.ones(2, 3), "a")
+    shared = sx.TensorExpr.relu(sx.TensorExpr.add(a, sx.TensorExpr.constant(torch.full((2, 3), -2.0))))
+    e = sx.TensorExpr.matmul(sx.TensorExpr.mul(shared, shared), sx.TensorExpr.constant(torch.ones(3, 1)))
+    plan = sx.TensorExprCompiler().compile(e)
+    assert len(plan) == 7 and float(e.evaluate().sum()) == 0.0                 # the shared sub-tree is planned once
+    assert e.evaluate({"a": torch.full((2, 3), 4.0)}).flatten().tolist() == [12.0, 12.0]
+    from sneppx_alg_b200.algorithms import npe
+    wts = {"w1": torch.randn(8, 16) / 3, "b1": torch.randn(16), "w2": torch.randn(16, 8) / 4}
+    ops_ = [{"type": "matmul", "args": ["x", "w1"], "dest": "h"}, {"type": "add", "args": ["h", "b1"], "dest": "h2"},
+            {"type": "nop"}, {"type": "relu", "args": ["h2"], "dest": "a"}, {"type": "matmul", "args": ["a", "w2"], "dest": "y"},
+            {"type": "add", "args": ["y", "x"], "dest": "out"}]
+    comp = sx.NPECompiler()
+    prog = comp.compile(ops_, wts)
+    ver = sx.NPEVerify()
+    assert ver.verify(prog)[0] and ver.check_bounds(prog, 64) and not ver.check_bounds(prog, 3) and ver.check_types(prog) == []
+    xin = torch.randn(4, 8)
+    want = torch.relu(xin @ wts["w1"] + wts["b1"]) @ wts["w2"] + xin
+    vm = npe.VM()
+    vm.load(prog)
+    assert torch.allclose(vm.run(xin), want, atol=1e-5)
+    opt = comp.jit_optimize(prog)
+    assert len(opt.instructions) < len(prog.instructions)
+    vm.load(opt)
+    assert torch.allclose(vm.run(xin), want, atol=1e-5)
+    broken = npe.Program(1, 8)
+    broken.append(npe.Instruction(npe.Op.ADD, 2, 0, 5)).append(npe.Instruction(npe.Op.HALT))
+    assert ver.check_types(broken) == ["Instr 0: register 5 read before it is written"]
+    with pytest.raises(KeyError):
+        comp.compile([{"type": "add", "args": ["x", "missing"], "dest": "o"}])
+    many = [{"type": "relu", "args": ["x"], "dest": f"v{i}"} for i in range(16)] + \
+           [{"type": "add", "args": [f"v{i}", "x"], "dest": f"s{i}"} for i in range(16)]
+    with pytest.raises(OverflowError):
+        comp.compile(many)
+
+
+def test_backbones_masked_autoencoder_and_small_records():
+    from sneppx_alg_b200.models.config import ModelConfig
+    cfg = ModelConfig(vocab_size=64, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, max_position_embeddings=32, tie_word_embeddings=False)
+    torch.manual_seed(0)
+    lm = sx.LlamaForCausalLM(cfg)
+    body = sx.LlamaModel(cfg)
+    assert body.lm_head is None and isinstance(body, sx.LlamaForCausalLM) and issubclass(sx.MistralModel, sx.LlamaModel)
+    body.load_state_dict({k: v for k, v in lm.state_dict().items() if not k.startswith("lm_head")})
+    ids = torch.randint(0, 64, (2, 8))
+    h = body(ids)["last_hidden_state"]
+    assert h.shape == (2, 8, 32) and torch.allclose(h @ lm.lm_head.weight.T, lm(ids)["logits"], atol=1e-4)
+    with pytest.raises(AttributeError):
+        body.head_weight()
+    gcfg = dict(vocab_size=50, n_positions=16, n_embd=16, n_layer=1, n_head=2)
+    g = sx.GPTLMHeadModel(**gcfg)
+    assert g.lm_head.weight.data_ptr() != g.wte.weight.data_ptr() and g(ids % 50)["logits"].shape == (2, 8, 50)
+    t5 = sx.T5Model(vocab_size=40, d_model=16, d_ff=32, num_layers=1, num_decoder_layers=1, num_heads=4)
+    out = t5(ids % 40, ids[:, :5] % 40)
+    assert out["last_hidden_state"].shape == (2, 5, 16) and out["encoder_last_hidden_state"].shape == (2, 8, 16)
+    mae = sx.MAE(img_size=32, patch_size=8, embed_dim=32, encoder_depth=2, decoder_depth=1, num_heads=2, decoder_embed_dim=32)
+    imgs = torch.randn(3, 3, 32, 32)
+    loss, pred, mask = mae(imgs)
+    assert pred.shape == (3, 16, 192) and mask.sum(1).tolist() == [12.0] * 3 and torch.allclose(mae.unpatchify(mae.patchify(imgs)), imgs)
+    loss.backward()
+    assert mae.mask_token.grad.abs().sum() > 0
+    noise = torch.arange(16.0).repeat(3, 1)
+    kept, m, restore = mae.random_masking(torch.arange(16.0).view(1, 16, 1).repeat(3, 1, 2), noise=noise)
+    assert kept[0, :, 0].tolist() == [0.0, 1.0, 2.0, 3.0] and m[0].tolist() == [0.0] * 4 + [1.0] * 12
+    opt = torch.optim.Adam(mae.parameters(), lr=3e-3)
+    first = last = None
+    for _ in range(30):
+        opt.zero_grad()
+        l, _, _ = mae(imgs)
+        l.backward()
+        opt.step()
+        first, last = first if first is not None else float(l.detach()), float(l.detach())
+    assert last < 0.8 * first
+    assert float(sx.MAELoss()(torch.tensor([1.0, 3.0]), torch.tensor([2.0, 1.0]))) == 1.5
+    d = sx.Dense(4, activation="relu")
+    y = d(torch.randn(5, 3))
+    assert y.shape == (5, 4) and (y >= 0).all() and d.weight.shape == (4, 3) and len(list(d.parameters())) == 2
+    st = sx.IncrementalAttentionState(2, 4)
+    q, k, v = torch.randn(2, 4), torch.randn(2, 10, 4), torch.randn(2, 10, 4)
+    scores = torch.einsum("hd,hkd->hk", q, k) / 2.0
+    for s0, s1 in ((0, 3), (3, 4), (4, 10)):
+        st.update(scores[:, s0:s1], v[:, s0:s1])
+    assert torch.allclose(st.output(), torch.einsum("hk,hkd->hd", scores.softmax(-1), v), atol=1e-5)
+    assert torch.allclose(st.logsumexp().squeeze(-1), scores.logsumexp(-1), atol=1e-5)
+    assert sx.MX_FORMATS[sx.MXFormat.MXFP6_E2M3].grid().max() == 7.5 and len(sx.MX_FORMATS[sx.MXFormat.MXFP4_E2M1].grid()) == 8
+    x = torch.randn(8, 64)
+    from sneppx_alg_b200.quant.algorithms import mx_quantize, mx_quantize_spec
+    assert torch.equal(mx_quantize_spec(x, sx.MXFormat.MXFP4_E2M1)[0], mx_quantize(x, "mxfp4")[0])
+    err = {f: float((mx_quantize_spec(x, f)[0] - x).abs().mean()) for f in sx.MX_FORMATS}
+    assert err["mxfp8_e4m3"] < err["mxfp6_e2m3"] < err["mxfp4_e2m1"] and err["mxfp8_e4m3"] < err["mxfp8_e5m2"]
+    ct = sx.ConstantTimeOps
+    assert ct.ct_select(5, 6, True) == 5 and ct.ct_select(5, 6, False) == 6 and ct.ct_swap(1, 2, True) == (2, 1) and \
+        ct.ct_swap(1, 2, False) == (1, 2) and [ct.cache_const_lookup(bytes(range(10, 20)), i) for i in (0, 9)] == [10, 19]
+    feats = sx.CPUFeatures()
+    assert set(feats.as_dict()) >= {"avx2", "aes_ni"} and feats.has("avx2") == feats.has_avx2
+    assert sx.ComputeCapability.BLACKWELL.value == (10, 0) and sx.TopologyType("ring") is sx.TopologyType.RING
+    pool = sx.EntropyPool(reseed_interval=2)
+    outs = {pool.random_bytes(16) for _ in range(6)}
+    assert len(outs) == 6 and all(len(o) == 16 for o in outs)
+    dev = sx.EdgeDevice.detect()
+    assert dev.cores >= 1 and isinstance(dev.supports_int8(), bool) and "EdgeDevice(" in repr(dev)
+    assert sx.DeviceInfo.probe()[-1].kind == "cpu" and sx.CUDADeviceProps("x", sm_count=148).sm_count == 148
+    assert sx.int_(1, 4).sample(__import__("random").Random(0)) in (1, 2, 3, 4) and sx.Input((None, 8)).example(2).shape == (2, 1, 8)
+    gm = sx.GemmConfig(tile_m=8, tile_n=8, tile_k=8).create_gemm()
+    a, b = torch.randn(20, 33), torch.randn(33, 7)
+    assert torch.allclose(gm(a, b), a @ b, atol=1e-4)
+    c, adv = sx.ARCAdversarialTrainGraph(0.1).build([torch.randn(8, 4), torch.randn(2, 8)], torch.randn(3, 4))
+    assert c.shape == adv.shape == (3, 2) and (c - adv).abs().max() > 0 and sx.ARCFForward.forward(torch.full((1, 2), 1e3), torch.eye(2)).max() == 10.0
+    assert torch.equal(sx.FMSync.all_reduce(torch.ones(3)), torch.ones(3)) and \
+        torch.allclose(sx.FMSync.federated_avg([torch.zeros(2), torch.ones(2) * 2]), torch.ones(2))
+    e = sx.SERExpert(3, 8, 16)
+    assert e.expert_id == 3 and e(torch.randn(5, 8)).shape == (5, 8)
+
+
+def test_worker_pool_drains_the_batch_queue():
+    import time as _t
+    from sneppx_alg_b200.serving.serving_engine import ServingEngine
+    eng = ServingEngine(max_batch=4, batch_timeout_ms=1.0)
+    done = []
+    with sx.WorkerPool(eng, lambda batch: done.extend(batch), num_workers=3) as pool:
+        for i in range(50):
+            eng.enqueue(i)
+        t0 = _t.time()
+        while len(done) < 50 and _t.time() - t0 < 5.0:
+            _t.sleep(0.005)
+    assert sorted(done) == list(range(50)) and pool.batches_done >= 13 and pool.errors == []
+    boom = sx.WorkerPool(eng, lambda batch: 1 / 0, num_workers=1)
+    boom.start()
+    eng.enqueue("x")
+    t0 = _t.time()
+    while not boom.errors and _t.time() - t0 < 5.0:
+        _t.sleep(0.005)
+    boom.stop()
+    assert isinstance(boom.errors[0], ZeroDivisionError)
