@@ -1,6 +1,8 @@
 """Security middleware for the gateway (the reference's ``security_middleware.py`` / ``api_gateway.py``): one
 ``check`` call applies firewall rules, per-client rate limiting with temporary bans, API-key scopes and the prompt
-filter, and records usage and an audit line."""
+filter, and records usage and an audit line. Optional stages from ``security.ai_extensions``: a jailbreak detector
+that also looks inside base64 / hex / rot13 / URL-escaped payloads, a prompt policy, and a guard that redacts secrets
+and personal data from generated text (``screen_output``)."""
 from __future__ import annotations
 
 from dataclasses import dataclass
@@ -20,8 +22,9 @@ class Decision:
 class SecurityMiddleware:
     def __init__(self, firewall: Optional[Firewall] = None, limiter: Optional[DDoSMitigator] = None,
                  keys: Optional[ApiKeyStore] = None, audit: Optional[AuditLogger] = None, prompt_filter=None,
-                 max_prompt_chars=32768):
+                 max_prompt_chars=32768, jailbreak_detector=None, prompt_policy=None, extraction_guard=None):
         self.firewall, self.limiter, self.keys, self.audit = firewall, limiter, keys, audit
+        self.jailbreak, self.policy, self.guard = jailbreak_detector, prompt_policy, extraction_guard
         self.filter = prompt_filter or PromptFilter()
         self.usage = UsageTracker()
         self.max_prompt_chars = max_prompt_chars
@@ -44,7 +47,17 @@ class SecurityMiddleware:
         res = self.filter.check(prompt)
         if not res.allowed:
             return Decision(False, 400, "prompt filter: " + ",".join(res.reasons))
+        if self.policy is not None:
+            ok, why = self.policy.enforce(prompt)
+            if not ok:
+                return Decision(False, 400, "prompt policy: " + why)
+        if self.jailbreak is not None and self.jailbreak.detect(prompt):
+            return Decision(False, 400, "jailbreak pattern")
         return Decision(True)
+
+    def screen_output(self, text: str) -> str:
+        """Generated text with secrets / personal data replaced by placeholders when an extraction guard is set."""
+        return text if self.guard is None else self.guard.redact(text)
 
     def record(self, owner: str, prompt_tokens: int, completion_tokens: int):
         self.usage.record(owner, prompt_tokens, completion_tokens)
