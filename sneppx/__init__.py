@@ -1,6 +1,10 @@
 """``import sneppx`` — the package name the reference's documentation uses (``sneppx.nn``, ``sneppx.serving``,
-``sneppx.hub``, ``sneppx.distributed``).  Every submodule is the corresponding module of ``sneppx_alg_b200``."""
+``sneppx.hub``, ``sneppx.distributed``).  Every submodule is the corresponding module of ``sneppx_alg_b200``:
+``sneppx.nn is sneppx_alg_b200.nn``, and ``from sneppx.models.llama import LlamaForCausalLM`` imports
+``sneppx_alg_b200.models.llama`` (an import hook maps the names; nothing is copied)."""
 import importlib
+import importlib.abc
+import importlib.util
 import sys
 
 import sneppx_alg_b200 as _impl
@@ -12,11 +16,43 @@ _SUB = {"nn": "nn", "ops": "ops", "optim": "optim", "serving": "serving", "hub":
         "cli": "cli", "benchmarks": "benchmarks"}
 
 
+def _target(fullname: str):
+    parts = fullname.split(".")
+    if len(parts) < 2 or parts[0] != __name__ or parts[1] not in _SUB:
+        return None
+    return ".".join(["sneppx_alg_b200", _SUB[parts[1]]] + parts[2:])
+
+
+class _AliasLoader(importlib.abc.Loader):
+    def __init__(self, target):
+        self.target = target
+
+    def create_module(self, spec):
+        mod = importlib.import_module(self.target)           # the real module object, under a second name
+        self._keep = {k: getattr(mod, k, None) for k in ("__spec__", "__loader__", "__package__", "__path__", "__file__", "__cached__")}
+        return mod
+
+    def exec_module(self, module):
+        for k, v in self._keep.items():                      # the import system re-labelled the module: undo that
+            if v is not None:
+                setattr(module, k, v)
+
+
+class _AliasFinder(importlib.abc.MetaPathFinder):
+    def find_spec(self, fullname, path=None, target=None):
+        real = _target(fullname)
+        if real is None or importlib.util.find_spec(real) is None:
+            return None
+        return importlib.util.spec_from_loader(fullname, _AliasLoader(real))
+
+
+if not any(isinstance(f, _AliasFinder) for f in sys.meta_path):
+    sys.meta_path.insert(0, _AliasFinder())
+
+
 def __getattr__(name):
     if name in _SUB:
-        mod = importlib.import_module(f"sneppx_alg_b200.{_SUB[name]}")
-        sys.modules[f"sneppx.{name}"] = mod
-        return mod
+        return importlib.import_module(f"{__name__}.{name}")
     return getattr(_impl, name)
 
 

@@ -528,3 +528,18 @@ def test_worker_pool_drains_the_batch_queue():
         _t.sleep(0.005)
     boom.stop()
     assert isinstance(boom.errors[0], ZeroDivisionError)
+
+
+def test_alias_package_submodules_import_by_name():
+    import importlib
+    import sneppx
+    from sneppx.models.llama import LlamaForCausalLM                              # noqa: F401  (a from-import of a deep submodule)
+    import sneppx.training.engine as eng
+    import sneppx_alg_b200.models.llama as real_llama
+    import sneppx_alg_b200.training.engine as real_eng
+    assert sneppx.models.llama is real_llama and eng is real_eng and sneppx.distributed.__name__ == "sneppx_alg_b200.parallel.distributed"
+    assert real_llama.__spec__.name == "sneppx_alg_b200.models.llama"            # the alias import does not re-label the module
+    with pytest.raises(ModuleNotFoundError):
+        importlib.import_module("sneppx.no_such_module")
+    with pytest.raises(ModuleNotFoundError):
+        importlib.import_module("sneppx.models.no_such_module")
