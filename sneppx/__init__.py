@@ -18,9 +18,9 @@ _SUB = {"nn": "nn", "ops": "ops", "optim": "optim", "serving": "serving", "hub":
 
 def _target(fullname: str):
     parts = fullname.split(".")
-    if len(parts) < 2 or parts[0] != __name__ or parts[1] not in _SUB:
+    if len(parts) < 2 or parts[0] != __name__:
         return None
-    return ".".join(["sneppx_alg_b200", _SUB[parts[1]]] + parts[2:])
+    return ".".join(["sneppx_alg_b200", _SUB.get(parts[1], parts[1])] + parts[2:])     # other modules keep their name
 
 
 class _AliasLoader(importlib.abc.Loader):
@@ -41,7 +41,10 @@ class _AliasLoader(importlib.abc.Loader):
 class _AliasFinder(importlib.abc.MetaPathFinder):
     def find_spec(self, fullname, path=None, target=None):
         real = _target(fullname)
-        if real is None or importlib.util.find_spec(real) is None:
+        try:
+            if real is None or importlib.util.find_spec(real) is None:
+                return None
+        except ModuleNotFoundError:                           # a parent package of the target does not exist
             return None
         return importlib.util.spec_from_loader(fullname, _AliasLoader(real))
 
@@ -53,7 +56,15 @@ if not any(isinstance(f, _AliasFinder) for f in sys.meta_path):
 def __getattr__(name):
     if name in _SUB:
         return importlib.import_module(f"{__name__}.{name}")
-    return getattr(_impl, name)
+    try:
+        return getattr(_impl, name)
+    except AttributeError:
+        if not name.startswith("_"):
+            try:
+                return importlib.import_module(f"{__name__}.{name}")
+            except ModuleNotFoundError:
+                pass
+        raise
 
 
 __version__ = getattr(_impl, "__version__", "0.1.0")

@@ -459,7 +459,7 @@ def differential_attention(q, k, v, lam, causal=True, scale=None):
 
 # ----------------------------------------------------------------------------- cross entropy (L1)
 def cross_entropy_reference(logits, target, ignore_index=-100):
-    return F.cross_entropy(logits.float().view(-1, logits.shape[-1]), target.view(-1), ignore_index=ignore_index)
+    return F.cross_entropy(logits.float().reshape(-1, logits.shape[-1]), target.reshape(-1), ignore_index=ignore_index)
 
 
 class _CEFn(torch.autograd.Function):
