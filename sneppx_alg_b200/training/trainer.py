@@ -97,7 +97,7 @@ class Trainer:
                     torch.nn.utils.clip_grad_norm_(self.model.parameters(), self.cfg.training.max_grad_norm)
                 self.optimizer.step()
         self.step_count += 1
-        return loss
+        return loss.detach() if torch.is_tensor(loss) else loss
 
     @staticmethod
     def _preshifted(x, y):
