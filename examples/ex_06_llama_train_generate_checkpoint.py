@@ -14,8 +14,12 @@ from sneppx.training.engine import TrainEngine
 
 def main(steps: int = 40) -> dict:
     g, dev = seed(5), device()
-    cfg = ModelConfig(vocab_size=128, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
-                      num_key_value_heads=2, max_position_embeddings=64)
+    if dev.type == "cuda":      # the tensor-core kernels want head size 128 and widths that are multiples of 128
+        cfg = ModelConfig(vocab_size=512, hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=2,
+                          num_key_value_heads=1, max_position_embeddings=64)
+    else:
+        cfg = ModelConfig(vocab_size=128, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                          num_key_value_heads=2, max_position_embeddings=64)
     dtype = torch.bfloat16 if dev.type == "cuda" else torch.float32
     model = LlamaForCausalLM(cfg, dtype=dtype, device=dev)
     engine = TrainEngine(model, lr=3e-3, betas=(0.9, 0.95), weight_decay=0.0, max_grad_norm=1.0)
@@ -29,7 +33,7 @@ def main(steps: int = 40) -> dict:
     out = model.generate(prompt, max_new_tokens=6)
     with tempfile.TemporaryDirectory() as d:
         path = os.path.join(d, "tiny.sneppx")
-        save_tensors(path, model.to_reference_state_dict(), metadata={"arch": "llama", "hidden_size": 64})
+        save_tensors(path, model.to_reference_state_dict(), metadata={"arch": "llama", "hidden_size": cfg.hidden_size})
         ok = validate_checkpoint(path)
         back, meta = load_tensors(path)
     same = all(torch.equal(back[k].cpu(), v.cpu()) for k, v in model.to_reference_state_dict().items())

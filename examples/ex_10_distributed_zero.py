@@ -16,8 +16,12 @@ def train(rank: int, world: int, steps: int = 30):
     torch.manual_seed(0)                                    # same initial weights on every rank
     on_gpu = torch.cuda.is_available() and dist.get_backend() == "nccl"
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", rank))) if on_gpu else torch.device("cpu")
-    cfg = ModelConfig(hidden_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
-                      intermediate_size=128, vocab_size=256, max_position_embeddings=32, rms_norm_eps=1e-5)
+    if on_gpu:                  # the tensor-core kernels want head size 128 and widths that are multiples of 128
+        cfg = ModelConfig(hidden_size=512, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                          intermediate_size=1024, vocab_size=4096, max_position_embeddings=256, rms_norm_eps=1e-5)
+    else:
+        cfg = ModelConfig(hidden_size=64, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                          intermediate_size=128, vocab_size=256, max_position_embeddings=32, rms_norm_eps=1e-5)
     model = build_model(cfg, dtype=torch.bfloat16 if on_gpu else torch.float32, device=dev)
     engine = ZeroEngine(model, zero_stage=3, lr=1e-2, weight_decay=0.1, max_grad_norm=1.0)
     # every rank trains on its own slice of one task: continue an arithmetic progression modulo the vocabulary size
