@@ -26,7 +26,7 @@ import re
 import struct
 from dataclasses import dataclass, field
 from fractions import Fraction
-from typing import Any, Callable, Dict, Iterable, List, Optional, Sequence, Set, Tuple
+from typing import Any, Dict, Iterable, List, Optional, Sequence, Set, Tuple
 
 from .formal import CheckResult, FormalModel, parse_ltl
 

@@ -26,7 +26,7 @@ import os
 import re
 import struct
 import time
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Callable, Dict, Iterable, List, Optional, Sequence, Tuple
 
 from . import crypto

@@ -23,7 +23,6 @@ import json
 import os
 import struct
 import time
-from dataclasses import dataclass, field
 from typing import Any, Callable, Dict, Iterable, List, Optional, Sequence, Tuple
 
 from . import crypto
