@@ -1703,3 +1703,21 @@ class TextDataset(torch.utils.data.Dataset):
         ids += [self.pad_id] * (self.max_length + 1 - len(ids))
         t = torch.tensor(ids, dtype=torch.long)
         return t[:-1], t[1:]
+
+
+# ------------------------------------------------------------------------------------------------ obfuscation pass
+class CfgFlattening:
+    """Control-flow flattening as a pass object: every basic block of a routine becomes a case of one dispatcher loop
+    keyed by a state register, so the original branch structure no longer shows in the graph
+    (reference: security/obfuscation/cfg_flatten.cpp). ``apply`` takes the routine's source in the obfuscation VM's
+    register IR, or an ``ObfuscatedRoutine``, and returns the flattened routine; its results are unchanged."""
+
+    def __init__(self, seed: int = 0):
+        self.seed = seed
+
+    def apply(self, routine):
+        from .security.obfuscation import ObfuscatedRoutine
+        r = ObfuscatedRoutine(routine) if isinstance(routine, str) else routine
+        return r.flatten(self.seed)
+
+    __call__ = apply

@@ -6,9 +6,8 @@ thread pools, streamers and the ``*_kernel`` entry points (``cuda_kernels.py``) 
 
 Not reproduced, by design (one CUDA sm_100a device layer, portable C++ host code): the multi-vendor back-end and
 driver tables (``NPUBackend``, ``OpenVINOBackend``, ``ROCmDriver``, ``TPUDriver``, ``TensorRTExporter``, ``AutoBackend``
-...), the x86 assembly wrappers (``AESNI``, ``SHANI``, ``Poly1305ASM``, ``Ed25519ASM``, ``ChaCha20AVX2``, ``FirewallASM``,
-``Asm*``) and control-flow flattening of native code (``CfgFlattening``; the obfuscation passes here work on NPE
-bytecode, ``security/obfuscation.py``).
+...) and the x86 assembly wrappers (``AESNI``, ``SHANI``, ``Poly1305ASM``, ``Ed25519ASM``, ``ChaCha20AVX2``,
+``FirewallASM``, ``Asm*``).
 """
 from __future__ import annotations
 

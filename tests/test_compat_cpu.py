@@ -10,12 +10,12 @@ import torch
 import SneppX_ALG as sx
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-# not reproduced on purpose: other vendors' back-ends and drivers, x86 assembly wrappers, code obfuscation,
-# post-quantum schemes (see the docstring of sneppx_alg_b200/compat_services.py)
+# not reproduced on purpose: other vendors' back-ends and drivers, x86 assembly wrappers
+# (see the docstring of sneppx_alg_b200/compat_services.py)
 EXCLUDED_PREFIXES = ("Asm", "AESNI", "SHANI", "Poly1305ASM", "Ed25519ASM", "ChaCha20AVX2", "FirewallASM", "MontgomeryMul",
                      "NPUBackend", "ONNXBackend", "OpenVINOBackend", "ROCmDriver", "TPUDriver", "TensorRTExporter", "AutoBackend",
                      "CPUBackend", "CPUFP16Backend", "CPUFP32Backend", "EdgeBackend", "InferenceBackend", "BackendRegistry",
-                     "register_backend", "CfgFlattening")
+                     "register_backend")
 
 
 def test_most_reference_names_resolve():
@@ -543,3 +543,22 @@ def test_alias_package_submodules_import_by_name():
         importlib.import_module("sneppx.no_such_module")
     with pytest.raises(ModuleNotFoundError):
         importlib.import_module("sneppx.models.no_such_module")
+
+
+def test_cfg_flattening_pass_object():
+    src = """
+entry: movi r1 0 ; movi r2 0 ; jmp loop
+loop: cmp r2 r0 ; jg done body
+body: add r1 r2 ; addi r2 1 ; jmp loop
+done: ret r1
+"""
+    from sneppx_alg_b200.security.obfuscation import ObfuscatedRoutine
+    plain = ObfuscatedRoutine(src)
+    flat = sx.CfgFlattening(seed=3).apply(src)
+    assert isinstance(flat, ObfuscatedRoutine) and flat.num_blocks > plain.num_blocks
+    for n in (0, 1, 5, 20):
+        assert flat.run_ir(n) == plain.run_ir(n) == (n * (n + 1) // 2, [])
+    assert flat.compile(seed=7).run(9)[0] == 45                               # flattened, re-encoded byte code on the VM
+    assert sx.CfgFlattening(1)(plain) is plain                                # a routine object is flattened in place
+    plain.close()
+    flat.close()
