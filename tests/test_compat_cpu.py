@@ -562,3 +562,19 @@ done: ret r1
     assert sx.CfgFlattening(1)(plain) is plain                                # a routine object is flattened in place
     plain.close()
     flat.close()
+
+
+def test_every_resolved_name_has_the_kind_it_has_in_the_reference():
+    """``tests/data/reference_flat_kinds.txt`` lists, for every public flat name, whether the reference's bindings define it
+    as a class or as a function (names that are neither, constants and aliases, are marked ``value`` and not checked)."""
+    import inspect
+    wrong = []
+    for line in open(os.path.join(HERE, "data", "reference_flat_kinds.txt")):
+        name, kind = line.split()
+        if kind == "value" or not hasattr(sx, name):
+            continue
+        obj = getattr(sx, name)
+        got = "class" if inspect.isclass(obj) else "function" if callable(obj) else "value"
+        if got != kind:
+            wrong.append((name, kind, got))
+    assert wrong == []
