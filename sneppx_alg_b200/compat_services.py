@@ -1687,15 +1687,7 @@ install_update = lambda mgr: mgr.install_update()  # noqa: E731
 rollback_update = lambda mgr, file_name: mgr.rollback_update(file_name)  # noqa: E731
 
 
-def _alg(attr):
-    def make(*a, **k):
-        from . import algorithms
-        return getattr(algorithms, attr)(*a, **k)
-    make.__name__ = attr
-    return make
-
-
-AlgoHSSModel, AlgoSERModel = _alg("HSSModel"), _alg("SERModel")
+AlgoHSSModel, AlgoSERModel = _lazy("algorithms", "HSSModel"), _lazy("algorithms", "SERModel")
 DeepSeekV2Model = _lazy("models.deepseek", "DeepSeekV2ForCausalLM")
 BlockTable = _lazy("serving.kv_cache", "PagedKVCache")
 DataBuffer = _lazy("utils.mm", "Arena")
