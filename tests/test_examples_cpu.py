@@ -59,3 +59,23 @@ def test_security_distributed_quantization_and_onnx():
     assert q["int8"] < q["fp8_e4m3"] < q["mxfp4"] and q["int4_gptq"] < q["int4_awq"] < q["int4_round_to_nearest"]
     o = _load("ex_12_onnx_export_and_run").main()
     assert o["problems"] == [] and o["max_error"] < 1e-3 and o["max_error_optimised"] < 1e-3 and o["max_error_qdq"] < 0.1
+
+
+def test_notebooks_are_current_and_run():
+    """``examples/notebooks/*.ipynb`` are what ``to_notebook.py`` makes of the scripts today, and the cells of one of
+    them execute top to bottom."""
+    import json
+    conv = _load("to_notebook")
+    scripts = sorted(f for f in os.listdir(EX) if f.startswith("ex_") and f.endswith(".py") and not f.startswith("ex_10_"))
+    books = sorted(os.listdir(os.path.join(EX, "notebooks")))
+    assert books == [s[:-3] + ".ipynb" for s in scripts]
+    for s in scripts:
+        on_disk = json.load(open(os.path.join(EX, "notebooks", s[:-3] + ".ipynb")))
+        assert on_disk == conv.convert(os.path.join(EX, s)), f"{s}: run python examples/to_notebook.py --all"
+        assert on_disk["nbformat"] == 4 and on_disk["cells"][0]["cell_type"] == "markdown" and on_disk["cells"][-1]["source"][0].startswith("result = main()")
+    nb = json.load(open(os.path.join(EX, "notebooks", "ex_01_linear_regression.ipynb")))
+    env = {"__name__": "__notebook__"}
+    for cell in nb["cells"]:
+        if cell["cell_type"] == "code":
+            exec(compile("".join(cell["source"]), "cell", "exec"), env)
+    assert abs(env["result"]["slope"] - 3.0) < 0.05
