@@ -239,11 +239,11 @@ class LlamaForCausalLM(Module):
 
 
 class MistralForCausalLM(LlamaForCausalLM):
-    pass
+    """Llama architecture under a Mistral configuration (``sliding_window`` selects the windowed attention kernel)."""
 
 
 class Qwen2ForCausalLM(LlamaForCausalLM):
-    pass
+    """Llama architecture under a Qwen2 configuration (``attention_bias`` adds the q / k / v biases)."""
 
 
 class LlamaModel(LlamaForCausalLM):
@@ -267,19 +267,19 @@ class LlamaModel(LlamaForCausalLM):
 
 
 class MistralModel(LlamaModel):
-    pass
+    """Head-less decoder stack under a Mistral configuration."""
 
 
 class Qwen2Model(LlamaModel):
-    pass
+    """Head-less decoder stack under a Qwen2 configuration."""
 
 
 class MistralMLP(LlamaMLP):
-    pass
+    """The SwiGLU feed-forward block; Mistral's is Llama's."""
 
 
 class Qwen2MLP(LlamaMLP):
-    pass
+    """The SwiGLU feed-forward block; Qwen2's is Llama's."""
 
 
 class MistralAttention(LlamaAttention):
@@ -291,11 +291,11 @@ class Qwen2Attention(LlamaAttention):
 
 
 class MistralDecoderLayer(LlamaBlock):
-    pass
+    """Pre-norm attention + feed-forward block under a Mistral configuration."""
 
 
 class Qwen2DecoderLayer(LlamaBlock):
-    pass
+    """Pre-norm attention + feed-forward block under a Qwen2 configuration."""
 
 
 def create_model(name_or_config, dtype=None, device=None, **overrides):
