@@ -37,6 +37,7 @@ HS_CLIENT_HELLO, HS_SERVER_HELLO, HS_NEW_SESSION_TICKET, HS_ENCRYPTED_EXTENSIONS
 HS_CERTIFICATE, HS_CERTIFICATE_REQUEST, HS_CERTIFICATE_VERIFY, HS_FINISHED, HS_KEY_UPDATE = 11, 13, 15, 20, 24
 EXT_SERVER_NAME, EXT_SUPPORTED_GROUPS, EXT_SIGNATURE_ALGORITHMS, EXT_ALPN = 0, 10, 13, 16
 EXT_PRE_SHARED_KEY, EXT_EARLY_DATA, EXT_SUPPORTED_VERSIONS, EXT_PSK_MODES, EXT_KEY_SHARE = 41, 42, 43, 45, 51
+EXT_QUIC_TRANSPORT_PARAMETERS = 57
 GROUP_X25519, SIG_ED25519, PSK_DHE_KE = 0x001D, 0x0807, 1
 ALERT_CLOSE_NOTIFY, ALERT_UNEXPECTED_MESSAGE, ALERT_BAD_RECORD_MAC, ALERT_HANDSHAKE_FAILURE = 0, 10, 20, 40
 ALERT_BAD_CERTIFICATE, ALERT_ILLEGAL_PARAMETER, ALERT_DECODE_ERROR, ALERT_DECRYPT_ERROR = 42, 47, 50, 51
@@ -382,8 +383,16 @@ class _Connection:
 
     is_client = False
 
-    def __init__(self):
+    def __init__(self, quic_transport_parameters: Optional[bytes] = None):
         self.records = _RecordLayer()
+        # QUIC carries the handshake messages itself (RFC 9001 section 4): no records, no ChangeCipherSpec, no KeyUpdate
+        # message; messages leave through ``crypto_out`` per encryption level and traffic secrets are handed over raw
+        self.quic = quic_transport_parameters is not None
+        self.quic_parameters = quic_transport_parameters
+        self.peer_quic_parameters: Optional[bytes] = None
+        self.crypto_out: Dict[str, bytearray] = {"initial": bytearray(), "handshake": bytearray(), "application": bytearray()}
+        self.quic_secrets: Dict[Tuple[str, str], bytes] = {}          # (level, "read" | "write") -> traffic secret
+        self._write_level = self._read_level = "initial"
         self.ks: Optional[Tls13KeySchedule] = None
         self.suite: Optional[int] = None
         self.transcript = hashlib.sha256()
@@ -420,12 +429,12 @@ class _Connection:
 
     def update_keys(self, request_peer: bool = True) -> None:
         """Send KeyUpdate and move the sending direction to its next traffic secret (RFC 8446 section 4.6.3)."""
-        if not self.handshake_complete:
-            raise TlsError("KeyUpdate before the handshake finished")
+        if not self.handshake_complete or self.quic:
+            raise TlsError("KeyUpdate before the handshake finished, or on a QUIC connection (which updates keys itself)")
         self.out += self.records.seal(CT_HANDSHAKE, _handshake(HS_KEY_UPDATE, bytes([1 if request_peer else 0])))
         label = "c ap traffic" if self.is_client else "s ap traffic"
         self.ks.update_traffic_secret(label)
-        self.records.set_write(self.suite, self.ks.traffic_keys(label))
+        self._install_write(label)
         self.key_updates_sent += 1
 
     def export_keying_material(self, label: str, context: bytes = b"", length: int = 32) -> bytes:
@@ -479,17 +488,52 @@ class _Connection:
         if self.hs_buf:
             raise TlsError("key change in the middle of a handshake message", ALERT_UNEXPECTED_MESSAGE)
 
-    def _send_handshake(self, msg: bytes) -> None:
-        self.transcript.update(msg)
-        self.out += self.records.seal(CT_HANDSHAKE, msg)
+    def _send_handshake(self, msg: bytes, in_transcript: bool = True) -> None:
+        if in_transcript:
+            self.transcript.update(msg)
+        if self.quic:
+            self.crypto_out[self._write_level] += msg
+        else:
+            self.out += self.records.seal(CT_HANDSHAKE, msg)
+
+    @staticmethod
+    def _level(label: str) -> str:
+        return "handshake" if " hs " in label else "application"
+
+    def _install_read(self, label: str) -> None:
+        if self.quic:
+            self._read_level = self._level(label)
+            self.quic_secrets[(self._read_level, "read")] = self.ks.secrets[label]
+        else:
+            self.records.set_read(self.suite, self.ks.traffic_keys(label))
+
+    def _install_write(self, label: str) -> None:
+        if self.quic:
+            self._write_level = self._level(label)
+            self.quic_secrets[(self._write_level, "write")] = self.ks.secrets[label]
+        else:
+            self.records.set_write(self.suite, self.ks.traffic_keys(label))
+
+    def receive_crypto(self, level: str, data: bytes) -> None:
+        """QUIC mode: in-order bytes of the CRYPTO stream of one encryption level."""
+        if not self.quic:
+            raise TlsError("not a QUIC connection")
+        if level != self._read_level:
+            if data:
+                raise TlsError(f"handshake data at level {level} while reading {self._read_level}", ALERT_UNEXPECTED_MESSAGE)
+            return
+        self.hs_buf += data
+        self._drain_handshake()
 
     def _on_key_update(self, body: bytes) -> None:
+        if self.quic:
+            raise TlsError("KeyUpdate message on a QUIC connection", ALERT_UNEXPECTED_MESSAGE)
         if body not in (b"\0", b"\x01"):
             raise TlsError("malformed KeyUpdate", ALERT_ILLEGAL_PARAMETER)
         self._boundary()
         label = "s ap traffic" if self.is_client else "c ap traffic"
         self.ks.update_traffic_secret(label)
-        self.records.set_read(self.suite, self.ks.traffic_keys(label))
+        self._install_read(label)
         self.key_updates_received += 1
         if body == b"\x01":
             self.update_keys(request_peer=False)
@@ -520,8 +564,11 @@ class TlsClient(_Connection):
 
     def __init__(self, server_name: Optional[str] = None, trusted_roots: Sequence[bytes] = (), pinned_keys: Iterable[bytes] = (),
                  psk: Optional[Tuple[bytes, bytes]] = None, session: Optional[Session] = None, alpn: Sequence[str] = (),
-                 suites: Sequence[int] = SUITES, insecure_skip_verify: bool = False):
-        super().__init__()
+                 suites: Sequence[int] = SUITES, insecure_skip_verify: bool = False,
+                 quic_transport_parameters: Optional[bytes] = None):
+        super().__init__(quic_transport_parameters)
+        if self.quic and not alpn:
+            raise ValueError("QUIC requires an application protocol to be negotiated")
         self.server_name, self.trusted_roots, self.pinned_keys = server_name, list(trusted_roots), set(pinned_keys)
         self.psk, self.session, self.alpn_offer, self.suites = psk, session, list(alpn), list(suites)
         self.skip_verify = insecure_skip_verify
@@ -546,6 +593,8 @@ class TlsClient(_Connection):
                  (EXT_KEY_SHARE, _v16(struct.pack(">H", GROUP_X25519) + _v16(crypto.x25519(self._private))))]
         if self.alpn_offer:
             exts.append((EXT_ALPN, _v16(b"".join(_v8(p.encode()) for p in self.alpn_offer))))
+        if self.quic:
+            exts.append((EXT_QUIC_TRANSPORT_PARAMETERS, self.quic_parameters))
         identity, age, external = None, 0, True
         if self.psk is not None:
             identity, self._psk_key = self.psk
@@ -556,7 +605,7 @@ class TlsClient(_Connection):
         if identity is not None:
             exts.append((EXT_PSK_MODES, _v8(bytes([PSK_DHE_KE]))))
             exts.append((EXT_PRE_SHARED_KEY, _v16(_v16(identity) + struct.pack(">I", age)) + _v16(_v8(b"\0" * 32))))
-        self._session_id = os.urandom(32)
+        self._session_id = b"" if self.quic else os.urandom(32)        # QUIC does not use compatibility mode
         body = b"\x03\x03" + os.urandom(32) + _v8(self._session_id) + _v16(b"".join(struct.pack(">H", s) for s in self.suites)) \
             + _v8(b"\0") + _extensions(exts)
         hello = _handshake(HS_CLIENT_HELLO, body)
@@ -608,7 +657,7 @@ class TlsClient(_Connection):
         self.transcript.update(raw)
         self.ks.set_shared_secret(shared, self.transcript.digest())
         self._boundary()
-        self.records.set_read(suite, self.ks.traffic_keys("s hs traffic"))
+        self._install_read("s hs traffic")
         self._state = "wait_encrypted_extensions"
 
     def _encrypted_extensions(self, msg_type: int, body: bytes, raw: bytes) -> None:
@@ -621,6 +670,12 @@ class TlsClient(_Connection):
             if chosen not in self.alpn_offer or not names.done():
                 raise TlsError("server chose a protocol that was not offered", ALERT_ILLEGAL_PARAMETER)
             self.alpn = chosen
+        if self.quic:
+            if EXT_QUIC_TRANSPORT_PARAMETERS not in ext:
+                raise TlsError("server sent no QUIC transport parameters", ALERT_MISSING_EXTENSION)
+            if self.alpn is None:
+                raise TlsError("server chose no application protocol", ALERT_NO_APPLICATION_PROTOCOL)
+            self.peer_quic_parameters = ext[EXT_QUIC_TRANSPORT_PARAMETERS]
         self.transcript.update(raw)
         self._state = "wait_finished" if self.used_psk else "wait_certificate"
 
@@ -674,12 +729,13 @@ class TlsClient(_Connection):
         self.transcript.update(raw)
         self._boundary()
         self.ks.set_server_finished(self.transcript.digest())
-        self.out += self.records.seal(CT_CCS, b"\x01")                                     # compatibility mode
-        self.records.set_write(self.suite, self.ks.traffic_keys("c hs traffic"))
+        if not self.quic:
+            self.out += self.records.seal(CT_CCS, b"\x01")                                 # compatibility mode
+        self._install_write("c hs traffic")
         self._send_handshake(_handshake(HS_FINISHED, self.ks.finished_mac("c hs traffic", self.transcript.digest())))
         self.ks.set_client_finished(self.transcript.digest())
-        self.records.set_read(self.suite, self.ks.traffic_keys("s ap traffic"))
-        self.records.set_write(self.suite, self.ks.traffic_keys("c ap traffic"))
+        self._install_read("s ap traffic")
+        self._install_write("c ap traffic")
         self.handshake_complete, self._state = True, "connected"
 
     def _post_handshake(self, msg_type: int, body: bytes, raw: bytes) -> None:
@@ -734,8 +790,11 @@ class TlsServer(_Connection):
 
     def __init__(self, certificate_chain: Sequence[bytes] = (), private_seed: Optional[bytes] = None,
                  psk_lookup: Optional[Callable[[bytes], Optional[bytes]]] = None, tickets: Optional[TicketStore] = None,
-                 alpn: Sequence[str] = (), suites: Sequence[int] = SUITES, send_tickets: int = 1):
-        super().__init__()
+                 alpn: Sequence[str] = (), suites: Sequence[int] = SUITES, send_tickets: int = 1,
+                 quic_transport_parameters: Optional[bytes] = None):
+        super().__init__(quic_transport_parameters)
+        if self.quic and not alpn:
+            raise ValueError("QUIC requires an application protocol to be negotiated")
         if bool(certificate_chain) != bool(private_seed):
             raise ValueError("a certificate chain needs its private seed, and the other way round")
         if not certificate_chain and psk_lookup is None:
@@ -840,6 +899,12 @@ class TlsServer(_Connection):
             self.alpn = next((p for p in self.alpn_supported if p in theirs), None)
             if self.alpn is None:
                 raise TlsError("no application protocol in common", ALERT_NO_APPLICATION_PROTOCOL)
+        if self.quic:
+            if EXT_QUIC_TRANSPORT_PARAMETERS not in ext:
+                raise TlsError("client sent no QUIC transport parameters", ALERT_MISSING_EXTENSION)
+            if self.alpn is None:
+                raise TlsError("no application protocol in common", ALERT_NO_APPLICATION_PROTOCOL)
+            self.peer_quic_parameters = ext[EXT_QUIC_TRANSPORT_PARAMETERS]
         self.suite, self.used_psk = suite, psk is not None
         self.ks = Tls13KeySchedule(suite, psk[1] if psk else None)
         self.transcript.update(raw)
@@ -852,10 +917,13 @@ class TlsServer(_Connection):
             sh_ext.append((EXT_PRE_SHARED_KEY, struct.pack(">H", psk[0])))
         self._send_handshake(_handshake(HS_SERVER_HELLO, b"\x03\x03" + os.urandom(32) + _v8(session_id) + struct.pack(">H", suite)
                                         + b"\0" + _extensions(sh_ext)))
-        self.out += self.records.seal(CT_CCS, b"\x01")
+        if not self.quic:
+            self.out += self.records.seal(CT_CCS, b"\x01")
         self.ks.set_shared_secret(shared, self.transcript.digest())
-        self.records.set_write(suite, self.ks.traffic_keys("s hs traffic"))
+        self._install_write("s hs traffic")
         ee = [(EXT_ALPN, _v16(_v8(self.alpn.encode())))] if self.alpn else []
+        if self.quic:
+            ee.append((EXT_QUIC_TRANSPORT_PARAMETERS, self.quic_parameters))
         self._send_handshake(_handshake(HS_ENCRYPTED_EXTENSIONS, _extensions(ee)))
         if psk is None:
             certs = b"".join(_v24(c) + _v16(b"") for c in self.chain)
@@ -864,9 +932,9 @@ class TlsServer(_Connection):
             self._send_handshake(_handshake(HS_CERTIFICATE_VERIFY, struct.pack(">H", SIG_ED25519) + _v16(sig)))
         self._send_handshake(_handshake(HS_FINISHED, self.ks.finished_mac("s hs traffic", self.transcript.digest())))
         self.ks.set_server_finished(self.transcript.digest())
-        self.records.set_write(suite, self.ks.traffic_keys("s ap traffic"))
+        self._install_write("s ap traffic")
         self._boundary()
-        self.records.set_read(suite, self.ks.traffic_keys("c hs traffic"))
+        self._install_read("c hs traffic")
         self._state = "wait_finished"
 
     def _client_finished(self, body: bytes, raw: bytes) -> None:
@@ -875,14 +943,14 @@ class TlsServer(_Connection):
         self.transcript.update(raw)
         self._boundary()
         self.ks.set_client_finished(self.transcript.digest())
-        self.records.set_read(self.suite, self.ks.traffic_keys("c ap traffic"))
+        self._install_read("c ap traffic")
         self.handshake_complete, self._state = True, "connected"
         if self.tickets is not None:
             for i in range(self.send_tickets):
                 nonce = bytes([i])
                 ticket, age_add = self.tickets.issue(self.ks.resumption_psk(nonce), self.suite)
                 msg = struct.pack(">II", self.tickets.lifetime, age_add) + _v8(nonce) + _v16(ticket) + _extensions([])
-                self.out += self.records.seal(CT_HANDSHAKE, _handshake(HS_NEW_SESSION_TICKET, msg))
+                self._send_handshake(_handshake(HS_NEW_SESSION_TICKET, msg), in_transcript=False)
 
     def _post_handshake(self, msg_type: int, body: bytes, raw: bytes) -> None:
         if msg_type != HS_KEY_UPDATE:

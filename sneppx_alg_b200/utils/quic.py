@@ -10,7 +10,8 @@ smoothed RTT, stream reassembly by offset with FIN. What it does not do: TLS 1.3
 X25519 exchange carried in CRYPTO frames, optionally bound to a pre-shared key), header protection, congestion
 control beyond a fixed window, migration, 0-RTT. It therefore talks to itself, not to other QUIC stacks.
 The wire-exact packet protection of QUIC version 1 (initial secrets, AES-128-GCM / ChaCha20-Poly1305 payload
-protection, header protection, Retry tags, key updates) is in ``utils/quic_protection.py``.
+protection, header protection, Retry tags, key updates) is in ``utils/quic_protection.py``, and the standard handshake
+(TLS 1.3 in CRYPTO frames over the three packet-number spaces) in ``utils/quic_tls.py``.
 
 The reference declares this surface as a shell whose functions return 0 / NULL (net/quic/quic_transport.c:30-119:
 create_listener / listen / accept / dial / send / recv / stream_open / stream_send / stream_recv / close); the names
