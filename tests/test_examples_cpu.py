@@ -21,7 +21,7 @@ def _load(name):
 def test_every_example_is_listed_and_has_a_main():
     scripts = sorted(f[:-3] for f in os.listdir(EX) if f.startswith("ex_") and f.endswith(".py"))
     readme = open(os.path.join(EX, "README.md")).read()
-    assert len(scripts) == 12 and all(f"`{s}.py`" in readme for s in scripts)
+    assert len(scripts) == 13 and all(f"`{s}.py`" in readme for s in scripts)
     for s in scripts:
         assert callable(_load(s).main)
 
@@ -59,6 +59,14 @@ def test_security_distributed_quantization_and_onnx():
     assert q["int8"] < q["fp8_e4m3"] < q["mxfp4"] and q["int4_gptq"] < q["int4_awq"] < q["int4_round_to_nearest"]
     o = _load("ex_12_onnx_export_and_run").main()
     assert o["problems"] == [] and o["max_error"] < 1e-3 and o["max_error_optimised"] < 1e-3 and o["max_error_qdq"] < 0.1
+
+
+def test_secure_transports():
+    r = _load("ex_13_secure_transports").main()
+    assert r["certificate"] == {"reply": b"REGISTER RANK 0", "alpn": "sx/1", "resumed": False}
+    assert r["ticket"] == {"reply": b"BACK AGAIN", "resumed": True} and r["psk"] == {"reply": b"NO CERTIFICATE NEEDED", "psk": True}
+    assert "trusted root" in r["impostor_root"]
+    assert r["quic"] == {"first_datagram": 1200, "lost": 1, "confirmed": True, "stream": b"gradient shard", "keys_left": ["application"]}
 
 
 def test_notebooks_are_current_and_run():
