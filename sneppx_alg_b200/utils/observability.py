@@ -312,6 +312,117 @@ class MLflowTracker(ExperimentTracker):
             return [(int(a), float(b), int(c)) for a, b, c in (line.split() for line in f if line.strip())]
 
 
+class TensorBoardTracker(ExperimentTracker):
+    """TensorBoard event files, written directly (TFRecord framing with masked CRC-32C, ``Event`` / ``Summary`` protobuf
+    messages encoded by hand), so that ``tensorboard --logdir <directory>`` shows the run without TensorFlow or the
+    ``tensorboard`` package being importable where training runs. Scalars become ``simple_value`` summaries, parameters a
+    text summary (``text`` plugin, markdown table), histograms ``HistogramProto`` values. The JSON files of the base
+    class are written too. The reference's run tracker keeps ``metadata.json`` + ``metrics.jsonl`` only and points to
+    TensorBoard's ``runs/`` layout as its model (bindings/python/SneppX_ALG/interface_bindings/experiment.py:1-18)."""
+
+    _CRC_TABLE = None
+
+    @classmethod
+    def _crc32c(cls, data: bytes) -> int:
+        if cls._CRC_TABLE is None:
+            table = []
+            for i in range(256):
+                c = i
+                for _ in range(8):
+                    c = (c >> 1) ^ 0x82F63B78 if c & 1 else c >> 1
+                table.append(c)
+            cls._CRC_TABLE = table
+        crc = 0xFFFFFFFF
+        for b in data:
+            crc = cls._CRC_TABLE[(crc ^ b) & 0xFF] ^ (crc >> 8)
+        return crc ^ 0xFFFFFFFF
+
+    @classmethod
+    def _masked_crc(cls, data: bytes) -> int:
+        c = cls._crc32c(data)
+        return ((((c >> 15) | (c << 17)) & 0xFFFFFFFF) + 0xA282EAD8) & 0xFFFFFFFF
+
+    @staticmethod
+    def _varint(v: int) -> bytes:
+        v &= (1 << 64) - 1
+        out = bytearray()
+        while True:
+            out.append((v & 0x7F) | (0x80 if v > 0x7F else 0))
+            v >>= 7
+            if not v:
+                return bytes(out)
+
+    @classmethod
+    def _field(cls, number: int, wire: int, payload: bytes) -> bytes:
+        key = cls._varint((number << 3) | wire)
+        return key + (cls._varint(len(payload)) + payload if wire == 2 else payload)
+
+    @classmethod
+    def _event(cls, wall_time: float, step: int = 0, file_version: Optional[str] = None, summary: Optional[bytes] = None) -> bytes:
+        import struct
+        msg = cls._field(1, 1, struct.pack("<d", wall_time)) + cls._field(2, 0, cls._varint(step))
+        if file_version is not None:
+            msg += cls._field(3, 2, file_version.encode())
+        if summary is not None:
+            msg += cls._field(5, 2, summary)
+        return msg
+
+    def _write_event(self, event: bytes) -> None:
+        import struct
+        head = struct.pack("<Q", len(event))
+        self._tb.write(head + struct.pack("<I", self._masked_crc(head)) + event + struct.pack("<I", self._masked_crc(event)))
+        self._tb.flush()
+
+    def start_run(self, run_name=None, params=None):
+        import socket
+        rid = super().start_run(run_name, None)
+        name = f"events.out.tfevents.{int(time.time())}.{socket.gethostname()}.{os.getpid()}.0"
+        self._tb = open(os.path.join(self.run_dir, name), "ab")
+        self._write_event(self._event(time.time(), 0, file_version="brain.Event:2"))
+        if params:
+            self.log_params(params)
+        return rid
+
+    def log_params(self, params: dict):
+        super().log_params(params)
+        rows = "".join(f"| {k} | {v} |\n" for k, v in sorted(params.items()))
+        text = ("| parameter | value |\n|---|---|\n" + rows).encode()
+        # TensorProto{dtype=DT_STRING(7), tensor_shape{dim{size=1}}, string_val=[text]}; metadata names the text plugin
+        tensor = self._field(1, 0, self._varint(7)) + self._field(2, 2, self._field(2, 2, self._field(1, 0, self._varint(1)))) \
+            + self._field(8, 2, text)
+        meta = self._field(1, 2, self._field(1, 2, b"text"))
+        value = self._field(1, 2, b"parameters/text_summary") + self._field(9, 2, meta) + self._field(8, 2, tensor)
+        self._write_event(self._event(time.time(), 0, summary=self._field(1, 2, value)))
+
+    def log_metrics(self, metrics, step=None):
+        import struct
+        super().log_metrics(metrics, step)
+        values = b"".join(self._field(1, 2, self._field(1, 2, str(k).encode()) + self._field(2, 5, struct.pack("<f", float(v))))
+                          for k, v in metrics.items())
+        self._write_event(self._event(time.time(), int(step or 0), summary=values))
+
+    def log_histogram(self, tag: str, values, step: int = 0, bins: int = 30):
+        """A histogram of ``values`` (tensor, array or list) under ``tag``."""
+        import struct
+        import numpy as np
+        v = np.asarray(values.detach().float().cpu().numpy() if hasattr(values, "detach") else values, dtype=np.float64).ravel()
+        if v.size == 0:
+            return
+        counts, edges = np.histogram(v, bins=bins)
+        packed = lambda arr: struct.pack(f"<{len(arr)}d", *[float(x) for x in arr])
+        histo = b"".join(self._field(i, 1, struct.pack("<d", x)) for i, x in
+                         ((1, v.min()), (2, v.max()), (3, float(v.size)), (4, v.sum()), (5, float((v * v).sum())))) \
+            + self._field(6, 2, packed(edges[1:])) + self._field(7, 2, packed(counts))
+        value = self._field(1, 2, tag.encode()) + self._field(5, 2, histo)
+        self._write_event(self._event(time.time(), int(step), summary=self._field(1, 2, value)))
+
+    def end_run(self):
+        super().end_run()
+        if getattr(self, "_tb", None):
+            self._tb.close()
+            self._tb = None
+
+
 class CompositeTracker:
     def __init__(self, trackers):
         self.trackers = list(trackers)
@@ -323,7 +434,8 @@ class CompositeTracker:
 
 
 def make_tracker(kind="local", **kw):
-    return {"local": ExperimentTracker, "wandb": WandbTracker, "mlflow": MLflowTracker}.get(kind, ExperimentTracker)(**kw)
+    return {"local": ExperimentTracker, "wandb": WandbTracker, "mlflow": MLflowTracker,
+            "tensorboard": TensorBoardTracker}.get(kind, ExperimentTracker)(**kw)
 
 
 

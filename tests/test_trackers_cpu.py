@@ -2,6 +2,8 @@
 import json
 import os
 
+import pytest
+
 from sneppx_alg_b200.utils.observability import CompositeTracker, MLflowTracker, WandbTracker, make_tracker
 
 
@@ -55,3 +57,41 @@ def test_wandb_offline_layout_and_composite(tmp_path):
     assert "wandb_version: 1" in cfg and "bs:\n  desc: null\n  value: 8" in cfg
     assert os.path.basename(os.path.dirname(files)).startswith("offline-run-")
     assert os.path.exists(os.path.join(str(tmp_path / "m"), "mlruns", "0"))
+
+
+def test_tensorboard_event_files(tmp_path):
+    """Event files written by hand: framing and checksums re-read here, content re-read by TensorBoard's own loader
+    where that package is importable."""
+    import glob
+    import struct
+
+    import numpy as np
+
+    from sneppx_alg_b200.utils.observability import TensorBoardTracker, make_tracker
+    assert TensorBoardTracker._crc32c(b"123456789") == 0xE3069283            # the CRC-32C check value
+    t = make_tracker("tensorboard", directory=str(tmp_path))
+    assert isinstance(t, TensorBoardTracker)
+    t.start_run("r1", {"lr": 3e-4, "model": "tiny"})
+    for i in range(5):
+        t.log_metrics({"loss": 1.0 / (i + 1), "lr": 1e-3}, step=i)
+    t.log_histogram("weights", np.linspace(-1, 1, 1000), step=4)
+    t.end_run()
+    files = glob.glob(str(tmp_path / "default" / "r1" / "events.out.tfevents.*"))
+    assert len(files) == 1 and (tmp_path / "default" / "r1" / "metrics.jsonl").exists()
+    raw, pos, records = open(files[0], "rb").read(), 0, []
+    while pos < len(raw):
+        (n,) = struct.unpack("<Q", raw[pos:pos + 8])
+        assert struct.unpack("<I", raw[pos + 8:pos + 12])[0] == TensorBoardTracker._masked_crc(raw[pos:pos + 8])
+        body = raw[pos + 12:pos + 12 + n]
+        assert struct.unpack("<I", raw[pos + 12 + n:pos + 16 + n])[0] == TensorBoardTracker._masked_crc(body)
+        records.append(body)
+        pos += 16 + n
+    assert len(records) == 8 and b"brain.Event:2" in records[0] and b"| lr | 0.0003 |" in records[1]
+    ea = pytest.importorskip("tensorboard.backend.event_processing.event_accumulator")
+    acc = ea.EventAccumulator(str(tmp_path / "default" / "r1"))
+    acc.Reload()
+    tags = acc.Tags()
+    assert tags["scalars"] == ["loss", "lr"] and tags["histograms"] == ["weights"] and tags["tensors"] == ["parameters/text_summary"]
+    assert [(s.step, round(s.value, 4)) for s in acc.Scalars("loss")] == [(0, 1.0), (1, 0.5), (2, 0.3333), (3, 0.25), (4, 0.2)]
+    h = acc.Histograms("weights")[0].histogram_value
+    assert h.num == 1000 and abs(h.min + 1) < 1e-9 and abs(h.max - 1) < 1e-9 and sum(h.bucket) == 1000
