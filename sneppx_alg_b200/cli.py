@@ -505,6 +505,16 @@ def tools_main(argv=None):
     kg = sub.add_parser("keygen", help="signing key pair (ed25519 or post-quantum ml-dsa-65) written as <prefix>.pub / <prefix>.key")
     kg.add_argument("prefix")
     kg.add_argument("--scheme", default="ml-dsa-65", choices=["ed25519", "ml-dsa-65", "slh-dsa-128f"])
+    ce = sub.add_parser("cert", help="X.509 certificate (DER, or PEM for a .pem target) for an ed25519 key made by keygen: "
+                        "self-signed, or issued by --issuer-key / --issuer-name; for security.tls13 and OpenSSL alike")
+    ce.add_argument("key", help="the subject's ed25519 private key file (32 bytes)")
+    ce.add_argument("subject", help="common name")
+    ce.add_argument("out")
+    ce.add_argument("--dns", action="append", default=[], help="DNS name the certificate covers (repeatable)")
+    ce.add_argument("--ca", action="store_true", help="mark as a certificate authority")
+    ce.add_argument("--issuer-key", default=None)
+    ce.add_argument("--issuer-name", default=None)
+    ce.add_argument("--days", type=float, default=365.0)
     sg = sub.add_parser("sign", help="signed manifest for a file (update package, weight file)")
     sg.add_argument("file")
     sg.add_argument("key")
@@ -599,6 +609,26 @@ def tools_main(argv=None):
         with os.fdopen(fd, "wb") as f:
             f.write(key)
         print(json.dumps({"scheme": a.scheme, "public": a.prefix + ".pub", "private": a.prefix + ".key", "public_bytes": len(pub)}))
+    elif a.cmd == "cert":
+        import base64
+        from .security import tls13
+        seed = open(a.key, "rb").read()
+        if len(seed) != 32:
+            ap.error("certificates are issued for ed25519 keys (a 32-byte private key file)")
+        if bool(a.issuer_key) != bool(a.issuer_name):
+            ap.error("--issuer-key and --issuer-name go together")
+        der = tls13.make_certificate(seed, a.subject, issuer_seed=open(a.issuer_key, "rb").read() if a.issuer_key else None,
+                                     issuer=a.issuer_name, days=a.days, dns_names=a.dns, ca=a.ca)
+        with open(a.out, "wb") as f:
+            if a.out.endswith(".pem"):
+                body = base64.encodebytes(der).decode().replace("\n", "")
+                f.write(("-----BEGIN CERTIFICATE-----\n" + "\n".join(body[i:i + 64] for i in range(0, len(body), 64))
+                         + "\n-----END CERTIFICATE-----\n").encode())
+            else:
+                f.write(der)
+        info = tls13.parse_certificate(der)
+        print(json.dumps({"subject": info["subject"], "issuer": info["issuer"], "dns_names": info["dns_names"], "ca": info["ca"],
+                          "not_after": time.strftime("%Y-%m-%d", time.gmtime(info["not_after"])), "out": a.out}))
     elif a.cmd == "sign":
         from .security.services import sign_update
         manifest = sign_update(a.file, open(a.key, "rb").read(), a.version, scheme=a.scheme)

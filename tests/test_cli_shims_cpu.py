@@ -130,3 +130,32 @@ def test_tools_card_keygen_sign_verify(tmp_path, capsys):
         assert tools_main(["verify", str(pkg), manifest, other + ".pub"]) == 1
     pkg.write_bytes(b"changed")
     assert tools_main(["verify", str(pkg), str(pkg) + ".manifest.json", str(tmp_path / "ed25519.pub")]) == 1
+
+
+def test_tools_cert_issues_chains_that_tls_and_openssl_accept(tmp_path, capsys):
+    import shutil
+    import subprocess
+    from sneppx_alg_b200.cli import tools_main
+    from sneppx_alg_b200.security import tls13
+    root, node = str(tmp_path / "root"), str(tmp_path / "node")
+    for prefix in (root, node):
+        assert tools_main(["keygen", prefix, "--scheme", "ed25519"]) == 0
+    assert tools_main(["cert", root + ".key", "cluster root", root + ".pem", "--ca"]) == 0
+    assert tools_main(["cert", node + ".key", "node0", node + ".der", "--dns", "node0.svc", "--dns", "*.pods.svc",
+                       "--issuer-key", root + ".key", "--issuer-name", "cluster root", "--days", "30"]) == 0
+    assert tools_main(["cert", node + ".key", "node0", node + ".pem", "--dns", "node0.svc",
+                       "--issuer-key", root + ".key", "--issuer-name", "cluster root"]) == 0
+    out = [json.loads(line) for line in capsys.readouterr().out.splitlines() if line.startswith('{"subject"')]
+    assert out[0]["ca"] and out[1]["issuer"] == "cluster root" and out[1]["dns_names"] == ["node0.svc", "*.pods.svc"]
+    pem = open(root + ".pem").read()
+    assert pem.startswith("-----BEGIN CERTIFICATE-----\n") and all(len(l) <= 64 for l in pem.splitlines()[1:-1])
+    import base64
+    root_der = base64.b64decode("".join(pem.splitlines()[1:-1]))
+    leaf_der = open(node + ".der", "rb").read()
+    assert tls13.verify_chain([leaf_der], [root_der], "a.pods.svc") == open(node + ".pub", "rb").read()
+    if shutil.which("openssl"):
+        r = subprocess.run(["openssl", "verify", "-CAfile", root + ".pem", "-verify_hostname", "node0.svc", node + ".pem"],
+                           capture_output=True, text=True)
+        assert r.returncode == 0, r.stderr
+    with pytest.raises(SystemExit):
+        tools_main(["cert", node + ".key", "x", str(tmp_path / "x.der"), "--issuer-key", root + ".key"])
