@@ -145,6 +145,13 @@ def make_certificate(subject_seed: bytes, subject: str, issuer_seed: Optional[by
 def parse_certificate(der: bytes) -> dict:
     """The fields chain validation needs: the signed bytes, signature and its algorithm, names, validity, the subject's
     key and its algorithm, DNS names, the CA flag."""
+    try:
+        return _parse_certificate(der)
+    except (IndexError, UnicodeDecodeError, TypeError):
+        raise ValueError("not a certificate") from None
+
+
+def _parse_certificate(der: bytes) -> dict:
     tag, cert, _, end = _der_read(der, 0)
     if tag != 0x30 or end != len(der):
         raise ValueError("not a certificate")
@@ -197,7 +204,10 @@ def verify_chain(chain: Sequence[bytes], trusted_roots: Iterable[bytes], hostnam
     window and CA flag, and the leaf's DNS names (or common name) against ``hostname``. Returns the leaf's public key."""
     now = time.time() if now is None else now
     roots = [parse_certificate(r) for r in trusted_roots]
-    certs = [parse_certificate(c) for c in chain]
+    try:
+        certs = [parse_certificate(c) for c in chain]
+    except ValueError as e:
+        raise TlsError(f"unreadable certificate in the chain: {e}", ALERT_BAD_CERTIFICATE) from None
     if not certs:
         raise TlsError("empty certificate chain", ALERT_BAD_CERTIFICATE)
     for c in certs:

@@ -322,8 +322,15 @@ def build_long_header(packet_type: int, dcid: bytes, scid: bytes, pn: bytes, pay
 def parse_long_header(packet: bytes) -> dict:
     """The unprotected part of a long header: type, version, connection ids, token, and where the packet-number field
     and the end of this packet are (several packets may share a datagram)."""
-    if not packet[0] & 0x80:
+    if not packet or not packet[0] & 0x80:
         raise ValueError("not a long header")
+    try:
+        return _parse_long_header(packet)
+    except (IndexError, struct.error):
+        raise ValueError("truncated long header") from None
+
+
+def _parse_long_header(packet: bytes) -> dict:
     ptype = (packet[0] >> 4) & 3
     version = struct.unpack(">I", packet[1:5])[0]
     pos = 5

@@ -149,7 +149,10 @@ class QuicTlsConnection:
                parameters: Optional[Dict[int, object]] = None) -> "QuicTlsConnection":
         """Server side, from the first datagram of a new client. ``make_tls(encoded transport parameters)`` returns the
         ``tls13.TlsServer`` for this connection (certificate or PSK, ALPN list, ticket store)."""
-        info = qp.parse_long_header(first_datagram)
+        try:
+            info = qp.parse_long_header(first_datagram)
+        except ValueError as e:
+            raise QuicTlsError(f"not a QUIC Initial packet: {e}") from None
         if info["version"] != 1 or info["type"] != qp.LONG_INITIAL:
             raise QuicTlsError("a connection starts with a version 1 Initial packet")
         if len(first_datagram) < MIN_INITIAL_DATAGRAM:
@@ -316,7 +319,7 @@ class QuicTlsConnection:
             if rest[0] & 0x80:
                 try:
                     info = qp.parse_long_header(rest)
-                except (IndexError, ValueError):
+                except ValueError:
                     return
                 if info["version"] != 1 or info["pn_offset"] is None or info["end"] > len(rest) or info["dcid"] not in self._accepted_dcids():
                     return

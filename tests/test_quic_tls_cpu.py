@@ -171,3 +171,60 @@ def test_over_udp_sockets(pki):
     finally:
         srv_sock.close()
         cli_sock.close()
+
+
+def test_damaged_input_fails_cleanly(pki):
+    """Random damage to the first flights, to certificates and to frames ends in the modules' own error types (or is
+    dropped), never in an IndexError or a struct error."""
+    import random
+    rng = random.Random(7)
+    seed, cert = pki
+
+    def mutate(d):
+        d = bytearray(d)
+        for _ in range(rng.randint(1, 4)):
+            k = rng.random()
+            if k < 0.5 and d:
+                d[rng.randrange(len(d))] = rng.randrange(256)
+            elif k < 0.7 and d:
+                del d[rng.randrange(len(d)):]
+            else:
+                d += os.urandom(rng.randint(1, 40))
+        return bytes(d)
+    make = lambda tp: tls13.TlsServer([cert], seed, alpn=["sx/1"], quic_transport_parameters=tp)
+    for it in range(120):
+        c = qt.QuicTlsConnection.client(["sx/1"], server_name="node0.cluster", trusted_roots=[cert])
+        first = c.datagrams_to_send()[0]
+        try:
+            if it % 2:
+                qt.QuicTlsConnection.accept(mutate(first), make)
+            else:
+                s = qt.QuicTlsConnection.accept(first, make)
+                for d in s.datagrams_to_send():
+                    c.receive_datagram(mutate(d))
+        except (qt.QuicTlsError, tls13.TlsError):
+            pass
+    for _ in range(2000):
+        try:
+            tls13.parse_certificate(mutate(cert))
+        except ValueError:
+            pass
+    for it in range(200):
+        c, s = tls13.TlsClient("node0.cluster", trusted_roots=[cert]), tls13.TlsServer([cert], seed, psk_lookup=lambda i: b"k" * 32)
+        c.start()
+        hello = c.data_to_send()
+        try:
+            if it % 2:
+                s.receive(mutate(hello))
+            else:
+                s.receive(hello)
+                c.receive(mutate(s.data_to_send()))
+        except tls13.TlsError:
+            pass
+    # an authenticated peer that sends a malformed frame gets a FRAME_ENCODING_ERROR close
+    c, s = make_pair(pki)
+    exchange(c, s)
+    c.spaces["application"].queue.append(bytes([0x06, 0x00, 0x40]))          # CRYPTO frame cut off in its length
+    with pytest.raises(qt.QuicTlsError) as e:
+        exchange(c, s)
+    assert e.value.code == 0x07 and s.closed[0] == 0x07
