@@ -10,7 +10,7 @@ of ``datagrams_to_send``. It covers
 * connection ids: keys for the Initial level from the client's first destination id, the switch to the server's chosen
   id, and authentication of all of them through the transport parameters (original_destination_connection_id,
   initial_source_connection_id), which ride in the TLS extension 57;
-* HANDSHAKE_DONE and the discarding of Initial and Handshake keys (RFC 9001 section 4.9);
+* HANDSHAKE_DONE and the discarding of Initial and Handshake keys (RFC 9001 section 4.9), 1-RTT key updates;
 * STREAM frames with offsets and FIN once the handshake is complete, CONNECTION_CLOSE, and re-queuing of
   unacknowledged frames on ``on_timeout`` (frames are retransmitted in new packets, never packets).
 
@@ -300,6 +300,13 @@ class QuicTlsConnection:
                                                     + qp._varint(len(chunk)) + chunk)
             off += len(chunk)
         self._stream_send_offset[stream_id] = off
+
+    def update_keys(self) -> None:
+        """Move to the next generation of 1-RTT keys (RFC 9001 section 6); the peer follows when it sees the flipped
+        key-phase bit. Allowed once the handshake is confirmed."""
+        if not self.handshake_confirmed:
+            raise QuicTlsError("a key update needs a confirmed handshake")
+        self.spaces["application"].protector.initiate_key_update()
 
     def close(self, code: int = 0, reason: str = "") -> None:
         if self.closed is None:

@@ -69,6 +69,13 @@ def test_handshake_streams_and_key_discard(pki):
     exchange(c, s)
     assert bytes(s.streams[0]) == blob and 0 in s.finished_streams and bytes(c.streams[3]) == b"server push"
     assert not c.spaces["application"].in_flight and not s.spaces["application"].in_flight       # all acknowledged
+    c.update_keys()                                                             # the key-phase bit flips; the server follows
+    c.send_stream(8, b"under new keys", fin=True)
+    exchange(c, s)
+    assert bytes(s.streams[8]) == b"under new keys" and s.spaces["application"].protector.key_phase == 1
+    s.send_stream(11, b"and back")
+    exchange(c, s)
+    assert bytes(c.streams[11]) == b"and back" and not s.spaces["application"].in_flight
     c.close(0, "done")
     exchange(c, s)
     assert s.closed == (0, "done")
